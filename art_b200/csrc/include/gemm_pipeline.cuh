@@ -1,0 +1,223 @@
+// Warp-specialised, persistent tcgen05 GEMM pipeline for sm_100a.
+//
+//   D[128 x BN] (fp32, TMEM) = A[128 x K] * B[BN x K]^T      (both operands K-major bf16)
+//
+// One CTA = 6 warps:
+//   warp 0      TMA producer  (one elected lane issues cp.async.bulk.tensor loads)
+//   warp 1      MMA issuer    (one elected lane issues tcgen05.mma; the warp owns TMEM alloc/dealloc)
+//   warps 2..5  epilogue      (each reads its 32-lane quarter of TMEM with tcgen05.ld)
+//
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of
+// tile i overlaps the main loop of tile i+1.  Operand stages live in shared
+// memory in the 128-byte-swizzled layout that TMA writes and UMMA reads.
+//
+// An optional second operand pair (A2, B2) is appended along K ("extra-K"): the
+// low-rank LoRA update  T[M x r] * (s*Bl)[N x r]^T  is accumulated by the tensor
+// cores into the same TMEM tile as the frozen-weight product, at the cost of one
+// extra 64-wide K block.
+//
+// Scheduling (which tiles a CTA visits, in which order) and the epilogue (what
+// happens to each 32-column slab of the accumulator) are template policies, so
+// the plain GEMM, the residual/SwiGLU variants and the fused LM-head log-prob
+// kernel share this file.
+#pragma once
+#include "ptx_sm100.cuh"
+
+namespace artb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+struct TileInfo {
+  int m_blk;   // tile row index   (rows m_blk*128 ..)
+  int n_blk;   // tile column index (cols n_blk*BN ..)
+  int first;   // first tile of an epilogue group (policy-defined)
+  int last;    // last tile of an epilogue group
+  int group;   // policy-defined group id (e.g. vocabulary split)
+};
+
+template <int BN, int STAGES>
+struct GemmSmemLayout {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES] empty[STAGES] tmem_full[2] tmem_empty[2] | tmem_base | abort
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = BAR_OFFSET + BAR_BYTES + 1024;  // + alignment slack
+};
+
+template <int BN, int STAGES, class Sched, class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA2,
+                    const __grid_constant__ CUtensorMap tmB2, int kb_main, int kb_extra,
+                    Sched sched, Epi epi_in, int* status) {
+  using L = GemmSmemLayout<BN, STAGES>;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+  static_assert(BN % 32 == 0 && BN <= 256, "BN");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kb_total = kb_main + kb_extra;
+  const int my_tiles = sched.tiles_for_cta(blockIdx.x, gridDim.x);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if (kb_extra > 0) {
+        tma_prefetch_desc(&tmA2);
+        tma_prefetch_desc(&tmB2);
+      }
+      uint32_t it = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicMax(status, ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            break;
+          }
+          if (*abort_flag) break;
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          if (kb < kb_main) {
+            tma_load_2d(sa, &tmA, kb * GEMM_BK, ti.m_blk * GEMM_BM, &full_bar[s]);
+            tma_load_2d(sb, &tmB, kb * GEMM_BK, ti.n_blk * BN, &full_bar[s]);
+          } else {
+            const int k2 = (kb - kb_main) * GEMM_BK;
+            tma_load_2d(sa, &tmA2, k2, ti.m_blk * GEMM_BM, &full_bar[s]);
+            tma_load_2d(sb, &tmB2, k2, ti.n_blk * BN, &full_bar[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, BN);
+      uint32_t it = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        const int buf = t & 1;
+        const uint32_t aph = (t >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[buf], aph ^ 1)) {
+          atomicMax(status, ST_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicMax(status, ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+          const uint64_t adesc = umma_smem_desc_k128(sa);
+          const uint64_t bdesc = umma_smem_desc_k128(sb);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // advance 16 bf16 = 32 B along K inside the swizzled row: +2 in 16-byte units
+            tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty_bar[s]);  // stage reusable once these MMAs retire
+        }
+        if (*abort_flag) break;
+        tc_commit(&tfull_bar[buf]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    Epi epi = epi_in;
+    const int q = warp & 3;  // TMEM lane quarter this warp may touch
+    const int row = q * 32 + lane;
+    for (int t = 0; t < my_tiles; ++t) {
+      // Abort decisions are made warp-uniform: the TMEM loads below are .sync.aligned.
+      if (__shfl_sync(0xffffffffu, *abort_flag, 0)) break;
+      const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
+      const int buf = t & 1;
+      const uint32_t aph = (t >> 1) & 1;
+      const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) {
+          atomicMax(status, ST_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after_sync();
+      epi.tile_begin(ti, row);
+      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c, acc);
+        tmem_ld_wait();
+        epi.chunk(ti, row, c, acc);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      epi.tile_end(ti, row);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give any copy that is still in flight time to land before smem is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace artb

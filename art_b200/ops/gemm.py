@@ -1,0 +1,93 @@
+"""tcgen05 GEMM front-end: ``C = A @ B.T (+ A2 @ B2.T)`` with fused epilogues.
+
+The kernel lives in ``csrc/kernels/gemm_tcgen05.cu``; this module validates
+shapes/strides and passes raw pointers.  ``reference_gemm_tn`` is the fp32
+PyTorch restatement used by the tests.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+EPI_BF16, EPI_BF16_RESID, EPI_F32, EPI_SWIGLU = 0, 1, 2, 3
+_configured = False
+
+
+def _fn():
+    global _configured
+    f = _lib.kernels().artb_gemm_bf16_tn
+    if not _configured:
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, ci, vp]
+        f.restype = ci
+        _configured = True
+    return f
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(1) != 1:
+        raise ValueError(f"{name}: expected a 2-D bf16 CUDA tensor with unit inner stride, got "
+                         f"{tuple(t.shape)} {t.dtype} strides {t.stride()}")
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
+            b2: torch.Tensor | None = None, out: torch.Tensor | None = None,
+            residual: torch.Tensor | None = None, swiglu_out: torch.Tensor | None = None,
+            out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ b[N,K].T (+ a2[M,K2] @ b2[N,K2].T) (+ residual)``.
+
+    ``swiglu_out`` ([M, N/2] bf16) selects the SwiGLU epilogue: ``b``'s rows must be
+    interleaved in blocks of 16 (gate rows, then the matching up rows); ``out`` receives
+    the pre-activation and ``swiglu_out`` receives ``silu(gate) * up``.
+    """
+    _check2d(a, "a")
+    _check2d(b, "b")
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"K mismatch: {K} vs {Kb}")
+    K2 = 0
+    if a2 is not None:
+        _check2d(a2, "a2")
+        _check2d(b2, "b2")
+        K2 = a2.shape[1]
+        if a2.shape[0] != M or b2.shape[0] != N or b2.shape[1] != K2:
+            raise ValueError("extra-K operands must be [M,K2] and [N,K2]")
+    if swiglu_out is not None:
+        epi = EPI_SWIGLU
+    elif residual is not None:
+        epi = EPI_BF16_RESID
+    elif out_dtype == torch.float32:
+        epi = EPI_F32
+    else:
+        epi = EPI_BF16
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
+    if out.stride(1) != 1 or tuple(out.shape) != (M, N):
+        raise ValueError("out must be [M,N] with unit inner stride")
+    if residual is not None:
+        _check2d(residual, "residual")
+    st = _lib.status_word(a.device)
+    rc = _fn()(
+        _lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0),
+        _lib.ptr(a2), a2.stride(0) if a2 is not None else 0,
+        _lib.ptr(b2), b2.stride(0) if b2 is not None else 0, K2,
+        _lib.ptr(out), out.stride(0),
+        _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+        _lib.ptr(swiglu_out), swiglu_out.stride(0) if swiglu_out is not None else 0,
+        M, N, K, epi, bn, _lib.ptr(st), max_ctas, _lib.stream_ptr())
+    _lib.check_rc(rc, "gemm_tn")
+    return out
+
+
+def reference_gemm_tn(a, b, a2=None, b2=None, residual=None) -> torch.Tensor:
+    """fp32 PyTorch restatement (inputs upcast, fp32 accumulation)."""
+    c = a.float() @ b.float().t()
+    if a2 is not None:
+        c = c + a2.float() @ b2.float().t()
+    if residual is not None:
+        c = c + residual.float()
+    return c
