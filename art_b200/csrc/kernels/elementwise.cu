@@ -1,0 +1,430 @@
+// Memory-bound layer ops of the decoder, each a single pass over its operands:
+// RMSNorm forward / backward (with fused residual-gradient add), rotary embedding
+// (forward and inverse, in place on the fused QKV buffer, positions taken from the
+// packed `input_pos`), SwiGLU backward on the gate|up-interleaved layout written by
+// the GEMM epilogue, per-head q/k RMSNorm (Qwen3), embedding gather / scatter-free
+// row gather, and GRPO advantage normalisation.
+//
+// These replace the Triton kernels the reference reaches through Unsloth
+// (src/art/local/train.py:239-241 model forward; advantage arithmetic is
+// src/art/local/tokenize.py:48-59).  All are bandwidth-bound: 16-byte vector
+// accesses, fp32 math, one read and one write per element.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "host_utils.h"
+
+namespace artb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  bf16x8 r = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(r.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  bf16x8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = r;
+}
+
+// ------------------------------------------------------------------- RMSNorm
+// One 128-thread CTA per row; the row is kept in registers between the reduction and
+// the scale (MAX_VEC 8-element vectors per thread).
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const float t = red[0] + red[1] + red[2] + red[3];
+  __syncthreads();
+  return t;
+}
+
+template <int MAX_VEC>
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int M, int D, float eps) {
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  const int nvec = D >> 3;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * D;
+  float vals[MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * 128;
+    if (v < nvec) {
+      load8(xr + v * 8, vals[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  ss = block_sum_128(ss, red);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * D;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * 128;
+    if (v < nvec) {
+      float wv[8], o[8];
+      load8(w + v * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // match the library formulation: normalise in fp32, round to bf16, then scale
+        o[j] = __bfloat162float(__float2bfloat16(vals[i][j] * r)) * wv[j];
+      }
+      store8(yr + v * 8, o);
+    }
+  }
+}
+
+// dx = rstd * g - x * rstd^3 * mean(g * x),  g = dy * w ;  out = dx (+ dres)
+template <int MAX_VEC>
+__global__ void __launch_bounds__(128)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int M, int D) {
+  __shared__ float red[4];
+  const int row = blockIdx.x;
+  const int nvec = D >> 3;
+  const size_t off = static_cast<size_t>(row) * D;
+  float g[MAX_VEC][8], xv[MAX_VEC][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * 128;
+    if (v < nvec) {
+      float wv[8];
+      load8(dy + off + v * 8, g[i]);
+      load8(x + off + v * 8, xv[i]);
+      load8(w + v * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        g[i][j] *= wv[j];
+        dot += g[i][j] * xv[i][j];
+      }
+    }
+  }
+  dot = block_sum_128(dot, red);
+  const float r = rstd[row];
+  const float c = dot * r * r * r / D;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * 128;
+    if (v < nvec) {
+      float o[8];
+      if (dres) load8(dres + off + v * 8, o);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += r * g[i][j] - xv[i][j] * c;
+      store8(dx + off + v * 8, o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------- RoPE
+// In place on rows of a [M, ld] buffer that holds `heads` heads of `hd` starting at
+// column `col0`.  Rotate-half convention: pair (i, i + hd/2).  sign = +1 forward, -1 inverse.
+// Optional per-head RMSNorm weight (Qwen3 q_norm / k_norm) applied before the rotation
+// is handled by headnorm_* below; here only the rotation.
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ pos, int M, int ld,
+                            int col0, int heads, int hd, float log2_theta, float sign) {
+  const int half = hd >> 1;
+  const int vec_per_head = half >> 3;  // 8 pairs per thread
+  const long total = static_cast<long>(M) * heads * vec_per_head;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int vv = idx % vec_per_head;
+    const int h = (idx / vec_per_head) % heads;
+    const int m = idx / (static_cast<long>(vec_per_head) * heads);
+    __nv_bfloat16* p = buf + static_cast<size_t>(m) * ld + col0 + h * hd + vv * 8;
+    float a[8], b[8];
+    load8(p, a);
+    load8(p + half, b);
+    const float fp = static_cast<float>(pos[m]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = vv * 8 + j;
+      const float inv_freq = exp2f(-log2_theta * (2.f * i) / hd);
+      float s, c;
+      sincosf(fp * inv_freq, &s, &c);
+      s *= sign;
+      const float x1 = a[j], x2 = b[j];
+      a[j] = x1 * c - x2 * s;
+      b[j] = x2 * c + x1 * s;
+    }
+    store8(p, a);
+    store8(p + half, b);
+  }
+}
+
+// ------------------------------------------------------------ SwiGLU backward
+// gu / dgu are [M, 2F] with columns interleaved in blocks of 16: [gate 16 | up 16].
+// dgate = dh * up * s * (1 + gate * (1 - s)),  dup = dh * gate * s,  s = sigmoid(gate)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, long M, int F) {
+  const int blocks = F >> 4;  // 16-wide blocks per row
+  const long total = M * blocks * 2;  // each thread: 8 elements of one block
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int part = idx & 1;
+    const long blk = idx >> 1;
+    const long m = blk / blocks;
+    const int b = blk % blocks;
+    const size_t gu_off = static_cast<size_t>(m) * 2 * F + b * 32 + part * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + gu_off, g);
+    load8(gu + gu_off + 16, u);
+    load8(dh + static_cast<size_t>(m) * F + b * 16 + part * 8, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-g[j]));
+      dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+      du[j] = d[j] * g[j] * s;
+    }
+    store8(dgu + gu_off, dg);
+    store8(dgu + gu_off + 16, du);
+  }
+}
+
+// SwiGLU forward on the interleaved layout (used when the GEMM epilogue fusion is off).
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h, long M,
+                                  int F) {
+  const int blocks = F >> 4;
+  const long total = M * blocks * 2;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int part = idx & 1;
+    const long blk = idx >> 1;
+    const long m = blk / blocks;
+    const int b = blk % blocks;
+    const size_t gu_off = static_cast<size_t>(m) * 2 * F + b * 32 + part * 8;
+    float g[8], u[8], o[8];
+    load8(gu + gu_off, g);
+    load8(gu + gu_off + 16, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(h + static_cast<size_t>(m) * F + b * 16 + part * 8, o);
+  }
+}
+
+// -------------------------------------------------- per-head RMSNorm (Qwen3 qk-norm)
+// One warp per (token, head); hd <= 256.  In place; saves rstd per (token, head).
+__global__ void headnorm_fwd_kernel(__nv_bfloat16* __restrict__ buf, const __nv_bfloat16* __restrict__ w,
+                                    float* __restrict__ rstd, int M, int ld, int col0, int heads, int hd,
+                                    float eps) {
+  const long wid = blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long>(M) * heads) return;
+  const int m = wid / heads, h = wid % heads;
+  __nv_bfloat16* p = buf + static_cast<size_t>(m) * ld + col0 + h * hd;
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) {
+    const float v = __bfloat162float(p[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / hd + eps);
+  if (lane == 0 && rstd) rstd[wid] = r;
+  for (int i = lane; i < hd; i += 32)
+    p[i] = __float2bfloat16(__bfloat162float(__float2bfloat16(__bfloat162float(p[i]) * r)) *
+                            __bfloat162float(w[i]));
+}
+// Backward of the per-head norm given the saved pre-norm input x (same layout) and rstd.
+__global__ void headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dbuf, const __nv_bfloat16* __restrict__ xbuf,
+                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd, int M,
+                                    int ld, int col0, int heads, int hd) {
+  const long wid = blockIdx.x * static_cast<long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long>(M) * heads) return;
+  const int m = wid / heads, h = wid % heads;
+  const size_t off = static_cast<size_t>(m) * ld + col0 + h * hd;
+  float dot = 0.f;
+  for (int i = lane; i < hd; i += 32)
+    dot += __bfloat162float(dbuf[off + i]) * __bfloat162float(w[i]) * __bfloat162float(xbuf[off + i]);
+  dot = warp_sum(dot);
+  const float r = rstd[wid];
+  const float c = dot * r * r * r / hd;
+  for (int i = lane; i < hd; i += 32) {
+    const float g = __bfloat162float(dbuf[off + i]) * __bfloat162float(w[i]);
+    dbuf[off + i] = __float2bfloat16(r * g - __bfloat162float(xbuf[off + i]) * c);
+  }
+}
+
+// ------------------------------------------------------------- row gather/scatter
+// out[i, :] = table[idx[i], :]   (embedding lookup, hidden-row compaction); D % 8 == 0.
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ out, long n, int D, long table_rows) {
+  const int nvec = D >> 3;
+  const long total = n * nvec;
+  for (long t = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = t / nvec;
+    const int v = t % nvec;
+    long src = idx[r];
+    bf16x8 val;
+    if (src < 0 || src >= table_rows) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) val.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+    } else {
+      val = *reinterpret_cast<const bf16x8*>(table + src * D + v * 8);
+    }
+    *reinterpret_cast<bf16x8*>(out + r * D + v * 8) = val;
+  }
+}
+// out[idx[i], :] = src[i, :]  (idx unique); rows not named by idx are left untouched.
+__global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const int64_t* __restrict__ idx,
+                                    __nv_bfloat16* __restrict__ out, long n, int D, long out_rows) {
+  const int nvec = D >> 3;
+  const long total = n * nvec;
+  for (long t = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long r = t / nvec;
+    const int v = t % nvec;
+    const long dst = idx[r];
+    if (dst < 0 || dst >= out_rows) continue;
+    *reinterpret_cast<bf16x8*>(out + dst * D + v * 8) =
+        *reinterpret_cast<const bf16x8*>(src + r * D + v * 8);
+  }
+}
+
+// --------------------------------------------------- GRPO advantage normalisation
+// rewards are grouped CSR-style: group g owns rewards[offsets[g] .. offsets[g+1]).
+// adv = (r - mean) / (population_std + 1e-6); keep[i] = adv != 0.  One warp per group.
+__global__ void adv_norm_kernel(const float* __restrict__ rewards, const int* __restrict__ offsets,
+                                float* __restrict__ adv, uint8_t* __restrict__ keep, int num_groups) {
+  const int g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (g >= num_groups) return;
+  const int b = offsets[g], e = offsets[g + 1];
+  const int n = e - b;
+  if (n <= 0) return;
+  float s = 0.f;
+  for (int i = b + lane; i < e; i += 32) s += rewards[i];
+  const float mean = warp_sum(s) / n;
+  float ss = 0.f;
+  for (int i = b + lane; i < e; i += 32) {
+    const float d = rewards[i] - mean;
+    ss += d * d;
+  }
+  const float sd = sqrtf(warp_sum(ss) / n);
+  for (int i = b + lane; i < e; i += 32) {
+    const float a = (rewards[i] - mean) / (sd + 1e-6f);
+    adv[i] = a;
+    if (keep) keep[i] = a != 0.f;
+  }
+}
+
+static inline int grid_for(long total, int threads, int cap_mult = 32) {
+  long g = (total + threads - 1) / threads;
+  long cap = static_cast<long>(sm_count()) * cap_mult;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace artb
+
+using namespace artb;
+typedef __nv_bfloat16 bf16;
+
+ARTB_EXPORT int artb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int M, int D, float eps,
+                                 cudaStream_t st) {
+  if (D % 8 || D > 128 * 8 * 16) return ERR_BAD_SHAPE;
+  if (M <= 0) return 0;
+  const int per = (D / 8 + 127) / 128;
+#define ARTB_RN(V) rmsnorm_fwd_kernel<V><<<M, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, M, D, eps)
+  if (per <= 2) ARTB_RN(2); else if (per <= 4) ARTB_RN(4); else if (per <= 8) ARTB_RN(8); else ARTB_RN(16);
+#undef ARTB_RN
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                 void* dx, int M, int D, cudaStream_t st) {
+  if (D % 8 || D > 128 * 8 * 8) return ERR_BAD_SHAPE;
+  if (M <= 0) return 0;
+  const int per = (D / 8 + 127) / 128;
+#define ARTB_RN(V) rmsnorm_bwd_kernel<V><<<M, 128, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, M, D)
+  if (per <= 2) ARTB_RN(2); else if (per <= 4) ARTB_RN(4); else ARTB_RN(8);
+#undef ARTB_RN
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_rope(void* buf, const int* pos, int M, int ld, int col0, int heads, int hd, float theta,
+                          int inverse, cudaStream_t st) {
+  if (hd % 16 || ld % 8 || col0 % 8) return ERR_BAD_SHAPE;
+  const long total = (long)M * heads * (hd / 16);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((bf16*)buf, pos, M, ld, col0, heads, hd, log2f(theta),
+                                                    inverse ? -1.f : 1.f);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_swiglu_bwd(const void* dh, const void* gu, void* dgu, long M, int F, cudaStream_t st) {
+  if (F % 16) return ERR_BAD_SHAPE;
+  swiglu_bwd_kernel<<<grid_for(M * (F / 16) * 2, 256), 256, 0, st>>>((const bf16*)dh, (const bf16*)gu, (bf16*)dgu, M, F);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_swiglu_fwd(const void* gu, void* h, long M, int F, cudaStream_t st) {
+  if (F % 16) return ERR_BAD_SHAPE;
+  swiglu_fwd_kernel<<<grid_for(M * (F / 16) * 2, 256), 256, 0, st>>>((const bf16*)gu, (bf16*)h, M, F);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_headnorm_fwd(void* buf, const void* w, float* rstd, int M, int ld, int col0, int heads, int hd,
+                                  float eps, cudaStream_t st) {
+  const long warps = (long)M * heads;
+  headnorm_fwd_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>((bf16*)buf, (const bf16*)w, rstd, M, ld, col0, heads, hd, eps);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_headnorm_bwd(void* dbuf, const void* xbuf, const void* w, const float* rstd, int M, int ld,
+                                  int col0, int heads, int hd, cudaStream_t st) {
+  const long warps = (long)M * heads;
+  headnorm_bwd_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>((bf16*)dbuf, (const bf16*)xbuf, (const bf16*)w, rstd, M, ld, col0, heads, hd);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_gather_rows(const void* table, const int64_t* idx, void* out, long n, int D, long table_rows,
+                                 cudaStream_t st) {
+  if (D % 8) return ERR_BAD_SHAPE;
+  if (n == 0) return 0;
+  gather_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)table, idx, (bf16*)out, n, D, table_rows);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_scatter_rows(const void* src, const int64_t* idx, void* out, long n, int D, long out_rows,
+                                  cudaStream_t st) {
+  if (D % 8) return ERR_BAD_SHAPE;
+  if (n == 0) return 0;
+  scatter_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)src, idx, (bf16*)out, n, D, out_rows);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_adv_norm(const float* rewards, const int* offsets, float* adv, uint8_t* keep, int num_groups,
+                              cudaStream_t st) {
+  if (num_groups <= 0) return 0;
+  adv_norm_kernel<<<(num_groups + 3) / 4, 128, 0, st>>>(rewards, offsets, adv, keep, num_groups);
+  return (int)cudaGetLastError();
+}

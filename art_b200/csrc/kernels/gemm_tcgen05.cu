@@ -46,6 +46,7 @@ struct EpiStore {
   void* C;
   const __nv_bfloat16* R;
   __nv_bfloat16* H;  // SwiGLU output
+  const float* bias;  // [N] fp32 or null
   int ldc, ldr, ldh;
   int M, N;
   int mode;
@@ -58,6 +59,11 @@ struct EpiStore {
     const int gc = ti.n_blk * BN + c;
     if (gr >= M || gc >= N) return;
     const bool full = (gc + 32 <= N);
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || gc + j < N) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __ldg(bias + gc + j));
+    }
     if (mode == EPI_F32) {
       float* out = reinterpret_cast<float*>(C) + static_cast<size_t>(gr) * ldc + gc;
       if (full) {
@@ -160,14 +166,15 @@ using namespace artb;
 //   A, B, A2, B2 : bf16 row-major, leading dimensions in elements (multiples of 8), 16-B aligned
 //   K2 == 0      : no extra-K operand (A2/B2 ignored)
 //   epilogue     : GemmEpilogue; R (bf16 [M,N]) for EPI_BF16_RESID; H (bf16 [M,N/2]) for EPI_SWIGLU
+//   bias         : optional fp32 [N], added to the accumulator before any other epilogue step
 //   bn           : tile width 64 / 128 / 256 (0 = choose)
 //   status       : device int32, receives a KernelStatus on a bounded-wait expiry (0 otherwise)
 //   max_ctas     : cap on the persistent grid (0 = one CTA per SM)
 // Returns 0, a negative HostError, or a positive cudaError_t.
 ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb, const void* A2,
                                   int lda2, const void* B2, int ldb2, int K2, void* C, int ldc,
-                                  const void* R, int ldr, void* H, int ldh, int M, int N, int K,
-                                  int epilogue, int bn, int* status, int max_ctas,
+                                  const void* R, int ldr, void* H, int ldh, const float* bias, int M,
+                                  int N, int K, int epilogue, int bn, int* status, int max_ctas,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || K2 < 0) return ERR_BAD_SHAPE;
   if ((K & 7) || (K2 & 7) || (N & 7)) return ERR_BAD_SHAPE;
@@ -204,7 +211,7 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
 #define ARTB_LAUNCH(BN_, ST_)                                                                     \
   {                                                                                               \
     EpiStore<BN_> epi{C, reinterpret_cast<const __nv_bfloat16*>(R),                               \
-                      reinterpret_cast<__nv_bfloat16*>(H), ldc, ldr, ldh, M, N, epilogue};       \
+                      reinterpret_cast<__nv_bfloat16*>(H), bias, ldc, ldr, ldh, M, N, epilogue}; \
     return launch_gemm<BN_, ST_>(tA, tB, tA2, tB2, kb_main, kb_extra, M, N, epi, status, max_ctas, \
                                  stream);                                                         \
   }

@@ -21,7 +21,7 @@ def _fn():
     f = _lib.kernels().artb_gemm_bf16_tn
     if not _configured:
         vp, ci = ctypes.c_void_p, ctypes.c_int
-        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, ci, vp]
+        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
         f.restype = ci
         _configured = True
     return f
@@ -36,6 +36,7 @@ def _check2d(t: torch.Tensor, name: str) -> None:
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
             b2: torch.Tensor | None = None, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, swiglu_out: torch.Tensor | None = None,
+            bias: torch.Tensor | None = None,
             out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K].T (+ a2[M,K2] @ b2[N,K2].T) (+ residual)``.
 
@@ -70,6 +71,8 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         raise ValueError("out must be [M,N] with unit inner stride")
     if residual is not None:
         _check2d(residual, "residual")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise ValueError("bias must be fp32 [N]")
     st = _lib.status_word(a.device)
     rc = _fn()(
         _lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0),
@@ -78,16 +81,19 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         _lib.ptr(out), out.stride(0),
         _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
         _lib.ptr(swiglu_out), swiglu_out.stride(0) if swiglu_out is not None else 0,
+        _lib.ptr(bias),
         M, N, K, epi, bn, _lib.ptr(st), max_ctas, _lib.stream_ptr())
     _lib.check_rc(rc, "gemm_tn")
     return out
 
 
-def reference_gemm_tn(a, b, a2=None, b2=None, residual=None) -> torch.Tensor:
+def reference_gemm_tn(a, b, a2=None, b2=None, residual=None, bias=None) -> torch.Tensor:
     """fp32 PyTorch restatement (inputs upcast, fp32 accumulation)."""
     c = a.float() @ b.float().t()
     if a2 is not None:
         c = c + a2.float() @ b2.float().t()
+    if bias is not None:
+        c = c + bias.float()
     if residual is not None:
         c = c + residual.float()
     return c

@@ -1,0 +1,229 @@
+"""GRPO LoRA trainer with an explicit ``step()`` contract.
+
+One :class:`Trainer` owns the frozen base model, the LoRA masters and the optimizer state
+of one trainable model on one GPU (one rank of a data-/tensor-parallel group).  It consumes
+packed tensors (``local/pack.py``) and performs optimizer steps; there is no background
+training loop fed through a queue as in the reference
+(``src/art/local/service.py:72-162`` + ``src/art/local/state.py:94-115``): the service calls
+``train_packed`` and iterates the metrics it yields, one dict per optimizer step.
+
+Two implementations share this interface:
+
+``native``     the sm_100a path: :class:`models.native.NativeDecoder`, fused LM-head/GRPO
+               loss kernel, flat fused AdamW.  CUDA only.
+``reference``  plain PyTorch autograd over :class:`models.reference.ReferenceModel`; runs on
+               CPU (oracle, tests) and on GPU (library baseline for the benchmarks).
+
+Step semantics follow the reference: by default one packed row is one optimizer step
+(``rows_per_optimizer_step=1``); the loss of a step is the mean over its rows of
+``sum(pg * w * mask) / (sum(mask) + 1e-6)``; the learning rate is whatever the caller passes
+for that call; gradients are clipped to ``max_grad_norm`` (0.1); AdamW betas (0.9, 0.99),
+weight decay 0.1 (``src/art/dev/model.py:69-85``, ``src/art/local/train.py:34-153``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Iterator
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.reference import ReferenceModel, grpo_loss, shift_left
+from ..models.weights import LoraConfig
+from ..ops.optim import FlatAdamW
+
+PACKED_KEYS = ("tokens", "group_ids", "parent_ids", "input_pos", "assistant_mask", "logprobs", "advantages", "weights")
+
+
+@dataclass
+class TrainHyper:
+    learning_rate: float = 5e-6
+    beta: float = 0.0
+    epsilon: float = 0.2
+    epsilon_high: float | None = None
+    rows_per_optimizer_step: int = 1
+    tokens_per_microbatch: int = 8192
+    compat_row_positions: bool = False
+
+
+class Trainer:
+    def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
+                 lora_init: dict[str, torch.Tensor], device: str | torch.device = "cpu", impl: str | None = None,
+                 betas=(0.9, 0.99), weight_decay: float = 0.1, max_grad_norm: float = 0.1, adam_eps: float = 1e-8,
+                 attn_impl: str = "native", dp_group=None, grad_sync=None):
+        self.cfg, self.lora_cfg = cfg, lora_cfg
+        self.device = torch.device(device)
+        self.impl = impl or ("native" if self.device.type == "cuda" else "reference")
+        self.dp_group = dp_group
+        self.grad_sync = grad_sync  # callable(flat_grads) -> None : data-parallel gradient all-reduce
+        if self.impl == "native":
+            from ..models.native import NativeDecoder
+
+            self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl)
+            self.flat = self.model.flat
+        else:
+            from ..models.native import LoraFlat
+
+            self.flat = LoraFlat(cfg, lora_cfg, lora_init, self.device)
+            dt = torch.float32 if self.device.type == "cpu" else torch.bfloat16
+            self.base = {k: v.to(self.device, dt) for k, v in base.items()}
+            for v in self.flat.views.values():
+                v.requires_grad_(True)
+            self.model = ReferenceModel(cfg, self.base, self.flat.views, lora_cfg)
+        self.opt = FlatAdamW(self.flat.params.detach(), self.flat.grads, betas=betas, eps=adam_eps,
+                             weight_decay=weight_decay, max_grad_norm=max_grad_norm)
+        self.global_step = 0
+
+    # ------------------------------------------------------------------ state
+    def lora_state_dict(self) -> dict[str, torch.Tensor]:
+        return {k: v.detach().clone() for k, v in self.flat.views.items()}
+
+    def load_lora_state_dict(self, sd: dict[str, torch.Tensor]) -> None:
+        with torch.no_grad():
+            self.flat.load_state_dict(sd)
+        if self.impl == "native":
+            self.model.refresh_lora()
+
+    def trainer_state(self) -> dict:
+        return {"optimizer": {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.opt.state_dict().items()},
+                "global_step": self.global_step}
+
+    def load_trainer_state(self, st: dict) -> None:
+        self.opt.load_state_dict({k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in st["optimizer"].items()})
+        self.global_step = int(st.get("global_step", 0))
+
+    # ------------------------------------------------------------------ training
+    def train_packed(self, packed: dict[str, torch.Tensor], hyper: TrainHyper) -> Iterator[dict[str, float]]:
+        """Yield one metrics dict per optimizer step over the rows of ``packed`` ([N,S] tensors)."""
+        n_rows = packed["tokens"].shape[0]
+        per = max(1, hyper.rows_per_optimizer_step)
+        for start in range(0, n_rows, per):
+            rows = {k: packed[k][start:start + per] for k in PACKED_KEYS}
+            yield self.step(rows, hyper)
+
+    def step(self, rows: dict[str, torch.Tensor], hyper: TrainHyper) -> dict[str, float]:
+        if self.impl == "native":
+            m = self._step_native(rows, hyper)
+        else:
+            m = self._step_reference(rows, hyper)
+        self.global_step += 1
+        return m
+
+    # ---- reference (autograd) ---------------------------------------------------------------
+    def _step_reference(self, rows: dict[str, torch.Tensor], hyper: TrainHyper) -> dict[str, float]:
+        dev = self.device
+        rows = {k: v.to(dev) for k, v in rows.items()}
+        R, S = rows["tokens"].shape
+        self.flat.grads.zero_()
+        total = {"loss": 0.0, "policy_loss": 0.0, "kl_div": 0.0}
+        pos_all = None if hyper.compat_row_positions else rows["input_pos"]
+        for r in range(R):  # one row at a time keeps the dense mask small
+            one = {k: v[r:r + 1] for k, v in rows.items()}
+            pos = None if pos_all is None else pos_all[r:r + 1]
+            hidden = self.model.hidden_states(one["tokens"], one["group_ids"], one["parent_ids"], pos)
+            nxt = shift_left(one["tokens"], 0)
+            new_lp = self.model.logprobs(hidden, nxt)
+            ref_lp = None
+            if hyper.beta > 0:
+                with torch.no_grad():
+                    rh = self.model.hidden_states(one["tokens"], one["group_ids"], one["parent_ids"], pos, use_lora=False)
+                    ref_lp = self.model.logprobs(rh, nxt)
+            loss, met = grpo_loss(new_lp, one, hyper.epsilon, hyper.epsilon_high, hyper.beta, ref_lp)
+            (loss / R).backward()
+            total["loss"] += float(loss.detach()) / R
+            total["policy_loss"] += float(met["policy_loss"]) / R
+            total["kl_div"] += float(met["kl_div"]) / R
+        for k, v in self.flat.views.items():
+            if v.grad is not None:
+                self.flat.grad_views[k].copy_(v.grad)
+                v.grad = None
+        return self._finish_step(total, hyper)
+
+    # ---- native -------------------------------------------------------------------------------
+    def _step_native(self, rows: dict[str, torch.Tensor], hyper: TrainHyper) -> dict[str, float]:
+        from ..ops import elementwise as ew
+        from ..ops import logprob_loss as lpl
+
+        dev = self.device
+        R, S = rows["tokens"].shape
+        on_host = not rows["tokens"].is_cuda
+        # next-token aligned per-token quantities (host side when the batch comes from the host,
+        # so the trainable-token index list is known without a device sync)
+        mask_s = shift_left(rows["assistant_mask"], False)
+        denom = mask_s.sum(dim=1, keepdim=True).float() + 1e-6
+        tok_w = shift_left(rows["weights"], 0.0) * mask_s.float() / denom / R
+        sel_all = torch.nonzero(tok_w.reshape(-1) != 0, as_tuple=False).squeeze(1)  # host op if on_host
+        rows_d = {k: v.to(dev, non_blocking=True) for k, v in rows.items()}
+        tok_w_d = tok_w.to(dev, non_blocking=True)
+        sel_all_d = sel_all.to(dev, non_blocking=True)
+        self.model.zero_grad()
+        accum = torch.zeros(4, dtype=torch.float32, device=dev)
+        rows_per_micro = max(1, min(R, hyper.tokens_per_microbatch // S))
+        eps_hi = hyper.epsilon if hyper.epsilon_high is None else hyper.epsilon_high
+        sel_host = sel_all if on_host else sel_all.cpu()
+        for r0 in range(0, R, rows_per_micro):
+            r1 = min(R, r0 + rows_per_micro)
+            M = (r1 - r0) * S
+            flat = lambda k: rows_d[k][r0:r1].reshape(-1)  # noqa: E731
+            tokens = flat("tokens")
+            pos = (torch.arange(S, device=dev, dtype=torch.int32).repeat(r1 - r0) if hyper.compat_row_positions
+                   else flat("input_pos").to(torch.int32))
+            # id compression runs where the batch lives: on the host for host batches (no device sync)
+            gid, pid = compress_ids(rows["group_ids"][r0:r1].reshape(-1), rows["parent_ids"][r0:r1].reshape(-1))
+            gid, pid = gid.to(dev, non_blocking=True), pid.to(dev, non_blocking=True)
+            lo = int(torch.searchsorted(sel_host, r0 * S))
+            hi = int(torch.searchsorted(sel_host, r1 * S))
+            if hi == lo:
+                continue
+            sel = sel_all_d[lo:hi] - r0 * S
+            hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S)
+            target = torch.cat([tokens[1:], tokens[:1]]).to(torch.int32)  # next token; row ends are masked out
+            hc = ew.gather_rows(hidden, sel)
+            tgt_c = target[sel]
+            w_c = tok_w_d.reshape(-1)[r0 * S:r1 * S][sel]
+            old_c = shift_left(rows_d["logprobs"][r0:r1], 0.0).reshape(-1)[sel]
+            adv_c = shift_left(rows_d["advantages"][r0:r1], 0.0).reshape(-1)[sel]
+            ref_c = None
+            if hyper.beta > 0:
+                ref_hidden, _, _ = self.model.forward(tokens, pos, gid, pid, S, use_lora=False, save=False)
+                rc = ew.gather_rows(ref_hidden, sel)
+                part, _ = lpl.partials(rc, self.model.lm_head, tgt_c)
+                ref_c = lpl.grpo_tokens(part).logprobs
+                del ref_hidden, rc, part
+            res = lpl.forward(hc, self.model.lm_head, tgt_c, old_c, adv_c, w_c, ref_c, hyper.epsilon, eps_hi,
+                              hyper.beta, accum)
+            dhc = lpl.backward(hc, self.model.lm_head, self.model.lm_head_t, tgt_c, res.lse, res.coef)
+            dhidden = torch.zeros_like(hidden)
+            ew.scatter_rows_(dhc, sel, dhidden)
+            del hc, dhc
+            self.model.backward(dhidden, saved, final, pos)
+        self.model.export_grads()
+        acc = accum  # read back together with the grad norm below
+        out = self._finish_step(None, hyper, device_accum=acc)
+        self.model.refresh_lora()
+        return out
+
+    def _finish_step(self, totals: dict | None, hyper: TrainHyper, device_accum: torch.Tensor | None = None):
+        if self.grad_sync is not None:
+            self.grad_sync(self.flat.grads)
+        gnorm = self.opt.step(hyper.learning_rate)
+        if device_accum is not None:
+            vals = torch.cat([device_accum[:2], gnorm.reshape(1)]).tolist()  # one D2H read per step
+            pl, kl, gn = vals
+            totals = {"policy_loss": pl, "kl_div": kl, "loss": pl + hyper.beta * kl}
+        else:
+            gn = float(gnorm)
+        out = {"loss": totals["loss"], "grad_norm": gn, "policy_loss": totals["policy_loss"],
+               "learning_rate": hyper.learning_rate}
+        if hyper.beta > 0:
+            out["kl_div"] = totals["kl_div"]
+        return out
+
+
+def compress_ids(group_ids: torch.Tensor, parent_ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Map the random int64 group / parent ids of a micro-batch to dense int32 ids (order-free)."""
+    both = torch.cat([group_ids, parent_ids])
+    _, inv = torch.unique(both, return_inverse=True)
+    n = group_ids.numel()
+    return inv[:n].to(torch.int32).contiguous(), inv[n:].to(torch.int32).contiguous()
