@@ -263,6 +263,7 @@ class NativeDecoder:
         """tokens int64 [M], pos/gid/pid int32 [M]; returns final-normed hidden [M,d] and saved state."""
         cfg = self.cfg
         x = ew.gather_rows(self.embed, tokens)
+        plan = attn_ops.make_plan(gid, pid, S, self.attn_impl)
         saved: list[LayerSaved] = []
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         for layer in self.layers:
@@ -276,7 +277,7 @@ class NativeDecoder:
                 rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
                 sv.qk_rstd = (rq, rk)
             ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
-            o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, gid, pid, S, self.attn_impl, need_grad=save)
+            o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
             x2, T_o = layer["o"].forward(o, use_lora, residual=x)
             h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
             hact = torch.empty((x.shape[0], cfg.intermediate_size), dtype=x.dtype, device=x.device)

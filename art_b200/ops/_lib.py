@@ -115,8 +115,13 @@ def check_status(device: torch.device | int | None = None, reset: bool = True) -
         raise KernelStatusError(code)
 
 
+LAUNCHES = 0  # native kernel launches issued by this process (each front-end call checks its return code once)
+
+
 def check_rc(rc: int, what: str) -> None:
+    global LAUNCHES
     if rc == 0:
+        LAUNCHES += 1
         return
     if rc < 0:
         names = {-1: "bad shape", -2: "bad alignment", -3: "driver entry point unavailable",

@@ -8,23 +8,31 @@ with ``M = rows * S``.  A query may attend a key of the same row iff
 
 ``impl="native"`` runs the flash-style kernels of ``csrc/kernels/attn_tree.cu`` (mask from
 ids per tile, fully-masked tiles skipped); ``impl="sdpa"`` is the library baseline, which
-builds the dense mask and calls ``scaled_dot_product_attention``.
+builds the dense mask and calls ``scaled_dot_product_attention``.  An :class:`AttnPlan` is
+made once per micro-batch and shared by all layers, forward and backward.
 """
 from __future__ import annotations
 
-import ctypes
 import math
 from dataclasses import dataclass
 
 import torch
 import torch.nn.functional as F
 
-from . import _lib
+
+@dataclass
+class AttnPlan:
+    impl: str
+    gid: torch.Tensor   # int32 [M]
+    pid: torch.Tensor   # int32 [M]
+    S: int
+    state: torch.Tensor | None = None   # native: uint8 tile states
+    mask: torch.Tensor | None = None    # sdpa: dense bool mask [rows,1,S,S]
 
 
 @dataclass
 class AttnCtx:
-    impl: str
+    plan: AttnPlan
     saved: tuple
 
 
@@ -35,6 +43,20 @@ def dense_mask(gid: torch.Tensor, pid: torch.Tensor) -> torch.Tensor:
     return causal & ((gid.unsqueeze(2) == gid.unsqueeze(1)) | (pid.unsqueeze(2) == gid.unsqueeze(1)))
 
 
+def make_plan(gid: torch.Tensor, pid: torch.Tensor, S: int, impl: str = "native") -> AttnPlan:
+    plan = AttnPlan(impl, gid, pid, S)
+    if impl == "native":
+        from . import attn_native
+
+        if S % 64:
+            raise ValueError("native attention needs the packed row length to be a multiple of 64")
+        plan.state = attn_native.tile_states(gid, pid, S)
+    else:
+        rows = gid.numel() // S
+        plan.mask = dense_mask(gid.view(rows, S), pid.view(rows, S)).unsqueeze(1)
+    return plan
+
+
 def _split(qkv: torch.Tensor, rows: int, S: int, Hq: int, Hkv: int, hd: int):
     q = qkv[:, : Hq * hd].reshape(rows, S, Hq, hd).transpose(1, 2)
     k = qkv[:, Hq * hd: (Hq + Hkv) * hd].reshape(rows, S, Hkv, hd).transpose(1, 2)
@@ -42,30 +64,30 @@ def _split(qkv: torch.Tensor, rows: int, S: int, Hq: int, Hkv: int, hd: int):
     return q, k, v
 
 
-def forward(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, gid: torch.Tensor, pid: torch.Tensor, S: int,
-            impl: str = "native", need_grad: bool = True) -> tuple[torch.Tensor, AttnCtx]:
-    M = qkv.shape[0]
+def forward(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, plan: AttnPlan,
+            need_grad: bool = True) -> tuple[torch.Tensor, AttnCtx]:
+    M, S = qkv.shape[0], plan.S
     rows = M // S
-    if impl == "native":
+    if plan.impl == "native":
         from . import attn_native
 
-        return attn_native.forward(qkv, Hq, Hkv, hd, gid, pid, S, need_grad)
+        o, saved = attn_native.forward(qkv, Hq, Hkv, hd, plan)
+        return o, AttnCtx(plan, saved)
     q, k, v = _split(qkv, rows, S, Hq, Hkv, hd)
     if need_grad:
         q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
-    mask = dense_mask(gid.view(rows, S), pid.view(rows, S)).unsqueeze(1)
     with torch.enable_grad() if need_grad else torch.no_grad():
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, enable_gqa=(Hq != Hkv))
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=plan.mask, enable_gqa=(Hq != Hkv))
         o2 = o.transpose(1, 2).reshape(M, Hq * hd)
-    return o2.detach(), AttnCtx("sdpa", (q, k, v, o2))
+    return o2.detach(), AttnCtx(plan, (q, k, v, o2))
 
 
 def backward(do: torch.Tensor, ctx: AttnCtx) -> torch.Tensor:
     """Gradient w.r.t. the fused post-RoPE ``qkv`` buffer, same layout."""
-    if ctx.impl == "native":
+    if ctx.plan.impl == "native":
         from . import attn_native
 
-        return attn_native.backward(do, ctx)
+        return attn_native.backward(do, ctx.saved, ctx.plan)
     q, k, v, o2 = ctx.saved
     dq, dk, dv = torch.autograd.grad(o2, (q, k, v), do)
     M = do.shape[0]

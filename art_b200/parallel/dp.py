@@ -1,0 +1,38 @@
+"""Data parallelism for LoRA training: one process per GPU, frozen base weights replicated,
+the flat fp32 LoRA gradient buffer summed across ranks before the optimizer step.
+
+Two gradient-sync implementations:
+
+``nccl``   ``torch.distributed.all_reduce`` on the flat buffer (the library baseline).
+``fused``  the in-tree NVLink kernel (``csrc/comm/lora_grad_allreduce.cu``): every rank
+           reduces its 1/P slice by reading the peers' symmetric buffers directly and
+           writes the sum back to all peers, with bounded flag waits.
+
+The reference has no data parallelism at all (one packed row per optimizer step on one GPU,
+``src/art/local/service.py:96-118``); this module exists for the multi-GPU configurations.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def nccl_grad_sync(world: int):
+    def sync(flat_grads: torch.Tensor) -> None:
+        dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM)
+        flat_grads.div_(world)
+    return sync
+
+
+def make_grad_sync(kind: str, device: torch.device, world: int):
+    """Returns ``(callable(flat_grads), name)``.  ``auto`` prefers the fused kernel when peer access works."""
+    if kind in ("auto", "fused"):
+        try:
+            from .symm_mem import fused_allreduce_sync
+
+            return fused_allreduce_sync(device, world), "fused-p2p-allreduce"
+        except Exception as e:  # peer mapping unavailable: fall back to the library path, loudly
+            if kind == "fused":
+                raise
+            print(f"[art_b200] fused all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+    return nccl_grad_sync(world), "nccl-allreduce"

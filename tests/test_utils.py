@@ -1,0 +1,118 @@
+import asyncio
+import os
+
+import pytest
+
+from art_b200.utils import format_message, iterate_dataset, limit_concurrency, retry
+from art_b200.utils.get_model_step import get_step_from_dir
+from art_b200.utils.trajectory_logging import deserialize_trajectory_groups, serialize_trajectory_groups
+
+
+def test_retry_sync_and_async():
+    calls = []
+
+    @retry(max_attempts=3, delay=0.0, on_retry=lambda e, n: calls.append(n))
+    def flaky():
+        if len(calls) < 2:
+            raise ValueError("x")
+        return 7
+
+    assert flaky() == 7 and calls == [1, 2]
+
+    @retry(max_attempts=2, delay=0.0, exceptions=(KeyError,))
+    async def always():
+        raise KeyError("k")
+
+    with pytest.raises(KeyError):
+        asyncio.run(always())
+
+
+def test_iterate_dataset_is_deterministic_and_resumable():
+    data = list(range(10))
+    full = list(iterate_dataset(data, groups_per_step=3, num_epochs=2, use_tqdm=False))
+    assert len(full) == 8 and full[0][1:] == (0, 0, 0) and full[4][1:] == (1, 4, 0)
+    assert sorted(sum((b for b, e, *_ in full if e == 0), [])) == data
+    resumed = list(iterate_dataset(data, groups_per_step=3, num_epochs=2, initial_step=5, use_tqdm=False))
+    assert [r[0] for r in resumed] == [f[0] for f in full[5:]]
+
+
+def test_limit_concurrency():
+    live = peak = 0
+
+    @limit_concurrency(2)
+    async def work():
+        nonlocal live, peak
+        live += 1
+        peak = max(peak, live)
+        await asyncio.sleep(0.005)
+        live -= 1
+
+    async def main():
+        await asyncio.gather(*[work() for _ in range(6)])
+
+    asyncio.run(main())
+    assert peak == 2
+
+
+def test_format_message_and_step_dir(tmp_path):
+    m = {"role": "assistant", "content": "hi", "tool_calls": [{"function": {"name": "f", "arguments": "{}"}}]}
+    assert format_message(m) == "Assistant:\nhi\nf({})"
+    assert get_step_from_dir(str(tmp_path)) == 0
+    os.makedirs(tmp_path / "0003")
+    os.makedirs(tmp_path / "notes")
+    assert get_step_from_dir(str(tmp_path)) == 3
+
+
+def test_trajectory_yaml_round_trip():
+    from tests.test_api_trajectories import traj
+    import art_b200 as art
+
+    groups = [art.TrajectoryGroup([traj(0.5, metrics={"a": 1}), traj(1.0)], metadata={"scenario": "s"})]
+    text = serialize_trajectory_groups(groups)
+    assert "logprobs" not in text
+    back = deserialize_trajectory_groups(text)
+    assert back[0].metadata == {"scenario": "s"} and [t.reward for t in back[0]] == [0.5, 1.0]
+    assert back[0].trajectories[0].messages()[1]["content"] == "abc"
+
+
+def test_s3_paths_and_sync_commands(monkeypatch):
+    from art_b200.utils import s3
+
+    assert s3.build_s3_path(model_name="m", project="p", step=3, s3_bucket="b", prefix="/x/") == "s3://b/x/p/models/m/0003"
+    assert s3.build_s3_zipped_step_path(model_name="m", project="p", step=3, s3_bucket="b").endswith("zipped-steps/0003.zip")
+    seen = []
+
+    async def fake_run(cmd, **kw):
+        seen.append(cmd)
+        return (1 if "head-bucket" in cmd else 0), "https://signed", ""
+
+    monkeypatch.setattr(s3, "_run", fake_run)
+    asyncio.run(s3.ensure_bucket_exists("b"))
+    assert seen[1][-3:] == ["create-bucket", "--bucket", "b"]
+    asyncio.run(s3.s3_sync("/tmp", "s3://b/x", delete=True))
+    assert seen[-1][:4] == ["aws", "s3", "sync", "--delete"]
+
+
+def test_deploy_model_reuses_running_job(monkeypatch, tmp_path):
+    import art_b200 as art
+    from art_b200.utils import deploy_model as dm
+
+    model = art.TrainableModel(name="m", project="p", base_model="Qwen/Qwen2.5-14B-Instruct")
+    calls = []
+
+    async def fake_request(method, url, body=None):
+        calls.append((method, url))
+        if url.endswith("/jobs"):
+            return {"data": [{"job_id": "j1", "updated_at": 1, "args": {"modelName": "acct/p-m-2"}}]}
+        if "/jobs/" in url:
+            return {"status": "Complete", "status_updates": [{"message": "ok"}], "args": {"modelName": "acct/p-m-2"}}
+        raise AssertionError("should not upload again")
+
+    async def fake_presign(**kw):
+        return "https://signed"
+
+    monkeypatch.setattr(dm, "_request", fake_request)
+    monkeypatch.setattr(dm, "archive_and_presign_step_url", fake_presign)
+    job = asyncio.run(dm.deploy_model(dm.LoRADeploymentProvider.TOGETHER, model, step=2, pull_s3=False, art_path=str(tmp_path)))
+    assert job.status == dm.LoRADeploymentJobStatus.COMPLETE and job.job_id == "j1"
+    assert dm.convert_together_job_status("Retry Queued") == dm.LoRADeploymentJobStatus.QUEUED
