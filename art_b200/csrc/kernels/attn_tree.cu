@@ -295,16 +295,17 @@ attn_tree_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_b
                      float scale_log2, long M) {
   constexpr int LD = HD + 8;
   constexpr int SLD = AT_B + 8;
+  constexpr int TILE = AT_B * LD;
   extern __shared__ __align__(16) uint8_t at_smem[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(at_smem);
-  __nv_bfloat16* sV = sK + AT_B * LD;
-  __nv_bfloat16* sQ = sV + AT_B * LD;
-  __nv_bfloat16* sdO = sQ + AT_B * LD;
-  __nv_bfloat16* sdS = sdO + AT_B * LD;  // [key][query]
-  float* sL = reinterpret_cast<float*>(sdS + AT_B * SLD);
-  float* sD = sL + AT_B;
-  int* sGq = reinterpret_cast<int*>(sD + AT_B);
-  int* sPq = sGq + AT_B;
+  __nv_bfloat16* sV = sK + TILE;
+  __nv_bfloat16* sQ = sV + TILE;        // [2][TILE]  double-buffered
+  __nv_bfloat16* sdO = sQ + 2 * TILE;   // [2][TILE]
+  __nv_bfloat16* sdS = sdO + 2 * TILE;  // [key][query]
+  float* sL = reinterpret_cast<float*>(sdS + AT_B * SLD);  // [2][64]
+  float* sD = sL + 2 * AT_B;
+  int* sGq = reinterpret_cast<int*>(sD + 2 * AT_B);
+  int* sPq = sGq + 2 * AT_B;
 
   const int kb = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int G = Hq / Hkv;
@@ -312,6 +313,7 @@ attn_tree_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_b
   const int g = lane >> 2, t = lane & 3, jm = lane >> 3, rr = lane & 7;
   const long base = static_cast<long>(row) * S;
   constexpr int VEC_ROW = HD / 8;
+  const uint8_t* st_col = state + static_cast<size_t>(row) * nb * nb + kb;  // + qb * nb
 
   const __nv_bfloat16* kptr = qkv + (base + kb * AT_B) * ld + (Hq + kvh) * HD;
   const __nv_bfloat16* vptr = qkv + (base + kb * AT_B) * ld + (Hq + Hkv + kvh) * HD;
@@ -320,7 +322,32 @@ attn_tree_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_b
     at_cp16(sK + r * LD + c * 8, kptr + static_cast<long>(r) * ld + c * 8);
     at_cp16(sV + r * LD + c * 8, vptr + static_cast<long>(r) * ld + c * 8);
   }
-  at_commit();
+
+  // work list: (hq, qb) pairs with a non-empty tile, visited in order; item index -> (hq, qb)
+  const int nq = nb - kb;
+  const int n_items = G * nq;
+  auto next_item = [&](int it) {
+    while (it < n_items && st_col[static_cast<size_t>(kb + it % nq) * nb] == 0) ++it;
+    return it;
+  };
+  auto load_item = [&](int it, int buf) {
+    const int hq = kvh * G + it / nq, qb = kb + it % nq;
+    const __nv_bfloat16* qptr = qkv + (base + qb * AT_B) * ld + hq * HD;
+    const __nv_bfloat16* doptr = dO + (base + qb * AT_B) * ldo + hq * HD;
+    for (int v = tid; v < AT_B * VEC_ROW; v += 128) {
+      const int r = v / VEC_ROW, c = v % VEC_ROW;
+      at_cp16(sQ + buf * TILE + r * LD + c * 8, qptr + static_cast<long>(r) * ld + c * 8);
+      at_cp16(sdO + buf * TILE + r * LD + c * 8, doptr + static_cast<long>(r) * ldo + c * 8);
+    }
+    if (tid < AT_B) {
+      const long qi = base + qb * AT_B + tid;
+      sL[buf * AT_B + tid] = lse2[static_cast<long>(hq) * M + qi];
+      sD[buf * AT_B + tid] = Dv[static_cast<long>(hq) * M + qi];
+      sGq[buf * AT_B + tid] = gid[qi];
+      sPq[buf * AT_B + tid] = pid[qi];
+    }
+    at_commit();
+  };
 
   const int krow0 = kb * AT_B + warp * 16 + g, krow1 = krow0 + 8;
   const int gk0 = gid[base + krow0], gk1 = gid[base + krow1];
@@ -331,124 +358,124 @@ attn_tree_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_b
 #pragma unroll
     for (int j = 0; j < 4; ++j) dk[i][j] = dv[i][j] = 0.f;
 
-  for (int hq = kvh * G; hq < (kvh + 1) * G; ++hq) {
-    for (int qb = kb; qb < nb; ++qb) {
-      const uint8_t stt = state[(static_cast<size_t>(row) * nb + qb) * nb + kb];
-      if (stt == 0) continue;
-      __syncthreads();  // previous iteration's readers of sQ / sdO / sdS are done
-      const __nv_bfloat16* qptr = qkv + (base + qb * AT_B) * ld + hq * HD;
-      const __nv_bfloat16* doptr = dO + (base + qb * AT_B) * ldo + hq * HD;
-      for (int v = tid; v < AT_B * VEC_ROW; v += 128) {
-        const int r = v / VEC_ROW, c = v % VEC_ROW;
-        at_cp16(sQ + r * LD + c * 8, qptr + static_cast<long>(r) * ld + c * 8);
-        at_cp16(sdO + r * LD + c * 8, doptr + static_cast<long>(r) * ldo + c * 8);
-      }
-      at_commit();
-      if (tid < AT_B) {
-        const long qi = base + qb * AT_B + tid;
-        sL[tid] = lse2[static_cast<long>(hq) * M + qi];
-        sD[tid] = Dv[static_cast<long>(hq) * M + qi];
-        sGq[tid] = gid[qi];
-        sPq[tid] = pid[qi];
-      }
+  int it = next_item(0);
+  int buf = 0;
+  if (it < n_items) load_item(it, 0);   // same async group as K/V
+  else at_commit();
+  while (it < n_items) {
+    const int it_next = next_item(it + 1);
+    if (it_next < n_items) {
+      load_item(it_next, buf ^ 1);      // buffer buf^1 was released by the barrier that ended the last iteration
+      at_wait<1>();
+    } else {
       at_wait<0>();
-      __syncthreads();
+    }
+    __syncthreads();
+    const int hq = kvh * G + it / nq, qb = kb + it % nq;
+    const uint8_t stt = st_col[static_cast<size_t>(qb) * nb];
+    const __nv_bfloat16* cQ = sQ + buf * TILE;
+    const __nv_bfloat16* cdO = sdO + buf * TILE;
+    const float* cL = sL + buf * AT_B;
+    const float* cD = sD + buf * AT_B;
+    const int* cGq = sGq + buf * AT_B;
+    const int* cPq = sPq + buf * AT_B;
 
-      // S^T = K_w Q^T  and  dP^T = V_w dO^T   (16 keys x 64 queries per warp)
-      float sT[8][4], dpT[8][4];
+    // S^T = K_w Q^T  and  dP^T = V_w dO^T   (16 keys x 64 queries per warp)
+    float sT[8][4], dpT[8][4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) sT[i][j] = dpT[i][j] = 0.f;
+      for (int j = 0; j < 4; ++j) sT[i][j] = dpT[i][j] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        uint32_t ka[4], va[4];
-        ldsm_x4(ka, sK + (warp * 16 + (jm & 1) * 8 + rr) * LD + ks * 16 + (jm >> 1) * 8);
-        ldsm_x4(va, sV + (warp * 16 + (jm & 1) * 8 + rr) * LD + ks * 16 + (jm >> 1) * 8);
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t ka[4], va[4];
+      ldsm_x4(ka, sK + (warp * 16 + (jm & 1) * 8 + rr) * LD + ks * 16 + (jm >> 1) * 8);
+      ldsm_x4(va, sV + (warp * 16 + (jm & 1) * 8 + rr) * LD + ks * 16 + (jm >> 1) * 8);
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
-          uint32_t b[4];
-          ldsm_x4(b, sQ + (np * 16 + (jm >> 1) * 8 + rr) * LD + ks * 16 + (jm & 1) * 8);
-          mma16816(sT[np * 2], ka, b[0], b[1]);
-          mma16816(sT[np * 2 + 1], ka, b[2], b[3]);
-          ldsm_x4(b, sdO + (np * 16 + (jm >> 1) * 8 + rr) * LD + ks * 16 + (jm & 1) * 8);
-          mma16816(dpT[np * 2], va, b[0], b[1]);
-          mma16816(dpT[np * 2 + 1], va, b[2], b[3]);
-        }
-      }
-      // P^T and dS^T (rows: keys g / g+8 of this warp; cols: queries)
-      uint32_t pA[4][4], dsA[4][4];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float p[4], ds[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int c = i * 8 + 2 * t + (j & 1);      // query index within the tile
-          const int kr = (j < 2) ? krow0 : krow1;
-          const int gk = (j < 2) ? gk0 : gk1;
-          bool ok = true;
-          if (stt == 1) ok = (kr <= qb * AT_B + c) && (gk == sGq[c] || gk == sPq[c]);
-          const float pv = ok ? exp2f(sT[i][j] * scale_log2 - sL[c]) : 0.f;
-          p[j] = pv;
-          ds[j] = pv * (dpT[i][j] - sD[c]) * scale;
-        }
-        pA[i >> 1][(i & 1) * 2] = pack2(p[0], p[1]);
-        pA[i >> 1][(i & 1) * 2 + 1] = pack2(p[2], p[3]);
-        dsA[i >> 1][(i & 1) * 2] = pack2(ds[0], ds[1]);
-        dsA[i >> 1][(i & 1) * 2 + 1] = pack2(ds[2], ds[3]);
-        // stash dS^T for the dQ product: sdS[key][query]
-        *reinterpret_cast<uint32_t*>(sdS + (warp * 16 + g) * SLD + i * 8 + 2 * t) = pack2(ds[0], ds[1]);
-        *reinterpret_cast<uint32_t*>(sdS + (warp * 16 + g + 8) * SLD + i * 8 + 2 * t) = pack2(ds[2], ds[3]);
-      }
-      // dV_w += P^T dO ;  dK_w += dS^T Q     (contraction over the 64 queries)
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-#pragma unroll
-        for (int dp = 0; dp < HD / 16; ++dp) {
-          uint32_t b[4];
-          ldsm_x4_t(b, sdO + (ks * 16 + (jm & 1) * 8 + rr) * LD + dp * 16 + (jm >> 1) * 8);
-          mma16816(dv[dp * 2], pA[ks], b[0], b[1]);
-          mma16816(dv[dp * 2 + 1], pA[ks], b[2], b[3]);
-          ldsm_x4_t(b, sQ + (ks * 16 + (jm & 1) * 8 + rr) * LD + dp * 16 + (jm >> 1) * 8);
-          mma16816(dk[dp * 2], dsA[ks], b[0], b[1]);
-          mma16816(dk[dp * 2 + 1], dsA[ks], b[2], b[3]);
-        }
-      }
-      __syncthreads();  // sdS complete
-      // dQ_w[16 queries x HD] = dS[16 q x 64 keys] K[64 keys x HD], in two halves of HD
-      float* dq0 = dq_acc + (base + qb * AT_B + warp * 16 + g) * (static_cast<long>(Hq) * HD) + hq * HD;
-      float* dq1 = dq0 + 8L * Hq * HD;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float dq[HD / 16][4];
-#pragma unroll
-        for (int i = 0; i < HD / 16; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) dq[i][j] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          uint32_t a[4];
-          // A = dS (rows: queries, k: keys) read transposed from sdS[key][query]
-          ldsm_x4_t(a, sdS + (ks * 16 + (jm >> 1) * 8 + rr) * SLD + warp * 16 + (jm & 1) * 8);
-#pragma unroll
-          for (int dp = 0; dp < HD / 32; ++dp) {
-            uint32_t b[4];
-            ldsm_x4_t(b, sK + (ks * 16 + (jm & 1) * 8 + rr) * LD + half * (HD / 2) + dp * 16 + (jm >> 1) * 8);
-            mma16816(dq[dp * 2], a, b[0], b[1]);
-            mma16816(dq[dp * 2 + 1], a, b[2], b[3]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < HD / 16; ++i) {
-          const int col = half * (HD / 2) + i * 8 + 2 * t;
-          atomicAdd(dq0 + col, dq[i][0]);
-          atomicAdd(dq0 + col + 1, dq[i][1]);
-          atomicAdd(dq1 + col, dq[i][2]);
-          atomicAdd(dq1 + col + 1, dq[i][3]);
-        }
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldsm_x4(b, cQ + (np * 16 + (jm >> 1) * 8 + rr) * LD + ks * 16 + (jm & 1) * 8);
+        mma16816(sT[np * 2], ka, b[0], b[1]);
+        mma16816(sT[np * 2 + 1], ka, b[2], b[3]);
+        ldsm_x4(b, cdO + (np * 16 + (jm >> 1) * 8 + rr) * LD + ks * 16 + (jm & 1) * 8);
+        mma16816(dpT[np * 2], va, b[0], b[1]);
+        mma16816(dpT[np * 2 + 1], va, b[2], b[3]);
       }
     }
+    // P^T and dS^T (rows: keys g / g+8 of this warp; cols: queries)
+    uint32_t pA[4][4], dsA[4][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float p[4], ds[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = i * 8 + 2 * t + (j & 1);      // query index within the tile
+        const int kr = (j < 2) ? krow0 : krow1;
+        const int gk = (j < 2) ? gk0 : gk1;
+        bool ok = true;
+        if (stt == 1) ok = (kr <= qb * AT_B + c) && (gk == cGq[c] || gk == cPq[c]);
+        const float pv = ok ? exp2f(sT[i][j] * scale_log2 - cL[c]) : 0.f;
+        p[j] = pv;
+        ds[j] = pv * (dpT[i][j] - cD[c]) * scale;
+      }
+      pA[i >> 1][(i & 1) * 2] = pack2(p[0], p[1]);
+      pA[i >> 1][(i & 1) * 2 + 1] = pack2(p[2], p[3]);
+      dsA[i >> 1][(i & 1) * 2] = pack2(ds[0], ds[1]);
+      dsA[i >> 1][(i & 1) * 2 + 1] = pack2(ds[2], ds[3]);
+      // stash dS^T for the dQ product: sdS[key][query]
+      *reinterpret_cast<uint32_t*>(sdS + (warp * 16 + g) * SLD + i * 8 + 2 * t) = pack2(ds[0], ds[1]);
+      *reinterpret_cast<uint32_t*>(sdS + (warp * 16 + g + 8) * SLD + i * 8 + 2 * t) = pack2(ds[2], ds[3]);
+    }
+    // dV_w += P^T dO ;  dK_w += dS^T Q     (contraction over the 64 queries)
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t b[4];
+        ldsm_x4_t(b, cdO + (ks * 16 + (jm & 1) * 8 + rr) * LD + dp * 16 + (jm >> 1) * 8);
+        mma16816(dv[dp * 2], pA[ks], b[0], b[1]);
+        mma16816(dv[dp * 2 + 1], pA[ks], b[2], b[3]);
+        ldsm_x4_t(b, cQ + (ks * 16 + (jm & 1) * 8 + rr) * LD + dp * 16 + (jm >> 1) * 8);
+        mma16816(dk[dp * 2], dsA[ks], b[0], b[1]);
+        mma16816(dk[dp * 2 + 1], dsA[ks], b[2], b[3]);
+      }
+    }
+    __syncthreads();  // sdS complete
+    // dQ_w[16 queries x HD] = dS[16 q x 64 keys] K[64 keys x HD], in two halves of HD
+    float* dq0 = dq_acc + (base + qb * AT_B + warp * 16 + g) * (static_cast<long>(Hq) * HD) + hq * HD;
+    float* dq1 = dq0 + 8L * Hq * HD;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float dq[HD / 16][4];
+#pragma unroll
+      for (int i = 0; i < HD / 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dq[i][j] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t a[4];
+        // A = dS (rows: queries, k: keys) read transposed from sdS[key][query]
+        ldsm_x4_t(a, sdS + (ks * 16 + (jm >> 1) * 8 + rr) * SLD + warp * 16 + (jm & 1) * 8);
+#pragma unroll
+        for (int dp = 0; dp < HD / 32; ++dp) {
+          uint32_t b[4];
+          ldsm_x4_t(b, sK + (ks * 16 + (jm & 1) * 8 + rr) * LD + half * (HD / 2) + dp * 16 + (jm >> 1) * 8);
+          mma16816(dq[dp * 2], a, b[0], b[1]);
+          mma16816(dq[dp * 2 + 1], a, b[2], b[3]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 16; ++i) {
+        const int col = half * (HD / 2) + i * 8 + 2 * t;
+        atomicAdd(reinterpret_cast<float2*>(dq0 + col), make_float2(dq[i][0], dq[i][1]));
+        atomicAdd(reinterpret_cast<float2*>(dq1 + col), make_float2(dq[i][2], dq[i][3]));
+      }
+    }
+    __syncthreads();  // all reads of this iteration's buffers and of sdS are done
+    it = it_next;
+    buf ^= 1;
   }
+  at_wait<0>();
   // write dK, dV (bf16) into the fused gradient buffer
   __nv_bfloat16* dk0 = dqkv + (base + krow0) * ld + (Hq + kvh) * HD;
   __nv_bfloat16* dk1 = dqkv + (base + krow1) * ld + (Hq + kvh) * HD;
@@ -483,7 +510,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
 template <int HD>
 static int fwd_smem() { return (AT_B * (HD + 8) * 5) * 2 + 2 * AT_B * 4; }
 template <int HD>
-static int bwd_smem() { return (AT_B * (HD + 8) * 4 + AT_B * (AT_B + 8)) * 2 + 4 * AT_B * 4; }
+static int bwd_smem() { return (AT_B * (HD + 8) * 6 + AT_B * (AT_B + 8)) * 2 + 8 * AT_B * 4; }
 
 }  // namespace artb
 

@@ -428,3 +428,68 @@ ARTB_EXPORT int artb_adv_norm(const float* rewards, const int* offsets, float* a
   adv_norm_kernel<<<(num_groups + 3) / 4, 128, 0, st>>>(rewards, offsets, adv, keep, num_groups);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------- multi-LoRA slot mask + decode bookkeeping
+namespace artb {
+// T [M, kpad] holds the shrink products of ALL resident adapters side by side (adapter a owns
+// columns [a*cols, (a+1)*cols)).  Zero every column that does not belong to the adapter of the
+// row's request (adapter id < 0 = base model, whole row zero), so that the following extra-K
+// GEMM block adds exactly that request's B_a (A_a x).
+__global__ void lora_slot_mask_kernel(__nv_bfloat16* __restrict__ T, int ld, const int* __restrict__ adapter, long M,
+                                      int kpad, int cols) {
+  const int vec = kpad >> 3;
+  const long total = M * vec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long m = i / vec;
+    const int c = (i % vec) * 8;
+    const int a = adapter[m];
+    const int lo = a * cols, hi = lo + cols;
+    if (a >= 0 && c >= lo && c + 8 <= hi) continue;  // fully inside the live range
+    __nv_bfloat16* p = T + m * ld + c;
+    if (a < 0 || c + 8 <= lo || c >= hi) {
+      *reinterpret_cast<uint4*>(p) = make_uint4(0, 0, 0, 0);
+    } else {
+      for (int j = 0; j < 8; ++j)
+        if (c + j < lo || c + j >= hi) p[j] = __float2bfloat16(0.f);
+    }
+  }
+}
+
+// Advance the per-sequence decode state on the device between the steps of a multi-step run:
+//   tokens <- sampled ; pos += 1 ; ctx_len += 1 ; slot <- block_table[seq][pos / bs] * bs + pos % bs
+// Sequences with active[i] == 0 are frozen (slot = -1 so nothing is written for them).
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, long* __restrict__ tokens,
+                                      int* __restrict__ pos, int* __restrict__ ctx_len, int* __restrict__ slot,
+                                      const int* __restrict__ block_table, int max_blocks, int block_size,
+                                      const int* __restrict__ active, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (active && !active[i]) {
+    slot[i] = -1;
+    return;
+  }
+  tokens[i] = sampled[i];
+  const int p = pos[i] + 1;
+  pos[i] = p;
+  ctx_len[i] = p + 1;
+  const int blk = p / block_size;
+  slot[i] = blk < max_blocks ? block_table[static_cast<size_t>(i) * max_blocks + blk] * block_size + p % block_size : -1;
+}
+}  // namespace artb
+
+ARTB_EXPORT int artb_lora_slot_mask(void* T, int ld, const int* adapter, long M, int kpad, int cols, cudaStream_t st) {
+  if (M <= 0) return 0;
+  if ((kpad & 7) || (ld & 7)) return ERR_BAD_SHAPE;
+  lora_slot_mask_kernel<<<grid_for(M * (kpad / 8), 256), 256, 0, st>>>((bf16*)T, ld, adapter, M, kpad, cols);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_decode_advance(const int* sampled, long* tokens, int* pos, int* ctx_len, int* slot,
+                                    const int* block_table, int max_blocks, int block_size, const int* active, int n,
+                                    cudaStream_t st) {
+  if (n <= 0) return 0;
+  decode_advance_kernel<<<(n + 127) / 128, 128, 0, st>>>(sampled, tokens, pos, ctx_len, slot, block_table, max_blocks,
+                                                        block_size, active, n);
+  return (int)cudaGetLastError();
+}

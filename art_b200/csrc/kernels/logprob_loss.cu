@@ -149,6 +149,111 @@ struct EpiDLogits {
   __device__ void tile_end(const TileInfo&, int) {}
 };
 
+// Sampling epilogue for the rollout engine: temperature-scaled online softmax statistics plus a
+// running Gumbel-max argmax, so one pass over the LM head yields the sampled token and its
+// log-probability under the sampling distribution without materialising logits.
+//   x = logit * inv_temp ;  sample = argmax_v (x_v + g_v),  g_v = -log(-log(u_v)),  u_v = hash(seed, row, v)
+// inv_temp == 0 selects greedy decoding (argmax of the raw logits, log-prob at temperature 1).
+__device__ __forceinline__ uint32_t mix32(uint32_t h) {
+  h ^= h >> 16;
+  h *= 0x85ebca6bu;
+  h ^= h >> 13;
+  h *= 0xc2b2ae35u;
+  h ^= h >> 16;
+  return h;
+}
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t row, uint32_t col) {
+  uint32_t h = mix32(seed ^ (row * 0x9e3779b1u));
+  h = mix32(h ^ (col * 0x85ebca77u) ^ 0x27d4eb2fu);
+  const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -__logf(-__logf(u));
+}
+
+struct EpiSample {
+  float* partials;        // [splits, M, 8]: max, sumexp, best_score, best_idx(bits), best_x, -, -, -
+  const float* inv_temp;  // [M] per-row 1/temperature (0 = greedy)
+  const uint32_t* row_seed;  // [M] per-row seed (request seed mixed with the decode step)
+  int M, V, vocab_offset;
+  float run_max, run_sum, best_score, best_x, it;
+  int best_idx;
+  uint32_t seed;
+
+  __device__ void tile_begin(const TileInfo& ti, int row) {
+    if (ti.first) {
+      run_max = -INFINITY;
+      run_sum = 0.f;
+      best_score = -INFINITY;
+      best_x = 0.f;
+      best_idx = -1;
+      const int gr = ti.m_blk * GEMM_BM + row;
+      it = (gr < M) ? inv_temp[gr] : 0.f;
+      seed = (gr < M) ? row_seed[gr] : 0u;
+    }
+  }
+  __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    const int gc = ti.n_blk * LP_BN + c;
+    if (gc >= V) return;
+    const uint32_t gr = ti.m_blk * GEMM_BM + row;
+    const bool greedy = it == 0.f;
+    const float sc = greedy ? 1.f : it;
+    float cmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(acc[j]) * sc;
+      if (gc + j >= V) x = -INFINITY;
+      acc[j] = __float_as_uint(x);
+      cmax = fmaxf(cmax, x);
+    }
+    const float nmax = fmaxf(run_max, cmax);
+    float ssum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float x = __uint_as_float(acc[j]);
+      ssum += __expf(x - nmax);
+      float score = x;
+      if (!greedy) score += gumbel_noise(seed, gr, static_cast<uint32_t>(vocab_offset + gc + j));
+      if (score > best_score) {
+        best_score = score;
+        best_x = x;
+        best_idx = vocab_offset + gc + j;
+      }
+    }
+    run_sum = run_sum * __expf(run_max - nmax) + ssum;
+    run_max = nmax;
+  }
+  __device__ void tile_end(const TileInfo& ti, int row) {
+    if (!ti.last) return;
+    const int gr = ti.m_blk * GEMM_BM + row;
+    if (gr >= M) return;
+    float* o = partials + (static_cast<size_t>(ti.group) * M + gr) * 8;
+    *reinterpret_cast<float4*>(o) = make_float4(run_max, run_sum, best_score, __int_as_float(best_idx));
+    *reinterpret_cast<float4*>(o + 4) = make_float4(best_x, 0.f, 0.f, 0.f);
+  }
+};
+
+// Merge sampling partials (over vocabulary splits and, for tensor-parallel heads, over ranks'
+// partial buffers laid out back to back): token id and log-prob per row.
+__global__ void sample_merge_kernel(const float* __restrict__ partials, int parts, int M, int* __restrict__ token,
+                                    float* __restrict__ logprob) {
+  const int tI = blockIdx.x * blockDim.x + threadIdx.x;
+  if (tI >= M) return;
+  float mx = -INFINITY;
+  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, partials[(static_cast<size_t>(s) * M + tI) * 8]);
+  float sum = 0.f, best = -INFINITY, bx = 0.f;
+  int bi = -1;
+  for (int s = 0; s < parts; ++s) {
+    const float* p = partials + (static_cast<size_t>(s) * M + tI) * 8;
+    sum += p[1] * __expf(p[0] - mx);
+    if (p[2] > best) {
+      best = p[2];
+      bi = __float_as_int(p[3]);
+      bx = p[4];
+    }
+  }
+  token[tI] = bi;
+  logprob[tI] = bx - (mx + logf(sum));
+}
+
 // Merge vocabulary-split partials and evaluate the per-token GRPO terms.
 //   partials [splits, M, 4];  old_lp may hold NaN (= "sampled under the current policy");
 //   tok_w = weight * mask / normaliser (already shifted to next-token alignment);
@@ -332,4 +437,29 @@ ARTB_EXPORT int artb_logprob_dlogits(const void* H, int ldh, const void* W, int 
   // vocab-split schedule so LM-head tiles are shared through L2 the same way.
   int splits = artb_logprob_splits(M, V);
   return launch_lp(H, ldh, W, ldw, M, V, K, splits, epi, status, stream);
+}
+
+// Rollout sampling: partials [splits, M, 8] for one vocabulary shard (see EpiSample).
+ARTB_EXPORT int artb_sample_partials(const void* H, int ldh, const void* W, int ldw, const float* inv_temp,
+                                     const uint32_t* row_seed, float* partials, int M, int V, int K, int splits,
+                                     int vocab_offset, int* status, cudaStream_t stream) {
+  if (M <= 0 || V <= 0 || (K & 7)) return ERR_BAD_SHAPE;
+  EpiSample epi;
+  epi.partials = partials;
+  epi.inv_temp = inv_temp;
+  epi.row_seed = row_seed;
+  epi.M = M;
+  epi.V = V;
+  epi.vocab_offset = vocab_offset;
+  epi.run_max = epi.run_sum = epi.best_score = epi.best_x = epi.it = 0.f;
+  epi.best_idx = -1;
+  epi.seed = 0;
+  return launch_lp(H, ldh, W, ldw, M, V, K, splits, epi, status, stream);
+}
+
+ARTB_EXPORT int artb_sample_merge(const float* partials, int parts, int M, int* token, float* logprob,
+                                  cudaStream_t stream) {
+  if (M <= 0) return 0;
+  sample_merge_kernel<<<(M + 127) / 128, 128, 0, stream>>>(partials, parts, M, token, logprob);
+  return static_cast<int>(cudaGetLastError());
 }

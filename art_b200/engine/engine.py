@@ -1,0 +1,397 @@
+"""Continuous-batching rollout engine.
+
+A background thread owns the model runner and loops: admit waiting requests (prefill, with
+prefix-cache reuse), otherwise advance every running sequence by up to ``num_scheduler_steps``
+tokens in one device-side multi-step decode, then publish tokens to the per-request asyncio
+queues.  ``pause()`` / ``resume()`` bracket a training phase: the loop stops at a step
+boundary, in-flight requests keep their KV (or have it offloaded / discarded according to the
+sleep level) and continue afterwards under whatever adapter weights are then loaded, which is
+the observable behaviour of the reference's train/infer time-sharing
+(``src/art/local/state.py:146-171``, ``src/art/local/vllm.py:115-145``) without its event-racing
+gate.  Adapters are addressed by name (LoRA-by-name routing, ``src/art/dev/openai_server.py:17-23``);
+loading one is a device-to-device copy into a slot (``service.py:164-174`` goes through disk).
+"""
+from __future__ import annotations
+
+import asyncio
+import itertools
+import threading
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import AsyncIterator
+
+from .kv_cache import BlockManager
+from .runner import SeqView
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 16
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    n: int = 1
+    stop: list[str] | None = None
+    stop_token_ids: list[int] | None = None
+    seed: int | None = None
+    ignore_eos: bool = False
+    guided_choice: list[str] | None = None
+
+
+@dataclass
+class TokenEvent:
+    token_id: int
+    logprob: float
+    finished: bool = False
+    finish_reason: str | None = None
+
+
+class Sequence:
+    _ids = itertools.count(1)
+
+    def __init__(self, prompt_ids: list[int], params: SamplingParams, adapter: int, loop: asyncio.AbstractEventLoop | None):
+        self.id = next(Sequence._ids)
+        self.prompt_ids = list(prompt_ids)
+        self.output_ids: list[int] = []
+        self.logprobs: list[float] = []
+        self.params = params
+        self.adapter = adapter
+        self.blocks: list[int] = []
+        self.num_cached = 0
+        self.finished = False
+        self.finish_reason: str | None = None
+        self.aborted = False
+        self.loop = loop
+        self.queue: asyncio.Queue | None = asyncio.Queue() if loop is not None else None
+        self.seed = params.seed if params.seed is not None else (self.id * 2654435761) & 0x7FFFFFFF
+        self.arrival = time.monotonic()
+        self.forced: deque[int] = deque()     # guided decoding: tokens to emit verbatim
+        self.done_event = threading.Event()
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt_ids + self.output_ids
+
+    def view(self) -> SeqView:
+        return SeqView(self.tokens, self.num_cached, self.blocks, self.adapter, self.params.temperature, self.seed,
+                       len(self.output_ids))
+
+
+@dataclass
+class EngineStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_steps: int = 0
+    decode_steps: int = 0
+    preemptions: int = 0
+    started: float = field(default_factory=time.monotonic)
+
+
+class Engine:
+    def __init__(self, runner, block_manager: BlockManager, *, eos_token_id: int | None, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 16384, num_scheduler_steps: int = 16, max_model_len: int = 32768,
+                 max_loras: int = 4, kv_cache=None):
+        self.runner, self.bm, self.kv = runner, block_manager, kv_cache
+        self.eos = eos_token_id
+        self.max_num_seqs, self.max_batched = max_num_seqs, max_num_batched_tokens
+        self.n_steps, self.max_model_len = max(1, num_scheduler_steps), max_model_len
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self.adapters: dict[str, int] = {}
+        self.adapter_version = [0] * max_loras
+        self.max_loras = max_loras
+        self.stats = EngineStats()
+        self._lock = threading.Lock()
+        self._wake = threading.Event()
+        self._run_gate = threading.Event()
+        self._run_gate.set()
+        self._step_lock = threading.Lock()
+        self._stop = False
+        self._thread: threading.Thread | None = None
+        self.error: BaseException | None = None
+
+    # -- adapters ---------------------------------------------------------------------------------
+    def set_adapter(self, name: str, state: dict | None) -> int:
+        """Load (or replace) the adapter served under ``name``; returns its slot.  Call while paused or idle."""
+        if name in self.adapters:
+            slot = self.adapters[name]
+        else:
+            used = set(self.adapters.values())
+            free = [s for s in range(self.max_loras) if s not in used]
+            if not free:
+                raise RuntimeError(f"all {self.max_loras} adapter slots are in use")
+            slot = free[0]
+            self.adapters[name] = slot
+        self.runner.set_adapter(slot, state)
+        self.adapter_version[slot] += 1   # new salt: KV computed under the old weights is not reused
+        return slot
+
+    def remove_adapter(self, name: str) -> None:
+        slot = self.adapters.pop(name, None)
+        if slot is not None:
+            self.runner.set_adapter(slot, None)
+            self.adapter_version[slot] += 1
+
+    def _salt(self, adapter: int) -> int:
+        return 0x51 if adapter < 0 else (adapter + 1) * 1_000_003 + self.adapter_version[adapter]
+
+    # -- lifecycle --------------------------------------------------------------------------------
+    def start(self) -> None:
+        if self._thread is None:
+            self._thread = threading.Thread(target=self._loop, name="art-b200-engine", daemon=True)
+            self._thread.start()
+
+    def shutdown(self) -> None:
+        self._stop = True
+        self._run_gate.set()
+        self._wake.set()
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+            self._thread = None
+
+    def pause(self, timeout: float = 600.0) -> None:
+        """Stop stepping at the next step boundary and wait until the loop is parked."""
+        self._run_gate.clear()
+        self._wake.set()
+        if not self._step_lock.acquire(timeout=timeout):   # waits for the step in progress, if any
+            raise TimeoutError("engine did not reach a step boundary")
+        self._step_lock.release()
+
+    def resume(self) -> None:
+        self._run_gate.set()
+        self._wake.set()
+
+    @property
+    def has_unfinished(self) -> bool:
+        with self._lock:
+            return bool(self.waiting or self.running)
+
+    def sleep(self, level: int = 1) -> None:
+        """Release KV memory while paused: level 1 keeps contents on the host when requests are in
+        flight, level 2 discards (and forgets the prefix cache)."""
+        if self.kv is None:
+            return
+        if level == 1 and self.has_unfinished:
+            self.kv.offload()
+        else:
+            self.reset_prefix_cache()
+            self.kv.discard()
+            with self._lock:   # KV of in-flight sequences is gone: recompute them from their tokens
+                for s in self.running:
+                    self.bm.free(s.blocks)
+                    s.blocks, s.num_cached = [], 0
+                    self.waiting.appendleft(s)
+                self.running = []
+
+    def wake_up(self) -> None:
+        if self.kv is not None:
+            self.kv.restore()
+
+    def reset_prefix_cache(self) -> None:
+        self.bm.reset_prefix_cache()
+
+    # -- requests ---------------------------------------------------------------------------------
+    def add_request(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None,
+                    loop: asyncio.AbstractEventLoop | None = None) -> Sequence:
+        if self.error is not None:
+            raise RuntimeError("engine stopped after an error") from self.error
+        if len(prompt_ids) + 1 > self.max_model_len:
+            raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_model_len}")
+        adapter = -1
+        if adapter_name is not None:
+            if adapter_name not in self.adapters:
+                raise KeyError(f"unknown adapter {adapter_name!r}")
+            adapter = self.adapters[adapter_name]
+        seq = Sequence(prompt_ids, params, adapter, loop)
+        with self._lock:
+            self.waiting.append(seq)
+        self._wake.set()
+        return seq
+
+    def abort(self, seq: Sequence) -> None:
+        seq.aborted = True
+        self._wake.set()
+
+    async def generate(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None
+                       ) -> AsyncIterator[TokenEvent]:
+        """Async stream of sampled tokens for one request; cancelling the consumer aborts the request."""
+        seq = self.add_request(prompt_ids, params, adapter_name, asyncio.get_running_loop())
+        try:
+            while True:
+                ev = await seq.queue.get()
+                if isinstance(ev, BaseException):
+                    raise ev
+                yield ev
+                if ev.finished:
+                    return
+        finally:
+            if not seq.finished:
+                self.abort(seq)
+
+    def generate_sync(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None) -> Sequence:
+        """Blocking helper (tests, benchmarks): drives the loop inline if no thread is running."""
+        seq = self.add_request(prompt_ids, params, adapter_name, None)
+        if self._thread is None:
+            while not seq.finished:
+                self.step()
+        else:
+            seq.done_event.wait()
+        return seq
+
+    # -- scheduling -------------------------------------------------------------------------------
+    def _emit(self, seq: Sequence, tok: int, lp: float) -> None:
+        seq.output_ids.append(tok)
+        seq.logprobs.append(lp)
+        self.stats.generated_tokens += 1
+        p = seq.params
+        reason = None
+        if not p.ignore_eos and self.eos is not None and tok == self.eos:
+            reason = "stop"
+        elif p.stop_token_ids and tok in p.stop_token_ids:
+            reason = "stop"
+        elif len(seq.output_ids) >= p.max_tokens or len(seq.prompt_ids) + len(seq.output_ids) >= self.max_model_len:
+            reason = "length"
+        if reason:
+            seq.finished, seq.finish_reason = True, reason
+        ev = TokenEvent(tok, lp, seq.finished, reason)
+        if seq.loop is not None:
+            seq.loop.call_soon_threadsafe(seq.queue.put_nowait, ev)
+
+    def _release(self, seq: Sequence) -> None:
+        if seq.blocks:
+            toks = seq.tokens
+            self.bm.commit(seq.blocks, toks[: len(toks) - 1], self._salt(seq.adapter))
+            self.bm.free(seq.blocks)
+            seq.blocks = []
+        seq.done_event.set()
+
+    def _blocks_needed(self, n_tokens: int) -> int:
+        bs = self.bm.block_size
+        return (n_tokens + bs - 1) // bs
+
+    def _admit(self) -> list[Sequence]:
+        """Pick waiting sequences for one prefill step (FCFS, bounded by tokens, seqs and free blocks)."""
+        picked: list[Sequence] = []
+        budget = self.max_batched
+        with self._lock:
+            while self.waiting and len(self.running) + len(picked) < self.max_num_seqs:
+                seq = self.waiting[0]
+                if seq.aborted:
+                    self.waiting.popleft()
+                    seq.finished, seq.finish_reason = True, "abort"
+                    seq.done_event.set()
+                    continue
+                toks = seq.tokens
+                cached = self.bm.match_prefix(toks[:-1], self._salt(seq.adapter))   # always recompute the last token
+                n_new = len(toks) - len(cached) * self.bm.block_size
+                if n_new > budget and picked:
+                    self.bm.free(cached)
+                    break
+                need = self._blocks_needed(len(toks) + 1) - len(cached)
+                fresh = self.bm.alloc(need)
+                if fresh is None:
+                    self.bm.free(cached)
+                    break
+                self.waiting.popleft()
+                seq.blocks = cached + fresh
+                seq.num_cached = len(cached) * self.bm.block_size
+                picked.append(seq)
+                budget -= n_new
+        return picked
+
+    def _ensure_decode_blocks(self, steps: int) -> int:
+        """Give every running sequence room for ``steps`` more tokens; preempt the newest if needed."""
+        while True:
+            steps = max(1, steps)
+            short = []
+            for s in self.running:
+                need = self._blocks_needed(len(s.tokens) + steps) - len(s.blocks)
+                if need > 0:
+                    short.append((s, need))
+            total = sum(n for _, n in short)
+            if total <= self.bm.num_free:
+                for s, n in short:
+                    s.blocks += self.bm.alloc(n)
+                return steps
+            if steps > 1:
+                steps = 1
+                continue
+            victim = self.running.pop()   # newest: recompute later
+            self.bm.free(victim.blocks)
+            victim.blocks, victim.num_cached = [], 0
+            with self._lock:
+                self.waiting.appendleft(victim)
+            self.stats.preemptions += 1
+            if not self.running:
+                return 0
+
+    def step(self) -> bool:
+        """One scheduler iteration.  Returns False when there was nothing to do."""
+        for s in [s for s in self.running if s.aborted and not s.finished]:
+            s.finished, s.finish_reason = True, "abort"
+        done = [s for s in self.running if s.finished]
+        if done:
+            self.running = [s for s in self.running if not s.finished]
+            for s in done:
+                self._release(s)
+        new = self._admit()
+        if new:
+            self.stats.prefill_steps += 1
+            self.stats.prompt_tokens += sum(len(s.tokens) - s.num_cached for s in new)
+            toks, lps = self.runner.prefill([s.view() for s in new])
+            for s, t, lp in zip(new, toks, lps):
+                if s.forced:
+                    t = s.forced.popleft()
+                s.num_cached = 0
+                self._emit(s, t, lp)
+                self.running.append(s)
+            return True
+        if not self.running:
+            return False
+        remaining = min(s.params.max_tokens - len(s.output_ids) for s in self.running)
+        steps = self._ensure_decode_blocks(min(self.n_steps, max(1, remaining)))
+        if steps == 0 or not self.running:
+            return True
+        if any(s.forced for s in self.running):
+            steps = 1
+        self.stats.decode_steps += steps
+        toks, lps = self.runner.decode([s.view() for s in self.running], steps)
+        for k in range(steps):
+            for i, s in enumerate(self.running):
+                if s.finished:
+                    continue
+                t = toks[k][i]
+                if s.forced:
+                    t = s.forced.popleft()
+                self._emit(s, t, lps[k][i])
+        return True
+
+    def _loop(self) -> None:
+        try:
+            while not self._stop:
+                self._run_gate.wait()
+                with self._step_lock:
+                    if self._stop or not self._run_gate.is_set():
+                        continue
+                    worked = self.step()
+                if not worked:
+                    self._wake.wait(timeout=0.05)
+                    self._wake.clear()
+        except BaseException as e:  # noqa: BLE001 - report to every waiter, then stop
+            self.error = e
+            with self._lock:
+                seqs = list(self.waiting) + self.running
+            for s in seqs:
+                if s.loop is not None:
+                    s.loop.call_soon_threadsafe(s.queue.put_nowait, e)
+                s.finished = True
+                s.done_event.set()
+
+    def metrics(self) -> dict:
+        st = self.bm.stats()
+        dt = max(1e-9, time.monotonic() - self.stats.started)
+        return {"running": len(self.running), "waiting": len(self.waiting), "prompt_tokens": self.stats.prompt_tokens,
+                "generated_tokens": self.stats.generated_tokens, "preemptions": self.stats.preemptions,
+                "kv_free_blocks": self.bm.num_free, "kv_total_blocks": self.bm.num_blocks,
+                "kv_utilisation": 1.0 - self.bm.num_free / self.bm.num_blocks, "tokens_per_s": self.stats.generated_tokens / dt, **st}

@@ -1,0 +1,332 @@
+"""Model execution for the rollout engine.
+
+``NativeRunner``    sm_100a path.  Shares the frozen base weights with the trainer's
+                    :class:`models.native.NativeDecoder` when both live in one process, holds
+                    ``max_loras`` resident adapters side by side in the extra-K operands of
+                    every projection (adapter ``a`` owns a column range of ``T = X A_all^T``; a
+                    per-row mask keeps only the requesting adapter's columns, so one GEMM serves
+                    a batch that mixes adapters and the base model), writes K/V into the paged
+                    cache, and samples with the fused LM-head sampler.  Decode runs several steps
+                    back to back on the device before the host looks at the tokens.
+``ReferenceRunner`` plain PyTorch, no KV cache (recomputes the prefix); used for CPU tests of
+                    the scheduler / server / backend and as a numerical oracle.
+
+Both return ``(token_ids, logprobs)`` as Python lists so the scheduler is device-agnostic.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import LoraConfig, lora_key
+
+
+@dataclass
+class SeqView:
+    """What a runner needs to know about one scheduled sequence."""
+    tokens: list[int]          # prompt + generated so far
+    num_cached: int            # tokens whose KV is already in the cache (multiple of block_size)
+    blocks: list[int]          # block table
+    adapter: int               # adapter slot, -1 = base model
+    temperature: float
+    seed: int
+    step: int                  # number of tokens generated so far (mixes into the sampling seed)
+
+
+def _mix_seed(seed: int, step: int) -> int:
+    return (seed * 0x9E3779B1 + step * 0x85EBCA77 + 0x165667B1) & 0xFFFFFFFF
+
+
+# ------------------------------------------------------------------------------- reference
+class ReferenceRunner:
+    def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig, max_loras: int = 4,
+                 device: str | torch.device = "cpu"):
+        from ..models.reference import ReferenceModel
+
+        self.cfg, self.lora_cfg, self.device = cfg, lora_cfg, torch.device(device)
+        self.base = {k: v.to(self.device) for k, v in base.items()}
+        self.adapters: list[dict[str, torch.Tensor] | None] = [None] * max_loras
+        self._model = ReferenceModel(cfg, self.base, {}, lora_cfg)
+
+    def set_adapter(self, slot: int, state: dict[str, torch.Tensor] | None) -> None:
+        self.adapters[slot] = None if state is None else {k: v.detach().to(self.device).float() for k, v in state.items()}
+
+    def _next(self, sv: SeqView) -> tuple[int, float]:
+        m = self._model
+        m.lora = self.adapters[sv.adapter] if sv.adapter >= 0 and self.adapters[sv.adapter] is not None else {}
+        toks = torch.tensor([sv.tokens], device=self.device)
+        z = torch.zeros_like(toks)
+        with torch.no_grad():
+            h = m.hidden_states(toks, z, z, None)[:, -1]
+            logits = (h.float() @ self.base["lm_head.weight"].float().t())[0]
+        if sv.temperature <= 0:
+            lp = torch.log_softmax(logits, -1)
+            t = int(lp.argmax())
+            return t, float(lp[t])
+        lp = torch.log_softmax(logits / sv.temperature, -1)
+        g = torch.Generator(device="cpu").manual_seed(_mix_seed(sv.seed, sv.step))
+        t = int(torch.multinomial(lp.exp().cpu(), 1, generator=g))
+        return t, float(lp[t])
+
+    def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
+        out = [self._next(s) for s in seqs]
+        return [o[0] for o in out], [o[1] for o in out]
+
+    def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
+        toks: list[list[int]] = []
+        lps: list[list[float]] = []
+        work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step) for s in seqs]
+        for _ in range(n_steps):
+            step_t, step_l = [], []
+            for s in work:
+                t, lp = self._next(s)
+                s.tokens.append(t)
+                s.step += 1
+                step_t.append(t)
+                step_l.append(lp)
+            toks.append(step_t)
+            lps.append(step_l)
+        return toks, lps
+
+
+# ---------------------------------------------------------------------------------- native
+class EngineLinear:
+    """A frozen projection plus ``max_loras`` adapter slots packed into the extra-K operands."""
+
+    def __init__(self, W: torch.Tensor, bias: torch.Tensor | None, member_rows: list[tuple[str, torch.Tensor]],
+                 r: int, max_loras: int):
+        self.W, self.bias = W, bias
+        self.members = member_rows                      # [(module name, row indices in the fused weight)]
+        self.r = r
+        self.cols = len(member_rows) * r                # columns per adapter
+        self.kpad = max(64, (max_loras * self.cols + 63) // 64 * 64)
+        N, K = W.shape
+        self.A_all = torch.zeros(self.kpad, K, dtype=torch.bfloat16, device=W.device)
+        self.B_all = torch.zeros(N, self.kpad, dtype=torch.bfloat16, device=W.device)
+
+    def load_slot(self, slot: int, layer: int, state: dict[str, torch.Tensor] | None, scale: float) -> None:
+        c0 = slot * self.cols
+        self.A_all[c0:c0 + self.cols].zero_()
+        self.B_all[:, c0:c0 + self.cols].zero_()
+        if state is None:
+            return
+        for j, (module, rows) in enumerate(self.members):
+            ka = lora_key(layer, module, "A")
+            if ka not in state:
+                continue
+            a, b = state[ka], state[lora_key(layer, module, "B")]
+            c = c0 + j * self.r
+            self.A_all[c:c + self.r] = a           # device-to-device copy straight from the trainer's master buffer
+            self.B_all[rows, c:c + self.r] = (b * scale).to(torch.bfloat16)
+
+    def __call__(self, x, adapter_ids, any_lora: bool, residual=None, swiglu_out=None):
+        from ..ops.gemm import gemm_tn
+        from ..ops.paged import lora_slot_mask_
+
+        bn = 64 if x.shape[0] <= 512 else 0
+        if any_lora:
+            T = gemm_tn(x, self.A_all, bn=64)
+            lora_slot_mask_(T, adapter_ids, self.cols)
+            return gemm_tn(x, self.W, a2=T, b2=self.B_all, residual=residual, swiglu_out=swiglu_out, bias=self.bias, bn=bn)
+        return gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out, bias=self.bias, bn=bn)
+
+
+class NativeRunner:
+    def __init__(self, cfg: ModelConfig, lora_cfg: LoraConfig, kv, *, decoder=None, base: dict | None = None,
+                 max_loras: int = 4, device="cuda"):
+        """``decoder``: a trainer-side NativeDecoder whose frozen weights are shared; else ``base`` weights."""
+        from ..ops import elementwise as ew
+
+        self.cfg, self.lora_cfg, self.kv, self.max_loras = cfg, lora_cfg, kv, max_loras
+        self.device = torch.device(device)
+        dev, bf = self.device, torch.bfloat16
+        if decoder is None:
+            from ..models.native import LoraLinear  # reuse the fused-weight construction without LoRA members
+
+            assert base is not None
+
+            class _Shim:
+                pass
+
+            decoder = _Shim()
+            decoder.embed = base["model.embed_tokens.weight"].to(dev, bf).contiguous()
+            decoder.lm_head = base["lm_head.weight"].to(dev, bf).contiguous()
+            decoder.final_norm = base["model.norm.weight"].to(dev, bf).contiguous()
+            decoder.layers = []
+            for i in range(cfg.num_layers):
+                p = f"model.layers.{i}."
+                W = lambda n: base[p + n + ".weight"].to(dev, bf)  # noqa: E731
+                wqkv = torch.cat([W("self_attn.q_proj"), W("self_attn.k_proj"), W("self_attn.v_proj")], 0)
+                bqkv = (torch.cat([base[p + f"self_attn.{n}.bias"].to(dev) for n in ("q_proj", "k_proj", "v_proj")])
+                        if cfg.qkv_bias else None)
+                layer = {"qkv": LoraLinear(wqkv, bqkv, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
+                         "o": LoraLinear(W("self_attn.o_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
+                         "gu": LoraLinear(ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj")), None, [],
+                                          lora_cfg.r, lora_cfg.scale, need_dgrad=False),
+                         "down": LoraLinear(W("mlp.down_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
+                         "ln1": base[p + "input_layernorm.weight"].to(dev, bf).contiguous(),
+                         "ln2": base[p + "post_attention_layernorm.weight"].to(dev, bf).contiguous()}
+                if cfg.qk_norm:
+                    layer["q_norm"] = base[p + "self_attn.q_norm.weight"].to(dev, bf).contiguous()
+                    layer["k_norm"] = base[p + "self_attn.k_norm.weight"].to(dev, bf).contiguous()
+                decoder.layers.append(layer)
+        self.embed, self.lm_head, self.final_norm = decoder.embed, decoder.lm_head, decoder.final_norm
+        q, kvw, d, F = cfg.q_size, cfg.kv_size, cfg.hidden_size, cfg.intermediate_size
+        ar = lambda a, b: torch.arange(a, b, device=dev)  # noqa: E731
+        fidx = torch.arange(F, device=dev)
+        gate_rows = (fidx // 16) * 32 + fidx % 16
+        r = lora_cfg.r
+        self.layers = []
+        for i, L in enumerate(decoder.layers):
+            self.layers.append({
+                "qkv": EngineLinear(L["qkv"].W, L["qkv"].bias, [("self_attn.q_proj", ar(0, q)), ("self_attn.k_proj", ar(q, q + kvw)),
+                                                               ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw))], r, max_loras),
+                "o": EngineLinear(L["o"].W, None, [("self_attn.o_proj", ar(0, d))], r, max_loras),
+                "gu": EngineLinear(L["gu"].W, None, [("mlp.gate_proj", gate_rows), ("mlp.up_proj", gate_rows + 16)], r, max_loras),
+                "down": EngineLinear(L["down"].W, None, [("mlp.down_proj", ar(0, d))], r, max_loras),
+                "ln1": L["ln1"], "ln2": L["ln2"], "q_norm": L.get("q_norm"), "k_norm": L.get("k_norm"),
+            })
+        self.slot_loaded = [False] * max_loras
+
+    # -- adapters -----------------------------------------------------------------------------
+    def set_adapter(self, slot: int, state: dict[str, torch.Tensor] | None) -> None:
+        """In-device hand-off: copy (and re-lay-out) LoRA factors into adapter slot ``slot``.
+
+        ``state`` tensors may be views of the trainer's flat fp32 master buffer; nothing touches
+        the host or the disk.  The engine must be between steps (callers pause it first).
+        """
+        for i, L in enumerate(self.layers):
+            for k in ("qkv", "o", "gu", "down"):
+                L[k].load_slot(slot, i, state, self.lora_cfg.scale)
+        self.slot_loaded[slot] = state is not None
+
+    # -- shared layer body ----------------------------------------------------------------------
+    def _mlp(self, L, x2, adapter_ids, any_lora):
+        from ..ops import elementwise as ew
+
+        h2, _ = ew.rmsnorm_fwd(x2, L["ln2"], self.cfg.rms_norm_eps, want_rstd=False)
+        hact = torch.empty((x2.shape[0], self.cfg.intermediate_size), dtype=x2.dtype, device=x2.device)
+        L["gu"](h2, adapter_ids, any_lora, swiglu_out=hact)
+        return L["down"](hact, adapter_ids, any_lora, residual=x2)
+
+    def _qkv(self, L, x, pos, adapter_ids, any_lora):
+        from ..ops import elementwise as ew
+
+        cfg = self.cfg
+        h1, _ = ew.rmsnorm_fwd(x, L["ln1"], cfg.rms_norm_eps, want_rstd=False)
+        qkv = L["qkv"](h1, adapter_ids, any_lora)
+        if cfg.qk_norm:
+            ew.headnorm_fwd_(qkv, L["q_norm"], 0, cfg.num_heads, cfg.head_dim, cfg.rms_norm_eps)
+            ew.headnorm_fwd_(qkv, L["k_norm"], cfg.q_size, cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+        ew.rope_(qkv, pos, 0, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta)
+        return qkv
+
+    # -- prefill ------------------------------------------------------------------------------------
+    def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
+        from ..ops import attention as attn_ops
+        from ..ops import elementwise as ew
+        from ..ops import paged
+
+        cfg, dev, bs = self.cfg, self.device, self.kv.shape[1]
+        tok, pos, gid, adapter, slot, new_rows, last_rows = [], [], [], [], [], [], []
+        cached_spans = []   # (att_row_start, n_cached, blocks)
+        att = 0
+        for i, s in enumerate(seqs):
+            n = len(s.tokens)
+            nc = s.num_cached
+            if nc:
+                cached_spans.append((att, nc, s.blocks))
+                gid += [i] * nc
+                att += nc
+            for t in range(nc, n):
+                tok.append(s.tokens[t])
+                pos.append(t)
+                adapter.append(s.adapter)
+                slot.append(s.blocks[t // bs] * bs + t % bs)
+                new_rows.append(att)
+                gid.append(i)
+                att += 1
+            last_rows.append(len(tok) - 1)
+        M = len(tok)
+        S_att = (att + 63) // 64 * 64
+        gid += [-(j + 1) for j in range(S_att - att)]
+        any_lora = any(a >= 0 for a in adapter)
+        use_index = bool(cached_spans) or S_att != M
+        t_tok = torch.tensor(tok, dtype=torch.int64, device=dev)
+        t_pos = torch.tensor(pos, dtype=torch.int32, device=dev)
+        t_ad = torch.tensor(adapter, dtype=torch.int32, device=dev)
+        t_slot = torch.tensor(slot, dtype=torch.int32, device=dev)
+        t_gid = torch.tensor(gid, dtype=torch.int32, device=dev)
+        t_rows = torch.tensor(new_rows, dtype=torch.int64, device=dev)
+        plan = attn_ops.make_plan(t_gid, t_gid, S_att, "native")
+        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        x = ew.gather_rows(self.embed, t_tok)
+        span_tables = [(a0, nc, torch.tensor(bl, dtype=torch.int32, device=dev)) for a0, nc, bl in cached_spans]
+        for li, L in enumerate(self.layers):
+            qkv = self._qkv(L, x, t_pos, t_ad, any_lora)
+            paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, t_slot, self.kv.k[li], self.kv.v[li])
+            if use_index:
+                buf = torch.zeros((S_att, qkv.shape[1]), dtype=qkv.dtype, device=dev)
+                buf.index_copy_(0, t_rows, qkv)
+                for a0, nc, bt in span_tables:
+                    paged.kv_gather(self.kv.k[li], self.kv.v[li], bt, bs, nc, buf[a0:], cfg.q_size, cfg.q_size + cfg.kv_size)
+                o_all, _ = attn_ops.forward(buf, Hq, Hkv, hd, plan, need_grad=False)
+                o = o_all.index_select(0, t_rows)
+            else:
+                o, _ = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=False)
+            x2 = L["o"](o, t_ad, any_lora, residual=x)
+            x = self._mlp(L, x2, t_ad, any_lora)
+        t_last = torch.tensor(last_rows, dtype=torch.int64, device=dev)
+        hl = ew.gather_rows(x, t_last)
+        hidden, _ = ew.rmsnorm_fwd(hl, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
+        inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
+        seeds = torch.tensor([_mix_seed(s.seed, s.step) for s in seqs], dtype=torch.int64, device=dev).to(torch.int32)
+        t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
+        return t.tolist(), lp.tolist()
+
+    # -- decode -------------------------------------------------------------------------------------
+    def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
+        from ..ops import elementwise as ew
+        from ..ops import paged
+
+        cfg, dev, bs = self.cfg, self.device, self.kv.shape[1]
+        n = len(seqs)
+        max_blocks = max(len(s.blocks) for s in seqs)
+        bt = torch.zeros((n, max_blocks), dtype=torch.int32)
+        for i, s in enumerate(seqs):
+            bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+        bt = bt.to(dev, non_blocking=True)
+        lens = [len(s.tokens) for s in seqs]
+        tokens = torch.tensor([s.tokens[-1] for s in seqs], dtype=torch.int64, device=dev)
+        pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
+        ctx = torch.tensor(lens, dtype=torch.int32, device=dev)
+        slot = torch.tensor([s.blocks[(l - 1) // bs] * bs + (l - 1) % bs for s, l in zip(seqs, lens)], dtype=torch.int32, device=dev)
+        ad = torch.tensor([s.adapter for s in seqs], dtype=torch.int32, device=dev)
+        any_lora = any(s.adapter >= 0 for s in seqs)
+        inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
+        seeds = torch.tensor([[_mix_seed(s.seed, s.step + k) for s in seqs] for k in range(n_steps)], dtype=torch.int64,
+                             device=dev).to(torch.int32)
+        out_t = torch.empty((n_steps, n), dtype=torch.int32, device=dev)
+        out_l = torch.empty((n_steps, n), dtype=torch.float32, device=dev)
+        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        max_ctx = max(lens) + n_steps
+        splits = 1 if n * Hkv >= 128 else min(8, max(1, max_ctx // 512))
+        ws = torch.empty(n * Hq * splits * (hd + 2), dtype=torch.float32, device=dev) if splits > 1 else None
+        attn_out = torch.empty((n, cfg.q_size), dtype=torch.bfloat16, device=dev)
+        for k in range(n_steps):
+            x = ew.gather_rows(self.embed, tokens)
+            for li, L in enumerate(self.layers):
+                qkv = self._qkv(L, x, pos, ad, any_lora)
+                paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, slot, self.kv.k[li], self.kv.v[li])
+                paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], bt, ctx, Hq, Hkv, hd, attn_out, splits, ws)
+                x2 = L["o"](attn_out, ad, any_lora, residual=x)
+                x = self._mlp(L, x2, ad, any_lora)
+            hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
+            t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds[k])
+            out_t[k], out_l[k] = t, lp
+            if k + 1 < n_steps:
+                paged.decode_advance(t, tokens, pos, ctx, slot, bt, bs)
+        return out_t.tolist(), out_l.tolist()

@@ -1,0 +1,92 @@
+"""Front-ends for the rollout-engine kernels: KV-cache write/gather, paged decode attention,
+multi-LoRA slot mask, fused LM-head sampler, device-side decode bookkeeping."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+_sigs = {
+    "artb_kv_write": [vp, ci, ci, ci, vp, vp, vp, ci, ci, vp],
+    "artb_kv_gather": [vp, vp, vp, ci, ci, vp, ci, ci, ci, ci, vp],
+    "artb_paged_decode": [vp, ci, vp, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp],
+    "artb_lora_slot_mask": [vp, ci, vp, cl, ci, ci, vp],
+    "artb_decode_advance": [vp, vp, vp, vp, vp, vp, ci, ci, vp, ci, vp],
+    "artb_sample_partials": [vp, ci, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
+    "artb_sample_merge": [vp, ci, ci, vp, vp, vp],
+    "artb_logprob_splits": [ci, ci],
+}
+_bound: dict[str, object] = {}
+
+
+def _f(name: str):
+    fn = _bound.get(name)
+    if fn is None:
+        fn = getattr(_lib.kernels(), name)
+        fn.argtypes = _sigs[name]
+        fn.restype = ci
+        _bound[name] = fn
+    return fn
+
+
+def kv_write(qkv: torch.Tensor, k_col: int, v_col: int, slot: torch.Tensor, k_cache: torch.Tensor,
+             v_cache: torch.Tensor) -> None:
+    kv_width = k_cache.shape[-2] * k_cache.shape[-1]
+    _lib.check_rc(_f("artb_kv_write")(_lib.ptr(qkv), qkv.stride(0), k_col, v_col, _lib.ptr(slot), _lib.ptr(k_cache),
+                                      _lib.ptr(v_cache), qkv.shape[0], kv_width, _lib.stream_ptr()), "kv_write")
+
+
+def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table_row: torch.Tensor, block_size: int, n_tok: int,
+              dst: torch.Tensor, k_col: int, v_col: int) -> None:
+    kv_width = k_cache.shape[-2] * k_cache.shape[-1]
+    _lib.check_rc(_f("artb_kv_gather")(_lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(block_table_row), block_size,
+                                       n_tok, _lib.ptr(dst), dst.stride(0), k_col, v_col, kv_width,
+                                       _lib.stream_ptr()), "kv_gather")
+
+
+def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                 ctx_len: torch.Tensor, Hq: int, Hkv: int, hd: int, out: torch.Tensor, splits: int = 1,
+                 ws: torch.Tensor | None = None) -> torch.Tensor:
+    """q [n, >=Hq*hd] (row stride arbitrary), caches [blocks, block_size, Hkv, hd]; out [n, Hq*hd]."""
+    n = q.shape[0]
+    block_size = k_cache.shape[1]
+    if splits > 1 and ws is None:
+        ws = torch.empty(n * Hq * splits * (hd + 2), dtype=torch.float32, device=q.device)
+    _lib.check_rc(_f("artb_paged_decode")(_lib.ptr(q), q.stride(0), _lib.ptr(k_cache), _lib.ptr(v_cache),
+                                          _lib.ptr(block_table), block_table.stride(0), _lib.ptr(ctx_len), block_size,
+                                          n, Hq, Hkv, hd, _lib.ptr(out), out.stride(0), _lib.ptr(ws), splits,
+                                          _lib.stream_ptr()), "paged_decode")
+    return out
+
+
+def lora_slot_mask_(T: torch.Tensor, adapter: torch.Tensor, cols_per_adapter: int) -> torch.Tensor:
+    _lib.check_rc(_f("artb_lora_slot_mask")(_lib.ptr(T), T.stride(0), _lib.ptr(adapter), T.shape[0], T.shape[1],
+                                            cols_per_adapter, _lib.stream_ptr()), "lora_slot_mask")
+    return T
+
+
+def decode_advance(sampled, tokens, pos, ctx_len, slot, block_table, block_size: int, active=None) -> None:
+    _lib.check_rc(_f("artb_decode_advance")(_lib.ptr(sampled), _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(ctx_len),
+                                            _lib.ptr(slot), _lib.ptr(block_table), block_table.stride(0), block_size,
+                                            _lib.ptr(active), tokens.numel(), _lib.stream_ptr()), "decode_advance")
+
+
+def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
+           vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Fused LM head + Gumbel-max sampling.  Returns (token int32 [M], logprob fp32 [M])."""
+    M, K = hidden.shape
+    V = lm_head.shape[0]
+    splits = _f("artb_logprob_splits")(M, V)
+    part = torch.empty((splits, M, 8), dtype=torch.float32, device=hidden.device)
+    _lib.check_rc(_f("artb_sample_partials")(_lib.ptr(hidden), hidden.stride(0), _lib.ptr(lm_head), lm_head.stride(0),
+                                             _lib.ptr(inv_temp), _lib.ptr(row_seed), _lib.ptr(part), M, V, K, splits,
+                                             vocab_offset, _lib.ptr(_lib.status_word(hidden.device)),
+                                             _lib.stream_ptr()), "sample_partials")
+    tok = torch.empty(M, dtype=torch.int32, device=hidden.device)
+    lp = torch.empty(M, dtype=torch.float32, device=hidden.device)
+    _lib.check_rc(_f("artb_sample_merge")(_lib.ptr(part), splits, M, _lib.ptr(tok), _lib.ptr(lp), _lib.stream_ptr()),
+                  "sample_merge")
+    return tok, lp

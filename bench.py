@@ -219,6 +219,13 @@ def main():
     clocks = sampler.stop()
     trainer.step(host_rows, hyper)  # warm the host-input path
     ms_e2e, _, _ = timed(host_rows, args.steps)
+    if os.environ.get("ARTB_PROFILE_STEP"):
+        # one extra step between cudaProfilerStart/Stop for `ncu --profile-from-start off`
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        trainer.step(dev_rows, hyper)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     _lib.check_status(dev)
 
     h2d = sum(v.numel() * v.element_size() for v in host_rows.values())

@@ -1,0 +1,129 @@
+"""Rollout engine on CPU: block manager, scheduler, prefix cache, adapters, pause/resume (reference runner)."""
+import asyncio
+
+import pytest
+import torch
+
+from art_b200.engine.engine import Engine, SamplingParams
+from art_b200.engine.kv_cache import BlockManager
+from art_b200.engine.runner import ReferenceRunner
+from art_b200.models.config import PRESETS
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+
+
+def test_block_manager_alloc_free_and_prefix_cache():
+    bm = BlockManager(8, 4, True)
+    a = bm.alloc(3)
+    assert len(a) == 3 and bm.num_free == 5
+    assert bm.alloc(6) is None and bm.num_free == 5
+    toks = list(range(12))
+    bm.commit(a, toks, salt=7)
+    bm.free(a)
+    assert bm.num_free == 8                      # cached blocks stay evictable
+    hit = bm.match_prefix(toks + [99], salt=7)
+    assert hit == a                              # whole-block prefix re-used, same ids
+    assert bm.match_prefix(toks, salt=8) == []   # other adapter salt: no reuse
+    assert bm.match_prefix([0, 1, 2, 3, 9, 9, 9, 9], salt=7) == a[:1]
+    bm.free(hit)
+    bm.free(a[:1])
+    got = bm.alloc(8)                            # eviction reclaims cached blocks when needed
+    assert got is not None and sorted(got) == list(range(8))
+    bm.free(got)
+    bm.reset_prefix_cache()
+    assert bm.match_prefix(toks, salt=7) == []
+    assert bm.stats()["prefix_hits"] == 2
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    cfg = PRESETS["tiny"]
+    base = init_base_weights(cfg, seed=0)
+    return cfg, base
+
+
+def make_engine(cfg, base, **kw):
+    runner = ReferenceRunner(cfg, base, LoraConfig(), max_loras=2)
+    bm = BlockManager(kw.pop("blocks", 64), 4, True)
+    return Engine(runner, bm, eos_token_id=None, max_loras=2, **kw)
+
+
+def test_greedy_is_deterministic_and_batching_invariant(tiny):
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=4)
+    p = SamplingParams(max_tokens=6, temperature=0.0)
+    a = eng.generate_sync([1, 2, 3, 4, 5], p)
+    # same prompt again while another request shares the batch
+    s1 = eng.add_request([1, 2, 3, 4, 5], p)
+    s2 = eng.add_request([9, 8, 7], SamplingParams(max_tokens=3, temperature=0.0))
+    while not (s1.finished and s2.finished):
+        eng.step()
+    assert a.output_ids == s1.output_ids and len(a.output_ids) == 6 and a.finish_reason == "length"
+    assert len(s2.output_ids) == 3
+    assert all(lp <= 0 for lp in a.logprobs)
+    assert eng.bm.stats()["prefix_hits"] >= 1     # second request re-used the first one's prompt block
+
+
+def test_adapter_changes_output_and_base_stays(tiny):
+    cfg, base = tiny
+    eng = make_engine(cfg, base)
+    lora = init_lora(cfg, LoraConfig())
+    g = torch.Generator().manual_seed(3)
+    for k in lora:
+        if "lora_B" in k:
+            lora[k] = torch.randn(lora[k].shape, generator=g) * 0.5
+    eng.set_adapter("my-model", lora)
+    p = SamplingParams(max_tokens=5, temperature=0.0)
+    base_out = eng.generate_sync([5, 6, 7, 8], p).output_ids
+    lora_out = eng.generate_sync([5, 6, 7, 8], p, "my-model").output_ids
+    assert base_out != lora_out
+    assert eng.generate_sync([5, 6, 7, 8], p).output_ids == base_out
+    with pytest.raises(KeyError):
+        eng.add_request([1], p, "nope")
+
+
+def test_preemption_when_blocks_run_out(tiny):
+    cfg, base = tiny
+    eng = make_engine(cfg, base, blocks=6, num_scheduler_steps=2)
+    p = SamplingParams(max_tokens=10, temperature=0.0)
+    seqs = [eng.add_request([i + 1, i + 2, i + 3], p) for i in range(3)]
+    for _ in range(200):
+        if all(s.finished for s in seqs):
+            break
+        eng.step()
+    assert all(len(s.output_ids) == 10 for s in seqs)
+    assert eng.stats.preemptions >= 1
+    ref = make_engine(cfg, base)
+    assert ref.generate_sync([1, 2, 3], p).output_ids == seqs[0].output_ids   # recompute after preemption is exact
+
+
+def test_async_stream_pause_resume_and_abort(tiny):
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    eng.start()
+
+    async def main():
+        got = []
+        async for ev in eng.generate([1, 2, 3], SamplingParams(max_tokens=4, temperature=1.0, seed=5)):
+            got.append(ev.token_id)
+            if len(got) == 2:
+                eng.pause()
+                assert not eng._run_gate.is_set()
+                eng.resume()
+        assert len(got) == 4
+        # abort by abandoning the stream
+        agen = eng.generate([4, 5, 6], SamplingParams(max_tokens=1000, temperature=0.0))
+        await agen.__anext__()
+        await agen.aclose()
+        await asyncio.sleep(0.2)
+        return got
+
+    try:
+        asyncio.run(main())
+        for _ in range(100):
+            if not eng.has_unfinished:
+                break
+            import time
+            time.sleep(0.05)
+        assert not eng.has_unfinished
+    finally:
+        eng.shutdown()
