@@ -98,6 +98,7 @@ class Engine:
         self.n_steps, self.max_model_len = max(1, num_scheduler_steps), max_model_len
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
+        self.score_queue: deque = deque()
         self.adapters: dict[str, int] = {}
         self.adapter_version = [0] * max_loras
         self.max_loras = max_loras
@@ -229,6 +230,18 @@ class Engine:
             if not seq.finished:
                 self.abort(seq)
 
+    async def score(self, prompt_ids: list[int], completion_ids: list[int], adapter_name: str | None = None) -> list[float]:
+        """Per-token log-probabilities of ``completion_ids`` after ``prompt_ids`` (teacher forcing)."""
+        adapter = -1 if adapter_name is None else self.adapters[adapter_name]
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        with self._lock:
+            self.score_queue.append((list(prompt_ids) + list(completion_ids), len(prompt_ids), adapter, loop, fut))
+        self._wake.set()
+        if self._thread is None:
+            self.step()
+        return await fut
+
     def generate_sync(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None) -> Sequence:
         """Blocking helper (tests, benchmarks): drives the loop inline if no thread is running."""
         seq = self.add_request(prompt_ids, params, adapter_name, None)
@@ -328,6 +341,14 @@ class Engine:
 
     def step(self) -> bool:
         """One scheduler iteration.  Returns False when there was nothing to do."""
+        while self.score_queue:
+            with self._lock:
+                toks, n_prompt, adapter, loop, fut = self.score_queue.popleft()
+            try:
+                res = self.runner.score(toks, n_prompt, adapter)
+                loop.call_soon_threadsafe(lambda f=fut, r=res: f.done() or f.set_result(r))
+            except BaseException as e:  # noqa: BLE001
+                loop.call_soon_threadsafe(lambda f=fut, e=e: f.done() or f.set_exception(e))
         for s in [s for s in self.running if s.aborted and not s.finished]:
             s.finished, s.finish_reason = True, "abort"
         done = [s for s in self.running if s.finished]

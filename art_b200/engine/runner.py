@@ -71,6 +71,17 @@ class ReferenceRunner:
         t = int(torch.multinomial(lp.exp().cpu(), 1, generator=g))
         return t, float(lp[t])
 
+    def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
+        m = self._model
+        m.lora = self.adapters[adapter] if adapter >= 0 and self.adapters[adapter] is not None else {}
+        toks = torch.tensor([tokens], device=self.device)
+        z = torch.zeros_like(toks)
+        with torch.no_grad():
+            h = m.hidden_states(toks, z, z, None)[0, n_prompt - 1: len(tokens) - 1]
+            lp = torch.log_softmax(h.float() @ self.base["lm_head.weight"].float().t(), -1)
+        tgt = torch.tensor(tokens[n_prompt:], device=self.device)
+        return lp.gather(-1, tgt.unsqueeze(-1)).squeeze(-1).tolist()
+
     def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
         out = [self._next(s) for s in seqs]
         return [o[0] for o in out], [o[1] for o in out]
@@ -225,12 +236,15 @@ class NativeRunner:
         return qkv
 
     # -- prefill ------------------------------------------------------------------------------------
-    def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
+    def _prompt_forward(self, seqs: list[SeqView], write_kv: bool = True):
+        """Run the decoder over the not-yet-cached tokens of ``seqs``; returns the residual stream
+        ``x`` [M_new, d] and, per sequence, the row range of its new tokens."""
         from ..ops import attention as attn_ops
         from ..ops import elementwise as ew
         from ..ops import paged
 
         cfg, dev, bs = self.cfg, self.device, self.kv.shape[1]
+        row_ranges = []
         tok, pos, gid, adapter, slot, new_rows, last_rows = [], [], [], [], [], [], []
         cached_spans = []   # (att_row_start, n_cached, blocks)
         att = 0
@@ -241,14 +255,16 @@ class NativeRunner:
                 cached_spans.append((att, nc, s.blocks))
                 gid += [i] * nc
                 att += nc
+            r0 = len(tok)
             for t in range(nc, n):
                 tok.append(s.tokens[t])
                 pos.append(t)
                 adapter.append(s.adapter)
-                slot.append(s.blocks[t // bs] * bs + t % bs)
+                slot.append(s.blocks[t // bs] * bs + t % bs if write_kv else -1)
                 new_rows.append(att)
                 gid.append(i)
                 att += 1
+            row_ranges.append((r0, len(tok)))
             last_rows.append(len(tok) - 1)
         M = len(tok)
         S_att = (att + 63) // 64 * 64
@@ -279,13 +295,34 @@ class NativeRunner:
                 o, _ = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=False)
             x2 = L["o"](o, t_ad, any_lora, residual=x)
             x = self._mlp(L, x2, t_ad, any_lora)
-        t_last = torch.tensor(last_rows, dtype=torch.int64, device=dev)
+        return x, row_ranges
+
+    def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
+        from ..ops import elementwise as ew
+        from ..ops import paged
+
+        cfg, dev = self.cfg, self.device
+        x, ranges = self._prompt_forward(seqs, write_kv=True)
+        t_last = torch.tensor([r1 - 1 for _, r1 in ranges], dtype=torch.int64, device=dev)
         hl = ew.gather_rows(x, t_last)
         hidden, _ = ew.rmsnorm_fwd(hl, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
         inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
         seeds = torch.tensor([_mix_seed(s.seed, s.step) for s in seqs], dtype=torch.int64, device=dev).to(torch.int32)
         t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
         return t.tolist(), lp.tolist()
+
+    def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
+        """Log-probabilities of ``tokens[n_prompt:]`` given what precedes them (no KV is written)."""
+        from ..ops import elementwise as ew
+        from ..ops import logprob_loss as lpl
+
+        sv = SeqView(tokens, 0, [], adapter, 0.0, 0, 0)
+        x, _ = self._prompt_forward([sv], write_kv=False)
+        rows = torch.arange(n_prompt - 1, len(tokens) - 1, dtype=torch.int64, device=self.device)
+        h, _ = ew.rmsnorm_fwd(ew.gather_rows(x, rows), self.final_norm, self.cfg.rms_norm_eps, want_rstd=False)
+        tgt = torch.tensor(tokens[n_prompt:], dtype=torch.int32, device=self.device)
+        part, _ = lpl.partials(h, self.lm_head, tgt)
+        return lpl.grpo_tokens(part).logprobs.tolist()
 
     # -- decode -------------------------------------------------------------------------------------
     def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:

@@ -1,0 +1,362 @@
+"""OpenAI-compatible completion server in front of :class:`engine.Engine`.
+
+Routes: ``GET /health``, ``GET /v1/models``, ``POST /v1/chat/completions`` (streaming and
+non-streaming, ``n``, ``stream_options.include_usage``, tools with Hermes-format parsing and
+auto tool choice, ``guided_choice``, ``chat_template_kwargs``), ``POST /v1/completions``,
+``POST /tokenize``, ``GET /metrics``.
+
+Contract details the trainer depends on (reference: ``src/art/dev/openai_server.py:7-35`` and the
+request subclass at ``src/art/local/vllm.py:234-247``):
+
+* log-probs are **always** returned (``top_logprobs`` defaults to 0), and every sampled token is
+  reported, including the tokens of tool calls;
+* with ``return_tokens_as_token_ids`` (default on) token strings are ``token_id:{id}`` so the
+  tokenizer pipeline can splice the exact sampled ids back into the conversation;
+* the ``model`` field routes by name: a registered adapter name selects that LoRA, the base
+  model name selects no adapter;
+* a client that disconnects mid-stream aborts its request and nothing else.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+from typing import Any, AsyncIterator
+
+from fastapi import FastAPI, HTTPException, Request
+from fastapi.responses import JSONResponse, StreamingResponse
+
+from .engine import Engine, SamplingParams
+from .tool_parser import HermesToolParser
+
+
+def _now() -> int:
+    return int(time.time())
+
+
+class OpenAIServer:
+    def __init__(self, engine: Engine, tokenizer, base_model_name: str, *, api_key: str | None = "default",
+                 return_tokens_as_token_ids: bool = True, enable_auto_tool_choice: bool = True,
+                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256):
+        self.engine, self.tok = engine, tokenizer
+        self.base_model_name = base_model_name
+        self.api_key = api_key
+        self.token_ids_as_strings = return_tokens_as_token_ids
+        self.auto_tools = enable_auto_tool_choice
+        self.tool_parser = HermesToolParser() if tool_call_parser in ("hermes", None) else HermesToolParser()
+        self.default_max_tokens = default_max_tokens
+        self.app = self._build()
+
+    # -- helpers ------------------------------------------------------------------------------------
+    def _auth(self, request: Request) -> None:
+        if not self.api_key:
+            return
+        got = request.headers.get("authorization", "")
+        if got != f"Bearer {self.api_key}":
+            raise HTTPException(status_code=401, detail="invalid api key")
+
+    def _route(self, model: str | None) -> str | None:
+        """Adapter name for ``model`` (None = base model)."""
+        if model is None or model == self.base_model_name:
+            return None
+        if model in self.engine.adapters:
+            return model
+        raise HTTPException(status_code=404, detail=f"The model `{model}` does not exist.")
+
+    def _token_str(self, tid: int) -> str:
+        return f"token_id:{tid}" if self.token_ids_as_strings else self.tok.decode([tid])
+
+    def _logprob_entry(self, tid: int, lp: float) -> dict:
+        text = self.tok.decode([tid])
+        return {"token": self._token_str(tid), "logprob": lp, "bytes": list(text.encode("utf-8")), "top_logprobs": []}
+
+    def _params(self, body: dict, prompt_len: int) -> SamplingParams:
+        max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
+        max_tokens = max(1, min(int(max_tokens), self.engine.max_model_len - prompt_len - 1))
+        stop = body.get("stop")
+        if isinstance(stop, str):
+            stop = [stop]
+        temp = body.get("temperature")
+        return SamplingParams(max_tokens=max_tokens, temperature=1.0 if temp is None else float(temp),
+                              top_p=float(body.get("top_p") or 1.0), top_k=int(body.get("top_k") or -1),
+                              n=int(body.get("n") or 1), stop=stop, stop_token_ids=body.get("stop_token_ids"),
+                              seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
+                              guided_choice=body.get("guided_choice"))
+
+    def _render_chat(self, body: dict) -> list[int]:
+        tools = body.get("tools")
+        if body.get("tool_choice") == "none":
+            tools = None
+        kwargs = dict(body.get("chat_template_kwargs") or {})
+        ids = self.tok.apply_chat_template(body["messages"], tools=tools, add_generation_prompt=True, tokenize=True, **kwargs)
+        if isinstance(ids, dict):
+            ids = ids["input_ids"]
+        return list(ids)
+
+    async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int):
+        """Async iterator over (index, token_id, logprob, finished, finish_reason) for one choice."""
+        if params.guided_choice:
+            async for item in self._run_guided(prompt_ids, params, adapter, index):
+                yield item
+            return
+        seq_params = SamplingParams(**{**params.__dict__, "n": 1,
+                                       "seed": None if params.seed is None else params.seed + index})
+        stops = params.stop or []
+        text = ""
+        agen = self.engine.generate(prompt_ids, seq_params, adapter)
+        try:
+            async for ev in agen:
+                yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason
+                if stops and not ev.finished:
+                    text += self.tok.decode([ev.token_id])
+                    if any(s in text for s in stops):
+                        yield index, None, None, True, "stop"
+                        return
+                if ev.finished:
+                    return
+        finally:
+            await agen.aclose()
+
+    async def _run_guided(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int):
+        """``guided_choice``: the completion is one of the given strings.  Every candidate is scored
+        under the model (teacher forcing), one is drawn from the renormalised distribution over
+        candidates (arg-max at temperature 0), and its tokens are returned with their log-probs."""
+        import math
+        import random
+
+        eos = [self.engine.eos] if self.engine.eos is not None else []
+        cands = [self.tok.encode(c) + eos for c in params.guided_choice]
+        scores = [await self.engine.score(prompt_ids, c, adapter) for c in cands]
+        totals = [sum(s) for s in scores]
+        if params.temperature <= 0 or len(cands) == 1:
+            pick = max(range(len(cands)), key=lambda i: totals[i])
+        else:
+            mx = max(totals)
+            w = [math.exp((t - mx) / params.temperature) for t in totals]
+            rng = random.Random(None if params.seed is None else params.seed + index)
+            pick = rng.choices(range(len(cands)), weights=w)[0]
+        ids, lps = cands[pick], scores[pick]
+        for k, (t, lp) in enumerate(zip(ids, lps)):
+            last = k == len(ids) - 1
+            yield index, t, lp, last, "stop" if last else None
+
+    # -- app ----------------------------------------------------------------------------------------
+    def _build(self) -> FastAPI:
+        app = FastAPI(title="art-b200 completion server", docs_url=None, redoc_url=None)
+        srv = self
+
+        @app.get("/health")
+        async def health():
+            if srv.engine.error is not None:
+                raise HTTPException(status_code=500, detail=repr(srv.engine.error))
+            return {"status": "ok"}
+
+        @app.get("/metrics")
+        async def metrics():
+            return srv.engine.metrics()
+
+        @app.get("/v1/models")
+        async def models(request: Request):
+            srv._auth(request)
+            names = [srv.base_model_name] + list(srv.engine.adapters)
+            return {"object": "list", "data": [{"id": n, "object": "model", "created": _now(), "owned_by": "art-b200",
+                                                "root": srv.base_model_name,
+                                                "parent": None if n == srv.base_model_name else srv.base_model_name}
+                                               for n in names]}
+
+        @app.post("/tokenize")
+        async def tokenize(request: Request):
+            body = await request.json()
+            ids = srv._render_chat(body) if "messages" in body else srv.tok.encode(body.get("prompt", ""))
+            return {"tokens": ids, "count": len(ids), "max_model_len": srv.engine.max_model_len}
+
+        @app.post("/v1/chat/completions")
+        async def chat(request: Request):
+            srv._auth(request)
+            body = await request.json()
+            adapter = srv._route(body.get("model"))
+            try:
+                prompt_ids = srv._render_chat(body)
+            except Exception as e:
+                raise HTTPException(status_code=400, detail=f"cannot render chat template: {e}") from e
+            if len(prompt_ids) + 1 >= srv.engine.max_model_len:
+                raise HTTPException(status_code=400, detail=f"prompt has {len(prompt_ids)} tokens; the maximum context "
+                                                            f"length is {srv.engine.max_model_len}")
+            params = srv._params(body, len(prompt_ids))
+            rid = "chatcmpl-" + uuid.uuid4().hex
+            model_name = body.get("model") or srv.base_model_name
+            tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and srv.auto_tools
+            if body.get("stream"):
+                include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+                return StreamingResponse(srv._chat_stream(request, rid, model_name, prompt_ids, params, adapter,
+                                                          tools_on, include_usage), media_type="text/event-stream")
+            return JSONResponse(await srv._chat_full(request, rid, model_name, prompt_ids, params, adapter, tools_on))
+
+        @app.post("/v1/completions")
+        async def completions(request: Request):
+            srv._auth(request)
+            body = await request.json()
+            adapter = srv._route(body.get("model"))
+            prompt = body.get("prompt", "")
+            prompt_ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else srv.tok.encode(prompt)
+            params = srv._params(body, len(prompt_ids))
+            out = await srv._collect(request, prompt_ids, params, adapter)
+            choices = []
+            for i, (ids, lps, reason) in enumerate(out):
+                choices.append({"index": i, "text": srv.tok.decode(ids, skip_special_tokens=True), "finish_reason": reason,
+                                "logprobs": {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}})
+            comp = sum(len(ids) for ids, _, _ in out)
+            return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": _now(),
+                    "model": body.get("model") or srv.base_model_name, "choices": choices,
+                    "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
+
+        return app
+
+    # -- non-streaming ----------------------------------------------------------------------------------
+    async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter):
+
+        async def one(i: int):
+            ids, lps, reason = [], [], "stop"
+            async for _, tid, lp, fin, why in self._run_one(prompt_ids, params, adapter, i):
+                if tid is not None:
+                    ids.append(tid)
+                    lps.append(lp)
+                if fin:
+                    reason = why or "stop"
+            return ids, lps, reason
+
+        tasks = [asyncio.create_task(one(i)) for i in range(params.n)]
+        watcher = asyncio.create_task(self._watch_disconnect(request, tasks))
+        try:
+            return await asyncio.gather(*tasks)
+        except asyncio.CancelledError:
+            raise HTTPException(status_code=499, detail="client disconnected") from None
+        finally:
+            watcher.cancel()
+
+    async def _watch_disconnect(self, request: Request, tasks: list[asyncio.Task]) -> None:
+        try:
+            while True:
+                if await request.is_disconnected():
+                    for t in tasks:
+                        t.cancel()
+                    return
+                await asyncio.sleep(0.25)
+        except asyncio.CancelledError:
+            pass
+        except Exception:
+            pass
+
+    def _strip_eos(self, ids: list[int]) -> list[int]:
+        eos = self.engine.eos
+        return ids[:-1] if ids and eos is not None and ids[-1] == eos else ids
+
+    def _message_from(self, ids: list[int], tools_on: bool, reason: str) -> tuple[dict, str]:
+        text = self.tok.decode(self._strip_eos(ids), skip_special_tokens=True)
+        msg: dict[str, Any] = {"role": "assistant", "content": text}
+        if tools_on:
+            content, calls = self.tool_parser.extract(text)
+            if calls:
+                msg["content"] = content
+                msg["tool_calls"] = calls
+                reason = "tool_calls"
+        return msg, reason
+
+    async def _chat_full(self, request, rid, model_name, prompt_ids, params, adapter, tools_on) -> dict:
+        out = await self._collect(request, prompt_ids, params, adapter)
+        choices = []
+        for i, (ids, lps, reason) in enumerate(out):
+            msg, reason = self._message_from(ids, tools_on, reason)
+            choices.append({"index": i, "message": msg, "finish_reason": reason,
+                            "logprobs": {"content": [self._logprob_entry(t, lp) for t, lp in zip(ids, lps)]}})
+        comp = sum(len(ids) for ids, _, _ in out)
+        return {"id": rid, "object": "chat.completion", "created": _now(), "model": model_name, "choices": choices,
+                "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
+
+    # -- streaming --------------------------------------------------------------------------------------
+    async def _chat_stream(self, request, rid, model_name, prompt_ids, params, adapter, tools_on, include_usage
+                           ) -> AsyncIterator[str]:
+        def chunk(choices: list[dict], usage: dict | None = None) -> str:
+            d = {"id": rid, "object": "chat.completion.chunk", "created": _now(), "model": model_name, "choices": choices}
+            if include_usage:
+                d["usage"] = usage
+            return "data: " + json.dumps(d) + "\n\n"
+
+        q: asyncio.Queue = asyncio.Queue()
+
+        async def pump(i: int):
+            try:
+                async for item in self._run_one(prompt_ids, params, adapter, i):
+                    await q.put(item)
+            except BaseException as e:  # noqa: BLE001
+                await q.put(e)
+            finally:
+                await q.put((i, "done"))
+
+        tasks = [asyncio.create_task(pump(i)) for i in range(params.n)]
+        live = params.n
+        completion_tokens = 0
+        bufs: dict[int, list[int]] = {i: [] for i in range(params.n)}
+        sent_text: dict[int, int] = {i: 0 for i in range(params.n)}
+        try:
+            for i in range(params.n):
+                yield chunk([{"index": i, "delta": {"role": "assistant", "content": ""}, "logprobs": None, "finish_reason": None}])
+            while live:
+                item = await q.get()
+                if isinstance(item, BaseException):
+                    raise item
+                if len(item) == 2:
+                    live -= 1
+                    continue
+                i, tid, lp, fin, why = item
+                delta: dict[str, Any] = {}
+                lps = None
+                if tid is not None:
+                    completion_tokens += 1
+                    bufs[i].append(tid)
+                    lps = {"content": [self._logprob_entry(tid, lp)]}
+                    if not tools_on:
+                        full = self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True)
+                        if not full.endswith("�"):
+                            delta["content"] = full[sent_text[i]:]
+                            sent_text[i] = len(full)
+                reason = None
+                if fin:
+                    reason = why or "stop"
+                    if tools_on:   # tool calls are parsed once the choice is complete; log-probs were streamed per token
+                        msg, reason = self._message_from(bufs[i], True, reason)
+                        if msg.get("content"):
+                            delta["content"] = msg["content"]
+                        if msg.get("tool_calls"):
+                            delta["tool_calls"] = [{"index": k, **c} for k, c in enumerate(msg["tool_calls"])]
+                yield chunk([{"index": i, "delta": delta, "logprobs": lps, "finish_reason": reason}])
+            if include_usage:
+                yield chunk([], {"prompt_tokens": len(prompt_ids), "completion_tokens": completion_tokens,
+                                 "total_tokens": len(prompt_ids) + completion_tokens})
+            yield "data: [DONE]\n\n"
+        finally:
+            for t in tasks:   # a disconnecting client lands here: abort only this request's sequences
+                t.cancel()
+
+
+async def serve(server: OpenAIServer, host: str = "0.0.0.0", port: int = 8000, log_level: str = "warning",
+                ready: asyncio.Event | None = None):
+    """Run the app with uvicorn inside the current event loop until cancelled."""
+    import uvicorn
+
+    config = uvicorn.Config(server.app, host=host, port=port, log_level=log_level, access_log=False)
+    uv = uvicorn.Server(config)
+    uv.install_signal_handlers = lambda: None  # type: ignore[method-assign]
+    task = asyncio.create_task(uv.serve())
+    while not uv.started and not task.done():
+        await asyncio.sleep(0.02)
+    if ready is not None:
+        ready.set()
+    try:
+        await task
+    except asyncio.CancelledError:
+        uv.should_exit = True
+        await asyncio.sleep(0)
+        raise
+    return uv

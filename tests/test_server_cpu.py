@@ -1,0 +1,121 @@
+"""OpenAI protocol conformance of the completion server (CPU, reference runner, in-process ASGI)."""
+import asyncio
+import json
+
+import httpx
+import pytest
+
+from art_b200.engine.engine import Engine
+from art_b200.engine.kv_cache import BlockManager
+from art_b200.engine.runner import ReferenceRunner
+from art_b200.engine.server import OpenAIServer
+from art_b200.engine.tool_parser import HermesToolParser
+from art_b200.local.tokenizer import ByteChatTokenizer
+from art_b200.models.config import PRESETS
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+
+
+@pytest.fixture(scope="module")
+def server():
+    cfg = PRESETS["tiny"]
+    base = init_base_weights(cfg, seed=0)
+    tok = ByteChatTokenizer(cfg.vocab_size)
+    eng = Engine(ReferenceRunner(cfg, base, LoraConfig(), max_loras=2), BlockManager(256, 4, True),
+                 eos_token_id=tok.eos_token_id, max_loras=2, num_scheduler_steps=2, max_model_len=512)
+    eng.set_adapter("agent-001", init_lora(cfg, LoraConfig()))
+    eng.start()
+    srv = OpenAIServer(eng, tok, "tiny-base")
+    yield srv
+    eng.shutdown()
+
+
+def client(srv):
+    return httpx.AsyncClient(transport=httpx.ASGITransport(app=srv.app), base_url="http://t",
+                             headers={"Authorization": "Bearer default"})
+
+
+def test_models_and_auth(server):
+    async def main():
+        async with client(server) as c:
+            r = await c.get("/v1/models")
+            assert [m["id"] for m in r.json()["data"]] == ["tiny-base", "agent-001"]
+            r = await c.get("/v1/models", headers={"Authorization": "Bearer nope"})
+            assert r.status_code == 401
+            r = await c.post("/v1/chat/completions", json={"model": "ghost", "messages": [{"role": "user", "content": "x"}]})
+            assert r.status_code == 404
+    asyncio.run(main())
+
+
+def test_chat_completion_always_has_token_id_logprobs(server):
+    async def main():
+        async with client(server) as c:
+            body = {"model": "agent-001", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 5, "n": 2, "seed": 1}
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 200
+            d = r.json()
+            assert len(d["choices"]) == 2 and d["usage"]["completion_tokens"] == 10
+            for ch in d["choices"]:
+                lps = ch["logprobs"]["content"]
+                assert len(lps) == 5 and all(e["token"].startswith("token_id:") and e["logprob"] <= 0 for e in lps)
+                assert ch["finish_reason"] in ("length", "stop")
+            from openai.types.chat import ChatCompletion
+            ChatCompletion.model_validate(d)            # parses as the official type
+    asyncio.run(main())
+
+
+def test_streaming_with_usage_folds_back(server):
+    from openai.types.chat.chat_completion_chunk import ChatCompletionChunk
+
+    from art_b200.openai import consume_chat_completion_stream
+
+    async def main():
+        async with client(server) as c:
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "stream": True,
+                    "stream_options": {"include_usage": True}, "temperature": 0}
+            chunks = []
+            async with c.stream("POST", "/v1/chat/completions", json=body) as r:
+                async for line in r.aiter_lines():
+                    if line.startswith("data: ") and line != "data: [DONE]":
+                        chunks.append(ChatCompletionChunk.model_validate(json.loads(line[6:])))
+
+            class S:
+                def __aiter__(self):
+                    async def g():
+                        for ch in chunks:
+                            yield ch
+                    return g()
+
+            comp = await consume_chat_completion_stream(S())
+            assert len(comp.choices[0].logprobs.content) == 4
+            assert comp.usage.completion_tokens == 4 and comp.usage.prompt_tokens > 0
+            # non-streaming greedy gives the same tokens
+            body2 = {k: v for k, v in body.items() if k not in ("stream", "stream_options")}
+            full = (await c.post("/v1/chat/completions", json=body2)).json()
+            assert [e["token"] for e in full["choices"][0]["logprobs"]["content"]] == \
+                [e.token for e in comp.choices[0].logprobs.content]
+    asyncio.run(main())
+
+
+def test_guided_choice_and_completions(server):
+    async def main():
+        async with client(server) as c:
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "pick"}], "guided_choice": ["yes", "no"],
+                    "temperature": 0}
+            d = (await c.post("/v1/chat/completions", json=body)).json()
+            assert d["choices"][0]["message"]["content"] in ("yes", "no")
+            assert len(d["choices"][0]["logprobs"]["content"]) == len(d["choices"][0]["message"]["content"]) + 1
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": "abc", "max_tokens": 3})
+            assert len(r.json()["choices"][0]["logprobs"]["tokens"]) == 3
+            r = await c.post("/tokenize", json={"prompt": "abc"})
+            assert r.json()["tokens"] == [97, 98, 99]
+    asyncio.run(main())
+
+
+def test_hermes_tool_parser():
+    p = HermesToolParser()
+    text = 'Let me check.\n<tool_call>\n{"name": "search", "arguments": {"q": "x"}}\n</tool_call>'
+    content, calls = p.extract(text)
+    assert content == "Let me check." and calls[0]["function"]["name"] == "search"
+    assert json.loads(calls[0]["function"]["arguments"]) == {"q": "x"}
+    assert p.extract("no tools here") == ("no tools here", [])
+    assert p.extract("<tool_call>not json</tool_call>")[1] == []
