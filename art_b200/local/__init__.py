@@ -1,0 +1,3 @@
+from .backend import LocalBackend
+
+__all__ = ["LocalBackend"]

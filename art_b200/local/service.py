@@ -1,0 +1,262 @@
+"""Model service: the process-local owner of one trainable model (weights, trainer, rollout
+engine, completion server).  ``LocalBackend`` talks to it directly (``in_process=True``) or
+through the actor proxy in a child process.
+
+Contract parity: reference ``src/art/local/service.py:26-174`` (``start_openai_server``,
+``stop_openai_server``, ``train`` as an async generator of per-step metrics, ``_set_lora``) and
+``state.py:35-177``.  What differs underneath:
+
+* there is no never-ending trainer loop fed through a queue; ``train`` calls
+  ``Trainer.step`` once per optimizer step (in a worker thread so the event loop keeps serving);
+* the engine is paused at a step boundary with ``Engine.pause()``; in-flight requests keep their
+  KV cache and continue after training under the new adapter;
+* the new adapter reaches the engine as a device-to-device copy from the trainer's fp32 master
+  buffer; the PEFT checkpoint ``{step:04d}/`` is written from a host copy in a background thread;
+* optimizer state is saved next to the adapter (``trainer_state.pt``) so a restarted process
+  resumes exactly.
+"""
+from __future__ import annotations
+
+import asyncio
+import os
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import AsyncIterator
+
+import torch
+
+from .. import dev, types
+from ..models.config import resolve_config
+from ..models.peft_io import is_adapter_dir, load_adapter, save_adapter
+from ..models.weights import LoraConfig, init_base_weights, init_lora, load_base_weights
+from ..utils.get_model_step import get_step_from_dir
+from ..utils.output_dirs import get_step_checkpoint_dir
+from .checkpoints import get_last_checkpoint_dir
+from .pack import DiskPackedTensors, packed_tensors_from_dir
+from .tokenizer import load_tokenizer
+
+TRAINER_STATE = "trainer_state.pt"
+
+
+class ModelState:
+    """Everything that lives on the device for one model."""
+
+    def __init__(self, base_model: str, config: dev.InternalModelConfig, output_dir: str):
+        from ..engine.engine import Engine
+        from ..engine.kv_cache import BlockManager, KVCache
+        from ..trainer.trainer import Trainer
+
+        init_args = config.get("init_args", {})
+        engine_args = config.get("engine_args", {})
+        peft_args = config.get("peft_args", {})
+        targs = config.get("trainer_args", {})
+        self.device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.cfg = resolve_config(base_model, init_args.get("architecture"))
+        self.lora_cfg = LoraConfig(r=int(peft_args.get("r", 8)), alpha=float(peft_args.get("lora_alpha", 16)),
+                                   target_modules=tuple(peft_args.get("target_modules", LoraConfig().target_modules)),
+                                   use_rslora=bool(peft_args.get("use_rslora", False)))
+        self.tokenizer = load_tokenizer(base_model, self.cfg.vocab_size)
+        seed = int(init_args.get("random_state", 0))
+        if os.path.isdir(base_model) and not init_args.get("random_init"):
+            base = load_base_weights(base_model, self.cfg, device=self.device)
+        else:
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            base = init_base_weights(self.cfg, seed=seed, dtype=dt, device=self.device)
+        # LoRA: resume from the newest checkpoint, else fresh init
+        last = get_last_checkpoint_dir(output_dir)
+        if last and is_adapter_dir(last):
+            lora, _ = load_adapter(last, self.device)
+        else:
+            lora = init_lora(self.cfg, self.lora_cfg, seed=int(peft_args.get("random_state", 3407)), device=self.device)
+        self.trainer = Trainer(self.cfg, base, self.lora_cfg, lora, device=self.device,
+                               betas=(float(targs.get("adam_beta1", 0.9)), float(targs.get("adam_beta2", 0.99))),
+                               weight_decay=float(targs.get("weight_decay", 0.1)),
+                               max_grad_norm=float(targs.get("max_grad_norm", 0.1)),
+                               adam_eps=float(targs.get("adam_epsilon", 1e-8)))
+        if last and os.path.exists(os.path.join(last, TRAINER_STATE)):
+            self.trainer.load_trainer_state(torch.load(os.path.join(last, TRAINER_STATE), map_location="cpu"))
+        # rollout engine
+        block_size = int(engine_args.get("block_size") or 16)
+        max_loras = int(engine_args.get("max_loras", 4))
+        max_len = int(engine_args.get("max_model_len") or init_args.get("max_seq_length", 32768))
+        if self.device.type == "cuda":
+            from ..engine.runner import NativeRunner
+
+            free, total = torch.cuda.mem_get_info(self.device)
+            util = float(engine_args.get("gpu_memory_utilization", init_args.get("gpu_memory_utilization", 0.5)))
+            per_block = KVCache.bytes_per_block(self.cfg.num_layers, block_size, self.cfg.num_kv_heads, self.cfg.head_dim)
+            budget = min(free * 0.6, total * util * 0.5)   # leave room for training activations
+            num_blocks = int(engine_args.get("num_gpu_blocks_override") or max(64, int(budget // per_block)))
+            self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim, self.device)
+            runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
+                                  device=self.device)
+        else:
+            from ..engine.runner import ReferenceRunner
+
+            num_blocks = int(engine_args.get("num_gpu_blocks_override") or 4096)
+            self.kv = None
+            runner = ReferenceRunner(self.cfg, base, self.lora_cfg, max_loras=max_loras, device=self.device)
+        self.engine = Engine(runner, BlockManager(num_blocks, block_size, bool(engine_args.get("enable_prefix_caching", True))),
+                             eos_token_id=getattr(self.tokenizer, "eos_token_id", None),
+                             max_num_seqs=int(engine_args.get("max_num_seqs") or 256),
+                             max_num_batched_tokens=int(engine_args.get("max_num_batched_tokens") or 16384),
+                             num_scheduler_steps=int(engine_args.get("num_scheduler_steps", 16)), max_model_len=max_len,
+                             max_loras=max_loras, kv_cache=self.kv)
+        self.sleep_mode = bool(engine_args.get("enable_sleep_mode", False))
+
+
+@dataclass
+class ModelService:
+    host: str
+    port: int
+    model_name: str
+    base_model: str
+    config: dev.InternalModelConfig
+    output_dir: str
+    _state: ModelState | None = field(default=None, repr=False, compare=False)
+    _server_task: asyncio.Task | None = field(default=None, repr=False, compare=False)
+    _ckpt_thread: threading.Thread | None = field(default=None, repr=False, compare=False)
+
+    def __getstate__(self):   # only the configuration crosses the process boundary
+        d = dict(self.__dict__)
+        d["_state"] = d["_server_task"] = d["_ckpt_thread"] = None
+        return d
+
+    @property
+    def state(self) -> ModelState:
+        if self._state is None:
+            self._state = ModelState(self.base_model, self.config, self.output_dir)
+        return self._state
+
+    # -- serving --------------------------------------------------------------------------------------
+    async def start_openai_server(self, config: dev.OpenAIServerConfig | None = None) -> tuple[str, int]:
+        from ..engine.server import OpenAIServer, serve
+
+        st = self.state
+        step0 = get_step_checkpoint_dir(self.output_dir, 0)
+        if get_last_checkpoint_dir(self.output_dir) is None:
+            save_adapter(step0, st.trainer.lora_state_dict(), st.lora_cfg, self.base_model)   # step 0 = untrained adapter
+        lora_path = get_last_checkpoint_dir(self.output_dir) or step0
+        cfg = dev.get_openai_server_config(self.model_name, self.base_model, f"{self.output_dir}/logs/engine.log",
+                                           lora_path, config)
+        sargs = cfg.get("server_args", {})
+        st.engine.start()
+        self._set_lora_in_device()
+        for spec in (sargs.get("lora_modules") or []):   # extra adapters served next to the trainable one
+            name, path = dev.openai_server.parse_lora_module(spec)
+            if name != self.model_name and is_adapter_dir(path):
+                st.engine.set_adapter(name, load_adapter(path, st.device)[0])
+        server = OpenAIServer(st.engine, st.tokenizer, self.base_model, api_key=sargs.get("api_key", "default"),
+                              return_tokens_as_token_ids=bool(sargs.get("return_tokens_as_token_ids", True)),
+                              enable_auto_tool_choice=bool(sargs.get("enable_auto_tool_choice", True)),
+                              tool_call_parser=sargs.get("tool_call_parser", "hermes"))
+        self._server = server
+        host, port = sargs.get("host") or "0.0.0.0", int(sargs.get("port", self.port))
+        await self.stop_openai_server()
+        ready = asyncio.Event()
+        self._server_task = asyncio.create_task(serve(server, host, port, sargs.get("uvicorn_log_level", "warning"), ready))
+        try:
+            await asyncio.wait_for(ready.wait(), timeout=30)
+        except asyncio.TimeoutError as e:
+            raise TimeoutError("completion server did not start within 30 s") from e
+        if self._server_task.done():
+            self._server_task.result()
+        return host, port
+
+    async def stop_openai_server(self) -> None:
+        if self._server_task is not None:
+            self._server_task.cancel()
+            try:
+                await self._server_task
+            except (asyncio.CancelledError, Exception):
+                pass
+            self._server_task = None
+
+    def _set_lora_in_device(self) -> None:
+        """Hand the trainer's current LoRA to the engine under the model's name (device-to-device)."""
+        st = self.state
+        st.engine.set_adapter(self.model_name, st.trainer.flat.views)
+
+    async def _set_lora(self, lora_path: str) -> None:
+        """Load an adapter directory into the engine (used for externally produced checkpoints)."""
+        st = self.state
+        state, _ = load_adapter(lora_path, st.device)
+        st.engine.pause()
+        try:
+            st.engine.set_adapter(self.model_name, state)
+        finally:
+            st.engine.resume()
+
+    # -- training -------------------------------------------------------------------------------------
+    async def train(self, disk_packed_tensors: DiskPackedTensors, config: types.TrainConfig, _config: dev.TrainConfig,
+                    verbose: bool = False) -> AsyncIterator[dict[str, float]]:
+        from ..trainer.trainer import PACKED_KEYS, TrainHyper
+
+        st = self.state
+        packed = packed_tensors_from_dir(**disk_packed_tensors)
+        hyper = TrainHyper(learning_rate=config.learning_rate, beta=config.beta,
+                           epsilon=float(_config.get("epsilon", 0.2)), epsilon_high=_config.get("epsilon_high"),
+                           rows_per_optimizer_step=int(_config.get("rows_per_optimizer_step", 1)),
+                           tokens_per_microbatch=int(_config.get("tokens_per_microbatch", 8192)),
+                           compat_row_positions=bool(_config.get("compat_row_positions", False)))
+        loop = asyncio.get_running_loop()
+        await loop.run_in_executor(None, st.engine.pause)
+        slept = False
+        try:
+            if st.sleep_mode:
+                await loop.run_in_executor(None, st.engine.sleep, 1 if st.engine.has_unfinished else 2)
+                slept = True
+            n_rows = packed["tokens"].shape[0]
+            per = max(1, hyper.rows_per_optimizer_step)
+            t0 = time.monotonic()
+            tokens_done = 0
+            for start in range(0, n_rows, per):
+                rows = {k: packed[k][start:start + per] for k in PACKED_KEYS}
+                if st.device.type == "cuda":
+                    rows = {k: v.pin_memory() for k, v in rows.items()}
+                metrics = await loop.run_in_executor(None, st.trainer.step, rows, hyper)
+                tokens_done += rows["tokens"].numel()
+                metrics["tokens_per_second"] = tokens_done / max(1e-9, time.monotonic() - t0)
+                if verbose:
+                    print(f"[train] step {st.trainer.global_step}: {metrics}", flush=True)
+                yield metrics
+            # new step directory = PEFT adapter (+ optimizer state), written off the critical path
+            step = get_step_from_dir(self.output_dir) + 1
+            ckpt_dir = get_step_checkpoint_dir(self.output_dir, step)
+            host_state = {k: v.detach().to("cpu", copy=True) for k, v in st.trainer.flat.views.items()}
+            tstate = st.trainer.trainer_state()
+            os.makedirs(ckpt_dir, exist_ok=True)   # the directory marks the step as taken immediately
+            if self._ckpt_thread is not None:
+                self._ckpt_thread.join()
+
+            def write():
+                save_adapter(ckpt_dir, host_state, st.lora_cfg, self.base_model)
+                torch.save(tstate, os.path.join(ckpt_dir, TRAINER_STATE))
+
+            self._ckpt_thread = threading.Thread(target=write, daemon=True)
+            self._ckpt_thread.start()
+            if slept:
+                await loop.run_in_executor(None, st.engine.wake_up)
+                slept = False
+            self._set_lora_in_device()
+        finally:
+            if slept:
+                await loop.run_in_executor(None, st.engine.wake_up)
+            st.engine.resume()
+
+    async def flush_checkpoints(self) -> None:
+        if self._ckpt_thread is not None:
+            await asyncio.get_running_loop().run_in_executor(None, self._ckpt_thread.join)
+
+    async def shutdown(self) -> None:
+        await self.stop_openai_server()
+        await self.flush_checkpoints()
+        if self._state is not None:
+            self._state.engine.shutdown()
+
+    def close(self) -> None:
+        if self._ckpt_thread is not None:
+            self._ckpt_thread.join()
+        if self._state is not None:
+            self._state.engine.shutdown()
