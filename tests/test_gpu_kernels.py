@@ -1,0 +1,151 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, device=DEV, generator=g) * scale).to(torch.bfloat16)
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from art_b200.ops import _lib
+
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,K2,bn", [(128, 64, 64, 0, 64), (256, 512, 512, 0, 256), (200, 264, 328, 0, 0),
+                                         (1024, 1024, 1024, 64, 0), (4096, 4608, 3584, 8, 0), (77, 3584, 128, 16, 64)])
+def test_gemm_tn(M, N, K, K2, bn):
+    from art_b200.ops.gemm import gemm_tn, reference_gemm_tn
+
+    a, b = bf(M, K, seed=1), bf(N, K, scale=0.05, seed=2)
+    a2 = bf(M, K2, seed=3) if K2 else None
+    b2 = bf(N, K2, scale=0.05, seed=4) if K2 else None
+    r = bf(M, N, seed=5)
+    bias = torch.randn(N, device=DEV)
+    out = gemm_tn(a, b, a2=a2, b2=b2, residual=r, bias=bias, bn=bn)
+    ref = reference_gemm_tn(a, b, a2, b2, r, bias)
+    assert rel_err(out, ref) < 5e-3
+    out32 = gemm_tn(a, b, out_dtype=torch.float32, bn=bn)
+    assert rel_err(out32, reference_gemm_tn(a, b)) < 1e-3
+
+
+def test_gemm_swiglu_epilogue():
+    from art_b200.ops import elementwise as ew
+    from art_b200.ops.gemm import gemm_tn
+
+    M, K, F = 300, 256, 384
+    x, wg, wu = bf(M, K, seed=1), bf(F, K, scale=0.1, seed=2), bf(F, K, scale=0.1, seed=3)
+    h = torch.empty(M, F, dtype=torch.bfloat16, device=DEV)
+    gu = gemm_tn(x, ew.interleave_gate_up(wg, wu), swiglu_out=h)
+    g, u = ew.deinterleave_gate_up(gu)
+    assert rel_err(g, x.float() @ wg.float().t()) < 5e-3 and rel_err(u, x.float() @ wu.float().t()) < 5e-3
+    assert rel_err(h, torch.nn.functional.silu(g.float()) * u.float()) < 1e-2
+    assert rel_err(ew.swiglu_fwd(gu), h) < 1e-2
+    dh = bf(M, F, seed=4)
+    g32, u32 = g.float().requires_grad_(True), u.float().requires_grad_(True)
+    (torch.nn.functional.silu(g32) * u32).backward(dh.float())
+    dg, du = ew.deinterleave_gate_up(ew.swiglu_bwd(dh, gu))
+    assert rel_err(dg, g32.grad) < 1e-2 and rel_err(du, u32.grad) < 1e-2
+
+
+@pytest.mark.parametrize("M,D", [(64, 128), (300, 3584), (17, 5120)])
+def test_rmsnorm_fwd_bwd(M, D):
+    from art_b200.ops import elementwise as ew
+
+    x, w, dy, dres = bf(M, D, seed=1), bf(D, scale=0.5, seed=2) + 1, bf(M, D, seed=3), bf(M, D, seed=4)
+    y, rstd = ew.rmsnorm_fwd(x, w, 1e-6)
+    assert rel_err(y, ew.rmsnorm_reference(x, w, 1e-6)) < 5e-3
+    x32 = x.float().requires_grad_(True)
+    (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).backward(dy.float())
+    dx = ew.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+    assert rel_err(dx, x32.grad + dres.float()) < 1e-2
+
+
+def test_rope_forward_inverse_and_headnorm():
+    from art_b200.ops import elementwise as ew
+
+    M, Hq, Hkv, hd = 100, 4, 2, 64
+    buf = bf(M, (Hq + 2 * Hkv) * hd, seed=1)
+    orig = buf.clone()
+    pos = torch.randint(0, 5000, (M,), device=DEV, dtype=torch.int32)
+    ew.rope_(buf, pos, 0, Hq + Hkv, hd, 1e6)
+    ref = ew.rope_reference(orig[:, :(Hq + Hkv) * hd].view(M, Hq + Hkv, hd), pos, 1e6).reshape(M, -1)
+    assert rel_err(buf[:, :(Hq + Hkv) * hd], ref) < 5e-3
+    assert torch.equal(buf[:, (Hq + Hkv) * hd:], orig[:, (Hq + Hkv) * hd:])       # v untouched
+    ew.rope_(buf, pos, 0, Hq + Hkv, hd, 1e6, inverse=True)
+    assert rel_err(buf, orig) < 1e-2
+    w = bf(hd, scale=0.2, seed=3) + 1
+    x = orig.clone()
+    rstd = ew.headnorm_fwd_(x, w, 0, Hq, hd, 1e-6)
+    q = orig[:, :Hq * hd].float().view(M, Hq, hd)
+    refn = (q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6)) * w.float()
+    assert rel_err(x[:, :Hq * hd], refn.reshape(M, -1)) < 5e-3
+    q32 = q.clone().requires_grad_(True)
+    dy = bf(M, (Hq + 2 * Hkv) * hd, seed=5)
+    ((q32 * torch.rsqrt(q32.pow(2).mean(-1, keepdim=True) + 1e-6)) * w.float()).backward(dy[:, :Hq * hd].float().view(M, Hq, hd))
+    d = dy.clone()
+    ew.headnorm_bwd_(d, orig, w, rstd, 0, Hq, hd)
+    assert rel_err(d[:, :Hq * hd], q32.grad.reshape(M, -1)) < 1e-2
+
+
+def test_gather_scatter_advnorm():
+    from art_b200.local.tokenize import group_advantages
+    from art_b200.ops import elementwise as ew
+
+    table = bf(50, 64, seed=1)
+    idx = torch.tensor([3, 49, 0, 7], device=DEV)
+    assert torch.equal(ew.gather_rows(table, idx), table[idx])
+    out = torch.zeros(50, 64, dtype=torch.bfloat16, device=DEV)
+    ew.scatter_rows_(table[:4].contiguous(), idx, out)
+    assert torch.equal(out[idx], table[:4]) and out.abs().sum() == table[:4].abs().sum()
+    rewards = [[1.0, 0.0, 0.0, 1.0], [0.5, 0.5], [3.0, 1.0, 2.0]]
+    flat = torch.tensor(sum(rewards, []), device=DEV)
+    offs = torch.tensor([0, 4, 6, 9], device=DEV, dtype=torch.int32)
+    adv, keep = ew.adv_norm(flat, offs)
+    ref = sum((group_advantages(r) for r in rewards), [])
+    assert torch.allclose(adv.cpu(), torch.tensor(ref), atol=1e-5)
+    assert keep.tolist() == [a != 0 for a in ref]
+
+
+def test_lora_wgrad():
+    from art_b200.ops import wgrad
+
+    M, C = 1000, 392
+    p, q = bf(M, C, seed=1), bf(M, 64, seed=2)
+    acc = torch.ones(C, 64, device=DEV)
+    wgrad.accumulate(acc, p, q)
+    assert rel_err(acc, 1 + p.float().t() @ q.float()) < 2e-3
+
+
+def test_flat_adamw_matches_torch():
+    from art_b200.ops.optim import FlatAdamW
+
+    n = 10_000
+    p0 = torch.randn(n, device=DEV)
+    p_ref = p0.clone().requires_grad_(True)
+    opt_ref = torch.optim.AdamW([p_ref], lr=1e-3, betas=(0.9, 0.99), weight_decay=0.1, eps=1e-8)
+    p, g = p0.clone(), torch.zeros(n, device=DEV)
+    opt = FlatAdamW(p, g, max_grad_norm=0.1)
+    for step in range(3):
+        grad = torch.randn(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(step))
+        g.copy_(grad)
+        p_ref.grad = grad.clone()
+        norm_ref = torch.nn.utils.clip_grad_norm_([p_ref], 0.1)
+        opt_ref.step()
+        norm = opt.step(1e-3)
+        assert abs(float(norm) - float(norm_ref)) < 1e-3 * float(norm_ref)
+    assert torch.allclose(p, p_ref.detach(), atol=1e-6, rtol=1e-5)
