@@ -228,3 +228,9 @@ ARTB_EXPORT int artb_lora_grad_allreduce(void* h, long n, float scale, int wait_
                                               dim3(threads), args, 0, st);
   return static_cast<int>(e);
 }
+
+// Clear the sticky failure flag after the host has handled a reported timeout.
+ARTB_EXPORT void artb_symm_reset(void* h) {
+  auto* s = static_cast<SymmState*>(h);
+  cudaMemset(s->gate, 0, 2 * sizeof(uint32_t));
+}
