@@ -355,3 +355,48 @@ ARTB_EXPORT int artb_paged_decode(const void* q, int ldq, const void* k_cache, c
 #undef ARTB_PD
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- allocation-free variant
+// Split-KV decode whose workspace is a file-scope device array (see include/artb_noalloc.h for
+// the contract).  In host code `g_decode_static_ws` is only a handle for the runtime: the device
+// address is obtained once per device with cudaGetSymbolAddress and that pointer is what the
+// kernels receive.
+#include "artb_noalloc.h"
+
+static __device__ __align__(256) float g_decode_static_ws[ARTB_DECODE_STATIC_WS_FLOATS];
+
+static float* decode_static_ws_ptr(int* err) {
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = e != cudaSuccess ? (int)e : ERR_BAD_SHAPE;
+    return nullptr;
+  }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_ws);   // address on the current device
+    if (e != cudaSuccess) {
+      *err = (int)e;
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  *err = 0;
+  return ptrs[dev];
+}
+
+ARTB_EXPORT int artb_paged_decode_noalloc(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                          const int* block_table, int max_blocks, const int* ctx_len, int block_size,
+                                          int num_seqs, int Hq, int Hkv, int hd, void* out, int ldo, int splits,
+                                          cudaStream_t st) {
+  if (num_seqs <= 0) return 0;
+  if (splits < 1 || hd <= 0 || Hq <= 0) return ERR_BAD_SHAPE;
+  const long need = (long)num_seqs * Hq * splits * (hd + 2);
+  if (need > (long)ARTB_DECODE_STATIC_WS_FLOATS) return ERR_TOO_LARGE;
+  int err = 0;
+  float* ws = decode_static_ws_ptr(&err);
+  if (!ws) return err;
+  return artb_paged_decode(q, ldq, k_cache, v_cache, block_table, max_blocks, ctx_len, block_size, num_seqs, Hq, Hkv,
+                           hd, out, ldo, ws, splits, st);
+}
