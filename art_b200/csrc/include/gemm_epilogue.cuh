@@ -1,0 +1,166 @@
+// Tile schedules and the store epilogue shared by the dense GEMM entry points.
+#pragma once
+#include "gemm_pipeline.cuh"
+
+namespace artb {
+
+enum GemmEpilogue : int { EPI_BF16 = 0, EPI_BF16_RESID = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+
+// Tiles are visited with the M index fastest, so the CTAs that run concurrently share a handful
+// of weight (B) tiles and sweep the activation matrix, which stays L2-resident.
+struct SchedMFast {
+  int m_tiles, n_tiles;
+  __device__ int tiles_for_cta(int cta, int ncta) const {
+    const int total = m_tiles * n_tiles;
+    return cta < total ? (total - cta + ncta - 1) / ncta : 0;
+  }
+  __device__ TileInfo get(int cta, int ncta, int i) const {
+    const int t = cta + i * ncta;
+    return make_tile(t % m_tiles, t / m_tiles);
+  }
+};
+
+// Split-K schedule for small-M (decode) GEMMs: work item = (m_blk, n_blk, k_split); every item
+// covers kb_per K blocks of the main operand, the extra-K operand goes with split 0.
+struct SchedSplitK {
+  int m_tiles, n_tiles, splits, kb_per, kb_main;
+  __device__ int tiles_for_cta(int cta, int ncta) const {
+    const int total = m_tiles * n_tiles * splits;
+    return cta < total ? (total - cta + ncta - 1) / ncta : 0;
+  }
+  __device__ TileInfo get(int cta, int ncta, int i) const {
+    const int t = cta + i * ncta;
+    TileInfo ti = make_tile(t % m_tiles, (t / m_tiles) % n_tiles);
+    const int sp = t / (m_tiles * n_tiles);
+    ti.group = sp;
+    ti.kb_lo = sp * kb_per;
+    ti.kb_n = min(kb_per, kb_main - ti.kb_lo);
+    if (ti.kb_n < 0) ti.kb_n = 0;
+    ti.extra = sp == 0;
+    return ti;
+  }
+};
+
+// acc (+ bias) (+ residual on the first res_cols columns) -> C as bf16 or fp32; optional SwiGLU
+// output H for gate|up-interleaved columns (blocks of 16).
+template <int BN>
+struct EpiStore {
+  void* C;
+  const __nv_bfloat16* R;
+  __nv_bfloat16* H;
+  const float* bias;
+  int ldc, ldr, ldh;
+  int M, N;
+  int out_f32;
+  int res_cols;
+
+  __device__ void tile_begin(const TileInfo&, int) {}
+  __device__ void tile_end(const TileInfo&, int) {}
+
+  __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    const int gr = ti.m_blk * GEMM_BM + row;
+    const int gc = ti.n_blk * BN + c;
+    if (gr >= M || gc >= N) return;
+    const bool full = (gc + 32 <= N);
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || gc + j < N) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __ldg(bias + gc + j));
+    }
+    if (R && gc < res_cols) {
+      const __nv_bfloat16* r = R + static_cast<size_t>(gr) * ldr + gc;
+      if (gc + 32 <= res_cols) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 rv = *reinterpret_cast<const uint4*>(r + j);
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(rp[e]);
+            acc[j + 2 * e] = __float_as_uint(__uint_as_float(acc[j + 2 * e]) + f.x);
+            acc[j + 2 * e + 1] = __float_as_uint(__uint_as_float(acc[j + 2 * e + 1]) + f.y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc + j < res_cols) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __bfloat162float(r[j]));
+      }
+    }
+    if (out_f32) {
+      float* out = reinterpret_cast<float*>(C) + static_cast<size_t>(gr) * ldc + gc;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<uint4*>(out + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc + j < N) out[j] = __uint_as_float(acc[j]);
+      }
+      return;
+    }
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<size_t>(gr) * ldc + gc;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]));
+        v.y = pack_bf16x2(__uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+        v.z = pack_bf16x2(__uint_as_float(acc[j + 4]), __uint_as_float(acc[j + 5]));
+        v.w = pack_bf16x2(__uint_as_float(acc[j + 6]), __uint_as_float(acc[j + 7]));
+        *reinterpret_cast<uint4*>(out + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (gc + j < N) out[j] = __float2bfloat16(__uint_as_float(acc[j]));
+    }
+    if (H && full) {
+      // slab = [gate 0..15 | up 0..15]; the activation uses the bf16-rounded values so that a
+      // backward pass that re-reads GU sees exactly what produced H.
+      __nv_bfloat16* h = H + static_cast<size_t>(gr) * ldh + (gc >> 1);
+      uint32_t hv[8];
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        float g0 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[j])));
+        float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[j + 1])));
+        float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[16 + j])));
+        float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[16 + j + 1])));
+        float h0 = g0 / (1.f + __expf(-g0)) * u0;
+        float h1 = g1 / (1.f + __expf(-g1)) * u1;
+        hv[j >> 1] = pack_bf16x2(h0, h1);
+      }
+      *reinterpret_cast<uint4*>(h) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
+      *reinterpret_cast<uint4*>(h + 8) = make_uint4(hv[4], hv[5], hv[6], hv[7]);
+    }
+  }
+};
+
+// Split-K partial: fp32 atomic accumulation into a zero-initialised workspace [M, ldw].
+template <int BN>
+struct EpiAtomic {
+  float* W;
+  int ldw, M, N;
+  __device__ void tile_begin(const TileInfo&, int) {}
+  __device__ void tile_end(const TileInfo&, int) {}
+  __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    const int gr = ti.m_blk * GEMM_BM + row;
+    const int gc = ti.n_blk * BN + c;
+    if (gr >= M || gc >= N || ti.kb_n == 0) return;
+    float* w = W + static_cast<size_t>(gr) * ldw + gc;
+    if (gc + 32 <= N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        atomicAdd(reinterpret_cast<float4*>(w + j),
+                  make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]), __uint_as_float(acc[j + 2]),
+                              __uint_as_float(acc[j + 3])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (gc + j < N) atomicAdd(w + j, __uint_as_float(acc[j]));
+    }
+  }
+};
+
+}  // namespace artb

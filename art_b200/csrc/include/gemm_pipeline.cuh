@@ -34,8 +34,23 @@ struct TileInfo {
   int n_blk;   // tile column index (cols n_blk*BN ..)
   int first;   // first tile of an epilogue group (policy-defined)
   int last;    // last tile of an epilogue group
-  int group;   // policy-defined group id (e.g. vocabulary split)
+  int group;   // policy-defined group id (e.g. vocabulary split, K split)
+  int kb_lo;   // first main-operand K block of this tile (split-K); 0 for a full tile
+  int kb_n;    // number of main-operand K blocks; < 0 means "all of them"
+  int extra;   // include the extra-K operand blocks in this tile
 };
+
+__device__ __forceinline__ TileInfo make_tile(int m_blk, int n_blk) {
+  TileInfo ti;
+  ti.m_blk = m_blk;
+  ti.n_blk = n_blk;
+  ti.first = ti.last = 1;
+  ti.group = 0;
+  ti.kb_lo = 0;
+  ti.kb_n = -1;
+  ti.extra = 1;
+  return ti;
+}
 
 template <int BN, int STAGES>
 struct GemmSmemLayout {
@@ -71,7 +86,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kb_total = kb_main + kb_extra;
   const int my_tiles = sched.tiles_for_cta(blockIdx.x, gridDim.x);
 
   if (threadIdx.x == 0) {
@@ -107,7 +121,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t it = 0;
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int nmain = ti.kb_n < 0 ? kb_main : ti.kb_n;
+        const int ntile = nmain + (ti.extra ? kb_extra : 0);
+        for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -119,11 +135,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-          if (kb < kb_main) {
-            tma_load_2d(sa, &tmA, kb * GEMM_BK, ti.m_blk * GEMM_BM, &full_bar[s]);
-            tma_load_2d(sb, &tmB, kb * GEMM_BK, ti.n_blk * BN, &full_bar[s]);
+          if (kb < nmain) {
+            tma_load_2d(sa, &tmA, (ti.kb_lo + kb) * GEMM_BK, ti.m_blk * GEMM_BM, &full_bar[s]);
+            tma_load_2d(sb, &tmB, (ti.kb_lo + kb) * GEMM_BK, ti.n_blk * BN, &full_bar[s]);
           } else {
-            const int k2 = (kb - kb_main) * GEMM_BK;
+            const int k2 = (kb - nmain) * GEMM_BK;
             tma_load_2d(sa, &tmA2, k2, ti.m_blk * GEMM_BM, &full_bar[s]);
             tma_load_2d(sb, &tmB2, k2, ti.n_blk * BN, &full_bar[s]);
           }
@@ -145,7 +161,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
+        const int ntile = (ti.kb_n < 0 ? kb_main : ti.kb_n) + (ti.extra ? kb_extra : 0);
+        for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph)) {

@@ -1,0 +1,210 @@
+// 2-CTA variant of the tcgen05 GEMM pipeline: a cluster of two CTAs computes one 256 x 256
+// output tile with `tcgen05.mma.cta_group::2` (UMMA M = 256, N = 256, K = 16).
+//
+// Why: with one CTA per 128 x 256 tile every UMMA reads 4 KB of A and 8 KB of B from shared
+// memory while TMA writes the same amount, which saturates the 128 B/clk shared-memory port.
+// In a pair each CTA stages only its own 128 rows of A and its own 128-row half of B (the
+// tensor core reads the other half from the partner's shared memory), so per-SM staging traffic
+// drops by a third and the B panel is fetched from L2 once per pair.
+//
+// Protocol (rank 0 of the pair is the leader):
+//   full[s]    leader only, count 1 (+ tx bytes of BOTH CTAs' loads; TMA uses .cta_group::2 so the
+//              partner's loads credit the leader's barrier; no multicast qualifier anywhere)
+//   empty[s]   in both CTAs, count 1, signalled by the leader's tcgen05.commit multicast to both
+//   tfull[b]   in both CTAs, count 1, same multicast commit once a tile's MMAs are issued
+//   tempty[b]  leader only, count 8: the 4 epilogue warps of each CTA arrive (the partner remotely)
+// All waits are bounded; a timeout sets the CTA's abort flag and the status word, and the CTA
+// falls through to the teardown (cluster barrier, TMEM dealloc).
+#pragma once
+#include "gemm_pipeline.cuh"
+
+namespace artb {
+
+constexpr int G2_BN = 256;        // cluster tile N
+constexpr int G2_BNH = 128;       // B rows staged per CTA
+constexpr int G2_STAGE_BYTES = (GEMM_BM + G2_BNH) * GEMM_BK * 2;   // 32 KB
+
+template <int STAGES>
+struct Gemm2SmemLayout {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int BAR_OFFSET = STAGES * G2_STAGE_BYTES;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = BAR_OFFSET + BAR_BYTES + 1024;
+};
+
+template <int STAGES, class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                         int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status) {
+  using L = Gemm2SmemLayout<STAGES>;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+  const int total_tiles = m_tiles2 * n_tiles;
+  const int my_tiles = cluster_id < total_tiles ? (total_tiles - cluster_id + n_clusters - 1) / n_clusters : 0;
+  const int kb_total = kb_main + kb_extra;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        const int tile = cluster_id + t * n_clusters;
+        const int m2 = tile % m_tiles2, nb = tile / m_tiles2;
+        const int row_a = m2 * 2 * GEMM_BM + rank * GEMM_BM;
+        const int row_b = nb * G2_BN + rank * G2_BNH;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            atomicMax(status, ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            break;
+          }
+          if (*abort_flag) break;
+          uint8_t* sa = smem + s * G2_STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * G2_STAGE_BYTES);
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
+          if (kb < kb_main) {
+            tma_load_2d_2cta(sa, &tmA, kb * GEMM_BK, row_a, fb);
+            tma_load_2d_2cta(sb, &tmB, kb * GEMM_BK, row_b, fb);
+          } else {
+            const int k2 = (kb - kb_main) * GEMM_BK;
+            tma_load_2d_2cta(sa, &tmA2, k2, row_a, fb);
+            tma_load_2d_2cta(sb, &tmB2, k2, row_b, fb);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * GEMM_BM, G2_BN);
+      uint32_t it = 0;
+      for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
+        const int buf = t & 1;
+        const uint32_t aph = (t >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[buf], aph ^ 1)) {
+          atomicMax(status, ST_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * G2_BN;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph)) {
+            atomicMax(status, ST_TIMEOUT_FULL);
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * G2_STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+          const uint64_t adesc = umma_smem_desc_k128(sa);
+          const uint64_t bdesc = umma_smem_desc_k128(sb);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k)
+            tc_mma_f16_2cta(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          tc_commit_2cta(&empty_bar[s], 3);   // both CTAs may refill this stage once the MMAs retire
+        }
+        if (*abort_flag) break;
+        tc_commit_2cta(&tfull_bar[buf], 3);   // accumulator complete in both CTAs
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    Epi epi = epi_in;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    for (int t = 0; t < my_tiles; ++t) {
+      if (__shfl_sync(0xffffffffu, *abort_flag, 0)) break;
+      const int tile = cluster_id + t * n_clusters;
+      TileInfo ti = make_tile((tile % m_tiles2) * 2 + static_cast<int>(rank), tile / m_tiles2);
+      const int buf = t & 1;
+      const uint32_t aph = (t >> 1) & 1;
+      const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) {
+          atomicMax(status, ST_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after_sync();
+      epi.tile_begin(ti, row);
+      const uint32_t taddr = tmem_base + buf * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < G2_BN; c += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c, acc);
+        tmem_ld_wait();
+        epi.chunk(ti, row, c, acc);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[buf]), 0));
+      epi.tile_end(ti, row);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  // neither CTA may leave (or free TMEM) while its partner can still touch its barriers / smem
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace artb

@@ -40,9 +40,8 @@ struct SchedVocabSplit {
   __device__ TileInfo get(int cta, int ncta, int i) const {
     const int item = cta + (i / tiles_per_split) * ncta;
     const int j = i % tiles_per_split;
-    TileInfo ti;
+    TileInfo ti = make_tile(item % m_tiles, 0);
     ti.group = item / m_tiles;  // split
-    ti.m_blk = item % m_tiles;
     ti.n_blk = ti.group * tiles_per_split + j;
     ti.first = (j == 0);
     ti.last = (j == tiles_per_split - 1);

@@ -51,7 +51,10 @@ class BlockManager:
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
         if h:
-            _rt().artb_bm_destroy(h)
+            try:
+                _rt().artb_bm_destroy(h)
+            except Exception:   # interpreter shutdown: the library handle may already be gone
+                pass
 
     @property
     def num_free(self) -> int:

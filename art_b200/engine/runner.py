@@ -16,6 +16,7 @@ Both return ``(token_ids, logprobs)`` as Python lists so the scheduler is device
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -105,18 +106,33 @@ class ReferenceRunner:
 
 # ---------------------------------------------------------------------------------- native
 class EngineLinear:
-    """A frozen projection plus ``max_loras`` adapter slots packed into the extra-K operands."""
+    """A frozen projection plus ``max_loras`` adapter slots.
 
-    def __init__(self, W: torch.Tensor, bias: torch.Tensor | None, member_rows: list[tuple[str, torch.Tensor]],
-                 r: int, max_loras: int):
-        self.W, self.bias = W, bias
-        self.members = member_rows                      # [(module name, row indices in the fused weight)]
-        self.r = r
-        self.cols = len(member_rows) * r                # columns per adapter
-        self.kpad = max(64, (max_loras * self.cols + 63) // 64 * 64)
+    The weight is stored as ``W_ext = [W ; A_all]`` (the stacked shrink factors of all resident
+    adapters are extra output rows), so at decode time one weight-streaming GEMM yields both the
+    base product and ``T = X A_all^T``; after the per-row slot mask a small second GEMM adds
+    ``T (sB_all)^T``.  Large-M (prefill) calls use the extra-K form instead.
+    """
+
+    def __init__(self, lin, member_rows: list[tuple[str, torch.Tensor]], r: int, max_loras: int, ws_holder: dict):
+        W = lin.W
         N, K = W.shape
-        self.A_all = torch.zeros(self.kpad, K, dtype=torch.bfloat16, device=W.device)
+        self.N, self.K = N, K
+        self.members = member_rows
+        self.r = r
+        self.cols = len(member_rows) * r
+        self.kpad = max(64, (max_loras * self.cols + 63) // 64 * 64)
+        self.W_ext = torch.zeros(N + self.kpad, K, dtype=torch.bfloat16, device=W.device)
+        self.W_ext[:N] = W
+        lin.W = self.W_ext[:N]                 # the trainer keeps using the same storage: no second copy of W
+        self.W = self.W_ext[:N]
+        self.A_all = self.W_ext[N:]
         self.B_all = torch.zeros(N, self.kpad, dtype=torch.bfloat16, device=W.device)
+        self.bias_ext = None
+        if lin.bias is not None:
+            self.bias_ext = torch.zeros(N + self.kpad, dtype=torch.float32, device=W.device)
+            self.bias_ext[:N] = lin.bias
+        self.ws_holder = ws_holder
 
     def load_slot(self, slot: int, layer: int, state: dict[str, torch.Tensor] | None, scale: float) -> None:
         c0 = slot * self.cols
@@ -133,16 +149,48 @@ class EngineLinear:
             self.A_all[c:c + self.r] = a           # device-to-device copy straight from the trainer's master buffer
             self.B_all[rows, c:c + self.r] = (b * scale).to(torch.bfloat16)
 
+    def _ws(self, M: int, N: int, device) -> torch.Tensor:
+        ws = self.ws_holder.get("ws")
+        if ws is None or ws.shape[0] < M or ws.shape[1] < N:
+            ws = torch.zeros((max(M, 512), max(N, 40960)), dtype=torch.float32, device=device)
+            self.ws_holder["ws"] = ws
+        return ws
+
     def __call__(self, x, adapter_ids, any_lora: bool, residual=None, swiglu_out=None):
-        from ..ops.gemm import gemm_tn
+        from ..ops import elementwise as ew
+        from ..ops.gemm import gemm_splitk_, gemm_tn, plan_small_m, splitk_finalize
         from ..ops.paged import lora_slot_mask_
 
-        bn = 64 if x.shape[0] <= 512 else 0
-        if any_lora:
-            T = gemm_tn(x, self.A_all, bn=64)
-            lora_slot_mask_(T, adapter_ids, self.cols)
-            return gemm_tn(x, self.W, a2=T, b2=self.B_all, residual=residual, swiglu_out=swiglu_out, bias=self.bias, bn=bn)
-        return gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out, bias=self.bias, bn=bn)
+        M = x.shape[0]
+        if M > 512:     # prefill: compute-bound, LoRA as extra K
+            if any_lora:
+                T = gemm_tn(x, self.A_all, bn=64)
+                lora_slot_mask_(T, adapter_ids, self.cols)
+                return gemm_tn(x, self.W, a2=T, b2=self.B_all, residual=residual, swiglu_out=swiglu_out,
+                               bias=None if self.bias_ext is None else self.bias_ext[:self.N])
+            return gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out,
+                           bias=None if self.bias_ext is None else self.bias_ext[:self.N])
+        N = self.N
+        Next = N + self.kpad if any_lora else N
+        Wv = self.W_ext[:Next]
+        bias = None if self.bias_ext is None else self.bias_ext[:Next]
+        bn, splits = plan_small_m(M, Next, self.K)
+        y_ext = torch.empty((M, Next), dtype=torch.bfloat16, device=x.device)
+        fuse_swiglu = swiglu_out is not None and not any_lora and splits == 1
+        if splits > 1:
+            ws = self._ws(M, Next, x.device)
+            gemm_splitk_(ws, x, Wv, bn, splits)
+            splitk_finalize(ws, y_ext, bias, residual, N)
+        else:
+            gemm_tn(x, Wv, out=y_ext, bias=bias, residual=residual, res_cols=N, bn=bn,
+                    swiglu_out=swiglu_out if fuse_swiglu else None)
+        if not any_lora:
+            if swiglu_out is not None and not fuse_swiglu:
+                ew.swiglu_fwd(y_ext, out=swiglu_out)
+            return y_ext
+        T = y_ext[:, N:]
+        lora_slot_mask_(T, adapter_ids, self.cols)
+        return gemm_tn(T, self.B_all, residual=y_ext[:, :N], swiglu_out=swiglu_out)
 
 
 class NativeRunner:
@@ -191,13 +239,14 @@ class NativeRunner:
         gate_rows = (fidx // 16) * 32 + fidx % 16
         r = lora_cfg.r
         self.layers = []
+        self._ws_holder: dict = {}
         for i, L in enumerate(decoder.layers):
             self.layers.append({
-                "qkv": EngineLinear(L["qkv"].W, L["qkv"].bias, [("self_attn.q_proj", ar(0, q)), ("self_attn.k_proj", ar(q, q + kvw)),
-                                                               ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw))], r, max_loras),
-                "o": EngineLinear(L["o"].W, None, [("self_attn.o_proj", ar(0, d))], r, max_loras),
-                "gu": EngineLinear(L["gu"].W, None, [("mlp.gate_proj", gate_rows), ("mlp.up_proj", gate_rows + 16)], r, max_loras),
-                "down": EngineLinear(L["down"].W, None, [("mlp.down_proj", ar(0, d))], r, max_loras),
+                "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q)), ("self_attn.k_proj", ar(q, q + kvw)),
+                                               ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw))], r, max_loras, self._ws_holder),
+                "o": EngineLinear(L["o"], [("self_attn.o_proj", ar(0, d))], r, max_loras, self._ws_holder),
+                "gu": EngineLinear(L["gu"], [("mlp.gate_proj", gate_rows), ("mlp.up_proj", gate_rows + 16)], r, max_loras, self._ws_holder),
+                "down": EngineLinear(L["down"], [("mlp.down_proj", ar(0, d))], r, max_loras, self._ws_holder),
                 "ln1": L["ln1"], "ln2": L["ln2"], "q_norm": L.get("q_norm"), "k_norm": L.get("k_norm"),
             })
         self.slot_loaded = [False] * max_loras
@@ -325,45 +374,104 @@ class NativeRunner:
         return lpl.grpo_tokens(part).logprobs.tolist()
 
     # -- decode -------------------------------------------------------------------------------------
-    def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
+    # The multi-step decode runs on persistent device buffers (one set per batch-size bucket) so that
+    # the whole run of n_steps x (all layers + sampler + state advance) can be captured in a CUDA
+    # graph and replayed: a decode step is ~500 small launches, which the host cannot issue as fast
+    # as the GPU retires them.  The first use of a (bucket, n_steps, lora, splits, table width) key
+    # runs eagerly, the second captures, later ones replay.
+    BUCKETS = (8, 16, 32, 64, 128, 256, 512, 1024)
+
+    def _decode_state(self, nb: int, max_blocks: int, n_steps: int):
+        key = (nb, max_blocks, n_steps)
+        st = self._dstate.get(key) if hasattr(self, "_dstate") else None
+        if st is None:
+            if not hasattr(self, "_dstate"):
+                self._dstate, self._dgraphs, self._dseen = {}, {}, set()
+            dev, cfg = self.device, self.cfg
+            st = {
+                "tokens": torch.zeros(nb, dtype=torch.int64, device=dev), "pos": torch.zeros(nb, dtype=torch.int32, device=dev),
+                "ctx": torch.zeros(nb, dtype=torch.int32, device=dev), "slot": torch.full((nb,), -1, dtype=torch.int32, device=dev),
+                "ad": torch.full((nb,), -1, dtype=torch.int32, device=dev), "active": torch.zeros(nb, dtype=torch.int32, device=dev),
+                "inv_t": torch.zeros(nb, dtype=torch.float32, device=dev),
+                "seeds": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
+                "bt": torch.zeros((nb, max_blocks), dtype=torch.int32, device=dev),
+                "out_t": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
+                "out_l": torch.zeros((n_steps, nb), dtype=torch.float32, device=dev),
+                "attn_out": torch.zeros((nb, cfg.q_size), dtype=torch.bfloat16, device=dev),
+            }
+            self._dstate[key] = st
+        return st
+
+    def _decode_body(self, st, n_steps: int, any_lora: bool, splits: int, ws):
         from ..ops import elementwise as ew
         from ..ops import paged
 
+        cfg, bs = self.cfg, self.kv.shape[1]
+        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        for k in range(n_steps):
+            x = ew.gather_rows(self.embed, st["tokens"])
+            for li, L in enumerate(self.layers):
+                qkv = self._qkv(L, x, st["pos"], st["ad"], any_lora)
+                paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, st["slot"], self.kv.k[li], self.kv.v[li])
+                paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], st["bt"], st["ctx"], Hq, Hkv, hd, st["attn_out"], splits, ws)
+                x2 = L["o"](st["attn_out"], st["ad"], any_lora, residual=x)
+                x = self._mlp(L, x2, st["ad"], any_lora)
+            hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
+            t, lp = paged.sample(hidden, self.lm_head, st["inv_t"], st["seeds"][k])
+            st["out_t"][k].copy_(t)
+            st["out_l"][k].copy_(lp)
+            if k + 1 < n_steps:
+                paged.decode_advance(t, st["tokens"], st["pos"], st["ctx"], st["slot"], st["bt"], bs, st["active"])
+
+    def decode(self, seqs: list[SeqView], n_steps: int, use_graph: bool = True) -> tuple[list[list[int]], list[list[float]]]:
         cfg, dev, bs = self.cfg, self.device, self.kv.shape[1]
         n = len(seqs)
-        max_blocks = max(len(s.blocks) for s in seqs)
-        bt = torch.zeros((n, max_blocks), dtype=torch.int32)
+        nb = next((b for b in self.BUCKETS if b >= n), (n + 255) // 256 * 256)
+        need_blocks = max(len(s.blocks) for s in seqs)
+        max_blocks = 64
+        while max_blocks < need_blocks:
+            max_blocks *= 2
+        st = self._decode_state(nb, max_blocks, n_steps)
+        lens = [len(s.tokens) for s in seqs]
+        pad = nb - n
+        bt = torch.zeros((nb, max_blocks), dtype=torch.int32)
         for i, s in enumerate(seqs):
             bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
-        bt = bt.to(dev, non_blocking=True)
-        lens = [len(s.tokens) for s in seqs]
-        tokens = torch.tensor([s.tokens[-1] for s in seqs], dtype=torch.int64, device=dev)
-        pos = torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=dev)
-        ctx = torch.tensor(lens, dtype=torch.int32, device=dev)
-        slot = torch.tensor([s.blocks[(l - 1) // bs] * bs + (l - 1) % bs for s, l in zip(seqs, lens)], dtype=torch.int32, device=dev)
-        ad = torch.tensor([s.adapter for s in seqs], dtype=torch.int32, device=dev)
+        st["bt"].copy_(bt, non_blocking=True)
+        st["tokens"].copy_(torch.tensor([s.tokens[-1] for s in seqs] + [0] * pad, dtype=torch.int64), non_blocking=True)
+        st["pos"].copy_(torch.tensor([l - 1 for l in lens] + [0] * pad, dtype=torch.int32), non_blocking=True)
+        st["ctx"].copy_(torch.tensor(lens + [0] * pad, dtype=torch.int32), non_blocking=True)
+        st["slot"].copy_(torch.tensor([s.blocks[(l - 1) // bs] * bs + (l - 1) % bs for s, l in zip(seqs, lens)] + [-1] * pad,
+                                      dtype=torch.int32), non_blocking=True)
+        st["ad"].copy_(torch.tensor([s.adapter for s in seqs] + [-1] * pad, dtype=torch.int32), non_blocking=True)
+        st["active"].copy_(torch.tensor([1] * n + [0] * pad, dtype=torch.int32), non_blocking=True)
+        st["inv_t"].copy_(torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs] + [0.0] * pad,
+                                       dtype=torch.float32), non_blocking=True)
+        seeds = torch.tensor([[_mix_seed(s.seed, s.step + k) for s in seqs] + [0] * pad for k in range(n_steps)],
+                             dtype=torch.int64).to(torch.int32)
+        st["seeds"].copy_(seeds, non_blocking=True)
         any_lora = any(s.adapter >= 0 for s in seqs)
-        inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
-        seeds = torch.tensor([[_mix_seed(s.seed, s.step + k) for s in seqs] for k in range(n_steps)], dtype=torch.int64,
-                             device=dev).to(torch.int32)
-        out_t = torch.empty((n_steps, n), dtype=torch.int32, device=dev)
-        out_l = torch.empty((n_steps, n), dtype=torch.float32, device=dev)
-        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         max_ctx = max(lens) + n_steps
-        splits = 1 if n * Hkv >= 128 else min(8, max(1, max_ctx // 512))
-        ws = torch.empty(n * Hq * splits * (hd + 2), dtype=torch.float32, device=dev) if splits > 1 else None
-        attn_out = torch.empty((n, cfg.q_size), dtype=torch.bfloat16, device=dev)
-        for k in range(n_steps):
-            x = ew.gather_rows(self.embed, tokens)
-            for li, L in enumerate(self.layers):
-                qkv = self._qkv(L, x, pos, ad, any_lora)
-                paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, slot, self.kv.k[li], self.kv.v[li])
-                paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], bt, ctx, Hq, Hkv, hd, attn_out, splits, ws)
-                x2 = L["o"](attn_out, ad, any_lora, residual=x)
-                x = self._mlp(L, x2, ad, any_lora)
-            hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
-            t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds[k])
-            out_t[k], out_l[k] = t, lp
-            if k + 1 < n_steps:
-                paged.decode_advance(t, tokens, pos, ctx, slot, bt, bs)
-        return out_t.tolist(), out_l.tolist()
+        splits = 1 if nb * cfg.num_kv_heads >= 128 else min(8, max(1, 1 << (max(1, max_ctx // 512).bit_length() - 1)))
+        key = (nb, max_blocks, n_steps, any_lora, splits)
+        ws = None
+        if splits > 1:
+            ws = st.get(("ws", splits))
+            if ws is None:
+                ws = st[("ws", splits)] = torch.empty(nb * cfg.num_heads * splits * (cfg.head_dim + 2), dtype=torch.float32, device=dev)
+        graph = self._dgraphs.get(key)
+        if graph is not None:
+            graph.replay()
+        elif use_graph and key in self._dseen and not os.environ.get("ARTB_DECODE_NO_GRAPH"):
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._decode_body(st, n_steps, any_lora, splits, ws)
+            self._dgraphs[key] = graph
+            graph.replay()
+        else:
+            self._dseen.add(key)
+            self._decode_body(st, n_steps, any_lora, splits, ws)
+        out_t = st["out_t"][:, :n].tolist()
+        out_l = st["out_l"][:, :n].tolist()
+        return out_t, out_l

@@ -21,7 +21,7 @@ def _fn():
     f = _lib.kernels().artb_gemm_bf16_tn
     if not _configured:
         vp, ci = ctypes.c_void_p, ctypes.c_int
-        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
+        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, ci, vp]
         f.restype = ci
         _configured = True
     return f
@@ -36,7 +36,7 @@ def _check2d(t: torch.Tensor, name: str) -> None:
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
             b2: torch.Tensor | None = None, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, swiglu_out: torch.Tensor | None = None,
-            bias: torch.Tensor | None = None,
+            bias: torch.Tensor | None = None, res_cols: int = 0,
             out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K].T (+ a2[M,K2] @ b2[N,K2].T) (+ residual)``.
 
@@ -82,7 +82,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
         _lib.ptr(swiglu_out), swiglu_out.stride(0) if swiglu_out is not None else 0,
         _lib.ptr(bias),
-        M, N, K, epi, bn, _lib.ptr(st), max_ctas, _lib.stream_ptr())
+        M, N, K, epi, res_cols, bn, _lib.ptr(st), max_ctas, _lib.stream_ptr())
     _lib.check_rc(rc, "gemm_tn")
     return out
 
@@ -97,3 +97,50 @@ def reference_gemm_tn(a, b, a2=None, b2=None, residual=None, bias=None) -> torch
     if residual is not None:
         c = c + residual.float()
     return c
+
+
+_sk_configured = False
+
+
+def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, splits: int) -> None:
+    """``ws[M, :N] += a @ b.T`` with the K dimension split across CTAs (fp32 atomics); ``ws`` fp32, zero on entry."""
+    global _sk_configured
+    f = _lib.kernels().artb_gemm_splitk_bf16_tn
+    g = _lib.kernels().artb_splitk_finalize
+    if not _sk_configured:
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        f.argtypes = [vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, vp]
+        f.restype = ci
+        g.argtypes = [vp, ci, vp, ci, vp, ci, ci, vp, ci, ci, vp]
+        g.restype = ci
+        _sk_configured = True
+    _check2d(a, "a")
+    _check2d(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    rc = f(_lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0), _lib.ptr(ws), ws.stride(0), M, N, K, bn, splits,
+           _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+    _lib.check_rc(rc, "gemm_splitk")
+
+
+def splitk_finalize(ws: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+                    residual: torch.Tensor | None = None, res_cols: int = 0) -> torch.Tensor:
+    """``out = bf16(ws[:, :N] + bias + residual)`` and ``ws[:, :N] = 0``."""
+    g = _lib.kernels().artb_splitk_finalize
+    M, N = out.shape
+    rc = g(_lib.ptr(ws), ws.stride(0), _lib.ptr(out), out.stride(0), _lib.ptr(residual),
+           residual.stride(0) if residual is not None else 0, res_cols, _lib.ptr(bias), M, N, _lib.stream_ptr())
+    _lib.check_rc(rc, "splitk_finalize")
+    return out
+
+
+def plan_small_m(M: int, N: int, K: int, sms: int = 148) -> tuple[int, int]:
+    """(bn, splits) for a weight-streaming GEMM: widest N tile, then split K until the machine is full."""
+    m_tiles = (M + 127) // 128
+    bn = 256 if N >= 256 else (128 if N >= 128 else 64)
+    tiles = m_tiles * ((N + bn - 1) // bn)
+    kb = (K + 63) // 64
+    if tiles >= 100:
+        return bn, 1
+    splits = max(1, min((sms + tiles - 1) // tiles, max(1, kb // 4)))
+    return bn, splits
