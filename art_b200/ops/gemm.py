@@ -7,6 +7,7 @@ PyTorch restatement used by the tests.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -14,6 +15,8 @@ from . import _lib
 
 EPI_BF16, EPI_BF16_RESID, EPI_F32, EPI_SWIGLU = 0, 1, 2, 3
 _configured = False
+_configured2 = False
+TWO_CTA_DEFAULT = os.environ.get("ARTB_GEMM_2CTA", "1") == "1"
 
 
 def _fn():
@@ -27,6 +30,17 @@ def _fn():
     return f
 
 
+def _fn2():
+    global _configured2
+    f = _lib.kernels().artb_gemm_bf16_tn_2cta
+    if not _configured2:
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        f.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp]
+        f.restype = ci
+        _configured2 = True
+    return f
+
+
 def _check2d(t: torch.Tensor, name: str) -> None:
     if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(1) != 1:
         raise ValueError(f"{name}: expected a 2-D bf16 CUDA tensor with unit inner stride, got "
@@ -37,7 +51,8 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
             b2: torch.Tensor | None = None, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, swiglu_out: torch.Tensor | None = None,
             bias: torch.Tensor | None = None, res_cols: int = 0,
-            out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+            out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0,
+            two_cta: bool | None = None) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K].T (+ a2[M,K2] @ b2[N,K2].T) (+ residual)``.
 
     ``swiglu_out`` ([M, N/2] bf16) selects the SwiGLU epilogue: ``b``'s rows must be
@@ -74,6 +89,20 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise ValueError("bias must be fp32 [N]")
     st = _lib.status_word(a.device)
+    if two_cta is None:
+        two_cta = TWO_CTA_DEFAULT and bn == 0 and M >= 1024 and N >= 512
+    if two_cta:
+        rc = _fn2()(
+            _lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0),
+            _lib.ptr(a2), a2.stride(0) if a2 is not None else 0,
+            _lib.ptr(b2), b2.stride(0) if b2 is not None else 0, K2,
+            _lib.ptr(out), out.stride(0),
+            _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+            _lib.ptr(swiglu_out), swiglu_out.stride(0) if swiglu_out is not None else 0,
+            _lib.ptr(bias),
+            M, N, K, epi, res_cols, _lib.ptr(st), max_ctas // 2, _lib.stream_ptr())
+        _lib.check_rc(rc, "gemm_tn_2cta")
+        return out
     rc = _fn()(
         _lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0),
         _lib.ptr(a2), a2.stride(0) if a2 is not None else 0,
