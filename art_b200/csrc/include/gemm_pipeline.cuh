@@ -63,12 +63,23 @@ struct GemmSmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + BAR_BYTES + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES, class Sched, class Epi>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// Communication policy of a fused compute+collective kernel.  `THREADS` extra threads (whole
+// warps, after the six pipeline warps) run `push()` concurrently with the main loop; the producer
+// calls `ready()` before the first load of a tile (bounded wait on data pushed by peers); thread 0
+// calls `finish()` after every store of the CTA has been issued.
+struct NoComm {
+  static constexpr int THREADS = 0;
+  __device__ void push(int /*tid*/, int* /*status*/) const {}
+  __device__ bool ready(const TileInfo&) const { return true; }
+  __device__ void finish(int* /*status*/) const {}
+};
+
+template <int BN, int STAGES, class Sched, class Epi, class Comm = NoComm>
+__global__ void __launch_bounds__(GEMM_THREADS + Comm::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB2, int kb_main, int kb_extra,
-                    Sched sched, Epi epi_in, int* status) {
+                    Sched sched, Epi epi_in, int* status, Comm comm) {
   using L = GemmSmemLayout<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
@@ -123,6 +134,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
         const int nmain = ti.kb_n < 0 ? kb_main : ti.kb_n;
         const int ntile = nmain + (ti.extra ? kb_extra : 0);
+        if (!comm.ready(ti)) {
+          atomicMax(status, ST_TIMEOUT_PEER);
+          *abort_flag = 1;
+          break;
+        }
         for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -187,6 +203,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_commit(&tfull_bar[buf]);  // accumulator complete
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ communication warps
+    comm.push(static_cast<int>(threadIdx.x) - GEMM_THREADS, status);
   } else {
     // ------------------------------------------------------------ epilogue
     Epi epi = epi_in;
@@ -226,6 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && !*abort_flag) comm.finish(status);
   if (*abort_flag) {
     // Give any copy that is still in flight time to land before smem is released.
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);

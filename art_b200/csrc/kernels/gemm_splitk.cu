@@ -36,7 +36,7 @@ static int launch_splitk(const CUtensorMap& tA, const CUtensorMap& tB, int kb_ma
   int grid = sched.m_tiles * sched.n_tiles * splits;
   if (grid > sm_count()) grid = sm_count();
   EpiAtomic<BN> epi{ws, ldw, M, N};
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, sched, epi, status);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, sched, epi, status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -39,7 +39,7 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
-                                                 status);
+                                                 status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -362,7 +362,7 @@ static int launch_lp(const void* H, int ldh, const void* W, int ldw, int M, int 
   int grid = sched.m_tiles * splits;
   if (grid > sm_count()) grid = sm_count();
   kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, (K + GEMM_BK - 1) / GEMM_BK, 0, sched, epi,
-                                                 status);
+                                                 status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 
