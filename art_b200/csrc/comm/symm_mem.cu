@@ -23,27 +23,11 @@
 
 #include "host_utils.h"
 #include "ptx_sm100.cuh"
+#include "symm.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace artb {
-
-constexpr int MAX_RANKS = 16;
-constexpr int PAD_SLOTS = 64;   // uint64 epoch slots per rank (slot q of channel c at c*16+q)
-
-struct PeerTable {
-  void* base[MAX_RANKS];      // data area of every rank (own included)
-  uint64_t* pad[MAX_RANKS];   // signal pad of every rank
-};
-
-__device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 
 // Executed by the first `world` threads of ONE block.  Returns false on timeout.
 __device__ __forceinline__ bool epoch_barrier(const PeerTable& pt, int rank, int world, int channel, uint64_t epoch,
@@ -125,15 +109,6 @@ lora_grad_allreduce_kernel(PeerTable pt, int rank, int world, long n, float scal
   grid_epoch_barrier(pt, rank, world, 0, 2 * epoch + 1, spin_limit, gate, status);
 }
 
-struct SymmState {
-  int rank = -1, world = 0;
-  size_t data_bytes = 0;
-  void* local = nullptr;          // cudaMalloc'd: data area + pad
-  PeerTable table;
-  void* opened[MAX_RANKS];
-  uint32_t* gate = nullptr;
-  uint64_t epoch = 0;
-};
 
 }  // namespace artb
 

@@ -1,0 +1,264 @@
+// Schedule / communication / epilogue policies that turn the tcgen05 GEMM pipeline into the two
+// tensor-parallel fused kernels:
+//
+//   all-gather -> GEMM   (column-parallel linear, activations sharded along tokens)
+//   GEMM -> reduce-scatter (row-parallel linear, output sharded along tokens)
+//
+// All cross-GPU traffic is plain st/ld through peer pointers of a symmetric buffer; the TMA
+// loads of the GEMM only ever read this GPU's own memory (remote shards are pushed into the local
+// copy of the gathered matrix first).  Flags carry a monotonically increasing call number
+// ("epoch"), so nothing is reset between calls; buffers are double-buffered by epoch parity and a
+// per-rank "done" word tells writers that the call two epochs back has been fully consumed.
+// Every wait is bounded and reports ST_TIMEOUT_PEER.
+#pragma once
+#include "gemm_epilogue.cuh"
+#include "symm.cuh"
+
+namespace artb {
+
+constexpr int TP_MAX = 8;
+constexpr int TP_PUSH_ROWS = 32;   // rows per push unit / arrival flag
+
+// Token segments (one per rank) are visited in rotated order, M fastest inside a segment.
+// first_off = 0: own segment first (all-gather: local data is there already);
+// first_off = 1: own segment last  (reduce-scatter: peers' partials arrive while we compute theirs).
+struct SchedSegRot {
+  int seg_m_tiles, n_tiles, world, rank, first_off;
+  __device__ int tiles_for_cta(int cta, int ncta) const {
+    const int total = seg_m_tiles * n_tiles * world;
+    return cta < total ? (total - cta + ncta - 1) / ncta : 0;
+  }
+  __device__ TileInfo get(int cta, int ncta, int i) const {
+    const int t = cta + i * ncta;
+    const int per_seg = seg_m_tiles * n_tiles;
+    const int si = t / per_seg, rem = t - si * per_seg;
+    const int seg = (rank + first_off + si) % world;
+    TileInfo ti = make_tile(seg * seg_m_tiles + rem % seg_m_tiles, rem / seg_m_tiles);
+    ti.group = seg;
+    return ti;
+  }
+};
+
+struct TpPeers {
+  char* base[TP_MAX];   // data area of every rank's symmetric buffer
+};
+
+// Select chain instead of a dynamic index, so that a policy object holding the table can stay in
+// registers.
+__device__ __forceinline__ char* tp_base(const TpPeers& pt, int i) {
+  char* b = pt.base[0];
+#pragma unroll
+  for (int p = 1; p < TP_MAX; ++p)
+    if (p == i) b = pt.base[p];
+  return b;
+}
+
+// Publishes "this rank has finished call `epoch`" to every peer once the last CTA retires.
+__device__ __forceinline__ void tp_publish_done(const TpPeers& pt, long off_done, int rank, int world,
+                                                uint32_t epoch, unsigned int* cta_counter) {
+  __threadfence();
+  const unsigned int prev = atomicAdd(cta_counter, 1u);
+  if (prev + 1 == gridDim.x) {
+    *cta_counter = 0;   // the next launch on this stream starts after this one has ended
+    __threadfence_system();
+    for (int p = 0; p < world; ++p)
+      st_release_sys_u32(reinterpret_cast<uint32_t*>(pt.base[p] + off_done) + rank, epoch);
+  }
+}
+
+// ------------------------------------------------------------------------------ all-gather side
+// Symmetric layout (same offsets on every rank): X [world * m_seg, K] bf16 dense at off_x,
+// optional T [world * m_seg, kt] bf16 dense at off_t (the low-rank LoRA activations, gathered with
+// X), arrival flags uint32 [world][m_seg / 32] at off_flag, done words uint32 [world] at off_done.
+// The caller has written its own shard into rows [rank * m_seg, (rank+1) * m_seg) of the local X / T.
+struct AgComm {
+  static constexpr int THREADS = 128;
+  TpPeers pt;
+  long off_x, off_t, off_flag, off_done;
+  int rank, world, m_seg;
+  int row_bytes_x, row_bytes_t;   // dense row sizes (multiples of 16); row_bytes_t == 0: no T
+  uint32_t epoch, spin;
+  unsigned int* cta_counter;
+
+  __device__ void copy_rows(char* dst, const char* src, long bytes, int tid) const {
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    const long n = bytes >> 4;
+    long i = tid;
+    for (; i + 3 * THREADS < n; i += 4 * THREADS) {   // four loads in flight per thread
+      uint4 a = s[i], b = s[i + THREADS], c = s[i + 2 * THREADS], e = s[i + 3 * THREADS];
+      d[i] = a;
+      d[i + THREADS] = b;
+      d[i + 2 * THREADS] = c;
+      d[i + 3 * THREADS] = e;
+    }
+    for (; i < n; i += THREADS) d[i] = s[i];
+  }
+
+  __device__ void push(int tid, int* status) const {
+    if (world == 1) return;
+    const int units = m_seg / TP_PUSH_ROWS;
+    __shared__ int s_ok;
+    // peers must have consumed the call that last used this parity of the buffer
+    if (tid == 0) {
+      int ok = 1;
+      const uint32_t* done = reinterpret_cast<const uint32_t*>(pt.base[rank] + off_done);
+      if (epoch > 2)
+        for (int p = 0; p < world; ++p)
+          if (p != rank && !wait_flag_ge(done + p, epoch - 2, spin)) ok = 0;
+      if (!ok) atomicMax(status, ST_TIMEOUT_PEER);
+      s_ok = ok;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!s_ok) return;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const long row0 = static_cast<long>(rank) * m_seg + static_cast<long>(u) * TP_PUSH_ROWS;
+      for (int i = 1; i < world; ++i) {
+        const int p = (rank - i + world) % world;   // rank-1 consumes our segment first
+        copy_rows(pt.base[p] + off_x + row0 * row_bytes_x, pt.base[rank] + off_x + row0 * row_bytes_x,
+                  static_cast<long>(TP_PUSH_ROWS) * row_bytes_x, tid);
+        if (row_bytes_t)
+          copy_rows(pt.base[p] + off_t + row0 * row_bytes_t, pt.base[rank] + off_t + row0 * row_bytes_t,
+                    static_cast<long>(TP_PUSH_ROWS) * row_bytes_t, tid);
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tid == 0)
+          st_release_sys_u32(reinterpret_cast<uint32_t*>(pt.base[p] + off_flag) + rank * units + u, epoch);
+      }
+    }
+  }
+
+  // producer lane, before the first load of a tile
+  __device__ bool ready(const TileInfo& ti) const {
+    const int seg = ti.group;
+    if (seg == rank) return true;
+    const int units = m_seg / TP_PUSH_ROWS;
+    const int u0 = (ti.m_blk * GEMM_BM - seg * m_seg) / TP_PUSH_ROWS;
+    const uint32_t* fl = reinterpret_cast<const uint32_t*>(pt.base[rank] + off_flag) + seg * units + u0;
+    for (int j = 0; j < GEMM_BM / TP_PUSH_ROWS; ++j)
+      if (!wait_flag_ge(fl + j, epoch, spin)) return false;
+    fence_proxy_async_all();   // peer's generic-proxy stores -> this CTA's TMA (async proxy) reads
+    return true;
+  }
+
+  __device__ void finish(int* /*status*/) const { tp_publish_done(pt, off_done, rank, world, epoch, cta_counter); }
+};
+
+// -------------------------------------------------------------------------- reduce-scatter side
+// Symmetric layout: staging fp32 [world-1][m_seg][N] at off_stage (slot s of owner o holds the
+// partial of rank (o + 1 + s) % world), flags uint32 [world-1][tile_cap][4] at off_flag, done
+// words at off_done.  Output: out[m_seg, N] bf16 = sum over ranks (+ residual shard R).
+struct RsComm {
+  static constexpr int THREADS = 0;
+  TpPeers pt;
+  long off_done;
+  int rank, world;
+  uint32_t epoch;
+  unsigned int* cta_counter;
+  __device__ void push(int, int*) const {}
+  __device__ bool ready(const TileInfo&) const { return true; }
+  __device__ void finish(int*) const { tp_publish_done(pt, off_done, rank, world, epoch, cta_counter); }
+};
+
+template <int BN>
+struct EpiReduceScatter {
+  TpPeers pt;
+  long off_stage, off_flag, off_done;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* R;
+  int ldc, ldr, N, m_seg, n_tiles, tile_cap, rank, world;
+  uint32_t epoch, spin;
+  int* status;
+  // per-tile state
+  int own, lrow;
+  float* stage;        // remote: my slot in the owner's staging; own: slot 0 of my staging
+  uint32_t* flag;      // remote: flag to publish; own: flag of slot 0 to wait on
+
+  __device__ void tile_begin(const TileInfo& ti, int row) {
+    const int seg = ti.group;
+    const int q = (row >> 5) & 3, lane = row & 31;
+    own = seg == rank;
+    const int lrow0 = ti.m_blk * GEMM_BM - seg * m_seg;
+    lrow = lrow0 + row;
+    const int tile_local = (lrow0 / GEMM_BM) * n_tiles + ti.n_blk;
+    int ok = 1;
+    if (!own) {
+      const int slot = (rank - seg - 1 + world) % world;
+      stage = reinterpret_cast<float*>(tp_base(pt, seg) + off_stage) +
+              (static_cast<size_t>(slot) * m_seg + lrow) * N;
+      flag = reinterpret_cast<uint32_t*>(tp_base(pt, seg) + off_flag) +
+             (static_cast<size_t>(slot) * tile_cap + tile_local) * 4 + q;
+      // the owner must have consumed the call that last used this parity of its staging buffer
+      if (lane == 0 && epoch > 2)
+        ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(tp_base(pt, rank) + off_done) + seg, epoch - 2, spin);
+    } else {
+      stage = reinterpret_cast<float*>(tp_base(pt, rank) + off_stage) + static_cast<size_t>(lrow) * N;
+      flag = reinterpret_cast<uint32_t*>(tp_base(pt, rank) + off_flag) + static_cast<size_t>(tile_local) * 4 + q;
+      if (lane == 0)
+        for (int s = 0; s < world - 1; ++s)
+          if (!wait_flag_ge(flag + static_cast<size_t>(s) * tile_cap * 4, epoch, spin)) ok = 0;
+    }
+    if (lane == 0 && !ok) atomicMax(status, ST_TIMEOUT_PEER);
+    __syncwarp();
+  }
+
+  __device__ void chunk(const TileInfo& ti, int /*row*/, int c, uint32_t (&acc)[32]) {
+    const int gc = ti.n_blk * BN + c;
+    if (gc >= N || lrow >= m_seg) return;
+    if (!own) {
+      float* d = stage + gc;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        if (gc + j < N)   // N is a multiple of 8: a group of four is entirely in or out
+          *reinterpret_cast<uint4*>(d + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      return;
+    }
+    for (int s = 0; s < world - 1; ++s) {
+      const float* p = stage + static_cast<size_t>(s) * m_seg * N + gc;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        if (gc + j < N) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p + j));
+          acc[j] = __float_as_uint(__uint_as_float(acc[j]) + v.x);
+          acc[j + 1] = __float_as_uint(__uint_as_float(acc[j + 1]) + v.y);
+          acc[j + 2] = __float_as_uint(__uint_as_float(acc[j + 2]) + v.z);
+          acc[j + 3] = __float_as_uint(__uint_as_float(acc[j + 3]) + v.w);
+        }
+    }
+    if (R) {
+      const __nv_bfloat16* r = R + static_cast<size_t>(lrow) * ldr + gc;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8)
+        if (gc + j < N) {
+          uint4 rv = *reinterpret_cast<const uint4*>(r + j);
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(rp[e]);
+            acc[j + 2 * e] = __float_as_uint(__uint_as_float(acc[j + 2 * e]) + f.x);
+            acc[j + 2 * e + 1] = __float_as_uint(__uint_as_float(acc[j + 2 * e + 1]) + f.y);
+          }
+        }
+    }
+    __nv_bfloat16* o = out + static_cast<size_t>(lrow) * ldc + gc;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+      if (gc + j < N) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]));
+        v.y = pack_bf16x2(__uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+        v.z = pack_bf16x2(__uint_as_float(acc[j + 4]), __uint_as_float(acc[j + 5]));
+        v.w = pack_bf16x2(__uint_as_float(acc[j + 6]), __uint_as_float(acc[j + 7]));
+        *reinterpret_cast<uint4*>(o + j) = v;
+      }
+  }
+
+  __device__ void tile_end(const TileInfo&, int row) {
+    if (own) return;
+    __threadfence_system();
+    __syncwarp();
+    if ((row & 31) == 0) st_release_sys_u32(flag, epoch);
+  }
+};
+
+}  // namespace artb
