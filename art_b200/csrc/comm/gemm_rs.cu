@@ -4,8 +4,9 @@
 //   out[m_seg, N] (rank r) = sum_p ( A_p[rows of r, K_p] * B_p[N, K_p]^T + A2_p * B2^T ) + R_r
 //
 // Each rank computes its partial product for ALL token rows.  Tiles whose rows belong to another
-// rank are stored straight from the epilogue registers into that rank's fp32 staging area over
-// NVLink (16-byte stores, one release flag per tile and epilogue warp); the rank's own tiles are
+// rank are stored straight from the epilogue registers into that rank's bf16 staging area over
+// NVLink (re-laid out through shared memory so that 8 lanes write 128 contiguous bytes; one
+// release flag per tile and epilogue warp); the rank's own tiles are
 // scheduled last, and their epilogue adds the partials the peers have pushed meanwhile, plus the
 // residual shard, and writes the final bf16 rows.  There is no separate reduction kernel, no
 // atomics, and the summation order is fixed (deterministic).
@@ -13,6 +14,8 @@
 // Unfused equivalent: a library GEMM followed by an NCCL reduce_scatter.  The reference has no
 // tensor parallelism of its own (src/art/dev/engine.py:27 forwards `tensor_parallel_size` to the
 // inference library).
+#include <string.h>
+
 #include "host_utils.h"
 #include "tp_policies.cuh"
 
@@ -44,13 +47,15 @@ static int launch_rs(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
 
 using namespace artb;
 
+extern "C" int artb_pick_bn(int M, int N, int ctas);
+
 // h            symmetric buffer handle; byte offsets into its data area, identical on every rank:
-//              off_stage fp32 [world-1][m_seg][N], off_flag uint32 [world-1][tile_cap][4],
+//              off_stage bf16 [world-1][m_seg][N], off_flag uint32 [world-1][tile_cap][4],
 //              off_done uint32 [world]
 // A, B         local operands [world*m_seg, K] and [N, K] (K = this rank's slice of the reduction dim)
 // A2, B2, K2   optional extra-K pair (LoRA partial), K2 multiple of 8
 // out, R       bf16 [m_seg, N] result shard and optional residual shard
-// tile_cap     flags per staging slot; >= (m_seg/128) * ceil(N/256)
+// tile_cap     flags per staging slot; >= (m_seg/128) * ceil(N/224)
 ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off_done, int tile_cap, const void* A,
                                 int lda, const void* B, int ldb, const void* A2, int lda2, const void* B2, int ldb2,
                                 int K2, void* out, int ldc, const void* R, int ldr, int m_seg, int N, int K,
@@ -62,21 +67,24 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
     return ERR_BAD_SHAPE;
   if ((off_stage & 127) || (off_flag & 15) || (off_done & 15) || (ldc & 7) || (R && (ldr & 7))) return ERR_BAD_ALIGN;
   const int world = s->world, M = world * m_seg;
-  constexpr int BN = 256;
-  const int n_tiles = (N + BN - 1) / BN;
+  int cap = sm_count();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  int bn = artb_pick_bn(M, N, cap);   // same inputs on every rank -> same tiling on every rank
+  if (bn != 224) bn = 256;   // 224 only if the tile chooser ever asks for it
+  const int n_tiles = (N + bn - 1) / bn;
   if ((m_seg / GEMM_BM) * n_tiles > tile_cap) return ERR_TOO_LARGE;
   CUtensorMap tA, tB, tA2, tB2;
   int e;
   if ((e = make_tmap_bf16_2d(&tA, A, M, K, lda, GEMM_BM, GEMM_BK))) return e;
-  if ((e = make_tmap_bf16_2d(&tB, B, N, K, ldb, BN, GEMM_BK))) return e;
+  if ((e = make_tmap_bf16_2d(&tB, B, N, K, ldb, bn, GEMM_BK))) return e;
   if (K2 > 0) {
     if ((e = make_tmap_bf16_2d(&tA2, A2, M, K2, lda2, GEMM_BM, GEMM_BK))) return e;
-    if ((e = make_tmap_bf16_2d(&tB2, B2, N, K2, ldb2, BN, GEMM_BK))) return e;
+    if ((e = make_tmap_bf16_2d(&tB2, B2, N, K2, ldb2, bn, GEMM_BK))) return e;
   } else {
     tA2 = tA;
     tB2 = tB;
   }
-  EpiReduceScatter<BN> epi;
+  EpiReduceScatter<256> epi;
   RsComm comm;
   for (int p = 0; p < TP_MAX; ++p) {
     epi.pt.base[p] = p < world ? static_cast<char*>(s->table.base[p]) : nullptr;
@@ -108,6 +116,11 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   comm.epoch = epoch;
   comm.cta_counter = cta_counter;
   SchedSegRot sched{m_seg / GEMM_BM, n_tiles, world, s->rank, 1};
-  return launch_rs<BN, 4>(tA, tB, tA2, tB2, (K + GEMM_BK - 1) / GEMM_BK, (K2 + GEMM_BK - 1) / GEMM_BK, sched, epi,
-                          comm, status, max_ctas, stream);
+  const int kb_main = (K + GEMM_BK - 1) / GEMM_BK, kb_extra = (K2 + GEMM_BK - 1) / GEMM_BK;
+  if (bn == 224) {
+    EpiReduceScatter<224> e224;
+    memcpy(&e224, &epi, sizeof(epi));   // the policy's fields do not depend on BN
+    return launch_rs<224, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, e224, comm, status, max_ctas, stream);
+  }
+  return launch_rs<256, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, comm, status, max_ctas, stream);
 }

@@ -81,8 +81,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const __grid_constant__ CUtensorMap tmB2, int kb_main, int kb_extra,
                     Sched sched, Epi epi_in, int* status, Comm comm) {
   using L = GemmSmemLayout<BN, STAGES>;
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+  // two accumulators of BN columns each; the allocation is rounded up to a power of two
+  constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static_assert(BN % 32 == 0 && BN <= 256, "BN");
 
   extern __shared__ uint8_t smem_raw[];

@@ -20,24 +20,25 @@
 
 namespace artb {
 
-constexpr int G2_BN = 256;        // cluster tile N
-constexpr int G2_BNH = 128;       // B rows staged per CTA
-constexpr int G2_STAGE_BYTES = (GEMM_BM + G2_BNH) * GEMM_BK * 2;   // 32 KB
-
-template <int STAGES>
+// BN2 = cluster tile N (256, or 224 when that wastes less of the last wave); each CTA stages
+// BN2 / 2 rows of B.  Stage sizes stay multiples of 1024 B (the 128-byte-swizzle atom).
+template <int STAGES, int BN2>
 struct Gemm2SmemLayout {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr int BAR_OFFSET = STAGES * G2_STAGE_BYTES;
+  static constexpr int STAGE_BYTES = (GEMM_BM + BN2 / 2) * GEMM_BK * 2;
+  static_assert(STAGE_BYTES % 1024 == 0 && BN2 % 32 == 0 && BN2 <= 256, "2-CTA tile");
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
   static constexpr int TOTAL = BAR_OFFSET + BAR_BYTES + 1024;
 };
 
-template <int STAGES, class Epi>
+template <int STAGES, int BN2, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                          int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status) {
-  using L = Gemm2SmemLayout<STAGES>;
+  using L = Gemm2SmemLayout<STAGES, BN2>;
+  constexpr int G2_BN = BN2, G2_BNH = BN2 / 2, G2_STAGE_BYTES = L::STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &

@@ -145,7 +145,7 @@ struct AgComm {
 };
 
 // -------------------------------------------------------------------------- reduce-scatter side
-// Symmetric layout: staging fp32 [world-1][m_seg][N] at off_stage (slot s of owner o holds the
+// Symmetric layout: staging bf16 [world-1][m_seg][N] at off_stage (slot s of owner o holds the
 // partial of rank (o + 1 + s) % world), flags uint32 [world-1][tile_cap][4] at off_flag, done
 // words at off_done.  Output: out[m_seg, N] bf16 = sum over ranks (+ residual shard R).
 struct RsComm {
@@ -171,8 +171,9 @@ struct EpiReduceScatter {
   int* status;
   // per-tile state
   int own, lrow;
-  float* stage;        // remote: my slot in the owner's staging; own: slot 0 of my staging
-  uint32_t* flag;      // remote: flag to publish; own: flag of slot 0 to wait on
+  __nv_bfloat16* stage;   // first row of this warp's 32-row band: in the owner's staging slot (remote tile)
+                          // or in slot 0 of the local staging (own tile)
+  uint32_t* flag;         // remote: flag to publish; own: flag of slot 0 to wait on
 
   __device__ void tile_begin(const TileInfo& ti, int row) {
     const int seg = ti.group;
@@ -184,15 +185,16 @@ struct EpiReduceScatter {
     int ok = 1;
     if (!own) {
       const int slot = (rank - seg - 1 + world) % world;
-      stage = reinterpret_cast<float*>(tp_base(pt, seg) + off_stage) +
-              (static_cast<size_t>(slot) * m_seg + lrow) * N;
+      stage = reinterpret_cast<__nv_bfloat16*>(tp_base(pt, seg) + off_stage) +
+              (static_cast<size_t>(slot) * m_seg + lrow0 + q * 32) * N;
       flag = reinterpret_cast<uint32_t*>(tp_base(pt, seg) + off_flag) +
              (static_cast<size_t>(slot) * tile_cap + tile_local) * 4 + q;
       // the owner must have consumed the call that last used this parity of its staging buffer
       if (lane == 0 && epoch > 2)
         ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(tp_base(pt, rank) + off_done) + seg, epoch - 2, spin);
     } else {
-      stage = reinterpret_cast<float*>(tp_base(pt, rank) + off_stage) + static_cast<size_t>(lrow) * N;
+      stage = reinterpret_cast<__nv_bfloat16*>(tp_base(pt, rank) + off_stage) +
+              static_cast<size_t>(lrow0 + q * 32) * N;
       flag = reinterpret_cast<uint32_t*>(tp_base(pt, rank) + off_flag) + static_cast<size_t>(tile_local) * 4 + q;
       if (lane == 0)
         for (int s = 0; s < world - 1; ++s)
@@ -202,27 +204,60 @@ struct EpiReduceScatter {
     __syncwarp();
   }
 
-  __device__ void chunk(const TileInfo& ti, int /*row*/, int c, uint32_t (&acc)[32]) {
+  __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
     const int gc = ti.n_blk * BN + c;
-    if (gc >= N || lrow >= m_seg) return;
+    const int q = (row >> 5) & 3, lane = row & 31;
     if (!own) {
-      float* d = stage + gc;
+      // Remote tile: the partial goes to the owner as bf16.  A thread holds one row, so a direct
+      // store would scatter 16-byte pieces over 32 rows; instead two 32-column slabs are parked in
+      // shared memory and written out with 8 lanes covering 128 contiguous bytes of a row.
+      __shared__ uint4 s_buf[4][32 * 9];   // per warp: 32 rows x (8 + 1 pad) 16-byte pieces
+      const int half = (c >> 5) & 1;
+      if (gc < N) {
+        uint4* w = s_buf[q] + lane * 9 + half * 4;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        if (gc + j < N)   // N is a multiple of 8: a group of four is entirely in or out
-          *reinterpret_cast<uint4*>(d + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(acc[8 * j]), __uint_as_float(acc[8 * j + 1]));
+          v.y = pack_bf16x2(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
+          v.z = pack_bf16x2(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
+          v.w = pack_bf16x2(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
+          w[j] = v;
+        }
+      }
+      if (half == 1) {
+        __syncwarp();
+        const int gc0 = gc - 32;
+        int pieces = (N - gc0) >> 3;   // N is a multiple of 8
+        pieces = pieces > 8 ? 8 : pieces;
+        const int j = lane & 7;
+        if (j < pieces) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const uint4 v = s_buf[q][r * 9 + j];
+            *reinterpret_cast<uint4*>(stage + static_cast<size_t>(r) * N + gc0 + j * 8) = v;
+          }
+        }
+        __syncwarp();
+      }
       return;
     }
+    if (gc >= N) return;
+    const __nv_bfloat16* mine = stage + static_cast<size_t>(lane) * N + gc;
     for (int s = 0; s < world - 1; ++s) {
-      const float* p = stage + static_cast<size_t>(s) * m_seg * N + gc;
+      const __nv_bfloat16* p = mine + static_cast<size_t>(s) * m_seg * N;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
+      for (int j = 0; j < 32; j += 8)
         if (gc + j < N) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(p + j));
-          acc[j] = __float_as_uint(__uint_as_float(acc[j]) + v.x);
-          acc[j + 1] = __float_as_uint(__uint_as_float(acc[j + 1]) + v.y);
-          acc[j + 2] = __float_as_uint(__uint_as_float(acc[j + 2]) + v.z);
-          acc[j + 3] = __float_as_uint(__uint_as_float(acc[j + 3]) + v.w);
+          const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p + j));
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(rp[e]);
+            acc[j + 2 * e] = __float_as_uint(__uint_as_float(acc[j + 2 * e]) + f.x);
+            acc[j + 2 * e + 1] = __float_as_uint(__uint_as_float(acc[j + 2 * e + 1]) + f.y);
+          }
         }
     }
     if (R) {

@@ -47,13 +47,24 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
 
 using namespace artb;
 
+// Tile width for an [M, N] output on `ctas` persistent CTAs: the widest tile that still fills the
+// machine.  Narrower tiles that would waste less of the last wave (224 for N = 3584: 6.92 waves
+// instead of 6.05) were measured and are no faster on a power-capped B200 (SMs idle in the last
+// wave let the others clock higher), so 224 / 192 are only used on request.
+ARTB_EXPORT int artb_pick_bn(int M, int N, int ctas) {
+  const long m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  if (N >= 256 && m_tiles * ((N + 255) / 256) >= ctas) return 256;
+  if (N >= 128 && m_tiles * ((N + 127) / 128) >= ctas / 2) return 128;
+  return N > 64 ? 128 : 64;
+}
+
 // C[M,N] = A[M,K] B[N,K]^T (+ A2[M,K2] B2[N,K2]^T), bf16 inputs, fp32 accumulation in TMEM.
 //   A, B, A2, B2 : bf16 row-major, leading dimensions in elements (multiples of 8), 16-B aligned
 //   K2 == 0      : no extra-K operand (A2/B2 ignored)
 //   epilogue     : GemmEpilogue; R (bf16 [M,res_cols]) is added for EPI_BF16_RESID and, when given, for EPI_SWIGLU;
 //                  H (bf16 [M,N/2]) receives silu(gate)*up for EPI_SWIGLU;  res_cols 0 = all N columns
 //   bias         : optional fp32 [N], added to the accumulator before any other epilogue step
-//   bn           : tile width 64 / 128 / 256 (0 = choose)
+//   bn           : tile width 64 / 128 / 192 / 224 / 256 (0 = choose, see artb_pick_bn)
 //   status       : device int32, receives a KernelStatus on a bounded-wait expiry (0 otherwise)
 //   max_ctas     : cap on the persistent grid (0 = one CTA per SM)
 // Returns 0, a negative HostError, or a positive cudaError_t.
@@ -72,15 +83,8 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
     return ERR_BAD_ALIGN;
   if (epilogue == EPI_SWIGLU && (!H || (ldh & 7) || (N & 31) || (reinterpret_cast<uintptr_t>(H) & 15)))
     return ERR_BAD_ALIGN;
-  if (bn == 0) {
-    // Largest tile that still yields at least ~one wave of CTAs.
-    const long m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
-    const int sms = sm_count();
-    if (N >= 256 && m_tiles * ((N + 255) / 256) >= sms) bn = 256;
-    else if (N >= 128 && m_tiles * ((N + 127) / 128) >= sms / 2) bn = 128;
-    else bn = (N > 64) ? 128 : 64;
-  }
-  if (bn != 64 && bn != 128 && bn != 256) return ERR_BAD_SHAPE;
+  if (bn == 0) bn = artb_pick_bn(M, N, max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count());
+  if (bn != 64 && bn != 128 && bn != 192 && bn != 224 && bn != 256) return ERR_BAD_SHAPE;
 
   CUtensorMap tA, tB, tA2, tB2;
   int e;
@@ -105,6 +109,8 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
                                  stream);                                                         \
   }
   if (bn == 256) ARTB_LAUNCH(256, 4)
+  if (bn == 224) ARTB_LAUNCH(224, 4)
+  if (bn == 192) ARTB_LAUNCH(192, 5)
   if (bn == 128) ARTB_LAUNCH(128, 6)
   ARTB_LAUNCH(64, 8)
 #undef ARTB_LAUNCH

@@ -90,7 +90,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         raise ValueError("bias must be fp32 [N]")
     st = _lib.status_word(a.device)
     if two_cta is None:
-        two_cta = TWO_CTA_DEFAULT and bn == 0 and M >= 1024 and N >= 512
+        two_cta = TWO_CTA_DEFAULT and bn == 0 and M >= 1024 and N >= 512   # bn = 224 with two_cta=True: 256 x 224 pair tiles
     if two_cta:
         rc = _fn2()(
             _lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0),
@@ -100,7 +100,8 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
             _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
             _lib.ptr(swiglu_out), swiglu_out.stride(0) if swiglu_out is not None else 0,
             _lib.ptr(bias),
-            M, N, K, epi, res_cols, _lib.ptr(st), max_ctas // 2, _lib.stream_ptr())
+            M, N, K, epi, res_cols, _lib.ptr(st), -(max_ctas // 2 or 1 << 20) if bn == 224 else max_ctas // 2,
+            _lib.stream_ptr())
         _lib.check_rc(rc, "gemm_tn_2cta")
         return out
     rc = _fn()(

@@ -1,0 +1,74 @@
+"""Kernel micro-benchmarks: ``python -m art_b200.ops.microbench gemm --m 8192 --n 3584 --k 3584``.
+
+Times one op with CUDA events on the launching stream after warm-up (inputs larger than L2 by
+default, or pass ``--flush`` to write a 256 MB buffer between iterations) and prints one JSON line
+with the achieved TFLOP/s or GB/s next to the library baseline.  The same entry point is what the
+profiler is pointed at when a single kernel is captured (``--iters 1 --warmup 1 --no-baseline``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def _time(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def bench_gemm(a) -> dict:
+    from . import _lib
+    from .gemm import gemm_tn
+
+    dev = "cuda"
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = (torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16()
+    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
+    two = None if a.two_cta < 0 else bool(a.two_cta)
+    ms = _time(lambda: gemm_tn(x, w, out=out, bn=a.bn, two_cta=two), a.iters, a.warmup, flush)
+    _lib.check_status()
+    fl = 2.0 * a.m * a.n * a.k
+    res = {"op": "gemm_tn", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "two_cta": a.two_cta, "ms": round(ms, 4),
+           "tflops": round(fl / ms / 1e9, 1)}
+    if not a.no_baseline:
+        ms_b = _time(lambda: torch.matmul(x, w.t(), out=out), a.iters, a.warmup, flush)
+        res["cublas_ms"] = round(ms_b, 4)
+        res["cublas_tflops"] = round(fl / ms_b / 1e9, 1)
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="op", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=3584)
+    g.add_argument("--k", type=int, default=3584)
+    g.add_argument("--bn", type=int, default=0)
+    g.add_argument("--two-cta", type=int, default=-1, help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
+    for p in (g,):
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--flush", action="store_true")
+        p.add_argument("--no-baseline", action="store_true")
+    a = ap.parse_args()
+    print(json.dumps(bench_gemm(a)))
+
+
+if __name__ == "__main__":
+    main()

@@ -5,7 +5,7 @@ regions the two kernels of ``csrc/comm`` need:
 
 * all-gather side: two copies (epoch parity) of the gathered activation matrix ``X`` and of the
   gathered LoRA low-rank activations ``T``, arrival flags, "done" words;
-* reduce-scatter side: two copies of the fp32 staging area that peers push partial tiles into,
+* reduce-scatter side: two copies of the bf16 staging area that peers push partial tiles into,
   per-tile flags, "done" words.
 
 Column-parallel linears (q/k/v, gate/up) call :meth:`ag_gemm` after writing their token shard
@@ -76,11 +76,11 @@ class TPContext:
         off = _align(off + self.world * (m_seg // PUSH_ROWS) * 4)
         self.off_ag_done = off
         off = _align(off + 64)
-        self.tile_cap = (m_seg // 128) * ((n_max + 255) // 256)
+        self.tile_cap = (m_seg // 128) * ((n_max + 127) // 128)
         self.off_stage = []
         for _ in range(2):
             self.off_stage.append(off)
-            off = _align(off + max(self.world - 1, 1) * m_seg * n_max * 4)
+            off = _align(off + max(self.world - 1, 1) * m_seg * n_max * 2)
         self.off_rs_flag = off
         off = _align(off + max(self.world - 1, 1) * self.tile_cap * 16)
         self.off_rs_done = off

@@ -27,7 +27,8 @@ def _status_clean():
 
 
 @pytest.mark.parametrize("M,N,K,K2,bn", [(128, 64, 64, 0, 64), (256, 512, 512, 0, 256), (200, 264, 328, 0, 0),
-                                         (1024, 1024, 1024, 64, 0), (4096, 4608, 3584, 8, 0), (77, 3584, 128, 16, 64)])
+                                         (1024, 1024, 1024, 64, 0), (4096, 4608, 3584, 8, 0), (77, 3584, 128, 16, 64),
+                                         (2048, 3584, 512, 64, 0), (512, 3584, 256, 0, 224), (300, 600, 320, 16, 192)])
 def test_gemm_tn(M, N, K, K2, bn):
     from art_b200.ops.gemm import gemm_tn, reference_gemm_tn
 
@@ -41,6 +42,14 @@ def test_gemm_tn(M, N, K, K2, bn):
     assert rel_err(out, ref) < 5e-3
     out32 = gemm_tn(a, b, out_dtype=torch.float32, bn=bn)
     assert rel_err(out32, reference_gemm_tn(a, b)) < 1e-3
+
+
+def test_gemm_two_cta_224_tiles():
+    from art_b200.ops.gemm import gemm_tn, reference_gemm_tn
+
+    a, b = bf(1024, 512, seed=1), bf(3584, 512, scale=0.05, seed=2)
+    out = gemm_tn(a, b, bn=224, two_cta=True)
+    assert rel_err(out, reference_gemm_tn(a, b)) < 5e-3
 
 
 def test_gemm_swiglu_epilogue():
