@@ -137,6 +137,42 @@ struct EpiStore {
   }
 };
 
+// Grouped (per-expert) GEMM: rows are sorted by expert and every expert's segment is padded to a
+// multiple of 128 rows, so an M tile belongs to exactly one expert, read from tile_expert[m_blk]
+// (-1: tile beyond the last segment, nothing to do).  B and B2 hold the experts' matrices stacked
+// along rows.
+struct SchedGrouped {
+  const int* tile_expert;
+  int m_tiles, n_tiles, b_rows_per_expert;
+  __device__ int tiles_for_cta(int cta, int ncta) const {
+    const int total = m_tiles * n_tiles;
+    return cta < total ? (total - cta + ncta - 1) / ncta : 0;
+  }
+  __device__ TileInfo get(int cta, int ncta, int i) const {
+    const int t = cta + i * ncta;
+    TileInfo ti = make_tile(t % m_tiles, t / m_tiles);
+    const int e = __ldg(tile_expert + ti.m_blk);
+    ti.group = e;
+    if (e < 0) {
+      ti.kb_n = 0;
+      ti.extra = 0;
+    } else {
+      ti.b_row = e * b_rows_per_expert;
+    }
+    return ti;
+  }
+};
+
+template <int BN>
+struct EpiGrouped {
+  EpiStore<BN> st;
+  __device__ void tile_begin(const TileInfo&, int) {}
+  __device__ void tile_end(const TileInfo&, int) {}
+  __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    if (ti.group >= 0) st.chunk(ti, row, c, acc);
+  }
+};
+
 // Split-K partial: fp32 atomic accumulation into a zero-initialised workspace [M, ldw].
 template <int BN>
 struct EpiAtomic {

@@ -38,6 +38,7 @@ struct TileInfo {
   int kb_lo;   // first main-operand K block of this tile (split-K); 0 for a full tile
   int kb_n;    // number of main-operand K blocks; < 0 means "all of them"
   int extra;   // include the extra-K operand blocks in this tile
+  int b_row;   // row offset added to the B / B2 coordinates (grouped GEMM: expert * rows per expert)
 };
 
 __device__ __forceinline__ TileInfo make_tile(int m_blk, int n_blk) {
@@ -49,6 +50,7 @@ __device__ __forceinline__ TileInfo make_tile(int m_blk, int n_blk) {
   ti.kb_lo = 0;
   ti.kb_n = -1;
   ti.extra = 1;
+  ti.b_row = 0;
   return ti;
 }
 
@@ -153,11 +155,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
           if (kb < nmain) {
             tma_load_2d(sa, &tmA, (ti.kb_lo + kb) * GEMM_BK, ti.m_blk * GEMM_BM, &full_bar[s]);
-            tma_load_2d(sb, &tmB, (ti.kb_lo + kb) * GEMM_BK, ti.n_blk * BN, &full_bar[s]);
+            tma_load_2d(sb, &tmB, (ti.kb_lo + kb) * GEMM_BK, ti.n_blk * BN + ti.b_row, &full_bar[s]);
           } else {
             const int k2 = (kb - nmain) * GEMM_BK;
             tma_load_2d(sa, &tmA2, k2, ti.m_blk * GEMM_BM, &full_bar[s]);
-            tma_load_2d(sb, &tmB2, k2, ti.n_blk * BN, &full_bar[s]);
+            tma_load_2d(sb, &tmB2, k2, ti.n_blk * BN + ti.b_row, &full_bar[s]);
           }
         }
       }

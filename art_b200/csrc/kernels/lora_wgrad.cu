@@ -50,13 +50,22 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 
 __global__ void __launch_bounds__(128)
 lora_wgrad_kernel(const __nv_bfloat16* __restrict__ P, int ldp, const __nv_bfloat16* __restrict__ Q, int ldq,
-                  float* __restrict__ out, int ldo, int M, int C, int rows_per_split) {
+                  float* __restrict__ out, int ldo, int M, int C, int rows_per_split,
+                  const int* __restrict__ seg_off, long out_stride) {
   __shared__ __align__(16) __nv_bfloat16 sP[2][WG_BM][WG_PLD];
   __shared__ __align__(16) __nv_bfloat16 sQ[2][WG_BM][WG_QLD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c0 = blockIdx.x * WG_BC;
-  const int m_begin = blockIdx.y * rows_per_split;
-  const int m_end = min(M, m_begin + rows_per_split);
+  int m_begin = blockIdx.y * rows_per_split;
+  int m_end = min(M, m_begin + rows_per_split);
+  if (seg_off) {
+    // grouped: blockIdx.z is the expert; its row segment is split evenly over gridDim.y CTAs
+    const int lo = seg_off[blockIdx.z], hi = seg_off[blockIdx.z + 1];
+    const int rows = ((hi - lo + static_cast<int>(gridDim.y) - 1) / static_cast<int>(gridDim.y) + WG_BM - 1) / WG_BM * WG_BM;
+    m_begin = lo + blockIdx.y * rows;
+    m_end = min(hi, m_begin + rows);
+    out += blockIdx.z * out_stride;
+  }
   if (m_begin >= m_end) return;
   const int chunks = (m_end - m_begin + WG_BM - 1) / WG_BM;
 
@@ -166,6 +175,22 @@ ARTB_EXPORT int artb_lora_wgrad(const void* P, int ldp, const void* Q, int ldq, 
   splits = (M + rows - 1) / rows;
   dim3 grid(cblocks, splits);
   lora_wgrad_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(P), ldp,
-                                          reinterpret_cast<const __nv_bfloat16*>(Q), ldq, out, ldo, M, C, rows);
+                                          reinterpret_cast<const __nv_bfloat16*>(Q), ldq, out, ldo, M, C, rows,
+                                          nullptr, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+// Grouped form for expert-sorted rows: out[e][C, 64] += P[seg_e, C]^T Q[seg_e, 64] for every expert e,
+// seg_e = rows seg_off[e] .. seg_off[e+1] (device array, padded rows are zero).  One launch covers all experts.
+ARTB_EXPORT int artb_lora_wgrad_grouped(const void* P, int ldp, const void* Q, int ldq, float* out, int ldo,
+                                        long out_stride, const int* seg_off, int num_experts, int C, int splits,
+                                        cudaStream_t st) {
+  if (num_experts <= 0 || C <= 0) return 0;
+  if ((C & 7) || (ldp & 7) || (ldq & 7) || ldo < WG_R || splits < 1) return ERR_BAD_SHAPE;
+  dim3 grid((C + WG_BC - 1) / WG_BC, splits, num_experts);
+  lora_wgrad_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(P), ldp,
+                                          reinterpret_cast<const __nv_bfloat16*>(Q), ldq, out, ldo, 0, C, 0, seg_off,
+                                          out_stride);
   return static_cast<int>(cudaGetLastError());
 }

@@ -130,7 +130,11 @@ def lora_wgrad(acc: torch.Tensor, p: torch.Tensor, q: torch.Tensor, transpose_ou
 class LoraFlat:
     """Flat fp32 master / gradient buffers holding every LoRA A and B (PEFT-named views)."""
 
-    def __init__(self, cfg: ModelConfig, lcfg: LoraConfig, init: dict[str, torch.Tensor], device):
+    def __init__(self, cfg: ModelConfig, lcfg: LoraConfig, init: dict[str, torch.Tensor], device,
+                 order: list[str] | None = None):
+        if order is not None:
+            assert sorted(order) == sorted(init.keys())
+            init = {k: init[k] for k in order}
         self.names = list(init.keys())
         total = sum(v.numel() for v in init.values())
         pad = (-total) % 1024
@@ -138,14 +142,27 @@ class LoraFlat:
         self.grads = torch.zeros_like(self.params)
         self.views: dict[str, torch.Tensor] = {}
         self.grad_views: dict[str, torch.Tensor] = {}
+        self.offsets: dict[str, int] = {}
         off = 0
         for k, v in init.items():
             n = v.numel()
             self.views[k] = self.params[off:off + n].view(v.shape)
             self.grad_views[k] = self.grads[off:off + n].view(v.shape)
             self.views[k].copy_(v)
+            self.offsets[k] = off
             off += n
         self.numel = total
+
+    def stacked(self, keys: list[str]) -> tuple[torch.Tensor, torch.Tensor]:
+        """Parameter and gradient views ``[len(keys), *shape]`` over keys that are adjacent in the flat buffer."""
+        shape = self.views[keys[0]].shape
+        n = self.views[keys[0]].numel()
+        o0 = self.offsets[keys[0]]
+        for i, k in enumerate(keys):
+            if self.offsets[k] != o0 + i * n or self.views[k].shape != shape:
+                raise ValueError("keys are not adjacent in the flat LoRA buffer")
+        span = slice(o0, o0 + n * len(keys))
+        return self.params[span].view(len(keys), *shape), self.grads[span].view(len(keys), *shape)
 
     def state_dict(self) -> dict[str, torch.Tensor]:
         return {k: v.detach().clone() for k, v in self.views.items()}
@@ -167,22 +184,47 @@ class LayerSaved:
     T_o: torch.Tensor = None
     x2: torch.Tensor = None
     rstd2: torch.Tensor = None
+    mlp: object = None          # DenseSaved or MoESaved
+    qk_pre: torch.Tensor = None
+    qk_rstd: tuple = None
+
+
+@dataclass
+class DenseSaved:
     h2: torch.Tensor = None
     T_gu: torch.Tensor = None
     gu: torch.Tensor = None
     hact: torch.Tensor = None
     T_d: torch.Tensor = None
-    qk_pre: torch.Tensor = None
-    qk_rstd: tuple = None
+
+
+class DenseMLP:
+    """SwiGLU feed-forward: fused gate|up GEMM with the activation in its epilogue, then down + residual."""
+
+    def __init__(self, gu: LoraLinear, down: LoraLinear, intermediate: int):
+        self.gu, self.down, self.F = gu, down, intermediate
+
+    def linears(self):
+        return (self.gu, self.down)
+
+    def forward(self, h2, x2, use_lora: bool, save: bool):
+        hact = torch.empty((h2.shape[0], self.F), dtype=h2.dtype, device=h2.device)
+        gu, T_gu = self.gu.forward(h2, use_lora, swiglu_out=hact)
+        x3, T_d = self.down.forward(hact, use_lora, residual=x2)
+        return x3, (DenseSaved(h2, T_gu, gu, hact, T_d) if save else None)
+
+    def backward(self, dx, sv: DenseSaved):
+        dhact = self.down.backward(dx, sv.hact, sv.T_d)
+        dgu = ew.swiglu_bwd(dhact, sv.gu)
+        del dhact
+        return self.gu.backward(dgu, sv.h2, sv.T_gu)
 
 
 class NativeDecoder:
-    """Dense Qwen2/Llama-style decoder on the native kernels (LoRA-only training)."""
+    """Qwen2/Llama-style dense and Qwen3-MoE-style sparse decoders on the native kernels (LoRA-only training)."""
 
     def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
                  lora_init: dict[str, torch.Tensor], device="cuda", attn_impl: str = "native"):
-        if cfg.is_moe:
-            raise ValueError("NativeDecoder is the dense model; use models.moe.NativeMoEDecoder")
         self.cfg, self.lora_cfg, self.attn_impl = cfg, lora_cfg, attn_impl
         self.device = torch.device(device)
         bf = torch.bfloat16
@@ -194,10 +236,15 @@ class NativeDecoder:
         self.lm_head_t = torch.zeros(d, ldo, dtype=bf, device=dev)
         self.lm_head_t[:, :V] = self.lm_head.t()
         self.final_norm = base["model.norm.weight"].to(dev, bf).contiguous()
-        self.flat = LoraFlat(cfg, lora_cfg, lora_init, dev)
+        order = None
+        if cfg.is_moe:
+            from .moe import MoEMLP, expert_lora_order
+
+            order = expert_lora_order(cfg, list(lora_init.keys()))
+        self.flat = LoraFlat(cfg, lora_cfg, lora_init, dev, order=order)
         self.layers: list[dict] = []
         r, s = lora_cfg.r, lora_cfg.scale
-        F = cfg.intermediate_size
+        F = max(cfg.intermediate_size, 16)
         fidx = torch.arange(F, device=dev)
         gate_rows = (fidx // 16) * 32 + fidx % 16
         up_rows = gate_rows + 16
@@ -227,10 +274,14 @@ class NativeDecoder:
                                                   ("self_attn.k_proj", ar(q, q + kv, device=dev)),
                                                   ("self_attn.v_proj", ar(q + kv, q + 2 * kv, device=dev))]), r, s)
             o = LoraLinear(W("self_attn.o_proj"), None, members([("self_attn.o_proj", ar(0, d, device=dev))]), r, s)
-            wgu = ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj"))
-            gu = LoraLinear(wgu, None, members([("mlp.gate_proj", gate_rows), ("mlp.up_proj", up_rows)]), r, s)
-            down = LoraLinear(W("mlp.down_proj"), None, members([("mlp.down_proj", ar(0, d, device=dev))]), r, s)
-            layer = {"qkv": qkv, "o": o, "gu": gu, "down": down,
+            if cfg.is_moe:
+                mlp = MoEMLP(cfg, i, base, self.flat, lora_cfg, dev)
+            else:
+                wgu = ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj"))
+                gu = LoraLinear(wgu, None, members([("mlp.gate_proj", gate_rows), ("mlp.up_proj", up_rows)]), r, s)
+                down = LoraLinear(W("mlp.down_proj"), None, members([("mlp.down_proj", ar(0, d, device=dev))]), r, s)
+                mlp = DenseMLP(gu, down, cfg.intermediate_size)
+            layer = {"qkv": qkv, "o": o, "mlp": mlp,
                      "ln1": base[p + "input_layernorm.weight"].to(dev, bf).contiguous(),
                      "ln2": base[p + "post_attention_layernorm.weight"].to(dev, bf).contiguous()}
             if cfg.qk_norm:
@@ -242,8 +293,9 @@ class NativeDecoder:
     # -- LoRA bookkeeping -------------------------------------------------------------------
     def linears(self):
         for layer in self.layers:
-            for k in ("qkv", "o", "gu", "down"):
-                yield layer[k]
+            yield layer["qkv"]
+            yield layer["o"]
+            yield from layer["mlp"].linears()
 
     def refresh_lora(self) -> None:
         for lin in self.linears():
@@ -280,12 +332,10 @@ class NativeDecoder:
             o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
             x2, T_o = layer["o"].forward(o, use_lora, residual=x)
             h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
-            hact = torch.empty((x.shape[0], cfg.intermediate_size), dtype=x.dtype, device=x.device)
-            gu, T_gu = layer["gu"].forward(h2, use_lora, swiglu_out=hact)
-            x3, T_d = layer["down"].forward(hact, use_lora, residual=x2)
+            x3, mctx = layer["mlp"].forward(h2, x2, use_lora, save)
             if save:
                 sv.x, sv.rstd1, sv.h1, sv.T_qkv, sv.attn_ctx, sv.o, sv.T_o = x, rstd1, h1, T_qkv, actx, o, T_o
-                sv.x2, sv.rstd2, sv.h2, sv.T_gu, sv.gu, sv.hact, sv.T_d = x2, rstd2, h2, T_gu, gu, hact, T_d
+                sv.x2, sv.rstd2, sv.mlp = x2, rstd2, mctx
                 saved.append(sv)
             x = x3
         hidden, rstd_f = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps)
@@ -300,11 +350,7 @@ class NativeDecoder:
         for li in range(cfg.num_layers - 1, -1, -1):
             layer, sv = self.layers[li], saved[li]
             # MLP
-            dhact = layer["down"].backward(dx, sv.hact, sv.T_d)
-            dgu = ew.swiglu_bwd(dhact, sv.gu)
-            del dhact
-            dh2 = layer["gu"].backward(dgu, sv.h2, sv.T_gu)
-            del dgu
+            dh2 = layer["mlp"].backward(dx, sv.mlp)
             dx2 = ew.rmsnorm_bwd(dh2, sv.x2, layer["ln2"], sv.rstd2, dres=dx)
             del dh2
             # attention
