@@ -114,6 +114,7 @@ class MoESaved:
     hact: torch.Tensor = None
     T_d: torch.Tensor = None
     yp: torch.Tensor = None
+    eplan: object = None        # layout of the expert-side rows (== plan without expert parallelism)
 
 
 def expert_lora_order(cfg: ModelConfig, keys: list[str]) -> list[str]:
@@ -136,8 +137,10 @@ def expert_lora_order(cfg: ModelConfig, keys: list[str]) -> list[str]:
 class MoEMLP:
     """Router + grouped experts + combine for one layer (all experts local)."""
 
-    def __init__(self, cfg: ModelConfig, layer: int, base: dict[str, torch.Tensor], flat, lora_cfg: LoraConfig, device):
+    def __init__(self, cfg: ModelConfig, layer: int, base: dict[str, torch.Tensor], flat, lora_cfg: LoraConfig, device,
+                 ep=None):
         self.cfg = cfg
+        self.ep = ep
         dev, bf = device, torch.bfloat16
         p = f"model.layers.{layer}."
         E, d, F = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
@@ -154,18 +157,21 @@ class MoEMLP:
         def W(e, name):
             return base[p + f"mlp.experts.{e}.{name}.weight"].to(dev, bf)
 
+        # with expert parallelism this rank holds (and trains) only its contiguous share of the experts
+        local = range(E) if ep is None else range(ep.rank * ep.El, (ep.rank + 1) * ep.El)
+
         def stack(leaf):
-            ka = [lora_key(layer, f"mlp.experts.{e}.{leaf}", "A") for e in range(E)]
+            ka = [lora_key(layer, f"mlp.experts.{e}.{leaf}", "A") for e in local]
             if ka[0] not in flat.views:
                 return None
-            kb = [lora_key(layer, f"mlp.experts.{e}.{leaf}", "B") for e in range(E)]
+            kb = [lora_key(layer, f"mlp.experts.{e}.{leaf}", "B") for e in local]
             return flat.stacked(ka), flat.stacked(kb)
 
         stacks = {leaf: stack(leaf) for leaf in ("gate_proj", "up_proj", "down_proj")}
         r, s = lora_cfg.r, lora_cfg.scale
-        self.gu = GroupedLoraLinear([ew.interleave_gate_up(W(e, "gate_proj"), W(e, "up_proj")) for e in range(E)],
+        self.gu = GroupedLoraLinear([ew.interleave_gate_up(W(e, "gate_proj"), W(e, "up_proj")) for e in local],
                                     [("gate_proj", gate_rows, 0), ("up_proj", up_rows, 1)], stacks, r, s)
-        self.down = GroupedLoraLinear([W(e, "down_proj") for e in range(E)],
+        self.down = GroupedLoraLinear([W(e, "down_proj") for e in local],
                                       [("down_proj", torch.arange(d, device=dev), 0)], stacks, r, s)
         self.F, self.d = F, d
 
@@ -175,23 +181,35 @@ class MoEMLP:
     def forward(self, h2: torch.Tensor, x2: torch.Tensor, use_lora: bool, save: bool):
         logits = gemm_tn(h2, self.Wg, out_dtype=torch.float32)[:, :self.E]
         plan = moe_ops.route(logits, self.k, self.norm)
-        xp = moe_ops.gather(h2, plan)
-        hact = torch.empty((plan.cap_rows, self.F), dtype=h2.dtype, device=h2.device)
-        gu, T_gu = self.gu.forward(xp, plan, use_lora, swiglu_out=hact)
-        yp, T_d = self.down.forward(hact, plan, use_lora)
+        if self.ep is None:
+            eplan = plan
+            xp = moe_ops.gather(h2, plan)
+        else:
+            eplan = self.ep.exchange(plan)
+            xp = self.ep.dispatch(h2, plan, eplan)
+        hact = torch.empty((eplan.cap_rows, self.F), dtype=h2.dtype, device=h2.device)
+        gu, T_gu = self.gu.forward(xp, eplan, use_lora, swiglu_out=hact)
+        yp, T_d = self.down.forward(hact, eplan, use_lora)
+        if self.ep is not None:
+            yp = self.ep.combine_return(yp, plan, eplan)      # back in this rank's own sorted order
         x3, _ = moe_ops.combine(yp, plan, weighted=True, residual=x2)
-        ctx = MoESaved(logits, plan, h2, xp, T_gu, gu, hact, T_d, yp) if save else None
+        ctx = MoESaved(logits, plan, h2, xp, T_gu, gu, hact, T_d, yp, eplan) if save else None
         return x3, ctx
 
     def backward(self, dx: torch.Tensor, sv: MoESaved) -> torch.Tensor:
-        plan = sv.plan
-        dyp = moe_ops.gather(dx, plan, weighted=True)
+        plan, eplan = sv.plan, sv.eplan
+        if self.ep is None:
+            dyp = moe_ops.gather(dx, plan, weighted=True)
+        else:
+            dyp = self.ep.dispatch(dx, plan, eplan, weighted=True)
         _, dw = moe_ops.combine(sv.yp, plan, weighted=False, grad_for_dots=dx, want_out=False)
-        dhact = self.down.backward(dyp, sv.hact, sv.T_d, plan)
+        dhact = self.down.backward(dyp, sv.hact, sv.T_d, eplan)
         dgu = ew.swiglu_bwd(dhact, sv.gu)
         del dhact
-        dxp = self.gu.backward(dgu, sv.xp, sv.T_gu, plan)
+        dxp = self.gu.backward(dgu, sv.xp, sv.T_gu, eplan)
         del dgu
+        if self.ep is not None:
+            dxp = self.ep.combine_return(dxp, plan, eplan)
         dh2, _ = moe_ops.combine(dxp, plan, weighted=False)
         dlogits = moe_ops.router_bwd(sv.logits, plan, dw, self.norm, self.Epad)
         return gemm_tn(dlogits, self.WgT, residual=dh2)

@@ -224,7 +224,7 @@ class NativeDecoder:
     """Qwen2/Llama-style dense and Qwen3-MoE-style sparse decoders on the native kernels (LoRA-only training)."""
 
     def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
-                 lora_init: dict[str, torch.Tensor], device="cuda", attn_impl: str = "native"):
+                 lora_init: dict[str, torch.Tensor], device="cuda", attn_impl: str = "native", ep=None):
         self.cfg, self.lora_cfg, self.attn_impl = cfg, lora_cfg, attn_impl
         self.device = torch.device(device)
         bf = torch.bfloat16
@@ -275,7 +275,7 @@ class NativeDecoder:
                                                   ("self_attn.v_proj", ar(q + kv, q + 2 * kv, device=dev))]), r, s)
             o = LoraLinear(W("self_attn.o_proj"), None, members([("self_attn.o_proj", ar(0, d, device=dev))]), r, s)
             if cfg.is_moe:
-                mlp = MoEMLP(cfg, i, base, self.flat, lora_cfg, dev)
+                mlp = MoEMLP(cfg, i, base, self.flat, lora_cfg, dev, ep=ep)
             else:
                 wgu = ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj"))
                 gu = LoraLinear(wgu, None, members([("mlp.gate_proj", gate_rows), ("mlp.up_proj", up_rows)]), r, s)

@@ -179,3 +179,146 @@ def test_tp_fused_gemm_collectives(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "AG_GEMM_OK" in res.stdout and "GEMM_RS_OK" in res.stdout
+
+
+EP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.ops import _lib, moe
+from art_b200.parallel.ep import ExpertParallel, reference_dispatch
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+
+# ---- dispatch / return against all_to_all_single, several calls in a row (parity, done words)
+M, k, E, D = 384, 2, 8, 64
+El = E // world
+ep = ExpertParallel(dev, None, M, k, E, D, capacity_factor=float(world))
+for it in range(5):
+    g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+    logits = torch.randn(M, E, device=dev, generator=g) * 2
+    x = torch.randn(M, D, device=dev, generator=g).to(torch.bfloat16)
+    ids = torch.arange(M, device=dev) + rank * M            # exact token ids in two bf16 columns
+    x[:, 0] = (ids // 256).to(torch.bfloat16); x[:, 1] = (ids % 256).to(torch.bfloat16)
+    plan = moe.route(logits, k, True)
+    rp = ep.exchange(plan)
+    weighted = it == 3
+    xp = ep.dispatch(x, plan, rp, weighted=weighted)
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    xs = x if not weighted else None
+    rows, eid = reference_dispatch(x, plan.topi, E)
+    seg, real = rp.seg_off.tolist(), rp.real_rows.tolist()
+    assert seg[-1] % 128 == 0 and len(seg) == El + 1
+    for j in range(El):
+        got = xp[seg[j]:seg[j] + real[j]]
+        want = rows[eid == j]
+        assert got.shape == want.shape, (j, got.shape, want.shape)
+        if not weighted:
+            key = lambda t: (t[:, 0].float() * 256 + t[:, 1].float()).argsort()
+            assert torch.equal(got[key(got)], want[key(want)]), ("dispatch rows", it, j)
+        assert (xp[seg[j] + real[j]:seg[j + 1]] == 0).all(), "padding rows must be zero"
+    # round trip: the owner doubles each row and sends it back
+    yr = ep.combine_return((xp.float() * 2).to(torch.bfloat16), plan, rp)
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    pos = plan.pos.long()
+    want = x.float().unsqueeze(1) * 2
+    if weighted:
+        want = (x.float().unsqueeze(1) * plan.topw.unsqueeze(-1)).to(torch.bfloat16).float() * 2
+    assert rel(yr[pos], want.expand(M, k, D)) < 1e-2, ("return rows", it)
+    total = int(plan.seg_off[-1])
+    assert (yr[:total][plan.row_token[:total] < 0] == 0).all()
+ep.close()
+
+# ---- MoE block with expert parallelism == the same block with all experts local
+from art_b200.models.config import ModelConfig
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+from art_b200.models.native import LoraFlat
+from art_b200.models.moe import MoEMLP, expert_lora_order
+cfg = ModelConfig(name="ep-moe", family="qwen3_moe", vocab_size=512, hidden_size=128, num_layers=1, num_heads=2,
+                  num_kv_heads=2, head_dim=64, intermediate_size=0, qkv_bias=False, qk_norm=True, num_experts=8,
+                  num_experts_per_tok=2, moe_intermediate_size=64)
+base = init_base_weights(cfg, seed=0)
+base["model.layers.0.mlp.gate.weight"] *= 8
+lcfg = LoraConfig()
+lora = init_lora(cfg, lcfg)
+gl = torch.Generator().manual_seed(5)
+for kk in lora:
+    if "lora_B" in kk: lora[kk] = torch.randn(lora[kk].shape, generator=gl) * 0.05
+M = 256
+flat_full = LoraFlat(cfg, lcfg, lora, dev, order=expert_lora_order(cfg, list(lora.keys())))
+full = MoEMLP(cfg, 0, base, flat_full, lcfg, dev)
+lo, hi = rank * (8 // world), (rank + 1) * (8 // world)
+lora_local = {kk: v for kk, v in lora.items() if ".experts." not in kk or lo <= int(kk.split(".experts.")[1].split(".")[0]) < hi}
+flat_ep = LoraFlat(cfg, lcfg, lora_local, dev, order=expert_lora_order(cfg, list(lora_local.keys())))
+ep = ExpertParallel(dev, None, M, 2, 8, 128, capacity_factor=float(world))
+part = MoEMLP(cfg, 0, base, flat_ep, lcfg, dev, ep=ep)
+for m in (full, part):
+    for lin in m.linears(): lin.refresh(); lin.zero_grad()
+g = torch.Generator(device=dev).manual_seed(7 + rank)
+h2 = torch.randn(M, 128, device=dev, generator=g).to(torch.bfloat16)
+x2 = torch.randn(M, 128, device=dev, generator=g).to(torch.bfloat16)
+dx = (torch.randn(M, 128, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+y_full, c_full = full.forward(h2, x2, True, True)
+y_ep, c_ep = part.forward(h2, x2, True, True)
+d_full = full.backward(dx, c_full)
+d_ep = part.backward(dx, c_ep)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert rel(y_ep, y_full) < 1e-2, rel(y_ep, y_full)
+assert rel(d_ep, d_full) < 2e-2, rel(d_ep, d_full)
+for a, b in zip(full.linears(), part.linears()):
+    a.export_grads(); b.export_grads()
+for kk in sorted(lora):                       # same key order on every rank: the all_reduce calls must pair up
+    if ".experts." in kk:
+        gsum = flat_full.grad_views[kk].clone(); dist.all_reduce(gsum)     # every rank's tokens reach the owner
+        if kk not in lora_local:
+            continue
+        assert rel(flat_ep.grad_views[kk], gsum) < 3e-2 or gsum.abs().max() < 1e-6, (kk, rel(flat_ep.grad_views[kk], gsum))
+ep.close()
+
+# ---- timing at the sparse benchmark shape (8192 tokens per rank, top-8 of 128 experts, d = 2048)
+M, k, E, D = 8192, 8, 128, 2048
+ep = ExpertParallel(dev, None, M, k, E, D, capacity_factor=1.5)
+g = torch.Generator(device=dev).manual_seed(rank)
+x = torch.randn(M, D, device=dev, generator=g).to(torch.bfloat16)
+plan = moe.route(torch.randn(M, E, device=dev, generator=g), k, True)
+rp = ep.exchange(plan)
+def timed(fn, iters=10, warm=3):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warm): fn()
+    dist.barrier(); torch.cuda.synchronize(); e0.record()
+    for _ in range(iters): fn()
+    e1.record(); torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+t_disp = timed(lambda: ep.dispatch(x, plan, rp))
+xp = ep.dispatch(x, plan, rp)
+t_ret = timed(lambda: ep.combine_return(xp, plan, rp))
+t_nccl = timed(lambda: reference_dispatch(x, plan.topi, E))
+torch.cuda.synchronize(); _lib.check_status(dev)
+remote = M * k * D * 2 * (world - 1) / world
+if rank == 0:
+    print(f"EP_OK world={world} rows={M*k} d={D} dispatch_ms={t_disp:.3f} return_ms={t_ret:.3f} "
+          f"nccl_all_to_all_dispatch_ms={t_nccl:.3f} remote_MB_per_rank={remote/1e6:.0f} "
+          f"dispatch_GBps={remote/t_disp/1e6:.0f}")
+ep.close()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_expert_parallel_dispatch_combine(tmp_path):
+    world = 1
+    while world * 2 <= min(torch.cuda.device_count(), 8):
+        world *= 2
+    script = tmp_path / "ep_worker.py"
+    script.write_text(EP_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29521", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "EP_OK" in res.stdout
