@@ -322,3 +322,94 @@ def test_expert_parallel_dispatch_combine(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "EP_OK" in res.stdout
+
+
+CP_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.ops import _lib, attention as attn_ops, attn_native
+from art_b200.parallel.cp import ContextParallel
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+
+rows, S, Hq, Hkv, hd, L = 2, 256 * world, 4, 2, 64, 2
+cp = ContextParallel(dev, None, rows, S, Hq, Hkv, hd, L)
+# tree-structured ids: a shared prompt segment followed by sibling completions (same on every rank)
+seg = S // 8
+gid = torch.empty(rows, S, dtype=torch.int32); pid = torch.empty(rows, S, dtype=torch.int32)
+nid = 0
+for r in range(rows):
+    o = 0
+    while o < S:
+        p = nid; nid += 1
+        gid[r, o:o + seg] = p; pid[r, o:o + seg] = p; o += seg
+        for _ in range(3):
+            if o >= S: break
+            gid[r, o:o + seg] = nid; pid[r, o:o + seg] = p; nid += 1; o += seg
+gid, pid = gid.reshape(-1).to(dev), pid.reshape(-1).to(dev)
+plan_full = attn_ops.make_plan(gid, pid, S, "native")
+plan_cp = cp.make_plan(gid, pid)
+for it in range(5):                                   # several calls per layer: slot parity, flags
+    layer = it % L
+    g = torch.Generator(device=dev).manual_seed(40 + it)          # same tensors on every rank
+    qkv = torch.randn(rows * S, (Hq + 2 * Hkv) * hd, device=dev, generator=g).to(torch.bfloat16)
+    do = torch.randn(rows * S, Hq * hd, device=dev, generator=g).to(torch.bfloat16)
+    o_ref, saved = attn_native.forward(qkv, Hq, Hkv, hd, plan_full)
+    dqkv_ref = attn_native.backward(do, saved, plan_full)
+    o_loc, ctx = cp.forward(layer, cp.shard(qkv).contiguous(), plan_cp)
+    dqkv_loc = cp.backward(cp.shard(do).contiguous(), ctx)
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    assert rel(o_loc, cp.shard(o_ref)) < 1e-3, ("fwd", it, rel(o_loc, cp.shard(o_ref)))
+    assert rel(dqkv_loc, cp.shard(dqkv_ref)) < 2e-2, ("bwd", it, rel(dqkv_loc, cp.shard(dqkv_ref)))
+cp.close()
+
+# ---- timing: 16k-token row, 40 q / 8 kv heads of 128 (the long-context configuration), one layer
+rows, S, Hq, Hkv, hd = 1, 16384, 40, 8, 128
+cp = ContextParallel(dev, None, rows, S, Hq, Hkv, hd, 1)
+g = torch.Generator(device=dev).manual_seed(1)
+seg = 2048
+gid = (torch.arange(S, dtype=torch.int32) // seg).to(dev); pid = torch.zeros(S, dtype=torch.int32, device=dev)
+plan_cp = cp.make_plan(gid, pid)
+qkv_loc = torch.randn(cp.n_local, cp.ld, device=dev, generator=g).to(torch.bfloat16)
+do_loc = torch.randn(cp.n_local, Hq * hd, device=dev, generator=g).to(torch.bfloat16)
+def timed(fn, iters=5, warm=2):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warm): fn()
+    dist.barrier(); torch.cuda.synchronize(); e0.record()
+    for _ in range(iters): fn()
+    e1.record(); torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+box = {}
+def fwd(): box["o"], box["ctx"] = cp.forward(0, qkv_loc, plan_cp)
+t_f = timed(fwd)
+t_fb = timed(lambda: (fwd(), cp.backward(do_loc, box["ctx"])))
+full = torch.empty(S, cp.ld, device=dev, dtype=torch.bfloat16)
+t_ag = timed(lambda: dist.all_gather_into_tensor(full, qkv_loc))
+torch.cuda.synchronize(); _lib.check_status(dev)
+if rank == 0:
+    print(f"CP_OK world={world} S={S} heads={Hq}/{Hkv}x{hd} fwd_ms={t_f:.3f} fwd+bwd_ms={t_fb:.3f} "
+          f"nccl_allgather_qkv_only_ms={t_ag:.3f} kv_bytes_per_rank_MB={cp.n_local*2*Hkv*hd*2*(world-1)/1e6:.1f}")
+cp.close()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_context_parallel_attention(tmp_path):
+    world = 1
+    while world * 2 <= min(torch.cuda.device_count(), 8):
+        world *= 2
+    script = tmp_path / "cp_worker.py"
+    script.write_text(CP_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29523", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "CP_OK" in res.stdout
