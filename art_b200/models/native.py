@@ -311,14 +311,18 @@ class NativeDecoder:
 
     # -- forward ----------------------------------------------------------------------------
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, gid: torch.Tensor, pid: torch.Tensor, S: int,
-                use_lora: bool = True, save: bool = True) -> tuple[torch.Tensor, list[LayerSaved], dict]:
-        """tokens int64 [M], pos/gid/pid int32 [M]; returns final-normed hidden [M,d] and saved state."""
+                use_lora: bool = True, save: bool = True, cp=None) -> tuple[torch.Tensor, list[LayerSaved], dict]:
+        """tokens int64 [M], pos/gid/pid int32 [M]; returns final-normed hidden [M,d] and saved state.
+
+        With ``cp`` (a :class:`parallel.cp.ContextParallel`) ``tokens`` / ``pos`` hold this rank's shard of
+        every packed row while ``gid`` / ``pid`` stay full-length; attention exchanges K/V with the peers.
+        """
         cfg = self.cfg
         x = ew.gather_rows(self.embed, tokens)
-        plan = attn_ops.make_plan(gid, pid, S, self.attn_impl)
+        plan = cp.make_plan(gid, pid) if cp is not None else attn_ops.make_plan(gid, pid, S, self.attn_impl)
         saved: list[LayerSaved] = []
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
-        for layer in self.layers:
+        for li, layer in enumerate(self.layers):
             sv = LayerSaved()
             h1, rstd1 = ew.rmsnorm_fwd(x, layer["ln1"], cfg.rms_norm_eps)
             qkv, T_qkv = layer["qkv"].forward(h1, use_lora)
@@ -329,7 +333,10 @@ class NativeDecoder:
                 rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
                 sv.qk_rstd = (rq, rk)
             ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
-            o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
+            if cp is not None:
+                o, actx = cp.forward(li, qkv, plan)
+            else:
+                o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
             x2, T_o = layer["o"].forward(o, use_lora, residual=x)
             h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
             x3, mctx = layer["mlp"].forward(h2, x2, use_lora, save)
@@ -339,7 +346,7 @@ class NativeDecoder:
                 saved.append(sv)
             x = x3
         hidden, rstd_f = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps)
-        return hidden, saved, {"x_last": x, "rstd_f": rstd_f}
+        return hidden, saved, {"x_last": x, "rstd_f": rstd_f, "cp": cp}
 
     # -- backward ---------------------------------------------------------------------------
     def backward(self, dhidden: torch.Tensor, saved: list[LayerSaved], final: dict, pos: torch.Tensor) -> None:
@@ -355,7 +362,7 @@ class NativeDecoder:
             del dh2
             # attention
             do = layer["o"].backward(dx2, sv.o, sv.T_o)
-            dqkv = attn_ops.backward(do, sv.attn_ctx)
+            dqkv = final["cp"].backward(do, sv.attn_ctx) if final.get("cp") is not None else attn_ops.backward(do, sv.attn_ctx)
             del do
             ew.rope_(dqkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, inverse=True)
             if cfg.qk_norm:

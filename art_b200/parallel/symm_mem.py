@@ -95,10 +95,11 @@ class SymmetricBuffer:
 
 
 class FusedGradAllReduce:
-    """Callable ``(flat_grads) -> None``: mean over ranks, in place, through the P2P kernel."""
+    """Callable ``(flat_grads) -> None``: mean (or sum, ``average=False``) over ranks, in place, through the P2P kernel."""
 
-    def __init__(self, device: torch.device, world: int, group=None, wait_ms: int = 5000):
+    def __init__(self, device: torch.device, world: int, group=None, wait_ms: int = 5000, average: bool = True):
         self.device, self.world, self.group, self.wait_ms = torch.device(device), world, group, wait_ms
+        self.scale = 1.0 / world if average else 1.0
         self.buf: SymmetricBuffer | None = None
         self.n = 0
 
@@ -112,7 +113,7 @@ class FusedGradAllReduce:
         sym[:n].copy_(flat_grads)
         if pad:
             sym[n:].zero_()
-        rc = _k().artb_lora_grad_allreduce(self.buf._h, self.n, 1.0 / self.world, self.wait_ms,
+        rc = _k().artb_lora_grad_allreduce(self.buf._h, self.n, self.scale, self.wait_ms,
                                            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
         _lib.check_rc(rc, "lora_grad_allreduce")
         flat_grads.copy_(sym[:n])

@@ -51,17 +51,27 @@ class Trainer:
     def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
                  lora_init: dict[str, torch.Tensor], device: str | torch.device = "cpu", impl: str | None = None,
                  betas=(0.9, 0.99), weight_decay: float = 0.1, max_grad_norm: float = 0.1, adam_eps: float = 1e-8,
-                 attn_impl: str = "native", dp_group=None, grad_sync=None):
+                 attn_impl: str = "native", dp_group=None, grad_sync=None, ep=None, cp_group=None):
         self.cfg, self.lora_cfg = cfg, lora_cfg
         self.device = torch.device(device)
         self.impl = impl or ("native" if self.device.type == "cuda" else "reference")
         self.dp_group = dp_group
         self.grad_sync = grad_sync  # callable(flat_grads) -> None : data-parallel gradient all-reduce
+        # expert parallelism (parallel.ep.ExpertParallel): experts sharded over the group, every rank trains on
+        # its own rows; context parallelism (process group): every packed row is sharded over the group
+        self.ep, self.cp_group = ep, cp_group
+        self._cp_cache: dict = {}
+        self._cp_sync = None
         if self.impl == "native":
             from ..models.native import NativeDecoder
 
-            self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl)
+            self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl, ep=ep)
             self.flat = self.model.flat
+            if cp_group is not None:
+                import torch.distributed as dist
+                from ..parallel.symm_mem import FusedGradAllReduce
+
+                self._cp_sync = FusedGradAllReduce(self.device, dist.get_world_size(cp_group), cp_group, average=False)
         else:
             from ..models.native import LoraFlat
 
@@ -174,19 +184,38 @@ class Trainer:
             gid, pid = gid.to(dev, non_blocking=True), pid.to(dev, non_blocking=True)
             lo = int(torch.searchsorted(sel_host, r0 * S))
             hi = int(torch.searchsorted(sel_host, r1 * S))
-            if hi == lo:
+            if hi == lo and self.cp_group is None:
                 continue
-            sel = sel_all_d[lo:hi] - r0 * S
-            hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S)
             target = torch.cat([tokens[1:], tokens[:1]]).to(torch.int32)  # next token; row ends are masked out
+            w_flat = tok_w_d.reshape(-1)[r0 * S:r1 * S]
+            old_flat = shift_left(rows_d["logprobs"][r0:r1], 0.0).reshape(-1)
+            adv_flat = shift_left(rows_d["advantages"][r0:r1], 0.0).reshape(-1)
+            cp = None
+            if self.cp_group is not None:
+                # every rank keeps its zig-zag share of each row; ids stay full-length for the mask
+                cp = self._cp(r1 - r0, S)
+                loc = cp.local_to_global.long()
+                tokens, pos, target = tokens[loc], pos[loc].contiguous(), target[loc]
+                w_flat, old_flat, adv_flat = w_flat[loc], old_flat[loc], adv_flat[loc]
+                sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
+            else:
+                sel = sel_all_d[lo:hi] - r0 * S
+            hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S, cp=cp)
+            if sel.numel() == 0:
+                # context parallel: this rank's shard holds no trainable token, but its peers still need its
+                # K/V in the forward passes and its (zero) dK/dV in the backward pass
+                if hyper.beta > 0:
+                    self.model.forward(tokens, pos, gid, pid, S, use_lora=False, save=False, cp=cp)
+                self.model.backward(torch.zeros_like(hidden), saved, final, pos)
+                continue
             hc = ew.gather_rows(hidden, sel)
             tgt_c = target[sel]
-            w_c = tok_w_d.reshape(-1)[r0 * S:r1 * S][sel]
-            old_c = shift_left(rows_d["logprobs"][r0:r1], 0.0).reshape(-1)[sel]
-            adv_c = shift_left(rows_d["advantages"][r0:r1], 0.0).reshape(-1)[sel]
+            w_c = w_flat[sel]
+            old_c = old_flat[sel]
+            adv_c = adv_flat[sel]
             ref_c = None
             if hyper.beta > 0:
-                ref_hidden, _, _ = self.model.forward(tokens, pos, gid, pid, S, use_lora=False, save=False)
+                ref_hidden, _, _ = self.model.forward(tokens, pos, gid, pid, S, use_lora=False, save=False, cp=cp)
                 rc = ew.gather_rows(ref_hidden, sel)
                 part, _ = lpl.partials(rc, self.model.lm_head, tgt_c)
                 ref_c = lpl.grpo_tokens(part).logprobs
@@ -204,9 +233,44 @@ class Trainer:
         self.model.refresh_lora()
         return out
 
-    def _finish_step(self, totals: dict | None, hyper: TrainHyper, device_accum: torch.Tensor | None = None):
-        if self.grad_sync is not None:
+    def _cp(self, rows: int, S: int):
+        key = (rows, S)
+        if key not in self._cp_cache:
+            from ..parallel.cp import ContextParallel
+
+            c = self.cfg
+            self._cp_cache[key] = ContextParallel(self.device, self.cp_group, rows, S, c.num_heads, c.num_kv_heads,
+                                                  c.head_dim, c.num_layers)
+        return self._cp_cache[key]
+
+    def _sync_grads(self, device_accum: torch.Tensor | None) -> None:
+        """Combine the LoRA gradients of the parallel groups this trainer is part of.
+
+        context parallel: every rank holds a partial gradient of the same rows -> sum (and the loss terms too);
+        expert parallel:  non-expert factors are averaged over the group like data parallelism; an expert's
+                          factors already received every rank's rows, so they are only scaled by 1/world;
+        data parallel:    mean over ranks (``grad_sync``).
+        """
+        import torch.distributed as dist
+
+        if self._cp_sync is not None:
+            self._cp_sync(self.flat.grads)
+            if device_accum is not None:
+                dist.all_reduce(device_accum, group=self.cp_group)
+        if self.ep is not None:
+            first = [self.flat.offsets[k] for k in self.flat.names if ".mlp.experts." in k]
+            n_shared = min(first) if first else self.flat.numel
+            if self.grad_sync is not None:
+                self.grad_sync(self.flat.grads[:n_shared])
+            else:
+                dist.all_reduce(self.flat.grads[:n_shared], group=self.ep.group)
+                self.flat.grads[:n_shared].div_(self.ep.world)
+            self.flat.grads[n_shared:].div_(self.ep.world)
+        elif self.grad_sync is not None:
             self.grad_sync(self.flat.grads)
+
+    def _finish_step(self, totals: dict | None, hyper: TrainHyper, device_accum: torch.Tensor | None = None):
+        self._sync_grads(device_accum)
         gnorm = self.opt.step(hyper.learning_rate)
         if device_accum is not None:
             vals = torch.cat([device_accum[:2], gnorm.reshape(1)]).tolist()  # one D2H read per step

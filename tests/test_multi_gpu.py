@@ -413,3 +413,85 @@ def test_context_parallel_attention(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "CP_OK" in res.stdout
+
+
+PAR_TRAINER_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.models.config import ModelConfig
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+from art_b200.trainer.trainer import TrainHyper, Trainer
+from art_b200.ops import _lib
+from tests.test_gpu_model import _packed
+
+def cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.reshape(-1).float(), b.reshape(-1).float(), dim=0).item()
+
+def randomize_b(lora):
+    g = torch.Generator().manual_seed(5)
+    for k in lora:
+        if "lora_B" in k: lora[k] = torch.randn(lora[k].shape, generator=g) * 0.05
+    return lora
+
+# ---- context parallel: every row sharded over the ranks == the same step on one GPU
+cfg = ModelConfig(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                  head_dim=64, intermediate_size=512)
+base = init_base_weights(cfg, seed=0)
+lcfg = LoraConfig()
+lora = randomize_b(init_lora(cfg, lcfg))
+packed = _packed(cfg, 2, 256 * world)
+hy = TrainHyper(learning_rate=1e-4, beta=0.05, rows_per_optimizer_step=2)
+one = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native")
+cpt = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native", cp_group=dist.group.WORLD)
+m1, m2 = one.step(packed, hy), cpt.step(packed, hy)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert abs(m1["loss"] - m2["loss"]) < 5e-3 * max(1.0, abs(m1["loss"])), (m1, m2)
+assert abs(m1["grad_norm"] - m2["grad_norm"]) < 3e-2 * m1["grad_norm"], (m1, m2)
+assert cos(one.flat.grads, cpt.flat.grads) > 0.995, cos(one.flat.grads, cpt.flat.grads)
+
+# ---- expert parallel: each rank trains on its own rows, experts sharded == mean of the per-rank full-model grads
+from art_b200.parallel.ep import ExpertParallel
+mcfg = ModelConfig(name="small-moe", family="qwen3_moe", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4,
+                   num_kv_heads=2, head_dim=64, intermediate_size=0, qkv_bias=False, qk_norm=True, num_experts=8,
+                   num_experts_per_tok=2, moe_intermediate_size=128)
+mbase = init_base_weights(mcfg, seed=0)
+for k in mbase:
+    if k.endswith("mlp.gate.weight"): mbase[k] = mbase[k] * 8
+mlora = randomize_b(init_lora(mcfg, lcfg))
+El = 8 // world
+local = {k: v for k, v in mlora.items() if ".experts." not in k or rank * El <= int(k.split(".experts.")[1].split(".")[0]) < (rank + 1) * El}
+mpacked = _packed(mcfg, 2, 256, seed=10 + rank)                  # different rows on every rank
+hy = TrainHyper(learning_rate=1e-4, beta=0.0, rows_per_optimizer_step=2)
+full = Trainer(mcfg, mbase, lcfg, {k: v.clone() for k, v in mlora.items()}, device=dev, impl="native")
+ep = ExpertParallel(dev, None, 512, 2, 8, 256, capacity_factor=float(world))
+part = Trainer(mcfg, mbase, lcfg, {k: v.clone() for k, v in local.items()}, device=dev, impl="native", ep=ep)
+mf, mp = full.step(mpacked, hy), part.step(mpacked, hy)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert abs(mf["loss"] - mp["loss"]) < 1e-2 * max(1.0, abs(mf["loss"])), (mf, mp)
+ga, gb = [], []
+for k in sorted(mlora):
+    g = full.flat.grad_views[k].clone(); dist.all_reduce(g); g /= world          # data-parallel mean of the full model
+    if k in local:
+        ga.append(g.reshape(-1)); gb.append(part.flat.grad_views[k].reshape(-1))
+c = cos(torch.cat(ga), torch.cat(gb))
+assert c > 0.99, c
+if rank == 0: print(f"PAR_TRAINER_OK world={world} cp_grad_cos={cos(one.flat.grads, cpt.flat.grads):.5f} ep_grad_cos={c:.5f}")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_trainer_context_and_expert_parallel(tmp_path):
+    world = 2
+    script = tmp_path / "par_worker.py"
+    script.write_text(PAR_TRAINER_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29525", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "PAR_TRAINER_OK" in res.stdout
