@@ -48,6 +48,10 @@ def parse_args():
     ap.add_argument("--lora-rank", type=int, default=8)
     ap.add_argument("--attn", default=None)
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"])
+    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep"],
+                    help="dp: rows split over GPUs; cp: every row sharded over GPUs (long context); "
+                         "ep: experts sharded over GPUs (MoE presets)")
+    ap.add_argument("--rollout", type=int, default=1, help="also measure rollout decode tokens/s (reported beside the headline)")
     return ap.parse_args()
 
 
@@ -176,20 +180,41 @@ def main():
     impl = "native" if args.impl == "native" else "reference"
     attn_impl = args.attn or ("native" if impl == "native" else "sdpa")
     base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
-    lora = init_lora(cfg, lcfg, seed=3407, device=dev)
     grad_sync = None
     sync_name = "none"
-    if world > 1:
+    par = args.parallel if world > 1 else "dp"
+    R, S = args.rows_per_gpu, args.seq_len
+    ep = cp_group = None
+    expert_range = None
+    if world > 1 and par == "dp":
         from art_b200.parallel.dp import make_grad_sync
 
         grad_sync, sync_name = make_grad_sync(args.grad_sync, dev, world)
-    trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync)
+    elif par == "cp":
+        cp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over cp)"
+    elif par == "ep":
+        from art_b200.parallel.ep import ExpertParallel
+
+        if not cfg.is_moe:
+            print("bench.py: --parallel ep needs a mixture-of-experts preset (e.g. --model qwen3-30b-a3b)", file=sys.stderr)
+            return 2
+        ep = ExpertParallel(dev, None, args.micro_tokens, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size,
+                            capacity_factor=1.5)
+        El = cfg.num_experts // world
+        expert_range, sync_name = (rank * El, (rank + 1) * El), "nccl-allreduce(shared factors) + 1/world(experts)"
+        # this rank keeps only its experts' frozen weights
+        base = {k: v for k, v in base.items()
+                if ".mlp.experts." not in k or expert_range[0] <= int(k.split(".experts.")[1].split(".")[0]) < expert_range[1]}
+    lora = init_lora(cfg, lcfg, seed=3407, device=dev, expert_range=expert_range)
+    trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync, ep=ep,
+                      cp_group=cp_group)
+    rollout_base = base if (args.rollout and impl == "native" and not cfg.is_moe) else None
     del base
-    R, S = args.rows_per_gpu, args.seq_len
     hyper = TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=R, tokens_per_microbatch=args.micro_tokens)
-    host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=rank + 1).items()}
+    # cp: all ranks work on the SAME rows (each holds 1/world of every row); dp / ep: every rank has its own rows
+    host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=(1 if par == "cp" else rank + 1)).items()}
     dev_rows = {k: v.to(dev) for k, v in host_rows.items()}
-    tokens_per_step = R * S * world
+    tokens_per_step = R * S * (1 if par == "cp" else world)
 
     def barrier():
         if world > 1:
@@ -228,27 +253,50 @@ def main():
         torch.cuda.profiler.stop()
     _lib.check_status(dev)
 
+    rollout = None
+    if rollout_base is not None:
+        # rollout half of the headline metric: decode tokens/s of the inference engine on the same weights
+        # (one engine replica per GPU, 256 sequences over 4 LoRA adapters), outside the timed training region
+        try:
+            from art_b200.engine.bench_decode import measure_decode
+
+            del trainer
+            torch.cuda.empty_cache()
+            rollout = measure_decode(cfg, dev, base=rollout_base)
+            del rollout_base
+            agg = torch.tensor([rollout["decode_tok_s"]], device=dev)
+            if world > 1:
+                dist.all_reduce(agg)
+            rollout["decode_tok_s_all_gpus"] = round(float(agg.item()), 1)
+        except Exception as e:  # the training number stands on its own
+            rollout = {"error": f"{type(e).__name__}: {e}"}
+            if world > 1:
+                dist.all_reduce(torch.zeros(1, device=dev))
+
     h2d = sum(v.numel() * v.element_size() for v in host_rows.values())
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
     if rank == 0:
         out = {
-            "metric": "GRPO train tokens/s, Qwen2.5-7B-arch LoRA",
+            "metric": ("GRPO train tokens/s, Qwen2.5-7B-arch LoRA" if cfg.name == "qwen2.5-7b"
+                       else f"GRPO train tokens/s, {cfg.name}-arch LoRA"),
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": round(value / PUBLISHED_REFERENCE_TOK_S, 3),
+            "vs_baseline": round(value / PUBLISHED_REFERENCE_TOK_S, 3) if cfg.name == "qwen2.5-7b" else None,
             "vs_baseline_note": "reference publishes only 9.2k packed tok/s on 1xH100 for Qwen2.5-3B 4-bit LoRA r=8",
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": args.impl,
-            "config": {"model": cfg.name, "global_batch": R * world, "seq_len": S, "parallelism": f"dp{world}",
+            "config": {"model": cfg.name, "global_batch": R * world, "seq_len": S, "parallelism": f"{par}{world}",
                        "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": args.micro_tokens,
                        "attention": attn_impl, "grad_sync": sync_name, "optimizer_steps_per_step": 1,
-                       "l2": "inputs larger than L2: each step streams 30 GB of bf16 weights (W and W^T) plus activations"},
+                       "l2": "inputs larger than L2: each step streams the bf16 weights (W and W^T, 30 GB for the 7B "
+                             "model) plus activations"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12,
                     "api": "art_b200.trainer.Trainer.step on pinned host tensors"},
             "gpu_launches": launches,
             "loss": last["loss"] if last else None,
+            "rollout": rollout,
         }
         print(json.dumps(out))
     if world > 1:
