@@ -51,7 +51,8 @@ class Trainer:
     def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
                  lora_init: dict[str, torch.Tensor], device: str | torch.device = "cpu", impl: str | None = None,
                  betas=(0.9, 0.99), weight_decay: float = 0.1, max_grad_norm: float = 0.1, adam_eps: float = 1e-8,
-                 attn_impl: str = "native", dp_group=None, grad_sync=None, ep=None, cp_group=None):
+                 attn_impl: str = "native", dp_group=None, grad_sync=None, ep=None, cp_group=None, tp_group=None,
+                 tp_tokens: int = 8192):
         self.cfg, self.lora_cfg = cfg, lora_cfg
         self.device = torch.device(device)
         self.impl = impl or ("native" if self.device.type == "cuda" else "reference")
@@ -59,19 +60,34 @@ class Trainer:
         self.grad_sync = grad_sync  # callable(flat_grads) -> None : data-parallel gradient all-reduce
         # expert parallelism (parallel.ep.ExpertParallel): experts sharded over the group, every rank trains on
         # its own rows; context parallelism (process group): every packed row is sharded over the group
-        self.ep, self.cp_group = ep, cp_group
+        # tensor parallelism (process group): heads / feed-forward width sharded, activations token-sharded;
+        # every micro-batch must hold exactly ``tp_tokens`` tokens
+        self.ep, self.cp_group, self.tp_group = ep, cp_group, tp_group
         self._cp_cache: dict = {}
         self._cp_sync = None
+        self.tp = None
         if self.impl == "native":
             from ..models.native import NativeDecoder
 
-            self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl, ep=ep)
+            if tp_group is not None:
+                import torch.distributed as dist
+                from ..models.tp import TPDecoder
+                from ..parallel.tp import TPContext
+
+                P = dist.get_world_size(tp_group)
+                self.tp = TPContext(self.device, tp_group, tp_tokens // P, k_max=cfg.hidden_size, n_max=cfg.hidden_size)
+                self.model = TPDecoder(cfg, base, lora_cfg, lora_init, self.tp, self.device)
+            else:
+                self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl, ep=ep)
             self.flat = self.model.flat
-            if cp_group is not None:
+            sum_group = cp_group if cp_group is not None else tp_group
+            if sum_group is not None:
                 import torch.distributed as dist
                 from ..parallel.symm_mem import FusedGradAllReduce
 
-                self._cp_sync = FusedGradAllReduce(self.device, dist.get_world_size(cp_group), cp_group, average=False)
+                # ranks of a context- or tensor-parallel group hold partial gradients of the SAME rows: sum them
+                self._cp_sync = FusedGradAllReduce(self.device, dist.get_world_size(sum_group), sum_group, average=False)
+                self._sum_group = sum_group
         else:
             from ..models.native import LoraFlat
 
@@ -184,7 +200,7 @@ class Trainer:
             gid, pid = gid.to(dev, non_blocking=True), pid.to(dev, non_blocking=True)
             lo = int(torch.searchsorted(sel_host, r0 * S))
             hi = int(torch.searchsorted(sel_host, r1 * S))
-            if hi == lo and self.cp_group is None:
+            if hi == lo and self.cp_group is None and self.tp is None:
                 continue
             target = torch.cat([tokens[1:], tokens[:1]]).to(torch.int32)  # next token; row ends are masked out
             w_flat = tok_w_d.reshape(-1)[r0 * S:r1 * S]
@@ -197,6 +213,15 @@ class Trainer:
                 loc = cp.local_to_global.long()
                 tokens, pos, target = tokens[loc], pos[loc].contiguous(), target[loc]
                 w_flat, old_flat, adv_flat = w_flat[loc], old_flat[loc], adv_flat[loc]
+                sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
+            elif self.tp is not None:
+                # this rank embeds, normalises and scores its contiguous token segment; positions and ids stay
+                # full-length because attention runs over all tokens for the local heads
+                if M != self.tp.world * self.tp.m_seg:
+                    raise ValueError(f"tensor-parallel micro-batches must hold {self.tp.world * self.tp.m_seg} tokens, got {M}")
+                seg = slice(self.tp.rank * self.tp.m_seg, (self.tp.rank + 1) * self.tp.m_seg)
+                tokens, target = tokens[seg], target[seg]
+                w_flat, old_flat, adv_flat = w_flat[seg], old_flat[seg], adv_flat[seg]
                 sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
             else:
                 sel = sel_all_d[lo:hi] - r0 * S
@@ -256,7 +281,7 @@ class Trainer:
         if self._cp_sync is not None:
             self._cp_sync(self.flat.grads)
             if device_accum is not None:
-                dist.all_reduce(device_accum, group=self.cp_group)
+                dist.all_reduce(device_accum, group=self._sum_group)
         if self.ep is not None:
             first = [self.flat.offsets[k] for k in self.flat.names if ".mlp.experts." in k]
             n_shared = min(first) if first else self.flat.numel

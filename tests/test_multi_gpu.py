@@ -453,6 +453,19 @@ assert abs(m1["loss"] - m2["loss"]) < 5e-3 * max(1.0, abs(m1["loss"])), (m1, m2)
 assert abs(m1["grad_norm"] - m2["grad_norm"]) < 3e-2 * m1["grad_norm"], (m1, m2)
 assert cos(one.flat.grads, cpt.flat.grads) > 0.995, cos(one.flat.grads, cpt.flat.grads)
 
+# ---- tensor parallel: heads / feed-forward sharded, token-sharded activations == the same step on one GPU
+packed_tp = _packed(cfg, 2, 256)
+tpt = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native",
+              tp_group=dist.group.WORLD, tp_tokens=512)
+one2 = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native")
+for it in range(2):                                     # second step: refreshed factors, flag epochs, buffer parity
+    m1, m3 = one2.step(packed_tp, hy), tpt.step(packed_tp, hy)
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    assert abs(m1["loss"] - m3["loss"]) < 5e-3 * max(1.0, abs(m1["loss"])), (m1, m3)
+    assert abs(m1["grad_norm"] - m3["grad_norm"]) < 3e-2 * m1["grad_norm"], (m1, m3)
+    tp_cos = cos(one2.flat.grads, tpt.flat.grads)
+    assert tp_cos > 0.995, tp_cos
+
 # ---- expert parallel: each rank trains on its own rows, experts sharded == mean of the per-rank full-model grads
 from art_b200.parallel.ep import ExpertParallel
 mcfg = ModelConfig(name="small-moe", family="qwen3_moe", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4,
@@ -479,13 +492,13 @@ for k in sorted(mlora):
         ga.append(g.reshape(-1)); gb.append(part.flat.grad_views[k].reshape(-1))
 c = cos(torch.cat(ga), torch.cat(gb))
 assert c > 0.99, c
-if rank == 0: print(f"PAR_TRAINER_OK world={world} cp_grad_cos={cos(one.flat.grads, cpt.flat.grads):.5f} ep_grad_cos={c:.5f}")
+if rank == 0: print(f"PAR_TRAINER_OK world={world} cp_grad_cos={cos(one.flat.grads, cpt.flat.grads):.5f} tp_grad_cos={tp_cos:.5f} ep_grad_cos={c:.5f}")
 dist.destroy_process_group()
 '''
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_trainer_context_and_expert_parallel(tmp_path):
+def test_trainer_context_tensor_expert_parallel(tmp_path):
     world = 2
     script = tmp_path / "par_worker.py"
     script.write_text(PAR_TRAINER_WORKER)
