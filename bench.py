@@ -48,9 +48,11 @@ def parse_args():
     ap.add_argument("--lora-rank", type=int, default=8)
     ap.add_argument("--attn", default=None)
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"])
-    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep"],
+    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep", "tp"],
                     help="dp: rows split over GPUs; cp: every row sharded over GPUs (long context); "
-                         "ep: experts sharded over GPUs (MoE presets)")
+                         "ep: experts sharded over GPUs (MoE presets); tp: tensor-parallel groups of --tp-size "
+                         "GPUs, data parallel across the groups")
+    ap.add_argument("--tp-size", type=int, default=2)
     ap.add_argument("--rollout", type=int, default=1, help="also measure rollout decode tokens/s (reported beside the headline)")
     return ap.parse_args()
 
@@ -184,14 +186,37 @@ def main():
     sync_name = "none"
     par = args.parallel if world > 1 else "dp"
     R, S = args.rows_per_gpu, args.seq_len
-    ep = cp_group = None
+    ep = cp_group = tp_group = None
     expert_range = None
+    data_ranks, data_index = world, rank        # how many ranks hold different rows, and which share this one has
     if world > 1 and par == "dp":
         from art_b200.parallel.dp import make_grad_sync
 
         grad_sync, sync_name = make_grad_sync(args.grad_sync, dev, world)
     elif par == "cp":
         cp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over cp)"
+        data_ranks, data_index = 1, 0
+    elif par == "tp":
+        T = args.tp_size
+        if world % T:
+            print("bench.py: --tp-size must divide the number of GPUs", file=sys.stderr)
+            return 2
+        for g0 in range(0, world, T):                       # every rank creates every group, in the same order
+            g = dist.new_group(list(range(g0, g0 + T)))
+            if g0 <= rank < g0 + T:
+                tp_group = g
+        dp_group = None
+        for j in range(T):
+            g = dist.new_group(list(range(j, world, T)))
+            if rank % T == j:
+                dp_group = g
+        data_ranks, data_index = world // T, rank // T
+        sync_name = f"fused-p2p-allreduce(sum over tp{T})"
+        if data_ranks > 1:
+            from art_b200.parallel.symm_mem import FusedGradAllReduce
+
+            grad_sync = FusedGradAllReduce(dev, data_ranks, dp_group)
+            sync_name += f" + fused-p2p-allreduce(mean over dp{data_ranks})"
     elif par == "ep":
         from art_b200.parallel.ep import ExpertParallel
 
@@ -207,14 +232,14 @@ def main():
                 if ".mlp.experts." not in k or expert_range[0] <= int(k.split(".experts.")[1].split(".")[0]) < expert_range[1]}
     lora = init_lora(cfg, lcfg, seed=3407, device=dev, expert_range=expert_range)
     trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync, ep=ep,
-                      cp_group=cp_group)
+                      cp_group=cp_group, tp_group=tp_group, tp_tokens=args.micro_tokens)
     rollout_base = base if (args.rollout and impl == "native" and not cfg.is_moe) else None
     del base
     hyper = TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=R, tokens_per_microbatch=args.micro_tokens)
     # cp: all ranks work on the SAME rows (each holds 1/world of every row); dp / ep: every rank has its own rows
-    host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=(1 if par == "cp" else rank + 1)).items()}
+    host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=data_index + 1).items()}
     dev_rows = {k: v.to(dev) for k, v in host_rows.items()}
-    tokens_per_step = R * S * (1 if par == "cp" else world)
+    tokens_per_step = R * S * data_ranks
 
     def barrier():
         if world > 1:
@@ -286,7 +311,7 @@ def main():
             "vs_baseline_note": "reference publishes only 9.2k packed tok/s on 1xH100 for Qwen2.5-3B 4-bit LoRA r=8",
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": args.impl,
-            "config": {"model": cfg.name, "global_batch": R * world, "seq_len": S, "parallelism": f"{par}{world}",
+            "config": {"model": cfg.name, "global_batch": R * data_ranks, "seq_len": S, "parallelism": (f"tp{args.tp_size}xdp{data_ranks}" if par == "tp" else f"{par}{world}"),
                        "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": args.micro_tokens,
                        "attention": attn_impl, "grad_sync": sync_name, "optimizer_steps_per_step": 1,
                        "l2": "inputs larger than L2: each step streams the bf16 weights (W and W^T, 30 GB for the 7B "
