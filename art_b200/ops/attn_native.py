@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -13,7 +14,10 @@ _sigs = {
     "artb_attn_tile_states": [vp, vp, vp, ci, ci, vp],
     "artb_attn_tree_fwd": [vp, ci, vp, vp, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp],
     "artb_attn_tree_bwd": [vp, ci, vp, vp, ci, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
+    "artb_attn_tc_fwd": [vp, ci, vp, vp, vp, vp, vp, ci, vp, ci, ci, ci, ci, vp, vp],
 }
+# forward on tcgen05 / TMEM when the shape allows it (head dim 128, rows a multiple of 128 tokens)
+USE_TC = os.environ.get("ARTB_ATTN_TC", "1") == "1"
 _bound: dict[str, object] = {}
 
 
@@ -42,6 +46,13 @@ def forward(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, plan) -> tuple[torch.
     S = plan.S
     out = torch.empty((M, Hq * hd), dtype=qkv.dtype, device=qkv.device)
     lse2 = torch.empty((Hq, M), dtype=torch.float32, device=qkv.device)
+    if USE_TC and hd == 128 and S % 128 == 0 and M % 8 == 0:
+        vt = torch.empty((Hkv * hd, M), dtype=qkv.dtype, device=qkv.device)
+        _lib.check_rc(_f("artb_attn_tc_fwd")(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(plan.gid), _lib.ptr(plan.pid),
+                                             _lib.ptr(plan.state), _lib.ptr(vt), _lib.ptr(out), out.stride(0),
+                                             _lib.ptr(lse2), M // S, S, Hq, Hkv,
+                                             _lib.ptr(_lib.status_word(qkv.device)), _lib.stream_ptr()), "attn_tc_fwd")
+        return out, (qkv, out, lse2, Hq, Hkv, hd)
     _lib.check_rc(_f("artb_attn_tree_fwd")(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(plan.gid), _lib.ptr(plan.pid),
                                            _lib.ptr(plan.state), _lib.ptr(out), out.stride(0), _lib.ptr(lse2),
                                            M // S, S, Hq, Hkv, hd, _lib.stream_ptr()), "attn_tree_fwd")

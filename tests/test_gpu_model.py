@@ -84,7 +84,8 @@ def test_fused_logprob_grpo_loss_fwd_bwd():
     assert rel_err(dh, h32.grad) < 2e-2
 
 
-@pytest.mark.parametrize("rows,S,Hq,Hkv,hd,seg", [(1, 128, 2, 1, 32, 48), (2, 256, 4, 2, 64, 80), (1, 512, 7, 1, 128, 160)])
+@pytest.mark.parametrize("rows,S,Hq,Hkv,hd,seg", [(1, 128, 2, 1, 32, 48), (2, 256, 4, 2, 64, 80), (1, 512, 7, 1, 128, 160),
+                                                  (2, 1024, 4, 2, 128, 200)])
 def test_tree_attention_fwd_bwd(rows, S, Hq, Hkv, hd, seg):
     from art_b200.ops import attention as A
 
