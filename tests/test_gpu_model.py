@@ -85,7 +85,7 @@ def test_fused_logprob_grpo_loss_fwd_bwd():
 
 
 @pytest.mark.parametrize("rows,S,Hq,Hkv,hd,seg", [(1, 128, 2, 1, 32, 48), (2, 256, 4, 2, 64, 80), (1, 512, 7, 1, 128, 160),
-                                                  (2, 1024, 4, 2, 128, 200)])
+                                                  (2, 1024, 4, 2, 128, 200), (1, 2048, 14, 2, 128, 512)])
 def test_tree_attention_fwd_bwd(rows, S, Hq, Hkv, hd, seg):
     from art_b200.ops import attention as A
 
