@@ -22,13 +22,15 @@
 // Reference semantics: autograd through SDPA with the dense bias of src/art/local/train.py:177-215.
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "host_utils.h"
 #include "ptx_sm100.cuh"
 
 namespace artb {
 
 constexpr int TB_HD = 128;
-constexpr int TB_THREADS = 320;   // TMA warp, MMA warp, 8 element-wise warps (two per TMEM lane quarter)
+constexpr int TB_THREADS = 576;   // TMA warp, MMA warp, 16 element-wise warps (four per TMEM lane quarter)
 
 __device__ __forceinline__ float tb_ex2(float x) {
   float y;
@@ -51,7 +53,7 @@ struct DkvSmem {
   static constexpr int STAGE = 65536;              // [2] x { Q 16K | dO 16K | Q^T 16K | dO^T 16K }
   static constexpr int PT = STAGE + 2 * 65536;     // P^T  [128 x 64] bf16
   static constexpr int DST = PT + 16384;           // dS^T [128 x 64] bf16
-  static constexpr int LD = DST + 16384;           // float2 [8 warps][32]: (lse2, D) of the warp's 32 queries
+  static constexpr int LD = DST + 16384;           // float2 [16 warps][16]: (lse2, D) of the warp's 16 queries
   static constexpr int BAR = LD + 4 * 64 * 8;
   static constexpr int TOTAL = BAR + 256;          // 231 680 B; the dynamic window must start 1024-aligned
 };
@@ -62,7 +64,7 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
                    const __grid_constant__ CUtensorMap tmDOt, const int* __restrict__ gid, const int* __restrict__ pid,
                    const uint8_t* __restrict__ state, const float* __restrict__ lse2, const float* __restrict__ Dv,
                    __nv_bfloat16* __restrict__ dqkv, int ld, int S, int Hq, int Hkv, float scale, float scale_log2, long M,
-                   int* status) {
+                   int GS, float* __restrict__ partial, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkvSmem::BAR);
   uint64_t* kv_full = bars;
@@ -77,8 +79,12 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int nb64 = S / 64;
-  const int kb = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
-  const int G = Hq / Hkv;
+  // The query heads of a kv group can be split over GS CTAs (shorter critical path for the key blocks near the
+  // start of a row, which see every later query); each then writes an fp32 partial that a combine kernel sums.
+  const int kb = blockIdx.x, kvh = blockIdx.y / GS, gs = blockIdx.y % GS, row = blockIdx.z;
+  const int Gall = Hq / Hkv, Gper = (Gall + GS - 1) / GS;
+  const int g_lo = gs * Gper;
+  const int G = min(Gall, g_lo + Gper) - g_lo;          // query heads handled here: g_lo .. g_lo + G - 1
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long base = static_cast<long>(row) * S;
   const uint8_t* st64 = state + static_cast<size_t>(row) * nb64 * nb64;
@@ -103,9 +109,9 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
       mbar_init(&stage_full[i], 1);
       mbar_init(&stage_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 8);
+      mbar_init(&s_empty[i], 16);
     }
-    mbar_init(pt_full, 8);
+    mbar_init(pt_full, 16);
     mbar_init(pt_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -138,7 +144,7 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
           *abort_flag = 1;
           break;
         }
-        const int hq = kvh * G + g;
+        const int hq = kvh * Gall + g_lo + g;
         const int qrow = static_cast<int>(base) + qb * 64;
         uint8_t* st = smem + DkvSmem::STAGE + s * 65536;
         mbar_expect_tx(&stage_full[s], 65536);
@@ -205,109 +211,134 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
       tc_commit(acc_full);
     }
   } else {
-    // thread = (key row r, half hf): 32 of the item's 64 query columns; two warps share a TMEM lane quarter
+    // thread = (key row r, column quarter hf): 16 of the item's 64 query columns; four warps share a TMEM lane
+    // quarter, which gives every scheduler four element-wise warps to overlap TMEM / MUFU / shared-memory latency
     const int q = warp & 3, hf = (warp - 2) >> 2;
     const int r = q * 32 + lane;                 // key row inside the block
     const long ki = base + kb * 128 + r;
     const int gk_mine = gid[ki];
     const int kpos = kb * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    float2* ldw = reinterpret_cast<float2*>(smem + DkvSmem::LD) + (q * 2 + hf) * 32;   // (lse2, D) of my 32 queries
+    float2* ldw = reinterpret_cast<float2*>(smem + DkvSmem::LD) + (q * 4 + hf) * 16;   // (lse2, D) of my 16 queries
     uint8_t* pt_row = smem + DkvSmem::PT + r * 128;
     uint8_t* dst_row = smem + DkvSmem::DST + r * 128;
     const int sw = r & 7;
+    const int l16 = lane & 15;
     bool dead = false;
     uint32_t it = 0;
-    for (int g = 0; g < G && !dead; ++g) {
-      const int hq = kvh * G + g;
-      const float* lse_h = lse2 + static_cast<long>(hq) * M + base + hf * 32 + lane;
-      const float* d_h = Dv + static_cast<long>(hq) * M + base + hf * 32 + lane;
-      for (int qb = qb_lo; qb < nb64; ++qb) {
+    // items are visited in (g, qb) order; the per-query constants of the NEXT valid item are fetched from global
+    // memory one item ahead so that their latency is off the critical path
+    auto next_valid = [&](int& g, int& qb) {      // advance (g, qb) to the next non-empty item; false at the end
+      for (;;) {
+        if (++qb >= nb64) {
+          qb = qb_lo;
+          if (++g >= G) return false;
+        }
         const uint8_t* sr = st64 + static_cast<size_t>(qb) * nb64 + 2 * kb;
-        const int sa = sr[0], sb = sr[1];
-        if ((sa | sb) == 0) continue;
-        if (__shfl_sync(0xffffffffu, *abort_flag, 0)) {
-          dead = true;
-          break;
-        }
-        const int s = it & 1;
-        const bool partial = !(sa == 2 && sb == 2);
-        __syncwarp();
-        ldw[lane] = make_float2(lse_h[qb * 64], d_h[qb * 64]);
-        int gq_h = 0, pq_h = 0;
-        if (partial) {
-          gq_h = gid[base + qb * 64 + hf * 32 + lane];
-          pq_h = pid[base + qb * 64 + hf * 32 + lane];
-        }
-        __syncwarp();
-        const int okw = mbar_wait(&s_full[s], (it >> 1) & 1) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, okw)) {
-          if (lane == 0) {
-            atomicMax(status, ST_TIMEOUT_TMEM_FULL);
-            *abort_flag = 1;
-          }
-          dead = true;
-          break;
-        }
-        tc_fence_after_sync();
-        uint32_t xs[32], xd[32];   // S^T and dP^T of my key row, my 32 query columns
-        tmem_ld_32x32(tmem + lane_off + s * 64 + hf * 32, xs);
-        tmem_ld_32x32(tmem + lane_off + 128 + s * 64 + hf * 32, xd);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[s]);
-        const int okp = mbar_wait(pt_empty, (it & 1) ^ 1) ? 1 : 0;
-        if (!__all_sync(0xffffffffu, okp)) {
-          if (lane == 0) {
-            atomicMax(status, ST_TIMEOUT_EMPTY);
-            *abort_flag = 1;
-          }
-          dead = true;
-          break;
-        }
-        const int qpos0 = qb * 64 + hf * 32;
-        const float4* ld4 = reinterpret_cast<const float4*>(ldw);
-#pragma unroll
-        for (int ii = 0; ii < 4; ++ii) {
-          float pe[8], de[8];
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            const int jj = 8 * ii + e;
-            const float4 l4 = ld4[jj >> 1];      // (lse, D) of queries jj and jj + 1
-            float p0 = tb_ex2(fmaf(__uint_as_float(xs[jj]), scale_log2, -l4.x));
-            float p1 = tb_ex2(fmaf(__uint_as_float(xs[jj + 1]), scale_log2, -l4.z));
-            if (partial) {
-              const int g0 = __shfl_sync(0xffffffffu, gq_h, jj), q0i = __shfl_sync(0xffffffffu, pq_h, jj);
-              const int g1 = __shfl_sync(0xffffffffu, gq_h, jj + 1), q1i = __shfl_sync(0xffffffffu, pq_h, jj + 1);
-              if (!(kpos <= qpos0 + jj && (gk_mine == g0 || gk_mine == q0i))) p0 = 0.f;
-              if (!(kpos <= qpos0 + jj + 1 && (gk_mine == g1 || gk_mine == q1i))) p1 = 0.f;
-            }
-            pe[e] = p0;
-            pe[e + 1] = p1;
-            de[e] = p0 * (__uint_as_float(xd[jj]) - l4.y);          // the softmax scale is applied to dK at the end
-            de[e + 1] = p1 * (__uint_as_float(xd[jj + 1]) - l4.w);
-          }
-          uint4 w, v;
-          w.x = pack_bf16x2(pe[0], pe[1]);
-          w.y = pack_bf16x2(pe[2], pe[3]);
-          w.z = pack_bf16x2(pe[4], pe[5]);
-          w.w = pack_bf16x2(pe[6], pe[7]);
-          v.x = pack_bf16x2(de[0], de[1]);
-          v.y = pack_bf16x2(de[2], de[3]);
-          v.z = pack_bf16x2(de[4], de[5]);
-          v.w = pack_bf16x2(de[6], de[7]);
-          const int piece = 4 * hf + ii;
-          *reinterpret_cast<uint4*>(pt_row + ((piece ^ sw) << 4)) = w;
-          *reinterpret_cast<uint4*>(dst_row + ((piece ^ sw) << 4)) = v;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(pt_full);
-        ++it;
+        if ((sr[0] | sr[1]) != 0) return true;
       }
+    };
+    auto fetch = [&](int g, int qb, float2& ld, int& gq, int& pq) {
+      const long qidx = base + qb * 64 + hf * 16 + l16;
+      const long hidx = static_cast<long>(kvh * Gall + g_lo + g) * M + qidx;
+      ld = make_float2(lse2[hidx], Dv[hidx]);
+      gq = gid[qidx];
+      pq = pid[qidx];
+    };
+    int g = 0, qb = qb_lo - 1;
+    bool have = G > 0 && next_valid(g, qb);
+    float2 ld_cur = make_float2(0.f, 0.f);
+    int gq_cur = 0, pq_cur = 0;
+    if (have) fetch(g, qb, ld_cur, gq_cur, pq_cur);
+    while (have) {
+      if (__shfl_sync(0xffffffffu, *abort_flag, 0)) {
+        dead = true;
+        break;
+      }
+      const uint8_t* sr = st64 + static_cast<size_t>(qb) * nb64 + 2 * kb;
+      const bool partial = !(sr[0] == 2 && sr[1] == 2);
+      const int qpos0 = qb * 64 + hf * 16;
+      const int s = it & 1;
+      __syncwarp();
+      if (lane < 16) ldw[lane] = ld_cur;
+      const int gq_h = gq_cur, pq_h = pq_cur;
+      int g2 = g, qb2 = qb;
+      const bool have2 = next_valid(g2, qb2);
+      if (have2) fetch(g2, qb2, ld_cur, gq_cur, pq_cur);   // in flight while this item is processed
+      __syncwarp();
+      const int okw = mbar_wait(&s_full[s], (it >> 1) & 1) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, okw)) {
+        if (lane == 0) {
+          atomicMax(status, ST_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        dead = true;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t xs[16], xd[16];   // S^T and dP^T of my key row, my 16 query columns
+      tmem_ld_32x16(tmem + lane_off + s * 64 + hf * 16, xs);
+      tmem_ld_32x16(tmem + lane_off + 128 + s * 64 + hf * 16, xd);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      const float4* ld4 = reinterpret_cast<const float4*>(ldw);
+      uint4 w[2], v[2];
+#pragma unroll
+      for (int ii = 0; ii < 2; ++ii) {
+        float pe[8], de[8];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const int jj = 8 * ii + e;
+          const float4 l4 = ld4[jj >> 1];      // (lse, D) of queries jj and jj + 1
+          float p0 = tb_ex2(fmaf(__uint_as_float(xs[jj]), scale_log2, -l4.x));
+          float p1 = tb_ex2(fmaf(__uint_as_float(xs[jj + 1]), scale_log2, -l4.z));
+          if (partial) {
+            const int g0 = __shfl_sync(0xffffffffu, gq_h, jj), q0i = __shfl_sync(0xffffffffu, pq_h, jj);
+            const int g1 = __shfl_sync(0xffffffffu, gq_h, jj + 1), q1i = __shfl_sync(0xffffffffu, pq_h, jj + 1);
+            if (!(kpos <= qpos0 + jj && (gk_mine == g0 || gk_mine == q0i))) p0 = 0.f;
+            if (!(kpos <= qpos0 + jj + 1 && (gk_mine == g1 || gk_mine == q1i))) p1 = 0.f;
+          }
+          pe[e] = p0;
+          pe[e + 1] = p1;
+          de[e] = p0 * (__uint_as_float(xd[jj]) - l4.y);          // the softmax scale is applied to dK at the end
+          de[e + 1] = p1 * (__uint_as_float(xd[jj + 1]) - l4.w);
+        }
+        w[ii].x = pack_bf16x2(pe[0], pe[1]);
+        w[ii].y = pack_bf16x2(pe[2], pe[3]);
+        w[ii].z = pack_bf16x2(pe[4], pe[5]);
+        w[ii].w = pack_bf16x2(pe[6], pe[7]);
+        v[ii].x = pack_bf16x2(de[0], de[1]);
+        v[ii].y = pack_bf16x2(de[2], de[3]);
+        v[ii].z = pack_bf16x2(de[4], de[5]);
+        v[ii].w = pack_bf16x2(de[6], de[7]);
+      }
+      // only now wait for the previous item's accumulate MMAs to release the P^T / dS^T tiles
+      const int okp = mbar_wait(pt_empty, (it & 1) ^ 1) ? 1 : 0;
+      if (!__all_sync(0xffffffffu, okp)) {
+        if (lane == 0) {
+          atomicMax(status, ST_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+        }
+        dead = true;
+        break;
+      }
+#pragma unroll
+      for (int ii = 0; ii < 2; ++ii) {
+        const int piece = 2 * hf + ii;
+        *reinterpret_cast<uint4*>(pt_row + ((piece ^ sw) << 4)) = w[ii];
+        *reinterpret_cast<uint4*>(dst_row + ((piece ^ sw) << 4)) = v[ii];
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pt_full);
+      ++it;
+      g = g2;
+      qb = qb2;
+      have = have2;
     }
-    // accumulators -> dK, dV rows of this key block (bf16 into the fused gradient buffer); my 64 columns of each
+    // accumulators -> dK, dV rows of this key block (bf16 into the fused gradient buffer); my 32 columns of each
     if (!dead) {
       const int okw = mbar_wait(acc_full, 0) ? 1 : 0;
       if (!__all_sync(0xffffffffu, okw)) {
@@ -320,15 +351,19 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
     }
     if (!dead) {
       tc_fence_after_sync();
-      __nv_bfloat16* dk = dqkv + ki * ld + (Hq + kvh) * TB_HD + hf * 64;
-      __nv_bfloat16* dv = dqkv + ki * ld + (Hq + Hkv + kvh) * TB_HD + hf * 64;
+      __nv_bfloat16* dk = dqkv + ki * ld + (Hq + kvh) * TB_HD + hf * 32;
+      __nv_bfloat16* dv = dqkv + ki * ld + (Hq + Hkv + kvh) * TB_HD + hf * 32;
+      // partial layout: fp32 [GS][M][2 * Hkv * 128], columns = dk of all kv heads, then dv of all kv heads
+      float* pk = partial ? partial + (static_cast<size_t>(gs) * M + ki) * (2 * Hkv * TB_HD) + kvh * TB_HD + hf * 32 : nullptr;
+      float* pv = partial ? pk + Hkv * TB_HD : nullptr;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* o = which == 0 ? dv : dk;
+        float* po = which == 0 ? pv : pk;
         const float f = which == 0 ? 1.f : scale;
-        const uint32_t col0 = 256 + which * 128 + hf * 64;
+        const uint32_t col0 = 256 + which * 128 + hf * 32;
 #pragma unroll 1
-        for (int c = 0; c < 64; c += 32) {
+        for (int c = 0; c < 32; c += 32) {
           uint32_t v[32];
           if (it > 0) {
             tmem_ld_32x32(tmem + lane_off + col0 + c, v);
@@ -336,6 +371,11 @@ attn_tc_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_co
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+          if (po) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(po + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            continue;
           }
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -368,7 +408,7 @@ struct DqSmem {
   static constexpr int Q = 0, DO = 32768;
   static constexpr int STAGE = 65536;              // [2] x { K 16K | V 16K | K^T 16K }
   static constexpr int DS = STAGE + 2 * 49152;     // [2] x dS [128 x 64] bf16
-  static constexpr int GK = DS + 2 * 16384;        // int [8 warps][32]
+  static constexpr int GK = DS + 2 * 16384;        // int [16 warps][16]
   static constexpr int BAR = GK + 4 * 64 * 4;
   static constexpr int TOTAL = BAR + 256;
 };
@@ -414,8 +454,8 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
       mbar_init(&stage_full[i], 1);
       mbar_init(&stage_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 8);
-      mbar_init(&ds_full[i], 8);
+      mbar_init(&s_empty[i], 16);
+      mbar_init(&ds_full[i], 16);
       mbar_init(&ds_empty[i], 1);
     }
     mbar_init(acc_full, 1);
@@ -509,7 +549,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
       tc_commit(acc_full);
     }
   } else {
-    // thread = (query row r, half hf): 32 of the item's 64 key columns
+    // thread = (query row r, column quarter hf): 16 of the item's 64 key columns
     const int q = warp & 3, hf = (warp - 2) >> 2;
     const int r = q * 32 + lane;                 // query row inside the block
     const long qi = base + qb * 128 + r;
@@ -517,7 +557,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
     const int qpos = qb * 128 + r;
     const float lse_r = lse2[static_cast<long>(h) * M + qi], D_r = Dv[static_cast<long>(h) * M + qi];
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    int* gk = reinterpret_cast<int*>(smem + DqSmem::GK) + (q * 2 + hf) * 32;
+    int* gk = reinterpret_cast<int*>(smem + DqSmem::GK) + (q * 4 + hf) * 16;
     const int sw = r & 7;
     bool dead = false;
     uint32_t it = 0;
@@ -533,7 +573,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
       const bool partial = stt == 1;
       if (partial) {
         __syncwarp();
-        gk[lane] = gid[base + kb * 64 + hf * 32 + lane];
+        if (lane < 16) gk[lane] = gid[base + kb * 64 + hf * 16 + lane];
         __syncwarp();
       }
       const int okw = mbar_wait(&s_full[s], ph) ? 1 : 0;
@@ -546,9 +586,9 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
         break;
       }
       tc_fence_after_sync();
-      uint32_t xs[32], xd[32];   // S and dP of my query row, my 32 key columns
-      tmem_ld_32x32(tmem + lane_off + s * 64 + hf * 32, xs);
-      tmem_ld_32x32(tmem + lane_off + 128 + s * 64 + hf * 32, xd);
+      uint32_t xs[16], xd[16];   // S and dP of my query row, my 16 key columns
+      tmem_ld_32x16(tmem + lane_off + s * 64 + hf * 16, xs);
+      tmem_ld_32x16(tmem + lane_off + 128 + s * 64 + hf * 16, xd);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -563,9 +603,9 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
         break;
       }
       uint8_t* ds_row = smem + DqSmem::DS + s * 16384 + r * 128;
-      const int k0 = kb * 64 + hf * 32;
+      const int k0 = kb * 64 + hf * 16;
 #pragma unroll
-      for (int ii = 0; ii < 4; ++ii) {
+      for (int ii = 0; ii < 2; ++ii) {
         float de[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -582,7 +622,7 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
         v.y = pack_bf16x2(de[2], de[3]);
         v.z = pack_bf16x2(de[4], de[5]);
         v.w = pack_bf16x2(de[6], de[7]);
-        *reinterpret_cast<uint4*>(ds_row + (((4 * hf + ii) ^ sw) << 4)) = v;
+        *reinterpret_cast<uint4*>(ds_row + (((2 * hf + ii) ^ sw) << 4)) = v;
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -601,12 +641,12 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
     }
     if (!dead) {
       tc_fence_after_sync();
-      __nv_bfloat16* o = dqkv + qi * ld + h * TB_HD + hf * 64;
+      __nv_bfloat16* o = dqkv + qi * ld + h * TB_HD + hf * 32;
 #pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
+      for (int c = 0; c < 32; c += 32) {
         uint32_t v[32];
         if (it > 0) {
-          tmem_ld_32x32(tmem + lane_off + 256 + hf * 64 + c, v);
+          tmem_ld_32x32(tmem + lane_off + 256 + hf * 32 + c, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -637,22 +677,58 @@ attn_tc_dq_kernel(const __grid_constant__ CUtensorMap tmQKV128, const __grid_con
   }
 }
 
-// dst[(c), token] = src[token, c0 + c]  for c < width
-__global__ void attn_tc_transpose_kernel(const __nv_bfloat16* __restrict__ src, int ld, int c0,
-                                         __nv_bfloat16* __restrict__ dst, long M, int width) {
-  __shared__ __nv_bfloat16 tile[32][33];
-  const long t0 = static_cast<long>(blockIdx.x) * 32;
-  const int cb = blockIdx.y * 32;
-  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-    const long t = t0 + i;
-    tile[i][threadIdx.x] = (t < M && cb + static_cast<int>(threadIdx.x) < width) ? src[t * ld + c0 + cb + threadIdx.x]
-                                                                               : __float2bfloat16(0.f);
+// dk|dv rows = sum over the GS partials (dk scaled), written as bf16 into the k|v columns of dqkv
+__global__ void attn_tc_combine_dkv_kernel(const float* __restrict__ partial, int GS, __nv_bfloat16* __restrict__ dqkv, int ld,
+                                           int kcol0, long M, int kvw /* Hkv * 128 */, float scale) {
+  const int vec = (2 * kvw) >> 2;
+  const long total = M * vec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long m = i / vec;
+    const int c = static_cast<int>(i % vec) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int g = 0; g < GS; ++g) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(g) * M + m) * (2 * kvw) + c);
+      a.x += v.x;
+      a.y += v.y;
+      a.z += v.z;
+      a.w += v.w;
+    }
+    const float f = c < kvw ? scale : 1.f;
+    uint2 o;
+    o.x = pack_bf16x2(a.x * f, a.y * f);
+    o.y = pack_bf16x2(a.z * f, a.w * f);
+    *reinterpret_cast<uint2*>(dqkv + m * ld + kcol0 + c) = o;
+  }
+}
+
+// dst[c, token] = src[token, c0 + c] for c < width: 64 x 64 tiles, 16-byte loads and stores (M % 8 == 0, width % 64 == 0)
+__global__ void __launch_bounds__(256)
+attn_tc_transpose_kernel(const __nv_bfloat16* __restrict__ src, int ld, int c0, __nv_bfloat16* __restrict__ dst, long M,
+                         int width) {
+  __shared__ __nv_bfloat16 tile[64][64 + 8];
+  const long t0 = static_cast<long>(blockIdx.x) * 64;
+  const int cb = blockIdx.y * 64;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int v = tid + i * 256;          // 512 vectors: 64 tokens x 8
+    const int r = v >> 3, cv = v & 7;
+    const long t = t0 + r;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (t < M) x = *reinterpret_cast<const uint4*>(src + t * ld + c0 + cb + cv * 8);
+    *reinterpret_cast<uint4*>(&tile[r][cv * 8]) = x;
   }
   __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-    const int c = cb + i;
-    const long t = t0 + threadIdx.x;
-    if (c < width && t < M) dst[static_cast<size_t>(c) * M + t] = tile[threadIdx.x][i];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int v = tid + i * 256;          // 512 vectors: 64 columns x 8 token groups
+    const int c = v >> 3, tv = v & 7;
+    __nv_bfloat16 e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = tile[tv * 8 + j][c];
+    const long t = t0 + tv * 8;
+    if (t < M) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(cb + c) * M + t) = *reinterpret_cast<const uint4*>(e);
   }
 }
 
@@ -681,10 +757,12 @@ __global__ void attn_tc_rowdot_kernel(const __nv_bfloat16* __restrict__ dO, cons
 using namespace artb;
 
 // qkv / dqkv [rows*S, ld] (q | k | v columns); out, dout [rows*S, ldo]; lse2, Dbuf fp32 [Hq, rows*S];
-// scratch bf16: qt, dot [Hq*128, rows*S], kt [Hkv*128, rows*S].  Head dim 128, S % 128 == 0.
+// scratch bf16: qt, dot [Hq*128, rows*S], kt [Hkv*128, rows*S]; partial: optional fp32 [2, rows*S, 2*Hkv*128]
+// (enables the two-way split of a kv group's query heads).  Head dim 128, S % 128 == 0.
 ARTB_EXPORT int artb_attn_tc_bwd(const void* qkv, int ld, const void* out, const void* dout, int ldo, const int* gid,
                                  const int* pid, const uint8_t* state, const float* lse2, float* Dbuf, void* qt, void* dot,
-                                 void* kt, void* dqkv, int rows, int S, int Hq, int Hkv, int* status, cudaStream_t st) {
+                                 void* kt, void* dqkv, float* partial, int rows, int S, int Hq, int Hkv, int* status,
+                                 cudaStream_t st) {
   if (S % 128 || Hq % Hkv || (ld & 7) || (ldo & 7)) return ERR_BAD_SHAPE;
   const long M = static_cast<long>(rows) * S;
   if (M > 0x7fffffffL) return ERR_BAD_SHAPE;
@@ -693,8 +771,8 @@ ARTB_EXPORT int artb_attn_tc_bwd(const void* qkv, int ld, const void* out, const
     const long warps = M * Hq;
     attn_tc_rowdot_kernel<<<static_cast<unsigned>((warps + 3) / 4), 128, 0, st>>>(
         reinterpret_cast<const bf*>(dout), reinterpret_cast<const bf*>(out), ldo, Dbuf, M, Hq);
-    dim3 block(32, 8);
-    dim3 gq(static_cast<unsigned>((M + 31) / 32), Hq * TB_HD / 32), gk(static_cast<unsigned>((M + 31) / 32), Hkv * TB_HD / 32);
+    const unsigned block = 256;
+    dim3 gq(static_cast<unsigned>((M + 63) / 64), Hq * TB_HD / 64), gk(static_cast<unsigned>((M + 63) / 64), Hkv * TB_HD / 64);
     attn_tc_transpose_kernel<<<gq, block, 0, st>>>(reinterpret_cast<const bf*>(qkv), ld, 0, reinterpret_cast<bf*>(qt), M,
                                                    Hq * TB_HD);
     attn_tc_transpose_kernel<<<gq, block, 0, st>>>(reinterpret_cast<const bf*>(dout), ldo, 0, reinterpret_cast<bf*>(dot), M,
@@ -724,10 +802,17 @@ ARTB_EXPORT int artb_attn_tc_bwd(const void* qkv, int ld, const void* out, const
   }
   const float scale = 1.f / sqrtf(static_cast<float>(TB_HD));
   const float scale_log2 = 1.4426950408889634f * scale;
-  dim3 g1(S / 128, Hkv, rows), g2(S / 128, Hq, rows);
+  // split the query heads of a group over two CTAs when a group has at least four heads and the caller gave scratch
+  const int GS = (partial != nullptr && Hq / Hkv >= 4) ? 2 : 1;
+  dim3 g1(S / 128, Hkv * GS, rows), g2(S / 128, Hq, rows);
   attn_tc_dkv_kernel<<<g1, TB_THREADS, DkvSmem::TOTAL, st>>>(tmQKV128, tmQKV64, tmDO64, tmQt, tmDOt, gid, pid, state, lse2,
                                                             Dbuf, reinterpret_cast<bf*>(dqkv), ld, S, Hq, Hkv, scale,
-                                                            scale_log2, M, status);
+                                                            scale_log2, M, GS, GS > 1 ? partial : nullptr, status);
+  if (GS > 1) {
+    const long total = M * ((2 * Hkv * TB_HD) >> 2);
+    attn_tc_combine_dkv_kernel<<<static_cast<unsigned>(std::min<long>((total + 255) / 256, 148 * 16)), 256, 0, st>>>(
+        partial, GS, reinterpret_cast<bf*>(dqkv), ld, Hq * TB_HD, M, Hkv * TB_HD, scale);
+  }
   attn_tc_dq_kernel<<<g2, TB_THREADS, DqSmem::TOTAL, st>>>(tmQKV128, tmQKV64, tmDO128, tmKt, gid, pid, state, lse2, Dbuf,
                                                           reinterpret_cast<bf*>(dqkv), ld, S, Hq, Hkv, scale, scale_log2,
                                                           M, status);

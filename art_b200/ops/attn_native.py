@@ -15,7 +15,7 @@ _sigs = {
     "artb_attn_tree_fwd": [vp, ci, vp, vp, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp],
     "artb_attn_tree_bwd": [vp, ci, vp, vp, ci, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
     "artb_attn_tc_fwd": [vp, ci, vp, vp, vp, vp, vp, ci, vp, ci, ci, ci, ci, vp, vp],
-    "artb_attn_tc_bwd": [vp, ci, vp, vp, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp],
+    "artb_attn_tc_bwd": [vp, ci, vp, vp, ci, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, vp],
 }
 # forward on tcgen05 / TMEM when the shape allows it (head dim 128, rows a multiple of 128 tokens)
 USE_TC = os.environ.get("ARTB_ATTN_TC", "1") == "1"
@@ -70,10 +70,11 @@ def backward(dout: torch.Tensor, saved: tuple, plan) -> torch.Tensor:
         qt = torch.empty((Hq * hd, M), dtype=qkv.dtype, device=qkv.device)
         dot = torch.empty((Hq * hd, M), dtype=qkv.dtype, device=qkv.device)
         kt = torch.empty((Hkv * hd, M), dtype=qkv.dtype, device=qkv.device)
+        partial = torch.empty((2, M, 2 * Hkv * hd), dtype=torch.float32, device=qkv.device) if Hq // Hkv >= 4 else None
         _lib.check_rc(_f("artb_attn_tc_bwd")(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(out), _lib.ptr(dout), out.stride(0),
                                              _lib.ptr(plan.gid), _lib.ptr(plan.pid), _lib.ptr(plan.state),
                                              _lib.ptr(lse2), _lib.ptr(dbuf), _lib.ptr(qt), _lib.ptr(dot), _lib.ptr(kt),
-                                             _lib.ptr(dqkv), M // S, S, Hq, Hkv,
+                                             _lib.ptr(dqkv), _lib.ptr(partial), M // S, S, Hq, Hkv,
                                              _lib.ptr(_lib.status_word(qkv.device)), _lib.stream_ptr()), "attn_tc_bwd")
         return dqkv
     dq_acc = torch.empty((M, Hq * hd), dtype=torch.float32, device=qkv.device)
