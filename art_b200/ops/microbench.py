@@ -52,6 +52,49 @@ def bench_gemm(a) -> dict:
     return res
 
 
+def bench_attn(a) -> dict:
+    """Tree-masked attention forward + backward on the benchmark mask (prompt + 3 sibling completions per row)."""
+    from . import _lib, attn_native
+    from . import attention as A
+
+    dev = "cuda"
+    rows, S, Hq, Hkv, hd = a.rows, a.seq, a.hq, a.hkv, a.hd
+    M = rows * S
+    g = torch.Generator(device=dev).manual_seed(0)
+    qkv = (torch.randn(M, (Hq + 2 * Hkv) * hd, device=dev, generator=g) * 0.5).bfloat16()
+    do = (torch.randn(M, Hq * hd, device=dev, generator=g) * 0.5).bfloat16()
+    seg = S // 4
+    gid = torch.empty(rows, S, dtype=torch.int32)
+    pid = torch.empty(rows, S, dtype=torch.int32)
+    for r in range(rows):
+        p = 100 * r
+        gid[r, :seg] = p
+        pid[r] = p
+        for c in range(3):
+            gid[r, seg * (c + 1): seg * (c + 2)] = p + c + 1
+    gid, pid = gid.reshape(-1).to(dev), pid.reshape(-1).to(dev)
+    plan = A.make_plan(gid, pid, S, "native")
+    density = (plan.state.float() > 0).float().mean().item()
+    fl = 4.0 * rows * S * S * hd * Hq * density
+    res = {"op": "tree_attention", "rows": rows, "seq": S, "heads": f"{Hq}/{Hkv}x{hd}", "tile_density": round(density, 3)}
+    for name, tc in (("tcgen05", True), ("mma_sync", False)):
+        if a.no_baseline and not tc:
+            continue
+        attn_native.USE_TC = attn_native.USE_TC_BWD = tc
+        box = {}
+
+        def fwd():
+            box["o"], box["saved"] = attn_native.forward(qkv, Hq, Hkv, hd, plan)
+
+        tf = _time(fwd, a.iters, a.warmup, None)
+        tb = _time(lambda: attn_native.backward(do, box["saved"], plan), a.iters, a.warmup, None)
+        res[name] = {"fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4), "fwd_tflops": round(fl / tf / 1e9, 1),
+                     "bwd_tflops": round(2.5 * fl / tb / 1e9, 1)}
+    attn_native.USE_TC = attn_native.USE_TC_BWD = True
+    _lib.check_status()
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -61,13 +104,19 @@ def main() -> None:
     g.add_argument("--k", type=int, default=3584)
     g.add_argument("--bn", type=int, default=0)
     g.add_argument("--two-cta", type=int, default=-1, help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
-    for p in (g,):
+    t = sub.add_parser("attn")
+    t.add_argument("--rows", type=int, default=4)
+    t.add_argument("--seq", type=int, default=2048)
+    t.add_argument("--hq", type=int, default=28)
+    t.add_argument("--hkv", type=int, default=4)
+    t.add_argument("--hd", type=int, default=128)
+    for p in (g, t):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    print(json.dumps(bench_gemm(a)))
+    print(json.dumps(bench_attn(a) if a.op == "attn" else bench_gemm(a)))
 
 
 if __name__ == "__main__":
