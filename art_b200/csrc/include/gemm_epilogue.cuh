@@ -4,7 +4,7 @@
 
 namespace artb {
 
-enum GemmEpilogue : int { EPI_BF16 = 0, EPI_BF16_RESID = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+enum GemmEpilogue : int { EPI_BF16 = 0, EPI_BF16_RESID = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_SWIGLU_BWD = 4 };
 
 // Tiles are visited with the M index fastest, so the CTAs that run concurrently share a handful
 // of weight (B) tiles and sweep the activation matrix, which stays L2-resident.
@@ -43,6 +43,9 @@ struct SchedSplitK {
 
 // acc (+ bias) (+ residual on the first res_cols columns) -> C as bf16 or fp32; optional SwiGLU
 // output H for gate|up-interleaved columns (blocks of 16).
+// swiglu_bwd: acc is d(silu(gate) * up) [M, N]; H holds the forward's gate|up pre-activations [M, 2N] (interleaved in
+// blocks of 16) and C receives d(gate|up) [M, 2N] in the same layout, so the activation gradient never exists in
+// memory as a separate tensor.
 template <int BN>
 struct EpiStore {
   void* C;
@@ -53,6 +56,7 @@ struct EpiStore {
   int M, N;
   int out_f32;
   int res_cols;
+  int swiglu_bwd = 0;
 
   __device__ void tile_begin(const TileInfo&, int) {}
   __device__ void tile_end(const TileInfo&, int) {}
@@ -62,6 +66,36 @@ struct EpiStore {
     const int gc = ti.n_blk * BN + c;
     if (gr >= M || gc >= N) return;
     const bool full = (gc + 32 <= N);
+    if (swiglu_bwd) {
+      // columns gc .. gc+31 of the activation map to columns 2gc .. 2gc+63 of gate|up: [g 0-15 | u 0-15 | g 16-31 | u 16-31]
+      const __nv_bfloat16* gu = H + static_cast<size_t>(gr) * ldh + 2 * gc;
+      __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<size_t>(gr) * ldc + 2 * gc;
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        uint4 gv[2], uv[2], dg[2], du[2];
+        gv[0] = *reinterpret_cast<const uint4*>(gu + blk * 32);
+        gv[1] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 8);
+        uv[0] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 16);
+        uv[1] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 24);
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(gv);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(uv);
+        uint32_t* dgp = reinterpret_cast<uint32_t*>(dg);
+        uint32_t* dup = reinterpret_cast<uint32_t*>(du);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 g2 = __bfloat1622float2(gp[e]), u2 = __bfloat1622float2(up[e]);
+          const float d0 = __uint_as_float(acc[blk * 16 + 2 * e]), d1 = __uint_as_float(acc[blk * 16 + 2 * e + 1]);
+          const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+          dgp[e] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+          dup[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+        }
+        *reinterpret_cast<uint4*>(dgu + blk * 32) = dg[0];
+        *reinterpret_cast<uint4*>(dgu + blk * 32 + 8) = dg[1];
+        *reinterpret_cast<uint4*>(dgu + blk * 32 + 16) = du[0];
+        *reinterpret_cast<uint4*>(dgu + blk * 32 + 24) = du[1];
+      }
+      return;
+    }
     if (bias) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)

@@ -61,7 +61,7 @@ ARTB_EXPORT int artb_pick_bn(int M, int N, int ctas) {
 // C[M,N] = A[M,K] B[N,K]^T (+ A2[M,K2] B2[N,K2]^T), bf16 inputs, fp32 accumulation in TMEM.
 //   A, B, A2, B2 : bf16 row-major, leading dimensions in elements (multiples of 8), 16-B aligned
 //   K2 == 0      : no extra-K operand (A2/B2 ignored)
-//   epilogue     : GemmEpilogue; R (bf16 [M,res_cols]) is added for EPI_BF16_RESID and, when given, for EPI_SWIGLU;
+//   epilogue     : GemmEpilogue (EPI_SWIGLU_BWD: H = forward gate|up [M,2N] input, C = d(gate|up) [M,2N] output); R (bf16 [M,res_cols]) is added for EPI_BF16_RESID and, when given, for EPI_SWIGLU;
 //                  H (bf16 [M,N/2]) receives silu(gate)*up for EPI_SWIGLU;  res_cols 0 = all N columns
 //   bias         : optional fp32 [N], added to the accumulator before any other epilogue step
 //   bn           : tile width 64 / 128 / 192 / 224 / 256 (0 = choose, see artb_pick_bn)
@@ -78,10 +78,10 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
   if (reinterpret_cast<uintptr_t>(C) & 15) return ERR_BAD_ALIGN;
   if (epilogue == EPI_F32 ? (ldc & 3) : (ldc & 7)) return ERR_BAD_ALIGN;
   if (epilogue != EPI_BF16_RESID && epilogue != EPI_SWIGLU) R = nullptr;
-  if (epilogue != EPI_SWIGLU) H = nullptr;
+  if (epilogue != EPI_SWIGLU && epilogue != EPI_SWIGLU_BWD) H = nullptr;
   if (epilogue == EPI_BF16_RESID && (!R || (ldr & 7) || (reinterpret_cast<uintptr_t>(R) & 15)))
     return ERR_BAD_ALIGN;
-  if (epilogue == EPI_SWIGLU && (!H || (ldh & 7) || (N & 31) || (reinterpret_cast<uintptr_t>(H) & 15)))
+  if ((epilogue == EPI_SWIGLU || epilogue == EPI_SWIGLU_BWD) && (!H || (ldh & 7) || (N & 31) || (reinterpret_cast<uintptr_t>(H) & 15)))
     return ERR_BAD_ALIGN;
   if (bn == 0) bn = artb_pick_bn(M, N, max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count());
   if (bn != 64 && bn != 128 && bn != 192 && bn != 224 && bn != 256) return ERR_BAD_SHAPE;
@@ -104,7 +104,8 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
   {                                                                                               \
     EpiStore<BN_> epi{C, reinterpret_cast<const __nv_bfloat16*>(R),                               \
                       reinterpret_cast<__nv_bfloat16*>(H), bias, ldc, ldr, ldh, M, N,              \
-                      epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N};                  \
+                      epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,                   \
+                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};                                        \
     return launch_gemm<BN_, ST_>(tA, tB, tA2, tB2, kb_main, kb_extra, M, N, epi, status, max_ctas, \
                                  stream);                                                         \
   }

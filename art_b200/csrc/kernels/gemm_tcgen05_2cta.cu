@@ -40,7 +40,8 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
   if (max_clusters > 0 && max_clusters < cap) cap = max_clusters;
   if (clusters > cap) clusters = cap;
   EpiStore<BN2> epi{C, reinterpret_cast<const __nv_bfloat16*>(R), reinterpret_cast<__nv_bfloat16*>(H), bias, ldc, ldr,
-                      ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N};
+                      ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
+                     epilogue == EPI_SWIGLU_BWD ? 1 : 0};
   kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, m_tiles2, n_tiles, epi,
                                                         status);
   return static_cast<int>(cudaGetLastError());
@@ -59,9 +60,9 @@ ARTB_EXPORT int artb_gemm_bf16_tn_2cta(const void* A, int lda, const void* B, in
   if (reinterpret_cast<uintptr_t>(C) & 15) return ERR_BAD_ALIGN;
   if (epilogue == EPI_F32 ? (ldc & 3) : (ldc & 7)) return ERR_BAD_ALIGN;
   if (epilogue != EPI_BF16_RESID && epilogue != EPI_SWIGLU) R = nullptr;
-  if (epilogue != EPI_SWIGLU) H = nullptr;
+  if (epilogue != EPI_SWIGLU && epilogue != EPI_SWIGLU_BWD) H = nullptr;
   if (epilogue == EPI_BF16_RESID && (!R || (ldr & 7) || (reinterpret_cast<uintptr_t>(R) & 15))) return ERR_BAD_ALIGN;
-  if (epilogue == EPI_SWIGLU && (!H || (ldh & 7) || (N & 31) || (reinterpret_cast<uintptr_t>(H) & 15)))
+  if ((epilogue == EPI_SWIGLU || epilogue == EPI_SWIGLU_BWD) && (!H || (ldh & 7) || (N & 31) || (reinterpret_cast<uintptr_t>(H) & 15)))
     return ERR_BAD_ALIGN;
   // 224-wide cluster tiles waste less of the last wave for some N (3584: 6.92 waves instead of 6.05) but
   // measured no faster under the power cap; they are kept for explicit requests (max_clusters < 0).

@@ -28,7 +28,7 @@ import torch
 
 from ..ops import attention as attn_ops
 from ..ops import elementwise as ew
-from ..ops.gemm import gemm_tn
+from ..ops.gemm import gemm_tn, skinny_gemm
 from .config import ModelConfig
 from .weights import LoraConfig, lora_key
 
@@ -98,7 +98,7 @@ class LoraLinear:
     # forward: returns (y, T) ; T is saved for the B-gradient
     def forward(self, x: torch.Tensor, use_lora: bool = True, residual=None, swiglu_out=None, out=None):
         if self.active and use_lora:
-            T = gemm_tn(x, self.A_cat)
+            T = skinny_gemm(x, self.A_cat)
             y = gemm_tn(x, self.W, a2=T, b2=self.B_cat, residual=residual, swiglu_out=swiglu_out, bias=self.bias, out=out)
             return y, T
         y = gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out, bias=self.bias, out=out)
@@ -106,17 +106,18 @@ class LoraLinear:
 
     # backward: dx, and accumulates dA_cat / dB_cat
     def backward(self, dy: torch.Tensor, x: torch.Tensor, T: torch.Tensor | None, need_dx: bool = True,
-                 dx_residual: torch.Tensor | None = None) -> torch.Tensor | None:
+                 dx_residual: torch.Tensor | None = None, swiglu_gu: torch.Tensor | None = None) -> torch.Tensor | None:
+        """``swiglu_gu``: this linear's input was ``silu(gate) * up``; return d(gate|up) instead of d(input)."""
         if self.active and T is not None:
-            dT = gemm_tn(dy, self.B_catT)                       # [M, kpad]
+            dT = skinny_gemm(dy, self.B_catT)                   # [M, kpad]
             # LoRA factor gradients: skinny contractions over the token dimension
             lora_wgrad(self.dA_acc, x, dT)     # dA_cat^T [K, kpad] += X^T dT
             lora_wgrad(self.dB_acc, dy, T)     # dB_cat   [N, kpad] += dY^T T
             if need_dx:
-                return gemm_tn(dy, self.WT, a2=dT, b2=self.A_catT, residual=dx_residual)
+                return gemm_tn(dy, self.WT, a2=dT, b2=self.A_catT, residual=dx_residual, swiglu_bwd_gu=swiglu_gu)
             return None
         if need_dx:
-            return gemm_tn(dy, self.WT, residual=dx_residual)
+            return gemm_tn(dy, self.WT, residual=dx_residual, swiglu_bwd_gu=swiglu_gu)
         return None
 
 
@@ -214,9 +215,8 @@ class DenseMLP:
         return x3, (DenseSaved(h2, T_gu, gu, hact, T_d) if save else None)
 
     def backward(self, dx, sv: DenseSaved):
-        dhact = self.down.backward(dx, sv.hact, sv.T_d)
-        dgu = ew.swiglu_bwd(dhact, sv.gu)
-        del dhact
+        # the SwiGLU backward sits in the epilogue of the down-projection's data-gradient GEMM
+        dgu = self.down.backward(dx, sv.hact, sv.T_d, swiglu_gu=sv.gu)
         return self.gu.backward(dgu, sv.h2, sv.T_gu)
 
 

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-EPI_BF16, EPI_BF16_RESID, EPI_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_BF16, EPI_BF16_RESID, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2, 3, 4
 _configured = False
 _configured2 = False
 TWO_CTA_DEFAULT = os.environ.get("ARTB_GEMM_2CTA", "1") == "1"
@@ -52,12 +52,16 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, swiglu_out: torch.Tensor | None = None,
             bias: torch.Tensor | None = None, res_cols: int = 0,
             out_dtype: torch.dtype = torch.bfloat16, bn: int = 0, max_ctas: int = 0,
-            two_cta: bool | None = None) -> torch.Tensor:
+            two_cta: bool | None = None, swiglu_bwd_gu: torch.Tensor | None = None) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K].T (+ a2[M,K2] @ b2[N,K2].T) (+ residual)``.
 
     ``swiglu_out`` ([M, N/2] bf16) selects the SwiGLU epilogue: ``b``'s rows must be
     interleaved in blocks of 16 (gate rows, then the matching up rows); ``out`` receives
     the pre-activation and ``swiglu_out`` receives ``silu(gate) * up``.
+
+    ``swiglu_bwd_gu`` ([M, 2N] bf16, the forward's interleaved gate|up pre-activations) selects the fused
+    SwiGLU-backward epilogue: the product is taken as ``d(silu(gate) * up)`` and ``out`` ([M, 2N]) receives
+    ``d(gate|up)`` in the same interleaved layout; the activation gradient itself is never written.
     """
     _check2d(a, "a")
     _check2d(b, "b")
@@ -72,7 +76,15 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         K2 = a2.shape[1]
         if a2.shape[0] != M or b2.shape[0] != N or b2.shape[1] != K2:
             raise ValueError("extra-K operands must be [M,K2] and [N,K2]")
-    if swiglu_out is not None:
+    if swiglu_bwd_gu is not None:
+        _check2d(swiglu_bwd_gu, "swiglu_bwd_gu")
+        if tuple(swiglu_bwd_gu.shape) != (M, 2 * N) or N % 32:
+            raise ValueError("swiglu_bwd_gu must be [M, 2N] with N a multiple of 32")
+        if out is None:
+            out = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=a.device)
+        epi = EPI_SWIGLU_BWD
+        swiglu_out = swiglu_bwd_gu          # travels in the H slot of the C entry point
+    elif swiglu_out is not None:
         epi = EPI_SWIGLU
     elif residual is not None:
         epi = EPI_BF16_RESID
@@ -82,7 +94,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, a2: torch.Tensor | None = None,
         epi = EPI_BF16
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=a.device)
-    if out.stride(1) != 1 or tuple(out.shape) != (M, N):
+    if out.stride(1) != 1 or tuple(out.shape) != (M, 2 * N if epi == EPI_SWIGLU_BWD else N):
         raise ValueError("out must be [M,N] with unit inner stride")
     if residual is not None:
         _check2d(residual, "residual")
@@ -174,3 +186,28 @@ def plan_small_m(M: int, N: int, K: int, sms: int = 148) -> tuple[int, int]:
         return bn, 1
     splits = max(1, min((sms + tiles - 1) // tiles, max(1, kb // 4)))
     return bn, splits
+
+
+_skinny_ws: dict = {}
+SKINNY_SPLITS = int(os.environ.get("ARTB_SKINNY_SPLITS", "4"))
+
+
+def skinny_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T`` for N <= 64 and large M (the LoRA shrink ``X A^T`` and ``dY B``).
+
+    One N tile means only ``M / 128`` CTAs in the plain kernel (64 for 8192 tokens), each streaming all of K, so the
+    op is latency-bound; here K is split ``SKINNY_SPLITS`` ways (fp32 atomics into a small zeroed workspace) so the
+    whole machine streams ``a`` once, and a finalize pass converts to bf16 and re-zeroes the workspace.
+    """
+    M, K = a.shape
+    N = b.shape[0]
+    if N > 64 or M < 2048 or K < 1024 or SKINNY_SPLITS <= 1:
+        return gemm_tn(a, b, out=out)
+    key = (a.device.index, M, N)
+    ws = _skinny_ws.get(key)
+    if ws is None:
+        ws = _skinny_ws[key] = torch.zeros((M, 64), dtype=torch.float32, device=a.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    gemm_splitk_(ws, a, b, 64, SKINNY_SPLITS)
+    return splitk_finalize(ws, out)

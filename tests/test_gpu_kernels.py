@@ -69,6 +69,14 @@ def test_gemm_swiglu_epilogue():
     (torch.nn.functional.silu(g32) * u32).backward(dh.float())
     dg, du = ew.deinterleave_gate_up(ew.swiglu_bwd(dh, gu))
     assert rel_err(dg, g32.grad) < 1e-2 and rel_err(du, u32.grad) < 1e-2
+    # the same backward fused into the epilogue of the GEMM that produces dh = dy @ Wd
+    for Mf, two in ((M, False), (1024, True)):
+        xf = bf(Mf, K, seed=11)
+        guf = gemm_tn(xf, ew.interleave_gate_up(wg, wu))
+        dy, wd = bf(Mf, 128, seed=5), bf(128, F, scale=0.1, seed=6)       # down-proj weight [d, F]; dh = dy @ wd
+        dh_ref = gemm_tn(dy, wd.t().contiguous())
+        fused = gemm_tn(dy, wd.t().contiguous(), swiglu_bwd_gu=guf, two_cta=two)
+        assert rel_err(fused, ew.swiglu_bwd(dh_ref, guf)) < 1e-2
 
 
 @pytest.mark.parametrize("M,D", [(64, 128), (300, 3584), (17, 5120)])
