@@ -508,3 +508,89 @@ def test_trainer_context_tensor_expert_parallel(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "PAR_TRAINER_OK" in res.stdout
+
+
+DECODE_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.ops import _lib
+from art_b200.parallel.tp_decode import DecodeAllReduce, LoraHandoff
+
+def rnd(shape, seed, scale=1.0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return (torch.randn(shape, device=dev, generator=g) * scale).to(torch.bfloat16)
+
+ar = DecodeAllReduce(dev, None, 256, 5120)
+for it, (M, N, Kp) in enumerate(((256, 5120, 3456), (64, 1024, 640), (200, 5120, 3456), (256, 5120, 3456), (1, 512, 256))):
+    x, w = rnd((M, Kp), 10 * it + rank), rnd((N, Kp), 100 + 10 * it + rank, 0.03)
+    bias = torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(7 + it))
+    res = rnd((M, N), 500 + it)
+    out = ar.gemm_allreduce(x, w, bias=bias, residual=res)
+    ref = x.float() @ w.float().t()
+    dist.all_reduce(ref)
+    ref = ref + bias + res.float()
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    e = ((out.float() - ref).norm() / ref.norm()).item()
+    assert e < 1e-2, ("gemm_allreduce", it, e)
+def timed(fn, iters=50, warm=5):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warm): fn()
+    dist.barrier(); torch.cuda.synchronize(); e0.record()
+    for _ in range(iters): fn()
+    e1.record(); torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+M, N, Kp = 256, 5120, 27648 // world
+x, w = rnd((M, Kp), 1 + rank), rnd((N, Kp), 2 + rank, 0.02)
+t_f = timed(lambda: ar.gemm_allreduce(x, w))
+def unfused():
+    y = x @ w.t(); dist.all_reduce(y); return y
+t_u = timed(unfused)
+t_g = timed(lambda: x @ w.t())
+ar.close()
+
+# LoRA hand-off: rank 0 (trainer) -> everyone else (engine ranks)
+n = 20_185_088
+ho = LoraHandoff(dev, None, n)
+for it in range(3):
+    flat = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(900 + it))   # same on all ranks
+    if rank == 0:
+        ho.push(flat)
+        ho.epoch += 0
+    else:
+        got = ho.receive(0, n)
+        torch.cuda.synchronize(); _lib.check_status(dev)
+        assert torch.equal(got, flat), "hand-off payload differs"
+    dist.barrier()
+e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+torch.cuda.synchronize(); dist.barrier(); e0.record()
+if rank == 0: ho.push(flat)
+else: ho.receive(0, n)
+e1.record(); torch.cuda.synchronize()
+t_h = torch.tensor([e0.elapsed_time(e1)], device=dev); dist.all_reduce(t_h, op=dist.ReduceOp.MAX)
+torch.cuda.synchronize(); _lib.check_status(dev)
+if rank == 0:
+    print(f"DECODE_TP_OK world={world} M={M} N={N} K/rank={Kp} fused_gemm_allreduce_ms={t_f:.4f} cublas+nccl_ms={t_u:.4f} "
+          f"cublas_only_ms={t_g:.4f} lora_handoff_81MB_ms={t_h.item():.3f}")
+ho.close()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_decode_gemm_allreduce_and_lora_handoff(tmp_path):
+    world = 1
+    while world * 2 <= min(torch.cuda.device_count(), 8):
+        world *= 2
+    script = tmp_path / "decode_worker.py"
+    script.write_text(DECODE_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29527", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "DECODE_TP_OK" in res.stdout
