@@ -79,7 +79,8 @@ def kernel_sources() -> list[Path]:
 
 
 def runtime_sources() -> list[Path]:
-    return sorted((CSRC / "engine").glob("*.cpp"))
+    # *_selftest.cpp are stand-alone sanitizer test programs (they define main), not part of the library
+    return sorted(p for p in (CSRC / "engine").glob("*.cpp") if not p.name.endswith("_selftest.cpp"))
 
 
 def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> None:

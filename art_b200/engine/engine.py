@@ -16,6 +16,7 @@ from __future__ import annotations
 import asyncio
 import itertools
 import threading
+import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -103,6 +104,7 @@ class Engine:
         self.adapter_version = [0] * max_loras
         self.max_loras = max_loras
         self.stats = EngineStats()
+        self._trace, self._trace_steps = None, 0
         self._lock = threading.Lock()
         self._wake = threading.Event()
         self._run_gate = threading.Event()
@@ -388,6 +390,27 @@ class Engine:
                 self._emit(s, t, lps[k][i])
         return True
 
+    def _traced_step(self) -> bool:
+        """``step()``; with ``ARTB_TRACE_FILE`` set every iteration becomes a span of a Chrome trace plus counters
+        (running / waiting sequences, free KV blocks), saved every 200 steps and on shutdown."""
+        path = os.environ.get("ARTB_TRACE_FILE")
+        if not path:
+            return self.step()
+        if self._trace is None:
+            from ..utils.profiling import ChromeTrace
+
+            self._trace = ChromeTrace("art_b200.engine")
+        n_run, n_wait = len(self.running), len(self.waiting)
+        with self._trace.span("engine.step", cat="scheduler", running=n_run, waiting=n_wait):
+            worked = self.step()
+        if worked:
+            self._trace.counter("sequences", running=len(self.running), waiting=len(self.waiting))
+            self._trace.counter("kv_blocks", free=self.bm.num_free)
+            self._trace_steps += 1
+            if self._trace_steps % 200 == 0:
+                self._trace.save(path)
+        return worked
+
     def _loop(self) -> None:
         try:
             while not self._stop:
@@ -395,7 +418,7 @@ class Engine:
                 with self._step_lock:
                     if self._stop or not self._run_gate.is_set():
                         continue
-                    worked = self.step()
+                    worked = self._traced_step()
                 if not worked:
                     self._wake.wait(timeout=0.05)
                     self._wake.clear()

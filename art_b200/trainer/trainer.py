@@ -23,6 +23,7 @@ weight decay 0.1 (``src/art/dev/model.py:69-85``, ``src/art/local/train.py:34-15
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Iterator
 
@@ -66,6 +67,10 @@ class Trainer:
         self._cp_cache: dict = {}
         self._cp_sync = None
         self.tp = None
+        # per-phase CUDA-event timing + NVTX ranges of every step (ARTB_PHASE_TIMING=1); read with phase_summary()
+        from ..utils.profiling import PhaseTimer
+
+        self.timer = PhaseTimer(self.device, enabled=os.environ.get("ARTB_PHASE_TIMING") == "1")
         if self.impl == "native":
             from ..models.native import NativeDecoder
 
@@ -225,7 +230,8 @@ class Trainer:
                 sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
             else:
                 sel = sel_all_d[lo:hi] - r0 * S
-            hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S, cp=cp)
+            with self.timer.phase("forward"):
+                hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S, cp=cp)
             if sel.numel() == 0:
                 # context parallel: this rank's shard holds no trainable token, but its peers still need its
                 # K/V in the forward passes and its (zero) dK/dV in the backward pass
@@ -245,13 +251,15 @@ class Trainer:
                 part, _ = lpl.partials(rc, self.model.lm_head, tgt_c)
                 ref_c = lpl.grpo_tokens(part).logprobs
                 del ref_hidden, rc, part
-            res = lpl.forward(hc, self.model.lm_head, tgt_c, old_c, adv_c, w_c, ref_c, hyper.epsilon, eps_hi,
-                              hyper.beta, accum)
-            dhc = lpl.backward(hc, self.model.lm_head, self.model.lm_head_t, tgt_c, res.lse, res.coef)
-            dhidden = torch.zeros_like(hidden)
-            ew.scatter_rows_(dhc, sel, dhidden)
-            del hc, dhc
-            self.model.backward(dhidden, saved, final, pos)
+            with self.timer.phase("lm_head_loss"):
+                res = lpl.forward(hc, self.model.lm_head, tgt_c, old_c, adv_c, w_c, ref_c, hyper.epsilon, eps_hi,
+                                  hyper.beta, accum)
+                dhc = lpl.backward(hc, self.model.lm_head, self.model.lm_head_t, tgt_c, res.lse, res.coef)
+                dhidden = torch.zeros_like(hidden)
+                ew.scatter_rows_(dhc, sel, dhidden)
+                del hc, dhc
+            with self.timer.phase("backward"):
+                self.model.backward(dhidden, saved, final, pos)
         self.model.export_grads()
         acc = accum  # read back together with the grad norm below
         out = self._finish_step(None, hyper, device_accum=acc)
@@ -294,9 +302,15 @@ class Trainer:
         elif self.grad_sync is not None:
             self.grad_sync(self.flat.grads)
 
+    def phase_summary(self, group=None) -> dict[str, float]:
+        """Milliseconds per phase (forward, lm_head_loss, backward, grad_sync, optimizer) since the last call."""
+        return self.timer.summary(group)
+
     def _finish_step(self, totals: dict | None, hyper: TrainHyper, device_accum: torch.Tensor | None = None):
-        self._sync_grads(device_accum)
-        gnorm = self.opt.step(hyper.learning_rate)
+        with self.timer.phase("grad_sync"):
+            self._sync_grads(device_accum)
+        with self.timer.phase("optimizer"):
+            gnorm = self.opt.step(hyper.learning_rate)
         if device_accum is not None:
             vals = torch.cat([device_accum[:2], gnorm.reshape(1)]).tolist()  # one D2H read per step
             pl, kl, gn = vals

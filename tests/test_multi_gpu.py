@@ -594,3 +594,57 @@ def test_decode_gemm_allreduce_and_lora_handoff(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "DECODE_TP_OK" in res.stdout
+
+
+FAILURE_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.ops import _lib
+from art_b200.ops._lib import KernelStatusError
+from art_b200.parallel.symm_mem import FusedGradAllReduce
+
+# A peer that never shows up: rank 1 skips one collective (host-side fault, nothing of rank 1 is in flight).  Rank 0's
+# kernel gives up after its bounded wait, records a status code and returns; the context stays usable.
+ar = FusedGradAllReduce(dev, world, wait_ms=300)
+x = torch.ones(4096, device=dev)
+ar(x.clone())                                   # healthy call first
+torch.cuda.synchronize(); _lib.check_status(dev)
+dist.barrier()
+timed_out = False
+if rank == 0:
+    y = x.clone()
+    ar(y)                                       # rank 1 does not call
+    torch.cuda.synchronize()
+    try:
+        _lib.check_status(dev)
+    except KernelStatusError as e:
+        timed_out = "peer" in str(e).lower() or e.code == 5
+    assert timed_out, "the bounded wait should have reported a peer timeout"
+    z = torch.arange(8, device=dev).float().sum().item()          # the CUDA context still works
+    assert z == 28.0
+dist.barrier()
+# recovery: both ranks rebuild the collective (fresh symmetric buffer, epochs in step again) and carry on
+ar = FusedGradAllReduce(dev, world, wait_ms=2000)
+v = torch.full((4096,), float(rank + 1), device=dev)
+ar(v)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert torch.allclose(v, torch.full_like(v, sum(range(1, world + 1)) / world))
+if rank == 0: print("FAILURE_DETECT_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_peer_timeout_is_reported_and_recoverable(tmp_path):
+    script = tmp_path / "failure_worker.py"
+    script.write_text(FAILURE_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29529", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "FAILURE_DETECT_OK" in res.stdout

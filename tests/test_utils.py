@@ -116,3 +116,54 @@ def test_deploy_model_reuses_running_job(monkeypatch, tmp_path):
     job = asyncio.run(dm.deploy_model(dm.LoRADeploymentProvider.TOGETHER, model, step=2, pull_s3=False, art_path=str(tmp_path)))
     assert job.status == dm.LoRADeploymentJobStatus.COMPLETE and job.job_id == "j1"
     assert dm.convert_together_job_status("Retry Queued") == dm.LoRADeploymentJobStatus.QUEUED
+
+
+def test_phase_timer_and_chrome_trace(tmp_path):
+    import json
+    import time
+
+    from art_b200.utils.profiling import ChromeTrace, PhaseTimer, nvtx_range
+
+    t = PhaseTimer("cpu")
+    with t.phase("a"):
+        time.sleep(0.01)
+    with t.phase("a"):
+        time.sleep(0.01)
+    with t.phase("b"), nvtx_range("inner"):
+        pass
+    rec = t.dump_jsonl(str(tmp_path / "phases.jsonl"), extra={"step": 3})
+    assert rec["step"] == 3 and rec["phases_ms"]["a"] >= 15 and "b" in rec["phases_ms"]
+    assert t.summary() == {}                                   # reset after the dump
+    off = PhaseTimer("cpu", enabled=False)
+    with off.phase("x"):
+        pass
+    assert off.summary() == {}
+    tr = ChromeTrace("test")
+    with tr.span("engine.step", running=2):
+        tr.counter("sequences", running=2, waiting=1)
+    tr.instant("preempt", seq=7)
+    tr.save(str(tmp_path / "trace.json"))
+    ev = json.load(open(tmp_path / "trace.json"))["traceEvents"]
+    assert {e["ph"] for e in ev} == {"M", "X", "C", "i"} and any(e.get("dur", 0) >= 0 and e["name"] == "engine.step" for e in ev)
+
+
+def test_truncated_adapter_checkpoint_fails_cleanly(tmp_path):
+    """A checkpoint cut short by a crash must raise on load (and never be mistaken for a usable adapter)."""
+    import pytest
+    import torch
+
+    from art_b200.models import peft_io
+    from art_b200.models.config import PRESETS
+    from art_b200.models.weights import LoraConfig, init_lora
+
+    cfg, lcfg = PRESETS["tiny"], LoraConfig()
+    lora = init_lora(cfg, lcfg)
+    d = tmp_path / "0001"
+    peft_io.save_adapter(str(d), lora, lcfg, "tiny")
+    back, lcfg_back = peft_io.load_adapter(str(d))
+    assert lcfg_back.r == lcfg.r and set(back) == set(lora) and all(torch.equal(back[k], lora[k]) for k in lora)
+    f = d / "adapter_model.safetensors"
+    raw = f.read_bytes()
+    f.write_bytes(raw[: len(raw) // 2])
+    with pytest.raises(Exception):
+        peft_io.load_adapter(str(d))
