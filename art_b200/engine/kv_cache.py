@@ -100,19 +100,103 @@ class BlockManager:
         return {"prefix_queries": out[0], "prefix_hits": out[1], "free_blocks": out[2], "cached_free_blocks": out[3]}
 
 
+class _DevMem:
+    """``__cuda_array_interface__`` carrier so torch can view arena memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class VmmArena:
+    """Reserved virtual address range whose physical backing can be mapped / unmapped (``csrc/kernels/kv_arena.cu``)."""
+
+    def __init__(self, nbytes: int, device: torch.device, chunk_bytes: int = 64 << 20):
+        lib = _lib.kernels()
+        vp, sz = ctypes.c_void_p, ctypes.c_size_t
+        lib.artb_arena_create.argtypes, lib.artb_arena_create.restype = [sz, sz], vp
+        lib.artb_arena_base.argtypes, lib.artb_arena_base.restype = [vp], ctypes.c_uint64
+        lib.artb_arena_reserved.argtypes, lib.artb_arena_reserved.restype = [vp], sz
+        lib.artb_arena_mapped_bytes.argtypes, lib.artb_arena_mapped_bytes.restype = [vp], sz
+        lib.artb_arena_map.argtypes, lib.artb_arena_map.restype = [vp, sz, sz], ctypes.c_int
+        lib.artb_arena_unmap.argtypes, lib.artb_arena_unmap.restype = [vp, sz, sz], ctypes.c_int
+        lib.artb_arena_destroy.argtypes = [vp]
+        self._lib, self.device = lib, torch.device(device)
+        with torch.cuda.device(self.device):
+            self._h = lib.artb_arena_create(nbytes, chunk_bytes)
+        if not self._h:
+            raise RuntimeError("virtual-memory arena unavailable on this device / driver")
+        self.base = int(lib.artb_arena_base(self._h))
+        self.reserved = int(lib.artb_arena_reserved(self._h))
+
+    @property
+    def mapped_bytes(self) -> int:
+        return int(self._lib.artb_arena_mapped_bytes(self._h))
+
+    def map(self, offset: int = 0, nbytes: int | None = None) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check_rc(self._lib.artb_arena_map(self._h, offset, self.reserved - offset if nbytes is None else nbytes),
+                          "arena_map")
+
+    def unmap(self, offset: int = 0, nbytes: int | None = None) -> None:
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            _lib.check_rc(self._lib.artb_arena_unmap(self._h, offset, self.reserved - offset if nbytes is None else nbytes),
+                          "arena_unmap")
+
+    def tensor(self, offset: int, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if offset + nbytes > self.reserved:
+            raise ValueError("view outside the arena")
+        raw = torch.as_tensor(_DevMem(self.base + offset, nbytes), device=self.device)
+        return raw.view(dtype).view(*shape)
+
+    def close(self) -> None:
+        h, self._h = self._h, None
+        if h:
+            self._lib.artb_arena_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class KVCache:
-    """Device tensors of the paged cache, one (k, v) pair per layer."""
+    """Device tensors of the paged cache, one (k, v) pair per layer.
+
+    With ``use_arena`` the tensors live in a :class:`VmmArena`: ``discard`` / ``offload`` hand the physical memory back
+    to the driver while every tensor keeps its address, so block tables, captured CUDA graphs and kernel arguments that
+    point into the cache stay valid across a sleep / wake cycle.
+    """
 
     def __init__(self, num_layers: int, num_blocks: int, block_size: int, num_kv_heads: int, head_dim: int,
-                 device: torch.device, dtype: torch.dtype = torch.bfloat16):
+                 device: torch.device, dtype: torch.dtype = torch.bfloat16, use_arena: bool = False):
         self.shape = (num_blocks, block_size, num_kv_heads, head_dim)
         self.device, self.dtype, self.num_layers = device, dtype, num_layers
         self.k: list[torch.Tensor] = []
         self.v: list[torch.Tensor] = []
         self._host: list[tuple[torch.Tensor, torch.Tensor]] | None = None
+        self.arena: VmmArena | None = None
+        self._views: tuple[list[torch.Tensor], list[torch.Tensor]] | None = None
+        if use_arena and torch.device(device).type == "cuda":
+            per = num_blocks * block_size * num_kv_heads * head_dim * torch.empty((), dtype=dtype).element_size()
+            per = (per + 255) // 256 * 256
+            self.arena = VmmArena(2 * num_layers * per, device)
+            self._views = ([self.arena.tensor((2 * i) * per, self.shape, dtype) for i in range(num_layers)],
+                           [self.arena.tensor((2 * i + 1) * per, self.shape, dtype) for i in range(num_layers)])
         self._allocate()
 
     def _allocate(self) -> None:
+        if self.arena is not None:
+            self.arena.map()
+            self.k, self.v = list(self._views[0]), list(self._views[1])
+            for t in self.k + self.v:
+                t.zero_()
+            return
         self.k = [torch.zeros(self.shape, dtype=self.dtype, device=self.device) for _ in range(self.num_layers)]
         self.v = [torch.zeros(self.shape, dtype=self.dtype, device=self.device) for _ in range(self.num_layers)]
 
@@ -127,7 +211,9 @@ class KVCache:
     def discard(self) -> None:
         """Sleep level 2: free the device memory, contents are lost."""
         self.k, self.v, self._host = [], [], None
-        if self.device.type == "cuda":
+        if self.arena is not None:
+            self.arena.unmap()
+        elif self.device.type == "cuda":
             torch.cuda.empty_cache()
 
     def offload(self) -> None:
@@ -137,7 +223,9 @@ class KVCache:
                        v.to("cpu", non_blocking=False).pin_memory() if pin else v.clone())
                       for k, v in zip(self.k, self.v)]
         self.k, self.v = [], []
-        if pin:
+        if self.arena is not None:
+            self.arena.unmap()
+        elif pin:
             torch.cuda.empty_cache()
 
     def restore(self) -> None:
@@ -145,6 +233,14 @@ class KVCache:
             return
         if self._host is None:
             self._allocate()
+            return
+        if self.arena is not None:
+            self.arena.map()
+            self.k, self.v = list(self._views[0]), list(self._views[1])
+            for (hk, hv), k, v in zip(self._host, self.k, self.v):
+                k.copy_(hk, non_blocking=True)
+                v.copy_(hv, non_blocking=True)
+            self._host = None
             return
         self.k = [k.to(self.device, non_blocking=True) for k, _ in self._host]
         self.v = [v.to(self.device, non_blocking=True) for _, v in self._host]

@@ -263,3 +263,29 @@ def test_native_engine_matches_reference_runner():
     import asyncio
     lps = asyncio.run(nat.score(prompts[0], again.output_ids[:3], "a"))
     assert all(abs(x - y) < 0.05 for x, y in zip(lps, again.logprobs[:3]))
+
+
+def test_kv_cache_vmm_arena_sleep_wake_keeps_addresses():
+    from art_b200.engine.kv_cache import KVCache
+
+    kv = KVCache(num_layers=2, num_blocks=4096, block_size=16, num_kv_heads=2, head_dim=128, device=torch.device(DEV),
+                 use_arena=True)                                  # 2 * 2 * 32 MiB = 128 MiB of cache
+    ptrs = [t.data_ptr() for t in kv.k + kv.v]
+    kv.k[1][5].fill_(3.0)
+    kv.v[0][7].fill_(-2.0)
+    torch.cuda.synchronize()
+    free_resident = torch.cuda.mem_get_info()[0]
+    mapped = kv.arena.mapped_bytes
+    assert mapped >= 128 << 20
+    kv.offload()                                                  # sleep level 1: contents to pinned host memory
+    assert not kv.resident and kv.arena.mapped_bytes == 0
+    assert torch.cuda.mem_get_info()[0] >= free_resident + mapped - (8 << 20)   # the physical memory really went back
+    kv.restore()
+    assert [t.data_ptr() for t in kv.k + kv.v] == ptrs            # same addresses after the wake-up
+    torch.cuda.synchronize()
+    assert float(kv.k[1][5].float().mean()) == 3.0 and float(kv.v[0][7].float().mean()) == -2.0
+    kv.discard()                                                  # sleep level 2: contents dropped
+    assert kv.arena.mapped_bytes == 0
+    kv.restore()
+    torch.cuda.synchronize()
+    assert [t.data_ptr() for t in kv.k + kv.v] == ptrs and float(kv.k[1].float().abs().sum()) == 0.0
