@@ -224,9 +224,15 @@ class NativeDecoder:
     """Qwen2/Llama-style dense and Qwen3-MoE-style sparse decoders on the native kernels (LoRA-only training)."""
 
     def __init__(self, cfg: ModelConfig, base: dict[str, torch.Tensor], lora_cfg: LoraConfig,
-                 lora_init: dict[str, torch.Tensor], device="cuda", attn_impl: str = "native", ep=None):
+                 lora_init: dict[str, torch.Tensor], device="cuda", attn_impl: str = "native", ep=None,
+                 layer_range: range | None = None):
         self.cfg, self.lora_cfg, self.attn_impl = cfg, lora_cfg, attn_impl
         self.device = torch.device(device)
+        # pipeline parallelism: this instance holds the decoder layers of `layer_range` only; the first stage embeds,
+        # the last applies the final norm (the LM head / loss stay with the caller, as without pipelining)
+        self.layer_ids = list(layer_range) if layer_range is not None else list(range(cfg.num_layers))
+        self.is_first = self.layer_ids[0] == 0
+        self.is_last = self.layer_ids[-1] == cfg.num_layers - 1
         bf = torch.bfloat16
         dev = self.device
         self.embed = base["model.embed_tokens.weight"].to(dev, bf).contiguous()
@@ -248,7 +254,7 @@ class NativeDecoder:
         fidx = torch.arange(F, device=dev)
         gate_rows = (fidx // 16) * 32 + fidx % 16
         up_rows = gate_rows + 16
-        for i in range(cfg.num_layers):
+        for i in self.layer_ids:
             p = f"model.layers.{i}."
 
             def W(name):
@@ -311,14 +317,15 @@ class NativeDecoder:
 
     # -- forward ----------------------------------------------------------------------------
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, gid: torch.Tensor, pid: torch.Tensor, S: int,
-                use_lora: bool = True, save: bool = True, cp=None) -> tuple[torch.Tensor, list[LayerSaved], dict]:
+                use_lora: bool = True, save: bool = True, cp=None, x_in: torch.Tensor | None = None
+                ) -> tuple[torch.Tensor, list[LayerSaved], dict]:
         """tokens int64 [M], pos/gid/pid int32 [M]; returns final-normed hidden [M,d] and saved state.
 
         With ``cp`` (a :class:`parallel.cp.ContextParallel`) ``tokens`` / ``pos`` hold this rank's shard of
         every packed row while ``gid`` / ``pid`` stay full-length; attention exchanges K/V with the peers.
         """
         cfg = self.cfg
-        x = ew.gather_rows(self.embed, tokens)
+        x = ew.gather_rows(self.embed, tokens) if x_in is None else x_in     # x_in: activations from the previous stage
         plan = cp.make_plan(gid, pid) if cp is not None else attn_ops.make_plan(gid, pid, S, self.attn_impl)
         saved: list[LayerSaved] = []
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
@@ -345,16 +352,20 @@ class NativeDecoder:
                 sv.x2, sv.rstd2, sv.mlp = x2, rstd2, mctx
                 saved.append(sv)
             x = x3
+        if not self.is_last:
+            return x, saved, {"cp": cp}                                        # raw residual stream for the next stage
         hidden, rstd_f = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps)
         return hidden, saved, {"x_last": x, "rstd_f": rstd_f, "cp": cp}
 
     # -- backward ---------------------------------------------------------------------------
-    def backward(self, dhidden: torch.Tensor, saved: list[LayerSaved], final: dict, pos: torch.Tensor) -> None:
-        """Accumulate LoRA gradients given dLoss/dhidden [M,d] (bf16)."""
+    def backward(self, dhidden: torch.Tensor, saved: list[LayerSaved], final: dict, pos: torch.Tensor
+                 ) -> torch.Tensor | None:
+        """Accumulate LoRA gradients given dLoss/dhidden [M,d] (bf16); returns the gradient w.r.t. the stage input
+        (None on the first stage: the embedding is frozen)."""
         cfg = self.cfg
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
-        dx = ew.rmsnorm_bwd(dhidden, final["x_last"], self.final_norm, final["rstd_f"])
-        for li in range(cfg.num_layers - 1, -1, -1):
+        dx = ew.rmsnorm_bwd(dhidden, final["x_last"], self.final_norm, final["rstd_f"]) if self.is_last else dhidden
+        for li in range(len(self.layers) - 1, -1, -1):
             layer, sv = self.layers[li], saved[li]
             # MLP
             dh2 = layer["mlp"].backward(dx, sv.mlp)
@@ -371,9 +382,10 @@ class NativeDecoder:
                 ew.headnorm_bwd_(dqkv, pre, layer["q_norm"], sv.qk_rstd[0], 0, Hq, hd)
                 ew.headnorm_bwd_(dqkv, pre, layer["k_norm"], sv.qk_rstd[1], Hq * hd, Hkv, hd)
                 del pre
-            need_dx = li > 0  # the embedding is frozen: layer 0 needs no input gradient
+            need_dx = li > 0 or not self.is_first  # the embedding is frozen: layer 0 needs no input gradient
             dh1 = layer["qkv"].backward(dqkv, sv.h1, sv.T_qkv, need_dx=need_dx)
             del dqkv
             if need_dx:
                 dx = ew.rmsnorm_bwd(dh1, sv.x, layer["ln1"], sv.rstd1, dres=dx2)
             saved[li] = None  # release this layer's activations
+        return dx if not self.is_first else None

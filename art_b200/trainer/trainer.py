@@ -53,7 +53,7 @@ class Trainer:
                  lora_init: dict[str, torch.Tensor], device: str | torch.device = "cpu", impl: str | None = None,
                  betas=(0.9, 0.99), weight_decay: float = 0.1, max_grad_norm: float = 0.1, adam_eps: float = 1e-8,
                  attn_impl: str = "native", dp_group=None, grad_sync=None, ep=None, cp_group=None, tp_group=None,
-                 tp_tokens: int = 8192):
+                 tp_tokens: int = 8192, pp_group=None):
         self.cfg, self.lora_cfg = cfg, lora_cfg
         self.device = torch.device(device)
         self.impl = impl or ("native" if self.device.type == "cuda" else "reference")
@@ -63,7 +63,9 @@ class Trainer:
         # its own rows; context parallelism (process group): every packed row is sharded over the group
         # tensor parallelism (process group): heads / feed-forward width sharded, activations token-sharded;
         # every micro-batch must hold exactly ``tp_tokens`` tokens
-        self.ep, self.cp_group, self.tp_group = ep, cp_group, tp_group
+        # pipeline parallelism (process group, ranks in group order = stages): contiguous layer ranges per stage,
+        # micro-batches flow through a 1F1B schedule, activations travel over NCCL point-to-point
+        self.ep, self.cp_group, self.tp_group, self.pp_group = ep, cp_group, tp_group, pp_group
         self._cp_cache: dict = {}
         self._cp_sync = None
         self.tp = None
@@ -83,9 +85,16 @@ class Trainer:
                 self.tp = TPContext(self.device, tp_group, tp_tokens // P, k_max=cfg.hidden_size, n_max=cfg.hidden_size)
                 self.model = TPDecoder(cfg, base, lora_cfg, lora_init, self.tp, self.device)
             else:
-                self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl, ep=ep)
+                layer_range = None
+                if pp_group is not None:
+                    import torch.distributed as dist
+                    from ..parallel.pp import split_layers
+
+                    layer_range = split_layers(cfg.num_layers, dist.get_world_size(pp_group))[dist.get_rank(pp_group)]
+                self.model = NativeDecoder(cfg, base, lora_cfg, lora_init, self.device, attn_impl=attn_impl, ep=ep,
+                                           layer_range=layer_range)
             self.flat = self.model.flat
-            sum_group = cp_group if cp_group is not None else tp_group
+            sum_group = cp_group if cp_group is not None else (tp_group if tp_group is not None else pp_group)
             if sum_group is not None:
                 import torch.distributed as dist
                 from ..parallel.symm_mem import FusedGradAllReduce
@@ -134,7 +143,9 @@ class Trainer:
             yield self.step(rows, hyper)
 
     def step(self, rows: dict[str, torch.Tensor], hyper: TrainHyper) -> dict[str, float]:
-        if self.impl == "native":
+        if self.impl == "native" and self.pp_group is not None:
+            m = self._step_native_pp(rows, hyper)
+        elif self.impl == "native":
             m = self._step_native(rows, hyper)
         else:
             m = self._step_reference(rows, hyper)
@@ -263,6 +274,85 @@ class Trainer:
         self.model.export_grads()
         acc = accum  # read back together with the grad norm below
         out = self._finish_step(None, hyper, device_accum=acc)
+        self.model.refresh_lora()
+        return out
+
+    # ---- native, pipeline parallel ---------------------------------------------------------------
+    def _step_native_pp(self, rows: dict[str, torch.Tensor], hyper: TrainHyper) -> dict[str, float]:
+        """One optimizer step with the layers split over the stages of ``pp_group`` (every stage sees the same rows).
+
+        Each micro-batch is one unit of the 1F1B schedule: stage s receives the residual stream [M, d] from stage s-1,
+        runs its layers, sends it on; the last stage applies the final norm, the fused LM-head loss and starts the
+        backward, whose input gradient travels the other way.  Every stage accumulates the LoRA gradients of its own
+        layers; the flat gradient buffers are summed over the group before the (replicated) optimizer step.
+        """
+        from ..ops import elementwise as ew
+        from ..ops import logprob_loss as lpl
+        from ..parallel.pp import PipelineRunner
+
+        dev = self.device
+        R, S = rows["tokens"].shape
+        mask_s = shift_left(rows["assistant_mask"], False)
+        denom = mask_s.sum(dim=1, keepdim=True).float() + 1e-6
+        tok_w = (shift_left(rows["weights"], 0.0) * mask_s.float() / denom / R).to(dev)
+        rows_d = {k: v.to(dev, non_blocking=True) for k, v in rows.items()}
+        self.model.zero_grad()
+        self.flat.grads.zero_()      # the factors of other stages' layers contribute zeros to the sum over the group
+        accum = torch.zeros(4, dtype=torch.float32, device=dev)
+        per = max(1, min(R, hyper.tokens_per_microbatch // S))
+        if R % per:
+            raise ValueError("pipeline micro-batches must all have the same number of rows")
+        eps_hi = hyper.epsilon if hyper.epsilon_high is None else hyper.epsilon_high
+        model, trainer = self.model, self
+        micro = []
+        for r0 in range(0, R, per):
+            r1 = r0 + per
+            tokens = rows_d["tokens"][r0:r1].reshape(-1)
+            pos = (torch.arange(S, device=dev, dtype=torch.int32).repeat(per) if hyper.compat_row_positions
+                   else rows_d["input_pos"][r0:r1].reshape(-1).to(torch.int32))
+            gid, pid = compress_ids(rows["group_ids"][r0:r1].reshape(-1), rows["parent_ids"][r0:r1].reshape(-1))
+            micro.append(dict(tokens=tokens, pos=pos, gid=gid.to(dev), pid=pid.to(dev), r0=r0, r1=r1))
+
+        class _Stage:
+            def __init__(self):
+                self.live: dict = {}
+
+            def forward(self, mb, x):
+                m = micro[mb]
+                with trainer.timer.phase("forward"):
+                    hidden, saved, final = model.forward(m["tokens"], m["pos"], m["gid"], m["pid"], S, x_in=x)
+                if not model.is_last:
+                    self.live[mb] = (saved, final, None)
+                    return hidden
+                r0, r1 = m["r0"], m["r1"]
+                w_flat = tok_w.reshape(-1)[r0 * S:r1 * S]
+                sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
+                dhidden = torch.zeros_like(hidden)
+                if sel.numel():
+                    target = torch.cat([m["tokens"][1:], m["tokens"][:1]]).to(torch.int32)
+                    old_c = shift_left(rows_d["logprobs"][r0:r1], 0.0).reshape(-1)[sel]
+                    adv_c = shift_left(rows_d["advantages"][r0:r1], 0.0).reshape(-1)[sel]
+                    hc = ew.gather_rows(hidden, sel)
+                    with trainer.timer.phase("lm_head_loss"):
+                        res = lpl.forward(hc, model.lm_head, target[sel], old_c, adv_c, w_flat[sel], None, hyper.epsilon,
+                                          eps_hi, 0.0, accum)
+                        dhc = lpl.backward(hc, model.lm_head, model.lm_head_t, target[sel], res.lse, res.coef)
+                    ew.scatter_rows_(dhc, sel, dhidden)
+                self.live[mb] = (saved, final, dhidden)
+                return None
+
+            def backward(self, mb, dy):
+                saved, final, dhidden = self.live.pop(mb)
+                with trainer.timer.phase("backward"):
+                    return model.backward(dhidden if model.is_last else dy, saved, final, micro[mb]["pos"])
+
+        if hyper.beta > 0:
+            raise NotImplementedError("the KL term needs a second (reference) pipeline pass; use beta = 0 with pp_group")
+        runner = PipelineRunner(_Stage(), self.pp_group, act_shape=(per * S, self.cfg.hidden_size),
+                                act_dtype=torch.bfloat16, device=dev)
+        runner.run(len(micro))
+        self.model.export_grads()
+        out = self._finish_step(None, hyper, device_accum=accum)
         self.model.refresh_lora()
         return out
 

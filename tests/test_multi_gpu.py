@@ -466,6 +466,18 @@ for it in range(2):                                     # second step: refreshed
     tp_cos = cos(one2.flat.grads, tpt.flat.grads)
     assert tp_cos > 0.995, tp_cos
 
+# ---- pipeline parallel: layers split over the ranks, 1F1B over NCCL p2p == the same step on one GPU
+hy_pp = TrainHyper(learning_rate=1e-4, beta=0.0, rows_per_optimizer_step=4, tokens_per_microbatch=512)
+packed_pp = _packed(cfg, 4, 256)
+ppt = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native", pp_group=dist.group.WORLD)
+one3 = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native")
+m1, m4 = one3.step(packed_pp, hy_pp), ppt.step(packed_pp, hy_pp)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert abs(m1["loss"] - m4["loss"]) < 5e-3 * max(1.0, abs(m1["loss"])), (m1, m4)
+assert abs(m1["grad_norm"] - m4["grad_norm"]) < 3e-2 * m1["grad_norm"], (m1, m4)
+pp_cos = cos(one3.flat.grads, ppt.flat.grads)
+assert pp_cos > 0.995, pp_cos
+
 # ---- expert parallel: each rank trains on its own rows, experts sharded == mean of the per-rank full-model grads
 from art_b200.parallel.ep import ExpertParallel
 mcfg = ModelConfig(name="small-moe", family="qwen3_moe", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4,
@@ -492,13 +504,13 @@ for k in sorted(mlora):
         ga.append(g.reshape(-1)); gb.append(part.flat.grad_views[k].reshape(-1))
 c = cos(torch.cat(ga), torch.cat(gb))
 assert c > 0.99, c
-if rank == 0: print(f"PAR_TRAINER_OK world={world} cp_grad_cos={cos(one.flat.grads, cpt.flat.grads):.5f} tp_grad_cos={tp_cos:.5f} ep_grad_cos={c:.5f}")
+if rank == 0: print(f"PAR_TRAINER_OK world={world} cp_grad_cos={cos(one.flat.grads, cpt.flat.grads):.5f} tp_grad_cos={tp_cos:.5f} pp_grad_cos={pp_cos:.5f} ep_grad_cos={c:.5f}")
 dist.destroy_process_group()
 '''
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_trainer_context_tensor_expert_parallel(tmp_path):
+def test_trainer_context_tensor_pipeline_expert_parallel(tmp_path):
     world = 2
     script = tmp_path / "par_worker.py"
     script.write_text(PAR_TRAINER_WORKER)
