@@ -186,6 +186,7 @@ class KVCache:
             per = num_blocks * block_size * num_kv_heads * head_dim * torch.empty((), dtype=dtype).element_size()
             per = (per + 255) // 256 * 256
             self.arena = VmmArena(2 * num_layers * per, device)
+            self.arena.map()     # views can only be created over mapped memory; they stay valid across unmap / map
             self._views = ([self.arena.tensor((2 * i) * per, self.shape, dtype) for i in range(num_layers)],
                            [self.arena.tensor((2 * i + 1) * per, self.shape, dtype) for i in range(num_layers)])
         self._allocate()

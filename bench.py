@@ -48,10 +48,10 @@ def parse_args():
     ap.add_argument("--lora-rank", type=int, default=8)
     ap.add_argument("--attn", default=None)
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"])
-    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep", "tp"],
+    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep", "tp", "pp"],
                     help="dp: rows split over GPUs; cp: every row sharded over GPUs (long context); "
                          "ep: experts sharded over GPUs (MoE presets); tp: tensor-parallel groups of --tp-size "
-                         "GPUs, data parallel across the groups")
+                         "GPUs, data parallel across the groups; pp: layers split over the GPUs, 1F1B pipeline")
     ap.add_argument("--tp-size", type=int, default=2)
     ap.add_argument("--rollout", type=int, default=1, help="also measure rollout decode tokens/s (reported beside the headline)")
     return ap.parse_args()
@@ -186,7 +186,7 @@ def main():
     sync_name = "none"
     par = args.parallel if world > 1 else "dp"
     R, S = args.rows_per_gpu, args.seq_len
-    ep = cp_group = tp_group = None
+    ep = cp_group = tp_group = pp_group = None
     expert_range = None
     data_ranks, data_index = world, rank        # how many ranks hold different rows, and which share this one has
     if world > 1 and par == "dp":
@@ -195,6 +195,9 @@ def main():
         grad_sync, sync_name = make_grad_sync(args.grad_sync, dev, world)
     elif par == "cp":
         cp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over cp)"
+        data_ranks, data_index = 1, 0
+    elif par == "pp":
+        pp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over pp) + NCCL p2p activations"
         data_ranks, data_index = 1, 0
     elif par == "tp":
         T = args.tp_size
@@ -232,7 +235,7 @@ def main():
                 if ".mlp.experts." not in k or expert_range[0] <= int(k.split(".experts.")[1].split(".")[0]) < expert_range[1]}
     lora = init_lora(cfg, lcfg, seed=3407, device=dev, expert_range=expert_range)
     trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync, ep=ep,
-                      cp_group=cp_group, tp_group=tp_group, tp_tokens=args.micro_tokens)
+                      cp_group=cp_group, tp_group=tp_group, tp_tokens=args.micro_tokens, pp_group=pp_group)
     rollout_base = base if (args.rollout and impl == "native" and not cfg.is_moe) else None
     del base
     hyper = TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=R, tokens_per_microbatch=args.micro_tokens)
