@@ -95,6 +95,48 @@ def bench_attn(a) -> dict:
     return res
 
 
+def bench_moe(a) -> dict:
+    """Router + gather + grouped gate|up GEMM (SwiGLU epilogue) + grouped down GEMM + combine at a sparse-model shape."""
+    from . import _lib, moe
+
+    dev = "cuda"
+    M, E, k, d, F = a.tokens, a.experts, a.topk, a.d_model, a.ffn
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(M, d, device=dev, generator=g).bfloat16()
+    logits = torch.randn(M, E, device=dev, generator=g)
+    wgu = (torch.randn(E * 2 * F, d, device=dev, generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(E * d, F, device=dev, generator=g) * 0.02).bfloat16()
+    plan = moe.route(logits, k, True)
+    xp = moe.gather(x, plan)
+    h = torch.empty(plan.cap_rows, F, device=dev, dtype=torch.bfloat16)
+    gu = torch.empty(plan.cap_rows, 2 * F, device=dev, dtype=torch.bfloat16)
+    y = torch.empty(plan.cap_rows, d, device=dev, dtype=torch.bfloat16)
+    t_route = _time(lambda: moe.route(logits, k, True), a.iters, a.warmup, None)
+    t_gather = _time(lambda: moe.gather(x, plan, out=xp), a.iters, a.warmup, None)
+    t_gu = _time(lambda: moe.grouped_gemm(xp, wgu, plan, 2 * F, swiglu_out=h, out=gu), a.iters, a.warmup, None)
+    t_dn = _time(lambda: moe.grouped_gemm(h, wd, plan, d, out=y), a.iters, a.warmup, None)
+    t_comb = _time(lambda: moe.combine(y, plan, weighted=True, residual=x), a.iters, a.warmup, None)
+    _lib.check_status()
+    rows = M * k
+    res = {"op": "moe_layer_fwd", "tokens": M, "experts": E, "topk": k, "d_model": d, "ffn": F, "rows": rows,
+           "route_ms": round(t_route, 4), "gather_ms": round(t_gather, 4), "combine_ms": round(t_comb, 4),
+           "gate_up_ms": round(t_gu, 4), "gate_up_tflops": round(2.0 * rows * 2 * F * d / t_gu / 1e9, 1),
+           "down_ms": round(t_dn, 4), "down_tflops": round(2.0 * rows * d * F / t_dn / 1e9, 1)}
+    if not a.no_baseline:
+        seg = plan.seg_off.tolist()
+
+        def loop():
+            for e in range(E):
+                r = slice(seg[e], seg[e + 1])
+                if seg[e + 1] > seg[e]:
+                    torch.matmul(xp[r], wgu[e * 2 * F:(e + 1) * 2 * F].t(), out=gu[r])
+
+        t_loop = _time(loop, max(1, a.iters // 4), 1, None)
+        res["cublas_loop_gate_up_ms"] = round(t_loop, 4)
+        res["cublas_loop_gate_up_tflops"] = round(2.0 * rows * 2 * F * d / t_loop / 1e9, 1)
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -110,13 +152,19 @@ def main() -> None:
     t.add_argument("--hq", type=int, default=28)
     t.add_argument("--hkv", type=int, default=4)
     t.add_argument("--hd", type=int, default=128)
-    for p in (g, t):
+    m = sub.add_parser("moe")
+    m.add_argument("--tokens", type=int, default=8192)
+    m.add_argument("--experts", type=int, default=128)
+    m.add_argument("--topk", type=int, default=8)
+    m.add_argument("--d-model", type=int, default=2048)
+    m.add_argument("--ffn", type=int, default=768)
+    for p in (g, t, m):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    print(json.dumps(bench_attn(a) if a.op == "attn" else bench_gemm(a)))
+    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm}[a.op](a)))
 
 
 if __name__ == "__main__":
