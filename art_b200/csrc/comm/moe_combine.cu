@@ -70,18 +70,21 @@ ep_return_kernel(EpPeers pt, long off_ret, long off_rflag, long off_rdone, int r
 __global__ void __launch_bounds__(128)
 ep_ret_finish_kernel(EpPeers pt, long off_ret, long off_rflag, long off_rdone, int rank, int P, int E, int D,
                      const int* __restrict__ row_token, const int* __restrict__ seg_off_src,
-                     const int* __restrict__ tile_expert_src, __nv_bfloat16* __restrict__ out, int ldo, uint32_t epoch,
-                     uint32_t spin, int* status, unsigned int* cta_counter) {
+                     const int* __restrict__ tile_expert_src, const int* __restrict__ send_off, int cap_recv,
+                     __nv_bfloat16* __restrict__ out, int ldo, uint32_t epoch, uint32_t spin, int* status,
+                     unsigned int* cta_counter) {
   const int r = blockIdx.x;
   const int El = E / P;
   __shared__ int s_ok;
   if (r < seg_off_src[E]) {
     const int nv = D >> 3;
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * ldo);
-    if (row_token[r] < 0) {
+    const int e_r = tile_expert_src[r >> 7];
+    // padding rows, and rows the dispatch dropped because their owner was over capacity, come back as zeros
+    if (row_token[r] < 0 || send_off[e_r] + (r - seg_off_src[e_r]) >= cap_recv) {
       for (int i = threadIdx.x; i < nv; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
     } else {
-      const int owner = tile_expert_src[r >> 7] / El;
+      const int owner = e_r / El;
       if (threadIdx.x == 0) {
         const int ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(pt.base[rank] + off_rflag) + owner, epoch, spin);
         if (!ok) atomicMax(status, ST_TIMEOUT_PEER);
@@ -135,15 +138,16 @@ ARTB_EXPORT int artb_ep_return(void* h, long off_ret, long off_rflag, long off_r
 
 // out bf16 [cap_src, D] private, in this rank's own expert-sorted row order.
 ARTB_EXPORT int artb_ep_ret_finish(void* h, long off_ret, long off_rflag, long off_rdone, int E, int D,
-                                   const int* row_token, const int* seg_off_src, const int* tile_expert_src, void* out,
-                                   int ldo, int cap_src, unsigned int epoch, int wait_ms, int* status,
-                                   unsigned int* cta_counter, cudaStream_t st) {
+                                   const int* row_token, const int* seg_off_src, const int* tile_expert_src,
+                                   const int* send_off, int cap_recv, void* out, int ldo, int cap_src, unsigned int epoch,
+                                   int wait_ms, int* status, unsigned int* cta_counter, cudaStream_t st) {
   auto* s = static_cast<SymmState*>(h);
   if (!s || (D & 7) || (ldo & 7) || cap_src <= 0) return ERR_BAD_SHAPE;
   EpPeers pt;
   fill_peers(pt, s);
   ep_ret_finish_kernel<<<cap_src, 128, 0, st>>>(pt, off_ret, off_rflag, off_rdone, s->rank, s->world, E, D, row_token,
-                                                seg_off_src, tile_expert_src, reinterpret_cast<__nv_bfloat16*>(out), ldo,
-                                                epoch, spin_for(wait_ms), status, cta_counter);
+                                                seg_off_src, tile_expert_src, send_off, cap_recv,
+                                                reinterpret_cast<__nv_bfloat16*>(out), ldo, epoch, spin_for(wait_ms), status,
+                                                cta_counter);
   return static_cast<int>(cudaGetLastError());
 }

@@ -65,9 +65,14 @@ ep_exchange_kernel(EpPeers pt, long off_cnt, long off_cnt_flag, int rank, int P,
     }
     plan.send_off[e] = seg + before;
     if (owner == rank) {
-      s_seg[j] = seg;
-      plan.real_rows[j] = tot;
-      if (j == El - 1) s_seg[El] = seg + (tot + 127) / 128 * 128;
+      // Everything the owner indexes is clipped to the receive capacity: rows that would land beyond it are dropped
+      // by their senders (same arithmetic on every rank), their segments shrink or become empty here.
+      const int cap_rows = cap_tiles * 128;
+      const int seg_c = seg < cap_rows ? seg : cap_rows;
+      const int end_c = seg + (tot + 127) / 128 * 128 < cap_rows ? seg + (tot + 127) / 128 * 128 : cap_rows;
+      s_seg[j] = seg_c;
+      plan.real_rows[j] = tot < cap_rows - seg_c ? tot : cap_rows - seg_c;
+      if (j == El - 1) s_seg[El] = end_c > seg_c ? end_c : seg_c;
       int run = 0;
       for (int s = 0; s < P; ++s) {
         plan.src_start[j * P + s] = run;
@@ -116,7 +121,7 @@ ep_dispatch_kernel(EpPeers pt, long off_recv, long off_dflag, long off_ddone, in
                    const __nv_bfloat16* __restrict__ x, int ldx, int D, const int* __restrict__ row_token,
                    const float* __restrict__ row_w, int use_w, const int* __restrict__ seg_off_src,
                    const int* __restrict__ tile_expert_src, EpPlan plan, int cap_recv, int* __restrict__ done_cnt,
-                   uint32_t epoch, uint32_t spin, int* status) {
+                   uint32_t epoch, uint32_t spin, int allow_drop, int* status) {
   const int El = E / P;
   const int r = blockIdx.x;
   if (r == static_cast<int>(gridDim.x) - 1) {
@@ -141,7 +146,10 @@ ep_dispatch_kernel(EpPeers pt, long off_recv, long off_dflag, long off_ddone, in
       ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(ep_base(pt, rank) + off_ddone) + owner, epoch - 2, spin);
     if (!ok) atomicMax(status, ST_TIMEOUT_PEER);
     if (dest >= cap_recv) {
-      atomicMax(status, ST_OVERFLOW);
+      // beyond the owner's capacity: the row is dropped (it contributes zero; status[1] counts such rows); unless the
+      // caller allows dropping this is an error
+      atomicAdd(status + 1, 1);
+      if (!allow_drop) atomicMax(status, ST_OVERFLOW);
       ok = 0;
     }
     s_ok = ok;
@@ -241,7 +249,7 @@ ARTB_EXPORT int artb_ep_exchange(void* h, long off_cnt, long off_cnt_flag, int E
 ARTB_EXPORT int artb_ep_dispatch(void* h, long off_recv, long off_dflag, long off_ddone, int E, const void* x, int ldx,
                                  int D, const int* row_token, const float* row_w, int use_w, const int* seg_off_src,
                                  const int* tile_expert_src, int cap_src, int** plan_ptrs, int cap_recv, int* done_cnt,
-                                 unsigned int epoch, int wait_ms, int* status, cudaStream_t st) {
+                                 unsigned int epoch, int wait_ms, int allow_drop, int* status, cudaStream_t st) {
   auto* s = static_cast<SymmState*>(h);
   if (!s || (D & 7) || (ldx & 7) || cap_src <= 0) return ERR_BAD_SHAPE;
   EpPeers pt;
@@ -250,7 +258,7 @@ ARTB_EXPORT int artb_ep_dispatch(void* h, long off_recv, long off_dflag, long of
   ep_dispatch_kernel<<<cap_src + 1, 128, 0, st>>>(pt, off_recv, off_dflag, off_ddone, s->rank, s->world, E,
                                                   reinterpret_cast<const __nv_bfloat16*>(x), ldx, D, row_token, row_w,
                                                   use_w, seg_off_src, tile_expert_src, plan, cap_recv, done_cnt, epoch,
-                                                  spin_for(wait_ms), status);
+                                                  spin_for(wait_ms), allow_drop, status);
   return static_cast<int>(cudaGetLastError());
 }
 

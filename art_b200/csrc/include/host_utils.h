@@ -49,6 +49,10 @@ inline int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t rows, u
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)   // say which descriptor was refused: the caller only sees ERR_TMAP
+    fprintf(stderr, "artb: cuTensorMapEncodeTiled failed (%d): ptr=%p rows=%llu cols=%llu ld=%llu box=[%u x %u]\n",
+            static_cast<int>(r), ptr, static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
+            static_cast<unsigned long long>(ld), box_rows, box_cols);
   return r == CUDA_SUCCESS ? 0 : ERR_TMAP;
 }
 

@@ -60,7 +60,8 @@ lora_wgrad_kernel(const __nv_bfloat16* __restrict__ P, int ldp, const __nv_bfloa
   int m_end = min(M, m_begin + rows_per_split);
   if (seg_off) {
     // grouped: blockIdx.z is the expert; its row segment is split evenly over gridDim.y CTAs
-    const int lo = seg_off[blockIdx.z], hi = seg_off[blockIdx.z + 1];
+    // (clipped to the M rows the operands really have, whatever the offsets say)
+    const int lo = min(seg_off[blockIdx.z], M), hi = min(seg_off[blockIdx.z + 1], M);
     const int rows = ((hi - lo + static_cast<int>(gridDim.y) - 1) / static_cast<int>(gridDim.y) + WG_BM - 1) / WG_BM * WG_BM;
     m_begin = lo + blockIdx.y * rows;
     m_end = min(hi, m_begin + rows);
@@ -185,12 +186,12 @@ ARTB_EXPORT int artb_lora_wgrad(const void* P, int ldp, const void* Q, int ldq, 
 // seg_e = rows seg_off[e] .. seg_off[e+1] (device array, padded rows are zero).  One launch covers all experts.
 ARTB_EXPORT int artb_lora_wgrad_grouped(const void* P, int ldp, const void* Q, int ldq, float* out, int ldo,
                                         long out_stride, const int* seg_off, int num_experts, int C, int splits,
-                                        cudaStream_t st) {
-  if (num_experts <= 0 || C <= 0) return 0;
+                                        int rows, cudaStream_t st) {
+  if (num_experts <= 0 || C <= 0 || rows <= 0) return 0;
   if ((C & 7) || (ldp & 7) || (ldq & 7) || ldo < WG_R || splits < 1) return ERR_BAD_SHAPE;
   dim3 grid((C + WG_BC - 1) / WG_BC, splits, num_experts);
   lora_wgrad_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(P), ldp,
-                                          reinterpret_cast<const __nv_bfloat16*>(Q), ldq, out, ldo, 0, C, 0, seg_off,
+                                          reinterpret_cast<const __nv_bfloat16*>(Q), ldq, out, ldo, rows, C, 0, seg_off,
                                           out_stride);
   return static_cast<int>(cudaGetLastError());
 }

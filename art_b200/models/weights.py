@@ -40,19 +40,26 @@ def linear_shapes(cfg: ModelConfig) -> dict[str, tuple[int, int]]:
 
 
 def init_base_weights(cfg: ModelConfig, seed: int = 0, dtype: torch.dtype = torch.float32,
-                      device: str | torch.device = "cpu", std: float = 0.02) -> dict[str, torch.Tensor]:
-    """Random base model in HF naming.  Generated layer by layer on ``device``."""
-    g = torch.Generator(device=device).manual_seed(seed)
+                      device: str | torch.device = "cpu", std: float = 0.02,
+                      scale_residual_out: bool = False) -> dict[str, torch.Tensor]:
+    """Random base model in HF naming.  Generated layer by layer on ``device``.
 
-    def rnd(*shape: int) -> torch.Tensor:
-        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
+    ``scale_residual_out`` draws the projections that write into the residual stream (``o_proj``, ``down_proj``)
+    with ``std / sqrt(2 * num_layers)``, the usual depth-scaled initialisation.  Without it the residual of a deep
+    random model is dominated by a component common to all tokens, and a random router then sends almost every
+    token to the same few experts, which no trained mixture-of-experts model does."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    out_scale = (2 * cfg.num_layers) ** -0.5 if scale_residual_out else 1.0
+
+    def rnd(*shape: int, scale: float = 1.0) -> torch.Tensor:
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * (std * scale)).to(dtype)
 
     w: dict[str, torch.Tensor] = {"model.embed_tokens.weight": rnd(cfg.vocab_size, cfg.hidden_size)}
     d = cfg.hidden_size
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}."
         for name, (o, n) in linear_shapes(cfg).items():
-            w[p + name + ".weight"] = rnd(o, n)
+            w[p + name + ".weight"] = rnd(o, n, scale=out_scale if name.endswith(("o_proj", "down_proj")) else 1.0)
         if cfg.qkv_bias:
             for name in ("q_proj", "k_proj", "v_proj"):
                 w[p + f"self_attn.{name}.bias"] = rnd(linear_shapes(cfg)[f"self_attn.{name}"][0])

@@ -33,7 +33,7 @@ def _k():
         lib.artb_moe_router_bwd.argtypes = [vp, ci, vp, vp, vp, ci, ci, ci, ci, vp, ci, vp]
         lib.artb_gemm_grouped_bf16_tn.argtypes = [vp, ci, vp, ci, vp, ci, vp, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci,
                                                   ci, ci, vp, vp]
-        lib.artb_lora_wgrad_grouped.argtypes = [vp, ci, vp, ci, vp, ci, cl, vp, ci, ci, ci, vp]
+        lib.artb_lora_wgrad_grouped.argtypes = [vp, ci, vp, ci, vp, ci, cl, vp, ci, ci, ci, ci, vp]
         for f in (lib.artb_moe_router, lib.artb_moe_plan, lib.artb_moe_gather, lib.artb_moe_combine,
                   lib.artb_moe_router_bwd, lib.artb_gemm_grouped_bf16_tn, lib.artb_lora_wgrad_grouped):
             f.restype = ci
@@ -157,7 +157,8 @@ def grouped_wgrad(acc: torch.Tensor, p: torch.Tensor, q: torch.Tensor, plan: Rou
     E, C, R = acc.shape
     assert R == 64 and q.shape[1] == 64 and p.shape[1] == C and acc.is_contiguous()
     _lib.check_rc(_k().artb_lora_wgrad_grouped(_lib.ptr(p), p.stride(0), _lib.ptr(q), q.stride(0), _lib.ptr(acc), R,
-                                               C * R, _lib.ptr(plan.seg_off), E, C, splits, _lib.stream_ptr()),
+                                               C * R, _lib.ptr(plan.seg_off), E, C, splits, min(p.shape[0], q.shape[0]),
+                                               _lib.stream_ptr()),
                   "lora_wgrad_grouped")
 
 

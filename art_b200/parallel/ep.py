@@ -40,10 +40,10 @@ def _k():
         vp, ci, cl, cu = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_uint
         lib.artb_ep_exchange.argtypes = [vp, cl, cl, ci, vp, cu, ci, vp, ci, vp, vp]
         lib.artb_ep_dispatch.argtypes = [vp, cl, cl, cl, ci, vp, ci, ci, vp, vp, ci, vp, vp, ci, vp, ci, vp, cu, ci,
-                                         vp, vp]
+                                         ci, vp, vp]
         lib.artb_ep_recv.argtypes = [vp, cl, cl, cl, ci, ci, vp, vp, ci, ci, cu, ci, vp, vp, vp]
         lib.artb_ep_return.argtypes = [vp, cl, cl, cl, ci, vp, ci, ci, vp, ci, ci, cu, ci, vp, vp, vp]
-        lib.artb_ep_ret_finish.argtypes = [vp, cl, cl, cl, ci, ci, vp, vp, vp, vp, ci, ci, cu, ci, vp, vp, vp]
+        lib.artb_ep_ret_finish.argtypes = [vp, cl, cl, cl, ci, ci, vp, vp, vp, vp, ci, vp, ci, ci, cu, ci, vp, vp, vp]
         for f in (lib.artb_ep_exchange, lib.artb_ep_dispatch, lib.artb_ep_recv, lib.artb_ep_return,
                   lib.artb_ep_ret_finish):
             f.restype = ci
@@ -81,7 +81,7 @@ class RecvPlan:
 
 class ExpertParallel:
     def __init__(self, device, group, max_tokens: int, k: int, num_experts: int, d_model: int,
-                 capacity_factor: float = 2.0, wait_ms: int = 4000):
+                 capacity_factor: float = 2.0, wait_ms: int = 4000, drop_overflow: bool = False):
         self.device = torch.device(device)
         self.group = group
         self.rank = dist.get_rank(group)
@@ -89,6 +89,9 @@ class ExpertParallel:
         if num_experts % self.world or self.world > 8:
             raise ValueError("experts must divide evenly over at most 8 ranks")
         self.E, self.El, self.k, self.D, self.wait_ms = num_experts, num_experts // self.world, k, d_model, wait_ms
+        # rows routed to an owner beyond its receive capacity are dropped (they contribute zero to the layer).  With
+        # drop_overflow=False that is reported as an error at the next status check; True = capacity-factor training.
+        self.drop_overflow = drop_overflow
         self.cap_src_tiles = (max_tokens * k + num_experts * 127 + 127) // 128
         recv_rows = int(capacity_factor * max_tokens * k) + self.El * 127
         self.cap_recv_tiles = (recv_rows + 127) // 128
@@ -159,7 +162,7 @@ class ExpertParallel:
                                    x.stride(0), D, _lib.ptr(plan.row_token), _lib.ptr(plan.row_w), int(weighted),
                                    _lib.ptr(plan.seg_off), _lib.ptr(plan.tile_expert), plan.cap_rows, rp.ptrs,
                                    self.cap_recv_rows, _lib.ptr(self.done_cnt), self.d_epoch, self.wait_ms,
-                                   self._status(), st)
+                                   int(self.drop_overflow), self._status(), st)
         _lib.check_rc(rc, "ep_dispatch")
         out = torch.empty((self.cap_recv_rows, D), dtype=torch.bfloat16, device=self.device)
         rc = _k().artb_ep_recv(self.buf._h, self.off_recv[par], self.off_dflag, self.off_ddone, self.E, D, rp.ptrs,
@@ -182,10 +185,18 @@ class ExpertParallel:
         out = torch.empty((plan.cap_rows, D), dtype=torch.bfloat16, device=self.device)
         rc = _k().artb_ep_ret_finish(self.buf._h, self.off_ret[par], self.off_rflag, self.off_rdone, self.E, D,
                                      _lib.ptr(plan.row_token), _lib.ptr(plan.seg_off), _lib.ptr(plan.tile_expert),
-                                     _lib.ptr(out), out.stride(0), plan.cap_rows, self.r_epoch, self.wait_ms,
+                                     _lib.ptr(rp.send_off), self.cap_recv_rows, _lib.ptr(out), out.stride(0), plan.cap_rows, self.r_epoch, self.wait_ms,
                                      self._status(), self.counters[2:3].data_ptr(), st)
         _lib.check_rc(rc, "ep_ret_finish")
         return out
+
+    def dropped_rows(self, reset: bool = True) -> int:
+        """Rows dropped for lack of capacity since the last call (one device-to-host read)."""
+        w = _lib.status_word(self.device)
+        n = int(w[1].item())
+        if reset:
+            w[1] = 0
+        return n
 
     def close(self) -> None:
         self.buf.close()

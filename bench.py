@@ -181,7 +181,7 @@ def main():
     lcfg = LoraConfig(r=args.lora_rank, alpha=2.0 * args.lora_rank)
     impl = "native" if args.impl == "native" else "reference"
     attn_impl = args.attn or ("native" if impl == "native" else "sdpa")
-    base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev, scale_residual_out=cfg.is_moe)
     grad_sync = None
     sync_name = "none"
     par = args.parallel if world > 1 else "dp"
@@ -227,7 +227,7 @@ def main():
             print("bench.py: --parallel ep needs a mixture-of-experts preset (e.g. --model qwen3-30b-a3b)", file=sys.stderr)
             return 2
         ep = ExpertParallel(dev, None, args.micro_tokens, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size,
-                            capacity_factor=1.5)
+                            capacity_factor=2.0, drop_overflow=True)
         El = cfg.num_experts // world
         expert_range, sync_name = (rank * El, (rank + 1) * El), "nccl-allreduce(shared factors) + 1/world(experts)"
         # this rank keeps only its experts' frozen weights
@@ -266,10 +266,20 @@ def main():
 
     for _ in range(args.warmup):
         trainer.step(dev_rows, hyper)
+    if ep is not None:
+        ep.dropped_rows()   # reset the counter: warm-up does not count
     sampler = ClockSampler(nvml_index(local_rank))
     sampler.start()
     ms, launches, last = timed(dev_rows, args.steps)
     clocks = sampler.stop()
+    ep_drop = None
+    if ep is not None:
+        # share of dispatched (token, expert) rows that found their expert's owner over capacity, forward + backward
+        n = torch.tensor([float(ep.dropped_rows())], device=dev)
+        dist.all_reduce(n)
+        n_layers_moe = cfg.num_layers
+        sent = 2.0 * args.steps * tokens_per_step * cfg.num_experts_per_tok * n_layers_moe
+        ep_drop = round(float(n.item()) / sent, 6)
     trainer.step(host_rows, hyper)  # warm the host-input path
     ms_e2e, _, _ = timed(host_rows, args.steps)
     if os.environ.get("ARTB_PROFILE_STEP"):
@@ -317,6 +327,7 @@ def main():
             "config": {"model": cfg.name, "global_batch": R * data_ranks, "seq_len": S, "parallelism": (f"tp{args.tp_size}xdp{data_ranks}" if par == "tp" else f"{par}{world}"),
                        "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": args.micro_tokens,
                        "attention": attn_impl, "grad_sync": sync_name, "optimizer_steps_per_step": 1,
+                       **({"ep_capacity_factor": 2.0, "ep_dropped_row_share": ep_drop} if ep_drop is not None else {}),
                        "l2": "inputs larger than L2: each step streams the bf16 weights (W and W^T, 30 GB for the 7B "
                              "model) plus activations"},
             "clocks": clocks,

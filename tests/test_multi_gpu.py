@@ -233,6 +233,45 @@ for it in range(5):
     assert (yr[:total][plan.row_token[:total] < 0] == 0).all()
 ep.close()
 
+# ---- routing that exceeds the owner's capacity: rows are dropped (zero contribution), nothing indexes out of range
+M, k, E, D = 384, 2, 8, 64
+for allow in (True, False):
+    ep = ExpertParallel(dev, None, M, k, E, D, capacity_factor=0.5, drop_overflow=allow)
+    ep.dropped_rows()
+    g = torch.Generator(device=dev).manual_seed(17 + rank)
+    logits = torch.randn(M, E, device=dev, generator=g)
+    logits[:, :2] += 30                                     # every token of every rank picks experts 0 and 1 (rank 0)
+    x = (torch.randn(M, D, device=dev, generator=g) + 3).to(torch.bfloat16)
+    plan = moe.route(logits, k, True)
+    rp = ep.exchange(plan)
+    xp = ep.dispatch(x, plan, rp)
+    yr = ep.combine_return((xp.float() * 2).to(torch.bfloat16), plan, rp)
+    acc = torch.zeros(El, D, 64, device=dev)
+    moe.grouped_wgrad(acc, xp, xp[:, :64].contiguous(), rp)
+    torch.cuda.synchronize()
+    seg, real = rp.seg_off.tolist(), rp.real_rows.tolist()
+    assert seg[-1] <= ep.cap_recv_rows and all(seg[j] + real[j] <= ep.cap_recv_rows for j in range(El)), (seg, real)
+    n = torch.tensor([float(ep.dropped_rows())], device=dev); dist.all_reduce(n)
+    per_owner = [2 * world * M] if El >= 2 else [world * M, world * M]      # experts 0 and 1 live on one or two ranks
+    want_drop = sum(max(0, r - ep.cap_recv_rows) for r in per_owner)
+    assert int(n.item()) == want_drop, (n.item(), want_drop)
+    got = yr[plan.pos.long()].float()                       # [M, k, D]: 2 * x for rows that were kept, 0 for dropped ones
+    kept = got.abs().sum(-1) > 0
+    assert rel(got[kept], (x.float().unsqueeze(1) * 2).expand(M, k, D)[kept]) < 1e-2
+    nk = kept.sum().float(); dist.all_reduce(nk)
+    assert int(nk.item()) == world * M * k - want_drop, (nk.item(), want_drop)
+    for j in range(El):
+        rows = xp[seg[j]:seg[j] + real[j]].float()
+        assert rel(acc[j], rows.t() @ rows[:, :64]) < 1e-2 or real[j] == 0
+    try:
+        _lib.check_status(dev)
+        raised = False
+    except _lib.KernelStatusError:
+        raised = True
+    assert raised == (not allow), (allow, raised)
+    ep.close()
+if rank == 0: print("EP_DROP_OK", flush=True)
+
 # ---- MoE block with expert parallelism == the same block with all experts local
 from art_b200.models.config import ModelConfig
 from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
