@@ -21,6 +21,7 @@
 
 #include "gemm_pipeline.cuh"
 #include "host_utils.h"
+#include "sampling.cuh"
 
 namespace artb {
 
@@ -153,21 +154,6 @@ struct EpiDLogits {
 // log-probability under the sampling distribution without materialising logits.
 //   x = logit * inv_temp ;  sample = argmax_v (x_v + g_v),  g_v = -log(-log(u_v)),  u_v = hash(seed, row, v)
 // inv_temp == 0 selects greedy decoding (argmax of the raw logits, log-prob at temperature 1).
-__device__ __forceinline__ uint32_t mix32(uint32_t h) {
-  h ^= h >> 16;
-  h *= 0x85ebca6bu;
-  h ^= h >> 13;
-  h *= 0xc2b2ae35u;
-  h ^= h >> 16;
-  return h;
-}
-__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t row, uint32_t col) {
-  uint32_t h = mix32(seed ^ (row * 0x9e3779b1u));
-  h = mix32(h ^ (col * 0x85ebca77u) ^ 0x27d4eb2fu);
-  const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
-  return -__logf(-__logf(u));
-}
-
 struct EpiSample {
   float* partials;        // [splits, M, 8]: max, sumexp, best_score, best_idx(bits), best_x, -, -, -
   const float* inv_temp;  // [M] per-row 1/temperature (0 = greedy)

@@ -90,3 +90,39 @@ def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, 
     _lib.check_rc(_f("artb_sample_merge")(_lib.ptr(part), splits, M, _lib.ptr(tok), _lib.ptr(lp), _lib.stream_ptr()),
                   "sample_merge")
     return tok, lp
+
+
+def sample_restricted(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
+                      top_k: torch.Tensor, top_p: torch.Tensor, vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """LM head + top-k / top-p sampling: fp32 logits from one GEMM, then one CTA per row selects the thresholds by
+    radix select and samples with the same Gumbel noise as :func:`sample` (identical tokens when nothing is
+    restricted).  ``top_k`` int32 [M] (<= 0: off), ``top_p`` fp32 [M] (>= 1: off)."""
+    from .gemm import gemm_tn
+
+    M = hidden.shape[0]
+    V = lm_head.shape[0]
+    logits = gemm_tn(hidden, lm_head, out_dtype=torch.float32)
+    tok = torch.empty(M, dtype=torch.int32, device=hidden.device)
+    lp = torch.empty(M, dtype=torch.float32, device=hidden.device)
+    _lib.check_rc(_f("artb_sample_restricted")(_lib.ptr(logits), logits.stride(0), _lib.ptr(inv_temp), _lib.ptr(row_seed),
+                                               _lib.ptr(top_k), _lib.ptr(top_p), M, V, vocab_offset, _lib.ptr(tok),
+                                               _lib.ptr(lp), _lib.stream_ptr()), "sample_restricted")
+    return tok, lp
+
+
+def reference_restrict(logits: torch.Tensor, top_k: int, top_p: float) -> torch.Tensor:
+    """Boolean keep-mask of one row of (temperature-scaled) logits: top-k first, then top-p on the renormalised rest;
+    values equal to a threshold are kept.  Plain PyTorch; the oracle of :func:`sample_restricted`."""
+    x = logits.float()
+    keep = torch.ones_like(x, dtype=torch.bool)
+    if 0 < top_k < x.numel():
+        keep &= x >= x.topk(top_k).values[-1]
+    if top_p < 1.0:
+        xs = torch.where(keep, x, torch.full_like(x, float("-inf")))
+        probs = torch.softmax(xs, -1)
+        sp, _ = probs.sort(descending=True)
+        cum = sp.cumsum(-1)
+        n_keep = int((cum < top_p).sum().item()) + 1           # smallest prefix whose mass reaches top_p
+        thr = sp[min(n_keep, sp.numel()) - 1]
+        keep &= probs >= thr
+    return keep
