@@ -40,10 +40,14 @@ static int launch_splitk(const CUtensorMap& tA, const CUtensorMap& tB, int kb_ma
   return static_cast<int>(cudaGetLastError());
 }
 
-// out = bf16(ws + bias + residual[:, :res_cols]); ws <- 0.  Optional SwiGLU on interleaved columns.
+// out = bf16(ws + bias + residual[:, :res_cols]); ws <- 0.
+// With `adapter`: columns >= mask_col0 hold the stacked LoRA shrink products of all resident adapters (`cols` per
+// slot); row m keeps only the columns of its own slot adapter[m] (none if negative) -- the multi-LoRA slot mask,
+// applied here so that it costs no launch of its own.
 __global__ void splitk_finalize_kernel(float* __restrict__ ws, int ldw, __nv_bfloat16* __restrict__ out, int ldc,
                                        const __nv_bfloat16* __restrict__ R, int ldr, int res_cols,
-                                       const float* __restrict__ bias, int M, int N) {
+                                       const float* __restrict__ bias, int M, int N, const int* __restrict__ adapter,
+                                       int mask_col0, int cols) {
   const int vec = N >> 2;
   const long total = static_cast<long>(M) * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -64,6 +68,14 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, int ldw, __nv_bfl
       v.y += __bfloat162float(r[1]);
       v.z += __bfloat162float(r[2]);
       v.w += __bfloat162float(r[3]);
+    }
+    if (adapter && c + 4 > mask_col0) {
+      const int a = adapter[m];
+      const int lo = mask_col0 + a * cols, hi = lo + cols;
+      if (c >= mask_col0 && (a < 0 || c < lo || c >= hi)) v.x = 0.f;
+      if (c + 1 >= mask_col0 && (a < 0 || c + 1 < lo || c + 1 >= hi)) v.y = 0.f;
+      if (c + 2 >= mask_col0 && (a < 0 || c + 2 < lo || c + 2 >= hi)) v.z = 0.f;
+      if (c + 3 >= mask_col0 && (a < 0 || c + 3 < lo || c + 3 >= hi)) v.w = 0.f;
     }
     uint2 o;
     o.x = pack_bf16x2(v.x, v.y);
@@ -94,7 +106,8 @@ ARTB_EXPORT int artb_gemm_splitk_bf16_tn(const void* A, int lda, const void* B, 
 }
 
 ARTB_EXPORT int artb_splitk_finalize(float* ws, int ldw, void* out, int ldc, const void* R, int ldr, int res_cols,
-                                     const float* bias, int M, int N, cudaStream_t stream) {
+                                     const float* bias, int M, int N, const int* adapter, int mask_col0, int cols,
+                                     cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((N & 3) || (ldc & 3) || (ldw & 3) || (R && (ldr & 1))) return ERR_BAD_SHAPE;
   long total = static_cast<long>(M) * (N / 4);
@@ -102,6 +115,6 @@ ARTB_EXPORT int artb_splitk_finalize(float* ws, int ldw, void* out, int ldc, con
   if (blocks > 148L * 8) blocks = 148L * 8;
   splitk_finalize_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
       ws, ldw, reinterpret_cast<__nv_bfloat16*>(out), ldc, reinterpret_cast<const __nv_bfloat16*>(R), ldr,
-      res_cols > 0 ? res_cols : N, bias, M, N);
+      res_cols > 0 ? res_cols : N, bias, M, N, adapter, mask_col0, cols);
   return static_cast<int>(cudaGetLastError());
 }

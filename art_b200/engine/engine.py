@@ -76,7 +76,7 @@ class Sequence:
 
     def view(self) -> SeqView:
         return SeqView(self.tokens, self.num_cached, self.blocks, self.adapter, self.params.temperature, self.seed,
-                       len(self.output_ids))
+                       len(self.output_ids), self.params.top_p, self.params.top_k)
 
 
 @dataclass

@@ -35,6 +35,12 @@ class SeqView:
     temperature: float
     seed: int
     step: int                  # number of tokens generated so far (mixes into the sampling seed)
+    top_p: float = 1.0         # nucleus mass (>= 1: off)
+    top_k: int = -1            # keep the k most likely tokens (<= 0: off)
+
+    @property
+    def restricted(self) -> bool:
+        return self.temperature > 0 and (self.top_p < 1.0 or self.top_k > 0)
 
 
 def _mix_seed(seed: int, step: int) -> int:
@@ -68,8 +74,13 @@ class ReferenceRunner:
             t = int(lp.argmax())
             return t, float(lp[t])
         lp = torch.log_softmax(logits / sv.temperature, -1)
+        probs = lp.exp()
+        if sv.restricted:      # top-k, then top-p on the rest; the log-prob stays that of the full distribution
+            from ..ops.paged import reference_restrict
+
+            probs = probs * reference_restrict(logits / sv.temperature, sv.top_k, sv.top_p)
         g = torch.Generator(device="cpu").manual_seed(_mix_seed(sv.seed, sv.step))
-        t = int(torch.multinomial(lp.exp().cpu(), 1, generator=g))
+        t = int(torch.multinomial(probs.cpu(), 1, generator=g))
         return t, float(lp[t])
 
     def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
@@ -90,7 +101,8 @@ class ReferenceRunner:
     def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
         toks: list[list[int]] = []
         lps: list[list[float]] = []
-        work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step) for s in seqs]
+        work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step, s.top_p, s.top_k)
+                for s in seqs]
         for _ in range(n_steps):
             step_t, step_l = [], []
             for s in work:
@@ -105,6 +117,9 @@ class ReferenceRunner:
 
 
 # ---------------------------------------------------------------------------------- native
+TWO_CTA_DECODE = os.environ.get("ARTB_DECODE_2CTA", "1") != "0"
+
+
 class EngineLinear:
     """A frozen projection plus ``max_loras`` adapter slots.
 
@@ -180,16 +195,20 @@ class EngineLinear:
         if splits > 1:
             ws = self._ws(M, Next, x.device)
             gemm_splitk_(ws, x, Wv, bn, splits)
-            splitk_finalize(ws, y_ext, bias, residual, N)
+            # the finalize pass also applies the per-row adapter-slot mask to the shrink columns
+            splitk_finalize(ws, y_ext, bias, residual, N, adapter_ids if any_lora else None, N, self.cols)
         else:
-            gemm_tn(x, Wv, out=y_ext, bias=bias, residual=residual, res_cols=N, bn=bn,
+            # two 128-row tiles would each pull the whole weight tile through L2: a CTA pair shares it instead
+            pair = TWO_CTA_DECODE and M % 256 == 0 and bn == 256
+            gemm_tn(x, Wv, out=y_ext, bias=bias, residual=residual, res_cols=N, bn=0 if pair else bn, two_cta=pair,
                     swiglu_out=swiglu_out if fuse_swiglu else None)
         if not any_lora:
             if swiglu_out is not None and not fuse_swiglu:
                 ew.swiglu_fwd(y_ext, out=swiglu_out)
             return y_ext
         T = y_ext[:, N:]
-        lora_slot_mask_(T, adapter_ids, self.cols)
+        if splits == 1:
+            lora_slot_mask_(T, adapter_ids, self.cols)
         return gemm_tn(T, self.B_all, residual=y_ext[:, :N], swiglu_out=swiglu_out)
 
 
@@ -357,7 +376,12 @@ class NativeRunner:
         hidden, _ = ew.rmsnorm_fwd(hl, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
         inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
         seeds = torch.tensor([_mix_seed(s.seed, s.step) for s in seqs], dtype=torch.int64, device=dev).to(torch.int32)
-        t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
+        if any(s.restricted for s in seqs):
+            tk = torch.tensor([s.top_k for s in seqs], dtype=torch.int32, device=dev)
+            tp = torch.tensor([s.top_p for s in seqs], dtype=torch.float32, device=dev)
+            t, lp = paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, tk, tp)
+        else:
+            t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
         return t.tolist(), lp.tolist()
 
     def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
@@ -393,6 +417,7 @@ class NativeRunner:
                 "ctx": torch.zeros(nb, dtype=torch.int32, device=dev), "slot": torch.full((nb,), -1, dtype=torch.int32, device=dev),
                 "ad": torch.full((nb,), -1, dtype=torch.int32, device=dev), "active": torch.zeros(nb, dtype=torch.int32, device=dev),
                 "inv_t": torch.zeros(nb, dtype=torch.float32, device=dev),
+                "top_k": torch.zeros(nb, dtype=torch.int32, device=dev), "top_p": torch.ones(nb, dtype=torch.float32, device=dev),
                 "seeds": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
                 "bt": torch.zeros((nb, max_blocks), dtype=torch.int32, device=dev),
                 "out_t": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
@@ -402,7 +427,7 @@ class NativeRunner:
             self._dstate[key] = st
         return st
 
-    def _decode_body(self, st, n_steps: int, any_lora: bool, splits: int, ws):
+    def _decode_body(self, st, n_steps: int, any_lora: bool, splits: int, ws, restricted: bool = False):
         from ..ops import elementwise as ew
         from ..ops import paged
 
@@ -417,7 +442,10 @@ class NativeRunner:
                 x2 = L["o"](st["attn_out"], st["ad"], any_lora, residual=x)
                 x = self._mlp(L, x2, st["ad"], any_lora)
             hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
-            t, lp = paged.sample(hidden, self.lm_head, st["inv_t"], st["seeds"][k])
+            if restricted:
+                t, lp = paged.sample_restricted(hidden, self.lm_head, st["inv_t"], st["seeds"][k], st["top_k"], st["top_p"])
+            else:
+                t, lp = paged.sample(hidden, self.lm_head, st["inv_t"], st["seeds"][k])
             st["out_t"][k].copy_(t)
             st["out_l"][k].copy_(lp)
             if k + 1 < n_steps:
@@ -451,9 +479,13 @@ class NativeRunner:
                              dtype=torch.int64).to(torch.int32)
         st["seeds"].copy_(seeds, non_blocking=True)
         any_lora = any(s.adapter >= 0 for s in seqs)
+        restricted = any(s.restricted for s in seqs)
+        if restricted:
+            st["top_k"].copy_(torch.tensor([s.top_k for s in seqs] + [0] * pad, dtype=torch.int32), non_blocking=True)
+            st["top_p"].copy_(torch.tensor([s.top_p for s in seqs] + [1.0] * pad, dtype=torch.float32), non_blocking=True)
         max_ctx = max(lens) + n_steps
         splits = 1 if nb * cfg.num_kv_heads >= 128 else min(8, max(1, 1 << (max(1, max_ctx // 512).bit_length() - 1)))
-        key = (nb, max_blocks, n_steps, any_lora, splits)
+        key = (nb, max_blocks, n_steps, any_lora, splits, restricted)
         ws = None
         if splits > 1:
             ws = st.get(("ws", splits))
@@ -466,12 +498,12 @@ class NativeRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self._decode_body(st, n_steps, any_lora, splits, ws)
+                self._decode_body(st, n_steps, any_lora, splits, ws, restricted)
             self._dgraphs[key] = graph
             graph.replay()
         else:
             self._dseen.add(key)
-            self._decode_body(st, n_steps, any_lora, splits, ws)
+            self._decode_body(st, n_steps, any_lora, splits, ws, restricted)
         out_t = st["out_t"][:, :n].tolist()
         out_l = st["out_l"][:, :n].tolist()
         return out_t, out_l

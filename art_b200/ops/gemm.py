@@ -153,7 +153,7 @@ def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, sp
         vp, ci = ctypes.c_void_p, ctypes.c_int
         f.argtypes = [vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, vp]
         f.restype = ci
-        g.argtypes = [vp, ci, vp, ci, vp, ci, ci, vp, ci, ci, vp]
+        g.argtypes = [vp, ci, vp, ci, vp, ci, ci, vp, ci, ci, vp, ci, ci, vp]
         g.restype = ci
         _sk_configured = True
     _check2d(a, "a")
@@ -166,25 +166,31 @@ def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, sp
 
 
 def splitk_finalize(ws: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
-                    residual: torch.Tensor | None = None, res_cols: int = 0) -> torch.Tensor:
-    """``out = bf16(ws[:, :N] + bias + residual)`` and ``ws[:, :N] = 0``."""
+                    residual: torch.Tensor | None = None, res_cols: int = 0, adapter: torch.Tensor | None = None,
+                    mask_col0: int = 0, cols_per_adapter: int = 0) -> torch.Tensor:
+    """``out = bf16(ws[:, :N] + bias + residual)`` and ``ws[:, :N] = 0``.
+
+    With ``adapter`` (int32 [M]) the columns from ``mask_col0`` on are the stacked LoRA shrink products of all
+    resident adapters, ``cols_per_adapter`` each: row ``m`` keeps only those of slot ``adapter[m]``."""
     g = _lib.kernels().artb_splitk_finalize
     M, N = out.shape
     rc = g(_lib.ptr(ws), ws.stride(0), _lib.ptr(out), out.stride(0), _lib.ptr(residual),
-           residual.stride(0) if residual is not None else 0, res_cols, _lib.ptr(bias), M, N, _lib.stream_ptr())
+           residual.stride(0) if residual is not None else 0, res_cols, _lib.ptr(bias), M, N, _lib.ptr(adapter),
+           mask_col0, cols_per_adapter, _lib.stream_ptr())
     _lib.check_rc(rc, "splitk_finalize")
     return out
 
 
 def plan_small_m(M: int, N: int, K: int, sms: int = 148) -> tuple[int, int]:
-    """(bn, splits) for a weight-streaming GEMM: widest N tile, then split K until the machine is full."""
+    """(bn, splits) for a weight-streaming GEMM: widest N tile, then split K as far as ONE wave of CTAs allows
+    (tiles * splits <= SMs: a second, nearly empty wave would double the time)."""
     m_tiles = (M + 127) // 128
     bn = 256 if N >= 256 else (128 if N >= 128 else 64)
     tiles = m_tiles * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
     if tiles >= 100:
         return bn, 1
-    splits = max(1, min((sms + tiles - 1) // tiles, max(1, kb // 4)))
+    splits = max(1, min(sms // tiles, max(1, kb // 4)))
     return bn, splits
 
 

@@ -1,5 +1,5 @@
 """Front-ends for the rollout-engine kernels: KV-cache write/gather, paged decode attention,
-multi-LoRA slot mask, fused LM-head sampler, device-side decode bookkeeping."""
+multi-LoRA slot mask, fused LM-head sampler, top-k / top-p sampler, device-side decode bookkeeping."""
 from __future__ import annotations
 
 import ctypes
@@ -18,6 +18,7 @@ _sigs = {
     "artb_sample_partials": [vp, ci, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
     "artb_sample_merge": [vp, ci, ci, vp, vp, vp],
     "artb_logprob_splits": [ci, ci],
+    "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
 }
 _bound: dict[str, object] = {}
 
@@ -99,11 +100,18 @@ def sample_restricted(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: tor
     restricted).  ``top_k`` int32 [M] (<= 0: off), ``top_p`` fp32 [M] (>= 1: off)."""
     from .gemm import gemm_tn
 
-    M = hidden.shape[0]
-    V = lm_head.shape[0]
     logits = gemm_tn(hidden, lm_head, out_dtype=torch.float32)
-    tok = torch.empty(M, dtype=torch.int32, device=hidden.device)
-    lp = torch.empty(M, dtype=torch.float32, device=hidden.device)
+    return sample_from_logits(logits, inv_temp, row_seed, top_k, top_p, vocab_offset)
+
+
+def sample_from_logits(logits: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor, top_k: torch.Tensor,
+                       top_p: torch.Tensor, vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """The sampling half of :func:`sample_restricted` on given fp32 logits [M, V] (unit inner stride)."""
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise ValueError("logits must be fp32 with unit inner stride")
+    M, V = logits.shape
+    tok = torch.empty(M, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(M, dtype=torch.float32, device=logits.device)
     _lib.check_rc(_f("artb_sample_restricted")(_lib.ptr(logits), logits.stride(0), _lib.ptr(inv_temp), _lib.ptr(row_seed),
                                                _lib.ptr(top_k), _lib.ptr(top_p), M, V, vocab_offset, _lib.ptr(tok),
                                                _lib.ptr(lp), _lib.stream_ptr()), "sample_restricted")

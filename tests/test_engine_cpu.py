@@ -127,3 +127,22 @@ def test_async_stream_pause_resume_and_abort(tiny):
         assert not eng.has_unfinished
     finally:
         eng.shutdown()
+
+
+def test_top_k_top_p_restrict_the_support(tiny):
+    from art_b200.ops.paged import reference_restrict
+
+    x = torch.log(torch.tensor([0.4, 0.3, 0.15, 0.1, 0.05]))
+    assert reference_restrict(x, 2, 1.0).tolist() == [True, True, False, False, False]
+    assert reference_restrict(x, -1, 0.6).tolist() == [True, True, False, False, False]      # 0.4 + 0.3 reaches 0.6
+    assert reference_restrict(x, -1, 0.75).tolist() == [True, True, True, False, False]
+    assert reference_restrict(x, 3, 0.5).tolist() == [True, True, False, False, False]       # 0.5 of the top-3 mass 0.85
+    assert reference_restrict(x, -1, 1.0).all()
+    cfg, base = tiny
+    eng = make_engine(cfg, base)
+    greedy = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=0.0))
+    top1 = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=1.3, top_k=1, seed=11))
+    tiny_p = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=1.3, top_p=1e-6, seed=12))
+    assert top1.output_ids == greedy.output_ids and tiny_p.output_ids == greedy.output_ids
+    free = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=1.3, seed=11))
+    assert all(lp <= 0 for lp in top1.logprobs + free.logprobs)

@@ -52,6 +52,45 @@ def test_gemm_two_cta_224_tiles():
     assert rel_err(out, reference_gemm_tn(a, b)) < 5e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 2112, 512), (300, 600, 320), (512, 37952, 256)])
+def test_gemm_two_cta_tails_and_partial_residual(M, N, K):
+    """Pair tiles with M and N tails, and a residual that covers only the first columns (the decode-time
+    ``[W ; A_all]`` product: base columns get the residual, the shrink columns do not)."""
+    from art_b200.ops.gemm import gemm_tn, reference_gemm_tn
+
+    a, b = bf(M, K, seed=1), bf(N, K, scale=0.05, seed=2)
+    bias = torch.randn(N, device=DEV)
+    rc = N - 64
+    r = bf(M, rc, seed=5)
+    out = gemm_tn(a, b, residual=r, res_cols=rc, bias=bias, two_cta=True)
+    ref = reference_gemm_tn(a, b, None, None, None, bias)
+    ref[:, :rc] += r.float()
+    assert rel_err(out, ref) < 5e-3
+
+
+def test_splitk_finalize_applies_the_adapter_slot_mask():
+    from art_b200.ops.gemm import gemm_splitk_, plan_small_m, reference_gemm_tn, splitk_finalize
+
+    M, N, K, kpad, cols = 256, 512, 1024, 64, 16
+    a, b = bf(M, K, seed=1), bf(N + kpad, K, scale=0.05, seed=2)
+    r = bf(M, N, seed=3)
+    adapter = (torch.arange(M, device=DEV, dtype=torch.int32) % 5) - 1          # -1 .. 3
+    bn, splits = plan_small_m(M, N + kpad, K)
+    assert splits > 1 and ((M + 127) // 128) * ((N + kpad + bn - 1) // bn) * splits <= 148
+    ws = torch.zeros(M, N + kpad, dtype=torch.float32, device=DEV)
+    out = torch.empty(M, N + kpad, dtype=torch.bfloat16, device=DEV)
+    gemm_splitk_(ws, a, b, bn, splits)
+    splitk_finalize(ws, out, None, r, N, adapter, N, cols)
+    ref = reference_gemm_tn(a, b)
+    ref[:, :N] += r.float()
+    col = torch.arange(kpad, device=DEV).unsqueeze(0)
+    lo = (adapter.long() * cols).unsqueeze(1)
+    keep = (adapter.unsqueeze(1) >= 0) & (col >= lo) & (col < lo + cols)
+    ref[:, N:] *= keep
+    assert rel_err(out, ref) < 5e-3
+    assert (out[:, N:][~keep] == 0).all() and float(ws.abs().max()) == 0.0
+
+
 def test_gemm_swiglu_epilogue():
     from art_b200.ops import elementwise as ew
     from art_b200.ops.gemm import gemm_tn
@@ -166,3 +205,60 @@ def test_flat_adamw_matches_torch():
         norm = opt.step(1e-3)
         assert abs(float(norm) - float(norm_ref)) < 1e-3 * float(norm_ref)
     assert torch.allclose(p, p_ref.detach(), atol=1e-6, rtol=1e-5)
+
+
+def test_restricted_sampler_matches_oracle_and_fused_sampler():
+    from art_b200.ops import paged
+
+    dev = torch.device(DEV)
+    g = torch.Generator(device=dev).manual_seed(5)
+    M, V = 96, 5003
+    logits = (torch.randn(M, V, device=dev, generator=g) * 3).contiguous()
+    temps = [0.0, 0.7, 1.0, 1.5]
+    ks = [-1, 1, 5, 50, 4000]
+    ps = [1.0, 0.9, 0.5, 0.05]
+    cfgs = [(temps[i % 4], ks[(i // 4) % 5], ps[(i // 20) % 4]) for i in range(M)]
+    inv_t = torch.tensor([0.0 if t <= 0 else 1.0 / t for t, _, _ in cfgs], dtype=torch.float32, device=dev)
+    tk = torch.tensor([k for _, k, _ in cfgs], dtype=torch.int32, device=dev)
+    tp = torch.tensor([p for _, _, p in cfgs], dtype=torch.float32, device=dev)
+    seeds = torch.arange(M, dtype=torch.int32, device=dev) * 7919 + 13
+    tok, lp = paged.sample_from_logits(logits, inv_t, seeds, tk, tp)
+    torch.cuda.synchronize()
+    for i, (t, k, p) in enumerate(cfgs):
+        x = logits[i] * (1.0 if t <= 0 else 1.0 / t)
+        full = torch.log_softmax(x.float(), -1)
+        ti = int(tok[i])
+        assert abs(float(lp[i]) - float(full[ti])) < 2e-3, (i, t, k, p)
+        if t <= 0 or k == 1:
+            assert ti == int(x.argmax()), (i, t, k, p)
+            continue
+        keep = paged.reference_restrict(x, k, p)
+        if not bool(keep[ti]):      # only a token sitting on the threshold may differ (summation order)
+            thr = full[keep].min()
+            assert float(full[ti]) > float(thr) - 1e-3, (i, t, k, p, float(full[ti]), float(thr))
+    # the empirical distribution over many seeds is the renormalised restricted one
+    V2, n = 64, 40000
+    row = torch.randn(V2, device=dev, generator=g) * 2
+    lg = row.unsqueeze(0).expand(n, V2).contiguous()
+    one = torch.ones(n, dtype=torch.float32, device=dev)
+    for k, p in ((10, 1.0), (-1, 0.8), (20, 0.6)):
+        tok2, _ = paged.sample_from_logits(lg, one, torch.arange(n, dtype=torch.int32, device=dev),
+                                           torch.full((n,), k, dtype=torch.int32, device=dev), one * p)
+        keep = paged.reference_restrict(row, k, p)
+        want = torch.softmax(row.float(), -1) * keep
+        want = want / want.sum()
+        got = torch.bincount(tok2.long(), minlength=V2).float() / n
+        assert float((got - want).abs().max()) < 0.012, (k, p, float((got - want).abs().max()))
+        assert float(got[~keep].sum()) < 1e-3
+    # nothing restricted: the same tokens as the fused LM-head sampler (same noise, same statistics)
+    hid = (torch.randn(48, 256, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    head = (torch.randn(3001, 256, device=dev, generator=g) * 0.2).to(torch.bfloat16)
+    it = torch.full((48,), 1.0 / 0.8, dtype=torch.float32, device=dev)
+    it[::5] = 0.0
+    sd = torch.arange(48, dtype=torch.int32, device=dev) + 1000
+    t_f, lp_f = paged.sample(hid, head, it, sd)
+    t_r, lp_r = paged.sample_restricted(hid, head, it, sd, torch.zeros(48, dtype=torch.int32, device=dev),
+                                        torch.ones(48, dtype=torch.float32, device=dev))
+    assert int((t_f == t_r).sum()) >= 46
+    same = t_f == t_r
+    assert float((lp_f[same] - lp_r[same]).abs().max()) < 5e-3
