@@ -171,6 +171,20 @@ class EngineLinear:
             self.ws_holder["ws"] = ws
         return ws
 
+    def _shrink(self, x, adapter_ids):
+        """``T[M, kpad] = X A_all^T`` with every row restricted to the columns of its own adapter slot."""
+        from ..ops.gemm import gemm_splitk_, gemm_tn, plan_small_m, splitk_finalize
+        from ..ops.paged import lora_slot_mask_
+
+        M = x.shape[0]
+        bn, splits = plan_small_m(M, self.kpad, self.K)
+        if splits > 1:
+            ws = self._ws(M, self.kpad, x.device)
+            T = torch.empty((M, self.kpad), dtype=torch.bfloat16, device=x.device)
+            gemm_splitk_(ws, x, self.A_all, bn, splits)
+            return splitk_finalize(ws, T, None, None, 0, adapter_ids, 0, self.cols)
+        return lora_slot_mask_(gemm_tn(x, self.A_all, bn=bn), adapter_ids, self.cols)
+
     def __call__(self, x, adapter_ids, any_lora: bool, residual=None, swiglu_out=None):
         from ..ops import elementwise as ew
         from ..ops.gemm import gemm_splitk_, gemm_tn, plan_small_m, splitk_finalize
@@ -186,6 +200,14 @@ class EngineLinear:
             return gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out,
                            bias=None if self.bias_ext is None else self.bias_ext[:self.N])
         N = self.N
+        if any_lora and plan_small_m(M, N, self.K)[1] == 1:
+            # wide projection (gate|up): the product is not split, so the low-rank update can ride in the same
+            # accumulator as extra K once T = mask(X A_all^T) is known -- a skinny split-K GEMM over X alone -- and the
+            # residual / SwiGLU epilogue runs in the weight-streaming GEMM itself (no [M, N] intermediate)
+            T = self._shrink(x, adapter_ids)
+            pair = TWO_CTA_DECODE and M % 256 == 0
+            return gemm_tn(x, self.W, a2=T, b2=self.B_all, residual=residual, swiglu_out=swiglu_out, two_cta=pair,
+                           bias=None if self.bias_ext is None else self.bias_ext[:N])
         Next = N + self.kpad if any_lora else N
         Wv = self.W_ext[:Next]
         bias = None if self.bias_ext is None else self.bias_ext[:Next]
