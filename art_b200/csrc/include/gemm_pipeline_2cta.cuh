@@ -36,7 +36,8 @@ template <int STAGES, int BN2, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                         int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status) {
+                         int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status, int splits,
+                         int kb_per) {
   using L = Gemm2SmemLayout<STAGES, BN2>;
   constexpr int G2_BN = BN2, G2_BNH = BN2 / 2, G2_STAGE_BYTES = L::STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
@@ -56,7 +57,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const bool leader = rank == 0;
   const int cluster_id = blockIdx.x >> 1;
   const int n_clusters = gridDim.x >> 1;
-  const int total_tiles = m_tiles2 * n_tiles;
+  // splits > 1: the K range of every output tile is cut into `splits` slices of kb_per blocks; a work item is
+  // (tile, slice) and its partial goes through an accumulating epilogue (no extra-K operands in that mode)
+  const int mn_tiles = m_tiles2 * n_tiles;
+  const int total_tiles = mn_tiles * splits;
   const int my_tiles = cluster_id < total_tiles ? (total_tiles - cluster_id + n_clusters - 1) / n_clusters : 0;
   const int kb_total = kb_main + kb_extra;
 
@@ -91,10 +95,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t it = 0;
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int tile = cluster_id + t * n_clusters;
-        const int m2 = tile % m_tiles2, nb = tile / m_tiles2;
+        const int mn = tile % mn_tiles, sp = tile / mn_tiles;
+        const int m2 = mn % m_tiles2, nb = mn / m_tiles2;
         const int row_a = m2 * 2 * GEMM_BM + rank * GEMM_BM;
         const int row_b = nb * G2_BN + rank * G2_BNH;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int kb_lo = sp * kb_per;
+        const int kb_hi = splits > 1 ? min(kb_main, kb_lo + kb_per) : kb_total;
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -133,7 +140,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * G2_BN;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int kb_lo = ((cluster_id + t * n_clusters) / mn_tiles) * kb_per;
+        const int kb_hi = splits > 1 ? min(kb_main, kb_lo + kb_per) : kb_total;
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph)) {
@@ -148,7 +157,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint64_t bdesc = umma_smem_desc_k128(sb);
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k)
-            tc_mma_f16_2cta(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            tc_mma_f16_2cta(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb_lo) | k) != 0);
           tc_commit_2cta(&empty_bar[s], 3);   // both CTAs may refill this stage once the MMAs retire
         }
         if (*abort_flag) break;
@@ -163,7 +172,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (int t = 0; t < my_tiles; ++t) {
       if (__shfl_sync(0xffffffffu, *abort_flag, 0)) break;
       const int tile = cluster_id + t * n_clusters;
-      TileInfo ti = make_tile((tile % m_tiles2) * 2 + static_cast<int>(rank), tile / m_tiles2);
+      const int mn = tile % mn_tiles;
+      TileInfo ti = make_tile((mn % m_tiles2) * 2 + static_cast<int>(rank), mn / m_tiles2);
+      if (splits > 1) {
+        ti.group = tile / mn_tiles;
+        ti.kb_lo = ti.group * kb_per;
+        ti.kb_n = max(0, min(kb_per, kb_main - ti.kb_lo));
+        ti.extra = 0;
+      }
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
       const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;

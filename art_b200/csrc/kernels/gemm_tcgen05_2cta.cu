@@ -43,7 +43,40 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
                       ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};
   kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, m_tiles2, n_tiles, epi,
-                                                        status);
+                                                        status, 1, kb_main);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Split-K on CTA pairs for small-M (decode) weight streaming: work item = (256 x 256 tile, K slice); the pair shares
+// each weight tile (every CTA stages half of it), so the weights cross L2 -> shared memory once per pair instead of
+// once per 128-row tile, and the partial goes into the fp32 workspace with vector atomics.
+static int launch_2cta_splitk(const void* A, int lda, const void* B, int ldb, float* ws, int ldw, int M, int N, int K,
+                              int splits, int* status, cudaStream_t stream) {
+  constexpr int STAGES = 6, BN2 = 256;
+  using L = Gemm2SmemLayout<STAGES, BN2>;
+  CUtensorMap tA, tB;
+  int e;
+  if ((e = make_tmap_bf16_2d(&tA, A, M, K, lda, GEMM_BM, GEMM_BK))) return e;
+  if ((e = make_tmap_bf16_2d(&tB, B, N, K, ldb, BN2 / 2, GEMM_BK))) return e;
+  const int kb_main = (K + GEMM_BK - 1) / GEMM_BK;
+  if (splits > kb_main) splits = kb_main;
+  const int kb_per = (kb_main + splits - 1) / splits;
+  splits = (kb_main + kb_per - 1) / kb_per;   // no empty slice
+  auto kern = gemm_tcgen05_2cta_kernel<STAGES, BN2, EpiAtomic<BN2>>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    configured[dev & 63] = true;
+  }
+  const int m_tiles2 = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM), n_tiles = (N + BN2 - 1) / BN2;
+  int clusters = m_tiles2 * n_tiles * splits;
+  if (clusters > sm_count() / 2) clusters = sm_count() / 2;
+  EpiAtomic<BN2> epi{ws, ldw, M, N};
+  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, m_tiles2, n_tiles, epi, status,
+                                                        splits, kb_per);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -71,4 +104,12 @@ ARTB_EXPORT int artb_gemm_bf16_tn_2cta(const void* A, int lda, const void* B, in
                                res_cols, status, -max_clusters, stream);
   return launch_2cta<6, 256>(A, lda, B, ldb, A2, lda2, B2, ldb2, K2, C, ldc, R, ldr, H, ldh, bias, M, N, K, epilogue,
                              res_cols, status, max_clusters, stream);
+}
+
+// ws[M, ldw] (fp32, zero on entry) += A[M,K] B[N,K]^T, K split `splits` ways over CTA pairs (256 x 256 tiles).
+ARTB_EXPORT int artb_gemm_splitk_bf16_tn_2cta(const void* A, int lda, const void* B, int ldb, float* ws, int ldw, int M,
+                                              int N, int K, int splits, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (N & 3) || (ldw & 3) || splits < 1) return ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(ws) & 15) return ERR_BAD_ALIGN;
+  return launch_2cta_splitk(A, lda, B, ldb, ws, ldw, M, N, K, splits, status, stream);
 }

@@ -200,28 +200,26 @@ class EngineLinear:
             return gemm_tn(x, self.W, residual=residual, swiglu_out=swiglu_out,
                            bias=None if self.bias_ext is None else self.bias_ext[:self.N])
         N = self.N
-        if any_lora and plan_small_m(M, N, self.K)[1] == 1:
+        pair = TWO_CTA_DECODE and M % 256 == 0 and N >= 256     # CTA pairs share each weight tile
+        if any_lora and plan_small_m(M, N, self.K, pair=pair)[1] == 1:
             # wide projection (gate|up): the product is not split, so the low-rank update can ride in the same
             # accumulator as extra K once T = mask(X A_all^T) is known -- a skinny split-K GEMM over X alone -- and the
             # residual / SwiGLU epilogue runs in the weight-streaming GEMM itself (no [M, N] intermediate)
             T = self._shrink(x, adapter_ids)
-            pair = TWO_CTA_DECODE and M % 256 == 0
             return gemm_tn(x, self.W, a2=T, b2=self.B_all, residual=residual, swiglu_out=swiglu_out, two_cta=pair,
                            bias=None if self.bias_ext is None else self.bias_ext[:N])
         Next = N + self.kpad if any_lora else N
         Wv = self.W_ext[:Next]
         bias = None if self.bias_ext is None else self.bias_ext[:Next]
-        bn, splits = plan_small_m(M, Next, self.K)
+        bn, splits = plan_small_m(M, Next, self.K, pair=pair)
         y_ext = torch.empty((M, Next), dtype=torch.bfloat16, device=x.device)
         fuse_swiglu = swiglu_out is not None and not any_lora and splits == 1
         if splits > 1:
             ws = self._ws(M, Next, x.device)
-            gemm_splitk_(ws, x, Wv, bn, splits)
+            gemm_splitk_(ws, x, Wv, bn, splits, two_cta=pair)
             # the finalize pass also applies the per-row adapter-slot mask to the shrink columns
             splitk_finalize(ws, y_ext, bias, residual, N, adapter_ids if any_lora else None, N, self.cols)
         else:
-            # two 128-row tiles would each pull the whole weight tile through L2: a CTA pair shares it instead
-            pair = TWO_CTA_DECODE and M % 256 == 0 and bn == 256
             gemm_tn(x, Wv, out=y_ext, bias=bias, residual=residual, res_cols=N, bn=0 if pair else bn, two_cta=pair,
                     swiglu_out=swiglu_out if fuse_swiglu else None)
         if not any_lora:

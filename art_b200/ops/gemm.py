@@ -144,15 +144,21 @@ def reference_gemm_tn(a, b, a2=None, b2=None, residual=None, bias=None) -> torch
 _sk_configured = False
 
 
-def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, splits: int) -> None:
-    """``ws[M, :N] += a @ b.T`` with the K dimension split across CTAs (fp32 atomics); ``ws`` fp32, zero on entry."""
+def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, splits: int,
+                 two_cta: bool = False) -> None:
+    """``ws[M, :N] += a @ b.T`` with the K dimension split across CTAs (fp32 atomics); ``ws`` fp32, zero on entry.
+
+    ``two_cta``: 256 x 256 tiles on CTA pairs (``bn`` is ignored); the pair shares every weight tile."""
     global _sk_configured
     f = _lib.kernels().artb_gemm_splitk_bf16_tn
+    f2 = _lib.kernels().artb_gemm_splitk_bf16_tn_2cta
     g = _lib.kernels().artb_splitk_finalize
     if not _sk_configured:
         vp, ci = ctypes.c_void_p, ctypes.c_int
         f.argtypes = [vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, ci, vp, vp]
         f.restype = ci
+        f2.argtypes = [vp, ci, vp, ci, vp, ci, ci, ci, ci, ci, vp, vp]
+        f2.restype = ci
         g.argtypes = [vp, ci, vp, ci, vp, ci, ci, vp, ci, ci, vp, ci, ci, vp]
         g.restype = ci
         _sk_configured = True
@@ -160,8 +166,12 @@ def gemm_splitk_(ws: torch.Tensor, a: torch.Tensor, b: torch.Tensor, bn: int, sp
     _check2d(b, "b")
     M, K = a.shape
     N = b.shape[0]
-    rc = f(_lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0), _lib.ptr(ws), ws.stride(0), M, N, K, bn, splits,
-           _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+    if two_cta:
+        rc = f2(_lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0), _lib.ptr(ws), ws.stride(0), M, N, K, splits,
+                _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+    else:
+        rc = f(_lib.ptr(a), a.stride(0), _lib.ptr(b), b.stride(0), _lib.ptr(ws), ws.stride(0), M, N, K, bn, splits,
+               _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
     _lib.check_rc(rc, "gemm_splitk")
 
 
@@ -181,13 +191,19 @@ def splitk_finalize(ws: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | No
     return out
 
 
-def plan_small_m(M: int, N: int, K: int, sms: int = 148) -> tuple[int, int]:
+def plan_small_m(M: int, N: int, K: int, sms: int = 148, pair: bool = False) -> tuple[int, int]:
     """(bn, splits) for a weight-streaming GEMM: widest N tile, then split K as far as ONE wave of CTAs allows
-    (tiles * splits <= SMs: a second, nearly empty wave would double the time)."""
+    (tiles * splits <= SMs: a second, nearly empty wave would double the time).  ``pair``: 256 x 256 tiles on CTA
+    pairs, so the unit is a cluster and there are ``sms // 2`` of them."""
+    kb = (K + 63) // 64
+    if pair:
+        tiles = ((M + 255) // 256) * ((N + 255) // 256)
+        if tiles >= 50:
+            return 256, 1
+        return 256, max(1, min((sms // 2) // tiles, max(1, kb // 4)))
     m_tiles = (M + 127) // 128
     bn = 256 if N >= 256 else (128 if N >= 128 else 64)
     tiles = m_tiles * ((N + bn - 1) // bn)
-    kb = (K + 63) // 64
     if tiles >= 100:
         return bn, 1
     splits = max(1, min(sms // tiles, max(1, kb // 4)))

@@ -68,18 +68,21 @@ def test_gemm_two_cta_tails_and_partial_residual(M, N, K):
     assert rel_err(out, ref) < 5e-3
 
 
-def test_splitk_finalize_applies_the_adapter_slot_mask():
+@pytest.mark.parametrize("pair,M,N,K", [(False, 256, 512, 1024), (True, 256, 512, 1024), (True, 512, 3584, 2304),
+                                        (True, 256, 4608, 3584)])
+def test_splitk_finalize_applies_the_adapter_slot_mask(pair, M, N, K):
     from art_b200.ops.gemm import gemm_splitk_, plan_small_m, reference_gemm_tn, splitk_finalize
 
-    M, N, K, kpad, cols = 256, 512, 1024, 64, 16
+    kpad, cols = 64, 16
     a, b = bf(M, K, seed=1), bf(N + kpad, K, scale=0.05, seed=2)
     r = bf(M, N, seed=3)
     adapter = (torch.arange(M, device=DEV, dtype=torch.int32) % 5) - 1          # -1 .. 3
-    bn, splits = plan_small_m(M, N + kpad, K)
-    assert splits > 1 and ((M + 127) // 128) * ((N + kpad + bn - 1) // bn) * splits <= 148
+    bn, splits = plan_small_m(M, N + kpad, K, pair=pair)
+    units = ((M + 255) // 256) * ((N + kpad + 255) // 256) if pair else ((M + 127) // 128) * ((N + kpad + bn - 1) // bn)
+    assert splits > 1 and units * splits <= (74 if pair else 148)
     ws = torch.zeros(M, N + kpad, dtype=torch.float32, device=DEV)
     out = torch.empty(M, N + kpad, dtype=torch.bfloat16, device=DEV)
-    gemm_splitk_(ws, a, b, bn, splits)
+    gemm_splitk_(ws, a, b, bn, splits, two_cta=pair)
     splitk_finalize(ws, out, None, r, N, adapter, N, cols)
     ref = reference_gemm_tn(a, b)
     ref[:, :N] += r.float()
@@ -252,7 +255,7 @@ def test_restricted_sampler_matches_oracle_and_fused_sampler():
         assert float(got[~keep].sum()) < 1e-3
     # nothing restricted: the same tokens as the fused LM-head sampler (same noise, same statistics)
     hid = (torch.randn(48, 256, device=dev, generator=g) * 0.5).to(torch.bfloat16)
-    head = (torch.randn(3001, 256, device=dev, generator=g) * 0.2).to(torch.bfloat16)
+    head = (torch.randn(3008, 256, device=dev, generator=g) * 0.2).to(torch.bfloat16)
     it = torch.full((48,), 1.0 / 0.8, dtype=torch.float32, device=dev)
     it[::5] = 0.0
     sd = torch.arange(48, dtype=torch.int32, device=dev) + 1000
