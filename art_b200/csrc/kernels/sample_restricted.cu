@@ -5,6 +5,7 @@
 // path takes fp32 logits [M, V] (one plain GEMM) and does, per row, with x = logit / temperature:
 //
 //   1. max and sum of exp            -> log Z of the full distribution
+//      min-p:  keep x >= max + log(min_p), i.e. tokens at least min_p times as likely as the best one
 //   2. top-k:  the k-th largest x by a 4-pass radix select (8 bits per pass) over an order-preserving integer key;
 //              per-warp shared-memory histograms keep the atomics local
 //   3. top-p:  among the survivors of 2, the largest threshold whose tail mass still reaches p x (surviving mass):
@@ -128,8 +129,8 @@ __device__ uint32_t radix_select(const float* __restrict__ x, int V, float sc, f
 __global__ void __launch_bounds__(SR_THREADS)
 sample_restricted_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ inv_temp,
                          const uint32_t* __restrict__ row_seed, const int* __restrict__ top_k,
-                         const float* __restrict__ top_p, int M, int V, int vocab_offset, int* __restrict__ token,
-                         float* __restrict__ logprob) {
+                         const float* __restrict__ top_p, const float* __restrict__ min_p, int M, int V,
+                         int vocab_offset, int* __restrict__ token, float* __restrict__ logprob) {
   __shared__ SrShared s;
   const int row = blockIdx.x, tid = threadIdx.x;
   if (row >= M) return;
@@ -148,7 +149,12 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
   if (!greedy) {
     const int k = top_k[row];
     const float p = top_p[row];
-    if (k > 0 && k < V) tau = radix_select<false>(x, V, sc, mx, 0u, static_cast<float>(k), s);
+    const float mp = min_p ? min_p[row] : 0.f;
+    if (mp > 0.f) tau = order_key(mx + __logf(fminf(mp, 1.f)));
+    if (k > 0 && k < V) {
+      const uint32_t tk = radix_select<false>(x, V, sc, mx, 0u, static_cast<float>(k), s);
+      tau = tk > tau ? tk : tau;
+    }
     if (p < 1.f) {
       float Zk = Z;
       if (tau) {
@@ -212,13 +218,14 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
 
 using namespace artb;
 
-// logits fp32 [M, V] (row stride ld elements); top_k <= 0 and top_p >= 1 leave a row unrestricted.
+// logits fp32 [M, V] (row stride ld elements); top_k <= 0, top_p >= 1 and min_p <= 0 (or a null min_p) leave a row
+// unrestricted.
 ARTB_EXPORT int artb_sample_restricted(const float* logits, long ld, const float* inv_temp, const uint32_t* row_seed,
-                                       const int* top_k, const float* top_p, int M, int V, int vocab_offset,
-                                       int* token, float* logprob, cudaStream_t stream) {
+                                       const int* top_k, const float* top_p, const float* min_p, int M, int V,
+                                       int vocab_offset, int* token, float* logprob, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (V <= 0 || ld < V) return ERR_BAD_SHAPE;
-  sample_restricted_kernel<<<M, SR_THREADS, 0, stream>>>(logits, ld, inv_temp, row_seed, top_k, top_p, M, V,
+  sample_restricted_kernel<<<M, SR_THREADS, 0, stream>>>(logits, ld, inv_temp, row_seed, top_k, top_p, min_p, M, V,
                                                          vocab_offset, token, logprob);
   return static_cast<int>(cudaGetLastError());
 }

@@ -32,6 +32,7 @@ class SamplingParams:
     temperature: float = 1.0
     top_p: float = 1.0
     top_k: int = -1
+    min_p: float = 0.0
     n: int = 1
     stop: list[str] | None = None
     stop_token_ids: list[int] | None = None
@@ -76,7 +77,7 @@ class Sequence:
 
     def view(self) -> SeqView:
         return SeqView(self.tokens, self.num_cached, self.blocks, self.adapter, self.params.temperature, self.seed,
-                       len(self.output_ids), self.params.top_p, self.params.top_k)
+                       len(self.output_ids), self.params.top_p, self.params.top_k, self.params.min_p)
 
 
 @dataclass

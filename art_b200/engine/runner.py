@@ -37,10 +37,11 @@ class SeqView:
     step: int                  # number of tokens generated so far (mixes into the sampling seed)
     top_p: float = 1.0         # nucleus mass (>= 1: off)
     top_k: int = -1            # keep the k most likely tokens (<= 0: off)
+    min_p: float = 0.0         # keep tokens at least min_p times as likely as the most likely one (<= 0: off)
 
     @property
     def restricted(self) -> bool:
-        return self.temperature > 0 and (self.top_p < 1.0 or self.top_k > 0)
+        return self.temperature > 0 and (self.top_p < 1.0 or self.top_k > 0 or self.min_p > 0)
 
 
 def _mix_seed(seed: int, step: int) -> int:
@@ -78,7 +79,7 @@ class ReferenceRunner:
         if sv.restricted:      # top-k, then top-p on the rest; the log-prob stays that of the full distribution
             from ..ops.paged import reference_restrict
 
-            probs = probs * reference_restrict(logits / sv.temperature, sv.top_k, sv.top_p)
+            probs = probs * reference_restrict(logits / sv.temperature, sv.top_k, sv.top_p, sv.min_p)
         g = torch.Generator(device="cpu").manual_seed(_mix_seed(sv.seed, sv.step))
         t = int(torch.multinomial(probs.cpu(), 1, generator=g))
         return t, float(lp[t])
@@ -101,8 +102,8 @@ class ReferenceRunner:
     def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
         toks: list[list[int]] = []
         lps: list[list[float]] = []
-        work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step, s.top_p, s.top_k)
-                for s in seqs]
+        work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step, s.top_p, s.top_k,
+                        s.min_p) for s in seqs]
         for _ in range(n_steps):
             step_t, step_l = [], []
             for s in work:
@@ -399,7 +400,8 @@ class NativeRunner:
         if any(s.restricted for s in seqs):
             tk = torch.tensor([s.top_k for s in seqs], dtype=torch.int32, device=dev)
             tp = torch.tensor([s.top_p for s in seqs], dtype=torch.float32, device=dev)
-            t, lp = paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, tk, tp)
+            mp = torch.tensor([s.min_p for s in seqs], dtype=torch.float32, device=dev)
+            t, lp = paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, tk, tp, mp)
         else:
             t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
         return t.tolist(), lp.tolist()
@@ -438,6 +440,7 @@ class NativeRunner:
                 "ad": torch.full((nb,), -1, dtype=torch.int32, device=dev), "active": torch.zeros(nb, dtype=torch.int32, device=dev),
                 "inv_t": torch.zeros(nb, dtype=torch.float32, device=dev),
                 "top_k": torch.zeros(nb, dtype=torch.int32, device=dev), "top_p": torch.ones(nb, dtype=torch.float32, device=dev),
+                "min_p": torch.zeros(nb, dtype=torch.float32, device=dev),
                 "seeds": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
                 "bt": torch.zeros((nb, max_blocks), dtype=torch.int32, device=dev),
                 "out_t": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
@@ -463,7 +466,8 @@ class NativeRunner:
                 x = self._mlp(L, x2, st["ad"], any_lora)
             hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
             if restricted:
-                t, lp = paged.sample_restricted(hidden, self.lm_head, st["inv_t"], st["seeds"][k], st["top_k"], st["top_p"])
+                t, lp = paged.sample_restricted(hidden, self.lm_head, st["inv_t"], st["seeds"][k], st["top_k"], st["top_p"],
+                                                st["min_p"])
             else:
                 t, lp = paged.sample(hidden, self.lm_head, st["inv_t"], st["seeds"][k])
             st["out_t"][k].copy_(t)
@@ -503,6 +507,7 @@ class NativeRunner:
         if restricted:
             st["top_k"].copy_(torch.tensor([s.top_k for s in seqs] + [0] * pad, dtype=torch.int32), non_blocking=True)
             st["top_p"].copy_(torch.tensor([s.top_p for s in seqs] + [1.0] * pad, dtype=torch.float32), non_blocking=True)
+            st["min_p"].copy_(torch.tensor([s.min_p for s in seqs] + [0.0] * pad, dtype=torch.float32), non_blocking=True)
         max_ctx = max(lens) + n_steps
         splits = 1 if nb * cfg.num_kv_heads >= 128 else min(8, max(1, 1 << (max(1, max_ctx // 512).bit_length() - 1)))
         key = (nb, max_blocks, n_steps, any_lora, splits, restricted)

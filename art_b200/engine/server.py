@@ -80,6 +80,7 @@ class OpenAIServer:
         temp = body.get("temperature")
         return SamplingParams(max_tokens=max_tokens, temperature=1.0 if temp is None else float(temp),
                               top_p=float(body.get("top_p") or 1.0), top_k=int(body.get("top_k") or -1),
+                              min_p=float(body.get("min_p") or 0.0),
                               n=int(body.get("n") or 1), stop=stop, stop_token_ids=body.get("stop_token_ids"),
                               seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
                               guided_choice=body.get("guided_choice"))

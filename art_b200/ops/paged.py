@@ -18,7 +18,7 @@ _sigs = {
     "artb_sample_partials": [vp, ci, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
     "artb_sample_merge": [vp, ci, ci, vp, vp, vp],
     "artb_logprob_splits": [ci, ci],
-    "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
+    "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
 }
 _bound: dict[str, object] = {}
 
@@ -94,18 +94,20 @@ def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, 
 
 
 def sample_restricted(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
-                      top_k: torch.Tensor, top_p: torch.Tensor, vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+                      top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor | None = None,
+                      vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
     """LM head + top-k / top-p sampling: fp32 logits from one GEMM, then one CTA per row selects the thresholds by
     radix select and samples with the same Gumbel noise as :func:`sample` (identical tokens when nothing is
-    restricted).  ``top_k`` int32 [M] (<= 0: off), ``top_p`` fp32 [M] (>= 1: off)."""
+    restricted).  ``top_k`` int32 [M] (<= 0: off), ``top_p`` fp32 [M] (>= 1: off), ``min_p`` fp32 [M] (<= 0: off)."""
     from .gemm import gemm_tn
 
     logits = gemm_tn(hidden, lm_head, out_dtype=torch.float32)
-    return sample_from_logits(logits, inv_temp, row_seed, top_k, top_p, vocab_offset)
+    return sample_from_logits(logits, inv_temp, row_seed, top_k, top_p, min_p, vocab_offset)
 
 
 def sample_from_logits(logits: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor, top_k: torch.Tensor,
-                       top_p: torch.Tensor, vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+                       top_p: torch.Tensor, min_p: torch.Tensor | None = None,
+                       vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
     """The sampling half of :func:`sample_restricted` on given fp32 logits [M, V] (unit inner stride)."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise ValueError("logits must be fp32 with unit inner stride")
@@ -113,16 +115,21 @@ def sample_from_logits(logits: torch.Tensor, inv_temp: torch.Tensor, row_seed: t
     tok = torch.empty(M, dtype=torch.int32, device=logits.device)
     lp = torch.empty(M, dtype=torch.float32, device=logits.device)
     _lib.check_rc(_f("artb_sample_restricted")(_lib.ptr(logits), logits.stride(0), _lib.ptr(inv_temp), _lib.ptr(row_seed),
-                                               _lib.ptr(top_k), _lib.ptr(top_p), M, V, vocab_offset, _lib.ptr(tok),
+                                               _lib.ptr(top_k), _lib.ptr(top_p), _lib.ptr(min_p), M, V, vocab_offset,
+                                               _lib.ptr(tok),
                                                _lib.ptr(lp), _lib.stream_ptr()), "sample_restricted")
     return tok, lp
 
 
-def reference_restrict(logits: torch.Tensor, top_k: int, top_p: float) -> torch.Tensor:
-    """Boolean keep-mask of one row of (temperature-scaled) logits: top-k first, then top-p on the renormalised rest;
-    values equal to a threshold are kept.  Plain PyTorch; the oracle of :func:`sample_restricted`."""
+def reference_restrict(logits: torch.Tensor, top_k: int, top_p: float, min_p: float = 0.0) -> torch.Tensor:
+    """Boolean keep-mask of one row of (temperature-scaled) logits: min-p, then top-k, then top-p on the renormalised
+    rest; values equal to a threshold are kept.  Plain PyTorch; the oracle of :func:`sample_restricted`."""
     x = logits.float()
     keep = torch.ones_like(x, dtype=torch.bool)
+    if min_p > 0:
+        import math
+
+        keep &= x >= x.max() + math.log(min(min_p, 1.0))
     if 0 < top_k < x.numel():
         keep &= x >= x.topk(top_k).values[-1]
     if top_p < 1.0:

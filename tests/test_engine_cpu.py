@@ -138,6 +138,7 @@ def test_top_k_top_p_restrict_the_support(tiny):
     assert reference_restrict(x, -1, 0.75).tolist() == [True, True, True, False, False]
     assert reference_restrict(x, 3, 0.5).tolist() == [True, True, False, False, False]       # 0.5 of the top-3 mass 0.85
     assert reference_restrict(x, -1, 1.0).all()
+    assert reference_restrict(x, -1, 1.0, 0.3).tolist() == [True, True, True, False, False]     # >= 0.3 * 0.4
     cfg, base = tiny
     eng = make_engine(cfg, base)
     greedy = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=0.0))

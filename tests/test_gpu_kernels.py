@@ -244,14 +244,14 @@ def test_restricted_sampler_matches_oracle_and_fused_sampler():
     row = torch.randn(V2, device=dev, generator=g) * 2
     lg = row.unsqueeze(0).expand(n, V2).contiguous()
     one = torch.ones(n, dtype=torch.float32, device=dev)
-    for k, p in ((10, 1.0), (-1, 0.8), (20, 0.6)):
+    for k, p, mp in ((10, 1.0, 0.0), (-1, 0.8, 0.0), (20, 0.6, 0.0), (-1, 1.0, 0.15), (8, 0.9, 0.05)):
         tok2, _ = paged.sample_from_logits(lg, one, torch.arange(n, dtype=torch.int32, device=dev),
-                                           torch.full((n,), k, dtype=torch.int32, device=dev), one * p)
-        keep = paged.reference_restrict(row, k, p)
+                                           torch.full((n,), k, dtype=torch.int32, device=dev), one * p, one * mp)
+        keep = paged.reference_restrict(row, k, p, mp)
         want = torch.softmax(row.float(), -1) * keep
         want = want / want.sum()
         got = torch.bincount(tok2.long(), minlength=V2).float() / n
-        assert float((got - want).abs().max()) < 0.012, (k, p, float((got - want).abs().max()))
+        assert float((got - want).abs().max()) < 0.012, (k, p, mp, float((got - want).abs().max()))
         assert float(got[~keep].sum()) < 1e-3
     # nothing restricted: the same tokens as the fused LM-head sampler (same noise, same statistics)
     hid = (torch.randn(48, 256, device=dev, generator=g) * 0.5).to(torch.bfloat16)

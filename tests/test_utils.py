@@ -167,3 +167,21 @@ def test_truncated_adapter_checkpoint_fails_cleanly(tmp_path):
     f.write_bytes(raw[: len(raw) // 2])
     with pytest.raises(Exception):
         peft_io.load_adapter(str(d))
+
+
+def test_small_m_gemm_plan_fills_one_wave_only():
+    """The split-K planner never asks for more work items than the GPU has CTAs (or CTA pairs): a second,
+    nearly empty wave would double the time of a weight-streaming GEMM."""
+    from art_b200.ops.gemm import plan_small_m
+
+    for M in (8, 64, 128, 256, 512):
+        for N in (64, 128, 576, 3648, 4736, 18944, 37888, 152064):
+            for K in (64, 1024, 3584, 18944):
+                bn, splits = plan_small_m(M, N, K)
+                tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+                assert splits >= 1 and (splits == 1 or tiles * splits <= 148), (M, N, K, bn, splits)
+                assert splits <= max(1, ((K + 63) // 64) // 4) or splits == 1
+                if M % 256 == 0 and N >= 256:
+                    bn2, sp2 = plan_small_m(M, N, K, pair=True)
+                    units = (M // 256) * ((N + 255) // 256)
+                    assert bn2 == 256 and (sp2 == 1 or units * sp2 <= 74), (M, N, K, sp2)
