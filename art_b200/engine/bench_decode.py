@@ -15,7 +15,7 @@ import torch
 
 
 def measure_decode(cfg, device, seqs: int = 256, prompt_len: int = 512, new_tokens: int = 128, loras: int = 4,
-                   runs: int = 2, base=None) -> dict:
+                   runs: int = 3, base=None) -> dict:
     from ..models.weights import LoraConfig, init_base_weights, init_lora
     from ..ops import _lib
     from .engine import Engine, SamplingParams
@@ -85,7 +85,7 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--loras", type=int, default=4)
-    ap.add_argument("--runs", type=int, default=2)
+    ap.add_argument("--runs", type=int, default=3)
     a = ap.parse_args()
     print(json.dumps(measure_decode(PRESETS[a.model], "cuda", a.seqs, a.prompt_len, a.new_tokens, a.loras, a.runs)))
 

@@ -118,7 +118,9 @@ class ReferenceRunner:
 
 
 # ---------------------------------------------------------------------------------- native
-TWO_CTA_DECODE = os.environ.get("ARTB_DECODE_2CTA", "1") != "0"
+# CTA-pair GEMMs at decode time: "1" = every projection, "wide" = only the unsplit (gate|up) ones, "0" = none
+_TWO_CTA_MODE = os.environ.get("ARTB_DECODE_2CTA", "1")
+TWO_CTA_DECODE = _TWO_CTA_MODE != "0"
 
 
 class EngineLinear:
@@ -212,6 +214,8 @@ class EngineLinear:
         Next = N + self.kpad if any_lora else N
         Wv = self.W_ext[:Next]
         bias = None if self.bias_ext is None else self.bias_ext[:Next]
+        if _TWO_CTA_MODE == "wide":
+            pair = pair and plan_small_m(M, Next, self.K, pair=True)[1] == 1
         bn, splits = plan_small_m(M, Next, self.K, pair=pair)
         y_ext = torch.empty((M, Next), dtype=torch.bfloat16, device=x.device)
         fuse_swiglu = swiglu_out is not None and not any_lora and splits == 1
