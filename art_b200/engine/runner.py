@@ -132,7 +132,9 @@ class EngineLinear:
     ``T (sB_all)^T``.  Large-M (prefill) calls use the extra-K form instead.
     """
 
-    def __init__(self, lin, member_rows: list[tuple[str, torch.Tensor]], r: int, max_loras: int, ws_holder: dict):
+    def __init__(self, lin, member_rows: list[tuple], r: int, max_loras: int, ws_holder: dict):
+        """``member_rows``: ``(module, rows)`` or ``(module, rows, out_slice, in_slice)``; the slices select this
+        tensor-parallel rank's part of the adapter's ``B`` rows / ``A`` columns (None = all)."""
         W = lin.W
         N, K = W.shape
         self.N, self.K = N, K
@@ -158,11 +160,17 @@ class EngineLinear:
         self.B_all[:, c0:c0 + self.cols].zero_()
         if state is None:
             return
-        for j, (module, rows) in enumerate(self.members):
+        for j, member in enumerate(self.members):
+            module, rows = member[0], member[1]
+            out_slice, in_slice = (member[2], member[3]) if len(member) > 2 else (None, None)
             ka = lora_key(layer, module, "A")
             if ka not in state:
                 continue
             a, b = state[ka], state[lora_key(layer, module, "B")]
+            if in_slice is not None:
+                a = a[:, in_slice]
+            if out_slice is not None:
+                b = b[out_slice]
             c = c0 + j * self.r
             self.A_all[c:c + self.r] = a           # device-to-device copy straight from the trainer's master buffer
             self.B_all[rows, c:c + self.r] = (b * scale).to(torch.bfloat16)
@@ -239,13 +247,40 @@ class EngineLinear:
 
 class NativeRunner:
     def __init__(self, cfg: ModelConfig, lora_cfg: LoraConfig, kv, *, decoder=None, base: dict | None = None,
-                 max_loras: int = 4, device="cuda"):
-        """``decoder``: a trainer-side NativeDecoder whose frozen weights are shared; else ``base`` weights."""
+                 max_loras: int = 4, device="cuda", tp_group=None):
+        """``decoder``: a trainer-side NativeDecoder whose frozen weights are shared; else ``base`` weights.
+
+        ``tp_group``: tensor-parallel replica.  Every rank of the group runs the same engine on the same requests
+        (same scheduler decisions, same seeds); this runner holds 1/T of the attention heads, of the FFN columns and
+        of the vocabulary: q|k|v and gate|up are column-parallel, o and down row-parallel (partial sums all-reduced,
+        the residual added on rank 0 only), the LM head is vocabulary-parallel (sampling statistics all-gathered and
+        merged, so every rank draws the same token).  ``kv`` must be sized for ``num_kv_heads / T`` heads.
+        The reference serves tensor-parallel models through vLLM (src/art/dev/engine.py: tensor_parallel_size)."""
+        import dataclasses
+
         from ..ops import elementwise as ew
 
+        self.full_cfg = cfg
+        self.tp_group = tp_group
+        self.tp = 1 if tp_group is None else torch.distributed.get_world_size(tp_group)
+        self.tp_rank = 0 if tp_group is None else torch.distributed.get_rank(tp_group)
+        T, tr = self.tp, self.tp_rank
+        if T > 1:
+            if decoder is not None or cfg.is_moe:
+                raise ValueError("tensor-parallel runners build their own dense weight shards from `base`")
+            if cfg.num_heads % T or cfg.num_kv_heads % T or cfg.intermediate_size % (16 * T) or cfg.vocab_size % (8 * T):
+                raise ValueError(f"heads, FFN width and vocabulary of {cfg.name} do not divide over {T} ranks")
+            cfg = dataclasses.replace(cfg, num_heads=cfg.num_heads // T, num_kv_heads=cfg.num_kv_heads // T,
+                                      intermediate_size=cfg.intermediate_size // T)
         self.cfg, self.lora_cfg, self.kv, self.max_loras = cfg, lora_cfg, kv, max_loras
         self.device = torch.device(device)
         dev, bf = self.device, torch.bfloat16
+        fc = self.full_cfg
+        sl_q = slice(tr * cfg.q_size, (tr + 1) * cfg.q_size) if T > 1 else None
+        sl_kv = slice(tr * cfg.kv_size, (tr + 1) * cfg.kv_size) if T > 1 else None
+        sl_f = slice(tr * cfg.intermediate_size, (tr + 1) * cfg.intermediate_size) if T > 1 else None
+        self.vocab_local = fc.vocab_size // T
+        self.vocab_offset = tr * self.vocab_local
         if decoder is None:
             from ..models.native import LoraLinear  # reuse the fused-weight construction without LoRA members
 
@@ -256,15 +291,26 @@ class NativeRunner:
 
             decoder = _Shim()
             decoder.embed = base["model.embed_tokens.weight"].to(dev, bf).contiguous()
-            decoder.lm_head = base["lm_head.weight"].to(dev, bf).contiguous()
+            decoder.lm_head = base["lm_head.weight"][self.vocab_offset:self.vocab_offset + self.vocab_local].to(dev, bf).contiguous()
             decoder.final_norm = base["model.norm.weight"].to(dev, bf).contiguous()
             decoder.layers = []
+            row_sl = {"self_attn.q_proj": sl_q, "self_attn.k_proj": sl_kv, "self_attn.v_proj": sl_kv,
+                      "mlp.gate_proj": sl_f, "mlp.up_proj": sl_f}
+            col_sl = {"self_attn.o_proj": sl_q, "mlp.down_proj": sl_f}
+
+            def shard(name: str, t: torch.Tensor) -> torch.Tensor:
+                if T == 1:
+                    return t
+                if name in row_sl:
+                    return t[row_sl[name]]
+                return t[:, col_sl[name]] if t.dim() == 2 else t
+
             for i in range(cfg.num_layers):
                 p = f"model.layers.{i}."
-                W = lambda n: base[p + n + ".weight"].to(dev, bf)  # noqa: E731
+                W = lambda n: shard(n, base[p + n + ".weight"]).to(dev, bf)  # noqa: E731
                 wqkv = torch.cat([W("self_attn.q_proj"), W("self_attn.k_proj"), W("self_attn.v_proj")], 0)
-                bqkv = (torch.cat([base[p + f"self_attn.{n}.bias"].to(dev) for n in ("q_proj", "k_proj", "v_proj")])
-                        if cfg.qkv_bias else None)
+                bqkv = (torch.cat([shard(f"self_attn.{n}", base[p + f"self_attn.{n}.bias"]).to(dev)
+                                   for n in ("q_proj", "k_proj", "v_proj")]) if cfg.qkv_bias else None)
                 layer = {"qkv": LoraLinear(wqkv, bqkv, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
                          "o": LoraLinear(W("self_attn.o_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
                          "gu": LoraLinear(ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj")), None, [],
@@ -286,14 +332,50 @@ class NativeRunner:
         self._ws_holder: dict = {}
         for i, L in enumerate(decoder.layers):
             self.layers.append({
-                "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q)), ("self_attn.k_proj", ar(q, q + kvw)),
-                                               ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw))], r, max_loras, self._ws_holder),
-                "o": EngineLinear(L["o"], [("self_attn.o_proj", ar(0, d))], r, max_loras, self._ws_holder),
-                "gu": EngineLinear(L["gu"], [("mlp.gate_proj", gate_rows), ("mlp.up_proj", gate_rows + 16)], r, max_loras, self._ws_holder),
-                "down": EngineLinear(L["down"], [("mlp.down_proj", ar(0, d))], r, max_loras, self._ws_holder),
+                "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q), sl_q, None),
+                                               ("self_attn.k_proj", ar(q, q + kvw), sl_kv, None),
+                                               ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw), sl_kv, None)],
+                                    r, max_loras, self._ws_holder),
+                "o": EngineLinear(L["o"], [("self_attn.o_proj", ar(0, d), None, sl_q)], r, max_loras, self._ws_holder),
+                "gu": EngineLinear(L["gu"], [("mlp.gate_proj", gate_rows, sl_f, None),
+                                             ("mlp.up_proj", gate_rows + 16, sl_f, None)], r, max_loras, self._ws_holder),
+                "down": EngineLinear(L["down"], [("mlp.down_proj", ar(0, d), None, sl_f)], r, max_loras, self._ws_holder),
                 "ln1": L["ln1"], "ln2": L["ln2"], "q_norm": L.get("q_norm"), "k_norm": L.get("k_norm"),
             })
         self.slot_loaded = [False] * max_loras
+        self.table_width: int | None = None    # fixed block-table width (else grown by doubling, which adds graph keys)
+
+    # -- tensor parallel ------------------------------------------------------------------------
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum the row-parallel partial products over the replica (in place; a no-op on one GPU)."""
+        if self.tp > 1:
+            torch.distributed.all_reduce(x, group=self.tp_group)
+        return x
+
+    def _res(self, x: torch.Tensor):
+        """The residual enters a row-parallel projection on one rank only: the all-reduce then adds it once."""
+        return x if self.tp_rank == 0 else None
+
+    def _sample(self, hidden, inv_t, seeds, restricted: bool, top_k=None, top_p=None, min_p=None):
+        from ..ops import paged
+
+        if self.tp == 1:
+            if restricted:
+                return paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, top_k, top_p, min_p)
+            return paged.sample(hidden, self.lm_head, inv_t, seeds)
+        dist = torch.distributed
+        if restricted:
+            from ..ops.gemm import gemm_tn
+
+            local = gemm_tn(hidden, self.lm_head, out_dtype=torch.float32)          # [M, V / T]
+            allv = torch.empty((self.tp,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+            dist.all_gather_into_tensor(allv, local, group=self.tp_group)
+            logits = allv.permute(1, 0, 2).reshape(local.shape[0], -1).contiguous()
+            return paged.sample_from_logits(logits, inv_t, seeds, top_k, top_p, min_p)
+        part = paged.sample_partials(hidden, self.lm_head, inv_t, seeds, self.vocab_offset)    # [splits, M, 8]
+        allp = torch.empty((self.tp * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(allp, part, group=self.tp_group)
+        return paged.sample_merge(allp)
 
     # -- adapters -----------------------------------------------------------------------------
     def set_adapter(self, slot: int, state: dict[str, torch.Tensor] | None) -> None:
@@ -314,7 +396,7 @@ class NativeRunner:
         h2, _ = ew.rmsnorm_fwd(x2, L["ln2"], self.cfg.rms_norm_eps, want_rstd=False)
         hact = torch.empty((x2.shape[0], self.cfg.intermediate_size), dtype=x2.dtype, device=x2.device)
         L["gu"](h2, adapter_ids, any_lora, swiglu_out=hact)
-        return L["down"](hact, adapter_ids, any_lora, residual=x2)
+        return self._reduce(L["down"](hact, adapter_ids, any_lora, residual=self._res(x2)))
 
     def _qkv(self, L, x, pos, adapter_ids, any_lora):
         from ..ops import elementwise as ew
@@ -386,7 +468,7 @@ class NativeRunner:
                 o = o_all.index_select(0, t_rows)
             else:
                 o, _ = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=False)
-            x2 = L["o"](o, t_ad, any_lora, residual=x)
+            x2 = self._reduce(L["o"](o, t_ad, any_lora, residual=self._res(x)))
             x = self._mlp(L, x2, t_ad, any_lora)
         return x, row_ranges
 
@@ -405,9 +487,9 @@ class NativeRunner:
             tk = torch.tensor([s.top_k for s in seqs], dtype=torch.int32, device=dev)
             tp = torch.tensor([s.top_p for s in seqs], dtype=torch.float32, device=dev)
             mp = torch.tensor([s.min_p for s in seqs], dtype=torch.float32, device=dev)
-            t, lp = paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, tk, tp, mp)
+            t, lp = self._sample(hidden, inv_t, seeds, True, tk, tp, mp)
         else:
-            t, lp = paged.sample(hidden, self.lm_head, inv_t, seeds)
+            t, lp = self._sample(hidden, inv_t, seeds, False)
         return t.tolist(), lp.tolist()
 
     def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
@@ -420,6 +502,14 @@ class NativeRunner:
         rows = torch.arange(n_prompt - 1, len(tokens) - 1, dtype=torch.int64, device=self.device)
         h, _ = ew.rmsnorm_fwd(ew.gather_rows(x, rows), self.final_norm, self.cfg.rms_norm_eps, want_rstd=False)
         tgt = torch.tensor(tokens[n_prompt:], dtype=torch.int32, device=self.device)
+        if self.tp > 1:      # rare path: gather the vocabulary shards of the logits and score in PyTorch
+            from ..ops.gemm import gemm_tn
+
+            local = gemm_tn(h, self.lm_head, out_dtype=torch.float32)
+            allv = torch.empty((self.tp,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+            torch.distributed.all_gather_into_tensor(allv, local, group=self.tp_group)
+            lp = torch.log_softmax(allv.permute(1, 0, 2).reshape(local.shape[0], -1), -1)
+            return lp.gather(-1, tgt.long().unsqueeze(-1)).squeeze(-1).tolist()
         part, _ = lpl.partials(h, self.lm_head, tgt)
         return lpl.grpo_tokens(part).logprobs.tolist()
 
@@ -466,14 +556,10 @@ class NativeRunner:
                 qkv = self._qkv(L, x, st["pos"], st["ad"], any_lora)
                 paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, st["slot"], self.kv.k[li], self.kv.v[li])
                 paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], st["bt"], st["ctx"], Hq, Hkv, hd, st["attn_out"], splits, ws)
-                x2 = L["o"](st["attn_out"], st["ad"], any_lora, residual=x)
+                x2 = self._reduce(L["o"](st["attn_out"], st["ad"], any_lora, residual=self._res(x)))
                 x = self._mlp(L, x2, st["ad"], any_lora)
             hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
-            if restricted:
-                t, lp = paged.sample_restricted(hidden, self.lm_head, st["inv_t"], st["seeds"][k], st["top_k"], st["top_p"],
-                                                st["min_p"])
-            else:
-                t, lp = paged.sample(hidden, self.lm_head, st["inv_t"], st["seeds"][k])
+            t, lp = self._sample(hidden, st["inv_t"], st["seeds"][k], restricted, st["top_k"], st["top_p"], st["min_p"])
             st["out_t"][k].copy_(t)
             st["out_l"][k].copy_(lp)
             if k + 1 < n_steps:
@@ -484,7 +570,7 @@ class NativeRunner:
         n = len(seqs)
         nb = next((b for b in self.BUCKETS if b >= n), (n + 255) // 256 * 256)
         need_blocks = max(len(s.blocks) for s in seqs)
-        max_blocks = 64
+        max_blocks = self.table_width or 64
         while max_blocks < need_blocks:
             max_blocks *= 2
         st = self._decode_state(nb, max_blocks, n_steps)

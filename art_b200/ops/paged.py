@@ -75,9 +75,11 @@ def decode_advance(sampled, tokens, pos, ctx_len, slot, block_table, block_size:
                                             _lib.ptr(active), tokens.numel(), _lib.stream_ptr()), "decode_advance")
 
 
-def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
-           vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
-    """Fused LM head + Gumbel-max sampling.  Returns (token int32 [M], logprob fp32 [M])."""
+def sample_partials(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
+                    vocab_offset: int = 0) -> torch.Tensor:
+    """Sampling statistics of one vocabulary shard: ``[splits, M, 8]`` fp32 (running max, sum of exponentials, best
+    perturbed score with its index and logit).  Partials of different shards concatenate along dim 0 and
+    :func:`sample_merge` reduces them, which is all a vocabulary-parallel LM head has to exchange."""
     M, K = hidden.shape
     V = lm_head.shape[0]
     splits = _f("artb_logprob_splits")(M, V)
@@ -86,11 +88,23 @@ def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, 
                                              _lib.ptr(inv_temp), _lib.ptr(row_seed), _lib.ptr(part), M, V, K, splits,
                                              vocab_offset, _lib.ptr(_lib.status_word(hidden.device)),
                                              _lib.stream_ptr()), "sample_partials")
-    tok = torch.empty(M, dtype=torch.int32, device=hidden.device)
-    lp = torch.empty(M, dtype=torch.float32, device=hidden.device)
-    _lib.check_rc(_f("artb_sample_merge")(_lib.ptr(part), splits, M, _lib.ptr(tok), _lib.ptr(lp), _lib.stream_ptr()),
+    return part
+
+
+def sample_merge(part: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Reduce ``[parts, M, 8]`` sampling statistics to (token int32 [M], logprob fp32 [M])."""
+    parts, M = part.shape[0], part.shape[1]
+    tok = torch.empty(M, dtype=torch.int32, device=part.device)
+    lp = torch.empty(M, dtype=torch.float32, device=part.device)
+    _lib.check_rc(_f("artb_sample_merge")(_lib.ptr(part), parts, M, _lib.ptr(tok), _lib.ptr(lp), _lib.stream_ptr()),
                   "sample_merge")
     return tok, lp
+
+
+def sample(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,
+           vocab_offset: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Fused LM head + Gumbel-max sampling.  Returns (token int32 [M], logprob fp32 [M])."""
+    return sample_merge(sample_partials(hidden, lm_head, inv_temp, row_seed, vocab_offset))
 
 
 def sample_restricted(hidden: torch.Tensor, lm_head: torch.Tensor, inv_temp: torch.Tensor, row_seed: torch.Tensor,

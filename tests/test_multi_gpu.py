@@ -647,6 +647,79 @@ def test_decode_gemm_allreduce_and_lora_handoff(tmp_path):
     assert res.returncode == 0 and "DECODE_TP_OK" in res.stdout
 
 
+TP_ENGINE_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from art_b200.engine.engine import Engine, SamplingParams
+from art_b200.engine.kv_cache import BlockManager, KVCache
+from art_b200.engine.runner import NativeRunner
+from art_b200.models.config import ModelConfig
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+from art_b200.ops import _lib
+
+cfg = ModelConfig(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                  head_dim=64, intermediate_size=512)
+base = {k: v.to(torch.bfloat16) for k, v in init_base_weights(cfg, seed=0).items()}
+lcfg = LoraConfig()
+lora = init_lora(cfg, lcfg)
+g = torch.Generator().manual_seed(5)
+for k in lora:
+    if "lora_B" in k: lora[k] = torch.randn(lora[k].shape, generator=g) * 0.05
+
+def make(tp_group):
+    T = 1 if tp_group is None else world
+    kv = KVCache(cfg.num_layers, 128, 16, cfg.num_kv_heads // T, cfg.head_dim, dev)
+    eng = Engine(NativeRunner(cfg, lcfg, kv, base=base, max_loras=2, device=dev, tp_group=tp_group),
+                 BlockManager(128, 16, True), eos_token_id=None, max_loras=2, num_scheduler_steps=4, kv_cache=kv)
+    eng.set_adapter("a", {k: v.to(dev) for k, v in lora.items()})
+    return eng
+
+one, tpe = make(None), make(dist.group.WORLD)
+prompts = [list(range(5, 40)), list(range(100, 117)), [7, 8, 9], list(range(300, 364))]
+def run(eng, params, adapter):
+    seqs = [eng.add_request(p, params, adapter) for p in prompts]
+    while not all(s.finished for s in seqs): eng.step()
+    return seqs
+for adapter in (None, "a"):
+    for params in (SamplingParams(max_tokens=24, temperature=0.0),
+                   SamplingParams(max_tokens=24, temperature=0.9, seed=77),
+                   SamplingParams(max_tokens=24, temperature=0.9, seed=78, top_k=8, top_p=0.9)):
+        a, b = run(one, params, adapter), run(tpe, params, adapter)
+        torch.cuda.synchronize(); _lib.check_status(dev)
+        for x, y in zip(a, b):
+            agree = sum(u == v for u, v in zip(x.output_ids, y.output_ids))
+            assert len(y.output_ids) == 24 and x.output_ids[0] == y.output_ids[0] and agree >= 12, (adapter, params, x.output_ids, y.output_ids)
+            assert abs(x.logprobs[0] - y.logprobs[0]) < 0.05, (x.logprobs[0], y.logprobs[0])
+        # every rank of the replica drew the same tokens
+        mine = torch.tensor([t for s in b for t in s.output_ids], device=dev)
+        ref = mine.clone(); dist.broadcast(ref, 0)
+        assert torch.equal(mine, ref), "ranks of one replica diverged"
+import asyncio
+lp_one = asyncio.run(one.score(prompts[0], [11, 12, 13], "a"))
+lp_tp = asyncio.run(tpe.score(prompts[0], [11, 12, 13], "a"))
+assert all(abs(u - v) < 0.05 for u, v in zip(lp_one, lp_tp)), (lp_one, lp_tp)
+dist.barrier()
+if rank == 0: print(f"TP_ENGINE_OK world={world}")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_engine_matches_single_gpu_engine(tmp_path):
+    script = tmp_path / "tp_engine_worker.py"
+    script.write_text(TP_ENGINE_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29529", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "TP_ENGINE_OK" in res.stdout
+
+
 FAILURE_WORKER = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["ARTB_ROOT"])
