@@ -99,6 +99,7 @@ def measure_decode(cfg, device, seqs: int = 256, prompt_len: int = 512, new_toke
             eng._release(s)
         eng.running = []
     _lib.check_status(dev)
+    runner.close()
     return res
 
 

@@ -345,6 +345,16 @@ class NativeRunner:
         self.slot_loaded = [False] * max_loras
         self.table_width: int | None = None    # fixed block-table width (else grown by doubling, which adds graph keys)
 
+    def close(self) -> None:
+        """Drop the captured decode graphs and their buffers.  A tensor-parallel runner must be closed before its
+        process group is destroyed: NCCL does not finish tearing down a communicator while CUDA graphs that captured
+        its collectives are alive."""
+        if hasattr(self, "_dgraphs"):
+            self._dgraphs.clear()
+            self._dstate.clear()
+            self._dseen.clear()
+        torch.cuda.synchronize(self.device) if self.device.type == "cuda" else None
+
     # -- tensor parallel ------------------------------------------------------------------------
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
         """Sum the row-parallel partial products over the replica (in place; a no-op on one GPU)."""

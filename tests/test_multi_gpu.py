@@ -706,7 +706,11 @@ lp_one = asyncio.run(one.score(prompts[0], [11, 12, 13], "a"))
 lp_tp = asyncio.run(tpe.score(prompts[0], [11, 12, 13], "a"))
 assert all(abs(u - v) < 0.05 for u, v in zip(lp_one, lp_tp)), (lp_one, lp_tp)
 dist.barrier()
-if rank == 0: print(f"TP_ENGINE_OK world={world}")
+if rank == 0: print(f"TP_ENGINE_OK world={world}", flush=True)
+# graphs that captured NCCL collectives must be gone before the communicator is torn down
+tpe.runner.close(); one.runner.close()
+del tpe, one
+import gc; gc.collect(); torch.cuda.synchronize()
 dist.destroy_process_group()
 '''
 
@@ -718,7 +722,7 @@ def test_tensor_parallel_engine_matches_single_gpu_engine(tmp_path):
     env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29529", str(script)]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     print(res.stdout[-3000:], res.stderr[-12000:])
     assert res.returncode == 0 and "TP_ENGINE_OK" in res.stdout
 
