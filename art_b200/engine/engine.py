@@ -198,6 +198,15 @@ class Engine:
     # -- requests ---------------------------------------------------------------------------------
     def add_request(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None,
                     loop: asyncio.AbstractEventLoop | None = None) -> Sequence:
+        seq = self._new_sequence(prompt_ids, params, adapter_name, loop)
+        with self._lock:
+            self.waiting.append(seq)
+        self._wake.set()
+        return seq
+
+    def _new_sequence(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None,
+                      loop: asyncio.AbstractEventLoop | None) -> Sequence:
+        """Validate a request and build its sequence (not yet queued)."""
         if self.error is not None:
             raise RuntimeError("engine stopped after an error") from self.error
         if len(prompt_ids) + 1 > self.max_model_len:
@@ -207,11 +216,7 @@ class Engine:
             if adapter_name not in self.adapters:
                 raise KeyError(f"unknown adapter {adapter_name!r}")
             adapter = self.adapters[adapter_name]
-        seq = Sequence(prompt_ids, params, adapter, loop)
-        with self._lock:
-            self.waiting.append(seq)
-        self._wake.set()
-        return seq
+        return Sequence(prompt_ids, params, adapter, loop)
 
     def abort(self, seq: Sequence) -> None:
         seq.aborted = True
