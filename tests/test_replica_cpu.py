@@ -71,3 +71,64 @@ def test_replica_engine_keeps_ranks_in_lockstep(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:], res.stderr[-6000:])
     assert res.returncode == 0 and "REPLICA_OK" in res.stdout
+
+
+SHARD_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+from art_b200.engine.runner import NativeRunner
+from art_b200.models.config import ModelConfig
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora, lora_key
+
+cfg = ModelConfig(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                  head_dim=64, intermediate_size=512)
+base = {k: v.to(torch.bfloat16) for k, v in init_base_weights(cfg, seed=0).items()}
+lcfg = LoraConfig()
+lora = init_lora(cfg, lcfg)
+g = torch.Generator().manual_seed(5)
+for k in lora:
+    if "lora_B" in k: lora[k] = torch.randn(lora[k].shape, generator=g) * 0.05
+full = NativeRunner(cfg, lcfg, None, base=base, max_loras=2, device="cpu")
+part = NativeRunner(cfg, lcfg, None, base=base, max_loras=2, device="cpu", tp_group=dist.group.WORLD)
+full.set_adapter(1, lora); part.set_adapter(1, lora)
+T, r = world, rank
+assert (part.cfg.num_heads, part.cfg.num_kv_heads, part.cfg.intermediate_size) == (4 // T, 2 // T, 512 // T)
+ql, kl, fl = part.cfg.q_size, part.cfg.kv_size, part.cfg.intermediate_size
+q, kv = cfg.q_size, cfg.kv_size
+assert torch.equal(part.lm_head, full.lm_head[r * 2048 // T:(r + 1) * 2048 // T]) and part.vocab_offset == r * 2048 // T
+for li in range(cfg.num_layers):
+    F, P = full.layers[li], part.layers[li]
+    rows = torch.cat([torch.arange(r * ql, (r + 1) * ql), q + torch.arange(r * kl, (r + 1) * kl),
+                      q + kv + torch.arange(r * kl, (r + 1) * kl)])
+    assert torch.equal(P["qkv"].W, F["qkv"].W[rows]) and torch.equal(P["qkv"].bias_ext[:len(rows)], F["qkv"].bias_ext[rows])
+    assert torch.equal(P["qkv"].B_all, F["qkv"].B_all[rows]) and torch.equal(P["qkv"].A_all, F["qkv"].A_all)
+    assert torch.equal(P["o"].W, F["o"].W[:, r * ql:(r + 1) * ql])
+    assert torch.equal(P["o"].A_all, F["o"].A_all[:, r * ql:(r + 1) * ql]) and torch.equal(P["o"].B_all, F["o"].B_all)
+    # gate|up rows are interleaved in blocks of 16: block b of this rank is block r * (fl / 16) + b of the full layer
+    blocks = torch.arange(r * fl // 16, (r + 1) * fl // 16)
+    gu_rows = (blocks.unsqueeze(1) * 32 + torch.arange(32)).reshape(-1)
+    assert torch.equal(P["gu"].W, F["gu"].W[gu_rows]) and torch.equal(P["gu"].B_all, F["gu"].B_all[gu_rows])
+    assert torch.equal(P["down"].W, F["down"].W[:, r * fl:(r + 1) * fl])
+    assert torch.equal(P["down"].A_all, F["down"].A_all[:, r * fl:(r + 1) * fl])
+    # row-parallel LoRA needs no exchange: the partial shrink products add up to the full one
+    x = torch.randn(3, cfg.q_size, generator=torch.Generator().manual_seed(li)).to(torch.bfloat16)
+    t_part = x[:, r * ql:(r + 1) * ql].float() @ P["o"].A_all.float().t()
+    dist.all_reduce(t_part)
+    assert torch.allclose(t_part, x.float() @ F["o"].A_all.float().t(), atol=1e-3)
+dist.barrier()
+if rank == 0: print("SHARDS_OK")
+dist.destroy_process_group()
+'''
+
+
+def test_tensor_parallel_runner_shards_reassemble(tmp_path):
+    script = tmp_path / "shard_worker.py"
+    script.write_text(SHARD_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29633", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    print(res.stdout[-3000:], res.stderr[-6000:])
+    assert res.returncode == 0 and "SHARDS_OK" in res.stdout
