@@ -12,6 +12,12 @@ vocabulary-parallel sampler already returns identical tokens on all ranks).  Fol
 ``follow()`` until the leader shuts down.  An idle leader sends a keep-alive tick so that followers
 never run into the group's collective timeout.
 
+Failure detection: every tick ends with a one-integer all-reduce over the control group in which a
+rank that raised (a bad adapter, an allocation failure, a kernel status error) reports it.  The
+failing rank re-raises its own exception, the others raise ``ReplicaError`` at the same tick, so
+nobody is left waiting in a later broadcast.  (A rank that dies inside a step that contains GPU
+collectives is caught by the collective library's own timeout, not here.)
+
 The reference reaches multi-GPU serving through vLLM's own executor (src/art/dev/engine.py:
 tensor_parallel_size); this is the equivalent for the native engine.
 """
@@ -24,6 +30,10 @@ import torch
 import torch.distributed as dist
 
 from .engine import Engine, SamplingParams, Sequence
+
+
+class ReplicaError(RuntimeError):
+    """A rank of the replica failed while applying commands or stepping; the replica must be rebuilt."""
 
 
 class _NoLoop:
@@ -162,14 +172,29 @@ class ReplicaEngine(Engine):
         dist.broadcast_object_list(box, src=self.leader_rank, group=self.ctrl)
         msg = box[0]
         self._last_tick = time.monotonic()
-        for cmd in msg["cmds"]:
-            self._apply(cmd)
-        if len(self._seq_of) > 4096:             # forget finished requests
-            self._seq_of = {r: q for r, q in self._seq_of.items() if not (isinstance(q, Sequence) and q.finished)}
-        if msg["stop"]:
-            self._stop = True
-            return False
-        return Engine.step(self) if msg["step"] else False
+        worked, failure = False, None
+        try:
+            if self.error is not None:
+                raise ReplicaError("this replica already failed") from self.error
+            for cmd in msg["cmds"]:
+                self._apply(cmd)
+            if len(self._seq_of) > 4096:             # forget finished requests
+                self._seq_of = {r: q for r, q in self._seq_of.items() if not (isinstance(q, Sequence) and q.finished)}
+            if msg["stop"]:
+                self._stop = True
+            elif msg["step"]:
+                worked = Engine.step(self)
+        except BaseException as e:  # noqa: BLE001 - reported to the peers below, then re-raised
+            failure = e
+        flag = torch.tensor([0 if failure is None else 1], dtype=torch.int32)
+        dist.all_reduce(flag, group=self.ctrl)
+        if failure is not None:
+            self.error = failure
+            raise failure
+        if int(flag.item()):
+            self.error = ReplicaError(f"{int(flag.item())} other rank(s) of the replica failed in this step")
+            raise self.error
+        return worked
 
     def step(self) -> bool:
         self._leader_only()
@@ -189,7 +214,8 @@ class ReplicaEngine(Engine):
     def shutdown(self) -> None:
         if self.is_leader:
             super().shutdown()                   # parks and joins the stepping thread, if any
-            with self._step_lock:
-                self._tick(step=False, stop=True)
+            if self.error is None:               # after a failure the followers have already left follow()
+                with self._step_lock:
+                    self._tick(step=False, stop=True)
         else:
             self._stop = True

@@ -73,6 +73,68 @@ def test_replica_engine_keeps_ranks_in_lockstep(tmp_path):
     assert res.returncode == 0 and "REPLICA_OK" in res.stdout
 
 
+FAIL_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+from art_b200.engine.engine import SamplingParams
+from art_b200.engine.kv_cache import BlockManager
+from art_b200.engine.replica import ReplicaEngine, ReplicaError
+from art_b200.engine.runner import ReferenceRunner
+from art_b200.models.config import PRESETS
+from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+
+cfg = PRESETS["tiny"]
+runner = ReferenceRunner(cfg, init_base_weights(cfg, seed=0), LoraConfig(), max_loras=2)
+if rank == 1:                                    # this rank cannot load the second adapter (host-side failure)
+    good = runner.set_adapter
+    def flaky(slot, state):
+        if slot == 1 and state is not None: raise MemoryError("no room for the adapter on this rank")
+        return good(slot, state)
+    runner.set_adapter = flaky
+eng = ReplicaEngine(runner, BlockManager(64, 4, True), ctrl_group=dist.group.WORLD, eos_token_id=None, max_loras=2,
+                    num_scheduler_steps=4)
+lora = init_lora(cfg, LoraConfig())
+seen = None
+if rank == 0:
+    eng.set_adapter("a", lora)
+    s = eng.generate_sync([1, 2, 3], SamplingParams(max_tokens=4, temperature=0.0), "a")
+    assert len(s.output_ids) == 4
+    try:
+        eng.set_adapter("b", lora)
+    except ReplicaError as e:
+        seen = "leader: " + str(e)
+    try:
+        eng.add_request([1, 2], SamplingParams())
+    except RuntimeError:
+        seen += " | refuses new work"
+    eng.shutdown()                               # no tick after a failure: nobody is listening any more
+else:
+    try:
+        eng.follow()
+    except MemoryError as e:
+        seen = "follower: " + str(e)
+allseen = [None] * world
+dist.all_gather_object(allseen, seen)
+assert allseen[0].startswith("leader: 1 other rank") and allseen[0].endswith("refuses new work"), allseen
+assert allseen[1].startswith("follower: no room"), allseen
+if rank == 0: print("REPLICA_FAILURE_OK", allseen)
+dist.destroy_process_group()
+'''
+
+
+def test_replica_failure_reaches_every_rank(tmp_path):
+    script = tmp_path / "replica_fail_worker.py"
+    script.write_text(FAIL_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29635", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    print(res.stdout[-3000:], res.stderr[-6000:])
+    assert res.returncode == 0 and "REPLICA_FAILURE_OK" in res.stdout
+
+
 SHARD_WORKER = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["ARTB_ROOT"])
