@@ -12,8 +12,11 @@ staging buffers, flags) and drives the kernels of ``csrc/comm/moe_dispatch.cu`` 
     out   = ops.moe.combine(yr, plan, ...)           # weighted sum over each token's k experts
 
 The backward pass dispatches ``w * dY`` and returns ``dX`` through the same calls with the saved
-``rplan``.  Capacity: the receive buffer holds ``capacity_factor * M * k`` rows (plus padding);
-a routing that needs more raises ``KernelStatusError`` (overflow) at the next status check.
+``rplan``.  Capacity: the receive buffer holds ``capacity_factor * M * k`` rows (plus padding).  Rows
+routed to an owner beyond that are dropped by their senders: they contribute zero to the layer (and
+receive a zero gradient), every owner-side offset is clipped to the buffer, and ``dropped_rows()``
+counts them.  With ``drop_overflow=False`` (default) such a call also raises ``KernelStatusError``
+(overflow) at the next status check; ``True`` is capacity-factor training as in GShard-style MoE.
 
 The reference has no expert parallelism (dense models only).  ``reference_dispatch`` is the
 ``all_to_all_single`` restatement used by the tests.
@@ -185,8 +188,8 @@ class ExpertParallel:
         out = torch.empty((plan.cap_rows, D), dtype=torch.bfloat16, device=self.device)
         rc = _k().artb_ep_ret_finish(self.buf._h, self.off_ret[par], self.off_rflag, self.off_rdone, self.E, D,
                                      _lib.ptr(plan.row_token), _lib.ptr(plan.seg_off), _lib.ptr(plan.tile_expert),
-                                     _lib.ptr(rp.send_off), self.cap_recv_rows, _lib.ptr(out), out.stride(0), plan.cap_rows, self.r_epoch, self.wait_ms,
-                                     self._status(), self.counters[2:3].data_ptr(), st)
+                                     _lib.ptr(rp.send_off), self.cap_recv_rows, _lib.ptr(out), out.stride(0), plan.cap_rows,
+                                     self.r_epoch, self.wait_ms, self._status(), self.counters[2:3].data_ptr(), st)
         _lib.check_rc(rc, "ep_ret_finish")
         return out
 
