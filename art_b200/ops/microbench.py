@@ -137,6 +137,36 @@ def bench_moe(a) -> dict:
     return res
 
 
+def bench_sampler(a) -> dict:
+    """LM head + sampling for one decode step: the fused Gumbel-max epilogue against the top-k / top-p path (fp32
+    logits GEMM + radix-select kernel) and, as the library baseline, cuBLAS logits + torch softmax / multinomial."""
+    from . import _lib, paged
+    from .gemm import gemm_tn
+
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    M, K, V = a.rows, a.k, a.vocab
+    hid = (torch.randn(M, K, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    head = (torch.randn(V, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    it = torch.ones(M, device=dev)
+    sd = torch.arange(M, dtype=torch.int32, device=dev)
+    tk = torch.full((M,), a.top_k, dtype=torch.int32, device=dev)
+    tp = torch.full((M,), a.top_p, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
+    logits = gemm_tn(hid, head, out_dtype=torch.float32)
+    out = {"op": "sampler", "rows": M, "k": K, "vocab": V, "top_k": a.top_k, "top_p": a.top_p,
+           "fused_ms": round(_time(lambda: paged.sample(hid, head, it, sd), a.iters, a.warmup, flush), 4),
+           "restricted_ms": round(_time(lambda: paged.sample_restricted(hid, head, it, sd, tk, tp), a.iters, a.warmup, flush), 4),
+           "select_kernel_ms": round(_time(lambda: paged.sample_from_logits(logits, it, sd, tk, tp), a.iters, a.warmup, flush), 4)}
+    if not a.no_baseline:
+        def lib():
+            p = torch.softmax((hid @ head.t()).float(), -1)
+            return torch.multinomial(p, 1)
+        out["cublas_softmax_multinomial_ms"] = round(_time(lib, a.iters, a.warmup, flush), 4)
+    _lib.check_status(dev)
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -158,13 +188,19 @@ def main() -> None:
     m.add_argument("--topk", type=int, default=8)
     m.add_argument("--d-model", type=int, default=2048)
     m.add_argument("--ffn", type=int, default=768)
-    for p in (g, t, m):
+    sp = sub.add_parser("sampler")
+    sp.add_argument("--rows", type=int, default=256)
+    sp.add_argument("--k", type=int, default=3584)
+    sp.add_argument("--vocab", type=int, default=152064)
+    sp.add_argument("--top-k", type=int, default=50)
+    sp.add_argument("--top-p", type=float, default=0.9)
+    for p in (g, t, m, sp):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm}[a.op](a)))
+    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler}[a.op](a)))
 
 
 if __name__ == "__main__":
