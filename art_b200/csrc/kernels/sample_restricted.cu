@@ -44,6 +44,27 @@ __device__ __forceinline__ uint32_t order_key(float x) {
   return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);   // larger float <=> larger unsigned key
 }
 
+// f(index, raw logit) over one row, block-strided; 16-byte loads when the row allows it (each thread still visits its
+// indices in ascending order).
+template <class F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ x, int V, bool vec, F f) {
+  const int tid = threadIdx.x;
+  if (vec) {
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int n4 = V >> 2;
+    for (int i = tid; i < n4; i += SR_THREADS) {
+      const float4 q = x4[i];
+      f(4 * i, q.x);
+      f(4 * i + 1, q.y);
+      f(4 * i + 2, q.z);
+      f(4 * i + 3, q.w);
+    }
+    for (int v = (n4 << 2) + tid; v < V; v += SR_THREADS) f(v, x[v]);
+  } else {
+    for (int v = tid; v < V; v += SR_THREADS) f(v, x[v]);
+  }
+}
+
 __device__ float block_max(float v, SrShared& s) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -77,7 +98,7 @@ __device__ float block_sum(float v, SrShared& s) {
 // Largest key t such that the total weight of {v : key_v >= max(t, floor_key)} reaches `target`; weight = 1 (MASS =
 // false: t is the target-th largest key) or exp(x - mx).  Four passes of 8 bits from the top.
 template <bool MASS>
-__device__ uint32_t radix_select(const float* __restrict__ x, int V, float sc, float mx, uint32_t floor_key,
+__device__ uint32_t radix_select(const float* __restrict__ x, int V, bool vec, float sc, float mx, uint32_t floor_key,
                                  float target, SrShared& s) {
   const int tid = threadIdx.x, warp = tid >> 5;
   uint32_t prefix = 0;
@@ -86,12 +107,12 @@ __device__ uint32_t radix_select(const float* __restrict__ x, int V, float sc, f
     for (int i = tid; i < SR_WARPS * 256; i += SR_THREADS) (&s.hist[0][0])[i] = 0.f;
     __syncthreads();
     const uint32_t himask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-    for (int v = tid; v < V; v += SR_THREADS) {
-      const float xs = x[v] * sc;
+    for_each_logit(x, V, vec, [&](int, float raw) {
+      const float xs = raw * sc;
       const uint32_t key = order_key(xs);
       if (key >= floor_key && (key & himask) == prefix)
         atomicAdd(&s.hist[warp][(key >> shift) & 255u], MASS ? __expf(xs - mx) : 1.f);
-    }
+    });
     __syncthreads();
     if (tid < 256) {
       float t = 0.f;
@@ -138,11 +159,12 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
   const float it = inv_temp[row];
   const bool greedy = it == 0.f;
   const float sc = greedy ? 1.f : it;
+  const bool vec = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   float lm = -INFINITY;
-  for (int v = tid; v < V; v += SR_THREADS) lm = fmaxf(lm, x[v] * sc);
+  for_each_logit(x, V, vec, [&](int, float raw) { lm = fmaxf(lm, raw * sc); });
   const float mx = block_max(lm, s);
   float ls = 0.f;
-  for (int v = tid; v < V; v += SR_THREADS) ls += __expf(x[v] * sc - mx);
+  for_each_logit(x, V, vec, [&](int, float raw) { ls += __expf(raw * sc - mx); });
   const float Z = block_sum(ls, s);
 
   uint32_t tau = 0u;
@@ -152,20 +174,20 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
     const float mp = min_p ? min_p[row] : 0.f;
     if (mp > 0.f) tau = order_key(mx + __logf(fminf(mp, 1.f)));
     if (k > 0 && k < V) {
-      const uint32_t tk = radix_select<false>(x, V, sc, mx, 0u, static_cast<float>(k), s);
+      const uint32_t tk = radix_select<false>(x, V, vec, sc, mx, 0u, static_cast<float>(k), s);
       tau = tk > tau ? tk : tau;
     }
     if (p < 1.f) {
       float Zk = Z;
       if (tau) {
         float part = 0.f;
-        for (int v = tid; v < V; v += SR_THREADS) {
-          const float xs = x[v] * sc;
+        for_each_logit(x, V, vec, [&](int, float raw) {
+          const float xs = raw * sc;
           if (order_key(xs) >= tau) part += __expf(xs - mx);
-        }
+        });
         Zk = block_sum(part, s);
       }
-      const uint32_t tp = radix_select<true>(x, V, sc, mx, tau, fmaxf(p, 0.f) * Zk, s);
+      const uint32_t tp = radix_select<true>(x, V, vec, sc, mx, tau, fmaxf(p, 0.f) * Zk, s);
       tau = tp > tau ? tp : tau;
     }
   }
@@ -173,9 +195,9 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
   const uint32_t seed = row_seed[row];
   float best = -INFINITY, best_x = 0.f;
   int best_i = -1;
-  for (int v = tid; v < V; v += SR_THREADS) {
-    const float xs = x[v] * sc;
-    if (order_key(xs) < tau) continue;
+  for_each_logit(x, V, vec, [&](int v, float raw) {
+    const float xs = raw * sc;
+    if (order_key(xs) < tau) return;
     float score = xs;
     if (!greedy) score += gumbel_noise(seed, static_cast<uint32_t>(row), static_cast<uint32_t>(vocab_offset + v));
     if (score > best) {
@@ -183,7 +205,7 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
       best_x = xs;
       best_i = v;
     }
-  }
+  });
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
     const float ob = __shfl_xor_sync(0xffffffffu, best, o);
