@@ -77,6 +77,13 @@ class ModelState:
         if last and os.path.exists(os.path.join(last, TRAINER_STATE)):
             self.trainer.load_trainer_state(torch.load(os.path.join(last, TRAINER_STATE), map_location="cpu"))
         # rollout engine
+        if int(engine_args.get("tensor_parallel_size") or 1) > 1:
+            import warnings
+
+            # this service time-shares ONE GPU between its trainer and its engine; a tensor-parallel replica is a
+            # separate set of processes (one per GPU) built from NativeRunner(tp_group=...) + ReplicaEngine
+            warnings.warn("engine_args.tensor_parallel_size > 1 is not applied by the in-process service: the model "
+                          "is served from this process's GPU", stacklevel=2)
         block_size = int(engine_args.get("block_size") or 16)
         max_loras = int(engine_args.get("max_loras", 4))
         max_len = int(engine_args.get("max_model_len") or init_args.get("max_seq_length", 32768))
