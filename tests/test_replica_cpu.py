@@ -194,3 +194,52 @@ def test_tensor_parallel_runner_shards_reassemble(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:], res.stderr[-6000:])
     assert res.returncode == 0 and "SHARDS_OK" in res.stdout
+
+
+def test_serve_replica_launcher_answers_http(tmp_path):
+    """Two gloo ranks (reference runner): rank 0 serves HTTP over the replica engine, rank 1 follows."""
+    import time
+
+    import httpx
+
+    port = 18731
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29637", "-m", "art_b200.engine.serve_replica", "--reference", "--model", "tiny",
+           "--host", "127.0.0.1", "--port", str(port), "--num-blocks", "256", "--block-size", "4",
+           "--num-scheduler-steps", "2", "--max-model-len", "512"]
+    log = open(tmp_path / "serve.log", "w")
+    proc = subprocess.Popen(cmd, env=dict(os.environ, PYTHONPATH=ROOT), stdout=log, stderr=subprocess.STDOUT, cwd=ROOT)
+    try:
+        hdr = {"Authorization": "Bearer default"}
+        base = f"http://127.0.0.1:{port}"
+        ok = False
+        for _ in range(240):
+            if proc.poll() is not None:
+                break
+            try:
+                ok = httpx.get(base + "/v1/models", headers=hdr, timeout=2).status_code == 200
+            except httpx.HTTPError:
+                ok = False
+            if ok:
+                break
+            time.sleep(0.5)
+        assert ok, open(tmp_path / "serve.log").read()[-3000:]
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "n": 2, "seed": 3}
+        r = httpx.post(base + "/v1/chat/completions", headers=hdr, json=body, timeout=120)
+        assert r.status_code == 200, r.text
+        d = r.json()
+        assert len(d["choices"]) == 2 and d["usage"]["completion_tokens"] >= 2
+        again = httpx.post(base + "/v1/chat/completions", headers=hdr, json=body, timeout=120).json()
+        pick = lambda x: [[e["token"] for e in c["logprobs"]["content"]] for c in x["choices"]]  # noqa: E731
+        assert pick(again) == pick(d)                       # same seed -> same tokens, on a replica too
+        g = dict(body, n=1, guided_choice=["yes", "no"], temperature=0)
+        r = httpx.post(base + "/v1/chat/completions", headers=hdr, json=g, timeout=120)
+        assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"] in ("yes", "no")
+        assert proc.poll() is None                          # both ranks still alive after scoring jobs
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+        log.close()
