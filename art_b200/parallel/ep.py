@@ -205,6 +205,54 @@ class ExpertParallel:
         self.buf.close()
 
 
+def reference_exchange_layout(cnt_all: torch.Tensor, rank: int, cap_tiles: int) -> dict[str, torch.Tensor]:
+    """Plain-Python restatement of the offsets the exchange kernel derives on ``rank`` from the gathered counts
+    ``cnt_all`` [P, E] (tokens of source s routed to expert e), for a receive buffer of ``cap_tiles`` 128-row tiles.
+
+    * ``send_off[e]``: row in the owner's receive buffer where this rank's rows for expert e start (sources are laid
+      out in rank order inside an expert's segment, segments are padded to 128 rows);
+    * owner side, clipped to the capacity: ``seg_off`` [El + 1], ``real_rows`` [El], ``tile_expert`` [cap_tiles]
+      (-1 beyond the last segment), ``src_start`` [El, P] (first row of source s inside segment j) and
+      ``src_seg_off`` [P, El] (where expert j's segment starts in source s's own sorted order).
+    A sender drops row i of expert e when ``send_off[e] + i >= cap_tiles * 128``; the clipped ``real_rows`` are exactly
+    the rows that were not dropped."""
+    cnt = cnt_all.to(torch.int64).cpu()
+    P, E = cnt.shape
+    El = E // P
+    cap = cap_tiles * 128
+    pad = lambda n: (int(n) + 127) // 128 * 128  # noqa: E731
+    send_off = torch.zeros(E, dtype=torch.int64)
+    for e in range(E):
+        owner, j = divmod(e, El)
+        seg = sum(pad(cnt[:, owner * El + j2].sum()) for j2 in range(j))
+        send_off[e] = seg + int(cnt[:rank, e].sum())
+    seg_off = torch.zeros(El + 1, dtype=torch.int64)
+    real = torch.zeros(El, dtype=torch.int64)
+    src_start = torch.zeros(El, P, dtype=torch.int64)
+    src_seg_off = torch.zeros(P, El, dtype=torch.int64)
+    seg = 0
+    for j in range(El):
+        e = rank * El + j
+        tot = int(cnt[:, e].sum())
+        seg_c = min(seg, cap)
+        seg_off[j] = seg_c
+        real[j] = min(tot, cap - seg_c)
+        run = 0
+        for s_ in range(P):
+            src_start[j, s_] = run
+            run += int(cnt[s_, e])
+            src_seg_off[s_, j] = sum(pad(cnt[s_, e2]) for e2 in range(e))
+        seg += pad(tot)
+    seg_off[El] = max(min(seg, cap), int(seg_off[El - 1]))
+    tile_expert = torch.full((cap_tiles,), -1, dtype=torch.int64)
+    for t in range(cap_tiles):
+        row = t * 128
+        if row < int(seg_off[El]):
+            tile_expert[t] = max(j for j in range(El) if int(seg_off[j]) <= row)
+    return {"send_off": send_off, "seg_off": seg_off, "real_rows": real, "tile_expert": tile_expert,
+            "src_start": src_start, "src_seg_off": src_seg_off}
+
+
 def reference_dispatch(x: torch.Tensor, topi: torch.Tensor, num_experts: int, group=None):
     """NCCL restatement: returns (rows for my experts sorted by (expert, source, token order), expert id per row)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
