@@ -202,7 +202,11 @@ def test_serve_replica_launcher_answers_http(tmp_path):
 
     import httpx
 
-    port = 18731
+    import socket
+
+    with socket.socket() as sk:                             # a port nobody listens on right now
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29637", "-m", "art_b200.engine.serve_replica", "--reference", "--model", "tiny",
            "--host", "127.0.0.1", "--port", str(port), "--num-blocks", "256", "--block-size", "4",
