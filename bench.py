@@ -204,16 +204,12 @@ def main():
         if world % T:
             print("bench.py: --tp-size must divide the number of GPUs", file=sys.stderr)
             return 2
-        for g0 in range(0, world, T):                       # every rank creates every group, in the same order
-            g = dist.new_group(list(range(g0, g0 + T)))
-            if g0 <= rank < g0 + T:
-                tp_group = g
-        dp_group = None
-        for j in range(T):
-            g = dist.new_group(list(range(j, world, T)))
-            if rank % T == j:
-                dp_group = g
-        data_ranks, data_index = world // T, rank // T
+        from art_b200.parallel.mesh import ParallelLayout
+
+        layout = ParallelLayout(world, tp=T)                # TP innermost: ranks (2i, 2i+1) share activations
+        groups = layout.create_groups(rank)                 # every rank creates every group, in the same order
+        tp_group, dp_group = groups["tp"], groups["dp"]
+        data_index, data_ranks = layout.data_shard(rank)
         sync_name = f"fused-p2p-allreduce(sum over tp{T})"
         if data_ranks > 1:
             from art_b200.parallel.symm_mem import FusedGradAllReduce
