@@ -353,7 +353,8 @@ class NativeRunner:
             self._dgraphs.clear()
             self._dstate.clear()
             self._dseen.clear()
-        torch.cuda.synchronize(self.device) if self.device.type == "cuda" else None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     # -- tensor parallel ------------------------------------------------------------------------
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:
