@@ -47,15 +47,13 @@ static int launch_rs(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
 
 using namespace artb;
 
-extern "C" int artb_pick_bn(int M, int N, int ctas);
-
 // h            symmetric buffer handle; byte offsets into its data area, identical on every rank:
 //              off_stage bf16 [world-1][m_seg][N], off_flag uint32 [world-1][tile_cap][4],
 //              off_done uint32 [world]
 // A, B         local operands [world*m_seg, K] and [N, K] (K = this rank's slice of the reduction dim)
 // A2, B2, K2   optional extra-K pair (LoRA partial), K2 multiple of 8
 // out, R       bf16 [m_seg, N] result shard and optional residual shard
-// tile_cap     flags per staging slot; >= (m_seg/128) * ceil(N/224)
+// tile_cap     flags per staging slot; >= (m_seg/128) * ceil(N/256)
 ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off_done, int tile_cap, const void* A,
                                 int lda, const void* B, int ldb, const void* A2, int lda2, const void* B2, int ldb2,
                                 int K2, void* out, int ldc, const void* R, int ldr, int m_seg, int N, int K,
@@ -69,8 +67,7 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   const int world = s->world, M = world * m_seg;
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
-  int bn = artb_pick_bn(M, N, cap);   // same inputs on every rank -> same tiling on every rank
-  if (bn != 224) bn = 256;   // 224 only if the tile chooser ever asks for it
+  const int bn = 256;   // EpiReduceScatter pairs 32-column slabs: the tile width must be a multiple of 64
   const int n_tiles = (N + bn - 1) / bn;
   if ((m_seg / GEMM_BM) * n_tiles > tile_cap) return ERR_TOO_LARGE;
   CUtensorMap tA, tB, tA2, tB2;
@@ -117,10 +114,5 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   comm.cta_counter = cta_counter;
   SchedSegRot sched{m_seg / GEMM_BM, n_tiles, world, s->rank, 1};
   const int kb_main = (K + GEMM_BK - 1) / GEMM_BK, kb_extra = (K2 + GEMM_BK - 1) / GEMM_BK;
-  if (bn == 224) {
-    EpiReduceScatter<224> e224;
-    memcpy(&e224, &epi, sizeof(epi));   // the policy's fields do not depend on BN
-    return launch_rs<224, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, e224, comm, status, max_ctas, stream);
-  }
   return launch_rs<256, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, comm, status, max_ctas, stream);
 }

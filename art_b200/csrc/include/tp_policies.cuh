@@ -162,6 +162,8 @@ struct RsComm {
 
 template <int BN>
 struct EpiReduceScatter {
+  // remote tiles leave through a shared-memory slab that is flushed after every SECOND 32-column chunk
+  static_assert(BN % 64 == 0, "EpiReduceScatter needs an even number of 32-column chunks per tile");
   TpPeers pt;
   long off_stage, off_flag, off_done;
   __nv_bfloat16* out;

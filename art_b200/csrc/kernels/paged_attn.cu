@@ -333,15 +333,17 @@ ARTB_EXPORT int artb_paged_decode(const void* q, int ldq, const void* k_cache, c
                                   int num_seqs, int Hq, int Hkv, int hd, void* out, int ldo, float* ws, int splits,
                                   cudaStream_t st) {
   if (num_seqs <= 0) return 0;
-  if (Hq % Hkv || Hq / Hkv > 16 || splits < 1 || (splits > 1 && !ws)) return ERR_BAD_SHAPE;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || splits < 1 || (splits > 1 && !ws)) return ERR_BAD_SHAPE;
+  int dev_ = 0;
+  if (cudaGetDevice(&dev_) != cudaSuccess || dev_ < 0 || dev_ >= 64) return ERR_BAD_SHAPE;
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   dim3 grid(num_seqs, Hkv, splits);
 #define ARTB_PD(HD_)                                                                                             \
   {                                                                                                              \
-    static bool cfgd = false;                                                                                    \
-    if (!cfgd) {                                                                                                 \
+    static bool cfgd[64] = {false};   /* the attribute is per device */                                          \
+    if (!cfgd[dev_]) {                                                                                           \
       cudaFuncSetAttribute(paged_decode_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<HD_>()); \
-      cfgd = true;                                                                                               \
+      cfgd[dev_] = true;                                                                                         \
     }                                                                                                            \
     paged_decode_kernel<HD_><<<grid, 128, decode_smem<HD_>(), st>>>((const bf16*)q, ldq, (const bf16*)k_cache,   \
         (const bf16*)v_cache, block_table, max_blocks, ctx_len, block_size, Hq, Hkv, (bf16*)out, ldo, ws, splits, \
@@ -391,7 +393,7 @@ ARTB_EXPORT int artb_paged_decode_noalloc(const void* q, int ldq, const void* k_
                                           int num_seqs, int Hq, int Hkv, int hd, void* out, int ldo, int splits,
                                           cudaStream_t st) {
   if (num_seqs <= 0) return 0;
-  if (splits < 1 || hd <= 0 || Hq <= 0) return ERR_BAD_SHAPE;
+  if (splits < 1 || hd <= 0 || Hq <= 0 || Hkv <= 0) return ERR_BAD_SHAPE;
   const long need = (long)num_seqs * Hq * splits * (hd + 2);
   if (need > (long)ARTB_DECODE_STATIC_WS_FLOATS) return ERR_TOO_LARGE;
   int err = 0;

@@ -61,6 +61,7 @@ class Sequence:
         self.adapter = adapter
         self.blocks: list[int] = []
         self.num_cached = 0
+        self.salt: int | None = None          # prefix-cache salt (adapter slot + version) the KV was computed under
         self.finished = False
         self.finish_reason: str | None = None
         self.aborted = False
@@ -176,6 +177,10 @@ class Engine:
         flight, level 2 discards (and forgets the prefix cache)."""
         if self.kv is None:
             return
+        if getattr(self.kv, "arena", None) is None and hasattr(self.runner, "drop_graphs"):
+            # without the address-stable arena the cache comes back at new addresses: captured decode graphs
+            # would replay against freed memory
+            self.runner.drop_graphs()
         if level == 1 and self.has_unfinished:
             self.kv.offload()
         else:
@@ -282,7 +287,9 @@ class Engine:
     def _release(self, seq: Sequence) -> None:
         if seq.blocks:
             toks = seq.tokens
-            self.bm.commit(seq.blocks, toks[: len(toks) - 1], self._salt(seq.adapter))
+            # KV computed (even partly) under weights that were replaced since admission must not become reusable
+            if seq.salt is not None and seq.salt == self._salt(seq.adapter):
+                self.bm.commit(seq.blocks, toks[: len(toks) - 1], seq.salt)
             self.bm.free(seq.blocks)
             seq.blocks = []
         seq.done_event.set()
@@ -304,7 +311,8 @@ class Engine:
                     seq.done_event.set()
                     continue
                 toks = seq.tokens
-                cached = self.bm.match_prefix(toks[:-1], self._salt(seq.adapter))   # always recompute the last token
+                salt = self._salt(seq.adapter)
+                cached = self.bm.match_prefix(toks[:-1], salt)   # always recompute the last token
                 n_new = len(toks) - len(cached) * self.bm.block_size
                 if n_new > budget and picked:
                     self.bm.free(cached)
@@ -317,6 +325,7 @@ class Engine:
                 self.waiting.popleft()
                 seq.blocks = cached + fresh
                 seq.num_cached = len(cached) * self.bm.block_size
+                seq.salt = salt
                 picked.append(seq)
                 budget -= n_new
         return picked

@@ -349,12 +349,18 @@ class NativeRunner:
         """Drop the captured decode graphs and their buffers.  A tensor-parallel runner must be closed before its
         process group is destroyed: NCCL does not finish tearing down a communicator while CUDA graphs that captured
         its collectives are alive."""
+        self.drop_graphs()
+
+    def drop_graphs(self) -> None:
+        """Forget every captured decode graph (and its buffers); the next decode of each shape runs eagerly and is
+        captured again.  Needed whenever an address baked into the graphs changes, e.g. a KV cache that was freed and
+        re-allocated around a training step."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
         if hasattr(self, "_dgraphs"):
             self._dgraphs.clear()
             self._dstate.clear()
             self._dseen.clear()
-        if self.device.type == "cuda":
-            torch.cuda.synchronize(self.device)
 
     # -- tensor parallel ------------------------------------------------------------------------
     def _reduce(self, x: torch.Tensor) -> torch.Tensor:

@@ -65,6 +65,11 @@ class ModelState:
             base = init_base_weights(self.cfg, seed=seed, dtype=dt, device=self.device)
         # LoRA: resume from the newest checkpoint, else fresh init
         last = get_last_checkpoint_dir(output_dir)
+        if last and not is_adapter_dir(last) and int(os.path.basename(last)) > 0:
+            # an empty or partial step directory (an interrupted write of an older layout): re-initialising here would
+            # silently throw the training away while the step counter carries on
+            raise RuntimeError(f"checkpoint directory {last} holds no complete adapter; delete it to resume from the "
+                               "step before it")
         if last and is_adapter_dir(last):
             lora, _ = load_adapter(last, self.device)
         else:
@@ -95,7 +100,15 @@ class ModelState:
             per_block = KVCache.bytes_per_block(self.cfg.num_layers, block_size, self.cfg.num_kv_heads, self.cfg.head_dim)
             budget = min(free * 0.6, total * util * 0.5)   # leave room for training activations
             num_blocks = int(engine_args.get("num_gpu_blocks_override") or max(64, int(budget // per_block)))
-            self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim, self.device)
+            # sleep mode frees the cache while the trainer runs: the virtual-memory arena keeps every address stable, so
+            # decode graphs captured before a training step stay valid after it
+            sleep_mode = bool(engine_args.get("enable_sleep_mode", False))
+            try:
+                self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim,
+                                  self.device, use_arena=sleep_mode)
+            except RuntimeError:   # no VMM support: plain tensors; Engine.sleep() then drops the captured graphs
+                self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim,
+                                  self.device)
             runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
                                   device=self.device)
         else:
@@ -124,10 +137,11 @@ class ModelService:
     _state: ModelState | None = field(default=None, repr=False, compare=False)
     _server_task: asyncio.Task | None = field(default=None, repr=False, compare=False)
     _ckpt_thread: threading.Thread | None = field(default=None, repr=False, compare=False)
+    _ckpt_error: BaseException | None = field(default=None, repr=False, compare=False)
 
     def __getstate__(self):   # only the configuration crosses the process boundary
         d = dict(self.__dict__)
-        d["_state"] = d["_server_task"] = d["_ckpt_thread"] = None
+        d["_state"] = d["_server_task"] = d["_ckpt_thread"] = d["_ckpt_error"] = None
         return d
 
     @property
@@ -228,33 +242,56 @@ class ModelService:
                 if verbose:
                     print(f"[train] step {st.trainer.global_step}: {metrics}", flush=True)
                 yield metrics
-            # new step directory = PEFT adapter (+ optimizer state), written off the critical path
+            # new step directory = PEFT adapter (+ optimizer state).  The files are written by a thread while the engine
+            # wakes up and takes the new adapter; they go into "{step}.tmp" and are renamed once complete, so a numeric
+            # directory always holds a whole checkpoint, and the write has finished (or raised) before train() returns,
+            # as in the reference (src/art/local/service.py:150-157: save_model before the generator ends)
             step = get_step_from_dir(self.output_dir) + 1
             ckpt_dir = get_step_checkpoint_dir(self.output_dir, step)
             host_state = {k: v.detach().to("cpu", copy=True) for k, v in st.trainer.flat.views.items()}
             tstate = st.trainer.trainer_state()
-            os.makedirs(ckpt_dir, exist_ok=True)   # the directory marks the step as taken immediately
-            if self._ckpt_thread is not None:
-                self._ckpt_thread.join()
-
-            def write():
-                save_adapter(ckpt_dir, host_state, st.lora_cfg, self.base_model)
-                torch.save(tstate, os.path.join(ckpt_dir, TRAINER_STATE))
-
-            self._ckpt_thread = threading.Thread(target=write, daemon=True)
-            self._ckpt_thread.start()
+            self._join_checkpoint()
+            self._start_checkpoint(ckpt_dir, host_state, tstate)
             if slept:
                 await loop.run_in_executor(None, st.engine.wake_up)
                 slept = False
             self._set_lora_in_device()
+            await loop.run_in_executor(None, self._join_checkpoint)
         finally:
             if slept:
                 await loop.run_in_executor(None, st.engine.wake_up)
             st.engine.resume()
 
+    def _start_checkpoint(self, ckpt_dir: str, host_state: dict, tstate: dict) -> None:
+        import shutil
+
+        st = self.state
+        tmp = ckpt_dir + ".tmp"
+        self._ckpt_error = None
+
+        def write():
+            try:
+                shutil.rmtree(tmp, ignore_errors=True)
+                save_adapter(tmp, host_state, st.lora_cfg, self.base_model)
+                torch.save(tstate, os.path.join(tmp, TRAINER_STATE))
+                os.replace(tmp, ckpt_dir)
+            except BaseException as e:  # noqa: BLE001 - handed to the caller of _join_checkpoint
+                self._ckpt_error = e
+
+        self._ckpt_thread = threading.Thread(target=write, daemon=True)
+        self._ckpt_thread.start()
+
+    def _join_checkpoint(self) -> None:
+        """Wait for the checkpoint writer; an exception it hit (disk full, ...) is raised here, once."""
+        t, self._ckpt_thread = self._ckpt_thread, None
+        if t is not None:
+            t.join()
+        err, self._ckpt_error = self._ckpt_error, None
+        if err is not None:
+            raise RuntimeError("writing the step checkpoint failed") from err
+
     async def flush_checkpoints(self) -> None:
-        if self._ckpt_thread is not None:
-            await asyncio.get_running_loop().run_in_executor(None, self._ckpt_thread.join)
+        await asyncio.get_running_loop().run_in_executor(None, self._join_checkpoint)
 
     async def shutdown(self) -> None:
         await self.stop_openai_server()
@@ -263,7 +300,6 @@ class ModelService:
             self._state.engine.shutdown()
 
     def close(self) -> None:
-        if self._ckpt_thread is not None:
-            self._ckpt_thread.join()
+        self._join_checkpoint()
         if self._state is not None:
             self._state.engine.shutdown()

@@ -4,7 +4,7 @@ the flat fp32 LoRA gradient buffer summed across ranks before the optimizer step
 Two gradient-sync implementations:
 
 ``nccl``   ``torch.distributed.all_reduce`` on the flat buffer (the library baseline).
-``fused``  the in-tree NVLink kernel (``csrc/comm/lora_grad_allreduce.cu``): every rank
+``fused``  the in-tree NVLink kernel (``csrc/comm/symm_mem.cu: lora_grad_allreduce_kernel``): every rank
            reduces its 1/P slice by reading the peers' symmetric buffers directly and
            writes the sum back to all peers, with bounded flag waits.
 
@@ -25,14 +25,13 @@ def nccl_grad_sync(world: int):
 
 
 def make_grad_sync(kind: str, device: torch.device, world: int):
-    """Returns ``(callable(flat_grads), name)``.  ``auto`` prefers the fused kernel when peer access works."""
+    """Returns ``(callable(flat_grads), name)``.  ``auto`` and ``fused`` are the in-tree kernel; a failure to set it
+    up (no peer access between the GPUs, ...) is an error, never a silent switch to the library path.  NCCL runs
+    only when it is asked for by name."""
     if kind in ("auto", "fused"):
-        try:
-            from .symm_mem import fused_allreduce_sync
+        from .symm_mem import fused_allreduce_sync
 
-            return fused_allreduce_sync(device, world), "fused-p2p-allreduce"
-        except Exception as e:  # peer mapping unavailable: fall back to the library path, loudly
-            if kind == "fused":
-                raise
-            print(f"[art_b200] fused all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+        return fused_allreduce_sync(device, world), "fused-p2p-allreduce"
+    if kind != "nccl":
+        raise ValueError(f"unknown gradient sync {kind!r} (auto, fused, nccl)")
     return nccl_grad_sync(world), "nccl-allreduce"

@@ -11,22 +11,12 @@ import asyncio
 import os
 from typing import Any
 
-import httpx
-
 from .. import dev
 from ..backend import Backend
+from . import utils
+from .utils import SERVER_TASK, _sky
 
-SERVER_TASK = "art_server"
 SERVER_COMMAND = "python -m art_b200.cli run --host 0.0.0.0 --port 7999"
-
-
-def _sky():
-    try:
-        import sky  # type: ignore
-
-        return sky
-    except ImportError as e:
-        raise RuntimeError("SkyPilotBackend needs the `skypilot` package, which is not installed") from e
 
 
 def _load_env_file(path: str) -> dict[str, str]:
@@ -49,8 +39,8 @@ class SkyPilotBackend(Backend):
     async def initialize_cluster(cls, *, cluster_name: str = "art", gpu: str | None = None, resources: Any = None,
                                  art_version: str | None = None, env_path: str | None = None,
                                  force_restart: bool = False, sky_module: Any = None,
-                                 health_timeout: float = 600.0) -> "SkyPilotBackend":
-        sky = sky_module or _sky()
+                                 health_timeout: float = 600.0, health_get=None) -> "SkyPilotBackend":
+        sky = _sky(sky_module)
         self = cls.__new__(cls)
         self._cluster_name = cluster_name
         self._sky = sky
@@ -78,8 +68,10 @@ class SkyPilotBackend(Backend):
                 task.workdir = art_version
             task.update_envs(self._envs)
             await asyncio.to_thread(lambda: sky.exec(task=task, cluster_name=cluster_name, detach_run=True))
-        base_url = await self._endpoint(7999)
-        await self._wait_healthy(base_url, health_timeout)
+        poll = 0.0 if sky_module is not None else 5.0     # a fake module answers at once
+        attempts = max(1, int(health_timeout // max(poll, 5.0)))
+        base_url = await utils.wait_for_art_server_to_start(cluster_name, sky, attempts=attempts, interval=poll,
+                                                            get=health_get)
         Backend.__init__(self, base_url=base_url)
         return self
 
@@ -94,30 +86,10 @@ class SkyPilotBackend(Backend):
         await asyncio.to_thread(lambda: sky.launch(task, cluster_name=self._cluster_name, retry_until_up=True))
 
     async def _task_running(self) -> bool:
-        sky = self._sky
-        queue = await asyncio.to_thread(lambda: sky.queue(self._cluster_name))
-        return any(job.get("job_name") == SERVER_TASK and str(job.get("status", "")).endswith(("RUNNING", "PENDING", "SETTING_UP"))
-                   for job in queue)
+        return await utils.is_task_created(self._cluster_name, SERVER_TASK, self._sky)
 
     async def _endpoint(self, port: int) -> str:
-        sky = self._sky
-        ep = await asyncio.to_thread(lambda: sky.endpoints(self._cluster_name, port))
-        url = ep[port] if isinstance(ep, dict) and port in ep else (ep[str(port)] if isinstance(ep, dict) else ep)
-        return url if str(url).startswith("http") else f"http://{url}"
-
-    async def _wait_healthy(self, base_url: str, timeout: float) -> None:
-        deadline = asyncio.get_running_loop().time() + timeout
-        async with httpx.AsyncClient() as client:
-            while True:
-                try:
-                    r = await client.get(f"{base_url}/healthcheck", timeout=5)
-                    if r.status_code == 200:
-                        return
-                except httpx.HTTPError:
-                    pass
-                if asyncio.get_running_loop().time() > deadline:
-                    raise TimeoutError(f"backend server at {base_url} did not become healthy")
-                await asyncio.sleep(2)
+        return await utils._endpoint(self._cluster_name, port, self._sky)
 
     async def _prepare_backend_for_training(self, model, config: dev.OpenAIServerConfig | None) -> tuple[str, str]:
         """The completion server is reached through the cluster's public port-8000 endpoint."""
@@ -130,6 +102,7 @@ class SkyPilotBackend(Backend):
 
 
 def stop_server(cluster_name: str = "art", sky_module: Any = None) -> None:
-    """Cancel the backend server task on the cluster (console helper)."""
-    sky = sky_module or _sky()
-    sky.cancel(cluster_name=cluster_name, all=True)
+    """Blocking wrapper of :func:`art_b200.skypilot.stop_server.stop_server` (console helper)."""
+    from .stop_server import stop_server as _stop
+
+    asyncio.run(_stop(cluster_name, sky_module))

@@ -147,3 +147,39 @@ def test_top_k_top_p_restrict_the_support(tiny):
     assert top1.output_ids == greedy.output_ids and tiny_p.output_ids == greedy.output_ids
     free = eng.generate_sync([1, 2, 3, 4], SamplingParams(max_tokens=5, temperature=1.3, seed=11))
     assert all(lp <= 0 for lp in top1.logprobs + free.logprobs)
+
+
+def test_kv_computed_under_replaced_adapter_is_not_reused(tiny):
+    """A request in flight across pause -> set_adapter -> resume holds KV of the OLD weights; when it finishes its
+    blocks must not enter the prefix cache under the new adapter version."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    g = torch.Generator().manual_seed(4)
+
+    def rand_lora(scale):
+        lora = init_lora(cfg, LoraConfig())
+        for k in lora:
+            if "lora_B" in k:
+                lora[k] = torch.randn(lora[k].shape, generator=g) * scale
+        return lora
+
+    eng.set_adapter("m", rand_lora(0.5))
+    prompt = list(range(1, 13))                      # three whole blocks of 4
+    seq = eng.add_request(prompt, SamplingParams(max_tokens=6, temperature=0.0), "m")
+    eng.step()                                       # prefill under version 1
+    eng.step()
+    assert not seq.finished
+    eng.pause()
+    eng.set_adapter("m", rand_lora(0.7))             # what ModelService.train does after a step
+    eng.resume()
+    while not seq.finished:
+        eng.step()
+    eng.step()                                       # releases the finished sequence
+    slot = eng.adapters["m"]
+    assert eng.bm.match_prefix(prompt, eng._salt(slot)) == []
+    # a request that ran wholly under the new version is cached as before
+    again = eng.generate_sync(prompt, SamplingParams(max_tokens=2, temperature=0.0), "m")
+    eng.step()
+    hit = eng.bm.match_prefix(prompt, eng._salt(slot))
+    assert len(hit) == 3 and again.finished
+    eng.bm.free(hit)

@@ -221,11 +221,16 @@ def test_native_trainer_matches_autograd_reference():
     hy = TrainHyper(learning_rate=1e-4, beta=0.05, rows_per_optimizer_step=2)
     ref = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=DEV, impl="reference")
     nat = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=DEV, impl="native")
+    p0_ref, p0_nat = ref.flat.params.clone(), nat.flat.params.clone()
     mr, mn = ref.step(packed, hy), nat.step(packed, hy)
     assert abs(mr["loss"] - mn["loss"]) < 5e-3 * max(1.0, abs(mr["loss"]))
     assert abs(mr["grad_norm"] - mn["grad_norm"]) < 3e-2 * mr["grad_norm"]
     assert torch.nn.functional.cosine_similarity(ref.flat.grads, nat.flat.grads, dim=0) > 0.995
-    assert torch.nn.functional.cosine_similarity(ref.flat.params - nat.flat.params + nat.flat.params, nat.flat.params, dim=0) > 0.9999
+    # the optimizer step itself: compare the parameter UPDATES (the parameters alone agree for any tiny step)
+    d_ref, d_nat = ref.flat.params - p0_ref, nat.flat.params - p0_nat
+    assert float(d_ref.norm()) > 0
+    assert torch.nn.functional.cosine_similarity(d_ref, d_nat, dim=0) > 0.99
+    assert abs(float(d_nat.norm()) - float(d_ref.norm())) < 0.05 * float(d_ref.norm())
 
 
 def test_native_engine_matches_reference_runner():
@@ -289,3 +294,70 @@ def test_kv_cache_vmm_arena_sleep_wake_keeps_addresses():
     kv.restore()
     torch.cuda.synchronize()
     assert [t.data_ptr() for t in kv.k + kv.v] == ptrs and float(kv.k[1].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("use_arena", [True, False])
+def test_engine_sleep_wake_keeps_captured_decode_graphs_valid(use_arena):
+    """Rollout -> sleep (both levels) -> wake -> rollout: with the arena every KV address survives, so replaying the
+    graphs captured before the sleep is safe; without it the engine drops them and captures again.  Either way the
+    greedy tokens equal those of an engine that never slept."""
+    from art_b200.engine.engine import Engine, SamplingParams
+    from art_b200.engine.kv_cache import BlockManager, KVCache
+    from art_b200.engine.runner import NativeRunner
+
+    cfg, base, lcfg, lora = _small_setup()
+    base_bf = {k: v.to(torch.bfloat16) for k, v in base.items()}
+
+    def make(arena):
+        kv = KVCache(cfg.num_layers, 256, 16, cfg.num_kv_heads, cfg.head_dim, torch.device(DEV), use_arena=arena)
+        eng = Engine(NativeRunner(cfg, lcfg, kv, base=base_bf, max_loras=2, device=DEV), BlockManager(256, 16, True),
+                     eos_token_id=None, max_loras=2, num_scheduler_steps=4, kv_cache=kv)
+        eng.set_adapter("a", {k: v.to(DEV) for k, v in lora.items()})
+        return eng, kv
+
+    eng, kv = make(use_arena)
+    ref, _ = make(False)
+    prompts = [list(range(5, 40)), list(range(100, 117)), [7, 8, 9]]
+    p = SamplingParams(max_tokens=20, temperature=0.0)
+
+    def run(e, prs):
+        seqs = [e.add_request(pr, p, "a") for pr in prs]
+        while not all(s.finished for s in seqs):
+            e.step()
+        e.step()
+        return [s.output_ids for s in seqs]
+
+    def same(a, b):      # split-K partial sums arrive in any order: late greedy near-ties may flip
+        return all(x[0] == y[0] and sum(u == v for u, v in zip(x, y)) >= 0.7 * len(y) for x, y in zip(a, b))
+
+    want = run(ref, prompts)
+    assert same(run(eng, prompts), want)
+    assert len(eng.runner._dgraphs) >= 1                      # 20 tokens at 4 per step: the decode shape was captured
+    ptrs = [t.data_ptr() for t in kv.k + kv.v]
+    for level in (2, 1):
+        if level == 1:                                        # level 1 keeps the KV of a request that is in flight
+            live = eng.add_request(list(range(200, 230)), p, "a")
+            eng.step()
+            eng.step()
+            assert not live.finished
+        eng.pause()
+        eng.sleep(level)
+        assert not kv.resident
+        eng.wake_up()
+        eng.resume()
+        torch.cuda.synchronize()
+        if use_arena:
+            assert [t.data_ptr() for t in kv.k + kv.v] == ptrs
+            assert len(eng.runner._dgraphs) >= 1
+        else:
+            assert len(eng.runner._dgraphs) == 0              # stale graphs were dropped, not replayed
+        if level == 1:
+            while not live.finished:
+                eng.step()
+            eng.step()
+            lone = ref.generate_sync(list(range(200, 230)), p, "a")
+            assert same([live.output_ids], [lone.output_ids])
+        shifted = [[t + 1 for t in pr] for pr in prompts]
+        assert same(run(eng, shifted), run(ref, shifted))
+    eng.runner.close()
+    ref.runner.close()

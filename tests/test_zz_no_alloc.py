@@ -51,12 +51,16 @@ def test_noalloc_decode_matches_regular_entry_point_twice():
         ref = torch.empty(n, Hq * hd, dtype=torch.bfloat16, device="cuda")
         paged.paged_decode(q, kc, vc, bt, ctx, Hq, Hkv, hd, ref, splits)          # caller-provided workspace
         out = torch.zeros_like(ref)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]      # the driver's view: would also see a cudaMalloc inside the C function
         rc = fn(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.data_ptr(), bs,
                 n, Hq, Hkv, hd, out.data_ptr(), out.stride(0), splits, torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call > 0:      # the first call on a device may load the kernels' module; from then on nothing may move
+            assert torch.cuda.mem_get_info()[0] == free_before
         err = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
         assert err < 1e-2, (call, err)
     # a request beyond the fixed workspace is refused with the documented code and launches nothing
@@ -64,5 +68,9 @@ def test_noalloc_decode_matches_regular_entry_point_twice():
     rc = fn(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.data_ptr(), bs,
             too_many, Hq, Hkv, hd, out.data_ptr(), out.stride(0), 8, torch.cuda.current_stream().cuda_stream)
     assert rc == -5
+    # a head count of zero is a shape error, not a host-side division by zero
+    rc = fn(q.data_ptr(), q.stride(0), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bt.stride(0), ctx.data_ptr(), bs,
+            n, Hq, 0, hd, out.data_ptr(), out.stride(0), 2, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
     torch.cuda.synchronize()
     _lib.check_status()
