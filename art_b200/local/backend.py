@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import json
 import math
+from datetime import datetime
 import os
 import random
 import socket
@@ -23,6 +24,7 @@ from ..model import Model, TrainableModel
 from ..trajectories import Trajectory, TrajectoryGroup
 from ..types import TrainConfig
 from ..utils import format_message, get_model_step
+from ..utils.old_benchmarking.calculate_step_metrics import calculate_step_std_dev
 from ..utils.deploy_model import LoRADeploymentJob, LoRADeploymentProvider, deploy_model
 from ..utils.output_dirs import get_default_art_path, get_model_dir, get_trajectories_split_dir
 from ..utils.s3 import pull_model_from_s3, push_model_to_s3
@@ -32,17 +34,6 @@ from .pack import PackedTensors, packed_tensors_from_tokenized_results, packed_t
 from .service import ModelService
 from .tokenize import tokenize_trajectory_groups
 from .tokenizer import load_tokenizer
-
-
-def calculate_step_std_dev(trajectory_groups: list[TrajectoryGroup]) -> float:
-    """Mean over groups of the population standard deviation of rewards inside the group."""
-    stds = []
-    for g in trajectory_groups:
-        r = [t.reward for t in g.trajectories if isinstance(t, Trajectory)]
-        if len(r) > 1:
-            m = sum(r) / len(r)
-            stds.append(math.sqrt(sum((x - m) ** 2 for x in r) / len(r)))
-    return sum(stds) / len(stds) if stds else 0.0
 
 
 def _free_port(preferred: int) -> int:
@@ -254,7 +245,8 @@ class LocalBackend(Backend):
         out = get_model_dir(model=model, art_path=self._path)
         os.makedirs(out, exist_ok=True)
         with open(f"{out}/history.jsonl", "a") as f:
-            f.write(json.dumps({"step": step, **metrics}) + "\n")
+            # recorded_at lets the benchmark loaders plot metrics against wall-clock time
+            f.write(json.dumps({"step": step, "recorded_at": datetime.now().isoformat(), **metrics}) + "\n")
         run = self._get_wandb_run(model)
         if run is not None:
             run.log(metrics, step=step)

@@ -226,11 +226,17 @@ def test_native_trainer_matches_autograd_reference():
     assert abs(mr["loss"] - mn["loss"]) < 5e-3 * max(1.0, abs(mr["loss"]))
     assert abs(mr["grad_norm"] - mn["grad_norm"]) < 3e-2 * mr["grad_norm"]
     assert torch.nn.functional.cosine_similarity(ref.flat.grads, nat.flat.grads, dim=0) > 0.995
-    # the optimizer step itself: compare the parameter UPDATES (the parameters alone agree for any tiny step)
+    # the optimizer step itself: the native UPDATE must be the AdamW update of the native gradients.  (Adam's first step
+    # is lr * sign(g) wherever |g| >> eps, so updates of two implementations whose small gradients differ in sign by
+    # bf16 noise agree less closely than the gradients do; the two deltas are compared loosely, the arithmetic tightly.)
     d_ref, d_nat = ref.flat.params - p0_ref, nat.flat.params - p0_nat
-    assert float(d_ref.norm()) > 0
-    assert torch.nn.functional.cosine_similarity(d_ref, d_nat, dim=0) > 0.99
-    assert abs(float(d_nat.norm()) - float(d_ref.norm())) < 0.05 * float(d_ref.norm())
+    g = nat.flat.grads.float()
+    g = g * torch.clamp(0.1 / (g.norm() + 1e-6), max=1.0)                    # max_grad_norm 0.1
+    m_hat, v_hat = g, g * g                                                  # bias-corrected moments after one step
+    want = -hy.learning_rate * 0.1 * p0_nat - hy.learning_rate * m_hat / (v_hat.sqrt() + 1e-8)
+    assert float(d_nat.norm()) > 0
+    assert ((d_nat - want).norm() / want.norm()).item() < 1e-3
+    assert torch.nn.functional.cosine_similarity(d_ref, d_nat, dim=0) > 0.9
 
 
 def test_native_engine_matches_reference_runner():
