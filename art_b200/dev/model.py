@@ -37,6 +37,7 @@ class InitArgs(TypedDict, total=False):
     # native additions
     random_init: bool  # build the architecture with N(0, 0.02) weights instead of loading a checkpoint
     architecture: dict  # explicit architecture (overrides config.json lookup); see models.config.ModelConfig
+    init_std: float  # standard deviation of the random initialisation (default 0.02)
 
 
 class PeftArgs(TypedDict, total=False):

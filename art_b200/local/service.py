@@ -62,7 +62,8 @@ class ModelState:
             base = load_base_weights(base_model, self.cfg, device=self.device)
         else:
             dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-            base = init_base_weights(self.cfg, seed=seed, dtype=dt, device=self.device)
+            base = init_base_weights(self.cfg, seed=seed, dtype=dt, device=self.device,
+                                     std=float(init_args.get("init_std", 0.02)))
         # LoRA: resume from the newest checkpoint, else fresh init
         last = get_last_checkpoint_dir(output_dir)
         if last and not is_adapter_dir(last) and int(os.path.basename(last)) > 0:
