@@ -236,6 +236,94 @@ sample_restricted_kernel(const float* __restrict__ logits, long ld, const float*
   }
 }
 
+// Sparse in-place logit edits before sampling: entry e rewrites logits[row[e], tok[e]] as
+//   x = x > 0 ? x * mul_pos[e] : x * mul_neg[e];  x -= sub[e]
+// which covers the repetition penalty (mul_pos = 1/p, mul_neg = p on every token of prompt + output), the frequency /
+// presence penalties (sub = f * count + p on output tokens) and logit_bias (sub = -bias).  The host merges all edits of
+// one (row, token) pair into one entry, so entries never collide.
+__global__ void logit_adjust_kernel(float* logits, long ld, const int* row, const int* tok, const float* mul_pos,
+                                    const float* mul_neg, const float* sub, int n, int M, int V) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const int r = row[e], t = tok[e];
+  if (r < 0 || r >= M || t < 0 || t >= V) return;
+  float* p = logits + static_cast<long>(r) * ld + t;
+  float x = *p;
+  x = x > 0.f ? x * mul_pos[e] : x * mul_neg[e];
+  *p = x - sub[e];
+}
+
+// The k most likely tokens of every row with their log-probabilities under softmax(logits * inv_temp) (inv_temp 0:
+// temperature 1 for reporting, as the greedy log-prob is reported): k rounds of a block-wide arg-max over values below
+// the previous pick (ties broken by the smaller index).  k is small (<= 20); one CTA per row.
+__global__ void __launch_bounds__(256) top_logprobs_kernel(const float* logits, long ld, const float* inv_temp, int M, int V,
+                                                           int k, int* out_tok, float* out_lp) {
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* x = logits + static_cast<long>(r) * ld;
+  float it = inv_temp ? inv_temp[r] : 1.f;
+  if (it <= 0.f) it = 1.f;
+  __shared__ float s_v[256];
+  __shared__ int s_i[256];
+  __shared__ float s_mx, s_lse;
+  // log-sum-exp of the row
+  float mx = -INFINITY;
+  for (int j = tid; j < V; j += 256) mx = fmaxf(mx, x[j] * it);
+  s_v[tid] = mx;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) s_v[tid] = fmaxf(s_v[tid], s_v[tid + o]);
+    __syncthreads();
+  }
+  if (tid == 0) s_mx = s_v[0];
+  __syncthreads();
+  mx = s_mx;
+  float z = 0.f;
+  for (int j = tid; j < V; j += 256) z += __expf(x[j] * it - mx);
+  s_v[tid] = z;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) s_v[tid] += s_v[tid + o];
+    __syncthreads();
+  }
+  if (tid == 0) s_lse = mx + logf(s_v[0]);
+  __syncthreads();
+  float prev_v = INFINITY;
+  int prev_i = -1;
+  for (int round = 0; round < k; ++round) {
+    float bv = -INFINITY;
+    int bi = V;
+    for (int j = tid; j < V; j += 256) {
+      const float v = x[j] * it;
+      const bool below = v < prev_v || (v == prev_v && j > prev_i);
+      if (below && (v > bv || (v == bv && j < bi))) {
+        bv = v;
+        bi = j;
+      }
+    }
+    s_v[tid] = bv;
+    s_i[tid] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+      if (tid < o) {
+        const float ov = s_v[tid + o];
+        const int oi = s_i[tid + o];
+        if (ov > s_v[tid] || (ov == s_v[tid] && oi < s_i[tid])) {
+          s_v[tid] = ov;
+          s_i[tid] = oi;
+        }
+      }
+      __syncthreads();
+    }
+    prev_v = s_v[0];
+    prev_i = s_i[0];
+    if (tid == 0) {
+      out_tok[r * k + round] = prev_i < V ? prev_i : -1;
+      out_lp[r * k + round] = prev_i < V ? prev_v - s_lse : -INFINITY;
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace artb
 
 using namespace artb;
@@ -249,5 +337,23 @@ ARTB_EXPORT int artb_sample_restricted(const float* logits, long ld, const float
   if (V <= 0 || ld < V) return ERR_BAD_SHAPE;
   sample_restricted_kernel<<<M, SR_THREADS, 0, stream>>>(logits, ld, inv_temp, row_seed, top_k, top_p, min_p, M, V,
                                                          vocab_offset, token, logprob);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// In-place sparse logit edits (penalties, logit_bias); see logit_adjust_kernel.
+ARTB_EXPORT int artb_logit_adjust(float* logits, long ld, const int* row, const int* tok, const float* mul_pos,
+                                  const float* mul_neg, const float* sub, int n, int M, int V, cudaStream_t stream) {
+  if (n <= 0 || M <= 0) return 0;
+  if (V <= 0 || ld < V) return ERR_BAD_SHAPE;
+  logit_adjust_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ld, row, tok, mul_pos, mul_neg, sub, n, M, V);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out_tok int32 [M, k], out_lp fp32 [M, k]: the k most likely tokens per row, most likely first.
+ARTB_EXPORT int artb_top_logprobs(const float* logits, long ld, const float* inv_temp, int M, int V, int k, int* out_tok,
+                                  float* out_lp, cudaStream_t stream) {
+  if (M <= 0 || k <= 0) return 0;
+  if (V <= 0 || ld < V || k > 64) return ERR_BAD_SHAPE;
+  top_logprobs_kernel<<<M, 256, 0, stream>>>(logits, ld, inv_temp, M, V, k, out_tok, out_lp);
   return static_cast<int>(cudaGetLastError());
 }

@@ -23,7 +23,7 @@ from dataclasses import dataclass, field
 from typing import AsyncIterator
 
 from .kv_cache import BlockManager
-from .runner import SeqView
+from .runner import LogitProc, SeqView
 
 
 @dataclass
@@ -39,6 +39,16 @@ class SamplingParams:
     seed: int | None = None
     ignore_eos: bool = False
     guided_choice: list[str] | None = None
+    top_logprobs: int = 0                  # alternatives reported per sampled token
+    repetition_penalty: float = 1.0        # > 1 discourages tokens of prompt + output
+    presence_penalty: float = 0.0          # subtracted once for every token already generated
+    frequency_penalty: float = 0.0         # subtracted per occurrence in the output
+    logit_bias: dict[int, float] | None = None
+
+    @property
+    def needs_logits(self) -> bool:
+        return (self.top_logprobs > 0 or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
+                or self.frequency_penalty != 0.0 or bool(self.logit_bias))
 
 
 @dataclass
@@ -47,6 +57,7 @@ class TokenEvent:
     logprob: float
     finished: bool = False
     finish_reason: str | None = None
+    top_logprobs: list[tuple[int, float]] | None = None
 
 
 class Sequence:
@@ -70,6 +81,10 @@ class Sequence:
         self.seed = params.seed if params.seed is not None else (self.id * 2654435761) & 0x7FFFFFFF
         self.arrival = time.monotonic()
         self.forced: deque[int] = deque()     # guided decoding: tokens to emit verbatim
+        self.top_logprobs: list = []          # per generated token: None or [(token, logprob)] (when requested)
+        self.proc = (LogitProc(len(self.prompt_ids), params.repetition_penalty, params.presence_penalty,
+                               params.frequency_penalty, params.logit_bias, params.top_logprobs)
+                     if params.needs_logits else None)
         self.done_event = threading.Event()
 
     @property
@@ -78,7 +93,7 @@ class Sequence:
 
     def view(self) -> SeqView:
         return SeqView(self.tokens, self.num_cached, self.blocks, self.adapter, self.params.temperature, self.seed,
-                       len(self.output_ids), self.params.top_p, self.params.top_k, self.params.min_p)
+                       len(self.output_ids), self.params.top_p, self.params.top_k, self.params.min_p, self.proc)
 
 
 @dataclass
@@ -266,9 +281,10 @@ class Engine:
         return seq
 
     # -- scheduling -------------------------------------------------------------------------------
-    def _emit(self, seq: Sequence, tok: int, lp: float) -> None:
+    def _emit(self, seq: Sequence, tok: int, lp: float, top=None) -> None:
         seq.output_ids.append(tok)
         seq.logprobs.append(lp)
+        seq.top_logprobs.append(top)
         self.stats.generated_tokens += 1
         p = seq.params
         reason = None
@@ -280,7 +296,7 @@ class Engine:
             reason = "length"
         if reason:
             seq.finished, seq.finish_reason = True, reason
-        ev = TokenEvent(tok, lp, seq.finished, reason)
+        ev = TokenEvent(tok, lp, seq.finished, reason, top)
         if seq.loop is not None:
             seq.loop.call_soon_threadsafe(seq.queue.put_nowait, ev)
 
@@ -378,11 +394,12 @@ class Engine:
             self.stats.prefill_steps += 1
             self.stats.prompt_tokens += sum(len(s.tokens) - s.num_cached for s in new)
             toks, lps = self.runner.prefill([s.view() for s in new])
-            for s, t, lp in zip(new, toks, lps):
+            tops = getattr(self.runner, "last_top_logprobs", None)
+            for i, (s, t, lp) in enumerate(zip(new, toks, lps)):
                 if s.forced:
                     t = s.forced.popleft()
                 s.num_cached = 0
-                self._emit(s, t, lp)
+                self._emit(s, t, lp, tops[0][i] if tops else None)
                 self.running.append(s)
             return True
         if not self.running:
@@ -391,10 +408,11 @@ class Engine:
         steps = self._ensure_decode_blocks(min(self.n_steps, max(1, remaining)))
         if steps == 0 or not self.running:
             return True
-        if any(s.forced for s in self.running):
-            steps = 1
+        if any(s.forced or s.proc is not None for s in self.running):
+            steps = 1      # the next step's input (forced token, penalties) depends on the host
         self.stats.decode_steps += steps
         toks, lps = self.runner.decode([s.view() for s in self.running], steps)
+        tops = getattr(self.runner, "last_top_logprobs", None)
         for k in range(steps):
             for i, s in enumerate(self.running):
                 if s.finished:
@@ -402,7 +420,7 @@ class Engine:
                 t = toks[k][i]
                 if s.forced:
                     t = s.forced.popleft()
-                self._emit(s, t, lps[k][i])
+                self._emit(s, t, lps[k][i], tops[k][i] if tops else None)
         return True
 
     def _traced_step(self) -> bool:

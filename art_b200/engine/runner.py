@@ -26,6 +26,22 @@ from ..models.weights import LoraConfig, lora_key
 
 
 @dataclass
+class LogitProc:
+    """Per-request logit processing that needs the materialised logits of a step (not the fused sampler)."""
+    n_prompt: int
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    logit_bias: dict | None = None
+    top_logprobs: int = 0
+
+    @property
+    def edits(self) -> bool:
+        return (self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+                or bool(self.logit_bias))
+
+
+@dataclass
 class SeqView:
     """What a runner needs to know about one scheduled sequence."""
     tokens: list[int]          # prompt + generated so far
@@ -38,6 +54,7 @@ class SeqView:
     top_p: float = 1.0         # nucleus mass (>= 1: off)
     top_k: int = -1            # keep the k most likely tokens (<= 0: off)
     min_p: float = 0.0         # keep tokens at least min_p times as likely as the most likely one (<= 0: off)
+    proc: LogitProc | None = None   # penalties / logit_bias / top_logprobs: the step materialises fp32 logits
 
     @property
     def restricted(self) -> bool:
@@ -58,6 +75,8 @@ class ReferenceRunner:
         self.base = {k: v.to(self.device) for k, v in base.items()}
         self.adapters: list[dict[str, torch.Tensor] | None] = [None] * max_loras
         self._model = ReferenceModel(cfg, self.base, {}, lora_cfg)
+        self._top = None
+        self.last_top_logprobs: list | None = None      # [step][seq] -> None or [(token, logprob)] of the last call
 
     def set_adapter(self, slot: int, state: dict[str, torch.Tensor] | None) -> None:
         self.adapters[slot] = None if state is None else {k: v.detach().to(self.device).float() for k, v in state.items()}
@@ -70,6 +89,16 @@ class ReferenceRunner:
         with torch.no_grad():
             h = m.hidden_states(toks, z, z, None)[:, -1]
             logits = (h.float() @ self.base["lm_head.weight"].float().t())[0]
+        self._top = None
+        if sv.proc is not None:
+            from ..ops.paged import build_logit_edits, logit_adjust_, top_logprobs
+
+            if sv.proc.edits:
+                logits = logit_adjust_(logits[None].clone(), build_logit_edits([(sv.proc, sv.tokens)]))[0]
+            if sv.proc.top_logprobs > 0:
+                it = torch.tensor([0.0 if sv.temperature <= 0 else 1.0 / sv.temperature])
+                ti, tl = top_logprobs(logits[None].cpu(), it, sv.proc.top_logprobs)
+                self._top = list(zip(ti[0].tolist(), tl[0].tolist()))
         if sv.temperature <= 0:
             lp = torch.log_softmax(logits, -1)
             t = int(lp.argmax())
@@ -96,24 +125,31 @@ class ReferenceRunner:
         return lp.gather(-1, tgt.unsqueeze(-1)).squeeze(-1).tolist()
 
     def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
-        out = [self._next(s) for s in seqs]
+        out, tops = [], []
+        for s in seqs:
+            out.append(self._next(s))
+            tops.append(self._top)
+        self.last_top_logprobs = [tops]
         return [o[0] for o in out], [o[1] for o in out]
 
     def decode(self, seqs: list[SeqView], n_steps: int) -> tuple[list[list[int]], list[list[float]]]:
         toks: list[list[int]] = []
         lps: list[list[float]] = []
         work = [SeqView(list(s.tokens), s.num_cached, s.blocks, s.adapter, s.temperature, s.seed, s.step, s.top_p, s.top_k,
-                        s.min_p) for s in seqs]
+                        s.min_p, s.proc) for s in seqs]
+        self.last_top_logprobs = []
         for _ in range(n_steps):
-            step_t, step_l = [], []
+            step_t, step_l, step_top = [], [], []
             for s in work:
                 t, lp = self._next(s)
                 s.tokens.append(t)
                 s.step += 1
                 step_t.append(t)
                 step_l.append(lp)
+                step_top.append(self._top)
             toks.append(step_t)
             lps.append(step_l)
+            self.last_top_logprobs.append(step_top)
         return toks, lps
 
 
@@ -331,6 +367,11 @@ class NativeRunner:
         self.layers = []
         self._ws_holder: dict = {}
         for i, L in enumerate(decoder.layers):
+            if "gu" not in L:       # a trainer-side decoder keeps its feed-forward linears inside an MLP object
+                mlp = L["mlp"]
+                if not hasattr(mlp, "gu"):
+                    raise ValueError("the rollout runner serves dense feed-forward layers; this decoder's MLP is not dense")
+                L = {**L, "gu": mlp.gu, "down": mlp.down}
             self.layers.append({
                 "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q), sl_q, None),
                                                ("self_attn.k_proj", ar(q, q + kvw), sl_kv, None),
@@ -373,9 +414,29 @@ class NativeRunner:
         """The residual enters a row-parallel projection on one rank only: the all-reduce then adds it once."""
         return x if self.tp_rank == 0 else None
 
-    def _sample(self, hidden, inv_t, seeds, restricted: bool, top_k=None, top_p=None, min_p=None):
+    def _sample(self, hidden, inv_t, seeds, restricted: bool, top_k=None, top_p=None, min_p=None, procs=None):
+        """``procs``: per-row ``(LogitProc, tokens)`` or None entries; any entry sends the step through fp32 logits
+        (one GEMM), the sparse logit-edit kernel, the restricted sampler and, if asked, the top-logprobs kernel."""
         from ..ops import paged
 
+        self._step_top = None
+        if procs is not None and any(p is not None for p in procs):
+            from ..ops.gemm import gemm_tn
+
+            logits = gemm_tn(hidden, self.lm_head, out_dtype=torch.float32)
+            if self.tp > 1:
+                allv = torch.empty((self.tp,) + tuple(logits.shape), dtype=logits.dtype, device=logits.device)
+                torch.distributed.all_gather_into_tensor(allv, logits, group=self.tp_group)
+                logits = allv.permute(1, 0, 2).reshape(logits.shape[0], -1).contiguous()
+            n = len(procs)
+            paged.logit_adjust_(logits, paged.build_logit_edits([p if p is not None and p[0].edits else None for p in procs]))
+            kmax = max((p[0].top_logprobs for p in procs if p is not None), default=0)
+            if kmax > 0:
+                ti, tl = paged.top_logprobs(logits, inv_t, kmax)
+                ti, tl = ti[:n].tolist(), tl[:n].tolist()
+                self._step_top = [None if p is None or p[0].top_logprobs <= 0 else
+                                  list(zip(ti[i][:p[0].top_logprobs], tl[i][:p[0].top_logprobs])) for i, p in enumerate(procs)]
+            return paged.sample_from_logits(logits, inv_t, seeds, top_k, top_p, min_p)
         if self.tp == 1:
             if restricted:
                 return paged.sample_restricted(hidden, self.lm_head, inv_t, seeds, top_k, top_p, min_p)
@@ -500,13 +561,15 @@ class NativeRunner:
         hidden, _ = ew.rmsnorm_fwd(hl, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
         inv_t = torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs], dtype=torch.float32, device=dev)
         seeds = torch.tensor([_mix_seed(s.seed, s.step) for s in seqs], dtype=torch.int64, device=dev).to(torch.int32)
-        if any(s.restricted for s in seqs):
+        procs = [(s.proc, s.tokens) if s.proc is not None else None for s in seqs]
+        if any(s.restricted or s.proc is not None for s in seqs):
             tk = torch.tensor([s.top_k for s in seqs], dtype=torch.int32, device=dev)
             tp = torch.tensor([s.top_p for s in seqs], dtype=torch.float32, device=dev)
             mp = torch.tensor([s.min_p for s in seqs], dtype=torch.float32, device=dev)
-            t, lp = self._sample(hidden, inv_t, seeds, True, tk, tp, mp)
+            t, lp = self._sample(hidden, inv_t, seeds, True, tk, tp, mp, procs=procs)
         else:
             t, lp = self._sample(hidden, inv_t, seeds, False)
+        self.last_top_logprobs = [self._step_top] if self._step_top is not None else None
         return t.tolist(), lp.tolist()
 
     def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
@@ -561,7 +624,7 @@ class NativeRunner:
             self._dstate[key] = st
         return st
 
-    def _decode_body(self, st, n_steps: int, any_lora: bool, splits: int, ws, restricted: bool = False):
+    def _decode_body(self, st, n_steps: int, any_lora: bool, splits: int, ws, restricted: bool = False, procs=None):
         from ..ops import elementwise as ew
         from ..ops import paged
 
@@ -576,7 +639,8 @@ class NativeRunner:
                 x2 = self._reduce(L["o"](st["attn_out"], st["ad"], any_lora, residual=self._res(x)))
                 x = self._mlp(L, x2, st["ad"], any_lora)
             hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
-            t, lp = self._sample(hidden, st["inv_t"], st["seeds"][k], restricted, st["top_k"], st["top_p"], st["min_p"])
+            t, lp = self._sample(hidden, st["inv_t"], st["seeds"][k], restricted, st["top_k"], st["top_p"], st["min_p"],
+                                 procs=procs)
             st["out_t"][k].copy_(t)
             st["out_l"][k].copy_(lp)
             if k + 1 < n_steps:
@@ -610,7 +674,14 @@ class NativeRunner:
                              dtype=torch.int64).to(torch.int32)
         st["seeds"].copy_(seeds, non_blocking=True)
         any_lora = any(s.adapter >= 0 for s in seqs)
-        restricted = any(s.restricted for s in seqs)
+        procs = None
+        if any(s.proc is not None for s in seqs):
+            # logit edits depend on every token sampled so far: one step at a time, outside the captured graphs
+            if n_steps != 1:
+                raise ValueError("sequences with penalties, logit_bias or top_logprobs decode one step per call")
+            procs = [(s.proc, s.tokens) if s.proc is not None else None for s in seqs] + [None] * pad
+            use_graph = False
+        restricted = any(s.restricted for s in seqs) or procs is not None
         if restricted:
             st["top_k"].copy_(torch.tensor([s.top_k for s in seqs] + [0] * pad, dtype=torch.int32), non_blocking=True)
             st["top_p"].copy_(torch.tensor([s.top_p for s in seqs] + [1.0] * pad, dtype=torch.float32), non_blocking=True)
@@ -623,8 +694,12 @@ class NativeRunner:
             ws = st.get(("ws", splits))
             if ws is None:
                 ws = st[("ws", splits)] = torch.empty(nb * cfg.num_heads * splits * (cfg.head_dim + 2), dtype=torch.float32, device=dev)
-        graph = self._dgraphs.get(key)
-        if graph is not None:
+        graph = self._dgraphs.get(key) if procs is None else None
+        self.last_top_logprobs = None
+        if procs is not None:
+            self._decode_body(st, 1, any_lora, splits, ws, True, procs=procs)
+            self.last_top_logprobs = [self._step_top] if self._step_top is not None else None
+        elif graph is not None:
             graph.replay()
         elif use_graph and key in self._dseen and not os.environ.get("ARTB_DECODE_NO_GRAPH"):
             torch.cuda.synchronize()

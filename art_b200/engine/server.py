@@ -67,9 +67,11 @@ class OpenAIServer:
     def _token_str(self, tid: int) -> str:
         return f"token_id:{tid}" if self.token_ids_as_strings else self.tok.decode([tid])
 
-    def _logprob_entry(self, tid: int, lp: float) -> dict:
+    def _logprob_entry(self, tid: int, lp: float, top=None) -> dict:
         text = self.tok.decode([tid])
-        return {"token": self._token_str(tid), "logprob": lp, "bytes": list(text.encode("utf-8")), "top_logprobs": []}
+        alts = [{"token": self._token_str(t), "logprob": l, "bytes": list(self.tok.decode([t]).encode("utf-8"))}
+                for t, l in (top or []) if t >= 0]
+        return {"token": self._token_str(tid), "logprob": lp, "bytes": list(text.encode("utf-8")), "top_logprobs": alts}
 
     def _params(self, body: dict, prompt_len: int) -> SamplingParams:
         max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
@@ -78,7 +80,25 @@ class OpenAIServer:
         if isinstance(stop, str):
             stop = [stop]
         temp = body.get("temperature")
-        return SamplingParams(max_tokens=max_tokens, temperature=1.0 if temp is None else float(temp),
+        top_lp = body.get("top_logprobs")
+        if top_lp is None and isinstance(body.get("logprobs"), int) and not isinstance(body.get("logprobs"), bool):
+            top_lp = body["logprobs"]                       # /v1/completions spelling
+        top_lp = int(top_lp or 0)
+        if not 0 <= top_lp <= 20:
+            raise HTTPException(status_code=400, detail="top_logprobs must be between 0 and 20")
+        bias = body.get("logit_bias") or None
+        if bias:
+            try:
+                bias = {int(k): max(-100.0, min(100.0, float(v))) for k, v in bias.items()}
+            except (TypeError, ValueError) as e:
+                raise HTTPException(status_code=400, detail="logit_bias maps token ids to numbers") from e
+        rep = float(body.get("repetition_penalty") or 1.0)
+        if rep <= 0:
+            raise HTTPException(status_code=400, detail="repetition_penalty must be positive")
+        return SamplingParams(top_logprobs=top_lp, repetition_penalty=rep,
+                              presence_penalty=float(body.get("presence_penalty") or 0.0),
+                              frequency_penalty=float(body.get("frequency_penalty") or 0.0), logit_bias=bias,
+                              max_tokens=max_tokens, temperature=1.0 if temp is None else float(temp),
                               top_p=float(body.get("top_p") or 1.0), top_k=int(body.get("top_k") or -1),
                               min_p=float(body.get("min_p") or 0.0),
                               n=int(body.get("n") or 1), stop=stop, stop_token_ids=body.get("stop_token_ids"),
@@ -96,7 +116,7 @@ class OpenAIServer:
         return list(ids)
 
     async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int):
-        """Async iterator over (index, token_id, logprob, finished, finish_reason) for one choice."""
+        """Async iterator over (index, token_id, logprob, finished, finish_reason, top_logprobs) for one choice."""
         if params.guided_choice:
             async for item in self._run_guided(prompt_ids, params, adapter, index):
                 yield item
@@ -108,11 +128,11 @@ class OpenAIServer:
         agen = self.engine.generate(prompt_ids, seq_params, adapter)
         try:
             async for ev in agen:
-                yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason
+                yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason, ev.top_logprobs
                 if stops and not ev.finished:
                     text += self.tok.decode([ev.token_id])
                     if any(s in text for s in stops):
-                        yield index, None, None, True, "stop"
+                        yield index, None, None, True, "stop", None
                         return
                 if ev.finished:
                     return
@@ -140,7 +160,7 @@ class OpenAIServer:
         ids, lps = cands[pick], scores[pick]
         for k, (t, lp) in enumerate(zip(ids, lps)):
             last = k == len(ids) - 1
-            yield index, t, lp, last, "stop" if last else None
+            yield index, t, lp, last, "stop" if last else None, None
 
     # -- app ----------------------------------------------------------------------------------------
     def _build(self) -> FastAPI:
@@ -204,10 +224,13 @@ class OpenAIServer:
             params = srv._params(body, len(prompt_ids))
             out = await srv._collect(request, prompt_ids, params, adapter)
             choices = []
-            for i, (ids, lps, reason) in enumerate(out):
+            for i, (ids, lps, reason, tops) in enumerate(out):
+                lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}
+                if params.top_logprobs > 0:
+                    lpo["top_logprobs"] = [{srv._token_str(t): l for t, l in (top or []) if t >= 0} for top in tops]
                 choices.append({"index": i, "text": srv.tok.decode(ids, skip_special_tokens=True), "finish_reason": reason,
-                                "logprobs": {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}})
-            comp = sum(len(ids) for ids, _, _ in out)
+                                "logprobs": lpo})
+            comp = sum(len(o[0]) for o in out)
             return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": _now(),
                     "model": body.get("model") or srv.base_model_name, "choices": choices,
                     "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
@@ -218,14 +241,15 @@ class OpenAIServer:
     async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter):
 
         async def one(i: int):
-            ids, lps, reason = [], [], "stop"
-            async for _, tid, lp, fin, why in self._run_one(prompt_ids, params, adapter, i):
+            ids, lps, tops, reason = [], [], [], "stop"
+            async for _, tid, lp, fin, why, top in self._run_one(prompt_ids, params, adapter, i):
                 if tid is not None:
                     ids.append(tid)
                     lps.append(lp)
+                    tops.append(top)
                 if fin:
                     reason = why or "stop"
-            return ids, lps, reason
+            return ids, lps, reason, tops
 
         tasks = [asyncio.create_task(one(i)) for i in range(params.n)]
         watcher = asyncio.create_task(self._watch_disconnect(request, tasks))
@@ -267,11 +291,11 @@ class OpenAIServer:
     async def _chat_full(self, request, rid, model_name, prompt_ids, params, adapter, tools_on) -> dict:
         out = await self._collect(request, prompt_ids, params, adapter)
         choices = []
-        for i, (ids, lps, reason) in enumerate(out):
+        for i, (ids, lps, reason, tops) in enumerate(out):
             msg, reason = self._message_from(ids, tools_on, reason)
             choices.append({"index": i, "message": msg, "finish_reason": reason,
-                            "logprobs": {"content": [self._logprob_entry(t, lp) for t, lp in zip(ids, lps)]}})
-        comp = sum(len(ids) for ids, _, _ in out)
+                            "logprobs": {"content": [self._logprob_entry(t, lp, top) for t, lp, top in zip(ids, lps, tops)]}})
+        comp = sum(len(o[0]) for o in out)
         return {"id": rid, "object": "chat.completion", "created": _now(), "model": model_name, "choices": choices,
                 "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
 
@@ -310,13 +334,13 @@ class OpenAIServer:
                 if len(item) == 2:
                     live -= 1
                     continue
-                i, tid, lp, fin, why = item
+                i, tid, lp, fin, why, top = item
                 delta: dict[str, Any] = {}
                 lps = None
                 if tid is not None:
                     completion_tokens += 1
                     bufs[i].append(tid)
-                    lps = {"content": [self._logprob_entry(tid, lp)]}
+                    lps = {"content": [self._logprob_entry(tid, lp, top)]}
                     if not tools_on:
                         full = self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True)
                         if not full.endswith("�"):

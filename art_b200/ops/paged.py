@@ -19,6 +19,8 @@ _sigs = {
     "artb_sample_merge": [vp, ci, ci, vp, vp, vp],
     "artb_logprob_splits": [ci, ci],
     "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
+    "artb_logit_adjust": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp],
+    "artb_top_logprobs": [vp, cl, vp, ci, ci, ci, vp, vp, vp],
 }
 _bound: dict[str, object] = {}
 
@@ -155,3 +157,84 @@ def reference_restrict(logits: torch.Tensor, top_k: int, top_p: float, min_p: fl
         thr = sp[min(n_keep, sp.numel()) - 1]
         keep &= probs >= thr
     return keep
+
+
+# ------------------------------------------------------------------------- logit processing
+def build_logit_edits(per_row: list) -> tuple[list[int], list[int], list[float], list[float], list[float]] | None:
+    """Sparse logit edits for a batch; ``per_row[i]`` is None or ``(proc, tokens)``: ``proc`` has
+    ``repetition_penalty``, ``presence_penalty``, ``frequency_penalty``, ``logit_bias`` ({token: bias}) and ``n_prompt``;
+    ``tokens`` is the sequence so far (prompt, then output).
+
+    Semantics (those of the OpenAI API and of the sampler the reference serves through,
+    ``src/art/local/vllm.py:234-247``): the repetition penalty divides positive / multiplies negative logits of every
+    token that occurs in the prompt or the output; the frequency penalty subtracts ``f * count`` and the presence
+    penalty ``p`` for tokens of the output; the bias is added last.  All edits of one (row, token) are merged, so
+    the device kernel writes every logit at most once."""
+    rows, toks, mp, mn, sub = [], [], [], [], []
+    for i, item in enumerate(per_row):
+        if item is None:
+            continue
+        a, tokens = item
+        output_ids = tokens[a.n_prompt:]
+        edits: dict[int, list[float]] = {}      # token -> [mul_pos, mul_neg, sub]
+        rp = float(a.repetition_penalty or 1.0)
+        if rp != 1.0 and rp > 0:
+            for t in set(tokens):
+                edits[t] = [1.0 / rp, rp, 0.0]
+        fp, pp = float(a.frequency_penalty or 0.0), float(a.presence_penalty or 0.0)
+        if fp or pp:
+            counts: dict[int, int] = {}
+            for t in output_ids:
+                counts[t] = counts.get(t, 0) + 1
+            for t, c in counts.items():
+                edits.setdefault(t, [1.0, 1.0, 0.0])[2] += fp * c + pp
+        for t, b in (a.logit_bias or {}).items():
+            edits.setdefault(int(t), [1.0, 1.0, 0.0])[2] -= float(b)
+        for t, (p_, n_, s_) in edits.items():
+            rows.append(i)
+            toks.append(int(t))
+            mp.append(p_)
+            mn.append(n_)
+            sub.append(s_)
+    return (rows, toks, mp, mn, sub) if rows else None
+
+
+def logit_adjust_(logits: torch.Tensor, edits) -> torch.Tensor:
+    """Apply :func:`build_logit_edits` output to fp32 ``logits`` [M, V] in place (CUDA kernel, or PyTorch on CPU)."""
+    if edits is None:
+        return logits
+    rows, toks, mp, mn, sub = edits
+    dev = logits.device
+    if not logits.is_cuda:
+        r, t = torch.tensor(rows), torch.tensor(toks)
+        ok = (t >= 0) & (t < logits.shape[1])
+        r, t = r[ok], t[ok]
+        x = logits[r, t]
+        x = torch.where(x > 0, x * torch.tensor(mp)[ok], x * torch.tensor(mn)[ok]) - torch.tensor(sub)[ok]
+        logits[r, t] = x
+        return logits
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise ValueError("logits must be fp32 with unit inner stride")
+    ti = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)      # noqa: E731
+    tf = lambda v: torch.tensor(v, dtype=torch.float32, device=dev)    # noqa: E731
+    r, t, a, b, c = ti(rows), ti(toks), tf(mp), tf(mn), tf(sub)
+    _lib.check_rc(_f("artb_logit_adjust")(_lib.ptr(logits), logits.stride(0), _lib.ptr(r), _lib.ptr(t), _lib.ptr(a),
+                                          _lib.ptr(b), _lib.ptr(c), len(rows), logits.shape[0], logits.shape[1],
+                                          _lib.stream_ptr()), "logit_adjust")
+    return logits
+
+
+def top_logprobs(logits: torch.Tensor, inv_temp: torch.Tensor | None, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(token int32 [M, k], logprob fp32 [M, k]) of the k most likely tokens under ``softmax(logits * inv_temp)``
+    (rows with ``inv_temp`` 0, i.e. greedy requests, are reported at temperature 1)."""
+    M, V = logits.shape
+    if not logits.is_cuda:
+        it = torch.ones(M) if inv_temp is None else torch.where(inv_temp > 0, inv_temp, torch.ones_like(inv_temp))
+        lp = torch.log_softmax(logits.float() * it[:, None], -1)
+        v, i = lp.topk(min(k, V), -1)
+        return i.to(torch.int32), v
+    tok = torch.empty((M, k), dtype=torch.int32, device=logits.device)
+    lp = torch.empty((M, k), dtype=torch.float32, device=logits.device)
+    _lib.check_rc(_f("artb_top_logprobs")(_lib.ptr(logits), logits.stride(0), _lib.ptr(inv_temp), M, V, k, _lib.ptr(tok),
+                                          _lib.ptr(lp), _lib.stream_ptr()), "top_logprobs")
+    return tok, lp

@@ -265,3 +265,29 @@ def test_restricted_sampler_matches_oracle_and_fused_sampler():
     assert int((t_f == t_r).sum()) >= 46
     same = t_f == t_r
     assert float((lp_f[same] - lp_r[same]).abs().max()) < 5e-3
+
+
+def test_logit_edit_and_top_logprobs_kernels_match_pytorch():
+    from art_b200.engine.runner import LogitProc
+    from art_b200.ops import paged
+
+    M, V = 5, 3001
+    g = torch.Generator(device="cuda").manual_seed(4)
+    logits = torch.randn(M, V, device="cuda", generator=g) * 3
+    procs = [None,
+             (LogitProc(3, repetition_penalty=1.7), [5, 9, 5, 2000, 9]),
+             (LogitProc(2, presence_penalty=0.5, frequency_penalty=0.25, logit_bias={7: 4.0, 3000: -100.0}), [1, 2, 7, 7, 8]),
+             None,
+             (LogitProc(0, repetition_penalty=0.5, frequency_penalty=1.0), [10, 10, 10])]
+    edits = paged.build_logit_edits(procs)
+    want = paged.logit_adjust_(logits.cpu().clone(), edits)            # the PyTorch restatement
+    got = paged.logit_adjust_(logits.clone(), edits)
+    assert torch.allclose(got.cpu(), want, atol=1e-6)
+    x = logits.cpu()
+    assert want[1, 5] == (x[1, 5] / 1.7 if x[1, 5] > 0 else x[1, 5] * 1.7)
+    assert torch.isclose(want[2, 7], x[2, 7] - (0.25 * 2 + 0.5) + 4.0) and torch.isclose(want[2, 8], x[2, 8] - 0.75)
+    assert want[2, 1] == x[2, 1] and torch.equal(want[0], x[0])       # prompt tokens carry no frequency / presence penalty
+    inv_t = torch.tensor([1.0, 0.5, 0.0, 2.0, 1.0], device="cuda")
+    ti, tl = paged.top_logprobs(got, inv_t, 6)
+    ri, rl = paged.top_logprobs(want, inv_t.cpu(), 6)
+    assert torch.equal(ti.cpu(), ri) and torch.allclose(tl.cpu(), rl, atol=1e-4)

@@ -119,3 +119,49 @@ def test_hermes_tool_parser():
     assert json.loads(calls[0]["function"]["arguments"]) == {"q": "x"}
     assert p.extract("no tools here") == ("no tools here", [])
     assert p.extract("<tool_call>not json</tool_call>")[1] == []
+
+
+def test_top_logprobs_penalties_and_logit_bias(server):
+    async def main():
+        async with client(server) as c:
+            msgs = [{"role": "user", "content": "hello there"}]
+            base = {"model": "tiny-base", "messages": msgs, "max_tokens": 6, "temperature": 0.0}
+            plain = (await c.post("/v1/chat/completions", json=base)).json()["choices"][0]["logprobs"]["content"]
+            assert all(e["top_logprobs"] == [] for e in plain)
+            # top_logprobs: k alternatives per token, most likely first; the greedy token is alternative 0
+            r = await c.post("/v1/chat/completions", json={**base, "logprobs": True, "top_logprobs": 3})
+            d = r.json()
+            from openai.types.chat import ChatCompletion
+            ChatCompletion.model_validate(d)
+            content = d["choices"][0]["logprobs"]["content"]
+            assert [e["token"] for e in content] == [e["token"] for e in plain]
+            for e in content:
+                tops = e["top_logprobs"]
+                assert len(tops) == 3 and tops[0]["token"] == e["token"] and abs(tops[0]["logprob"] - e["logprob"]) < 1e-4
+                assert tops[0]["logprob"] >= tops[1]["logprob"] >= tops[2]["logprob"]
+            # a large positive bias forces that token; a large negative bias on the greedy tokens bans them
+            forced = (await c.post("/v1/chat/completions", json={**base, "logit_bias": {"77": 100}})).json()
+            assert [e["token"] for e in forced["choices"][0]["logprobs"]["content"]] == ["token_id:77"] * 6
+            banned_ids = {int(e["token"].split(":")[1]) for e in plain}
+            banned = (await c.post("/v1/chat/completions", json={**base, "logit_bias": {str(t): -100 for t in banned_ids}})).json()
+            assert not banned_ids & {int(e["token"].split(":")[1]) for e in banned["choices"][0]["logprobs"]["content"]}
+            # frequency / presence / repetition penalties: after a strong bias towards two tokens, penalties stop the
+            # repetition that the bias alone would cause
+            two = {"77": 30, "78": 29.5}
+            rep = (await c.post("/v1/chat/completions", json={**base, "logit_bias": two})).json()
+            assert {e["token"] for e in rep["choices"][0]["logprobs"]["content"]} == {"token_id:77"}
+            for pen in ({"frequency_penalty": 2.0}, {"presence_penalty": 2.0}):
+                alt = (await c.post("/v1/chat/completions", json={**base, "logit_bias": two, **pen})).json()
+                toks = [e["token"] for e in alt["choices"][0]["logprobs"]["content"]]
+                assert toks[0] == "token_id:77" and "token_id:78" in toks[:3]
+            r = await c.post("/v1/chat/completions", json={**base, "repetition_penalty": 1.5})
+            assert r.status_code == 200 and len(r.json()["choices"][0]["logprobs"]["content"]) == 6
+            # bad values are 400s
+            assert (await c.post("/v1/chat/completions", json={**base, "top_logprobs": 50})).status_code == 400
+            assert (await c.post("/v1/chat/completions", json={**base, "logit_bias": {"x": 1}})).status_code == 400
+            # the legacy completions route reports alternatives as a mapping per token
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": "abc", "max_tokens": 3, "logprobs": 2,
+                                                      "temperature": 0.0})
+            lp = r.json()["choices"][0]["logprobs"]
+            assert len(lp["top_logprobs"]) == 3 and all(len(m) == 2 for m in lp["top_logprobs"])
+    asyncio.run(main())
