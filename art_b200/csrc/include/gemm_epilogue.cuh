@@ -6,19 +6,29 @@ namespace artb {
 
 enum GemmEpilogue : int { EPI_BF16 = 0, EPI_BF16_RESID = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_SWIGLU_BWD = 4 };
 
-// Tiles are visited with the M index fastest, so the CTAs that run concurrently share a handful
-// of weight (B) tiles and sweep the activation matrix, which stays L2-resident.
+// Tiles are visited with the M index fastest inside bands of group_m tile rows (see raster_tile), so the CTAs that
+// run concurrently share a band of the activation matrix that stays L2-resident and a handful of weight (B) tiles.
 struct SchedMFast {
-  int m_tiles, n_tiles;
+  int m_tiles, n_tiles, group_m;
   __device__ int tiles_for_cta(int cta, int ncta) const {
     const int total = m_tiles * n_tiles;
     return cta < total ? (total - cta + ncta - 1) / ncta : 0;
   }
   __device__ TileInfo get(int cta, int ncta, int i) const {
-    const int t = cta + i * ncta;
-    return make_tile(t % m_tiles, t / m_tiles);
+    int m, n;
+    raster_tile(cta + i * ncta, m_tiles, n_tiles, group_m, m, n);
+    return make_tile(m, n);
   }
 };
+
+// Tile rows per band so that a band of A (rows x K bf16) is about 28 MB: small enough to stay in the 126 MB L2 next to
+// the streaming B and C traffic, large enough that B is re-read only a few times.
+inline int pick_group_m(int m_tiles, int tile_rows, int K) {
+  long g = (28L << 20) / (static_cast<long>(tile_rows) * K * 2);
+  if (g < 4) g = 4;
+  if (g > m_tiles) g = m_tiles;
+  return static_cast<int>(g);
+}
 
 // Split-K schedule for small-M (decode) GEMMs: work item = (m_blk, n_blk, k_split); every item
 // covers kb_per K blocks of the main operand, the extra-K operand goes with split 0.

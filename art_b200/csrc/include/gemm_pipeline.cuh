@@ -54,6 +54,18 @@ __device__ __forceinline__ TileInfo make_tile(int m_blk, int n_blk) {
   return ti;
 }
 
+// Grouped tile order: the M tiles are cut into bands of `group_m`; inside a band M runs fastest, then N; the bands
+// follow one another.  The CTAs that run at the same time then share a band of A (group_m * tile rows * K, sized by the
+// host to stay resident in L2) while B streams through once per band, instead of sweeping all of A for every few
+// columns of B.
+__device__ __forceinline__ void raster_tile(int tile, int m_tiles, int n_tiles, int group_m, int& m, int& n) {
+  const int per_group = group_m * n_tiles;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int rows = min(group_m, m_tiles - g * group_m);
+  m = g * group_m + r % rows;
+  n = r / rows;
+}
+
 template <int BN, int STAGES>
 struct GemmSmemLayout {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;

@@ -37,7 +37,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                          int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status, int splits,
-                         int kb_per) {
+                         int kb_per, int group_m) {
   using L = Gemm2SmemLayout<STAGES, BN2>;
   constexpr int G2_BN = BN2, G2_BNH = BN2 / 2, G2_STAGE_BYTES = L::STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
@@ -96,7 +96,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int tile = cluster_id + t * n_clusters;
         const int mn = tile % mn_tiles, sp = tile / mn_tiles;
-        const int m2 = mn % m_tiles2, nb = mn / m_tiles2;
+        int m2, nb;
+        raster_tile(mn, m_tiles2, n_tiles, group_m, m2, nb);
         const int row_a = m2 * 2 * GEMM_BM + rank * GEMM_BM;
         const int row_b = nb * G2_BN + rank * G2_BNH;
         const int kb_lo = sp * kb_per;
@@ -173,7 +174,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (__shfl_sync(0xffffffffu, *abort_flag, 0)) break;
       const int tile = cluster_id + t * n_clusters;
       const int mn = tile % mn_tiles;
-      TileInfo ti = make_tile((mn % m_tiles2) * 2 + static_cast<int>(rank), mn / m_tiles2);
+      int m2, nb;
+      raster_tile(mn, m_tiles2, n_tiles, group_m, m2, nb);
+      TileInfo ti = make_tile(m2 * 2 + static_cast<int>(rank), nb);
       if (splits > 1) {
         ti.group = tile / mn_tiles;
         ti.kb_lo = ti.group * kb_per;

@@ -33,7 +33,8 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev & 63] = true;
   }
-  SchedMFast sched{(M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN};
+  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  SchedMFast sched{m_tiles, (N + BN - 1) / BN, pick_group_m(m_tiles, GEMM_BM, kb_main * GEMM_BK)};
   int grid = sched.m_tiles * sched.n_tiles;
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;

@@ -43,7 +43,7 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
                       ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};
   kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, m_tiles2, n_tiles, epi,
-                                                        status, 1, kb_main);
+                                                        status, 1, kb_main, pick_group_m(m_tiles2, 2 * GEMM_BM, K));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -76,7 +76,7 @@ static int launch_2cta_splitk(const void* A, int lda, const void* B, int ldb, fl
   if (clusters > sm_count() / 2) clusters = sm_count() / 2;
   EpiAtomic<BN2> epi{ws, ldw, M, N};
   kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, m_tiles2, n_tiles, epi, status,
-                                                        splits, kb_per);
+                                                        splits, kb_per, m_tiles2);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -34,6 +34,7 @@ class EngineArgs(TypedDict, total=False):
     cpu_offload_gb: float
     # parallel layout
     tensor_parallel_size: int
+    data_parallel_size: int  # native: groups of tensor_parallel_size GPUs (trainer data parallel, one engine replica per GPU)
     pipeline_parallel_size: int
     context_parallel_size: int
     expert_parallel_size: int

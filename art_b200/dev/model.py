@@ -38,6 +38,7 @@ class InitArgs(TypedDict, total=False):
     random_init: bool  # build the architecture with N(0, 0.02) weights instead of loading a checkpoint
     architecture: dict  # explicit architecture (overrides config.json lookup); see models.config.ModelConfig
     init_std: float  # standard deviation of the random initialisation (default 0.02)
+    activation_recompute: str  # "auto" (default) | "none" | "mlp" | "full": what the trainer re-runs instead of storing
 
 
 class PeftArgs(TypedDict, total=False):

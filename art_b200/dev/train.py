@@ -11,3 +11,4 @@ class TrainConfig(TypedDict, total=False):
     tokens_per_microbatch: int  # packed rows are grouped to about this many tokens per fwd/bwd
     rows_per_optimizer_step: int  # packed rows accumulated into one AdamW step (default 1)
     compat_row_positions: bool  # RoPE positions = position in the packed row instead of input_pos
+    activation_recompute: str  # "auto" | "none" | "mlp" | "full" (overrides init_args.activation_recompute)

@@ -109,8 +109,14 @@ class EngineStats:
 class Engine:
     def __init__(self, runner, block_manager: BlockManager, *, eos_token_id: int | None, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 16384, num_scheduler_steps: int = 16, max_model_len: int = 32768,
-                 max_loras: int = 4, kv_cache=None):
+                 max_loras: int = 4, kv_cache=None, enable_chunked_prefill: bool = True):
+        """``max_num_batched_tokens`` bounds the new tokens of one prefill step.  With ``enable_chunked_prefill`` a
+        prompt longer than what is left of that budget is computed over several steps, a block-aligned chunk at a
+        time (its KV accumulates in its blocks; the token is sampled after the last chunk), so a long prompt neither
+        waits for an empty step nor builds one oversized forward pass; without it such a prompt runs alone, whole."""
         self.runner, self.bm, self.kv = runner, block_manager, kv_cache
+        self.chunked = enable_chunked_prefill
+        self.prefilling: list[Sequence] = []      # admitted, prompt KV partly computed
         self.eos = eos_token_id
         self.max_num_seqs, self.max_batched = max_num_seqs, max_num_batched_tokens
         self.n_steps, self.max_model_len = max(1, num_scheduler_steps), max_model_len
@@ -185,7 +191,7 @@ class Engine:
     @property
     def has_unfinished(self) -> bool:
         with self._lock:
-            return bool(self.waiting or self.running)
+            return bool(self.waiting or self.running or self.prefilling)
 
     def sleep(self, level: int = 1) -> None:
         """Release KV memory while paused: level 1 keeps contents on the host when requests are in
@@ -202,11 +208,11 @@ class Engine:
             self.reset_prefix_cache()
             self.kv.discard()
             with self._lock:   # KV of in-flight sequences is gone: recompute them from their tokens
-                for s in self.running:
+                for s in self.running + self.prefilling:
                     self.bm.free(s.blocks)
                     s.blocks, s.num_cached = [], 0
                     self.waiting.appendleft(s)
-                self.running = []
+                self.running, self.prefilling = [], []
 
     def wake_up(self) -> None:
         if self.kv is not None:
@@ -314,12 +320,31 @@ class Engine:
         bs = self.bm.block_size
         return (n_tokens + bs - 1) // bs
 
-    def _admit(self) -> list[Sequence]:
-        """Pick waiting sequences for one prefill step (FCFS, bounded by tokens, seqs and free blocks)."""
-        picked: list[Sequence] = []
+    def _admit(self) -> list[tuple[Sequence, int]]:
+        """Work of one prefill step: ``(sequence, upto)`` pairs, ``upto`` = prompt tokens computed after the step.
+        Partly prefilled sequences go first, then waiting ones FCFS; bounded by the token budget, the sequence limit
+        and free blocks."""
+        picked: list[tuple[Sequence, int]] = []
         budget = self.max_batched
+        bs = self.bm.block_size
+
+        def chunk(n_new: int) -> int:
+            """How many of ``n_new`` missing tokens fit this step (0: none)."""
+            if n_new <= budget:
+                return n_new
+            if self.chunked:
+                return budget // bs * bs
+            return n_new if not picked else 0          # unchunked: an oversized prompt runs alone
+
+        for seq in self.prefilling:
+            take = chunk(len(seq.tokens) - seq.num_cached)
+            if take <= 0:
+                break
+            picked.append((seq, seq.num_cached + take))
+            budget -= take
         with self._lock:
-            while self.waiting and len(self.running) + len(picked) < self.max_num_seqs:
+            while self.waiting and budget > 0 and len(self.running) + len(self.prefilling) + \
+                    sum(1 for s, _ in picked if s not in self.prefilling) < self.max_num_seqs:
                 seq = self.waiting[0]
                 if seq.aborted:
                     self.waiting.popleft()
@@ -329,8 +354,9 @@ class Engine:
                 toks = seq.tokens
                 salt = self._salt(seq.adapter)
                 cached = self.bm.match_prefix(toks[:-1], salt)   # always recompute the last token
-                n_new = len(toks) - len(cached) * self.bm.block_size
-                if n_new > budget and picked:
+                n_new = len(toks) - len(cached) * bs
+                take = chunk(n_new)
+                if take <= 0:
                     self.bm.free(cached)
                     break
                 need = self._blocks_needed(len(toks) + 1) - len(cached)
@@ -340,10 +366,10 @@ class Engine:
                     break
                 self.waiting.popleft()
                 seq.blocks = cached + fresh
-                seq.num_cached = len(cached) * self.bm.block_size
+                seq.num_cached = len(cached) * bs
                 seq.salt = salt
-                picked.append(seq)
-                budget -= n_new
+                picked.append((seq, seq.num_cached + take))
+                budget -= take
         return picked
 
     def _ensure_decode_blocks(self, steps: int) -> int:
@@ -382,24 +408,42 @@ class Engine:
                 loop.call_soon_threadsafe(lambda f=fut, r=res: f.done() or f.set_result(r))
             except BaseException as e:  # noqa: BLE001
                 loop.call_soon_threadsafe(lambda f=fut, e=e: f.done() or f.set_exception(e))
-        for s in [s for s in self.running if s.aborted and not s.finished]:
+        for s in [s for s in self.running + self.prefilling if s.aborted and not s.finished]:
             s.finished, s.finish_reason = True, "abort"
+        for s in [s for s in self.prefilling if s.finished]:    # aborted half-way through its prompt
+            self.prefilling.remove(s)
+            self.bm.free(s.blocks)
+            s.blocks = []
+            s.done_event.set()
         done = [s for s in self.running if s.finished]
         if done:
             self.running = [s for s in self.running if not s.finished]
             for s in done:
                 self._release(s)
-        new = self._admit()
-        if new:
+        work = self._admit()
+        if work:
             self.stats.prefill_steps += 1
-            self.stats.prompt_tokens += sum(len(s.tokens) - s.num_cached for s in new)
-            toks, lps = self.runner.prefill([s.view() for s in new])
+            self.stats.prompt_tokens += sum(upto - s.num_cached for s, upto in work)
+            views = []
+            for s, upto in work:
+                v = s.view()
+                v.upto = upto
+                views.append(v)
+            toks, lps = self.runner.prefill(views)
             tops = getattr(self.runner, "last_top_logprobs", None)
-            for i, (s, t, lp) in enumerate(zip(new, toks, lps)):
+            for i, (s, upto) in enumerate(work):
+                if upto < len(s.tokens):                # more chunks to come: the KV so far stays in its blocks
+                    s.num_cached = upto
+                    if s not in self.prefilling:
+                        self.prefilling.append(s)
+                    continue
+                if s in self.prefilling:
+                    self.prefilling.remove(s)
+                t = toks[i]
                 if s.forced:
                     t = s.forced.popleft()
                 s.num_cached = 0
-                self._emit(s, t, lp, tops[0][i] if tops else None)
+                self._emit(s, t, lps[i], tops[0][i] if tops else None)
                 self.running.append(s)
             return True
         if not self.running:
@@ -458,7 +502,7 @@ class Engine:
         except BaseException as e:  # noqa: BLE001 - report to every waiter, then stop
             self.error = e
             with self._lock:
-                seqs = list(self.waiting) + self.running
+                seqs = list(self.waiting) + self.running + self.prefilling
             for s in seqs:
                 if s.loop is not None:
                     s.loop.call_soon_threadsafe(s.queue.put_nowait, e)

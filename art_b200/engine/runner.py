@@ -55,6 +55,11 @@ class SeqView:
     top_k: int = -1            # keep the k most likely tokens (<= 0: off)
     min_p: float = 0.0         # keep tokens at least min_p times as likely as the most likely one (<= 0: off)
     proc: LogitProc | None = None   # penalties / logit_bias / top_logprobs: the step materialises fp32 logits
+    upto: int | None = None    # chunked prefill: compute KV for tokens[num_cached:upto] only and sample nothing
+
+    @property
+    def partial(self) -> bool:
+        return self.upto is not None and self.upto < len(self.tokens)
 
     @property
     def restricted(self) -> bool:
@@ -127,6 +132,10 @@ class ReferenceRunner:
     def prefill(self, seqs: list[SeqView]) -> tuple[list[int], list[float]]:
         out, tops = [], []
         for s in seqs:
+            if s.partial:                # no KV cache to fill here: the last chunk recomputes the whole prefix
+                out.append((None, None))
+                tops.append(None)
+                continue
             out.append(self._next(s))
             tops.append(self._top)
         self.last_top_logprobs = [tops]
@@ -502,7 +511,7 @@ class NativeRunner:
         cached_spans = []   # (att_row_start, n_cached, blocks)
         att = 0
         for i, s in enumerate(seqs):
-            n = len(s.tokens)
+            n = len(s.tokens) if s.upto is None else min(s.upto, len(s.tokens))
             nc = s.num_cached
             if nc:
                 cached_spans.append((att, nc, s.blocks))
@@ -556,6 +565,31 @@ class NativeRunner:
 
         cfg, dev = self.cfg, self.device
         x, ranges = self._prompt_forward(seqs, write_kv=True)
+        if any(s.partial for s in seqs):
+            # chunks that do not reach the end of their prompt only fill the cache; sample for the others
+            done = [i for i, s in enumerate(seqs) if not s.partial]
+            toks: list = [None] * len(seqs)
+            lps: list = [None] * len(seqs)
+            self.last_top_logprobs = None
+            if done:
+                t, lp, tops = self._sample_rows(x, [ranges[i] for i in done], [seqs[i] for i in done])
+                for j, i in enumerate(done):
+                    toks[i], lps[i] = t[j], lp[j]
+                if tops is not None:
+                    full = [None] * len(seqs)
+                    for j, i in enumerate(done):
+                        full[i] = tops[j]
+                    self.last_top_logprobs = [full]
+            return toks, lps
+        t, lp, tops = self._sample_rows(x, ranges, seqs)
+        self.last_top_logprobs = [tops] if tops is not None else None
+        return t, lp
+
+    def _sample_rows(self, x, ranges, seqs):
+        """Sample the next token of every sequence from the last row of its range in ``x``."""
+        from ..ops import elementwise as ew
+
+        cfg, dev = self.cfg, self.device
         t_last = torch.tensor([r1 - 1 for _, r1 in ranges], dtype=torch.int64, device=dev)
         hl = ew.gather_rows(x, t_last)
         hidden, _ = ew.rmsnorm_fwd(hl, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
@@ -569,8 +603,7 @@ class NativeRunner:
             t, lp = self._sample(hidden, inv_t, seeds, True, tk, tp, mp, procs=procs)
         else:
             t, lp = self._sample(hidden, inv_t, seeds, False)
-        self.last_top_logprobs = [self._step_top] if self._step_top is not None else None
-        return t.tolist(), lp.tolist()
+        return t.tolist(), lp.tolist(), self._step_top
 
     def score(self, tokens: list[int], n_prompt: int, adapter: int) -> list[float]:
         """Log-probabilities of ``tokens[n_prompt:]`` given what precedes them (no KV is written)."""

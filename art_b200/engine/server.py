@@ -38,8 +38,15 @@ def _now() -> int:
 class OpenAIServer:
     def __init__(self, engine: Engine, tokenizer, base_model_name: str, *, api_key: str | None = "default",
                  return_tokens_as_token_ids: bool = True, enable_auto_tool_choice: bool = True,
-                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256):
+                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256, peers: list[str] | None = None):
+        """``peers``: base URLs of further replicas of the same model (other GPUs of the node).  This server then
+        spreads ``/v1/chat/completions`` and ``/v1/completions`` over itself and the peers, least loaded first,
+        passing a peer's answer (JSON or event stream) through unchanged; a client only ever sees this one URL."""
         self.engine, self.tok = engine, tokenizer
+        self.peers = list(peers or [])
+        self._load = [0] * (1 + len(self.peers))       # requests in flight: [this replica, peer 0, peer 1, ...]
+        self._rr = 0
+        self._http = None
         self.base_model_name = base_model_name
         self.api_key = api_key
         self.token_ids_as_strings = return_tokens_as_token_ids
@@ -63,6 +70,48 @@ class OpenAIServer:
         if model in self.engine.adapters:
             return model
         raise HTTPException(status_code=404, detail=f"The model `{model}` does not exist.")
+
+    # -- replica routing ----------------------------------------------------------------------------
+    def _pick_replica(self) -> int:
+        """Index into ``_load`` of the least-loaded replica (0 = this process); ties rotate."""
+        n = len(self._load)
+        best = min(range(n), key=lambda i: (self._load[i], (i - self._rr) % n))
+        self._rr = (best + 1) % n
+        return best
+
+    async def _forward(self, idx: int, path: str, body: dict, request: Request):
+        """Send the request to peer ``idx - 1`` and pass its answer through."""
+        import httpx
+
+        if self._http is None:
+            self._http = httpx.AsyncClient(timeout=httpx.Timeout(None, connect=10.0),
+                                           limits=httpx.Limits(max_connections=None, max_keepalive_connections=256))
+        url = self.peers[idx - 1] + path
+        headers = {"authorization": request.headers.get("authorization", ""), "x-art-routed": "1"}
+        self._load[idx] += 1
+        if body.get("stream"):
+            req = self._http.build_request("POST", url, json=body, headers=headers)
+            try:
+                resp = await self._http.send(req, stream=True)
+            except BaseException:
+                self._load[idx] -= 1
+                raise
+
+            async def relay():
+                try:
+                    async for chunk in resp.aiter_raw():
+                        yield chunk
+                finally:       # also reached when the client goes away: closing the upstream aborts the request there
+                    await resp.aclose()
+                    self._load[idx] -= 1
+
+            return StreamingResponse(relay(), status_code=resp.status_code,
+                                     media_type=resp.headers.get("content-type", "text/event-stream"))
+        try:
+            resp = await self._http.post(url, json=body, headers=headers)
+        finally:
+            self._load[idx] -= 1
+        return JSONResponse(resp.json(), status_code=resp.status_code)
 
     def _token_str(self, tid: int) -> str:
         return f"token_id:{tid}" if self.token_ids_as_strings else self.tok.decode([tid])
@@ -175,7 +224,10 @@ class OpenAIServer:
 
         @app.get("/metrics")
         async def metrics():
-            return srv.engine.metrics()
+            m = srv.engine.metrics()
+            if srv.peers:
+                m["replica_load"] = list(srv._load)
+            return m
 
         @app.get("/v1/models")
         async def models(request: Request):
@@ -197,6 +249,9 @@ class OpenAIServer:
             srv._auth(request)
             body = await request.json()
             adapter = srv._route(body.get("model"))
+            idx = srv._pick_replica() if srv.peers and not request.headers.get("x-art-routed") else 0
+            if idx:
+                return await srv._forward(idx, "/v1/chat/completions", body, request)
             try:
                 prompt_ids = srv._render_chat(body)
             except Exception as e:
@@ -210,15 +265,23 @@ class OpenAIServer:
             tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and srv.auto_tools
             if body.get("stream"):
                 include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
-                return StreamingResponse(srv._chat_stream(request, rid, model_name, prompt_ids, params, adapter,
-                                                          tools_on, include_usage), media_type="text/event-stream")
-            return JSONResponse(await srv._chat_full(request, rid, model_name, prompt_ids, params, adapter, tools_on))
+                return StreamingResponse(srv._counted(srv._chat_stream(request, rid, model_name, prompt_ids, params, adapter,
+                                                                       tools_on, include_usage)),
+                                         media_type="text/event-stream")
+            srv._load[0] += 1
+            try:
+                return JSONResponse(await srv._chat_full(request, rid, model_name, prompt_ids, params, adapter, tools_on))
+            finally:
+                srv._load[0] -= 1
 
         @app.post("/v1/completions")
         async def completions(request: Request):
             srv._auth(request)
             body = await request.json()
             adapter = srv._route(body.get("model"))
+            idx = srv._pick_replica() if srv.peers and not request.headers.get("x-art-routed") else 0
+            if idx:
+                return await srv._forward(idx, "/v1/completions", body, request)
             prompt = body.get("prompt", "")
             prompt_ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else srv.tok.encode(prompt)
             params = srv._params(body, len(prompt_ids))
@@ -236,6 +299,15 @@ class OpenAIServer:
                     "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
 
         return app
+
+    async def _counted(self, agen):
+        """Count a locally served stream as load of this replica while it runs."""
+        self._load[0] += 1
+        try:
+            async for item in agen:
+                yield item
+        finally:
+            self._load[0] -= 1
 
     # -- non-streaming ----------------------------------------------------------------------------------
     async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter):

@@ -36,15 +36,21 @@ from .tokenize import tokenize_trajectory_groups
 from .tokenizer import load_tokenizer
 
 
-def _free_port(preferred: int) -> int:
-    for port in [preferred] + list(range(preferred + 1, preferred + 50)):
-        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
-            s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
-            try:
-                s.bind(("0.0.0.0", port))
-                return port
-            except OSError:
-                continue
+def _port_is_free(port: int) -> bool:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        try:
+            s.bind(("0.0.0.0", port))
+            return True
+        except OSError:
+            return False
+
+
+def _free_port(preferred: int, span: int = 1) -> int:
+    """First port at or after ``preferred`` from which ``span`` consecutive ports are free."""
+    for port in range(preferred, preferred + 200):
+        if all(_port_is_free(port + i) for i in range(span)):
+            return port
     with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
         s.bind(("0.0.0.0", 0))
         return s.getsockname()[1]
@@ -118,15 +124,16 @@ class LocalBackend(Backend):
         if model.name not in self._services:
             out = get_model_dir(model=model, art_path=self._path)
             config = dev.get_model_config(base_model=model.base_model, output_dir=out, config=model._internal_config)
-            service = ModelService(host="localhost", port=_free_port(8000 + len(self._services)), model_name=model.name,
-                                   base_model=model.base_model, config=config, output_dir=out)
-            if not self._in_process:
-                from ..runtime.actors import move_to_child_process
+            from .node import build_node_service
+            from .service import node_layout
 
-                os.makedirs(f"{out}/logs", exist_ok=True)
-                service = move_to_child_process(service, log_file=f"{out}/logs/model-service.log",
-                                                process_name=f"model-service:{model.name}")
-            self._services[model.name] = service
+            tp, dp = node_layout(config)
+            os.makedirs(f"{out}/logs", exist_ok=True)
+            # a model over several GPUs serves rank r on port + r: look for that many free ports in a row
+            port = _free_port(8000 + 16 * len(self._services), span=tp * dp)
+            self._services[model.name] = build_node_service(model_name=model.name, base_model=model.base_model,
+                                                            config=config, output_dir=out, port=port,
+                                                            in_process=self._in_process, log_dir=f"{out}/logs")
         return self._services[model.name]
 
 

@@ -39,10 +39,40 @@ from .tokenizer import load_tokenizer
 TRAINER_STATE = "trainer_state.pt"
 
 
-class ModelState:
-    """Everything that lives on the device for one model."""
+def shard_rows(packed: dict, keys, start: int, count: int, n_rows: int) -> dict:
+    """Rows ``[start, start + count)`` of the packed tensors; positions past ``n_rows`` become copies of row 0 with
+    zero weight and no trainable token, which add nothing to loss or gradient."""
+    take = list(range(start, min(start + count, n_rows)))
+    pad = count - len(take)
+    if pad == 0:
+        return {k: packed[k][start:start + count] for k in keys}
+    idx = torch.tensor(take + [0] * pad, dtype=torch.long)
+    rows = {k: packed[k][idx].clone() for k in keys}
+    rows["weights"][len(take):] = 0
+    rows["assistant_mask"][len(take):] = False
+    return rows
 
-    def __init__(self, base_model: str, config: dev.InternalModelConfig, output_dir: str):
+
+def node_layout(config: dev.InternalModelConfig) -> tuple[int, int]:
+    """(tensor_parallel_size, data_parallel_size) a model's configuration asks for; (1, 1) = one GPU.
+
+    ``engine_args.tensor_parallel_size`` is the knob the reference forwards to its inference library
+    (src/art/dev/engine.py:27); here it also sets the trainer's tensor-parallel group size, and
+    ``engine_args.data_parallel_size`` the number of such groups.  The service then runs one rank per GPU."""
+    ea = config.get("engine_args", {}) or {}
+    return max(1, int(ea.get("tensor_parallel_size") or 1)), max(1, int(ea.get("data_parallel_size") or 1))
+
+
+class ModelState:
+    """Everything that lives on the device for one model (on one rank of the node, if the model spans several GPUs).
+
+    With ``world > 1`` every rank builds the same state: the trainer is tensor parallel inside groups of ``tp``
+    consecutive ranks and data parallel across them (LoRA gradients averaged by the fused all-reduce); the rollout
+    engine is one replica per rank over a full copy of the frozen weights, so that after a training step every rank
+    hands the new adapter to its own engine without any transfer (all ranks hold identical LoRA masters)."""
+
+    def __init__(self, base_model: str, config: dev.InternalModelConfig, output_dir: str, rank: int = 0, world: int = 1,
+                 tp: int = 1, master_port: int = 0):
         from ..engine.engine import Engine
         from ..engine.kv_cache import BlockManager, KVCache
         from ..trainer.trainer import Trainer
@@ -51,7 +81,30 @@ class ModelState:
         engine_args = config.get("engine_args", {})
         peft_args = config.get("peft_args", {})
         targs = config.get("trainer_args", {})
-        self.device = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.rank, self.world, self.tp_size = rank, world, tp
+        self.data_index, self.data_ranks = 0, 1
+        has_gpu = torch.cuda.is_available()
+        if has_gpu:
+            torch.cuda.set_device(rank % torch.cuda.device_count())
+        self.device = torch.device("cuda", torch.cuda.current_device()) if has_gpu else torch.device("cpu")
+        tp_group = dp_group = None
+        self._owns_pg = False
+        if world > 1:
+            import datetime
+
+            import torch.distributed as dist
+
+            from ..parallel.mesh import ParallelLayout
+
+            if not dist.is_initialized():
+                kw = {"device_id": self.device} if has_gpu else {}
+                dist.init_process_group("nccl" if has_gpu else "gloo", init_method=f"tcp://127.0.0.1:{master_port}",
+                                        rank=rank, world_size=world, timeout=datetime.timedelta(seconds=600), **kw)
+                self._owns_pg = True
+            layout = ParallelLayout(world, tp=tp)
+            groups = layout.create_groups(rank)
+            tp_group, dp_group = groups["tp"], groups["dp"]
+            self.data_index, self.data_ranks = layout.data_shard(rank)
         self.cfg = resolve_config(base_model, init_args.get("architecture"))
         self.lora_cfg = LoraConfig(r=int(peft_args.get("r", 8)), alpha=float(peft_args.get("lora_alpha", 16)),
                                    target_modules=tuple(peft_args.get("target_modules", LoraConfig().target_modules)),
@@ -75,21 +128,28 @@ class ModelState:
             lora, _ = load_adapter(last, self.device)
         else:
             lora = init_lora(self.cfg, self.lora_cfg, seed=int(peft_args.get("random_state", 3407)), device=self.device)
+        grad_sync = None
+        if self.data_ranks > 1:
+            if has_gpu:
+                from ..parallel.symm_mem import FusedGradAllReduce
+
+                grad_sync = FusedGradAllReduce(self.device, self.data_ranks, dp_group)
+            else:
+                from ..parallel.dp import nccl_grad_sync
+
+                grad_sync = nccl_grad_sync(self.data_ranks, dp_group)      # CPU ranks: the library all-reduce on gloo
+        if tp > 1 and not has_gpu:
+            raise ValueError("tensor-parallel training needs GPUs (the CPU path is data parallel only)")
+        self.tp_tokens = int(targs.get("tokens_per_microbatch") or 8192 * tp)
         self.trainer = Trainer(self.cfg, base, self.lora_cfg, lora, device=self.device,
                                betas=(float(targs.get("adam_beta1", 0.9)), float(targs.get("adam_beta2", 0.99))),
                                weight_decay=float(targs.get("weight_decay", 0.1)),
                                max_grad_norm=float(targs.get("max_grad_norm", 0.1)),
-                               adam_eps=float(targs.get("adam_epsilon", 1e-8)))
+                               adam_eps=float(targs.get("adam_epsilon", 1e-8)), grad_sync=grad_sync, dp_group=dp_group,
+                               tp_group=tp_group, tp_tokens=self.tp_tokens)
         if last and os.path.exists(os.path.join(last, TRAINER_STATE)):
             self.trainer.load_trainer_state(torch.load(os.path.join(last, TRAINER_STATE), map_location="cpu"))
-        # rollout engine
-        if int(engine_args.get("tensor_parallel_size") or 1) > 1:
-            import warnings
-
-            # this service time-shares ONE GPU between its trainer and its engine; a tensor-parallel replica is a
-            # separate set of processes (one per GPU) built from NativeRunner(tp_group=...) + ReplicaEngine
-            warnings.warn("engine_args.tensor_parallel_size > 1 is not applied by the in-process service: the model "
-                          "is served from this process's GPU", stacklevel=2)
+        # rollout engine: one replica per rank
         block_size = int(engine_args.get("block_size") or 16)
         max_loras = int(engine_args.get("max_loras", 4))
         max_len = int(engine_args.get("max_model_len") or init_args.get("max_seq_length", 32768))
@@ -110,8 +170,11 @@ class ModelState:
             except RuntimeError:   # no VMM support: plain tensors; Engine.sleep() then drops the captured graphs
                 self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim,
                                   self.device)
-            runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
-                                  device=self.device)
+            if tp > 1:      # the trainer's weights are sharded: the replica keeps its own full copy
+                runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, base=base, max_loras=max_loras, device=self.device)
+            else:           # trainer and engine share the frozen weights
+                runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
+                                      device=self.device)
         else:
             from ..engine.runner import ReferenceRunner
 
@@ -123,8 +186,24 @@ class ModelState:
                              max_num_seqs=int(engine_args.get("max_num_seqs") or 256),
                              max_num_batched_tokens=int(engine_args.get("max_num_batched_tokens") or 16384),
                              num_scheduler_steps=int(engine_args.get("num_scheduler_steps", 16)), max_model_len=max_len,
-                             max_loras=max_loras, kv_cache=self.kv)
+                             max_loras=max_loras, kv_cache=self.kv,
+                             enable_chunked_prefill=bool(engine_args.get("enable_chunked_prefill", True)))
         self.sleep_mode = bool(engine_args.get("enable_sleep_mode", False))
+
+    def close(self) -> None:
+        self.engine.shutdown()
+        runner = self.engine.runner
+        if hasattr(runner, "close"):
+            runner.close()
+        tpctx = getattr(self.trainer, "tp", None)
+        if tpctx is not None:
+            tpctx.close()
+        if self._owns_pg:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                dist.destroy_process_group()
+            self._owns_pg = False
 
 
 @dataclass
@@ -135,6 +214,12 @@ class ModelService:
     base_model: str
     config: dev.InternalModelConfig
     output_dir: str
+    # this service's place among the ranks of a model that spans several GPUs (rank 0 leads: it owns the public
+    # port, the checkpoints and the metrics); see local/node.py
+    rank: int = 0
+    world: int = 1
+    tp_size: int = 1
+    master_port: int = 0
     _state: ModelState | None = field(default=None, repr=False, compare=False)
     _server_task: asyncio.Task | None = field(default=None, repr=False, compare=False)
     _ckpt_thread: threading.Thread | None = field(default=None, repr=False, compare=False)
@@ -148,7 +233,8 @@ class ModelService:
     @property
     def state(self) -> ModelState:
         if self._state is None:
-            self._state = ModelState(self.base_model, self.config, self.output_dir)
+            self._state = ModelState(self.base_model, self.config, self.output_dir, self.rank, self.world, self.tp_size,
+                                     self.master_port)
         return self._state
 
     # -- serving --------------------------------------------------------------------------------------
@@ -157,7 +243,7 @@ class ModelService:
 
         st = self.state
         step0 = get_step_checkpoint_dir(self.output_dir, 0)
-        if get_last_checkpoint_dir(self.output_dir) is None:
+        if self.rank == 0 and get_last_checkpoint_dir(self.output_dir) is None:
             save_adapter(step0, st.trainer.lora_state_dict(), st.lora_cfg, self.base_model)   # step 0 = untrained adapter
         lora_path = get_last_checkpoint_dir(self.output_dir) or step0
         cfg = dev.get_openai_server_config(self.model_name, self.base_model, f"{self.output_dir}/logs/engine.log",
@@ -169,12 +255,15 @@ class ModelService:
             name, path = dev.openai_server.parse_lora_module(spec)
             if name != self.model_name and is_adapter_dir(path):
                 st.engine.set_adapter(name, load_adapter(path, st.device)[0])
+        host, port0 = sargs.get("host") or "0.0.0.0", int(sargs.get("port", self.port))
+        port = port0 + self.rank                # rank r serves its replica on the leader's port + r
+        # the leader spreads requests over all replicas (its own included); the others serve what they are sent
+        peers = [f"http://127.0.0.1:{port0 + r}" for r in range(1, self.world)] if self.rank == 0 else []
         server = OpenAIServer(st.engine, st.tokenizer, self.base_model, api_key=sargs.get("api_key", "default"),
                               return_tokens_as_token_ids=bool(sargs.get("return_tokens_as_token_ids", True)),
                               enable_auto_tool_choice=bool(sargs.get("enable_auto_tool_choice", True)),
-                              tool_call_parser=sargs.get("tool_call_parser", "hermes"))
+                              tool_call_parser=sargs.get("tool_call_parser", "hermes"), peers=peers)
         self._server = server
-        host, port = sargs.get("host") or "0.0.0.0", int(sargs.get("port", self.port))
         await self.stop_openai_server()
         ready = asyncio.Event()
         self._server_task = asyncio.create_task(serve(server, host, port, sargs.get("uvicorn_log_level", "warning"), ready))
@@ -221,7 +310,9 @@ class ModelService:
                            epsilon=float(_config.get("epsilon", 0.2)), epsilon_high=_config.get("epsilon_high"),
                            rows_per_optimizer_step=int(_config.get("rows_per_optimizer_step", 1)),
                            tokens_per_microbatch=int(_config.get("tokens_per_microbatch", 8192)),
-                           compat_row_positions=bool(_config.get("compat_row_positions", False)))
+                           compat_row_positions=bool(_config.get("compat_row_positions", False)),
+                           recompute=str(_config.get("activation_recompute")
+                                         or self.config.get("init_args", {}).get("activation_recompute", "auto")))
         loop = asyncio.get_running_loop()
         await loop.run_in_executor(None, st.engine.pause)
         slept = False
@@ -231,10 +322,18 @@ class ModelService:
                 slept = True
             n_rows = packed["tokens"].shape[0]
             per = max(1, hyper.rows_per_optimizer_step)
+            if st.tp_size > 1:      # a tensor-parallel micro-batch has a fixed token count: whole micro-batches per step
+                S_row = packed["tokens"].shape[1]
+                rows_mb = max(1, st.tp_tokens // S_row)
+                per = (per + rows_mb - 1) // rows_mb * rows_mb
+                hyper.rows_per_optimizer_step, hyper.tokens_per_microbatch = per, rows_mb * S_row
+            D, j = st.data_ranks, st.data_index
             t0 = time.monotonic()
             tokens_done = 0
-            for start in range(0, n_rows, per):
-                rows = {k: packed[k][start:start + per] for k in PACKED_KEYS}
+            for start in range(0, n_rows, per * D):
+                # data-parallel group j takes the j-th slice of this optimizer step's rows; a slice that runs past the
+                # end is filled with weightless copies of the first row, so that every rank still joins the step
+                rows = shard_rows(packed, PACKED_KEYS, start + j * per, per, n_rows)
                 if st.device.type == "cuda":
                     rows = {k: v.pin_memory() for k, v in rows.items()}
                 metrics = await loop.run_in_executor(None, st.trainer.step, rows, hyper)
@@ -243,6 +342,12 @@ class ModelService:
                 if verbose:
                     print(f"[train] step {st.trainer.global_step}: {metrics}", flush=True)
                 yield metrics
+            if self.rank != 0:      # only the leader writes checkpoints; every rank holds the same adapter
+                if slept:
+                    await loop.run_in_executor(None, st.engine.wake_up)
+                    slept = False
+                self._set_lora_in_device()
+                return
             # new step directory = PEFT adapter (+ optimizer state).  The files are written by a thread while the engine
             # wakes up and takes the new adapter; they go into "{step}.tmp" and are renamed once complete, so a numeric
             # directory always holds a whole checkpoint, and the write has finished (or raised) before train() returns,
@@ -298,9 +403,16 @@ class ModelService:
         await self.stop_openai_server()
         await self.flush_checkpoints()
         if self._state is not None:
-            self._state.engine.shutdown()
+            self._state.close()
+            self._state = None
+
+    async def ready(self) -> int:
+        """Builds the state (on a multi-GPU model: joins the ranks' rendezvous); returns this service's rank."""
+        await asyncio.get_running_loop().run_in_executor(None, lambda: self.state)
+        return self.rank
 
     def close(self) -> None:
         self._join_checkpoint()
         if self._state is not None:
-            self._state.engine.shutdown()
+            self._state.close()
+            self._state = None

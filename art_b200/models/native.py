@@ -12,8 +12,13 @@ of kernel launches over preallocated activations.  Design points:
   K-major "TN" GEMM too: ``dX = [dY | dT] @ [W.T | A_cat.T].T`` with ``dT = dY @ (s*B_cat)``.
   Holding W and W.T doubles weight memory (2 x 15 GB for a 7B model), which 180 GB of HBM
   makes the right trade.
-* All activations a backward pass needs are kept (no recomputation) while a micro-batch
-  fits; ``recompute`` drops the per-layer intermediates and re-runs the layer forward.
+* All activations a backward pass needs are kept while a micro-batch fits.  ``recompute="mlp"``
+  drops the feed-forward intermediates (gate|up pre-activations and the activation, three
+  quarters of the saved bytes) and re-runs the gate|up GEMM in the backward pass;
+  ``recompute="full"`` keeps only each layer's input and re-runs the whole layer forward
+  (:func:`activation_bytes_per_token`, :func:`pick_recompute`).  This is what lets one GPU train
+  the reference's default 32 768-token rows (``src/art/dev/model.py:28``, gradient
+  checkpointing at ``:65``).
 * LoRA masters/gradients live in flat fp32 buffers (:class:`LoraFlat`); the bf16 operand
   copies (A_cat, B_cat and their transposes) are rebuilt after each optimizer step.
 
@@ -174,8 +179,32 @@ class LoraFlat:
                 self.views[k].copy_(v)
 
 
+RECOMPUTE_MODES = ("none", "mlp", "full")
+
+
+def activation_bytes_per_token(cfg: ModelConfig, mode: str = "none") -> int:
+    """bf16 bytes one token keeps alive per decoder layer between forward and backward."""
+    d, q, kv = cfg.hidden_size, cfg.q_size, cfg.kv_size
+    F = cfg.moe_intermediate_size * cfg.num_experts_per_tok if cfg.is_moe else cfg.intermediate_size
+    if mode == "full":
+        return 2 * d
+    attn = 4 * d + 2 * q + 2 * kv                    # x, h1, x2, h2, qkv, o
+    return 2 * (attn + (0 if mode == "mlp" else 3 * F))
+
+
+def pick_recompute(cfg: ModelConfig, tokens: int, num_layers: int, free_bytes: int) -> str:
+    """The cheapest mode whose saved activations (plus the working set of one layer's backward pass and the LM-head
+    buffers) fit into ``free_bytes``."""
+    work = tokens * (4 * activation_bytes_per_token(cfg, "none") + 16 * cfg.hidden_size)
+    for mode in RECOMPUTE_MODES:
+        if tokens * num_layers * activation_bytes_per_token(cfg, mode) + work <= 0.85 * free_bytes:
+            return mode
+    return "full"
+
+
 @dataclass
 class LayerSaved:
+    recompute: str = "none"     # what has to be rebuilt from x (full) or x2 (mlp) before this layer's backward
     x: torch.Tensor = None
     rstd1: torch.Tensor = None
     h1: torch.Tensor = None
@@ -213,6 +242,13 @@ class DenseMLP:
         gu, T_gu = self.gu.forward(h2, use_lora, swiglu_out=hact)
         x3, T_d = self.down.forward(hact, use_lora, residual=x2)
         return x3, (DenseSaved(h2, T_gu, gu, hact, T_d) if save else None)
+
+    def recompute(self, h2, x2, use_lora: bool) -> DenseSaved:
+        """What :meth:`forward` would have saved, without the down projection (its output is not needed again)."""
+        hact = torch.empty((h2.shape[0], self.F), dtype=h2.dtype, device=h2.device)
+        gu, T_gu = self.gu.forward(h2, use_lora, swiglu_out=hact)
+        T_d = skinny_gemm(hact, self.down.A_cat) if (self.down.active and use_lora) else None
+        return DenseSaved(h2, T_gu, gu, hact, T_d)
 
     def backward(self, dx, sv: DenseSaved):
         # the SwiGLU backward sits in the epilogue of the down-projection's data-gradient GEMM
@@ -316,46 +352,72 @@ class NativeDecoder:
             lin.export_grads()
 
     # -- forward ----------------------------------------------------------------------------
+    def _layer_forward(self, li: int, x, pos, plan, use_lora: bool, save: bool, cp=None, need_out: bool = True):
+        """One decoder layer; returns (output or None, LayerSaved or None)."""
+        cfg, layer = self.cfg, self.layers[li]
+        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        sv = LayerSaved()
+        h1, rstd1 = ew.rmsnorm_fwd(x, layer["ln1"], cfg.rms_norm_eps)
+        qkv, T_qkv = layer["qkv"].forward(h1, use_lora)
+        if cfg.qk_norm:
+            if save:
+                sv.qk_pre = qkv[:, : (Hq + Hkv) * hd].clone()
+            rq = ew.headnorm_fwd_(qkv, layer["q_norm"], 0, Hq, hd, cfg.rms_norm_eps)
+            rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
+            sv.qk_rstd = (rq, rk)
+        ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
+        if cp is not None:
+            o, actx = cp.forward(li, qkv, plan)
+        else:
+            o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
+        x2, T_o = layer["o"].forward(o, use_lora, residual=x)
+        h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
+        if need_out or not hasattr(layer["mlp"], "recompute"):
+            x3, mctx = layer["mlp"].forward(h2, x2, use_lora, save)
+        else:
+            x3, mctx = None, layer["mlp"].recompute(h2, x2, use_lora)
+        if not save:
+            return x3, None
+        sv.x, sv.rstd1, sv.h1, sv.T_qkv, sv.attn_ctx, sv.o, sv.T_o = x, rstd1, h1, T_qkv, actx, o, T_o
+        sv.x2, sv.rstd2, sv.mlp = x2, rstd2, mctx
+        return x3, sv
+
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, gid: torch.Tensor, pid: torch.Tensor, S: int,
-                use_lora: bool = True, save: bool = True, cp=None, x_in: torch.Tensor | None = None
-                ) -> tuple[torch.Tensor, list[LayerSaved], dict]:
+                use_lora: bool = True, save: bool = True, cp=None, x_in: torch.Tensor | None = None,
+                recompute: str = "none") -> tuple[torch.Tensor, list[LayerSaved], dict]:
         """tokens int64 [M], pos/gid/pid int32 [M]; returns final-normed hidden [M,d] and saved state.
 
         With ``cp`` (a :class:`parallel.cp.ContextParallel`) ``tokens`` / ``pos`` hold this rank's shard of
         every packed row while ``gid`` / ``pid`` stay full-length; attention exchanges K/V with the peers.
+        ``recompute``: "none" keeps every activation, "mlp" drops the feed-forward intermediates, "full" keeps only
+        the layer inputs; :meth:`backward` rebuilds what is missing layer by layer.
         """
         cfg = self.cfg
+        if recompute not in RECOMPUTE_MODES:
+            raise ValueError(f"recompute must be one of {RECOMPUTE_MODES}")
+        if recompute != "none" and cp is not None:
+            raise ValueError("activation recompute is not combined with context parallelism (the K/V exchange of a "
+                             "layer would have to run a second time on every rank)")
         x = ew.gather_rows(self.embed, tokens) if x_in is None else x_in     # x_in: activations from the previous stage
         plan = cp.make_plan(gid, pid) if cp is not None else attn_ops.make_plan(gid, pid, S, self.attn_impl)
         saved: list[LayerSaved] = []
-        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
-        for li, layer in enumerate(self.layers):
-            sv = LayerSaved()
-            h1, rstd1 = ew.rmsnorm_fwd(x, layer["ln1"], cfg.rms_norm_eps)
-            qkv, T_qkv = layer["qkv"].forward(h1, use_lora)
-            if cfg.qk_norm:
-                if save:
-                    sv.qk_pre = qkv[:, : (Hq + Hkv) * hd].clone()
-                rq = ew.headnorm_fwd_(qkv, layer["q_norm"], 0, Hq, hd, cfg.rms_norm_eps)
-                rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
-                sv.qk_rstd = (rq, rk)
-            ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
-            if cp is not None:
-                o, actx = cp.forward(li, qkv, plan)
+        for li in range(len(self.layers)):
+            if save and recompute == "full":
+                x3, _ = self._layer_forward(li, x, pos, plan, use_lora, False, cp)
+                saved.append(LayerSaved(recompute="full", x=x))
             else:
-                o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
-            x2, T_o = layer["o"].forward(o, use_lora, residual=x)
-            h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
-            x3, mctx = layer["mlp"].forward(h2, x2, use_lora, save)
-            if save:
-                sv.x, sv.rstd1, sv.h1, sv.T_qkv, sv.attn_ctx, sv.o, sv.T_o = x, rstd1, h1, T_qkv, actx, o, T_o
-                sv.x2, sv.rstd2, sv.mlp = x2, rstd2, mctx
-                saved.append(sv)
+                x3, sv = self._layer_forward(li, x, pos, plan, use_lora, save, cp)
+                if save:
+                    if recompute == "mlp":
+                        sv.recompute, sv.mlp = "mlp", None
+                    saved.append(sv)
             x = x3
+        final = {"cp": cp, "plan": plan, "use_lora": use_lora}
         if not self.is_last:
-            return x, saved, {"cp": cp}                                        # raw residual stream for the next stage
+            return x, saved, final                                             # raw residual stream for the next stage
         hidden, rstd_f = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps)
-        return hidden, saved, {"x_last": x, "rstd_f": rstd_f, "cp": cp}
+        final.update(x_last=x, rstd_f=rstd_f)
+        return hidden, saved, final
 
     # -- backward ---------------------------------------------------------------------------
     def backward(self, dhidden: torch.Tensor, saved: list[LayerSaved], final: dict, pos: torch.Tensor
@@ -367,6 +429,13 @@ class NativeDecoder:
         dx = ew.rmsnorm_bwd(dhidden, final["x_last"], self.final_norm, final["rstd_f"]) if self.is_last else dhidden
         for li in range(len(self.layers) - 1, -1, -1):
             layer, sv = self.layers[li], saved[li]
+            if sv.recompute == "full":       # rebuild this layer's activations from its input
+                _, sv = self._layer_forward(li, sv.x, pos, final["plan"], final["use_lora"], True, None, need_out=False)
+            elif sv.recompute == "mlp":      # rebuild the feed-forward intermediates from x2
+                h2, _ = ew.rmsnorm_fwd(sv.x2, layer["ln2"], cfg.rms_norm_eps, want_rstd=False)
+                mlp = layer["mlp"]
+                sv.mlp = (mlp.recompute(h2, sv.x2, final["use_lora"]) if hasattr(mlp, "recompute")
+                          else mlp.forward(h2, sv.x2, final["use_lora"], True)[1])
             # MLP
             dh2 = layer["mlp"].backward(dx, sv.mlp)
             dx2 = ew.rmsnorm_bwd(dh2, sv.x2, layer["ln2"], sv.rstd2, dres=dx)

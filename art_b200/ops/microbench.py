@@ -52,6 +52,85 @@ def bench_gemm(a) -> dict:
     return res
 
 
+def _sustained(fn, seconds: float = 0.6, warm: int = 5) -> float:
+    """Milliseconds per call with the calls issued back to back (no host sync, no flush) for about ``seconds``: the
+    rate a kernel holds inside a long training step, under the power cap."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    reps = max(10, int(seconds * 1e3 / max(1e-3, e0.elapsed_time(e1))))
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def bench_gemm_layer(a) -> dict:
+    """The eight projection / data-gradient GEMMs of one decoder layer at ``--tokens`` rows, each with the epilogue and
+    the LoRA extra-K block the trainer uses, sustained (back to back), next to cuBLAS on the plain product."""
+    from ..models.config import PRESETS
+    from . import _lib
+    from .gemm import gemm_tn
+
+    cfg = PRESETS[a.model]
+    dev, bf = "cuda", torch.bfloat16
+    M, d, q, kv, F = a.tokens, cfg.hidden_size, cfg.q_size, cfg.kv_size, cfg.intermediate_size
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, sc=1.0: (torch.randn(*s, device=dev, generator=g) * sc).to(bf)      # noqa: E731
+    # name, N, K, epilogue
+    shapes = [("qkv", q + 2 * kv, d, "bias" if cfg.qkv_bias else "plain"), ("o", d, q, "resid"), ("gate_up", 2 * F, d, "swiglu"),
+              ("down", d, F, "resid"), ("d_down", F, d, "swiglu_bwd"), ("d_gate_up", d, 2 * F, "plain"), ("d_o", q, d, "plain"),
+              ("d_qkv", d, q + 2 * kv, "plain")]
+    rows, tot_ms, tot_lib, tot_fl = [], 0.0, 0.0, 0.0
+    for name, N, K, epi in shapes:
+        x, w = rnd(M, K), rnd(N, K, sc=0.02)
+        t, b2 = rnd(M, 64, sc=0.1), rnd(N, 64, sc=0.02)
+        kw: dict = {"a2": t, "b2": b2}
+        if epi == "resid":
+            kw["residual"] = rnd(M, N)
+        elif epi == "bias":
+            kw["bias"] = torch.randn(N, device=dev, generator=g)
+        elif epi == "swiglu":
+            kw["swiglu_out"] = torch.empty(M, N // 2, device=dev, dtype=bf)
+        elif epi == "swiglu_bwd":
+            kw["swiglu_bwd_gu"] = rnd(M, 2 * N)
+        out = torch.empty(M, 2 * N if epi == "swiglu_bwd" else N, device=dev, dtype=bf)
+        plain = torch.empty(M, N, device=dev, dtype=bf)
+        fl = 2.0 * M * N * K
+        row = {"gemm": name, "n": N, "k": K, "epilogue": epi}
+        ms = _sustained(lambda: gemm_tn(x, w, out=out, **kw), a.seconds)
+        row["ms"], row["tflops"] = round(ms, 4), round(fl / ms / 1e9, 1)
+        if a.try_bn:
+            for bn in a.try_bn:
+                try:
+                    ms_b = _sustained(lambda: gemm_tn(x, w, out=out, bn=bn, two_cta=True, **kw), a.seconds)
+                    row[f"bn{bn}_tflops"] = round(fl / ms_b / 1e9, 1)
+                except Exception as e:  # noqa: BLE001 - a tile width this epilogue does not support
+                    row[f"bn{bn}_tflops"] = f"{type(e).__name__}"
+        if not a.no_baseline:
+            ms_l = _sustained(lambda: torch.matmul(x, w.t(), out=plain), a.seconds)
+            row["cublas_tflops"] = round(fl / ms_l / 1e9, 1)
+            tot_lib += ms_l
+        tot_ms += ms
+        tot_fl += fl
+        rows.append(row)
+        del x, w, out, plain, kw
+    _lib.check_status()
+    res = {"op": "gemm_layer", "model": cfg.name, "tokens": M, "layer_ms": round(tot_ms, 3),
+           "layer_tflops": round(tot_fl / tot_ms / 1e9, 1), "gemms": rows}
+    if tot_lib:
+        res["cublas_layer_ms"] = round(tot_lib, 3)
+        res["cublas_layer_tflops"] = round(tot_fl / tot_lib / 1e9, 1)
+    return res
+
+
 def bench_attn(a) -> dict:
     """Tree-masked attention forward + backward on the benchmark mask (prompt + 3 sibling completions per row)."""
     from . import _lib, attn_native
@@ -194,13 +273,19 @@ def main() -> None:
     sp.add_argument("--vocab", type=int, default=152064)
     sp.add_argument("--top-k", type=int, default=50)
     sp.add_argument("--top-p", type=float, default=0.9)
-    for p in (g, t, m, sp):
+    gl = sub.add_parser("gemm-layer")
+    gl.add_argument("--model", default="qwen2.5-7b")
+    gl.add_argument("--tokens", type=int, default=8192)
+    gl.add_argument("--seconds", type=float, default=0.5, help="length of each back-to-back timing run")
+    gl.add_argument("--try-bn", type=int, nargs="*", default=[], help="also time CTA-pair tiles of these widths (224)")
+    for p in (g, t, m, sp, gl):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler}[a.op](a)))
+    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler,
+                      "gemm-layer": bench_gemm_layer}[a.op](a)))
 
 
 if __name__ == "__main__":

@@ -17,9 +17,10 @@ import torch
 import torch.distributed as dist
 
 
-def nccl_grad_sync(world: int):
+def nccl_grad_sync(world: int, group=None):
+    """Mean over the ranks of ``group`` (default: all ranks) with the library all-reduce of the group's backend."""
     def sync(flat_grads: torch.Tensor) -> None:
-        dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM)
+        dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM, group=group)
         flat_grads.div_(world)
     return sync
 

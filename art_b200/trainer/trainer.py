@@ -46,6 +46,9 @@ class TrainHyper:
     rows_per_optimizer_step: int = 1
     tokens_per_microbatch: int = 8192
     compat_row_positions: bool = False
+    # activation recompute of the native decoder: "none" | "mlp" | "full", or "auto" = the cheapest that fits the
+    # free device memory (the reference always checkpoints: use_gradient_checkpointing, src/art/dev/model.py:65)
+    recompute: str = "auto"
 
 
 class Trainer:
@@ -111,6 +114,7 @@ class Trainer:
             for v in self.flat.views.values():
                 v.requires_grad_(True)
             self.model = ReferenceModel(cfg, self.base, self.flat.views, lora_cfg)
+        self.last_recompute = "none"     # activation-recompute mode of the latest native step
         self.opt = FlatAdamW(self.flat.params.detach(), self.flat.grads, betas=betas, eps=adam_eps,
                              weight_decay=weight_decay, max_grad_norm=max_grad_norm)
         self.global_step = 0
@@ -204,6 +208,16 @@ class Trainer:
         rows_per_micro = max(1, min(R, hyper.tokens_per_microbatch // S))
         eps_hi = hyper.epsilon if hyper.epsilon_high is None else hyper.epsilon_high
         sel_host = sel_all if on_host else sel_all.cpu()
+        fwd_kw = {}
+        if self.cp_group is None and self.tp is None:
+            mode = hyper.recompute
+            if mode == "auto":     # decided once per step, before any activation of the step is alive
+                from ..models.native import pick_recompute
+
+                free = torch.cuda.mem_get_info(dev)[0] + torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+                mode = pick_recompute(self.cfg, rows_per_micro * S, len(self.model.layers), free)
+            self.last_recompute = mode
+            fwd_kw["recompute"] = mode
         for r0 in range(0, R, rows_per_micro):
             r1 = min(R, r0 + rows_per_micro)
             M = (r1 - r0) * S
@@ -242,7 +256,7 @@ class Trainer:
             else:
                 sel = sel_all_d[lo:hi] - r0 * S
             with self.timer.phase("forward"):
-                hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S, cp=cp)
+                hidden, saved, final = self.model.forward(tokens, pos, gid, pid, S, cp=cp, **fwd_kw)
             if sel.numel() == 0:
                 # context parallel: this rank's shard holds no trainable token, but its peers still need its
                 # K/V in the forward passes and its (zero) dK/dV in the backward pass
@@ -391,6 +405,10 @@ class Trainer:
             self.flat.grads[n_shared:].div_(self.ep.world)
         elif self.grad_sync is not None:
             self.grad_sync(self.flat.grads)
+            if device_accum is not None and self.dp_group is not None:
+                # loss terms are per-rank means over that rank's rows: report the mean over the data-parallel ranks
+                dist.all_reduce(device_accum[:2], group=self.dp_group)
+                device_accum[:2].div_(dist.get_world_size(self.dp_group))
 
     def phase_summary(self, group=None) -> dict[str, float]:
         """Milliseconds per phase (forward, lm_head_loss, backward, grad_sync, optimizer) since the last call."""
@@ -407,6 +425,14 @@ class Trainer:
             totals = {"policy_loss": pl, "kl_div": kl, "loss": pl + hyper.beta * kl}
         else:
             gn = float(gnorm)
+            if self.dp_group is not None:      # host-side loss terms of the autograd path: mean over the data ranks
+                import torch.distributed as dist
+
+                t = torch.tensor([totals["loss"], totals["policy_loss"], totals["kl_div"]], dtype=torch.float64)
+                t = t.to(self.device) if self.device.type == "cuda" else t
+                dist.all_reduce(t, group=self.dp_group)
+                t = (t / dist.get_world_size(self.dp_group)).tolist()
+                totals = {"loss": t[0], "policy_loss": t[1], "kl_div": t[2]}
         out = {"loss": totals["loss"], "grad_norm": gn, "policy_loss": totals["policy_loss"],
                "learning_rate": hyper.learning_rate}
         if hyper.beta > 0:

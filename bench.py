@@ -9,7 +9,12 @@ One "step" is one GRPO optimizer step over the per-GPU share of the batch the ba
 configuration names (32 groups x 8 rollouts of 2048 tokens over 8 GPUs = 32 packed rows of
 2048 tokens per GPU, 512 shared-prompt tokens + 3 x 512... see ``synthetic_rows``), i.e.
 forward, fused log-prob/GRPO loss, backward, LoRA-gradient all-reduce across the data-parallel
-ranks, gradient clipping and AdamW.  Weights are random-initialised bf16 of the named
+ranks, gradient clipping and AdamW.  On one GPU the model is whole; on N >= 2 GPUs the default
+layout is the one that configuration names, tensor-parallel pairs x data parallel (TP2 x DP N/2:
+fused all-gather->GEMM / GEMM->reduce-scatter inside a pair, fused LoRA-gradient all-reduce
+across pairs); a pair shares its rows, so it gets the rows of two GPUs and the per-GPU work stays
+the same at every N.  ``--parallel dp`` is plain data parallelism; with ``--extra-dp 1`` that
+number is measured too and printed beside the headline as ``extra``.  Weights are random-initialised bf16 of the named
 architecture and token ids are uniform random (no datasets or checkpoints are available).
 
 Timing: ``W`` warm-up steps, then exactly ``K`` steps between CUDA events, bracketed by a
@@ -31,9 +36,6 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Reference numbers on other hardware (1x H100, Qwen2.5-3B 4-bit + LoRA r=8): 9.1-9.2 k packed tok/s
-PUBLISHED_REFERENCE_TOK_S = 9200.0
-
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -48,12 +50,17 @@ def parse_args():
     ap.add_argument("--lora-rank", type=int, default=8)
     ap.add_argument("--attn", default=None)
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"])
-    ap.add_argument("--parallel", default="dp", choices=["dp", "cp", "ep", "tp", "pp"],
-                    help="dp: rows split over GPUs; cp: every row sharded over GPUs (long context); "
+    ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "cp", "ep", "tp", "pp"],
+                    help="auto: tp with --tp-size 2 on two or more GPUs (dense presets; ep for MoE presets); "
+                         "dp: rows split over GPUs; cp: every row sharded over GPUs (long context); "
                          "ep: experts sharded over GPUs (MoE presets); tp: tensor-parallel groups of --tp-size "
                          "GPUs, data parallel across the groups; pp: layers split over the GPUs, 1F1B pipeline")
     ap.add_argument("--tp-size", type=int, default=2)
     ap.add_argument("--rollout", type=int, default=1, help="also measure rollout decode tokens/s (reported beside the headline)")
+    ap.add_argument("--rollout-new-tokens", type=int, default=1536,
+                    help="sampled tokens per sequence in the rollout measurement (the configuration: up to 1536)")
+    ap.add_argument("--extra-dp", type=int, default=0,
+                    help="after a tensor-parallel run also measure plain data parallelism on the same GPUs (reported as `extra`)")
     return ap.parse_args()
 
 
@@ -181,111 +188,138 @@ def main():
     lcfg = LoraConfig(r=args.lora_rank, alpha=2.0 * args.lora_rank)
     impl = "native" if args.impl == "native" else "reference"
     attn_impl = args.attn or ("native" if impl == "native" else "sdpa")
-    base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev, scale_residual_out=cfg.is_moe)
-    grad_sync = None
-    sync_name = "none"
     par = args.parallel if world > 1 else "dp"
-    R, S = args.rows_per_gpu, args.seq_len
-    ep = cp_group = tp_group = pp_group = None
-    expert_range = None
-    data_ranks, data_index = world, rank        # how many ranks hold different rows, and which share this one has
-    if world > 1 and par == "dp":
-        from art_b200.parallel.dp import make_grad_sync
-
-        grad_sync, sync_name = make_grad_sync(args.grad_sync, dev, world)
-    elif par == "cp":
-        cp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over cp)"
-        data_ranks, data_index = 1, 0
-    elif par == "pp":
-        pp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over pp) + NCCL p2p activations"
-        data_ranks, data_index = 1, 0
-    elif par == "tp":
-        T = args.tp_size
-        if world % T:
-            print("bench.py: --tp-size must divide the number of GPUs", file=sys.stderr)
-            return 2
-        from art_b200.parallel.mesh import ParallelLayout
-
-        layout = ParallelLayout(world, tp=T)                # TP innermost: ranks (2i, 2i+1) share activations
-        groups = layout.create_groups(rank)                 # every rank creates every group, in the same order
-        tp_group, dp_group = groups["tp"], groups["dp"]
-        data_index, data_ranks = layout.data_shard(rank)
-        sync_name = f"fused-p2p-allreduce(sum over tp{T})"
-        if data_ranks > 1:
-            from art_b200.parallel.symm_mem import FusedGradAllReduce
-
-            grad_sync = FusedGradAllReduce(dev, data_ranks, dp_group)
-            sync_name += f" + fused-p2p-allreduce(mean over dp{data_ranks})"
-    elif par == "ep":
-        from art_b200.parallel.ep import ExpertParallel
-
-        if not cfg.is_moe:
-            print("bench.py: --parallel ep needs a mixture-of-experts preset (e.g. --model qwen3-30b-a3b)", file=sys.stderr)
-            return 2
-        ep = ExpertParallel(dev, None, args.micro_tokens, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size,
-                            capacity_factor=2.0, drop_overflow=True)
-        El = cfg.num_experts // world
-        expert_range, sync_name = (rank * El, (rank + 1) * El), "nccl-allreduce(shared factors) + 1/world(experts)"
-        # this rank keeps only its experts' frozen weights
-        base = {k: v for k, v in base.items()
-                if ".mlp.experts." not in k or expert_range[0] <= int(k.split(".experts.")[1].split(".")[0]) < expert_range[1]}
-    lora = init_lora(cfg, lcfg, seed=3407, device=dev, expert_range=expert_range)
-    trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync, ep=ep,
-                      cp_group=cp_group, tp_group=tp_group, tp_tokens=args.micro_tokens, pp_group=pp_group)
-    rollout_base = base if (args.rollout and impl == "native" and not cfg.is_moe) else None
-    del base
-    hyper = TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=R, tokens_per_microbatch=args.micro_tokens)
-    # cp: all ranks work on the SAME rows (each holds 1/world of every row); dp / ep: every rank has its own rows
-    host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=data_index + 1).items()}
-    dev_rows = {k: v.to(dev) for k, v in host_rows.items()}
-    tokens_per_step = R * S * data_ranks
+    if par == "auto":
+        par = "ep" if cfg.is_moe else "tp"
+    S = args.seq_len
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(rows, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = _lib.LAUNCHES
-        e0.record()
-        last = None
-        for _ in range(steps):
-            last = trainer.step(rows, hyper)
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), _lib.LAUNCHES - l0, last
+    def measure(par: str, steps: int, warmup: int, keep_base: bool):
+        """Build the trainer for one layout, time it; returns a dict (and the base weights if ``keep_base``)."""
+        base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev, scale_residual_out=cfg.is_moe)
+        grad_sync = None
+        sync_name = "none"
+        R, micro = args.rows_per_gpu, args.micro_tokens
+        ep = cp_group = tp_group = pp_group = None
+        expert_range = None
+        data_ranks, data_index = world, rank        # how many ranks hold different rows, and which share this one has
+        label = f"{par}{world}"
+        if world > 1 and par == "dp":
+            from art_b200.parallel.dp import make_grad_sync
 
-    for _ in range(args.warmup):
-        trainer.step(dev_rows, hyper)
-    if ep is not None:
-        ep.dropped_rows()   # reset the counter: warm-up does not count
-    sampler = ClockSampler(nvml_index(local_rank))
-    sampler.start()
-    ms, launches, last = timed(dev_rows, args.steps)
-    clocks = sampler.stop()
-    ep_drop = None
-    if ep is not None:
-        # share of dispatched (token, expert) rows that found their expert's owner over capacity, forward + backward
-        n = torch.tensor([float(ep.dropped_rows())], device=dev)
-        dist.all_reduce(n)
-        n_layers_moe = cfg.num_layers
-        sent = 2.0 * args.steps * tokens_per_step * cfg.num_experts_per_tok * n_layers_moe
-        ep_drop = round(float(n.item()) / sent, 6)
-    trainer.step(host_rows, hyper)  # warm the host-input path
-    ms_e2e, _, _ = timed(host_rows, args.steps)
-    if os.environ.get("ARTB_PROFILE_STEP"):
-        # one extra step between cudaProfilerStart/Stop for `ncu --profile-from-start off`
-        torch.cuda.synchronize()
-        torch.cuda.profiler.start()
-        trainer.step(dev_rows, hyper)
-        torch.cuda.synchronize()
-        torch.cuda.profiler.stop()
-    _lib.check_status(dev)
+            grad_sync, sync_name = make_grad_sync(args.grad_sync, dev, world)
+        elif par == "cp":
+            cp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over cp)"
+            data_ranks, data_index = 1, 0
+        elif par == "pp":
+            pp_group, sync_name = dist.group.WORLD, "fused-p2p-allreduce(sum over pp) + NCCL p2p activations"
+            data_ranks, data_index = 1, 0
+        elif par == "tp":
+            T = args.tp_size
+            if world % T:
+                raise SystemExit("bench.py: --tp-size must divide the number of GPUs")
+            from art_b200.parallel.mesh import ParallelLayout
+
+            layout = ParallelLayout(world, tp=T)                # TP innermost: ranks (2i, 2i+1) share activations
+            groups = layout.create_groups(rank)                 # every rank creates every group, in the same order
+            tp_group, dp_group = groups["tp"], groups["dp"]
+            data_index, data_ranks = layout.data_shard(rank)
+            # a tensor-parallel group shares its rows: it takes the rows (and micro-batch tokens) of all its GPUs
+            R, micro = R * T, micro * T
+            label = f"tp{T}xdp{data_ranks}"
+            sync_name = f"fused-p2p-allreduce(sum over tp{T})"
+            if data_ranks > 1:
+                from art_b200.parallel.symm_mem import FusedGradAllReduce
+
+                grad_sync = FusedGradAllReduce(dev, data_ranks, dp_group)
+                sync_name += f" + fused-p2p-allreduce(mean over dp{data_ranks})"
+        elif par == "ep":
+            from art_b200.parallel.ep import ExpertParallel
+
+            if not cfg.is_moe:
+                raise SystemExit("bench.py: --parallel ep needs a mixture-of-experts preset (e.g. --model qwen3-30b-a3b)")
+            ep = ExpertParallel(dev, None, micro, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size,
+                                capacity_factor=2.0, drop_overflow=True)
+            El = cfg.num_experts // world
+            expert_range, sync_name = (rank * El, (rank + 1) * El), "nccl-allreduce(shared factors) + 1/world(experts)"
+            # this rank keeps only its experts' frozen weights
+            base = {k: v for k, v in base.items()
+                    if ".mlp.experts." not in k or expert_range[0] <= int(k.split(".experts.")[1].split(".")[0]) < expert_range[1]}
+        lora = init_lora(cfg, lcfg, seed=3407, device=dev, expert_range=expert_range)
+        trainer = Trainer(cfg, base, lcfg, lora, device=dev, impl=impl, attn_impl=attn_impl, grad_sync=grad_sync, ep=ep,
+                          cp_group=cp_group, tp_group=tp_group, tp_tokens=micro, pp_group=pp_group)
+        if not keep_base:
+            base = None
+        hyper = TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=R, tokens_per_microbatch=micro)
+        # cp: all ranks work on the SAME rows (each holds 1/world of every row); dp / ep: every rank has its own rows
+        host_rows = {k: v.pin_memory() for k, v in synthetic_rows(cfg, R, S, seed=data_index + 1).items()}
+        dev_rows = {k: v.to(dev) for k, v in host_rows.items()}
+        tokens_per_step = R * S * data_ranks
+
+        def timed(rows, n):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = _lib.LAUNCHES
+            e0.record()
+            last = None
+            for _ in range(n):
+                last = trainer.step(rows, hyper)
+            e1.record()
+            barrier()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item()), _lib.LAUNCHES - l0, last
+
+        for _ in range(warmup):
+            trainer.step(dev_rows, hyper)
+        if ep is not None:
+            ep.dropped_rows()   # reset the counter: warm-up does not count
+        sampler = ClockSampler(nvml_index(local_rank))
+        sampler.start()
+        ms, launches, last = timed(dev_rows, steps)
+        clocks = sampler.stop()
+        ep_drop = None
+        if ep is not None:
+            # share of dispatched (token, expert) rows that found their expert's owner over capacity, forward + backward
+            n = torch.tensor([float(ep.dropped_rows())], device=dev)
+            dist.all_reduce(n)
+            sent = 2.0 * steps * tokens_per_step * cfg.num_experts_per_tok * cfg.num_layers
+            ep_drop = round(float(n.item()) / sent, 6)
+        trainer.step(host_rows, hyper)  # warm the host-input path
+        ms_e2e, _, _ = timed(host_rows, steps)
+        if os.environ.get("ARTB_PROFILE_STEP"):
+            # one extra step between cudaProfilerStart/Stop for `ncu --profile-from-start off`
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            trainer.step(dev_rows, hyper)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        if os.environ.get("ARTB_PHASE_TIMING") == "1" and rank == 0:
+            print("phases(ms):", json.dumps(trainer.phase_summary()), file=sys.stderr, flush=True)
+        _lib.check_status(dev)
+        if trainer.tp is not None:
+            trainer.tp.close()
+        del trainer
+        torch.cuda.empty_cache()
+        return {"label": label, "ms": ms, "ms_e2e": ms_e2e, "launches": launches, "last": last, "clocks": clocks,
+                "tokens_per_step": tokens_per_step, "global_batch": R * data_ranks, "micro": micro, "sync": sync_name,
+                "ep_drop": ep_drop, "h2d": sum(v.numel() * v.element_size() for v in host_rows.values()), "base": base}
+
+    want_rollout = bool(args.rollout and impl == "native" and not cfg.is_moe)
+    m = measure(par, args.steps, args.warmup, keep_base=want_rollout)
+    rollout_base = m.pop("base")
+    extra = None
+    if args.extra_dp and world > 1 and par == "tp":
+        x = measure("dp", max(2, args.steps // 2), max(3, args.warmup // 2), keep_base=False)
+        extra = {"parallelism": x["label"], "value": round(x["tokens_per_step"] * max(2, args.steps // 2) / (x["ms"] / 1e3), 1),
+                 "unit": "tokens/s", "note": "plain data parallelism on the same GPUs, same per-GPU rows"}
+    ms, ms_e2e, launches, last, clocks = m["ms"], m["ms_e2e"], m["launches"], m["last"], m["clocks"]
+    tokens_per_step, sync_name, ep_drop, h2d = m["tokens_per_step"], m["sync"], m["ep_drop"], m["h2d"]
 
     rollout = None
     if rollout_base is not None:
@@ -294,9 +328,7 @@ def main():
         try:
             from art_b200.engine.bench_decode import measure_decode
 
-            del trainer
-            torch.cuda.empty_cache()
-            rollout = measure_decode(cfg, dev, base=rollout_base)
+            rollout = measure_decode(cfg, dev, base=rollout_base, new_tokens=args.rollout_new_tokens)
             del rollout_base
             agg = torch.tensor([rollout["decode_tok_s"]], device=dev)
             if world > 1:
@@ -307,7 +339,10 @@ def main():
             if world > 1:
                 dist.all_reduce(torch.zeros(1, device=dev))
 
-    h2d = sum(v.numel() * v.element_size() for v in host_rows.values())
+    # frozen weights resident per GPU (W and W^T of the layer stack, bf16), for the note on L2
+    shard = args.tp_size if m["label"].startswith("tp") else (world if par in ("pp", "ep") else 1)
+    emb = cfg.vocab_size * cfg.hidden_size * (1 if cfg.tie_word_embeddings else 2)
+    weight_gb = 2 * 2 * (cfg.num_params() - emb) / shard / 1e9
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
     if rank == 0:
@@ -316,16 +351,15 @@ def main():
                        else f"GRPO train tokens/s, {cfg.name}-arch LoRA"),
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": round(value / PUBLISHED_REFERENCE_TOK_S, 3) if cfg.name == "qwen2.5-7b" else None,
-            "vs_baseline_note": "reference publishes only 9.2k packed tok/s on 1xH100 for Qwen2.5-3B 4-bit LoRA r=8",
+            "vs_baseline": None,     # the reference publishes no throughput for this model / hardware
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": args.impl,
-            "config": {"model": cfg.name, "global_batch": R * data_ranks, "seq_len": S, "parallelism": (f"tp{args.tp_size}xdp{data_ranks}" if par == "tp" else f"{par}{world}"),
-                       "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": args.micro_tokens,
+            "config": {"model": cfg.name, "global_batch": m["global_batch"], "seq_len": S, "parallelism": m["label"],
+                       "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": m["micro"],
                        "attention": attn_impl, "grad_sync": sync_name, "optimizer_steps_per_step": 1,
                        **({"ep_capacity_factor": 2.0, "ep_dropped_row_share": ep_drop} if ep_drop is not None else {}),
-                       "l2": "inputs larger than L2: each step streams the bf16 weights (W and W^T, 30 GB for the 7B "
-                             "model) plus activations"},
+                       "l2": f"inputs larger than L2: each step streams the bf16 weights (W and W^T, "
+                             f"{weight_gb:.0f} GB on this GPU for {cfg.name}) plus activations"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 12,
                     "api": "art_b200.trainer.Trainer.step on pinned host tensors"},
@@ -333,6 +367,8 @@ def main():
             "loss": last["loss"] if last else None,
             "rollout": rollout,
         }
+        if extra is not None:
+            out["extra"] = extra
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -183,3 +183,45 @@ def test_kv_computed_under_replaced_adapter_is_not_reused(tiny):
     hit = eng.bm.match_prefix(prompt, eng._salt(slot))
     assert len(hit) == 3 and again.finished
     eng.bm.free(hit)
+
+
+def test_chunked_prefill_splits_long_prompts_and_matches_unchunked(tiny):
+    cfg, base = tiny
+    p = SamplingParams(max_tokens=4, temperature=0.0)
+    long_prompt = [(7 * i) % 900 + 1 for i in range(50)]
+    short = [3, 4, 5]
+    whole = make_engine(cfg, base, max_num_batched_tokens=4096).generate_sync(long_prompt, p).output_ids
+    eng = make_engine(cfg, base, max_num_batched_tokens=16, num_scheduler_steps=1)      # 4-token blocks
+    a = eng.add_request(long_prompt, p)
+    b = eng.add_request(short, p)
+    eng.step()
+    # first step: a 16-token chunk of the long prompt; the short request waits for budget (FCFS)
+    assert a in eng.prefilling and a.num_cached == 16 and not a.output_ids and eng.has_unfinished
+    steps = 1
+    while not (a.finished and b.finished):
+        eng.step()
+        steps += 1
+        assert steps < 100
+    assert a.output_ids == whole and len(b.output_ids) == 4
+    assert eng.stats.prefill_steps >= 4 and not eng.prefilling        # 50 tokens at <= 16 per step
+    assert eng.stats.prompt_tokens == 50 + 3
+    # the last chunk shares its step with the short prompt when both fit the budget
+    eng2 = make_engine(cfg, base, max_num_batched_tokens=16, num_scheduler_steps=1)
+    a2 = eng2.add_request(long_prompt[:18], p)
+    b2 = eng2.add_request(short, p)
+    eng2.step()
+    eng2.step()
+    assert len(a2.output_ids) == 1 and len(b2.output_ids) == 1
+    # an aborted request gives its blocks back half-way through its prompt
+    eng3 = make_engine(cfg, base, max_num_batched_tokens=16, blocks=32)
+    c = eng3.add_request(long_prompt, p)
+    eng3.step()
+    free_mid = eng3.bm.num_free
+    eng3.abort(c)
+    eng3.step()
+    assert c.finished and c.finish_reason == "abort" and eng3.bm.num_free > free_mid and not eng3.has_unfinished
+    # without chunking an oversized prompt runs whole, alone
+    eng4 = make_engine(cfg, base, max_num_batched_tokens=16, enable_chunked_prefill=False)
+    d = eng4.add_request(long_prompt, p)
+    eng4.step()
+    assert len(d.output_ids) == 1 and not eng4.prefilling

@@ -284,7 +284,7 @@ def test_logit_edit_and_top_logprobs_kernels_match_pytorch():
     got = paged.logit_adjust_(logits.clone(), edits)
     assert torch.allclose(got.cpu(), want, atol=1e-6)
     x = logits.cpu()
-    assert want[1, 5] == (x[1, 5] / 1.7 if x[1, 5] > 0 else x[1, 5] * 1.7)
+    assert torch.isclose(want[1, 5], x[1, 5] / 1.7 if x[1, 5] > 0 else x[1, 5] * 1.7)
     assert torch.isclose(want[2, 7], x[2, 7] - (0.25 * 2 + 0.5) + 4.0) and torch.isclose(want[2, 8], x[2, 8] - 0.75)
     assert want[2, 1] == x[2, 1] and torch.equal(want[0], x[0])       # prompt tokens carry no frequency / presence penalty
     inv_t = torch.tensor([1.0, 0.5, 0.0, 2.0, 1.0], device="cuda")

@@ -367,3 +367,57 @@ def test_engine_sleep_wake_keeps_captured_decode_graphs_valid(use_arena):
         assert same(run(eng, shifted), run(ref, shifted))
     eng.runner.close()
     ref.runner.close()
+
+
+@pytest.mark.parametrize("mode", ["mlp", "full"])
+def test_activation_recompute_gives_the_same_gradients(mode):
+    """Dropping activations and rebuilding them in the backward pass changes memory, not the result."""
+    from art_b200.trainer.trainer import TrainHyper, Trainer
+
+    cfg, base, lcfg, lora = _small_setup()
+    packed = _packed(cfg, 2, 512)
+    make = lambda: Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=DEV, impl="native")  # noqa: E731
+    keep, drop = make(), make()
+    hy = dict(learning_rate=1e-4, beta=0.05, rows_per_optimizer_step=2, tokens_per_microbatch=512)
+    m0 = keep.step(packed, TrainHyper(recompute="none", **hy))
+    m1 = drop.step(packed, TrainHyper(recompute=mode, **hy))
+    assert keep.last_recompute == "none" and drop.last_recompute == mode
+    assert abs(m0["loss"] - m1["loss"]) < 1e-6 and abs(m0["grad_norm"] - m1["grad_norm"]) < 1e-3 * m0["grad_norm"]
+    # same kernels on the same inputs; only the order of the fp32 atomics in the skinny LoRA reductions differs
+    assert rel_err(drop.flat.grads, keep.flat.grads) < 1e-3
+
+
+def test_recompute_policy_and_long_row_memory():
+    """The automatic policy keeps everything when memory allows and falls back as rows grow; one 32 768-token row of
+    a mid-size model trains under "full" with far less memory than "none" needs."""
+    from art_b200.models.config import ModelConfig, PRESETS
+    from art_b200.models.native import activation_bytes_per_token, pick_recompute
+    from art_b200.models.weights import LoraConfig, init_base_weights, init_lora
+    from art_b200.trainer.trainer import TrainHyper, Trainer
+
+    c7 = PRESETS["qwen2.5-7b"]
+    free = 140 << 30
+    assert pick_recompute(c7, 8192, 28, free) == "none"
+    assert pick_recompute(c7, 32768, 28, free) == "mlp"             # the reference's default row length
+    assert pick_recompute(c7, 131072, 28, free) == "full"
+    assert activation_bytes_per_token(c7, "none") > 3 * activation_bytes_per_token(c7, "mlp") > 12 * activation_bytes_per_token(c7, "full")
+    cfg = ModelConfig(name="mid", vocab_size=8192, hidden_size=1024, num_layers=8, num_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=4096)
+    base = init_base_weights(cfg, seed=0, dtype=torch.bfloat16, device=DEV)
+    lcfg = LoraConfig()
+    S = 32768
+    packed = _packed(cfg, 1, S)
+    grads, peaks = {}, {}
+    for mode in ("none", "full"):
+        tr = Trainer(cfg, base, lcfg, init_lora(cfg, lcfg, device=DEV), device=DEV, impl="native")
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        before = torch.cuda.memory_allocated()
+        tr.step(packed, TrainHyper(learning_rate=1e-5, rows_per_optimizer_step=1, tokens_per_microbatch=S, recompute=mode))
+        torch.cuda.synchronize()
+        peaks[mode] = torch.cuda.max_memory_allocated() - before
+        grads[mode] = tr.flat.grads.clone()
+        del tr
+    assert rel_err(grads["full"], grads["none"]) < 1e-3
+    saved_none = S * cfg.num_layers * activation_bytes_per_token(cfg, "none")
+    assert peaks["none"] > saved_none and peaks["full"] < 0.45 * peaks["none"]
