@@ -67,45 +67,105 @@ struct EpiStore {
   int out_f32;
   int res_cols;
   int swiglu_bwd = 0;
+  // Global operands of the NEXT 32-column chunk, loaded while the current chunk is converted and stored.
+  // Residual (4 pieces): each thread reads its own row.  SwiGLU backward (8 pieces = 128 bytes of gate|up per row):
+  // read cooperatively, 8 lanes per row, so that a warp-wide load touches 4 rows x 128 contiguous bytes instead of 32
+  // rows x 16 bytes; the pieces reach their owning thread through a per-warp shared-memory slab, and the result leaves
+  // the same way.  (One row per thread in global memory costs one L1 wavefront per lane and instruction; for this
+  // epilogue, which moves 256 bytes per output row and chunk, that was more LSU time than the tile's main loop has.)
+  uint4 pre[8];
+  int pre_n = 0;     // pieces of `pre` that hold the chunk about to be processed (0: load at the point of use)
 
-  __device__ void tile_begin(const TileInfo&, int) {}
+  __device__ __forceinline__ void issue(const TileInfo& ti, int row, int c) {
+    const int gc = ti.n_blk * BN + c;
+    pre_n = 0;
+    if (gc + 32 > N) return;
+    if (swiglu_bwd) {
+      const int lane = row & 31;
+      const int row0 = ti.m_blk * GEMM_BM + (row & ~31);       // first row of this warp's 32-row band
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int gr = row0 + i * 4 + (lane >> 3);
+        pre[i] = gr < M ? *reinterpret_cast<const uint4*>(H + static_cast<size_t>(gr) * ldh + 2 * gc + (lane & 7) * 8)
+                        : make_uint4(0, 0, 0, 0);
+      }
+      pre_n = 8;
+      return;
+    }
+    const int gr = ti.m_blk * GEMM_BM + row;
+    if (gr < M && R && gc + 32 <= res_cols) {
+      const uint4* r = reinterpret_cast<const uint4*>(R + static_cast<size_t>(gr) * ldr + gc);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pre[j] = r[j];
+      pre_n = 4;
+    }
+  }
+
+  __device__ void tile_begin(const TileInfo& ti, int row) { issue(ti, row, 0); }
   __device__ void tile_end(const TileInfo&, int) {}
 
+  // d(gate|up) of one 32-column chunk of d(activation); executed by whole warps (rows past M are masked, not skipped)
+  __device__ __forceinline__ void chunk_swiglu_bwd(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    __shared__ uint4 s_slab[4][32 * 9];      // per epilogue warp: 32 rows x (8 + 1 pad) 16-byte pieces
+    const int gc = ti.n_blk * BN + c;
+    if (gc >= N) return;                     // warp-uniform
+    const int lane = row & 31;
+    uint4* sb = s_slab[(row >> 5) & 3];
+    const int row0 = ti.m_blk * GEMM_BM + (row & ~31);
+    // gate|up pieces -> slab (row-major, padded), then every thread picks up its own row
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sb[(i * 4 + (lane >> 3)) * 9 + (lane & 7)] = pre[i];
+    __syncwarp();
+    if (c + 32 < BN) issue(ti, row, c + 32);
+    uint4 in[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) in[j] = sb[lane * 9 + j];
+    __syncwarp();
+    // columns gc .. gc+31 of the activation map to columns 2gc .. 2gc+63 of gate|up: [g 0-15 | u 0-15 | g 16-31 | u 16-31]
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&in[blk * 4]);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&in[blk * 4 + 2]);
+      uint4 dg[2], du[2];
+      uint32_t* dgp = reinterpret_cast<uint32_t*>(dg);
+      uint32_t* dup = reinterpret_cast<uint32_t*>(du);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float2 g2 = __bfloat1622float2(gp[e]), u2 = __bfloat1622float2(up[e]);
+        const float d0 = __uint_as_float(acc[blk * 16 + 2 * e]), d1 = __uint_as_float(acc[blk * 16 + 2 * e + 1]);
+        const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+        dgp[e] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+        dup[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+      }
+      sb[lane * 9 + blk * 4] = dg[0];
+      sb[lane * 9 + blk * 4 + 1] = dg[1];
+      sb[lane * 9 + blk * 4 + 2] = du[0];
+      sb[lane * 9 + blk * 4 + 3] = du[1];
+    }
+    __syncwarp();
+    __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(C) + 2 * gc + (lane & 7) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      if (row0 + r < M) *reinterpret_cast<uint4*>(dgu + static_cast<size_t>(row0 + r) * ldc) = sb[r * 9 + (lane & 7)];
+    }
+    __syncwarp();
+  }
+
   __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
+    if (swiglu_bwd) {
+      chunk_swiglu_bwd(ti, row, c, acc);
+      return;
+    }
     const int gr = ti.m_blk * GEMM_BM + row;
     const int gc = ti.n_blk * BN + c;
     if (gr >= M || gc >= N) return;
     const bool full = (gc + 32 <= N);
-    if (swiglu_bwd) {
-      // columns gc .. gc+31 of the activation map to columns 2gc .. 2gc+63 of gate|up: [g 0-15 | u 0-15 | g 16-31 | u 16-31]
-      const __nv_bfloat16* gu = H + static_cast<size_t>(gr) * ldh + 2 * gc;
-      __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<size_t>(gr) * ldc + 2 * gc;
+    uint4 cur[4];
+    const int cur_n = pre_n;
 #pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        uint4 gv[2], uv[2], dg[2], du[2];
-        gv[0] = *reinterpret_cast<const uint4*>(gu + blk * 32);
-        gv[1] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 8);
-        uv[0] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 16);
-        uv[1] = *reinterpret_cast<const uint4*>(gu + blk * 32 + 24);
-        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(gv);
-        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(uv);
-        uint32_t* dgp = reinterpret_cast<uint32_t*>(dg);
-        uint32_t* dup = reinterpret_cast<uint32_t*>(du);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float2 g2 = __bfloat1622float2(gp[e]), u2 = __bfloat1622float2(up[e]);
-          const float d0 = __uint_as_float(acc[blk * 16 + 2 * e]), d1 = __uint_as_float(acc[blk * 16 + 2 * e + 1]);
-          const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
-          dgp[e] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
-          dup[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
-        }
-        *reinterpret_cast<uint4*>(dgu + blk * 32) = dg[0];
-        *reinterpret_cast<uint4*>(dgu + blk * 32 + 8) = dg[1];
-        *reinterpret_cast<uint4*>(dgu + blk * 32 + 16) = du[0];
-        *reinterpret_cast<uint4*>(dgu + blk * 32 + 24) = du[1];
-      }
-      return;
-    }
+    for (int j = 0; j < 4; ++j) cur[j] = pre[j];
+    if (c + 32 < BN) issue(ti, row, c + 32);
     if (bias) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -116,7 +176,7 @@ struct EpiStore {
       if (gc + 32 <= res_cols) {
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-          uint4 rv = *reinterpret_cast<const uint4*>(r + j);
+          uint4 rv = cur_n == 4 ? cur[j >> 3] : *reinterpret_cast<const uint4*>(r + j);
           const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -210,7 +270,9 @@ struct SchedGrouped {
 template <int BN>
 struct EpiGrouped {
   EpiStore<BN> st;
-  __device__ void tile_begin(const TileInfo&, int) {}
+  __device__ void tile_begin(const TileInfo& ti, int row) {
+    if (ti.group >= 0) st.tile_begin(ti, row);
+  }
   __device__ void tile_end(const TileInfo&, int) {}
   __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
     if (ti.group >= 0) st.chunk(ti, row, c, acc);

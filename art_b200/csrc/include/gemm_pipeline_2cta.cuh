@@ -110,7 +110,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             *abort_flag = 1;
             break;
           }
-          if (*abort_flag) break;
           uint8_t* sa = smem + s * G2_STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           if (leader) mbar_expect_tx(&full_bar[s], 2 * G2_STAGE_BYTES);

@@ -100,7 +100,7 @@ ARTB_EXPORT int artb_gemm_bf16_tn_2cta(const void* A, int lda, const void* B, in
   // 224-wide cluster tiles waste less of the last wave for some N (3584: 6.92 waves instead of 6.05) but
   // measured no faster under the power cap; they are kept for explicit requests (max_clusters < 0).
   if (max_clusters < 0)
-    return launch_2cta<7, 224>(A, lda, B, ldb, A2, lda2, B2, ldb2, K2, C, ldc, R, ldr, H, ldh, bias, M, N, K, epilogue,
+    return launch_2cta<6, 224>(A, lda, B, ldb, A2, lda2, B2, ldb2, K2, C, ldc, R, ldr, H, ldh, bias, M, N, K, epilogue,
                                res_cols, status, -max_clusters, stream);
   return launch_2cta<6, 256>(A, lda, B, ldb, A2, lda2, B2, ldb2, K2, C, ldc, R, ldr, H, ldh, bias, M, N, K, epilogue,
                              res_cols, status, max_clusters, stream);

@@ -107,6 +107,11 @@ def bench_gemm_layer(a) -> dict:
         row = {"gemm": name, "n": N, "k": K, "epilogue": epi}
         ms = _sustained(lambda: gemm_tn(x, w, out=out, **kw), a.seconds)
         row["ms"], row["tflops"] = round(ms, 4), round(fl / ms / 1e9, 1)
+        if a.ablate:      # what the LoRA extra-K block and the epilogue cost: the same product without them
+            ms_p = _sustained(lambda: gemm_tn(x, w, out=plain), a.seconds)
+            row["plain_tflops"] = round(fl / ms_p / 1e9, 1)
+            ms_e = _sustained(lambda: gemm_tn(x, w, out=out, **{k: v for k, v in kw.items() if k not in ("a2", "b2")}), a.seconds)
+            row["no_lora_tflops"] = round(fl / ms_e / 1e9, 1)
         if a.try_bn:
             for bn in a.try_bn:
                 try:
@@ -278,6 +283,7 @@ def main() -> None:
     gl.add_argument("--tokens", type=int, default=8192)
     gl.add_argument("--seconds", type=float, default=0.5, help="length of each back-to-back timing run")
     gl.add_argument("--try-bn", type=int, nargs="*", default=[], help="also time CTA-pair tiles of these widths (224)")
+    gl.add_argument("--ablate", action="store_true", help="also time each product without LoRA / without its epilogue")
     for p in (g, t, m, sp, gl):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)

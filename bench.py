@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--model", default="qwen2.5-7b")
     ap.add_argument("--rows-per-gpu", type=int, default=32)
     ap.add_argument("--seq-len", type=int, default=2048)
-    ap.add_argument("--micro-tokens", type=int, default=8192)
+    ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--lora-rank", type=int, default=8)
     ap.add_argument("--attn", default=None)
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"])
