@@ -16,6 +16,7 @@
 // inference library).
 #include <string.h>
 
+#include "gemm_pipeline_2cta.cuh"
 #include "host_utils.h"
 #include "tp_policies.cuh"
 
@@ -40,6 +41,28 @@ static int launch_rs(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, comm);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// CTA-pair form (256 x 256 tiles): each CTA of a pair scatters / reduces its own 128 x 256 half of the tile.
+static int launch_rs_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2, const CUtensorMap& tB2,
+                          int kb_main, int kb_extra, const SchedSegRot& sched, const EpiReduceScatter<256>& epi,
+                          const RsComm& comm, int* status, int max_ctas, cudaStream_t stream) {
+  using L = Gemm2SmemLayout<6, 256>;
+  auto kern = gemm_tcgen05_2cta_kernel<6, 256, SchedSegRot, EpiReduceScatter<256>, RsComm>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev & 63] = true;
+  }
+  int clusters = sched.seg_m_tiles * sched.n_tiles * sched.world;
+  int cap = sm_count() / 2;
+  if (max_ctas > 0 && max_ctas / 2 < cap) cap = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (clusters > cap) clusters = cap;
+  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, comm);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -70,13 +93,15 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   const int bn = 256;   // EpiReduceScatter pairs 32-column slabs: the tile width must be a multiple of 64
   const int n_tiles = (N + bn - 1) / bn;
   if ((m_seg / GEMM_BM) * n_tiles > tile_cap) return ERR_TOO_LARGE;
+  const bool pair = m_seg % (2 * GEMM_BM) == 0 && max_ctas != 1;
+  const int b_box = pair ? bn / 2 : bn;      // a CTA of a pair stages half of the B tile
   CUtensorMap tA, tB, tA2, tB2;
   int e;
   if ((e = make_tmap_bf16_2d(&tA, A, M, K, lda, GEMM_BM, GEMM_BK))) return e;
-  if ((e = make_tmap_bf16_2d(&tB, B, N, K, ldb, bn, GEMM_BK))) return e;
+  if ((e = make_tmap_bf16_2d(&tB, B, N, K, ldb, b_box, GEMM_BK))) return e;
   if (K2 > 0) {
     if ((e = make_tmap_bf16_2d(&tA2, A2, M, K2, lda2, GEMM_BM, GEMM_BK))) return e;
-    if ((e = make_tmap_bf16_2d(&tB2, B2, N, K2, ldb2, bn, GEMM_BK))) return e;
+    if ((e = make_tmap_bf16_2d(&tB2, B2, N, K2, ldb2, b_box, GEMM_BK))) return e;
   } else {
     tA2 = tA;
     tB2 = tB;
@@ -112,7 +137,11 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   comm.world = world;
   comm.epoch = epoch;
   comm.cta_counter = cta_counter;
-  SchedSegRot sched{m_seg / GEMM_BM, n_tiles, world, s->rank, 1};
+  SchedSegRot sched{m_seg / GEMM_BM, n_tiles, world, s->rank, 1, pick_group_m(m_seg / GEMM_BM, GEMM_BM, K)};
   const int kb_main = (K + GEMM_BK - 1) / GEMM_BK, kb_extra = (K2 + GEMM_BK - 1) / GEMM_BK;
+  if (pair) {
+    SchedSegRot sched2{m_seg / (2 * GEMM_BM), n_tiles, world, s->rank, 1, pick_group_m(m_seg / (2 * GEMM_BM), 2 * GEMM_BM, K)};
+    return launch_rs_pair(tA, tB, tA2, tB2, kb_main, kb_extra, sched2, epi, comm, status, max_ctas, stream);
+  }
   return launch_rs<256, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, comm, status, max_ctas, stream);
 }

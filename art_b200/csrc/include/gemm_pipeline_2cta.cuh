@@ -32,12 +32,41 @@ struct Gemm2SmemLayout {
   static constexpr int TOTAL = BAR_OFFSET + BAR_BYTES + 1024;
 };
 
-template <int STAGES, int BN2, class Epi>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+// Schedule of the plain and split-K CTA-pair GEMMs.  `m_blk` of the tiles it returns counts 256-row PAIR tiles (the
+// kernel turns it into each CTA's 128-row index).  splits > 1: the K range of every output tile is cut into `splits`
+// slices of kb_per blocks; a work item is (tile, slice) and its partial goes through an accumulating epilogue (no
+// extra-K operands in that mode).
+struct SchedPair {
+  int m_tiles2, n_tiles, group_m, splits, kb_per, kb_main;
+  __device__ int tiles_for_cta(int cluster, int nclusters) const {
+    const int total = m_tiles2 * n_tiles * splits;
+    return cluster < total ? (total - cluster + nclusters - 1) / nclusters : 0;
+  }
+  __device__ TileInfo get(int cluster, int nclusters, int i) const {
+    const int tile = cluster + i * nclusters;
+    const int mn_tiles = m_tiles2 * n_tiles;
+    const int mn = tile % mn_tiles, sp = tile / mn_tiles;
+    int m2, nb;
+    raster_tile(mn, m_tiles2, n_tiles, group_m, m2, nb);
+    TileInfo ti = make_tile(m2, nb);
+    if (splits > 1) {
+      ti.group = sp;
+      ti.kb_lo = sp * kb_per;
+      ti.kb_n = max(0, min(kb_per, kb_main - ti.kb_lo));
+      ti.extra = 0;
+    }
+    return ti;
+  }
+};
+
+// Sched: tiles in units of 256 x BN2 (see SchedPair); Epi / Comm: the same policies as the one-CTA pipeline, called
+// per CTA with that CTA's 128-row tile index, so the fused tensor-parallel policies work unchanged (each CTA's producer
+// waits for the arrival of its own 128 rows; each CTA's epilogue scatters / reduces its own 128 x BN2 half).
+template <int STAGES, int BN2, class Sched, class Epi, class Comm = NoComm>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS + Comm::THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                         int kb_main, int kb_extra, int m_tiles2, int n_tiles, Epi epi_in, int* status, int splits,
-                         int kb_per, int group_m) {
+                         int kb_main, int kb_extra, Sched sched, Epi epi_in, int* status, Comm comm) {
   using L = Gemm2SmemLayout<STAGES, BN2>;
   constexpr int G2_BN = BN2, G2_BNH = BN2 / 2, G2_STAGE_BYTES = L::STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
@@ -57,12 +86,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const bool leader = rank == 0;
   const int cluster_id = blockIdx.x >> 1;
   const int n_clusters = gridDim.x >> 1;
-  // splits > 1: the K range of every output tile is cut into `splits` slices of kb_per blocks; a work item is
-  // (tile, slice) and its partial goes through an accumulating epilogue (no extra-K operands in that mode)
-  const int mn_tiles = m_tiles2 * n_tiles;
-  const int total_tiles = mn_tiles * splits;
-  const int my_tiles = cluster_id < total_tiles ? (total_tiles - cluster_id + n_clusters - 1) / n_clusters : 0;
-  const int kb_total = kb_main + kb_extra;
+  const int my_tiles = sched.tiles_for_cta(cluster_id, n_clusters);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -92,19 +116,28 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      if (kb_extra > 0) {
+        tma_prefetch_desc(&tmA2);
+        tma_prefetch_desc(&tmB2);
+      }
       uint32_t it = 0;
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
-        const int tile = cluster_id + t * n_clusters;
-        const int mn = tile % mn_tiles, sp = tile / mn_tiles;
-        int m2, nb;
-        raster_tile(mn, m_tiles2, n_tiles, group_m, m2, nb);
-        const int row_a = m2 * 2 * GEMM_BM + rank * GEMM_BM;
-        const int row_b = nb * G2_BN + rank * G2_BNH;
-        const int kb_lo = sp * kb_per;
-        const int kb_hi = splits > 1 ? min(kb_main, kb_lo + kb_per) : kb_total;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        TileInfo ti = sched.get(cluster_id, n_clusters, t);
+        ti.m_blk = ti.m_blk * 2 + static_cast<int>(rank);
+        const int row_a = ti.m_blk * GEMM_BM;
+        const int row_b = ti.n_blk * G2_BN + static_cast<int>(rank) * G2_BNH + ti.b_row;
+        const int nmain = ti.kb_n < 0 ? kb_main : ti.kb_n;
+        const int ntile = nmain + (ti.extra ? kb_extra : 0);
+        if (!comm.ready(ti)) {
+          atomicMax(status, ST_TIMEOUT_PEER);
+          *abort_flag = 1;
+          break;
+        }
+        for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          // no abort poll in this loop: the time from "stage free" to "loads issued" is on the pipeline's critical
+          // path; a partner that gave up is noticed through this wait's own limit
           if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
             atomicMax(status, ST_TIMEOUT_EMPTY);
             *abort_flag = 1;
@@ -114,11 +147,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint8_t* sb = sa + L::A_BYTES;
           if (leader) mbar_expect_tx(&full_bar[s], 2 * G2_STAGE_BYTES);
           const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
-          if (kb < kb_main) {
-            tma_load_2d_2cta(sa, &tmA, kb * GEMM_BK, row_a, fb);
-            tma_load_2d_2cta(sb, &tmB, kb * GEMM_BK, row_b, fb);
+          if (kb < nmain) {
+            tma_load_2d_2cta(sa, &tmA, (ti.kb_lo + kb) * GEMM_BK, row_a, fb);
+            tma_load_2d_2cta(sb, &tmB, (ti.kb_lo + kb) * GEMM_BK, row_b, fb);
           } else {
-            const int k2 = (kb - kb_main) * GEMM_BK;
+            const int k2 = (kb - nmain) * GEMM_BK;
             tma_load_2d_2cta(sa, &tmA2, k2, row_a, fb);
             tma_load_2d_2cta(sb, &tmB2, k2, row_b, fb);
           }
@@ -140,9 +173,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * G2_BN;
-        const int kb_lo = ((cluster_id + t * n_clusters) / mn_tiles) * kb_per;
-        const int kb_hi = splits > 1 ? min(kb_main, kb_lo + kb_per) : kb_total;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        const TileInfo ti = sched.get(cluster_id, n_clusters, t);
+        const int ntile = (ti.kb_n < 0 ? kb_main : ti.kb_n) + (ti.extra ? kb_extra : 0);
+        for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph)) {
@@ -157,13 +190,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint64_t bdesc = umma_smem_desc_k128(sb);
 #pragma unroll
           for (int k = 0; k < GEMM_BK / 16; ++k)
-            tc_mma_f16_2cta(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb_lo) | k) != 0);
+            tc_mma_f16_2cta(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
           tc_commit_2cta(&empty_bar[s], 3);   // both CTAs may refill this stage once the MMAs retire
         }
         if (*abort_flag) break;
         tc_commit_2cta(&tfull_bar[buf], 3);   // accumulator complete in both CTAs
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ communication warps
+    comm.push(static_cast<int>(threadIdx.x) - GEMM_THREADS, status);
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     Epi epi = epi_in;
@@ -171,17 +207,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int row = q * 32 + lane;
     for (int t = 0; t < my_tiles; ++t) {
       if (__shfl_sync(0xffffffffu, *abort_flag, 0)) break;
-      const int tile = cluster_id + t * n_clusters;
-      const int mn = tile % mn_tiles;
-      int m2, nb;
-      raster_tile(mn, m_tiles2, n_tiles, group_m, m2, nb);
-      TileInfo ti = make_tile(m2 * 2 + static_cast<int>(rank), nb);
-      if (splits > 1) {
-        ti.group = tile / mn_tiles;
-        ti.kb_lo = ti.group * kb_per;
-        ti.kb_n = max(0, min(kb_per, kb_main - ti.kb_lo));
-        ti.extra = 0;
-      }
+      TileInfo ti = sched.get(cluster_id, n_clusters, t);
+      ti.m_blk = ti.m_blk * 2 + static_cast<int>(rank);
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
       const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;
@@ -212,6 +239,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0 && !*abort_flag) comm.finish(status);
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();

@@ -19,11 +19,12 @@ namespace artb {
 constexpr int TP_MAX = 8;
 constexpr int TP_PUSH_ROWS = 32;   // rows per push unit / arrival flag
 
-// Token segments (one per rank) are visited in rotated order, M fastest inside a segment.
+// Token segments (one per rank) are visited in rotated order; inside a segment the tiles follow the grouped order
+// of raster_tile (bands of group_m tile rows, M fastest inside a band), so that the band of A in use stays in L2.
 // first_off = 0: own segment first (all-gather: local data is there already);
 // first_off = 1: own segment last  (reduce-scatter: peers' partials arrive while we compute theirs).
 struct SchedSegRot {
-  int seg_m_tiles, n_tiles, world, rank, first_off;
+  int seg_m_tiles, n_tiles, world, rank, first_off, group_m;
   __device__ int tiles_for_cta(int cta, int ncta) const {
     const int total = seg_m_tiles * n_tiles * world;
     return cta < total ? (total - cta + ncta - 1) / ncta : 0;
@@ -33,7 +34,9 @@ struct SchedSegRot {
     const int per_seg = seg_m_tiles * n_tiles;
     const int si = t / per_seg, rem = t - si * per_seg;
     const int seg = (rank + first_off + si) % world;
-    TileInfo ti = make_tile(seg * seg_m_tiles + rem % seg_m_tiles, rem / seg_m_tiles);
+    int m, n;
+    raster_tile(rem, seg_m_tiles, n_tiles, group_m, m, n);
+    TileInfo ti = make_tile(seg * seg_m_tiles + m, n);
     ti.group = seg;
     return ti;
   }

@@ -25,7 +25,7 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
     tB2 = tB;
   }
   const int kb_main = (K + GEMM_BK - 1) / GEMM_BK, kb_extra = (K2 + GEMM_BK - 1) / GEMM_BK;
-  auto kern = gemm_tcgen05_2cta_kernel<STAGES, BN2, EpiStore<BN2>>;
+  auto kern = gemm_tcgen05_2cta_kernel<STAGES, BN2, SchedPair, EpiStore<BN2>>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -42,8 +42,9 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
   EpiStore<BN2> epi{C, reinterpret_cast<const __nv_bfloat16*>(R), reinterpret_cast<__nv_bfloat16*>(H), bias, ldc, ldr,
                       ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};
-  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, m_tiles2, n_tiles, epi,
-                                                        status, 1, kb_main, pick_group_m(m_tiles2, 2 * GEMM_BM, K));
+  SchedPair sched{m_tiles2, n_tiles, pick_group_m(m_tiles2, 2 * GEMM_BM, K), 1, kb_main, kb_main};
+  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status,
+                                                        NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -62,7 +63,7 @@ static int launch_2cta_splitk(const void* A, int lda, const void* B, int ldb, fl
   if (splits > kb_main) splits = kb_main;
   const int kb_per = (kb_main + splits - 1) / splits;
   splits = (kb_main + kb_per - 1) / kb_per;   // no empty slice
-  auto kern = gemm_tcgen05_2cta_kernel<STAGES, BN2, EpiAtomic<BN2>>;
+  auto kern = gemm_tcgen05_2cta_kernel<STAGES, BN2, SchedPair, EpiAtomic<BN2>>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -75,8 +76,8 @@ static int launch_2cta_splitk(const void* A, int lda, const void* B, int ldb, fl
   int clusters = m_tiles2 * n_tiles * splits;
   if (clusters > sm_count() / 2) clusters = sm_count() / 2;
   EpiAtomic<BN2> epi{ws, ldw, M, N};
-  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, m_tiles2, n_tiles, epi, status,
-                                                        splits, kb_per, m_tiles2);
+  SchedPair sched{m_tiles2, n_tiles, m_tiles2, splits, kb_per, kb_main};
+  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, sched, epi, status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -98,9 +98,12 @@ class ColumnParallelLinear(_TPLinear):
             m.gb_view[m.own] = self.dB_acc[m.rows, c0:c0 + r] * self.scale
 
     def forward(self, h_shard, use_lora=True, swiglu_out=None, save=True):
+        """``h_shard`` may already BE the view returned by ``tp.ag_input(K)`` (the producer wrote into it)."""
         tp = self.tp
         K = self.W.shape[1]
-        tp.ag_input(K).copy_(h_shard)
+        dst = tp.ag_input(K)
+        if h_shard.data_ptr() != dst.data_ptr():
+            dst.copy_(h_shard)
         lora = self.active and use_lora
         if lora:
             gemm_tn(h_shard, self.A_cat, out=tp.ag_t_input())
@@ -167,14 +170,18 @@ class RowParallelLinear(_TPLinear):
             return y, (T if save else None)
         return self.tp.gemm_rs(x_p, self.W, residual=residual_shard), None
 
-    def backward(self, dy_shard, x_p, T):
+    def backward(self, dy_shard, x_p, T, swiglu_gu=None):
+        """``swiglu_gu``: this linear's input was ``silu(gate) * up``; return d(gate|up) instead of d(input).
+        ``dy_shard`` may already be the view returned by ``tp.ag_input(N)``."""
         tp = self.tp
         N = self.W.shape[0]
-        tp.ag_input(N).copy_(dy_shard)
+        dst = tp.ag_input(N)
+        if dy_shard.data_ptr() != dst.data_ptr():
+            dst.copy_(dy_shard)
         lora = self.active and T is not None
         if lora:
             gemm_tn(dy_shard, self.B_catT, out=tp.ag_t_input())
-        dx_p, dy_full, dT_full = tp.ag_gemm(N, self.WT, b2=self.A_catT if lora else None)
+        dx_p, dy_full, dT_full = tp.ag_gemm(N, self.WT, b2=self.A_catT if lora else None, swiglu_bwd_gu=swiglu_gu)
         if lora:
             lora_wgrad(self.dA_acc, x_p, dT_full)
             lora_wgrad(self.dB_acc, dy_full, T)
@@ -292,7 +299,8 @@ class TPDecoder:
         saved = []
         for layer in self.layers:
             sv = TPLayerSaved()
-            h1, rstd1 = ew.rmsnorm_fwd(x, layer["ln1"], cfg.rms_norm_eps)
+            # the norm writes its output straight into this rank's rows of the gathered operand
+            h1, rstd1 = ew.rmsnorm_fwd(x, layer["ln1"], cfg.rms_norm_eps, out=self.tp.ag_input(cfg.hidden_size))
             qkv, qkv_in = layer["qkv"].forward(h1, use_lora, save=save)
             if cfg.qk_norm:
                 if save:
@@ -303,7 +311,7 @@ class TPDecoder:
             ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
             o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
             x2, T_o = layer["o"].forward(o, x, use_lora, save=save)
-            h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps)
+            h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps, out=self.tp.ag_input(cfg.hidden_size))
             hact = torch.empty((qkv.shape[0], self.Fl), dtype=x.dtype, device=x.device)
             gu, gu_in = layer["gu"].forward(h2, use_lora, swiglu_out=hact, save=save)
             x3, T_d = layer["down"].forward(hact, x2, use_lora, save=save)
@@ -317,15 +325,18 @@ class TPDecoder:
 
     def backward(self, dhidden, saved, final, pos):
         cfg, Hq, Hkv, hd = self.cfg, self.Hq, self.Hkv, self.cfg.head_dim
-        dx = ew.rmsnorm_bwd(dhidden, final["x_last"], self.final_norm, final["rstd_f"])
+        # every residual-stream gradient is the input of the next all-gather->GEMM: the norm backward writes it straight
+        # into this rank's rows of the gathered operand (the buffers alternate per call, so the previous one, still
+        # needed as the residual term of the following norm backward, stays intact)
+        d = cfg.hidden_size
+        dx = ew.rmsnorm_bwd(dhidden, final["x_last"], self.final_norm, final["rstd_f"], out=self.tp.ag_input(d))
         for li in range(cfg.num_layers - 1, -1, -1):
             layer, sv = self.layers[li], saved[li]
-            dhact = layer["down"].backward(dx, sv.hact, sv.T_d)                 # [M, F/P]
-            dgu = ew.swiglu_bwd(dhact, sv.gu)
-            del dhact
+            # d(gate|up) [M, 2F/P]: the SwiGLU backward sits in the epilogue of the down projection's data-gradient GEMM
+            dgu = layer["down"].backward(dx, sv.hact, sv.T_d, swiglu_gu=sv.gu)
             dh2 = layer["gu"].backward(dgu, sv.gu_in)                          # [m_seg, d]
             del dgu
-            dx2 = ew.rmsnorm_bwd(dh2, sv.x2, layer["ln2"], sv.rstd2, dres=dx)
+            dx2 = ew.rmsnorm_bwd(dh2, sv.x2, layer["ln2"], sv.rstd2, dres=dx, out=self.tp.ag_input(d))
             del dh2
             do = layer["o"].backward(dx2, sv.o, sv.T_o)                        # [M, q/P]
             dqkv = attn_ops.backward(do, sv.attn_ctx)
@@ -341,5 +352,5 @@ class TPDecoder:
             dh1 = layer["qkv"].backward(dqkv, sv.qkv_in, need_dx=need_dx)
             del dqkv
             if need_dx:
-                dx = ew.rmsnorm_bwd(dh1, sv.x, layer["ln1"], sv.rstd1, dres=dx2)
+                dx = ew.rmsnorm_bwd(dh1, sv.x, layer["ln1"], sv.rstd1, dres=dx2, out=self.tp.ag_input(d))
             saved[li] = None

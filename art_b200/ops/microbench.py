@@ -52,9 +52,10 @@ def bench_gemm(a) -> dict:
     return res
 
 
-def _sustained(fn, seconds: float = 0.6, warm: int = 5) -> float:
+def _sustained(fn, seconds: float = 0.6, warm: int = 5, agree=None) -> float:
     """Milliseconds per call with the calls issued back to back (no host sync, no flush) for about ``seconds``: the
-    rate a kernel holds inside a long training step, under the power cap."""
+    rate a kernel holds inside a long training step, under the power cap.  ``agree`` (int -> int) makes several ranks
+    settle on ONE repetition count: a call that contains a collective must run equally often everywhere."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -64,6 +65,8 @@ def _sustained(fn, seconds: float = 0.6, warm: int = 5) -> float:
     e1.record()
     torch.cuda.synchronize()
     reps = max(10, int(seconds * 1e3 / max(1e-3, e0.elapsed_time(e1))))
+    if agree is not None:
+        reps = agree(reps)
     e0.record()
     for _ in range(reps):
         fn()
@@ -134,6 +137,101 @@ def bench_gemm_layer(a) -> dict:
         res["cublas_layer_ms"] = round(tot_lib, 3)
         res["cublas_layer_tflops"] = round(tot_fl / tot_lib / 1e9, 1)
     return res
+
+
+def bench_tp_layer(a) -> dict:
+    """The eight fused tensor-parallel GEMMs of one decoder layer (run under torchrun, one rank per GPU): all-gather->GEMM
+    for the column-parallel products, GEMM->reduce-scatter for the row-parallel ones, each sustained, next to (a) the
+    same product as a plain local GEMM without communication (the compute floor of this kernel family) and (b) the
+    library pair NCCL collective + cuBLAS.  Times are the maximum over ranks."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..models.config import PRESETS
+    from ..parallel.tp import TPContext, unfused_ag_gemm, unfused_gemm_rs
+    from . import _lib
+    from .gemm import gemm_tn
+
+    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import datetime
+
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
+    P = dist.get_world_size()
+    cfg = PRESETS[a.model]
+    bf = torch.bfloat16
+    M, d, q, kv, F = a.tokens, cfg.hidden_size, cfg.q_size // P, cfg.kv_size // P, cfg.intermediate_size // P
+    m_seg = M // P
+    g = torch.Generator(device=dev).manual_seed(rank)
+    rnd = lambda *s, sc=1.0: (torch.randn(*s, device=dev, generator=g) * sc).to(bf)      # noqa: E731
+    ctx = TPContext(dev, None, m_seg, k_max=d, n_max=d, kt=64)
+
+    def mx(ms: float) -> float:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def agree(reps: int) -> int:
+        t = torch.tensor([reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return int(t)
+
+    def sustained(fn):
+        dist.barrier()
+        return mx(_sustained(fn, a.seconds, agree=agree))
+
+    rows = []
+    # all-gather -> GEMM: gathered K = d; name, local N, epilogue
+    for name, N, epi in (("qkv", q + 2 * kv, "plain"), ("gate_up", 2 * F, "swiglu"), ("d_down", F, "swiglu_bwd"), ("d_o", q, "plain")):
+        x_shard, w, b2 = rnd(m_seg, d), rnd(N, d, sc=0.02), rnd(N, 64, sc=0.02)
+        t_shard = rnd(m_seg, 64, sc=0.1)
+        kw = {}
+        if epi == "swiglu":
+            kw["swiglu_out"] = torch.empty(M, N // 2, device=dev, dtype=bf)
+        elif epi == "swiglu_bwd":
+            kw["swiglu_bwd_gu"] = rnd(M, 2 * N)
+        out = torch.empty(M, 2 * N if epi == "swiglu_bwd" else N, device=dev, dtype=bf)
+
+        def fused():
+            ctx.ag_input(d).copy_(x_shard)
+            ctx.ag_t_input().copy_(t_shard)
+            ctx.ag_gemm(d, w, b2=b2, out=out, **kw)
+
+        x_full, t_full = rnd(M, d), rnd(M, 64, sc=0.1)
+        fl = 2.0 * M * N * d
+        ms_f = sustained(fused)
+        ms_l = sustained(lambda: gemm_tn(x_full, w, a2=t_full, b2=b2, out=out, **kw))
+        ms_u = sustained(lambda: unfused_ag_gemm(x_shard, w))
+        rows.append({"op": "ag_gemm", "gemm": name, "n": N, "k": d, "epilogue": epi, "fused_ms": round(ms_f, 4),
+                     "fused_tflops": round(fl / ms_f / 1e9, 1), "local_gemm_ms": round(ms_l, 4), "nccl_cublas_ms": round(ms_u, 4),
+                     "nvlink_mb_in": round((P - 1) * m_seg * (d + 64) * 2 / 1e6, 1)})
+        del x_shard, w, b2, out, x_full, kw
+    # GEMM -> reduce-scatter: N = d; name, local K
+    for name, K in (("o", q), ("down", F), ("d_gate_up", 2 * F), ("d_qkv", q + 2 * kv)):
+        x, w = rnd(M, K), rnd(d, K, sc=0.02)
+        t, b2 = rnd(M, 64, sc=0.1), rnd(d, 64, sc=0.02)
+        res = rnd(m_seg, d)
+        out = torch.empty(m_seg, d, device=dev, dtype=bf)
+        full = torch.empty(M, d, device=dev, dtype=bf)
+        fl = 2.0 * M * d * K
+        ms_f = sustained(lambda: ctx.gemm_rs(x, w, a2=t, b2=b2, residual=res, out=out))
+        ms_l = sustained(lambda: gemm_tn(x, w, a2=t, b2=b2, out=full))
+        ms_u = sustained(lambda: unfused_gemm_rs(x, w).add_(res))
+        rows.append({"op": "gemm_rs", "gemm": name, "n": d, "k": K, "fused_ms": round(ms_f, 4),
+                     "fused_tflops": round(fl / ms_f / 1e9, 1), "local_gemm_ms": round(ms_l, 4), "nccl_cublas_ms": round(ms_u, 4),
+                     "nvlink_mb_out": round((P - 1) * m_seg * d * 2 / 1e6, 1)})
+        del x, w, t, b2, res, out, full
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    ctx.close()
+    res = {"op": "tp_layer", "model": cfg.name, "tokens": M, "tp": P, "fused_layer_ms": round(sum(r["fused_ms"] for r in rows), 3),
+           "local_gemm_layer_ms": round(sum(r["local_gemm_ms"] for r in rows), 3),
+           "nccl_cublas_layer_ms": round(sum(r["nccl_cublas_ms"] for r in rows), 3), "gemms": rows}
+    dist.barrier()
+    dist.destroy_process_group()
+    return res if rank == 0 else {}
 
 
 def bench_attn(a) -> dict:
@@ -284,14 +382,20 @@ def main() -> None:
     gl.add_argument("--seconds", type=float, default=0.5, help="length of each back-to-back timing run")
     gl.add_argument("--try-bn", type=int, nargs="*", default=[], help="also time CTA-pair tiles of these widths (224)")
     gl.add_argument("--ablate", action="store_true", help="also time each product without LoRA / without its epilogue")
-    for p in (g, t, m, sp, gl):
+    tl = sub.add_parser("tp-layer", help="run under torchrun: one rank per GPU of the tensor-parallel group")
+    tl.add_argument("--model", default="qwen2.5-7b")
+    tl.add_argument("--tokens", type=int, default=16384)
+    tl.add_argument("--seconds", type=float, default=0.4)
+    for p in (g, t, m, sp, gl, tl):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    print(json.dumps({"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler,
-                      "gemm-layer": bench_gemm_layer}[a.op](a)))
+    res = {"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler,
+           "gemm-layer": bench_gemm_layer, "tp-layer": bench_tp_layer}[a.op](a)
+    if res:
+        print(json.dumps(res))
 
 
 if __name__ == "__main__":

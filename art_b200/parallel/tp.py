@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
-from ..ops.gemm import EPI_BF16, EPI_F32, EPI_SWIGLU
+from ..ops.gemm import EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD
 from .symm_mem import SymmetricBuffer
 
 _configured = False
@@ -112,11 +112,13 @@ class TPContext:
 
     def ag_gemm(self, K: int, b: torch.Tensor, b2: torch.Tensor | None = None, out: torch.Tensor | None = None,
                 swiglu_out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
-                out_dtype: torch.dtype = torch.bfloat16, max_ctas: int = 0):
+                out_dtype: torch.dtype = torch.bfloat16, max_ctas: int = 0,
+                swiglu_bwd_gu: torch.Tensor | None = None):
         """``out[M, N] = gather(X) @ b.T (+ gather(T) @ b2.T)``; returns ``(out, x_full, t_full)``.
 
         ``x_full`` / ``t_full`` are views of the gathered operands; they stay valid until the
-        second-next call of this method.
+        second-next call of this method.  ``swiglu_bwd_gu`` ([M, 2N], the forward's interleaved gate|up
+        pre-activations): the product is d(silu(gate) * up) and ``out`` ([M, 2N]) receives d(gate|up).
         """
         self.ag_epoch += 1
         par = self.ag_epoch & 1
@@ -125,6 +127,12 @@ class TPContext:
         if b.shape[1] != K or b.stride(1) != 1:
             raise ValueError("weight shard must be [N, K] with unit inner stride")
         epi = EPI_SWIGLU if swiglu_out is not None else (EPI_F32 if out_dtype == torch.float32 else EPI_BF16)
+        if swiglu_bwd_gu is not None:
+            if tuple(swiglu_bwd_gu.shape) != (M, 2 * N) or N % 32 or swiglu_bwd_gu.stride(1) != 1:
+                raise ValueError("swiglu_bwd_gu must be [M, 2N] with N a multiple of 32")
+            epi, swiglu_out = EPI_SWIGLU_BWD, swiglu_bwd_gu      # travels in the H slot of the C entry point
+            if out is None:
+                out = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=self.device)
         if out is None:
             out = torch.empty((M, N), dtype=torch.float32 if epi == EPI_F32 else torch.bfloat16, device=self.device)
         kt = self.kt if b2 is not None else 0

@@ -108,6 +108,29 @@ g = gu.float().view(M, N // 32, 2, 16)
 href = (torch.nn.functional.silu(g[:, :, 0]) * g[:, :, 1]).reshape(M, N // 2)
 torch.cuda.synchronize(); _lib.check_status(dev)
 assert rel(h, href) < 1e-2
+# SwiGLU-backward epilogue through the gathered path: the product is d(activation), the output d(gate|up)
+from art_b200.ops import elementwise as ew
+N = 256
+dy_shard = rnd((m_seg, K), 700 + rank); wT = rnd((N, K), 800 + rank, 0.05)
+guf = rnd((M, 2 * N), 900 + rank)
+ctx.ag_input(K).copy_(dy_shard)
+dgu, dy_full, _ = ctx.ag_gemm(K, wT, swiglu_bwd_gu=guf)
+dh_ref = (dy_full.float() @ wT.float().t()).to(torch.bfloat16)
+torch.cuda.synchronize(); _lib.check_status(dev)
+assert rel(dgu, ew.swiglu_bwd(dh_ref, guf)) < 1e-2
+# token segments that are not a multiple of 256 rows take the one-CTA tiles
+ctx1 = TPContext(dev, None, 128, k_max=512, n_max=1024, kt=kt)
+for it in range(3):
+    x_shard = rnd((128, K), 50 + 10 * it + rank); w = rnd((512, K), 60 + it + 31 * rank, 0.05)
+    ctx1.ag_input(K).copy_(x_shard)
+    out, x_full, _ = ctx1.ag_gemm(K, w)
+    assert rel(out, x_full.float() @ w.float().t()) < 1e-2
+    a = rnd((world * 128, 192), 70 + 10 * it + rank); w = rnd((264, 192), 80 + 10 * it + rank, 0.05)
+    out = ctx1.gemm_rs(a, w)
+    part = a.float() @ w.float().t(); dist.all_reduce(part)
+    torch.cuda.synchronize(); _lib.check_status(dev)
+    assert rel(out, part[rank * 128:(rank + 1) * 128]) < 1e-2
+ctx1.close()
 
 for it, N in enumerate((512, 264, 1024, 96, 512, 512)):
     Kp = 192                                                       # this rank's slice of the reduction dim
