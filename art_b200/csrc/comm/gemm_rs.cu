@@ -129,6 +129,8 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   epi.spin = static_cast<uint32_t>(wait_ms <= 0 ? 2000000 : static_cast<long>(wait_ms) * 1000);
   epi.status = status;
   epi.own = 0;
+  epi.pre_ok = 0;
+  epi.done_seen = 0;
   epi.lrow = 0;
   epi.stage = nullptr;
   epi.flag = nullptr;
@@ -140,7 +142,10 @@ ARTB_EXPORT int artb_tp_gemm_rs(void* h, long off_stage, long off_flag, long off
   SchedSegRot sched{m_seg / GEMM_BM, n_tiles, world, s->rank, 1, pick_group_m(m_seg / GEMM_BM, GEMM_BM, K)};
   const int kb_main = (K + GEMM_BK - 1) / GEMM_BK, kb_extra = (K2 + GEMM_BK - 1) / GEMM_BK;
   if (pair) {
-    SchedSegRot sched2{m_seg / (2 * GEMM_BM), n_tiles, world, s->rank, 1, pick_group_m(m_seg / (2 * GEMM_BM), 2 * GEMM_BM, K)};
+    int cl = sm_count() / 2;
+    if (max_ctas > 0 && max_ctas / 2 < cl) cl = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+    SchedSegRot sched2{m_seg / (2 * GEMM_BM), n_tiles, world, s->rank, 1, pick_group_m(m_seg / (2 * GEMM_BM), 2 * GEMM_BM, K),
+                       2 * cl};      // own tiles two grid waves behind the peers' tiles
     return launch_rs_pair(tA, tB, tA2, tB2, kb_main, kb_extra, sched2, epi, comm, status, max_ctas, stream);
   }
   return launch_rs<256, 4>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, comm, status, max_ctas, stream);

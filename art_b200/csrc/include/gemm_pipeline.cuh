@@ -88,6 +88,15 @@ struct NoComm {
   __device__ void finish(int* /*status*/) const {}
 };
 
+// Optional epilogue hook `flush(row)`: called by every epilogue thread after its last tile (policies that defer work,
+// e.g. the publication of arrival flags, finish it there).
+template <class E>
+__device__ __forceinline__ auto epi_flush(E& e, int row, int) -> decltype(e.flush(row), void()) {
+  e.flush(row);
+}
+template <class E>
+__device__ __forceinline__ void epi_flush(E&, int, long) {}
+
 template <int BN, int STAGES, class Sched, class Epi, class Comm = NoComm>
 __global__ void __launch_bounds__(GEMM_THREADS + Comm::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -253,6 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       epi.tile_end(ti, row);
     }
+    epi_flush(epi, row, 0);
   }
 
   // ---------------------------------------------------------------- teardown

@@ -234,6 +234,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[buf]), 0));
       epi.tile_end(ti, row);
     }
+    epi_flush(epi, row, 0);
   }
 
   // ---------------------------------------------------------------- teardown

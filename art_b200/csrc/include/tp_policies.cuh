@@ -25,6 +25,12 @@ constexpr int TP_PUSH_ROWS = 32;   // rows per push unit / arrival flag
 // first_off = 1: own segment last  (reduce-scatter: peers' partials arrive while we compute theirs).
 struct SchedSegRot {
   int seg_m_tiles, n_tiles, world, rank, first_off, group_m;
+  // Reduce-scatter only (first_off = 1): instead of all peers' tiles first and the own segment last, the own tiles are
+  // woven in `lag` tile positions behind the peers' tiles of the same position, so that the partial sums cross
+  // NVLink during the whole kernel rather than during its first (world-1)/world, which for short reductions is more
+  // than the link carries in that time.  The peers run the mirror-image order, so the partial an own tile adds was
+  // pushed lag * world tiles (a few grid waves) earlier.  0 or >= tiles per segment: peers first, own last.
+  int lag = 0;
   __device__ int tiles_for_cta(int cta, int ncta) const {
     const int total = seg_m_tiles * n_tiles * world;
     return cta < total ? (total - cta + ncta - 1) / ncta : 0;
@@ -32,10 +38,36 @@ struct SchedSegRot {
   __device__ TileInfo get(int cta, int ncta, int i) const {
     const int t = cta + i * ncta;
     const int per_seg = seg_m_tiles * n_tiles;
-    const int si = t / per_seg, rem = t - si * per_seg;
-    const int seg = (rank + first_off + si) % world;
+    int seg, pos;
+    if (lag <= 0 || lag >= per_seg || first_off != 1 || world < 2) {
+      const int si = t / per_seg;
+      pos = t - si * per_seg;
+      seg = (rank + first_off + si) % world;
+    } else {
+      const int others = world - 1;
+      const int a_end = lag * others;                  // positions [0, lag): peers' tiles only
+      if (t < a_end) {
+        pos = t / others;
+        seg = (rank + 1 + t % others) % world;
+      } else {
+        const int u = t - a_end, b_len = (per_seg - lag) * world;
+        if (u < b_len) {                               // positions [lag, per_seg): peers' tiles + the own tile `lag` behind
+          const int k = u % world;
+          pos = lag + u / world;
+          if (k < others) {
+            seg = (rank + 1 + k) % world;
+          } else {
+            seg = rank;
+            pos -= lag;
+          }
+        } else {                                       // the last `lag` own tiles
+          seg = rank;
+          pos = per_seg - lag + (u - b_len);
+        }
+      }
+    }
     int m, n;
-    raster_tile(rem, seg_m_tiles, n_tiles, group_m, m, n);
+    raster_tile(pos, seg_m_tiles, n_tiles, group_m, m, n);
     TileInfo ti = make_tile(seg * seg_m_tiles + m, n);
     ti.group = seg;
     return ti;
@@ -179,6 +211,28 @@ struct EpiReduceScatter {
   __nv_bfloat16* stage;   // first row of this warp's 32-row band: in the owner's staging slot (remote tile)
                           // or in slot 0 of the local staging (own tile)
   uint32_t* flag;         // remote: flag to publish; own: flag of slot 0 to wait on
+  // Own tiles: the staged partial of slot 0 and the residual of the NEXT 32-column chunk, loaded while the current
+  // chunk is summed and stored.  A thread reads its own row, so issued at the point of use these loads cost one DRAM
+  // round trip per chunk, which for short reductions (K of a few thousand) is longer than the tile's main loop.
+  uint4 pre[8];
+  int pre_ok = 0;
+  uint32_t done_seen = 0;   // bit seg: the owner's "done" word was already checked in this launch
+
+  __device__ __forceinline__ void issue(const TileInfo& ti, int row, int c) {
+    const int gc = ti.n_blk * BN + c;
+    pre_ok = 0;
+    if (!own || gc + 32 > N) return;
+    const int lane = row & 31;
+    const uint4* p = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(lane) * N + gc);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pre[j] = __ldcg(p + j);
+    if (R) {
+      const uint4* r = reinterpret_cast<const uint4*>(R + static_cast<size_t>(lrow) * ldr + gc);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pre[4 + j] = r[j];
+    }
+    pre_ok = 1;
+  }
 
   __device__ void tile_begin(const TileInfo& ti, int row) {
     const int seg = ti.group;
@@ -194,9 +248,13 @@ struct EpiReduceScatter {
               (static_cast<size_t>(slot) * m_seg + lrow0 + q * 32) * N;
       flag = reinterpret_cast<uint32_t*>(tp_base(pt, seg) + off_flag) +
              (static_cast<size_t>(slot) * tile_cap + tile_local) * 4 + q;
-      // the owner must have consumed the call that last used this parity of its staging buffer
-      if (lane == 0 && epoch > 2)
-        ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(tp_base(pt, rank) + off_done) + seg, epoch - 2, spin);
+      // the owner must have consumed the call that last used this parity of its staging buffer (checked once per
+      // launch and owner: the word only grows)
+      if (epoch > 2 && !((done_seen >> seg) & 1u)) {
+        if (lane == 0)
+          ok = wait_flag_ge(reinterpret_cast<const uint32_t*>(tp_base(pt, rank) + off_done) + seg, epoch - 2, spin);
+        done_seen |= 1u << seg;
+      }
     } else {
       stage = reinterpret_cast<__nv_bfloat16*>(tp_base(pt, rank) + off_stage) +
               static_cast<size_t>(lrow0 + q * 32) * N;
@@ -207,11 +265,17 @@ struct EpiReduceScatter {
     }
     if (lane == 0 && !ok) atomicMax(status, ST_TIMEOUT_PEER);
     __syncwarp();
+    issue(ti, row, 0);       // after the flags: the staged partials are complete
   }
 
   __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
     const int gc = ti.n_blk * BN + c;
     const int q = (row >> 5) & 3, lane = row & 31;
+    uint4 cur[8];
+    const int cur_ok = pre_ok;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cur[j] = pre[j];
+    if (own && c + 32 < BN) issue(ti, row, c + 32);
     if (!own) {
       // Remote tile: the partial goes to the owner as bf16.  A thread holds one row, so a direct
       // store would scatter 16-byte pieces over 32 rows; instead two 32-column slabs are parked in
@@ -255,7 +319,7 @@ struct EpiReduceScatter {
 #pragma unroll
       for (int j = 0; j < 32; j += 8)
         if (gc + j < N) {
-          const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p + j));
+          const uint4 rv = (s == 0 && cur_ok) ? cur[j >> 3] : __ldcg(reinterpret_cast<const uint4*>(p + j));
           const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -270,7 +334,7 @@ struct EpiReduceScatter {
 #pragma unroll
       for (int j = 0; j < 32; j += 8)
         if (gc + j < N) {
-          uint4 rv = *reinterpret_cast<const uint4*>(r + j);
+          uint4 rv = cur_ok ? cur[4 + (j >> 3)] : *reinterpret_cast<const uint4*>(r + j);
           const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -295,6 +359,8 @@ struct EpiReduceScatter {
 
   __device__ void tile_end(const TileInfo&, int row) {
     if (own) return;
+    // a tile's flag is published at once (a system-scope fence, one NVLink round trip): holding it back to share the
+    // fence between several tiles was measured and is slower, because the owner then waits for it
     __threadfence_system();
     __syncwarp();
     if ((row & 31) == 0) st_release_sys_u32(flag, epoch);
