@@ -83,9 +83,15 @@ class ModelState:
         targs = config.get("trainer_args", {})
         self.rank, self.world, self.tp_size = rank, world, tp
         self.data_index, self.data_ranks = 0, 1
+        if world > 1 and rank > 0 and not torch.cuda.is_initialized():
+            # a worker rank lives in a process of its own: list its GPU first, so that it is device 0 for every thread of
+            # the process (event loop, executor threads, the engine thread) without each of them having to select it;
+            # the other GPUs stay visible, as peer mappings of their memory need them to be
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            ids = [v for v in vis.split(",") if v] if vis else [str(i) for i in range(max(world, rank + 1))]
+            if len(ids) > rank:
+                os.environ["CUDA_VISIBLE_DEVICES"] = ",".join([ids[rank]] + ids[:rank] + ids[rank + 1:])
         has_gpu = torch.cuda.is_available()
-        if has_gpu:
-            torch.cuda.set_device(rank % torch.cuda.device_count())
         self.device = torch.device("cuda", torch.cuda.current_device()) if has_gpu else torch.device("cpu")
         tp_group = dp_group = None
         self._owns_pg = False
@@ -99,7 +105,8 @@ class ModelState:
             if not dist.is_initialized():
                 kw = {"device_id": self.device} if has_gpu else {}
                 dist.init_process_group("nccl" if has_gpu else "gloo", init_method=f"tcp://127.0.0.1:{master_port}",
-                                        rank=rank, world_size=world, timeout=datetime.timedelta(seconds=600), **kw)
+                                        rank=rank, world_size=world,
+                                        timeout=datetime.timedelta(seconds=float(os.environ.get("ART_B200_DIST_TIMEOUT_S", 600))), **kw)
                 self._owns_pg = True
             layout = ParallelLayout(world, tp=tp)
             groups = layout.create_groups(rank)

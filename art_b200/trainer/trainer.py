@@ -85,7 +85,9 @@ class Trainer:
                 from ..parallel.tp import TPContext
 
                 P = dist.get_world_size(tp_group)
-                self.tp = TPContext(self.device, tp_group, tp_tokens // P, k_max=cfg.hidden_size, n_max=cfg.hidden_size)
+                # generous peer wait: a rank can be held up for seconds by first-touch allocations of a large micro-batch
+                self.tp = TPContext(self.device, tp_group, tp_tokens // P, k_max=cfg.hidden_size, n_max=cfg.hidden_size,
+                                    wait_ms=20000)
                 self.model = TPDecoder(cfg, base, lora_cfg, lora_init, self.tp, self.device)
             else:
                 layer_range = None

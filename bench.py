@@ -228,8 +228,9 @@ def main():
             groups = layout.create_groups(rank)                 # every rank creates every group, in the same order
             tp_group, dp_group = groups["tp"], groups["dp"]
             data_index, data_ranks = layout.data_shard(rank)
-            # a tensor-parallel group shares its rows: it takes the rows (and micro-batch tokens) of all its GPUs
-            R, micro = R * T, micro * T
+            # a tensor-parallel group shares its rows: it takes the rows of all its GPUs (the micro-batch stays: its
+            # tokens are split over the group, and the all-token activations of the local heads / columns grow with it)
+            R = R * T
             label = f"tp{T}xdp{data_ranks}"
             sync_name = f"fused-p2p-allreduce(sum over tp{T})"
             if data_ranks > 1:

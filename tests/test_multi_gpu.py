@@ -802,3 +802,73 @@ def test_peer_timeout_is_reported_and_recoverable(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     print(res.stdout[-3000:], res.stderr[-3000:])
     assert res.returncode == 0 and "FAILURE_DETECT_OK" in res.stdout
+
+
+NODE_WORKER = r'''
+import asyncio, os, sys, json
+sys.path.insert(0, os.environ["ARTB_ROOT"])
+import httpx, torch
+import art_b200 as art
+from art_b200 import dev
+from art_b200.local.node import NodeService, build_node_service
+from art_b200.local.pack import packed_tensors_to_dir
+sys.path.insert(0, os.path.join(os.environ["ARTB_ROOT"], "tests"))
+from test_node_service_cpu import _packed
+
+ARCH = dict(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+            intermediate_size=512)
+out_root, tp, dp = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+
+
+async def main():
+    out = f"{out_root}/tp{tp}dp{dp}"
+    packed = _packed(4, 1024)
+    packed["tokens"] = packed["tokens"] % ARCH["vocab_size"]
+    disk = packed_tensors_to_dir(packed, f"{out}/tensors")
+    cfg = dev.get_model_config("random:small", out, {
+        "init_args": {"architecture": ARCH, "max_seq_length": 2048},
+        "engine_args": {"num_scheduler_steps": 4, "max_model_len": 512, "tensor_parallel_size": tp, "data_parallel_size": dp,
+                        "num_gpu_blocks_override": 512},
+        "trainer_args": {"tokens_per_microbatch": 2048}})
+    port = 18800 + (os.getpid() % 40) * 8
+    svc = build_node_service(model_name="m", base_model="random:small", config=cfg, output_dir=out, port=port, in_process=True)
+    assert isinstance(svc, NodeService) and len(svc.ranks) == tp * dp
+    try:
+        await svc.start_openai_server(None)
+        async with httpx.AsyncClient(headers={"Authorization": "Bearer default"}, timeout=120) as c:
+            async def ask(seed):
+                r = await c.post(f"http://127.0.0.1:{port}/v1/chat/completions",
+                                 json={"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6,
+                                       "seed": seed, "temperature": 1.0})
+                assert r.status_code == 200, r.text
+                return [e["logprob"] for e in r.json()["choices"][0]["logprobs"]["content"]]
+            before = await asyncio.gather(*[ask(s) for s in range(8)])
+            served = [(await c.get(f"http://127.0.0.1:{port + r}/metrics")).json()["generated_tokens"] for r in range(tp * dp)]
+            assert all(n >= 12 for n in served), served          # every replica took part
+            steps = [m async for m in svc.train(disk, art.TrainConfig(learning_rate=1e-2), {"rows_per_optimizer_step": 2})]
+            assert len(steps) == (1 if dp == 2 else 2) and all(s["grad_norm"] > 0 for s in steps), steps
+            after = await asyncio.gather(*[ask(s) for s in range(8)])
+            assert all(a != b for a, b in zip(after, before))    # every replica serves the new adapter
+        assert os.path.exists(f"{out}/0001/adapter_model.safetensors")
+        print(f"NODE_OK tp={tp} dp={dp} steps={len(steps)} loss={steps[0]['loss']:.5f} served={served}", flush=True)
+    finally:
+        await svc.shutdown()
+
+if __name__ == "__main__":       # the rank-1 service is a spawned child that imports this file again
+    asyncio.run(main())
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("tp,dp", [(1, 2), (2, 1)])
+def test_node_service_over_two_gpus(tmp_path, tp, dp):
+    """The model service over two GPUs through its public entry point: one engine replica per GPU behind one port,
+    a training call that runs data parallel (tp=1, dp=2) or tensor parallel (tp=2) across the ranks, the adapter handed
+    to every replica on its own device."""
+    script = tmp_path / "node_worker.py"
+    script.write_text(NODE_WORKER)
+    env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0", ART_B200_DIST_TIMEOUT_S="60")
+    res = subprocess.run([sys.executable, str(script), str(tmp_path), str(tp), str(dp)], env=env, capture_output=True,
+                         text=True, timeout=180)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0 and "NODE_OK" in res.stdout
