@@ -55,12 +55,14 @@ def _stats(xs: list[float]) -> dict:
 
 
 async def run(base_model: str, architecture: dict | None = None, concurrency: int = 800, iterations: int = 1,
-              prompt_repeats: int = 500, max_tokens: int = 1000, temperature: float = 1.0, stream: bool = False,
+              prompt_repeats: int | None = None, prompt_tokens: int = 1000, max_tokens: int = 1000, temperature: float = 1.0, stream: bool = False,
               path: str | None = None, engine_args: dict | None = None, in_process: bool = True) -> dict:
     import art_b200 as art
     from art_b200.local import LocalBackend
 
-    prompt = ("Hello world. " * prompt_repeats).strip() + "Please repeat the entire prompt back to me verbatim"
+    def make_prompt(reps: int) -> str:
+        return ("Hello world. " * reps).strip() + "Please repeat the entire prompt back to me verbatim"
+
     init_args: dict = {}
     if architecture is not None:
         init_args["architecture"] = architecture
@@ -72,6 +74,18 @@ async def run(base_model: str, architecture: dict | None = None, concurrency: in
         await model.register(backend)
         client = model.openai_client()
         name = model.get_inference_name()
+        if prompt_repeats is None:
+            # the reference's prompt is about 1000 tokens under its tokenizer; size ours to ``prompt_tokens`` under the
+            # tokenizer that is actually serving (the offline byte-level tokenizer needs far fewer repetitions)
+            import httpx
+
+            async with httpx.AsyncClient(timeout=60) as hc:
+                url = str(client.base_url).rstrip("/").removesuffix("/v1") + "/tokenize"
+                n1 = (await hc.post(url, json={"messages": [{"role": "user", "content": make_prompt(1)}]})).json()["count"]
+                n9 = (await hc.post(url, json={"messages": [{"role": "user", "content": make_prompt(9)}]})).json()["count"]
+            per = max(1e-6, (n9 - n1) / 8)
+            prompt_repeats = max(1, round((prompt_tokens - (n1 - per)) / per))
+        prompt = make_prompt(prompt_repeats)
         await timed_request(client, name, "warm up", 4, temperature, stream)
         for i in range(iterations):
             t0 = time.perf_counter()
@@ -88,6 +102,7 @@ async def run(base_model: str, architecture: dict | None = None, concurrency: in
     comp = sum(r["completion_tokens"] or 0 for r in results)
     prom = sum(r["prompt_tokens"] or 0 for r in results)
     out = {"op": "serving_load", "model": base_model, "concurrency": concurrency, "iterations": iterations,
+           "prompt_repeats": prompt_repeats,
            "total_s": round(total, 3), "iteration_s": _stats(durations), "request_s": _stats([r["elapsed"] for r in results]),
            "requests_per_s": round(len(results) / total, 2), "avg_prompt_tokens": round(prom / max(1, len(results)), 1),
            "avg_completion_tokens": round(comp / max(1, len(results)), 1),
@@ -103,7 +118,9 @@ def main() -> None:
     ap.add_argument("--model", default="qwen2.5-7b", help="architecture preset (random weights) or a local checkpoint directory")
     ap.add_argument("--concurrency", type=int, default=800)
     ap.add_argument("--iterations", type=int, default=1)
-    ap.add_argument("--prompt-repeats", type=int, default=500, help='"Hello world. " repeated this often (500 is about 1000 tokens)')
+    ap.add_argument("--prompt-repeats", type=int, default=None,
+                    help='"Hello world. " repeated this often (default: as often as gives --prompt-tokens tokens)')
+    ap.add_argument("--prompt-tokens", type=int, default=1000)
     ap.add_argument("--max-tokens", type=int, default=1000)
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--stream", action="store_true", help="stream the answers and report the time to the first token")
@@ -113,7 +130,8 @@ def main() -> None:
     import os
 
     base = a.model if os.path.isdir(a.model) else f"random:{a.model}"
-    res = asyncio.run(run(base, None, a.concurrency, a.iterations, a.prompt_repeats, a.max_tokens, a.temperature, a.stream,
+    res = asyncio.run(run(base, None, a.concurrency, a.iterations, a.prompt_repeats, a.prompt_tokens, a.max_tokens,
+                          a.temperature, a.stream,
                           engine_args={"max_num_seqs": a.max_num_seqs, "max_model_len": a.max_model_len}))
     print(json.dumps(res))
 

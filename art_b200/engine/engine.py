@@ -326,6 +326,9 @@ class Engine:
         and free blocks."""
         picked: list[tuple[Sequence, int]] = []
         budget = self.max_batched
+        # tokens attended in the step (cached prefix + new): the prefill gathers the cached K/V of every picked sequence
+        # into one dense buffer, so many prefix-cache hits with long prefixes must not all land in the same step
+        att_budget = 2 * self.max_batched
         bs = self.bm.block_size
 
         def chunk(n_new: int) -> int:
@@ -338,10 +341,11 @@ class Engine:
 
         for seq in self.prefilling:
             take = chunk(len(seq.tokens) - seq.num_cached)
-            if take <= 0:
+            if take <= 0 or (picked and seq.num_cached + take > att_budget):
                 break
             picked.append((seq, seq.num_cached + take))
             budget -= take
+            att_budget -= seq.num_cached + take
         with self._lock:
             while self.waiting and budget > 0 and len(self.running) + len(self.prefilling) + \
                     sum(1 for s, _ in picked if s not in self.prefilling) < self.max_num_seqs:
@@ -356,7 +360,7 @@ class Engine:
                 cached = self.bm.match_prefix(toks[:-1], salt)   # always recompute the last token
                 n_new = len(toks) - len(cached) * bs
                 take = chunk(n_new)
-                if take <= 0:
+                if take <= 0 or (picked and len(cached) * bs + take > att_budget):
                     self.bm.free(cached)
                     break
                 need = self._blocks_needed(len(toks) + 1) - len(cached)
@@ -370,6 +374,7 @@ class Engine:
                 seq.salt = salt
                 picked.append((seq, seq.num_cached + take))
                 budget -= take
+                att_budget -= seq.num_cached + take
         return picked
 
     def _ensure_decode_blocks(self, steps: int) -> int:
@@ -490,6 +495,11 @@ class Engine:
 
     def _loop(self) -> None:
         try:
+            dev = getattr(self.runner, "device", None)
+            if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+                import torch
+
+                torch.cuda.set_device(dev)      # the current device is per thread and starts at 0
             while not self._stop:
                 self._run_gate.wait()
                 with self._step_lock:

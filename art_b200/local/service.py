@@ -228,14 +228,31 @@ class ModelService:
     tp_size: int = 1
     master_port: int = 0
     _state: ModelState | None = field(default=None, repr=False, compare=False)
+    _pool: object = field(default=None, repr=False, compare=False)
     _server_task: asyncio.Task | None = field(default=None, repr=False, compare=False)
     _ckpt_thread: threading.Thread | None = field(default=None, repr=False, compare=False)
     _ckpt_error: BaseException | None = field(default=None, repr=False, compare=False)
 
     def __getstate__(self):   # only the configuration crosses the process boundary
         d = dict(self.__dict__)
-        d["_state"] = d["_server_task"] = d["_ckpt_thread"] = d["_ckpt_error"] = None
+        d["_state"] = d["_server_task"] = d["_ckpt_thread"] = d["_ckpt_error"] = d["_pool"] = None
         return d
+
+    @property
+    def pool(self):
+        """Worker threads for blocking device work.  CUDA's current device is per thread and starts at device 0, so
+        every thread of this pool selects the model's device when it starts (what matters for a rank other than 0
+        living in a process that sees several GPUs)."""
+        if self._pool is None:
+            from concurrent.futures import ThreadPoolExecutor
+
+            def bind():
+                st = self._state
+                if st is not None and st.device.type == "cuda":
+                    torch.cuda.set_device(st.device)
+
+            self._pool = ThreadPoolExecutor(max_workers=4, thread_name_prefix="art-b200-service", initializer=bind)
+        return self._pool
 
     @property
     def state(self) -> ModelState:
@@ -321,11 +338,11 @@ class ModelService:
                            recompute=str(_config.get("activation_recompute")
                                          or self.config.get("init_args", {}).get("activation_recompute", "auto")))
         loop = asyncio.get_running_loop()
-        await loop.run_in_executor(None, st.engine.pause)
+        await loop.run_in_executor(self.pool, st.engine.pause)
         slept = False
         try:
             if st.sleep_mode:
-                await loop.run_in_executor(None, st.engine.sleep, 1 if st.engine.has_unfinished else 2)
+                await loop.run_in_executor(self.pool, st.engine.sleep, 1 if st.engine.has_unfinished else 2)
                 slept = True
             n_rows = packed["tokens"].shape[0]
             per = max(1, hyper.rows_per_optimizer_step)
@@ -343,7 +360,7 @@ class ModelService:
                 rows = shard_rows(packed, PACKED_KEYS, start + j * per, per, n_rows)
                 if st.device.type == "cuda":
                     rows = {k: v.pin_memory() for k, v in rows.items()}
-                metrics = await loop.run_in_executor(None, st.trainer.step, rows, hyper)
+                metrics = await loop.run_in_executor(self.pool, st.trainer.step, rows, hyper)
                 tokens_done += rows["tokens"].numel()
                 metrics["tokens_per_second"] = tokens_done / max(1e-9, time.monotonic() - t0)
                 if verbose:
@@ -351,7 +368,7 @@ class ModelService:
                 yield metrics
             if self.rank != 0:      # only the leader writes checkpoints; every rank holds the same adapter
                 if slept:
-                    await loop.run_in_executor(None, st.engine.wake_up)
+                    await loop.run_in_executor(self.pool, st.engine.wake_up)
                     slept = False
                 self._set_lora_in_device()
                 return
@@ -361,19 +378,39 @@ class ModelService:
             # as in the reference (src/art/local/service.py:150-157: save_model before the generator ends)
             step = get_step_from_dir(self.output_dir) + 1
             ckpt_dir = get_step_checkpoint_dir(self.output_dir, step)
-            host_state = {k: v.detach().to("cpu", copy=True) for k, v in st.trainer.flat.views.items()}
-            tstate = st.trainer.trainer_state()
             self._join_checkpoint()
+            host_state, tstate = self._host_copies()
             self._start_checkpoint(ckpt_dir, host_state, tstate)
             if slept:
-                await loop.run_in_executor(None, st.engine.wake_up)
+                await loop.run_in_executor(self.pool, st.engine.wake_up)
                 slept = False
             self._set_lora_in_device()
-            await loop.run_in_executor(None, self._join_checkpoint)
+            # the adapter of the new step must be on disk before train() returns; the optimizer state (twice its size)
+            # may still be in flight: it is joined by the next train / flush / close
+            await loop.run_in_executor(self.pool, self._join_adapter)
         finally:
             if slept:
-                await loop.run_in_executor(None, st.engine.wake_up)
+                await loop.run_in_executor(self.pool, st.engine.wake_up)
             st.engine.resume()
+
+    def _host_copies(self) -> tuple[dict, dict]:
+        """Host copies of the adapter and of the optimizer state for the checkpoint writer.  The LoRA masters and the
+        AdamW moments are three flat fp32 buffers, so this is three device-to-host copies into pinned buffers that are
+        kept between steps (the per-tensor dictionary is views of the first)."""
+        st = self.state
+        flat = st.trainer.flat
+        if st.device.type != "cuda":
+            return ({k: v.detach().to("cpu", copy=True) for k, v in flat.views.items()}, st.trainer.trainer_state())
+        if getattr(self, "_pinned", None) is None or self._pinned[0].numel() != flat.params.numel():
+            self._pinned = [torch.empty(flat.params.numel(), dtype=torch.float32).pin_memory() for _ in range(3)]
+        hp, hm, hv = self._pinned
+        hp.copy_(flat.params.detach(), non_blocking=True)
+        hm.copy_(st.trainer.opt.m, non_blocking=True)
+        hv.copy_(st.trainer.opt.v, non_blocking=True)
+        torch.cuda.current_stream(st.device).synchronize()
+        host_state = {k: hp[flat.offsets[k]:flat.offsets[k] + v.numel()].view(v.shape) for k, v in flat.views.items()}
+        tstate = {"optimizer": {"m": hm, "v": hv, "step": st.trainer.opt.step_count}, "global_step": st.trainer.global_step}
+        return host_state, tstate
 
     def _start_checkpoint(self, ckpt_dir: str, host_state: dict, tstate: dict) -> None:
         import shutil
@@ -381,18 +418,32 @@ class ModelService:
         st = self.state
         tmp = ckpt_dir + ".tmp"
         self._ckpt_error = None
+        self._adapter_done = threading.Event()
 
         def write():
             try:
                 shutil.rmtree(tmp, ignore_errors=True)
                 save_adapter(tmp, host_state, st.lora_cfg, self.base_model)
-                torch.save(tstate, os.path.join(tmp, TRAINER_STATE))
-                os.replace(tmp, ckpt_dir)
-            except BaseException as e:  # noqa: BLE001 - handed to the caller of _join_checkpoint
+                os.replace(tmp, ckpt_dir)          # a numeric directory always holds a complete adapter
+                self._adapter_done.set()
+                part = os.path.join(ckpt_dir, TRAINER_STATE + ".tmp")
+                torch.save(tstate, part)
+                os.replace(part, os.path.join(ckpt_dir, TRAINER_STATE))
+            except BaseException as e:  # noqa: BLE001 - handed to the caller of _join_checkpoint / _join_adapter
                 self._ckpt_error = e
+            finally:
+                self._adapter_done.set()
 
         self._ckpt_thread = threading.Thread(target=write, daemon=True)
         self._ckpt_thread.start()
+
+    def _join_adapter(self) -> None:
+        """Wait until the adapter files of the step being written are in place (or the writer failed)."""
+        ev = getattr(self, "_adapter_done", None)
+        if ev is not None:
+            ev.wait()
+        if self._ckpt_error is not None:
+            self._join_checkpoint()
 
     def _join_checkpoint(self) -> None:
         """Wait for the checkpoint writer; an exception it hit (disk full, ...) is raised here, once."""
@@ -404,7 +455,7 @@ class ModelService:
             raise RuntimeError("writing the step checkpoint failed") from err
 
     async def flush_checkpoints(self) -> None:
-        await asyncio.get_running_loop().run_in_executor(None, self._join_checkpoint)
+        await asyncio.get_running_loop().run_in_executor(self.pool, self._join_checkpoint)
 
     async def shutdown(self) -> None:
         await self.stop_openai_server()

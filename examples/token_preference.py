@@ -38,10 +38,11 @@ async def rollout(model: art.TrainableModel, client, prompt: str, max_tokens: in
 
 async def run(steps: int = 6, groups: int = 8, group_size: int = 8, max_tokens: int = 16, learning_rate: float = 2e-2,
               path: str | None = None, base_model: str = "random:tiny", architecture: dict | None = TINY,
-              verbose: bool = True, in_process: bool = True) -> list[float]:
+              verbose: bool = True, in_process: bool = True, stop_above: float | None = None) -> list[float]:
     """Returns the mean reward of the rollouts gathered before each training step (plus a final evaluation).
 
-    Liked tokens are the ids below 1/16 of the vocabulary: rare enough to need learning, common enough to be found
+    ``stop_above``: stop early once the mean reward exceeds it (the step at which the reward takes off depends on
+    the sampling seeds).  Liked tokens are the ids below 1/16 of the vocabulary: rare enough to need learning, common enough to be found
     by sampling."""
     liked_below = (architecture or TINY)["vocab_size"] // 16
     backend = LocalBackend(in_process=in_process, path=path or tempfile.mkdtemp(prefix="art-token-pref-"))
@@ -66,7 +67,7 @@ async def run(steps: int = 6, groups: int = 8, group_size: int = 8, max_tokens: 
             history.append(sum(rewards) / len(rewards))
             if verbose:
                 print(f"step {step}: mean reward {history[-1]:.3f}", flush=True)
-            if step == steps:
+            if step == steps or (stop_above is not None and history[-1] > stop_above):
                 break
             await model.train(train_groups, config=art.TrainConfig(learning_rate=learning_rate))
         await client.close()

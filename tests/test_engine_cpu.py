@@ -225,3 +225,21 @@ def test_chunked_prefill_splits_long_prompts_and_matches_unchunked(tiny):
     d = eng4.add_request(long_prompt, p)
     eng4.step()
     assert len(d.output_ids) == 1 and not eng4.prefilling
+
+
+def test_prefix_cache_hits_are_budgeted_by_attended_tokens(tiny):
+    """Sequences whose prompts hit the prefix cache bring few NEW tokens but many attended ones; one prefill step takes
+    only as many of them as its attended-token budget (twice the batched-token budget) allows."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, max_num_batched_tokens=32, num_scheduler_steps=1, blocks=256)
+    p = SamplingParams(max_tokens=2, temperature=0.0)
+    prompt = [(3 * i) % 500 + 1 for i in range(41)]           # ten whole blocks of 4 + one token
+    first = eng.generate_sync(prompt, p)
+    eng.step()                                                # release -> the prompt's blocks enter the cache
+    seqs = [eng.add_request(prompt, p) for _ in range(6)]     # each: 40 cached tokens, 1 new
+    eng.step()
+    started = [s for s in seqs if s.output_ids]
+    assert 1 <= len(started) <= 2                             # 2 x 41 attended tokens > 64 stops the third
+    while not all(s.finished for s in seqs):
+        eng.step()
+    assert all(s.output_ids == first.output_ids for s in seqs)

@@ -10,11 +10,11 @@ from examples.token_preference import run
 
 
 def test_grpo_steps_raise_the_reward_cpu(tmp_path):
-    hist = asyncio.run(run(steps=6, path=str(tmp_path), verbose=False))
-    assert len(hist) == 7
+    # the reward takes off after 4 to 8 steps depending on the sampling seeds (0.08 -> 0.9 within two steps once it does)
+    hist = asyncio.run(run(steps=14, path=str(tmp_path), verbose=False, stop_above=0.5))
     assert hist[0] < 0.2                                   # the untrained policy likes 1/16 of the vocabulary
-    assert hist[-1] > hist[0] + 0.3, hist                  # 0.08 -> ~0.9 in a typical run
-    assert max(hist[-2:]) == max(hist)                     # still improving (or saturated) at the end
+    assert hist[-1] > 0.5, hist
+    assert hist[-1] == max(hist)
 
 
 @pytest.mark.gpu
@@ -23,6 +23,6 @@ def test_grpo_steps_raise_the_reward_native_path(tmp_path):
     device-to-device adapter hand-off -> resume."""
     arch = dict(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
                 intermediate_size=512)
-    hist = asyncio.run(run(steps=8, path=str(tmp_path), architecture=arch, verbose=False))
+    hist = asyncio.run(run(steps=16, path=str(tmp_path), architecture=arch, verbose=False, stop_above=0.5))
     assert hist[0] < 0.2
-    assert hist[-1] > hist[0] + 0.3, hist
+    assert hist[-1] > 0.5, hist

@@ -175,11 +175,13 @@ def test_http_load_benchmark_runs_against_the_server(tmp_path):
     arch = dict(name="tiny", vocab_size=1024, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32,
                 intermediate_size=384)
     for stream in (False, True):
-        res = asyncio.run(run("random:tiny", arch, concurrency=6, iterations=2, prompt_repeats=3, max_tokens=5,
-                              stream=stream, path=str(tmp_path / f"s{int(stream)}"),
+        res = asyncio.run(run("random:tiny", arch, concurrency=6, iterations=2, prompt_repeats=None if stream else 3,
+                              prompt_tokens=120, max_tokens=5, stream=stream, path=str(tmp_path / f"s{int(stream)}"),
                               engine_args={"max_model_len": 256, "num_scheduler_steps": 2}))
         assert res["concurrency"] == 6 and res["iterations"] == 2
         assert res["avg_completion_tokens"] == 5.0 and res["avg_prompt_tokens"] > 20
         assert res["requests_per_s"] > 0 and res["completion_tokens_per_s"] > 0
         assert res["request_s"]["max"] <= res["iteration_s"]["max"] + 1e-3
         assert ("ttft_s" in res) == stream
+        if stream:      # the prompt was sized to the requested token count under the serving tokenizer
+            assert abs(res["avg_prompt_tokens"] - 120) <= 14
