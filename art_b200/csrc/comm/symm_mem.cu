@@ -38,9 +38,9 @@ __device__ __forceinline__ bool epoch_barrier(const PeerTable& pt, int rank, int
     __threadfence_system();
     st_release_sys(pt.pad[q] + channel * MAX_RANKS + rank, epoch);
     const uint64_t* mine = pt.pad[rank] + channel * MAX_RANKS + q;
-    uint32_t it = 0;
+    WaitBudget w(spin_limit);      // microseconds
     while (ld_acquire_sys(mine) < epoch) {
-      if (++it > spin_limit) {
+      if (w.expired()) {
         ok = false;
         break;
       }

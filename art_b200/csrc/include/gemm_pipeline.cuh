@@ -165,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+          if (!mbar_wait_abortable(&empty_bar[s], ph ^ 1, abort_flag)) {
             atomicMax(status, ST_TIMEOUT_EMPTY);
             *abort_flag = 1;
             break;
@@ -192,7 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int buf = t & 1;
         const uint32_t aph = (t >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[buf], aph ^ 1)) {
+        if (!mbar_wait_abortable(&tempty_bar[buf], aph ^ 1, abort_flag)) {
           atomicMax(status, ST_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
           break;
@@ -204,7 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph)) {
+          if (!mbar_wait_abortable(&full_bar[s], ph, abort_flag)) {
             atomicMax(status, ST_TIMEOUT_FULL);
             *abort_flag = 1;
             break;
@@ -239,7 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
-      const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;
+      const int ok = mbar_wait_abortable(&tfull_bar[buf], aph, abort_flag) ? 1 : 0;
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) {
           atomicMax(status, ST_TIMEOUT_TMEM_FULL);

@@ -87,6 +87,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int cluster_id = blockIdx.x >> 1;
   const int n_clusters = gridDim.x >> 1;
   const int my_tiles = sched.tiles_for_cta(cluster_id, n_clusters);
+  // a role that gives up raises the flag in both CTAs of the pair: the partner's roles wait on barriers this CTA
+  // would have signalled
+  const uint32_t partner_abort = mapa_shared(smem_u32(const_cast<const int*>(abort_flag)), rank ^ 1u);
+  auto raise_abort = [&]() {
+    *abort_flag = 1;
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(partner_abort), "r"(1) : "memory");
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -130,7 +137,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int ntile = nmain + (ti.extra ? kb_extra : 0);
         if (!comm.ready(ti)) {
           atomicMax(status, ST_TIMEOUT_PEER);
-          *abort_flag = 1;
+          raise_abort();
           break;
         }
         for (int kb = 0; kb < ntile; ++kb, ++it) {
@@ -138,9 +145,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint32_t ph = (it / STAGES) & 1;
           // no abort poll in this loop: the time from "stage free" to "loads issued" is on the pipeline's critical
           // path; a partner that gave up is noticed through this wait's own limit
-          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+          if (!mbar_wait_abortable(&empty_bar[s], ph ^ 1, abort_flag)) {
             atomicMax(status, ST_TIMEOUT_EMPTY);
-            *abort_flag = 1;
+            raise_abort();
             break;
           }
           uint8_t* sa = smem + s * G2_STAGE_BYTES;
@@ -166,9 +173,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (int t = 0; t < my_tiles && !*abort_flag; ++t) {
         const int buf = t & 1;
         const uint32_t aph = (t >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[buf], aph ^ 1)) {
+        if (!mbar_wait_abortable(&tempty_bar[buf], aph ^ 1, abort_flag)) {
           atomicMax(status, ST_TIMEOUT_TMEM_EMPTY);
-          *abort_flag = 1;
+          raise_abort();
           break;
         }
         tc_fence_after_sync();
@@ -178,9 +185,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int kb = 0; kb < ntile; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph)) {
+          if (!mbar_wait_abortable(&full_bar[s], ph, abort_flag)) {
             atomicMax(status, ST_TIMEOUT_FULL);
-            *abort_flag = 1;
+            raise_abort();
             break;
           }
           tc_fence_after_sync();
@@ -211,11 +218,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ti.m_blk = ti.m_blk * 2 + static_cast<int>(rank);
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
-      const int ok = mbar_wait(&tfull_bar[buf], aph) ? 1 : 0;
+      const int ok = mbar_wait_abortable(&tfull_bar[buf], aph, abort_flag) ? 1 : 0;
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) {
           atomicMax(status, ST_TIMEOUT_TMEM_FULL);
-          *abort_flag = 1;
+          raise_abort();
         }
         break;
       }

@@ -88,6 +88,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return false;
 }
 
+// Bounded wait for the GEMM pipelines, by wall time instead of poll count: a role of a fused compute+collective
+// kernel may legitimately sit behind a peer GPU that is hundreds of milliseconds late (its host was busy), so the
+// roles downstream of that wait must not give up after a fixed number of polls.  Every 1024 polls the wait looks
+// at the CTA's abort flag (another role gave up: unwind at once) and at the global timer.
+#ifndef ARTB_MBAR_BUDGET_MS
+#define ARTB_MBAR_BUDGET_MS 30000ull
+#endif
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      if (now - t0 > ARTB_MBAR_BUDGET_MS * 1000000ull || i > 0xF0000000u) return false;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------ TMA
 // Tiled 2-D load global -> shared, completion on an mbarrier (transaction bytes).
 // No multicast qualifier anywhere: each CTA fetches its own tiles.

@@ -33,11 +33,32 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   return v;
 }
 
-// Bounded wait until *p >= target.  `spin` polls of ~0.1-1 us each.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, uint32_t spin) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Deadline of a bounded wait of `budget_us` microseconds, and its check (polled every 64th iteration; an iteration cap
+// stands behind it, so the wait ends even where the timer does not advance).
+struct WaitBudget {
+  uint64_t t0, budget_ns;
   uint32_t it = 0;
+  __device__ __forceinline__ explicit WaitBudget(uint32_t budget_us)
+      : t0(global_timer_ns()), budget_ns(static_cast<uint64_t>(budget_us) * 1000ull) {}
+  __device__ __forceinline__ bool expired() {
+    ++it;
+    if (it > 0xF0000000u) return true;
+    return (it & 63u) == 0 && global_timer_ns() - t0 > budget_ns;
+  }
+};
+
+// Bounded wait until *p >= target: gives up after `budget_us` microseconds of wall time (callers pass wait_ms * 1000).
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, uint32_t budget_us) {
+  if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
+  WaitBudget w(budget_us);
   while (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) < 0) {
-    if (++it > spin) return false;
+    if (w.expired()) return false;
     __nanosleep(64);
   }
   return true;

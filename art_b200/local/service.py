@@ -140,7 +140,7 @@ class ModelState:
             if has_gpu:
                 from ..parallel.symm_mem import FusedGradAllReduce
 
-                grad_sync = FusedGradAllReduce(self.device, self.data_ranks, dp_group)
+                grad_sync = FusedGradAllReduce(self.device, self.data_ranks, dp_group, wait_ms=20000)
             else:
                 from ..parallel.dp import nccl_grad_sync
 

@@ -105,7 +105,8 @@ class Trainer:
                 from ..parallel.symm_mem import FusedGradAllReduce
 
                 # ranks of a context- or tensor-parallel group hold partial gradients of the SAME rows: sum them
-                self._cp_sync = FusedGradAllReduce(self.device, dist.get_world_size(sum_group), sum_group, average=False)
+                self._cp_sync = FusedGradAllReduce(self.device, dist.get_world_size(sum_group), sum_group, average=False,
+                                                   wait_ms=20000)
                 self._sum_group = sum_group
         else:
             from ..models.native import LoraFlat

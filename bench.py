@@ -238,7 +238,7 @@ def main():
             if data_ranks > 1:
                 from art_b200.parallel.symm_mem import FusedGradAllReduce
 
-                grad_sync = FusedGradAllReduce(dev, data_ranks, dp_group)
+                grad_sync = FusedGradAllReduce(dev, data_ranks, dp_group, wait_ms=20000)
                 sync_name += f" + fused-p2p-allreduce(mean over dp{data_ranks})"
         elif par == "ep":
             from art_b200.parallel.ep import ExpertParallel
@@ -351,6 +351,7 @@ def main():
                            output_dir=out, rank=rank, world=world, tp_size=T)
         try:
             st = svc.state            # every rank builds trainer + engine on the launcher's process group
+            barrier()
             tcfg = arttypes.TrainConfig(learning_rate=1e-5)
             dcfg = {"rows_per_optimizer_step": R, "tokens_per_microbatch": args.micro_tokens}
 
