@@ -24,6 +24,7 @@ static int launch_ag(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
                      int kb_main, int kb_extra, const SchedSegRot& sched, const EpiStore<BN>& epi, const AgComm& comm,
                      int* status, int max_ctas, cudaStream_t stream) {
   using L = GemmSmemLayout<BN, STAGES>;
+  static_assert(L::TOTAL + 4 * EpiStore<BN>::COL_SPLIT * 4096 + 64 <= 227 * 1024, "shared memory");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, SchedSegRot, EpiStore<BN>, AgComm>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -37,7 +38,7 @@ static int launch_ag(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
-  kern<<<grid, GEMM_THREADS + AgComm::THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
+  kern<<<grid, gemm_pipe_threads<EpiStore<BN>>() + AgComm::THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
                                                                    status, comm);
   return static_cast<int>(cudaGetLastError());
 }
@@ -61,7 +62,7 @@ static int launch_ag_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CU
   int cap = sm_count() / 2;
   if (max_ctas > 0 && max_ctas / 2 < cap) cap = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (clusters > cap) clusters = cap;
-  kern<<<2 * clusters, GEMM_THREADS + AgComm::THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched,
+  kern<<<2 * clusters, gemm_pipe_threads<EpiStore<256>>() + AgComm::THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched,
                                                                           epi, status, comm);
   return static_cast<int>(cudaGetLastError());
 }

@@ -27,6 +27,7 @@ static int launch_rs(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
                      int kb_main, int kb_extra, const SchedSegRot& sched, const EpiReduceScatter<BN>& epi,
                      const RsComm& comm, int* status, int max_ctas, cudaStream_t stream) {
   using L = GemmSmemLayout<BN, STAGES>;
+  static_assert(L::TOTAL + 8 * 4096 + 64 <= 227 * 1024, "shared memory");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, SchedSegRot, EpiReduceScatter<BN>, RsComm>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -40,7 +41,8 @@ static int launch_rs(const CUtensorMap& tA, const CUtensorMap& tB, const CUtenso
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, comm);
+  kern<<<grid, gemm_pipe_threads<EpiReduceScatter<BN>>() + RsComm::THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra,
+                                                                                              sched, epi, status, comm);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -62,7 +64,8 @@ static int launch_rs_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CU
   int cap = sm_count() / 2;
   if (max_ctas > 0 && max_ctas / 2 < cap) cap = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (clusters > cap) clusters = cap;
-  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, comm);
+  kern<<<2 * clusters, gemm_pipe_threads<EpiReduceScatter<256>>() + RsComm::THREADS, L::TOTAL, stream>>>(
+      tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, comm);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -71,7 +74,7 @@ static int launch_rs_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CU
 using namespace artb;
 
 // h            symmetric buffer handle; byte offsets into its data area, identical on every rank:
-//              off_stage bf16 [world-1][m_seg][N], off_flag uint32 [world-1][tile_cap][4],
+//              off_stage bf16 [world-1][m_seg][N], off_flag uint32 [world-1][tile_cap][8],
 //              off_done uint32 [world]
 // A, B         local operands [world*m_seg, K] and [N, K] (K = this rank's slice of the reduction dim)
 // A2, B2, K2   optional extra-K pair (LoRA partial), K2 multiple of 8

@@ -56,8 +56,9 @@ struct SchedSplitK {
 // swiglu_bwd: acc is d(silu(gate) * up) [M, N]; H holds the forward's gate|up pre-activations [M, 2N] (interleaved in
 // blocks of 16) and C receives d(gate|up) [M, 2N] in the same layout, so the activation gradient never exists in
 // memory as a separate tensor.
-template <int BN>
+template <int BN, int CS = 2>
 struct EpiStore {
+  static constexpr int COL_SPLIT = CS;   // two epilogue warps per TMEM lane quarter, half of the columns each
   void* C;
   const __nv_bfloat16* R;
   __nv_bfloat16* H;
@@ -73,13 +74,14 @@ struct EpiStore {
   // rows x 16 bytes; the pieces reach their owning thread through a per-warp shared-memory slab, and the result leaves
   // the same way.  (One row per thread in global memory costs one L1 wavefront per lane and instruction; for this
   // epilogue, which moves 256 bytes per output row and chunk, that was more LSU time than the tile's main loop has.)
+  // A second chunk of look-ahead was measured and does not help: these warps wait on issue latency, not on memory.
   uint4 pre[8];
   int pre_n = 0;     // pieces of `pre` that hold the chunk about to be processed (0: load at the point of use)
 
   __device__ __forceinline__ void issue(const TileInfo& ti, int row, int c) {
     const int gc = ti.n_blk * BN + c;
     pre_n = 0;
-    if (gc + 32 > N) return;
+    if (c >= epi_col_end<BN, CS>() || gc + 32 > N) return;
     if (swiglu_bwd) {
       const int lane = row & 31;
       const int row0 = ti.m_blk * GEMM_BM + (row & ~31);       // first row of this warp's 32-row band
@@ -101,25 +103,31 @@ struct EpiStore {
     }
   }
 
-  __device__ void tile_begin(const TileInfo& ti, int row) { issue(ti, row, 0); }
+  __device__ void tile_begin(const TileInfo& ti, int row) { issue(ti, row, epi_col_begin<BN, CS>()); }
   __device__ void tile_end(const TileInfo&, int) {}
 
   // d(gate|up) of one 32-column chunk of d(activation); executed by whole warps (rows past M are masked, not skipped)
   __device__ __forceinline__ void chunk_swiglu_bwd(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
-    __shared__ uint4 s_slab[4][32 * 9];      // per epilogue warp: 32 rows x (8 + 1 pad) 16-byte pieces
+    // per epilogue warp: 32 rows x 8 16-byte pieces; piece p of row r sits at r * 8 + (p ^ (r & 7)), which keeps both
+    // access patterns (8 lanes along a row; 32 lanes down a column of pieces) free of bank conflicts without padding
+    __shared__ uint4 s_slab[4 * CS][32 * 8];
     const int gc = ti.n_blk * BN + c;
     if (gc >= N) return;                     // warp-uniform
     const int lane = row & 31;
-    uint4* sb = s_slab[(row >> 5) & 3];
+    uint4* sb = s_slab[epi_warp_slot()];
     const int row0 = ti.m_blk * GEMM_BM + (row & ~31);
-    // gate|up pieces -> slab (row-major, padded), then every thread picks up its own row
+    const int sw = lane & 7;
+    // gate|up pieces -> slab, then every thread picks up its own row
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sb[(i * 4 + (lane >> 3)) * 9 + (lane & 7)] = pre[i];
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      sb[r * 8 + (sw ^ (r & 7))] = pre[i];
+    }
     __syncwarp();
-    if (c + 32 < BN) issue(ti, row, c + 32);
+    issue(ti, row, c + 32);
     uint4 in[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) in[j] = sb[lane * 9 + j];
+    for (int j = 0; j < 8; ++j) in[j] = sb[lane * 8 + (j ^ sw)];
     __syncwarp();
     // columns gc .. gc+31 of the activation map to columns 2gc .. 2gc+63 of gate|up: [g 0-15 | u 0-15 | g 16-31 | u 16-31]
 #pragma unroll
@@ -133,21 +141,25 @@ struct EpiStore {
       for (int e = 0; e < 8; ++e) {
         const float2 g2 = __bfloat1622float2(gp[e]), u2 = __bfloat1622float2(up[e]);
         const float d0 = __uint_as_float(acc[blk * 16 + 2 * e]), d1 = __uint_as_float(acc[blk * 16 + 2 * e + 1]);
-        const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
-        dgp[e] = pack_bf16x2(d0 * u2.x * s0 * (1.f + g2.x * (1.f - s0)), d1 * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
-        dup[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+        // s = sigmoid(g); d gate = d u s (1 + g (1 - s)); d up = d g s   (approximate ex2 / rcp: the result is bf16)
+        const float s0 = rcp_approx(1.f + __expf(-g2.x)), s1 = rcp_approx(1.f + __expf(-g2.y));
+        const float a0 = d0 * s0, a1 = d1 * s1;
+        const float t0 = fmaf(-g2.x, s0, g2.x), t1 = fmaf(-g2.y, s1, g2.y);
+        const float p0 = a0 * u2.x, p1 = a1 * u2.y;
+        dgp[e] = pack_bf16x2(fmaf(p0, t0, p0), fmaf(p1, t1, p1));
+        dup[e] = pack_bf16x2(a0 * g2.x, a1 * g2.y);
       }
-      sb[lane * 9 + blk * 4] = dg[0];
-      sb[lane * 9 + blk * 4 + 1] = dg[1];
-      sb[lane * 9 + blk * 4 + 2] = du[0];
-      sb[lane * 9 + blk * 4 + 3] = du[1];
+      sb[lane * 8 + ((blk * 4) ^ sw)] = dg[0];
+      sb[lane * 8 + ((blk * 4 + 1) ^ sw)] = dg[1];
+      sb[lane * 8 + ((blk * 4 + 2) ^ sw)] = du[0];
+      sb[lane * 8 + ((blk * 4 + 3) ^ sw)] = du[1];
     }
     __syncwarp();
-    __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(C) + 2 * gc + (lane & 7) * 8;
+    __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(C) + 2 * gc + sw * 8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r = i * 4 + (lane >> 3);
-      if (row0 + r < M) *reinterpret_cast<uint4*>(dgu + static_cast<size_t>(row0 + r) * ldc) = sb[r * 9 + (lane & 7)];
+      if (row0 + r < M) *reinterpret_cast<uint4*>(dgu + static_cast<size_t>(row0 + r) * ldc) = sb[r * 8 + (sw ^ (r & 7))];
     }
     __syncwarp();
   }
@@ -165,7 +177,7 @@ struct EpiStore {
     const int cur_n = pre_n;
 #pragma unroll
     for (int j = 0; j < 4; ++j) cur[j] = pre[j];
-    if (c + 32 < BN) issue(ti, row, c + 32);
+    issue(ti, row, c + 32);
     if (bias) {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -231,8 +243,8 @@ struct EpiStore {
         float g1 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[j + 1])));
         float u0 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[16 + j])));
         float u1 = __bfloat162float(__float2bfloat16(__uint_as_float(acc[16 + j + 1])));
-        float h0 = g0 / (1.f + __expf(-g0)) * u0;
-        float h1 = g1 / (1.f + __expf(-g1)) * u1;
+        float h0 = g0 * rcp_approx(1.f + __expf(-g0)) * u0;
+        float h1 = g1 * rcp_approx(1.f + __expf(-g1)) * u1;
         hv[j >> 1] = pack_bf16x2(h0, h1);
       }
       *reinterpret_cast<uint4*>(h) = make_uint4(hv[0], hv[1], hv[2], hv[3]);
@@ -269,7 +281,7 @@ struct SchedGrouped {
 
 template <int BN>
 struct EpiGrouped {
-  EpiStore<BN> st;
+  EpiStore<BN, 1> st;
   __device__ void tile_begin(const TileInfo& ti, int row) {
     if (ti.group >= 0) st.tile_begin(ti, row);
   }

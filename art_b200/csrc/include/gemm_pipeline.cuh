@@ -2,10 +2,14 @@
 //
 //   D[128 x BN] (fp32, TMEM) = A[128 x K] * B[BN x K]^T      (both operands K-major bf16)
 //
-// One CTA = 6 warps:
+// One CTA = 6 or 10 warps (+ communication warps of a fused collective):
 //   warp 0      TMA producer  (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer    (one elected lane issues tcgen05.mma; the warp owns TMEM alloc/dealloc)
 //   warps 2..5  epilogue      (each reads its 32-lane quarter of TMEM with tcgen05.ld)
+//   warps 6..9  second epilogue set, when the epilogue policy asks for it (COL_SPLIT = 2): the two warps of a lane
+//               quarter then take half of the tile's columns each.  One warp per scheduler issues an instruction
+//               every ~8 cycles (dependent fixed-latency arithmetic); an epilogue with real arithmetic in it (SwiGLU
+//               backward: ~40 instructions per element) is then slower than the tile's main loop, two warps are not.
 //
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of
 // tile i overlaps the main loop of tile i+1.  Operand stages live in shared
@@ -27,7 +31,33 @@ namespace artb {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;   // pipeline threads of a kernel whose epilogue policy does not split columns
+
+// Epilogue policies may declare `static constexpr int COL_SPLIT = 2` (default 1).
+template <class E, class = void>
+struct EpiColSplit {
+  static constexpr int value = 1;
+};
+template <class E>
+struct EpiColSplit<E, decltype(void(E::COL_SPLIT))> {
+  static constexpr int value = E::COL_SPLIT;
+};
+// threads of the producer, MMA and epilogue warps (communication warps come after them)
+template <class Epi>
+constexpr int gemm_pipe_threads() {
+  return 64 + 128 * EpiColSplit<Epi>::value;
+}
+// Index of the calling epilogue warp (0 .. 4 * COL_SPLIT - 1) and the column range [begin, end) of a BN-wide tile it
+// handles (multiples of 32; with an odd number of chunks the first set takes one more).
+__device__ __forceinline__ int epi_warp_slot() { return static_cast<int>(threadIdx.x >> 5) - 2; }
+template <int BN, int CS>
+__device__ __forceinline__ int epi_col_begin() {
+  return CS == 1 ? 0 : (epi_warp_slot() >> 2) * (((BN / 32 + 1) / 2) * 32);
+}
+template <int BN, int CS>
+__device__ __forceinline__ int epi_col_end() {
+  return (CS == 1 || (epi_warp_slot() >> 2) == 1) ? BN : ((BN / 32 + 1) / 2) * 32;
+}
 
 struct TileInfo {
   int m_blk;   // tile row index   (rows m_blk*128 ..)
@@ -98,7 +128,7 @@ template <class E>
 __device__ __forceinline__ void epi_flush(E&, int, long) {}
 
 template <int BN, int STAGES, class Sched, class Epi, class Comm = NoComm>
-__global__ void __launch_bounds__(GEMM_THREADS + Comm::THREADS, 1)
+__global__ void __launch_bounds__(gemm_pipe_threads<Epi>() + Comm::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB2, int kb_main, int kb_extra,
@@ -107,6 +137,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // two accumulators of BN columns each; the allocation is rounded up to a power of two
   constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static_assert(BN % 32 == 0 && BN <= 256, "BN");
+  constexpr int CS = EpiColSplit<Epi>::value;
+  constexpr int PIPE_THREADS = gemm_pipe_threads<Epi>();
+  static_assert(CS == 1 || (CS == 2 && BN >= 64), "COL_SPLIT");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -129,7 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4);
+      mbar_init(&tempty_bar[b], 4 * CS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -225,12 +258,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_commit(&tfull_bar[buf]);  // accumulator complete
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 2 + 4 * CS) {
     // ------------------------------------------------------------ communication warps
-    comm.push(static_cast<int>(threadIdx.x) - GEMM_THREADS, status);
+    comm.push(static_cast<int>(threadIdx.x) - PIPE_THREADS, status);
   } else {
     // ------------------------------------------------------------ epilogue
     Epi epi = epi_in;
+    const int c_begin = epi_col_begin<BN, CS>(), c_end = epi_col_end<BN, CS>();
     const int q = warp & 3;  // TMEM lane quarter this warp may touch
     const int row = q * 32 + lane;
     for (int t = 0; t < my_tiles; ++t) {
@@ -239,6 +273,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const TileInfo ti = sched.get(blockIdx.x, gridDim.x, t);
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
+      // per-tile setup (peer-flag waits, first operand prefetches) runs while the tile's MMAs are still in flight
+      epi.tile_begin(ti, row);
       const int ok = mbar_wait_abortable(&tfull_bar[buf], aph, abort_flag) ? 1 : 0;
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) {
@@ -248,10 +284,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after_sync();
-      epi.tile_begin(ti, row);
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         uint32_t acc[32];
         tmem_ld_32x32(taddr + c, acc);
         tmem_ld_wait();

@@ -12,7 +12,8 @@
 //              partner's loads credit the leader's barrier; no multicast qualifier anywhere)
 //   empty[s]   in both CTAs, count 1, signalled by the leader's tcgen05.commit multicast to both
 //   tfull[b]   in both CTAs, count 1, same multicast commit once a tile's MMAs are issued
-//   tempty[b]  leader only, count 8: the 4 epilogue warps of each CTA arrive (the partner remotely)
+//   tempty[b]  leader only, count 8 (16 with a column-split epilogue): the epilogue warps of each CTA arrive (the
+//              partner's remotely)
 // All waits are bounded; a timeout sets the CTA's abort flag and the status word, and the CTA
 // falls through to the teardown (cluster barrier, TMEM dealloc).
 #pragma once
@@ -63,13 +64,15 @@ struct SchedPair {
 // per CTA with that CTA's 128-row tile index, so the fused tensor-parallel policies work unchanged (each CTA's producer
 // waits for the arrival of its own 128 rows; each CTA's epilogue scatters / reduces its own 128 x BN2 half).
 template <int STAGES, int BN2, class Sched, class Epi, class Comm = NoComm>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS + Comm::THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm_pipe_threads<Epi>() + Comm::THREADS, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                          int kb_main, int kb_extra, Sched sched, Epi epi_in, int* status, Comm comm) {
   using L = Gemm2SmemLayout<STAGES, BN2>;
   constexpr int G2_BN = BN2, G2_BNH = BN2 / 2, G2_STAGE_BYTES = L::STAGE_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
+  constexpr int CS = EpiColSplit<Epi>::value;
+  constexpr int PIPE_THREADS = gemm_pipe_threads<Epi>();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -102,7 +105,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 8);
+      mbar_init(&tempty_bar[b], 8 * CS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -204,12 +207,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tc_commit_2cta(&tfull_bar[buf], 3);   // accumulator complete in both CTAs
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 2 + 4 * CS) {
     // ------------------------------------------------------------ communication warps
-    comm.push(static_cast<int>(threadIdx.x) - GEMM_THREADS, status);
+    comm.push(static_cast<int>(threadIdx.x) - PIPE_THREADS, status);
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     Epi epi = epi_in;
+    const int c_begin = epi_col_begin<G2_BN, CS>(), c_end = epi_col_end<G2_BN, CS>();
     const int q = warp & 3;
     const int row = q * 32 + lane;
     for (int t = 0; t < my_tiles; ++t) {
@@ -218,6 +222,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ti.m_blk = ti.m_blk * 2 + static_cast<int>(rank);
       const int buf = t & 1;
       const uint32_t aph = (t >> 1) & 1;
+      // per-tile setup (peer-flag waits, first operand prefetches) runs while the tile's MMAs are still in flight
+      epi.tile_begin(ti, row);
       const int ok = mbar_wait_abortable(&tfull_bar[buf], aph, abort_flag) ? 1 : 0;
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) {
@@ -227,10 +233,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         break;
       }
       tc_fence_after_sync();
-      epi.tile_begin(ti, row);
       const uint32_t taddr = tmem_base + buf * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < G2_BN; c += 32) {
+      for (int c = c_begin; c < c_end; c += 32) {
         uint32_t acc[32];
         tmem_ld_32x32(taddr + c, acc);
         tmem_ld_wait();

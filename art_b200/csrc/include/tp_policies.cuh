@@ -107,7 +107,7 @@ __device__ __forceinline__ void tp_publish_done(const TpPeers& pt, long off_done
 // X), arrival flags uint32 [world][m_seg / 32] at off_flag, done words uint32 [world] at off_done.
 // The caller has written its own shard into rows [rank * m_seg, (rank+1) * m_seg) of the local X / T.
 struct AgComm {
-  static constexpr int THREADS = 128;
+  static constexpr int THREADS = 64;   // two warps; eight 16-byte loads in flight per thread
   TpPeers pt;
   long off_x, off_t, off_flag, off_done;
   int rank, world, m_seg;
@@ -120,12 +120,12 @@ struct AgComm {
     uint4* d = reinterpret_cast<uint4*>(dst);
     const long n = bytes >> 4;
     long i = tid;
-    for (; i + 3 * THREADS < n; i += 4 * THREADS) {   // four loads in flight per thread
-      uint4 a = s[i], b = s[i + THREADS], c = s[i + 2 * THREADS], e = s[i + 3 * THREADS];
-      d[i] = a;
-      d[i + THREADS] = b;
-      d[i + 2 * THREADS] = c;
-      d[i + 3 * THREADS] = e;
+    for (; i + 7 * THREADS < n; i += 8 * THREADS) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s[i + j * THREADS];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d[i + j * THREADS] = v[j];
     }
     for (; i < n; i += THREADS) d[i] = s[i];
   }
@@ -144,7 +144,7 @@ struct AgComm {
       if (!ok) atomicMax(status, ST_TIMEOUT_PEER);
       s_ok = ok;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, 64;" ::: "memory");
     if (!s_ok) return;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const long row0 = static_cast<long>(rank) * m_seg + static_cast<long>(u) * TP_PUSH_ROWS;
@@ -156,7 +156,7 @@ struct AgComm {
           copy_rows(pt.base[p] + off_t + row0 * row_bytes_t, pt.base[rank] + off_t + row0 * row_bytes_t,
                     static_cast<long>(TP_PUSH_ROWS) * row_bytes_t, tid);
         __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 64;" ::: "memory");
         if (tid == 0)
           st_release_sys_u32(reinterpret_cast<uint32_t*>(pt.base[p] + off_flag) + rank * units + u, epoch);
       }
@@ -181,7 +181,7 @@ struct AgComm {
 
 // -------------------------------------------------------------------------- reduce-scatter side
 // Symmetric layout: staging bf16 [world-1][m_seg][N] at off_stage (slot s of owner o holds the
-// partial of rank (o + 1 + s) % world), flags uint32 [world-1][tile_cap][4] at off_flag, done
+// partial of rank (o + 1 + s) % world), flags uint32 [world-1][tile_cap][8] at off_flag (one per epilogue warp), done
 // words at off_done.  Output: out[m_seg, N] bf16 = sum over ranks (+ residual shard R).
 struct RsComm {
   static constexpr int THREADS = 0;
@@ -197,8 +197,9 @@ struct RsComm {
 
 template <int BN>
 struct EpiReduceScatter {
+  static constexpr int COL_SPLIT = 2;   // two epilogue warps per TMEM lane quarter, half of the columns each
   // remote tiles leave through a shared-memory slab that is flushed after every SECOND 32-column chunk
-  static_assert(BN % 64 == 0, "EpiReduceScatter needs an even number of 32-column chunks per tile");
+  static_assert(BN % 128 == 0, "EpiReduceScatter needs an even number of 32-column chunks per epilogue warp");
   TpPeers pt;
   long off_stage, off_flag, off_done;
   __nv_bfloat16* out;
@@ -221,7 +222,7 @@ struct EpiReduceScatter {
   __device__ __forceinline__ void issue(const TileInfo& ti, int row, int c) {
     const int gc = ti.n_blk * BN + c;
     pre_ok = 0;
-    if (!own || gc + 32 > N) return;
+    if (!own || c >= epi_col_end<BN, COL_SPLIT>() || gc + 32 > N) return;
     const int lane = row & 31;
     const uint4* p = reinterpret_cast<const uint4*>(stage + static_cast<size_t>(lane) * N + gc);
 #pragma unroll
@@ -237,6 +238,7 @@ struct EpiReduceScatter {
   __device__ void tile_begin(const TileInfo& ti, int row) {
     const int seg = ti.group;
     const int q = (row >> 5) & 3, lane = row & 31;
+    const int ws = epi_warp_slot();     // the owner's warp of the same slot reads what this warp stages
     own = seg == rank;
     const int lrow0 = ti.m_blk * GEMM_BM - seg * m_seg;
     lrow = lrow0 + row;
@@ -247,7 +249,7 @@ struct EpiReduceScatter {
       stage = reinterpret_cast<__nv_bfloat16*>(tp_base(pt, seg) + off_stage) +
               (static_cast<size_t>(slot) * m_seg + lrow0 + q * 32) * N;
       flag = reinterpret_cast<uint32_t*>(tp_base(pt, seg) + off_flag) +
-             (static_cast<size_t>(slot) * tile_cap + tile_local) * 4 + q;
+             (static_cast<size_t>(slot) * tile_cap + tile_local) * 8 + ws;
       // the owner must have consumed the call that last used this parity of its staging buffer (checked once per
       // launch and owner: the word only grows)
       if (epoch > 2 && !((done_seen >> seg) & 1u)) {
@@ -258,32 +260,34 @@ struct EpiReduceScatter {
     } else {
       stage = reinterpret_cast<__nv_bfloat16*>(tp_base(pt, rank) + off_stage) +
               static_cast<size_t>(lrow0 + q * 32) * N;
-      flag = reinterpret_cast<uint32_t*>(tp_base(pt, rank) + off_flag) + static_cast<size_t>(tile_local) * 4 + q;
+      flag = reinterpret_cast<uint32_t*>(tp_base(pt, rank) + off_flag) + static_cast<size_t>(tile_local) * 8 + ws;
       if (lane == 0)
         for (int s = 0; s < world - 1; ++s)
-          if (!wait_flag_ge(flag + static_cast<size_t>(s) * tile_cap * 4, epoch, spin)) ok = 0;
+          if (!wait_flag_ge(flag + static_cast<size_t>(s) * tile_cap * 8, epoch, spin)) ok = 0;
     }
     if (lane == 0 && !ok) atomicMax(status, ST_TIMEOUT_PEER);
     __syncwarp();
-    issue(ti, row, 0);       // after the flags: the staged partials are complete
+    issue(ti, row, epi_col_begin<BN, COL_SPLIT>());       // after the flags: the staged partials are complete
   }
 
   __device__ void chunk(const TileInfo& ti, int row, int c, uint32_t (&acc)[32]) {
     const int gc = ti.n_blk * BN + c;
-    const int q = (row >> 5) & 3, lane = row & 31;
+    const int lane = row & 31;
     uint4 cur[8];
     const int cur_ok = pre_ok;
 #pragma unroll
     for (int j = 0; j < 8; ++j) cur[j] = pre[j];
-    if (own && c + 32 < BN) issue(ti, row, c + 32);
+    if (own) issue(ti, row, c + 32);
     if (!own) {
       // Remote tile: the partial goes to the owner as bf16.  A thread holds one row, so a direct
       // store would scatter 16-byte pieces over 32 rows; instead two 32-column slabs are parked in
       // shared memory and written out with 8 lanes covering 128 contiguous bytes of a row.
-      __shared__ uint4 s_buf[4][32 * 9];   // per warp: 32 rows x (8 + 1 pad) 16-byte pieces
+      // per warp: 32 rows x 8 16-byte pieces; piece p of row r at r * 8 + (p ^ (r & 7)) (no bank conflicts, no padding)
+      __shared__ uint4 s_buf[8][32 * 8];
+      uint4* sb = s_buf[epi_warp_slot()];
       const int half = (c >> 5) & 1;
       if (gc < N) {
-        uint4* w = s_buf[q] + lane * 9 + half * 4;
+        uint4* w = sb + lane * 8;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 v;
@@ -291,7 +295,7 @@ struct EpiReduceScatter {
           v.y = pack_bf16x2(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
           v.z = pack_bf16x2(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
           v.w = pack_bf16x2(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
-          w[j] = v;
+          w[(half * 4 + j) ^ (lane & 7)] = v;
         }
       }
       if (half == 1) {
@@ -304,7 +308,7 @@ struct EpiReduceScatter {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = i * 4 + (lane >> 3);
-            const uint4 v = s_buf[q][r * 9 + j];
+            const uint4 v = sb[r * 8 + (j ^ (r & 7))];
             *reinterpret_cast<uint4*>(stage + static_cast<size_t>(r) * N + gc0 + j * 8) = v;
           }
         }

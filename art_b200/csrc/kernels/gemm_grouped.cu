@@ -69,7 +69,7 @@ ARTB_EXPORT int artb_gemm_grouped_bf16_tn(const void* A, int lda, const void* B,
 #define ARTB_LAUNCH(BN_, ST_)                                                                                  \
   {                                                                                                            \
     SchedGrouped sched{tile_expert, m_tiles, (N + BN_ - 1) / BN_, N};                                          \
-    EpiGrouped<BN_> epi{EpiStore<BN_>{C, nullptr, reinterpret_cast<__nv_bfloat16*>(H), nullptr, ldc, 0, ldh,   \
+    EpiGrouped<BN_> epi{EpiStore<BN_, 1>{C, nullptr, reinterpret_cast<__nv_bfloat16*>(H), nullptr, ldc, 0, ldh,   \
                                       M, N, 0, N}};                                                            \
     return launch_grouped<BN_, ST_>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, stream);          \
   }

@@ -24,6 +24,8 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
                        const CUtensorMap& tB2, int kb_main, int kb_extra, int M, int N,
                        const EpiStore<BN>& epi, int* status, int max_ctas, cudaStream_t stream) {
   using L = GemmSmemLayout<BN, STAGES>;
+  // operand stages + the epilogue warps' 4 KB re-layout slabs (static shared memory) must fit the 227 KB of a CTA
+  static_assert(L::TOTAL + 4 * EpiStore<BN>::COL_SPLIT * 4096 + 64 <= 227 * 1024, "shared memory");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, SchedMFast, EpiStore<BN>>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -39,7 +41,7 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
+  kern<<<grid, gemm_pipe_threads<EpiStore<BN>>(), L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
                                                  status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
@@ -112,7 +114,7 @@ ARTB_EXPORT int artb_gemm_bf16_tn(const void* A, int lda, const void* B, int ldb
   }
   if (bn == 256) ARTB_LAUNCH(256, 4)
   if (bn == 224) ARTB_LAUNCH(224, 4)
-  if (bn == 192) ARTB_LAUNCH(192, 5)
+  if (bn == 192) ARTB_LAUNCH(192, 4)
   if (bn == 128) ARTB_LAUNCH(128, 6)
   ARTB_LAUNCH(64, 8)
 #undef ARTB_LAUNCH

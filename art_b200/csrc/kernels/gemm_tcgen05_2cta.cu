@@ -13,6 +13,7 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
                        int M, int N, int K, int epilogue, int res_cols, int* status, int max_clusters,
                        cudaStream_t stream) {
   using L = Gemm2SmemLayout<STAGES, BN2>;
+  static_assert(L::TOTAL + 4 * EpiStore<BN2>::COL_SPLIT * 4096 + 64 <= 227 * 1024, "shared memory");
   CUtensorMap tA, tB, tA2, tB2;
   int e;
   if ((e = make_tmap_bf16_2d(&tA, A, M, K, lda, GEMM_BM, GEMM_BK))) return e;
@@ -43,7 +44,7 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
                       ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};
   SchedPair sched{m_tiles2, n_tiles, pick_group_m(m_tiles2, 2 * GEMM_BM, K), 1, kb_main, kb_main};
-  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status,
+  kern<<<2 * clusters, gemm_pipe_threads<EpiStore<BN2>>(), L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status,
                                                         NoComm{});
   return static_cast<int>(cudaGetLastError());
 }

@@ -37,13 +37,20 @@ def bench_gemm(a) -> dict:
     dev = "cuda"
     x = torch.randn(a.m, a.k, device=dev).bfloat16()
     w = (torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16()
-    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(a.m, 2 * a.n if a.epilogue == "swiglu_bwd" else a.n, device=dev, dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
     two = None if a.two_cta < 0 else bool(a.two_cta)
-    ms = _time(lambda: gemm_tn(x, w, out=out, bn=a.bn, two_cta=two), a.iters, a.warmup, flush)
+    kw = {}
+    if a.epilogue == "resid":
+        kw["residual"] = torch.randn(a.m, a.n, device=dev).bfloat16()
+    elif a.epilogue == "swiglu":
+        kw["swiglu_out"] = torch.empty(a.m, a.n // 2, device=dev, dtype=torch.bfloat16)
+    elif a.epilogue == "swiglu_bwd":
+        kw["swiglu_bwd_gu"] = torch.randn(a.m, 2 * a.n, device=dev).bfloat16()
+    ms = _time(lambda: gemm_tn(x, w, out=out, bn=a.bn, two_cta=two, **kw), a.iters, a.warmup, flush)
     _lib.check_status()
     fl = 2.0 * a.m * a.n * a.k
-    res = {"op": "gemm_tn", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "two_cta": a.two_cta, "ms": round(ms, 4),
+    res = {"op": "gemm_tn", "m": a.m, "n": a.n, "k": a.k, "bn": a.bn, "two_cta": a.two_cta, "epilogue": a.epilogue, "ms": round(ms, 4),
            "tflops": round(fl / ms / 1e9, 1)}
     if not a.no_baseline:
         ms_b = _time(lambda: torch.matmul(x, w.t(), out=out), a.iters, a.warmup, flush)
@@ -142,8 +149,10 @@ def bench_gemm_layer(a) -> dict:
 def bench_tp_layer(a) -> dict:
     """The eight fused tensor-parallel GEMMs of one decoder layer (run under torchrun, one rank per GPU): all-gather->GEMM
     for the column-parallel products, GEMM->reduce-scatter for the row-parallel ones, each sustained, next to (a) the
-    same product as a plain local GEMM without communication (the compute floor of this kernel family) and (b) the
-    library pair NCCL collective + cuBLAS.  Times are the maximum over ranks."""
+    same product as a plain local GEMM without communication (the compute floor of this kernel family), (b) the bare
+    library pair NCCL collective + cuBLAS (no LoRA term, no element-wise work) and (c) library calls that compute what the
+    fused kernel computes (both gathers, LoRA as ``addmm_``, SwiGLU forward / backward as eager tensor ops, residual
+    add).  Times are the maximum over ranks."""
     import os
 
     import torch.distributed as dist
@@ -204,8 +213,26 @@ def bench_tp_layer(a) -> dict:
         ms_f = sustained(fused)
         ms_l = sustained(lambda: gemm_tn(x_full, w, a2=t_full, b2=b2, out=out, **kw))
         ms_u = sustained(lambda: unfused_ag_gemm(x_shard, w))
+
+        def library_same_math():
+            # what the fused kernel computes, from library calls: both gathers, the LoRA term, the element-wise pass
+            y = unfused_ag_gemm(x_shard, w)
+            t_all = torch.empty(M, 64, device=dev, dtype=bf)
+            dist.all_gather_into_tensor(t_all, t_shard)
+            y.addmm_(t_all, b2.t())
+            if epi == "swiglu":
+                return torch.nn.functional.silu(y[:, : N // 2]) * y[:, N // 2:]
+            if epi == "swiglu_bwd":
+                gu = kw["swiglu_bwd_gu"]
+                g, u = gu[:, :N], gu[:, N:]
+                sg = torch.sigmoid(g)
+                return torch.cat([y * u * sg * (1 + g * (1 - sg)), y * g * sg], dim=1)
+            return y
+
+        ms_s = sustained(library_same_math)
         rows.append({"op": "ag_gemm", "gemm": name, "n": N, "k": d, "epilogue": epi, "fused_ms": round(ms_f, 4),
                      "fused_tflops": round(fl / ms_f / 1e9, 1), "local_gemm_ms": round(ms_l, 4), "nccl_cublas_ms": round(ms_u, 4),
+                     "library_same_math_ms": round(ms_s, 4),
                      "nvlink_mb_in": round((P - 1) * m_seg * (d + 64) * 2 / 1e6, 1)})
         del x_shard, w, b2, out, x_full, kw
     # GEMM -> reduce-scatter: N = d; name, local K
@@ -219,8 +246,17 @@ def bench_tp_layer(a) -> dict:
         ms_f = sustained(lambda: ctx.gemm_rs(x, w, a2=t, b2=b2, residual=res, out=out))
         ms_l = sustained(lambda: gemm_tn(x, w, a2=t, b2=b2, out=full))
         ms_u = sustained(lambda: unfused_gemm_rs(x, w).add_(res))
+
+        def library_same_math():
+            part = (x @ w.t()).addmm_(t, b2.t())
+            o = torch.empty(m_seg, d, device=dev, dtype=bf)
+            dist.reduce_scatter_tensor(o, part)
+            return o.add_(res)
+
+        ms_s = sustained(library_same_math)
         rows.append({"op": "gemm_rs", "gemm": name, "n": d, "k": K, "fused_ms": round(ms_f, 4),
                      "fused_tflops": round(fl / ms_f / 1e9, 1), "local_gemm_ms": round(ms_l, 4), "nccl_cublas_ms": round(ms_u, 4),
+                     "library_same_math_ms": round(ms_s, 4),
                      "nvlink_mb_out": round((P - 1) * m_seg * d * 2 / 1e6, 1)})
         del x, w, t, b2, res, out, full
     torch.cuda.synchronize()
@@ -228,7 +264,8 @@ def bench_tp_layer(a) -> dict:
     ctx.close()
     res = {"op": "tp_layer", "model": cfg.name, "tokens": M, "tp": P, "fused_layer_ms": round(sum(r["fused_ms"] for r in rows), 3),
            "local_gemm_layer_ms": round(sum(r["local_gemm_ms"] for r in rows), 3),
-           "nccl_cublas_layer_ms": round(sum(r["nccl_cublas_ms"] for r in rows), 3), "gemms": rows}
+           "nccl_cublas_layer_ms": round(sum(r["nccl_cublas_ms"] for r in rows), 3),
+           "library_same_math_layer_ms": round(sum(r["library_same_math_ms"] for r in rows), 3), "gemms": rows}
     dist.barrier()
     dist.destroy_process_group()
     return res if rank == 0 else {}
@@ -358,6 +395,7 @@ def main() -> None:
     g.add_argument("--k", type=int, default=3584)
     g.add_argument("--bn", type=int, default=0)
     g.add_argument("--two-cta", type=int, default=-1, help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
+    g.add_argument("--epilogue", default="plain", choices=["plain", "resid", "swiglu", "swiglu_bwd"])
     t = sub.add_parser("attn")
     t.add_argument("--rows", type=int, default=4)
     t.add_argument("--seq", type=int, default=2048)

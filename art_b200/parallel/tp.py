@@ -82,7 +82,7 @@ class TPContext:
             self.off_stage.append(off)
             off = _align(off + max(self.world - 1, 1) * m_seg * n_max * 2)
         self.off_rs_flag = off
-        off = _align(off + max(self.world - 1, 1) * self.tile_cap * 16)
+        off = _align(off + max(self.world - 1, 1) * self.tile_cap * 32)    # 8 epilogue warps per tile, one flag each
         self.off_rs_done = off
         off = _align(off + 64)
         self.buf = SymmetricBuffer(off, self.device, group)
