@@ -19,7 +19,7 @@
 // src/art/local/train.py:245-281 and the loss arithmetic at src/art/local/train.py:112-151.
 #include <math.h>
 
-#include "gemm_pipeline.cuh"
+#include "gemm_pipeline_2cta.cuh"
 #include "host_utils.h"
 #include "sampling.cuh"
 
@@ -323,32 +323,52 @@ __global__ void grpo_token_kernel(const float* __restrict__ partials, int splits
   }
 }
 
+// From this many token rows on, the LM-head kernels run on CTA pairs (256 x 256 logit tiles, the pair shares each
+// LM-head tile in shared memory); below it (decode batches) one CTA per 128 x 256 tile fills the machine better.
+static bool lp_pairs(int M) { return M >= 4 * GEMM_BM; }
+
 template <class Epi>
 static int launch_lp(const void* H, int ldh, const void* W, int ldw, int M, int V, int K, int splits,
                      const Epi& epi, int* status, cudaStream_t stream) {
-  using L = GemmSmemLayout<LP_BN, LP_STAGES>;
-  auto kern = gemm_tcgen05_kernel<LP_BN, LP_STAGES, SchedVocabSplit, Epi>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured[dev & 63] = true;
-  }
   CUtensorMap tA, tB;
   int e;
-  if ((e = make_tmap_bf16_2d(&tA, H, M, K, ldh, GEMM_BM, GEMM_BK))) return e;
-  if ((e = make_tmap_bf16_2d(&tB, W, V, K, ldw, LP_BN, GEMM_BK))) return e;
+  int dev = 0;
+  cudaGetDevice(&dev);
   SchedVocabSplit sched;
-  sched.m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
   sched.n_tiles = (V + LP_BN - 1) / LP_BN;
   sched.splits = splits;
   sched.tiles_per_split = (sched.n_tiles + splits - 1) / splits;
+  const int kb = (K + GEMM_BK - 1) / GEMM_BK;
+  if ((e = make_tmap_bf16_2d(&tA, H, M, K, ldh, GEMM_BM, GEMM_BK))) return e;
+  if (lp_pairs(M)) {
+    using L = Gemm2SmemLayout<6, LP_BN>;
+    auto kern = gemm_tcgen05_2cta_kernel<6, LP_BN, SchedVocabSplit, Epi>;
+    static bool configured[64] = {false};
+    if (!configured[dev & 63]) {
+      cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+      if (ce != cudaSuccess) return static_cast<int>(ce);
+      configured[dev & 63] = true;
+    }
+    if ((e = make_tmap_bf16_2d(&tB, W, V, K, ldw, LP_BN / 2, GEMM_BK))) return e;
+    sched.m_tiles = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);      // pair tiles of 256 rows
+    int clusters = sched.m_tiles * splits;
+    if (clusters > sm_count() / 2) clusters = sm_count() / 2;
+    kern<<<2 * clusters, gemm_pipe_threads<Epi>(), L::TOTAL, stream>>>(tA, tB, tA, tB, kb, 0, sched, epi, status, NoComm{});
+    return static_cast<int>(cudaGetLastError());
+  }
+  using L = GemmSmemLayout<LP_BN, LP_STAGES>;
+  auto kern = gemm_tcgen05_kernel<LP_BN, LP_STAGES, SchedVocabSplit, Epi>;
+  static bool configured[64] = {false};
+  if (!configured[dev & 63]) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    configured[dev & 63] = true;
+  }
+  if ((e = make_tmap_bf16_2d(&tB, W, V, K, ldw, LP_BN, GEMM_BK))) return e;
+  sched.m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
   int grid = sched.m_tiles * splits;
   if (grid > sm_count()) grid = sm_count();
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, (K + GEMM_BK - 1) / GEMM_BK, 0, sched, epi,
-                                                 status, NoComm{});
+  kern<<<grid, gemm_pipe_threads<Epi>(), L::TOTAL, stream>>>(tA, tB, tA, tB, kb, 0, sched, epi, status, NoComm{});
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -359,9 +379,11 @@ using namespace artb;
 // Number of vocabulary splits the forward uses for (M, V): enough (m_blk, split) items to
 // fill the machine, never more splits than n-tiles.  The partials buffer is [splits, M, 4] fp32.
 ARTB_EXPORT int artb_logprob_splits(int M, int V) {
-  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  const bool pairs = lp_pairs(M);
+  const int m_tiles = pairs ? (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM) : (M + GEMM_BM - 1) / GEMM_BM;
   const int n_tiles = (V + LP_BN - 1) / LP_BN;
-  int splits = (2 * sm_count() + m_tiles - 1) / m_tiles;
+  const int workers = pairs ? sm_count() / 2 : sm_count();
+  int splits = (2 * workers + m_tiles - 1) / m_tiles;
   if (splits < 1) splits = 1;
   if (splits > n_tiles) splits = n_tiles;
   // make the last split non-empty

@@ -48,10 +48,10 @@ def tree_ids(rows, S, seg):
     return gid.reshape(-1).to(DEV), pid.reshape(-1).to(DEV)
 
 
-def test_fused_logprob_grpo_loss_fwd_bwd():
+@pytest.mark.parametrize("M,K,V", [(333, 256, 5000), (1100, 192, 9000)])     # one CTA per tile; CTA pairs (M >= 512)
+def test_fused_logprob_grpo_loss_fwd_bwd(M, K, V):
     from art_b200.ops import logprob_loss as lpl
 
-    M, K, V = 333, 256, 5000
     h = bf(M, K, seed=1)
     w = bf(V, K, scale=0.08, seed=2)
     wt = torch.zeros(K, (V + 7) // 8 * 8, dtype=torch.bfloat16, device=DEV)
