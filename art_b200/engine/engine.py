@@ -44,6 +44,7 @@ class SamplingParams:
     presence_penalty: float = 0.0          # subtracted once for every token already generated
     frequency_penalty: float = 0.0         # subtracted per occurrence in the output
     logit_bias: dict[int, float] | None = None
+    stream_events: bool = True             # False: only the final event is delivered (see Engine.complete)
 
     @property
     def needs_logits(self) -> bool:
@@ -96,6 +97,12 @@ class Sequence:
                        len(self.output_ids), self.params.top_p, self.params.top_k, self.params.min_p, self.proc)
 
 
+def _deliver(per_queue: dict) -> None:
+    """Runs on the event loop: hands every sequence the token events of one scheduler step."""
+    for q, events in per_queue.items():
+        q.put_nowait(events)
+
+
 @dataclass
 class EngineStats:
     prompt_tokens: int = 0
@@ -122,6 +129,7 @@ class Engine:
         self.n_steps, self.max_model_len = max(1, num_scheduler_steps), max_model_len
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
+        self._outbox: dict = {}     # event loop -> {queue: [TokenEvent, ...]} of the scheduler step in progress
         self.score_queue: deque = deque()
         self.adapters: dict[str, int] = {}
         self.adapter_version = [0] * max_loras
@@ -254,12 +262,32 @@ class Engine:
         seq = self.add_request(prompt_ids, params, adapter_name, asyncio.get_running_loop())
         try:
             while True:
-                ev = await seq.queue.get()
-                if isinstance(ev, BaseException):
-                    raise ev
-                yield ev
-                if ev.finished:
-                    return
+                item = await seq.queue.get()
+                if isinstance(item, BaseException):
+                    raise item
+                for ev in (item if isinstance(item, list) else (item,)):     # one list per scheduler step
+                    yield ev
+                    if ev.finished:
+                        return
+        finally:
+            if not seq.finished:
+                self.abort(seq)
+
+    async def complete(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None) -> Sequence:
+        """Runs one request to its end and returns its sequence (``output_ids``, ``logprobs``, ``top_logprobs``,
+        ``finish_reason``).  No per-token events cross threads: a non-streaming HTTP request costs the event loop one
+        wake-up instead of one per token.  Cancelling the caller aborts the request."""
+        import dataclasses
+
+        seq = self.add_request(prompt_ids, dataclasses.replace(params, stream_events=False), adapter_name,
+                               asyncio.get_running_loop())
+        try:
+            while True:
+                item = await seq.queue.get()
+                if isinstance(item, BaseException):
+                    raise item
+                if seq.finished:
+                    return seq
         finally:
             if not seq.finished:
                 self.abort(seq)
@@ -302,9 +330,17 @@ class Engine:
             reason = "length"
         if reason:
             seq.finished, seq.finish_reason = True, reason
-        ev = TokenEvent(tok, lp, seq.finished, reason, top)
-        if seq.loop is not None:
-            seq.loop.call_soon_threadsafe(seq.queue.put_nowait, ev)
+        if seq.loop is not None and (p.stream_events or seq.finished):
+            # delivered by _flush_events at the end of the scheduler step: one wake-up of the event loop per step and
+            # one queue item per sequence, however many sequences and decode steps the step covered
+            self._outbox.setdefault(seq.loop, {}).setdefault(seq.queue, []).append(TokenEvent(tok, lp, seq.finished, reason, top))
+
+    def _flush_events(self) -> None:
+        if not self._outbox:
+            return
+        outbox, self._outbox = self._outbox, {}
+        for loop, per_queue in outbox.items():
+            loop.call_soon_threadsafe(_deliver, per_queue)
 
     def _release(self, seq: Sequence) -> None:
         if seq.blocks:
@@ -405,6 +441,12 @@ class Engine:
 
     def step(self) -> bool:
         """One scheduler iteration.  Returns False when there was nothing to do."""
+        try:
+            return self._step()
+        finally:
+            self._flush_events()
+
+    def _step(self) -> bool:
         while self.score_queue:
             with self._lock:
                 toks, n_prompt, adapter, loop, fut = self.score_queue.popleft()

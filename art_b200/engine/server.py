@@ -313,6 +313,12 @@ class OpenAIServer:
     async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter):
 
         async def one(i: int):
+            if not params.guided_choice and not params.stop and hasattr(self.engine, "complete"):
+                # nothing has to look at the tokens on their way: let the engine run the request to its end
+                seq_params = SamplingParams(**{**params.__dict__, "n": 1,
+                                               "seed": None if params.seed is None else params.seed + i})
+                seq = await self.engine.complete(prompt_ids, seq_params, adapter)
+                return list(seq.output_ids), list(seq.logprobs), seq.finish_reason or "stop", list(seq.top_logprobs)
             ids, lps, tops, reason = [], [], [], "stop"
             async for _, tid, lp, fin, why, top in self._run_one(prompt_ids, params, adapter, i):
                 if tid is not None:

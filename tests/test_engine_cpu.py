@@ -129,6 +129,43 @@ def test_async_stream_pause_resume_and_abort(tiny):
         eng.shutdown()
 
 
+def test_complete_matches_the_token_stream_and_batches_events(tiny):
+    """``Engine.complete`` returns the same tokens as the event stream; a multi-step decode hands a sequence its events
+    of one scheduler step as one queue item."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=4)
+    eng.start()
+    p = SamplingParams(max_tokens=9, temperature=1.0, seed=11)
+
+    async def main():
+        streamed = [ev.token_id async for ev in eng.generate([1, 2, 3], p)]
+        seq = await eng.complete([1, 2, 3], p)
+        assert seq.output_ids == streamed and seq.finish_reason == "length" and len(seq.logprobs) == 9
+        # per step, not per token: the first item is the prefill's token, later items hold up to four events
+        s2 = eng.add_request([1, 2, 3], p, None, asyncio.get_running_loop())
+        sizes = []
+        while not (sizes and s2.finished and s2.queue.empty()):
+            item = await s2.queue.get()
+            sizes.append(len(item))
+        assert sum(sizes) == 9 and max(sizes) > 1 and len(sizes) < 9
+        # a cancelled caller aborts its request
+        t = asyncio.ensure_future(eng.complete([7, 8, 9], SamplingParams(max_tokens=100000, temperature=0.0)))
+        await asyncio.sleep(0.3)
+        t.cancel()
+        await asyncio.sleep(0.3)
+
+    try:
+        asyncio.run(main())
+        import time
+        for _ in range(100):
+            if not eng.has_unfinished:
+                break
+            time.sleep(0.05)
+        assert not eng.has_unfinished
+    finally:
+        eng.shutdown()
+
+
 def test_top_k_top_p_restrict_the_support(tiny):
     from art_b200.ops.paged import reference_restrict
 
