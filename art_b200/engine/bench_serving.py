@@ -69,7 +69,7 @@ async def run(base_model: str, architecture: dict | None = None, concurrency: in
     model = art.TrainableModel(name="benchmark", project="benchmark-serving", base_model=base_model,
                                _internal_config={"init_args": init_args, "engine_args": dict(engine_args or {})})
     backend = LocalBackend(in_process=in_process, path=path or tempfile.mkdtemp(prefix="art-bench-serving-"))
-    durations, results = [], []
+    durations, results, engine_metrics = [], [], {}
     try:
         await model.register(backend)
         client = model.openai_client()
@@ -93,6 +93,16 @@ async def run(base_model: str, architecture: dict | None = None, concurrency: in
                                          for _ in range(concurrency)])
             durations.append(time.perf_counter() - t0)
             results += res
+        try:      # where the engine's time went: inside the runner (device work) or in the scheduler around it
+            import httpx
+
+            async with httpx.AsyncClient(timeout=60) as hc:
+                url = str(client.base_url).rstrip("/").removesuffix("/v1") + "/metrics"
+                em = (await hc.get(url, params={"format": "json"})).json()
+            engine_metrics = {k: em[k] for k in ("decode_steps", "prefill_steps", "runner_seconds", "step_seconds", "preemptions",
+                                                 "kv_total_blocks") if k in em}
+        except Exception:  # noqa: BLE001 - the metrics are a diagnostic, not the measurement
+            engine_metrics = {}
         await client.close()
     finally:
         for s in getattr(backend, "_services", {}).values():
@@ -107,6 +117,8 @@ async def run(base_model: str, architecture: dict | None = None, concurrency: in
            "requests_per_s": round(len(results) / total, 2), "avg_prompt_tokens": round(prom / max(1, len(results)), 1),
            "avg_completion_tokens": round(comp / max(1, len(results)), 1),
            "completion_tokens_per_s": round(comp / total, 1), "total_tokens_per_s": round((comp + prom) / total, 1)}
+    if engine_metrics:
+        out["engine"] = engine_metrics
     ttft = [r["ttft"] for r in results if r["ttft"] is not None]
     if ttft:
         out["ttft_s"] = _stats(ttft)
@@ -124,6 +136,9 @@ def main() -> None:
     ap.add_argument("--max-tokens", type=int, default=1000)
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--stream", action="store_true", help="stream the answers and report the time to the first token")
+    ap.add_argument("--server-process", action="store_true",
+                    help="run the model service (engine + HTTP server) in a child process, as a deployment would; "
+                         "by default it shares this process, and its interpreter lock, with the 800 client coroutines")
     ap.add_argument("--max-num-seqs", type=int, default=512)
     ap.add_argument("--max-model-len", type=int, default=8192)
     a = ap.parse_args()
@@ -132,7 +147,8 @@ def main() -> None:
     base = a.model if os.path.isdir(a.model) else f"random:{a.model}"
     res = asyncio.run(run(base, None, a.concurrency, a.iterations, a.prompt_repeats, a.prompt_tokens, a.max_tokens,
                           a.temperature, a.stream,
-                          engine_args={"max_num_seqs": a.max_num_seqs, "max_model_len": a.max_model_len}))
+                          engine_args={"max_num_seqs": a.max_num_seqs, "max_model_len": a.max_model_len},
+                          in_process=not a.server_process))
     print(json.dumps(res))
 
 

@@ -68,6 +68,7 @@ class Sequence:
         self.id = next(Sequence._ids)
         self.prompt_ids = list(prompt_ids)
         self.output_ids: list[int] = []
+        self._tokens: list[int] = list(prompt_ids)     # prompt + output, grown in place (read-only for everyone else)
         self.logprobs: list[float] = []
         self.params = params
         self.adapter = adapter
@@ -90,7 +91,9 @@ class Sequence:
 
     @property
     def tokens(self) -> list[int]:
-        return self.prompt_ids + self.output_ids
+        """Prompt followed by the tokens generated so far: one list that grows in place (the scheduler asks for it
+        several times per sequence and step; callers must not modify it)."""
+        return self._tokens
 
     def view(self) -> SeqView:
         return SeqView(self.tokens, self.num_cached, self.blocks, self.adapter, self.params.temperature, self.seed,
@@ -110,6 +113,8 @@ class EngineStats:
     prefill_steps: int = 0
     decode_steps: int = 0
     preemptions: int = 0
+    runner_s: float = 0.0       # wall time inside runner.prefill / runner.decode (device work + its host staging)
+    step_s: float = 0.0         # wall time of scheduler steps that did work (runner time included)
     started: float = field(default_factory=time.monotonic)
 
 
@@ -317,6 +322,7 @@ class Engine:
     # -- scheduling -------------------------------------------------------------------------------
     def _emit(self, seq: Sequence, tok: int, lp: float, top=None) -> None:
         seq.output_ids.append(tok)
+        seq._tokens.append(tok)
         seq.logprobs.append(lp)
         seq.top_logprobs.append(top)
         self.stats.generated_tokens += 1
@@ -441,10 +447,15 @@ class Engine:
 
     def step(self) -> bool:
         """One scheduler iteration.  Returns False when there was nothing to do."""
+        t0 = time.monotonic()
+        worked = False
         try:
-            return self._step()
+            worked = self._step()
+            return worked
         finally:
             self._flush_events()
+            if worked:
+                self.stats.step_s += time.monotonic() - t0
 
     def _step(self) -> bool:
         while self.score_queue:
@@ -476,7 +487,9 @@ class Engine:
                 v = s.view()
                 v.upto = upto
                 views.append(v)
+            t0 = time.monotonic()
             toks, lps = self.runner.prefill(views)
+            self.stats.runner_s += time.monotonic() - t0
             tops = getattr(self.runner, "last_top_logprobs", None)
             for i, (s, upto) in enumerate(work):
                 if upto < len(s.tokens):                # more chunks to come: the KV so far stays in its blocks
@@ -502,7 +515,9 @@ class Engine:
         if any(s.forced or s.proc is not None for s in self.running):
             steps = 1      # the next step's input (forced token, penalties) depends on the host
         self.stats.decode_steps += steps
+        t0 = time.monotonic()
         toks, lps = self.runner.decode([s.view() for s in self.running], steps)
+        self.stats.runner_s += time.monotonic() - t0
         tops = getattr(self.runner, "last_top_logprobs", None)
         for k in range(steps):
             for i, s in enumerate(self.running):
@@ -567,4 +582,6 @@ class Engine:
         return {"running": len(self.running), "waiting": len(self.waiting), "prompt_tokens": self.stats.prompt_tokens,
                 "generated_tokens": self.stats.generated_tokens, "preemptions": self.stats.preemptions,
                 "kv_free_blocks": self.bm.num_free, "kv_total_blocks": self.bm.num_blocks,
-                "kv_utilisation": 1.0 - self.bm.num_free / self.bm.num_blocks, "tokens_per_s": self.stats.generated_tokens / dt, **st}
+                "kv_utilisation": 1.0 - self.bm.num_free / self.bm.num_blocks, "tokens_per_s": self.stats.generated_tokens / dt,
+                "decode_steps": self.stats.decode_steps, "prefill_steps": self.stats.prefill_steps,
+                "runner_seconds": round(self.stats.runner_s, 3), "step_seconds": round(self.stats.step_s, 3), **st}

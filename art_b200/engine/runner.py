@@ -700,24 +700,44 @@ class NativeRunner:
         while max_blocks < need_blocks:
             max_blocks *= 2
         st = self._decode_state(nb, max_blocks, n_steps)
+        import numpy as np
+
         lens = [len(s.tokens) for s in seqs]
         pad = nb - n
-        bt = torch.zeros((nb, max_blocks), dtype=torch.int32)
+        # host-side staging with numpy: one array per input instead of one small tensor per sequence
+        bt = np.zeros((nb, max_blocks), dtype=np.int32)
         for i, s in enumerate(seqs):
-            bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
-        st["bt"].copy_(bt, non_blocking=True)
-        st["tokens"].copy_(torch.tensor([s.tokens[-1] for s in seqs] + [0] * pad, dtype=torch.int64), non_blocking=True)
-        st["pos"].copy_(torch.tensor([l - 1 for l in lens] + [0] * pad, dtype=torch.int32), non_blocking=True)
-        st["ctx"].copy_(torch.tensor(lens + [0] * pad, dtype=torch.int32), non_blocking=True)
-        st["slot"].copy_(torch.tensor([s.blocks[(l - 1) // bs] * bs + (l - 1) % bs for s, l in zip(seqs, lens)] + [-1] * pad,
-                                      dtype=torch.int32), non_blocking=True)
-        st["ad"].copy_(torch.tensor([s.adapter for s in seqs] + [-1] * pad, dtype=torch.int32), non_blocking=True)
-        st["active"].copy_(torch.tensor([1] * n + [0] * pad, dtype=torch.int32), non_blocking=True)
-        st["inv_t"].copy_(torch.tensor([0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs] + [0.0] * pad,
-                                       dtype=torch.float32), non_blocking=True)
-        seeds = torch.tensor([[_mix_seed(s.seed, s.step + k) for s in seqs] + [0] * pad for k in range(n_steps)],
-                             dtype=torch.int64).to(torch.int32)
-        st["seeds"].copy_(seeds, non_blocking=True)
+            bt[i, :len(s.blocks)] = s.blocks
+        la = np.zeros(nb, dtype=np.int64)
+        la[:n] = lens
+        last = np.zeros(nb, dtype=np.int64)
+        last[:n] = [s.tokens[-1] for s in seqs]
+        slot = np.full(nb, -1, dtype=np.int32)
+        rows = np.arange(n)
+        slot[:n] = bt[rows, (la[:n] - 1) // bs] * bs + (la[:n] - 1) % bs
+        ad = np.full(nb, -1, dtype=np.int32)
+        ad[:n] = [s.adapter for s in seqs]
+        act = np.zeros(nb, dtype=np.int32)
+        act[:n] = 1
+        inv_t = np.zeros(nb, dtype=np.float32)
+        inv_t[:n] = [0.0 if s.temperature <= 0 else 1.0 / s.temperature for s in seqs]
+        # _mix_seed(seed, step + k) for every sequence and step, in 64-bit arithmetic
+        sd = np.zeros((1, nb), dtype=np.uint64)
+        sd[0, :n] = [s.seed & 0xFFFFFFFF for s in seqs]
+        stp = np.zeros((1, nb), dtype=np.uint64)
+        stp[0, :n] = [s.step for s in seqs]
+        ks = np.arange(n_steps, dtype=np.uint64)[:, None]
+        seeds = (sd * np.uint64(0x9E3779B1) + (stp + ks) * np.uint64(0x85EBCA77) + np.uint64(0x165667B1)) & np.uint64(0xFFFFFFFF)
+        seeds[:, n:] = 0
+        st["bt"].copy_(torch.from_numpy(bt), non_blocking=True)
+        st["tokens"].copy_(torch.from_numpy(last), non_blocking=True)
+        st["pos"].copy_(torch.from_numpy((la - 1).clip(min=0).astype(np.int32)), non_blocking=True)
+        st["ctx"].copy_(torch.from_numpy(la.astype(np.int32)), non_blocking=True)
+        st["slot"].copy_(torch.from_numpy(slot), non_blocking=True)
+        st["ad"].copy_(torch.from_numpy(ad), non_blocking=True)
+        st["active"].copy_(torch.from_numpy(act), non_blocking=True)
+        st["inv_t"].copy_(torch.from_numpy(inv_t), non_blocking=True)
+        st["seeds"].copy_(torch.from_numpy(seeds.astype(np.int64)).to(torch.int32), non_blocking=True)
         any_lora = any(s.adapter >= 0 for s in seqs)
         procs = None
         if any(s.proc is not None for s in seqs):
