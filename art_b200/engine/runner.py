@@ -199,6 +199,7 @@ class EngineLinear:
         self.W = self.W_ext[:N]
         self.A_all = self.W_ext[N:]
         self.B_all = torch.zeros(N, self.kpad, dtype=torch.bfloat16, device=W.device)
+        self.B_T = torch.zeros(self.kpad, N, dtype=torch.bfloat16, device=W.device)    # same values, transposed (decode)
         self.bias_ext = None
         if lin.bias is not None:
             self.bias_ext = torch.zeros(N + self.kpad, dtype=torch.float32, device=W.device)
@@ -209,6 +210,7 @@ class EngineLinear:
         c0 = slot * self.cols
         self.A_all[c0:c0 + self.cols].zero_()
         self.B_all[:, c0:c0 + self.cols].zero_()
+        self.B_T[c0:c0 + self.cols].zero_()
         if state is None:
             return
         for j, member in enumerate(self.members):
@@ -225,12 +227,27 @@ class EngineLinear:
             c = c0 + j * self.r
             self.A_all[c:c + self.r] = a           # device-to-device copy straight from the trainer's master buffer
             self.B_all[rows, c:c + self.r] = (b * scale).to(torch.bfloat16)
+            self.B_T[c:c + self.r, rows] = (b * scale).to(torch.bfloat16).t()
 
     def _ws(self, M: int, N: int, device) -> torch.Tensor:
         ws = self.ws_holder.get("ws")
         if ws is None or ws.shape[0] < M or ws.shape[1] < N:
             ws = torch.zeros((max(M, 512), max(N, 40960)), dtype=torch.float32, device=device)
             self.ws_holder["ws"] = ws
+        return ws
+
+    def partial_sums(self, x, any_lora: bool) -> torch.Tensor:
+        """Decode-time product left as fp32 partial sums in the shared workspace: columns ``[0, N)`` hold ``X W^T`` and,
+        with ``any_lora``, columns ``[N, N + kpad)`` the stacked shrink products ``X A_all^T``.  The fused consumers
+        (``ops.paged.decode_finalize_norm`` / ``decode_finalize_qkv``) finish the projection and re-zero the columns."""
+        from ..ops.gemm import gemm_splitk_, plan_small_m
+
+        M, N = x.shape[0], self.N
+        Next = N + self.kpad if any_lora else N
+        pair = TWO_CTA_DECODE and M % 256 == 0 and N >= 256
+        bn, splits = plan_small_m(M, Next, self.K, pair=pair)
+        ws = self._ws(M, Next, x.device)
+        gemm_splitk_(ws, x, self.W_ext[:Next], bn, splits, two_cta=pair)
         return ws
 
     def _shrink(self, x, adapter_ids):
@@ -665,6 +682,7 @@ class NativeRunner:
                 "out_t": torch.zeros((n_steps, nb), dtype=torch.int32, device=dev),
                 "out_l": torch.zeros((n_steps, nb), dtype=torch.float32, device=dev),
                 "attn_out": torch.zeros((nb, cfg.q_size), dtype=torch.bfloat16, device=dev),
+                "q": torch.zeros((nb, cfg.q_size), dtype=torch.bfloat16, device=dev),
             }
             self._dstate[key] = st
         return st
@@ -675,21 +693,68 @@ class NativeRunner:
 
         cfg, bs = self.cfg, self.kv.shape[1]
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        fused = self._fused_decode_ok(st["tokens"].shape[0])
         for k in range(n_steps):
             x = ew.gather_rows(self.embed, st["tokens"])
-            for li, L in enumerate(self.layers):
-                qkv = self._qkv(L, x, st["pos"], st["ad"], any_lora)
-                paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, st["slot"], self.kv.k[li], self.kv.v[li])
-                paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], st["bt"], st["ctx"], Hq, Hkv, hd, st["attn_out"], splits, ws)
-                x2 = self._reduce(L["o"](st["attn_out"], st["ad"], any_lora, residual=self._res(x)))
-                x = self._mlp(L, x2, st["ad"], any_lora)
-            hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
+            if fused:
+                # every split projection stays in the fp32 workspace until ONE kernel finishes it together with what
+                # follows it (RoPE + cache write, or the residual add + the next RMSNorm)
+                h, _ = ew.rmsnorm_fwd(x, self.layers[0]["ln1"], cfg.rms_norm_eps, want_rstd=False)
+                for li, L in enumerate(self.layers):
+                    nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else self.final_norm
+                    x, h = self._layer_decode_fused(li, L, x, h, nxt, st, any_lora, splits, ws)
+                hidden = h
+            else:
+                for li, L in enumerate(self.layers):
+                    qkv = self._qkv(L, x, st["pos"], st["ad"], any_lora)
+                    paged.kv_write(qkv, cfg.q_size, cfg.q_size + cfg.kv_size, st["slot"], self.kv.k[li], self.kv.v[li])
+                    paged.paged_decode(qkv, self.kv.k[li], self.kv.v[li], st["bt"], st["ctx"], Hq, Hkv, hd, st["attn_out"], splits, ws)
+                    x2 = self._reduce(L["o"](st["attn_out"], st["ad"], any_lora, residual=self._res(x)))
+                    x = self._mlp(L, x2, st["ad"], any_lora)
+                hidden, _ = ew.rmsnorm_fwd(x, self.final_norm, cfg.rms_norm_eps, want_rstd=False)
             t, lp = self._sample(hidden, st["inv_t"], st["seeds"][k], restricted, st["top_k"], st["top_p"], st["min_p"],
                                  procs=procs)
             st["out_t"][k].copy_(t)
             st["out_l"][k].copy_(lp)
             if k + 1 < n_steps:
                 paged.decode_advance(t, st["tokens"], st["pos"], st["ctx"], st["slot"], st["bt"], bs, st["active"])
+
+    def _fused_decode_ok(self, M: int) -> bool:
+        """The fused finish kernels cover one GPU per replica (a tensor-parallel replica all-reduces between the
+        projection and the norm), no per-head q/k norm, dense MLPs, and adapter slots of at most 64 shrink columns."""
+        if self.tp > 1 or self.cfg.qk_norm or M > 512 or os.environ.get("ARTB_DECODE_FUSED", "1") == "0":
+            return False
+        L = self.layers[0]
+        return all(isinstance(L.get(k), EngineLinear) and L[k].cols <= 64 for k in ("qkv", "o", "gu", "down"))
+
+    def _layer_decode_fused(self, li: int, L, x, h, next_norm, st, any_lora: bool, splits: int, ws):
+        from ..ops import paged
+
+        cfg = self.cfg
+        M, d = x.shape
+        Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        ad = st["ad"] if any_lora else None
+        lin = L["qkv"]
+        w = lin.partial_sums(h, any_lora)
+        paged.decode_finalize_qkv(w, M, Hq, Hkv, hd, lin.kpad, st["pos"], cfg.rope_theta, st["slot"], self.kv.k[li],
+                                  self.kv.v[li], st["q"], bias=None if lin.bias_ext is None else lin.bias_ext[:lin.N],
+                                  adapter=ad, B_all=lin.B_T, cols=lin.cols)
+        paged.paged_decode(st["q"], self.kv.k[li], self.kv.v[li], st["bt"], st["ctx"], Hq, Hkv, hd, st["attn_out"], splits, ws)
+        lin = L["o"]
+        w = lin.partial_sums(st["attn_out"], any_lora)
+        x2, h2 = torch.empty_like(x), torch.empty_like(x)
+        paged.decode_finalize_norm(w, M, d, lin.kpad, x2, bias=None if lin.bias_ext is None else lin.bias_ext[:d],
+                                   residual=x, adapter=ad, B_all=lin.B_T, cols=lin.cols, norm_w=L["ln2"],
+                                   eps=cfg.rms_norm_eps, h_out=h2)
+        hact = torch.empty((M, cfg.intermediate_size), dtype=x.dtype, device=x.device)
+        L["gu"](h2, st["ad"], any_lora, swiglu_out=hact)
+        lin = L["down"]
+        w = lin.partial_sums(hact, any_lora)
+        x3, h3 = torch.empty_like(x), torch.empty_like(x)
+        paged.decode_finalize_norm(w, M, d, lin.kpad, x3, bias=None if lin.bias_ext is None else lin.bias_ext[:d],
+                                   residual=x2, adapter=ad, B_all=lin.B_T, cols=lin.cols, norm_w=next_norm,
+                                   eps=cfg.rms_norm_eps, h_out=h3)
+        return x3, h3
 
     def decode(self, seqs: list[SeqView], n_steps: int, use_graph: bool = True) -> tuple[list[list[int]], list[list[float]]]:
         cfg, dev, bs = self.cfg, self.device, self.kv.shape[1]

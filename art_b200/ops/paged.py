@@ -21,6 +21,8 @@ _sigs = {
     "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
     "artb_logit_adjust": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp],
     "artb_top_logprobs": [vp, cl, vp, ci, ci, ci, vp, vp, vp],
+    "artb_decode_finalize_norm": [vp, ci, ci, ci, ci, vp, vp, ci, vp, vp, ci, ci, vp, ctypes.c_float, vp, ci, vp, ci, vp],
+    "artb_decode_finalize_qkv": [vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, ci, vp, ctypes.c_float, vp, vp, vp, vp, ci, vp],
 }
 _bound: dict[str, object] = {}
 
@@ -40,6 +42,33 @@ def kv_write(qkv: torch.Tensor, k_col: int, v_col: int, slot: torch.Tensor, k_ca
     kv_width = k_cache.shape[-2] * k_cache.shape[-1]
     _lib.check_rc(_f("artb_kv_write")(_lib.ptr(qkv), qkv.stride(0), k_col, v_col, _lib.ptr(slot), _lib.ptr(k_cache),
                                       _lib.ptr(v_cache), qkv.shape[0], kv_width, _lib.stream_ptr()), "kv_write")
+
+
+def decode_finalize_norm(ws: torch.Tensor, M: int, N: int, kpad: int, x_out: torch.Tensor, *, bias: torch.Tensor | None = None,
+                         residual: torch.Tensor | None = None, adapter: torch.Tensor | None = None,
+                         B_all: torch.Tensor | None = None, cols: int = 0, norm_w: torch.Tensor | None = None,
+                         eps: float = 1e-6, h_out: torch.Tensor | None = None) -> None:
+    """Finish a decode-time split-K projection whose fp32 partial sums sit in ``ws[:M, :N]`` (and, with ``adapter``, the
+    stacked LoRA shrink products in ``ws[:M, N:N+kpad]``; ``B_all`` is the scaled LoRA B transposed, [kpad, N]):
+    ``x_out = bf16(ws + bias + residual + T_slot sB_slot^T)``
+    and, with ``norm_w``, ``h_out = RMSNorm(x_out) * norm_w``.  The consumed workspace columns are left zero."""
+    _lib.check_rc(_f("artb_decode_finalize_norm")(
+        _lib.ptr(ws), ws.stride(0), M, N, kpad, _lib.ptr(bias), _lib.ptr(residual),
+        residual.stride(0) if residual is not None else 0, _lib.ptr(adapter), _lib.ptr(B_all),
+        B_all.stride(0) if B_all is not None else 0, cols, _lib.ptr(norm_w), eps, _lib.ptr(x_out), x_out.stride(0),
+        _lib.ptr(h_out), h_out.stride(0) if h_out is not None else 0, _lib.stream_ptr()), "decode_finalize_norm")
+
+
+def decode_finalize_qkv(ws: torch.Tensor, M: int, Hq: int, Hkv: int, hd: int, kpad: int, pos: torch.Tensor, theta: float,
+                        slot: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, *,
+                        bias: torch.Tensor | None = None, adapter: torch.Tensor | None = None,
+                        B_all: torch.Tensor | None = None, cols: int = 0) -> None:
+    """Finish the decode-time q|k|v projection from its split-K workspace: bias, LoRA expand of the row's adapter slot,
+    RoPE on q and k; q goes to ``q_out`` [M, Hq*hd], k and v straight into the paged cache at ``slot``."""
+    _lib.check_rc(_f("artb_decode_finalize_qkv")(
+        _lib.ptr(ws), ws.stride(0), M, Hq, Hkv, hd, kpad, _lib.ptr(bias), _lib.ptr(adapter), _lib.ptr(B_all),
+        B_all.stride(0) if B_all is not None else 0, cols, _lib.ptr(pos), theta, _lib.ptr(slot), _lib.ptr(k_cache),
+        _lib.ptr(v_cache), _lib.ptr(q_out), q_out.stride(0), _lib.stream_ptr()), "decode_finalize_qkv")
 
 
 def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table_row: torch.Tensor, block_size: int, n_tok: int,

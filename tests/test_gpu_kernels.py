@@ -291,3 +291,80 @@ def test_logit_edit_and_top_logprobs_kernels_match_pytorch():
     ti, tl = paged.top_logprobs(got, inv_t, 6)
     ri, rl = paged.top_logprobs(want, inv_t.cpu(), 6)
     assert torch.equal(ti.cpu(), ri) and torch.allclose(tl.cpu(), rl, atol=1e-4)
+
+
+@pytest.mark.parametrize("with_lora", [False, True])
+def test_decode_finalize_kernels_match_pytorch(with_lora):
+    """The fused finish of a decode-time split-K projection (bias + residual + LoRA expand of the row's slot + RMSNorm,
+    and bias + LoRA expand + RoPE + cache write for q|k|v) against plain fp32 tensor code."""
+    from art_b200.ops import paged
+
+    g = torch.Generator(device=DEV).manual_seed(5)
+    M, N, slots, cols = 40, 1536, 3, 16
+    kpad = 64
+    ldw = N + kpad + 24
+    ws = torch.randn(M, ldw, device=DEV, generator=g)
+    ws0 = ws.clone()
+    bias = torch.randn(N, device=DEV, generator=g)
+    R = bf(M, N, seed=1)
+    B_all = bf(kpad, N, scale=0.3, seed=2)          # scaled LoRA B, transposed: [shrink column, output feature]
+    adapter = torch.randint(-1, slots, (M,), device=DEV, generator=g, dtype=torch.int32)
+    nw = (1 + 0.1 * torch.randn(N, device=DEV, generator=g)).bfloat16()
+    x_out, h_out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16), torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    paged.decode_finalize_norm(ws, M, N, kpad, x_out, bias=bias, residual=R, adapter=adapter if with_lora else None,
+                               B_all=B_all if with_lora else None, cols=cols if with_lora else 0, norm_w=nw, eps=1e-6, h_out=h_out)
+
+    def lora_term(w0, n_main, bt):
+        out = torch.zeros(M, n_main, device=DEV)
+        if with_lora:
+            for m in range(M):
+                a = int(adapter[m])
+                if a >= 0:
+                    t = w0[m, n_main + a * cols:n_main + (a + 1) * cols]
+                    out[m] = t @ bt[a * cols:(a + 1) * cols].float()
+        return out
+
+    want = ws0[:, :N] + bias + R.float() + lora_term(ws0, N, B_all)
+    assert rel_err(x_out, want) < 5e-3
+    xr = x_out.float()
+    hn = (xr * torch.rsqrt((xr * xr).mean(-1, keepdim=True) + 1e-6)).bfloat16().float() * nw.float()
+    assert rel_err(h_out, hn) < 5e-3
+    assert float(ws[:, :N].abs().max()) == 0.0
+    if with_lora:
+        assert float(ws[:, N:N + kpad].abs().max()) == 0.0
+    assert torch.equal(ws[:, N + kpad:], ws0[:, N + kpad:])
+
+    # q|k|v
+    Hq, Hkv, hd, bs, blocks = 6, 2, 128, 16, 8
+    qs, kvs = Hq * hd, Hkv * hd
+    Nq = qs + 2 * kvs
+    ldw = Nq + kpad
+    ws = torch.randn(M, ldw, device=DEV, generator=g)
+    ws0 = ws.clone()
+    bias = torch.randn(Nq, device=DEV, generator=g)
+    B_all = bf(kpad, Nq, scale=0.3, seed=3)
+    pos = torch.randint(0, 5000, (M,), device=DEV, generator=g, dtype=torch.int32)
+    slot = torch.randperm(blocks * bs, device=DEV, generator=g)[:M].to(torch.int32)
+    slot[3] = -1
+    kc = torch.zeros(blocks, bs, Hkv, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(M, qs, device=DEV, dtype=torch.bfloat16)
+    paged.decode_finalize_qkv(ws, M, Hq, Hkv, hd, kpad, pos, 1e6, slot, kc, vc, q_out, bias=bias,
+                              adapter=adapter if with_lora else None, B_all=B_all if with_lora else None,
+                              cols=cols if with_lora else 0)
+    y = ws0[:, :Nq] + bias + lora_term(ws0, Nq, B_all)
+
+    def rope(t, heads):
+        t = t.view(M, heads, hd)
+        i = torch.arange(hd // 2, device=DEV, dtype=torch.float32)
+        ang = pos.float()[:, None] * torch.exp2(-torch.log2(torch.tensor(1e6)) * 2 * i / hd)[None]
+        c, s_ = ang.cos()[:, None], ang.sin()[:, None]
+        a, b = t[..., :hd // 2], t[..., hd // 2:]
+        return torch.cat([a * c - b * s_, b * c + a * s_], -1).reshape(M, heads * hd)
+
+    assert rel_err(q_out, rope(y[:, :qs], Hq)) < 5e-3
+    kw, vw = rope(y[:, qs:qs + kvs], Hkv), y[:, qs + kvs:]
+    ok = slot >= 0
+    assert rel_err(kc.view(-1, kvs)[slot[ok].long()], kw[ok]) < 5e-3
+    assert rel_err(vc.view(-1, kvs)[slot[ok].long()], vw[ok]) < 5e-3
+    assert float(ws[:, :Nq].abs().max()) == 0.0
