@@ -60,15 +60,60 @@ __device__ __forceinline__ void take8(float* w, float (&f)[8]) {
 }
 
 // f[e] += sum_j t[j] * Bt[j * ldb + n0 + e],  j < cols; `Bt` (the scaled LoRA B, transposed: one row per shrink column,
-// so that the threads of a warp read consecutive addresses) already points at the slot's first row
+// so that the threads of a warp read consecutive addresses) already points at the slot's first row.  The loads are
+// issued eight at a time before any of them is used: one at a time, a row of `cols` dependent L2 round trips was the
+// whole cost of these kernels.
 __device__ __forceinline__ void lora_expand8(float (&f)[8], const float* t, const __nv_bfloat16* Bt, int ldb, int n0, int cols) {
-  for (int j = 0; j < cols; ++j) {
-    float bv[8];
-    ld8(Bt + static_cast<size_t>(j) * ldb + n0, bv);
-    const float tj = t[j];
+  for (int j0 = 0; j0 < cols; j0 += 8) {
+    bf8 b[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = fmaf(tj, bv[e], f[e]);
+    for (int i = 0; i < 8; ++i)
+      if (j0 + i < cols) b[i] = *reinterpret_cast<const bf8*>(Bt + static_cast<size_t>(j0 + i) * ldb + n0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (j0 + i < cols) {
+        const float tj = t[j0 + i];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 v = __bfloat1622float2(b[i].v[e]);
+          f[2 * e] = fmaf(tj, v.x, f[2 * e]);
+          f[2 * e + 1] = fmaf(tj, v.y, f[2 * e + 1]);
+        }
+      }
   }
+}
+
+// the same for two 8-element pieces of one row (the two halves of a RoPE pair): four rows, i.e. eight loads, at a time
+__device__ __forceinline__ void lora_expand8x2(float (&f)[8], float (&g)[8], const float* t, const __nv_bfloat16* Bt, int ldb,
+                                               int n0, int n1, int cols) {
+  for (int j0 = 0; j0 < cols; j0 += 4) {
+    bf8 b[4], c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (j0 + i < cols) {
+        const __nv_bfloat16* r = Bt + static_cast<size_t>(j0 + i) * ldb;
+        b[i] = *reinterpret_cast<const bf8*>(r + n0);
+        c[i] = *reinterpret_cast<const bf8*>(r + n1);
+      }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (j0 + i < cols) {
+        const float tj = t[j0 + i];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 v = __bfloat1622float2(b[i].v[e]), w = __bfloat1622float2(c[i].v[e]);
+          f[2 * e] = fmaf(tj, v.x, f[2 * e]);
+          f[2 * e + 1] = fmaf(tj, v.y, f[2 * e + 1]);
+          g[2 * e] = fmaf(tj, w.x, g[2 * e]);
+          g[2 * e + 1] = fmaf(tj, w.y, g[2 * e + 1]);
+        }
+      }
+  }
+}
+
+__device__ __forceinline__ void add_bias8(float (&f)[8], const float* bias) {
+  const float4 a = *reinterpret_cast<const float4*>(bias), b = *reinterpret_cast<const float4*>(bias + 4);
+  f[0] += a.x, f[1] += a.y, f[2] += a.z, f[3] += a.w, f[4] += b.x, f[5] += b.y, f[6] += b.z, f[7] += b.w;
 }
 
 // One CTA per token row.  512 threads: a 3584-wide row is one 8-element vector per thread, so the row costs a handful of
@@ -83,7 +128,7 @@ __device__ __forceinline__ int stage_shrink(float* wrow, int N, int kpad, int co
   if (a >= 0 && static_cast<int>(threadIdx.x) < cols) t_s[threadIdx.x] = wrow[N + a * cols + threadIdx.x];
   __syncthreads();
   if (adapter)
-    for (int j = threadIdx.x * 4; j < kpad; j += DF_THREADS * 4)
+    for (int j = threadIdx.x * 4; j < kpad; j += blockDim.x * 4)
       *reinterpret_cast<float4*>(wrow + N + j) = make_float4(0.f, 0.f, 0.f, 0.f);
   return a;
 }
@@ -91,7 +136,7 @@ __device__ __forceinline__ int stage_shrink(float* wrow, int N, int kpad, int co
 }  // namespace
 
 template <int MAX_VEC>
-__global__ void __launch_bounds__(DF_THREADS)
+__global__ void __launch_bounds__(DF_THREADS, MAX_VEC == 1 ? 2 : 1)
 decode_finalize_norm_kernel(float* __restrict__ ws, int ldw, int N, int kpad, const float* __restrict__ bias,
                             const __nv_bfloat16* __restrict__ R, int ldr, const int* __restrict__ adapter,
                             const __nv_bfloat16* __restrict__ B_all, int ldb, int cols,
@@ -112,10 +157,7 @@ decode_finalize_norm_kernel(float* __restrict__ ws, int ldw, int N, int kpad, co
       const int n0 = v * 8;
       float f[8];
       take8(wrow + n0, f);
-      if (bias) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] += bias[n0 + e];
-      }
+      if (bias) add_bias8(f, bias + n0);
       if (R) {
         float r[8];
         ld8(R + static_cast<size_t>(row) * ldr + n0, r);
@@ -156,23 +198,30 @@ decode_finalize_norm_kernel(float* __restrict__ ws, int ldw, int N, int kpad, co
 
 // Columns of the workspace row: [ q: Hq heads | k: Hkv heads | v: Hkv heads | shrink: kpad ], heads of hd values.
 // Rotate-half RoPE: the pair is (i, i + hd/2) inside a head, angle pos * theta^(-2i/hd).
-__global__ void __launch_bounds__(DF_THREADS)
+// 256 threads, two CTAs per SM (128 registers each): the 320 (rope pair | v) units of a 7B row take two short passes
+constexpr int DQ_THREADS = 256;
+
+__global__ void __launch_bounds__(DQ_THREADS, 2)
 decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int hd, int kpad,
                            const float* __restrict__ bias, const int* __restrict__ adapter,
                            const __nv_bfloat16* __restrict__ B_all, int ldb, int cols, const int* __restrict__ pos,
                            float log2_theta, const int* __restrict__ slot, __nv_bfloat16* __restrict__ k_cache,
                            __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ q_out, int ldq) {
   __shared__ float t_s[DF_MAX_COLS];
+  __shared__ float cs_s[128], sn_s[128];     // cos / sin of the row's position for every frequency: shared by all heads
   const int row = blockIdx.x;
   const int q_size = Hq * hd, kv_size = Hkv * hd, N = q_size + 2 * kv_size;
   float* wrow = ws + static_cast<size_t>(row) * ldw;
-  const int a = stage_shrink(wrow, N, kpad, cols, adapter, row, t_s);
+  if (static_cast<int>(threadIdx.x) < (hd >> 1)) {
+    const float inv_freq = exp2f(-log2_theta * (2.f * threadIdx.x) / hd);
+    sincosf(static_cast<float>(pos[row]) * inv_freq, &sn_s[threadIdx.x], &cs_s[threadIdx.x]);
+  }
+  const int a = stage_shrink(wrow, N, kpad, cols, adapter, row, t_s);      // contains the block barrier
   const __nv_bfloat16* Bs = B_all + (a >= 0 ? static_cast<size_t>(a) * cols * ldb : 0);
   const int s = slot[row];
-  const float fp = static_cast<float>(pos[row]);
   const int half = hd >> 1, per_head = half >> 3;
   const int rope_units = (Hq + Hkv) * per_head, v_units = kv_size >> 3;
-  for (int u = threadIdx.x; u < rope_units + v_units; u += DF_THREADS) {
+  for (int u = threadIdx.x; u < rope_units + v_units; u += DQ_THREADS) {
     if (u < rope_units) {
       const int h = u / per_head, vv = u - h * per_head;
       const int c1 = h * hd + vv * 8, c2 = c1 + half;
@@ -180,22 +229,13 @@ decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int
       take8(wrow + c1, x1);
       take8(wrow + c2, x2);
       if (bias) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          x1[e] += bias[c1 + e];
-          x2[e] += bias[c2 + e];
-        }
+        add_bias8(x1, bias + c1);
+        add_bias8(x2, bias + c2);
       }
-      if (a >= 0) {
-        lora_expand8(x1, t_s, Bs, ldb, c1, cols);
-        lora_expand8(x2, t_s, Bs, ldb, c2, cols);
-      }
+      if (a >= 0) lora_expand8x2(x1, x2, t_s, Bs, ldb, c1, c2, cols);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const int i = vv * 8 + e;
-        const float inv_freq = exp2f(-log2_theta * (2.f * i) / hd);
-        float sn, cs;
-        sincosf(fp * inv_freq, &sn, &cs);
+        const float sn = sn_s[vv * 8 + e], cs = cs_s[vv * 8 + e];
         const float p = x1[e], q = x2[e];
         x1[e] = p * cs - q * sn;
         x2[e] = q * cs + p * sn;
@@ -213,10 +253,7 @@ decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int
       const int c = q_size + kv_size + (u - rope_units) * 8;
       float x[8];
       take8(wrow + c, x);
-      if (bias) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] += bias[c + e];
-      }
+      if (bias) add_bias8(x, bias + c);
       if (a >= 0) lora_expand8(x, t_s, Bs, ldb, c, cols);
       if (s >= 0) st8(v_cache + static_cast<size_t>(s) * kv_size + (c - q_size - kv_size), x);
     }
@@ -259,10 +296,10 @@ ARTB_EXPORT int artb_decode_finalize_qkv(float* ws, int ldw, int M, int Hq, int 
                                          float theta, const int* slot, void* k_cache, void* v_cache, void* q_out, int ldq,
                                          cudaStream_t st) {
   if (M <= 0) return 0;
-  if ((hd & 15) || (ldw & 3) || (ldq & 7) || Hq <= 0 || Hkv <= 0 || !pos || !slot) return ERR_BAD_SHAPE;
+  if ((hd & 15) || hd > 256 || (ldw & 3) || (ldq & 7) || Hq <= 0 || Hkv <= 0 || !pos || !slot) return ERR_BAD_SHAPE;
   if (adapter && (cols <= 0 || cols > DF_MAX_COLS || (kpad & 3) || (ldb & 7) || !B_all)) return ERR_BAD_SHAPE;
   if (reinterpret_cast<uintptr_t>(ws) & 15) return ERR_BAD_ALIGN;
-  decode_finalize_qkv_kernel<<<M, DF_THREADS, 0, st>>>(
+  decode_finalize_qkv_kernel<<<M, DQ_THREADS, 0, st>>>(
       ws, ldw, Hq, Hkv, hd, kpad, bias, adapter, reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, pos,
       log2f(theta), slot, reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
       reinterpret_cast<__nv_bfloat16*>(q_out), ldq);
