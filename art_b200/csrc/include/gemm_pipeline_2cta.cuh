@@ -120,6 +120,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_wait();                  // everything above overlapped the previous kernel's tail (when launched that way)
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)

@@ -56,6 +56,33 @@ inline int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t rows, u
   return r == CUDA_SUCCESS ? 0 : ERR_TMAP;
 }
 
+// Programmatic dependent launch.  While the switch is on (the rollout engine turns it on around its decode step), the
+// launchers below mark their kernels as allowed to start before the previous kernel of the stream has finished; every
+// such kernel executes `griddepcontrol.wait` (pdl_wait() in device code) before its first access to global memory, so
+// only its prologue (barrier / TMEM setup, descriptor prefetch, block scheduling) overlaps the predecessor's tail.  A
+// decode step is ~230 short launches whose hand-over gaps add up to a fifth of the step.  Kernels launched without
+// the attribute (everything while the switch is off, and all library kernels) keep full stream order.
+inline int& pdl_switch() {
+  static int on = 0;
+  return on;
+}
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_switch() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline int sm_count() {
   static int n[64] = {0};
   int dev = 0;

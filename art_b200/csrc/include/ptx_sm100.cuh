@@ -229,6 +229,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
          | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// Programmatic dependent launch: wait until the kernels this one depends on have completed and their writes are
+// visible (a no-op for a kernel launched in plain stream order), and let the next kernel of the stream begin its
+// own prologue.  Every kernel that can be launched with the attribute calls pdl_wait() before it touches global memory.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 1 / x with the hardware approximation (one MUFU instruction, about 1 ulp); an IEEE division is ~10 instructions
 // with a slow-path branch, which matters in epilogues that run one warp per scheduler.
 __device__ __forceinline__ float rcp_approx(float x) {

@@ -24,6 +24,7 @@
 #include <stdint.h>
 
 #include "host_utils.h"
+#include "ptx_sm100.cuh"
 
 namespace artb {
 
@@ -144,6 +145,8 @@ decode_finalize_norm_kernel(float* __restrict__ ws, int ldw, int N, int kpad, co
                             __nv_bfloat16* __restrict__ h_out, int ldh) {
   __shared__ float t_s[DF_MAX_COLS];
   __shared__ float red[DF_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   float* wrow = ws + static_cast<size_t>(row) * ldw;
   const int a = stage_shrink(wrow, N, kpad, cols, adapter, row, t_s);
@@ -209,6 +212,8 @@ decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int
                            __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ q_out, int ldq) {
   __shared__ float t_s[DF_MAX_COLS];
   __shared__ float cs_s[128], sn_s[128];     // cos / sin of the row's position for every frequency: shared by all heads
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const int q_size = Hq * hd, kv_size = Hkv * hd, N = q_size + 2 * kv_size;
   float* wrow = ws + static_cast<size_t>(row) * ldw;
@@ -279,15 +284,15 @@ ARTB_EXPORT int artb_decode_finalize_norm(float* ws, int ldw, int M, int N, int 
   if ((reinterpret_cast<uintptr_t>(ws) & 15) || ((N * 4) & 15)) return ERR_BAD_ALIGN;
   const int per = (N / 8 + DF_THREADS - 1) / DF_THREADS;
 #define ARTB_DF(V)                                                                                                      \
-  decode_finalize_norm_kernel<V><<<M, DF_THREADS, 0, st>>>(                                                             \
-      ws, ldw, N, kpad, bias, reinterpret_cast<const __nv_bfloat16*>(R), ldr, adapter,                                  \
-      reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, reinterpret_cast<const __nv_bfloat16*>(norm_w), eps,    \
-      reinterpret_cast<__nv_bfloat16*>(x_out), ldx, reinterpret_cast<__nv_bfloat16*>(h_out), ldh)
+  return static_cast<int>(launch_kernel(                                                                                \
+      decode_finalize_norm_kernel<V>, dim3(M), dim3(DF_THREADS), 0, st, ws, ldw, N, kpad, bias,                         \
+      reinterpret_cast<const __nv_bfloat16*>(R), ldr, adapter, reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, \
+      reinterpret_cast<const __nv_bfloat16*>(norm_w), eps, reinterpret_cast<__nv_bfloat16*>(x_out), ldx,                \
+      reinterpret_cast<__nv_bfloat16*>(h_out), ldh))
   if (per <= 1) ARTB_DF(1);
-  else if (per <= 2) ARTB_DF(2);
-  else ARTB_DF(4);
+  if (per <= 2) ARTB_DF(2);
+  ARTB_DF(4);
 #undef ARTB_DF
-  return static_cast<int>(cudaGetLastError());
 }
 
 // k_cache / v_cache: [slots, Hkv * hd] bf16 (slot = block * block_size + offset; slot[m] < 0: row not written).
@@ -299,9 +304,17 @@ ARTB_EXPORT int artb_decode_finalize_qkv(float* ws, int ldw, int M, int Hq, int 
   if ((hd & 15) || hd > 256 || (ldw & 3) || (ldq & 7) || Hq <= 0 || Hkv <= 0 || !pos || !slot) return ERR_BAD_SHAPE;
   if (adapter && (cols <= 0 || cols > DF_MAX_COLS || (kpad & 3) || (ldb & 7) || !B_all)) return ERR_BAD_SHAPE;
   if (reinterpret_cast<uintptr_t>(ws) & 15) return ERR_BAD_ALIGN;
-  decode_finalize_qkv_kernel<<<M, DQ_THREADS, 0, st>>>(
-      ws, ldw, Hq, Hkv, hd, kpad, bias, adapter, reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, pos,
-      log2f(theta), slot, reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
-      reinterpret_cast<__nv_bfloat16*>(q_out), ldq);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(
+      decode_finalize_qkv_kernel, dim3(M), dim3(DQ_THREADS), 0, st, ws, ldw, Hq, Hkv, hd, kpad, bias, adapter,
+      reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, pos, log2f(theta), slot,
+      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
+      reinterpret_cast<__nv_bfloat16*>(q_out), ldq));
+}
+
+// Programmatic dependent launch for the kernels of the decode step (see pdl_switch in host_utils.h); returns the
+// previous setting.  The engine turns it on around its decode body and off again afterwards.
+ARTB_EXPORT int artb_set_pdl(int on) {
+  const int prev = pdl_switch();
+  pdl_switch() = on ? 1 : 0;
+  return prev;
 }

@@ -36,8 +36,8 @@ static int launch_splitk(const CUtensorMap& tA, const CUtensorMap& tB, int kb_ma
   int grid = sched.m_tiles * sched.n_tiles * splits;
   if (grid > sm_count()) grid = sm_count();
   EpiAtomic<BN> epi{ws, ldw, M, N};
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, sched, epi, status, NoComm{});
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), L::TOTAL, stream, tA, tB, tA, tB, kb_main, 0,
+                                        sched, epi, status, NoComm{}));
 }
 
 // out = bf16(ws + bias + residual[:, :res_cols]); ws <- 0.
@@ -48,6 +48,8 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, int ldw, __nv_bfl
                                        const __nv_bfloat16* __restrict__ R, int ldr, int res_cols,
                                        const float* __restrict__ bias, int M, int N, const int* __restrict__ adapter,
                                        int mask_col0, int cols) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int vec = N >> 2;
   const long total = static_cast<long>(M) * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -113,8 +115,8 @@ ARTB_EXPORT int artb_splitk_finalize(float* ws, int ldw, void* out, int ldc, con
   long total = static_cast<long>(M) * (N / 4);
   long blocks = (total + 255) / 256;
   if (blocks > 148L * 8) blocks = 148L * 8;
-  splitk_finalize_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
-      ws, ldw, reinterpret_cast<__nv_bfloat16*>(out), ldc, reinterpret_cast<const __nv_bfloat16*>(R), ldr,
-      res_cols > 0 ? res_cols : N, bias, M, N, adapter, mask_col0, cols);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(splitk_finalize_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, ws,
+                                        ldw, reinterpret_cast<__nv_bfloat16*>(out), ldc,
+                                        reinterpret_cast<const __nv_bfloat16*>(R), ldr, res_cols > 0 ? res_cols : N,
+                                        bias, M, N, adapter, mask_col0, cols));
 }

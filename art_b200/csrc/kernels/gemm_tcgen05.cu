@@ -41,9 +41,8 @@ static int launch_gemm(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   int cap = sm_count();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
-  kern<<<grid, gemm_pipe_threads<EpiStore<BN>>(), L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi,
-                                                 status, NoComm{});
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(gemm_pipe_threads<EpiStore<BN>>()), L::TOTAL, stream, tA, tB,
+                                        tA2, tB2, kb_main, kb_extra, sched, epi, status, NoComm{}));
 }
 
 }  // namespace artb

@@ -44,9 +44,8 @@ static int launch_2cta(const void* A, int lda, const void* B, int ldb, const voi
                       ldh, M, N, epilogue == EPI_F32 ? 1 : 0, res_cols > 0 ? res_cols : N,
                      epilogue == EPI_SWIGLU_BWD ? 1 : 0};
   SchedPair sched{m_tiles2, n_tiles, pick_group_m(m_tiles2, 2 * GEMM_BM, K), 1, kb_main, kb_main};
-  kern<<<2 * clusters, gemm_pipe_threads<EpiStore<BN2>>(), L::TOTAL, stream>>>(tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status,
-                                                        NoComm{});
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(2 * clusters), dim3(gemm_pipe_threads<EpiStore<BN2>>()), L::TOTAL, stream,
+                                        tA, tB, tA2, tB2, kb_main, kb_extra, sched, epi, status, NoComm{}));
 }
 
 // Split-K on CTA pairs for small-M (decode) weight streaming: work item = (256 x 256 tile, K slice); the pair shares
@@ -78,8 +77,8 @@ static int launch_2cta_splitk(const void* A, int lda, const void* B, int ldb, fl
   if (clusters > sm_count() / 2) clusters = sm_count() / 2;
   EpiAtomic<BN2> epi{ws, ldw, M, N};
   SchedPair sched{m_tiles2, n_tiles, m_tiles2, splits, kb_per, kb_main};
-  kern<<<2 * clusters, GEMM_THREADS, L::TOTAL, stream>>>(tA, tB, tA, tB, kb_main, 0, sched, epi, status, NoComm{});
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(2 * clusters), dim3(GEMM_THREADS), L::TOTAL, stream, tA, tB, tA, tB,
+                                        kb_main, 0, sched, epi, status, NoComm{}));
 }
 
 }  // namespace artb

@@ -353,8 +353,8 @@ static int launch_lp(const void* H, int ldh, const void* W, int ldw, int M, int 
     sched.m_tiles = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);      // pair tiles of 256 rows
     int clusters = sched.m_tiles * splits;
     if (clusters > sm_count() / 2) clusters = sm_count() / 2;
-    kern<<<2 * clusters, gemm_pipe_threads<Epi>(), L::TOTAL, stream>>>(tA, tB, tA, tB, kb, 0, sched, epi, status, NoComm{});
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_kernel(kern, dim3(2 * clusters), dim3(gemm_pipe_threads<Epi>()), L::TOTAL, stream, tA, tB,
+                                          tA, tB, kb, 0, sched, epi, status, NoComm{}));
   }
   using L = GemmSmemLayout<LP_BN, LP_STAGES>;
   auto kern = gemm_tcgen05_kernel<LP_BN, LP_STAGES, SchedVocabSplit, Epi>;
@@ -368,8 +368,8 @@ static int launch_lp(const void* H, int ldh, const void* W, int ldw, int M, int 
   sched.m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
   int grid = sched.m_tiles * splits;
   if (grid > sm_count()) grid = sm_count();
-  kern<<<grid, gemm_pipe_threads<Epi>(), L::TOTAL, stream>>>(tA, tB, tA, tB, kb, 0, sched, epi, status, NoComm{});
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kern, dim3(grid), dim3(gemm_pipe_threads<Epi>()), L::TOTAL, stream, tA, tB, tA, tB, kb,
+                                        0, sched, epi, status, NoComm{}));
 }
 
 }  // namespace artb

@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "host_utils.h"
+#include "ptx_sm100.cuh"
 
 namespace artb {
 
@@ -107,6 +108,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
   float* sM = reinterpret_cast<float*>(sKV + 4 * 2 * PA_KT * LD);      // merge: [4][16] max, [4][16] sum
   float* sAcc = sM + 2 * 4 * 16;                                       // [4][16][HD]
 
+  pdl_wait();                  // q, the cache rows of this step and the block table come from earlier kernels
+  pdl_launch_dependents();
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -345,9 +348,9 @@ ARTB_EXPORT int artb_paged_decode(const void* q, int ldq, const void* k_cache, c
       cudaFuncSetAttribute(paged_decode_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<HD_>()); \
       cfgd[dev_] = true;                                                                                         \
     }                                                                                                            \
-    paged_decode_kernel<HD_><<<grid, 128, decode_smem<HD_>(), st>>>((const bf16*)q, ldq, (const bf16*)k_cache,   \
-        (const bf16*)v_cache, block_table, max_blocks, ctx_len, block_size, Hq, Hkv, (bf16*)out, ldo, ws, splits, \
-        scale_log2);                                                                                             \
+    launch_kernel(paged_decode_kernel<HD_>, grid, dim3(128), decode_smem<HD_>(), st, (const bf16*)q, ldq,        \
+                  (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, ctx_len, block_size, Hq, Hkv, \
+                  (bf16*)out, ldo, ws, splits, scale_log2);                                                      \
     if (splits > 1) paged_decode_merge_kernel<HD_><<<dim3(num_seqs, Hq), HD_, 0, st>>>(ws, splits, Hq, (bf16*)out, ldo); \
   }
   if (hd == 128) ARTB_PD(128)

@@ -691,6 +691,16 @@ class NativeRunner:
         from ..ops import elementwise as ew
         from ..ops import paged
 
+        prev_pdl = paged.set_pdl(os.environ.get("ARTB_PDL", "1") != "0")
+        try:
+            self._decode_steps(st, n_steps, any_lora, splits, ws, restricted, procs)
+        finally:
+            paged.set_pdl(prev_pdl)
+
+    def _decode_steps(self, st, n_steps: int, any_lora: bool, splits: int, ws, restricted: bool, procs) -> None:
+        from ..ops import elementwise as ew
+        from ..ops import paged
+
         cfg, bs = self.cfg, self.kv.shape[1]
         Hq, Hkv, hd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         fused = self._fused_decode_ok(st["tokens"].shape[0])

@@ -21,6 +21,7 @@ _sigs = {
     "artb_sample_restricted": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp],
     "artb_logit_adjust": [vp, cl, vp, vp, vp, vp, vp, ci, ci, ci, vp],
     "artb_top_logprobs": [vp, cl, vp, ci, ci, ci, vp, vp, vp],
+    "artb_set_pdl": [ci],
     "artb_decode_finalize_norm": [vp, ci, ci, ci, ci, vp, vp, ci, vp, vp, ci, ci, vp, ctypes.c_float, vp, ci, vp, ci, vp],
     "artb_decode_finalize_qkv": [vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, ci, vp, ctypes.c_float, vp, vp, vp, vp, ci, vp],
 }
@@ -42,6 +43,13 @@ def kv_write(qkv: torch.Tensor, k_col: int, v_col: int, slot: torch.Tensor, k_ca
     kv_width = k_cache.shape[-2] * k_cache.shape[-1]
     _lib.check_rc(_f("artb_kv_write")(_lib.ptr(qkv), qkv.stride(0), k_col, v_col, _lib.ptr(slot), _lib.ptr(k_cache),
                                       _lib.ptr(v_cache), qkv.shape[0], kv_width, _lib.stream_ptr()), "kv_write")
+
+
+def set_pdl(on: bool) -> bool:
+    """Programmatic dependent launch for the decode-step kernels launched from now on (returns the previous setting):
+    each may start its prologue while its predecessor in the stream drains, and waits on the device before touching
+    global memory."""
+    return bool(_f("artb_set_pdl")(1 if on else 0))
 
 
 def decode_finalize_norm(ws: torch.Tensor, M: int, N: int, kpad: int, x_out: torch.Tensor, *, bias: torch.Tensor | None = None,

@@ -124,8 +124,16 @@ class PipelineRunner:
     # -- schedule -------------------------------------------------------------------------------
     def run(self, n_micro: int) -> list[Any]:
         """Execute one optimizer step's worth of micro-batches; returns the last stage's forward outputs."""
+        return self._run(schedule_1f1b(self.stage, self.n_stages, n_micro), self.stage_obj.forward, self.stage_obj.backward)
+
+    def run_forward(self, n_micro: int, fn) -> list[Any]:
+        """A forward-only sweep of all micro-batches through the stages, in order (no activations are kept, so nothing
+        limits how many are in flight): ``fn(mb, x)`` returns the tensor to send downstream; on the last stage its
+        return values are collected.  Used for the reference-policy pass of the KL term."""
+        return self._run([("F", i) for i in range(n_micro)], fn, None)
+
+    def _run(self, ops: list[tuple[str, int]], fwd, bwd) -> list[Any]:
         first, last = self.stage == 0, self.stage == self.n_stages - 1
-        ops = schedule_1f1b(self.stage, self.n_stages, n_micro)
         sends: list[_Pending] = []
         outputs: list[Any] = []
 
@@ -145,13 +153,13 @@ class PipelineRunner:
                 inp = pending.tensor
             send_t, send_delta = None, 0
             if kind == "F":
-                out = self.stage_obj.forward(mb, inp)
+                out = fwd(mb, inp)
                 if last:
                     outputs.append(out)
                 else:
                     send_t, send_delta = out, +1
             else:
-                dx = self.stage_obj.backward(mb, inp)
+                dx = bwd(mb, inp)
                 if not first:
                     send_t, send_delta = dx, -1
             nxt = recv_delta(ops[i + 1]) if i + 1 < len(ops) else None

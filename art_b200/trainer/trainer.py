@@ -330,6 +330,8 @@ class Trainer:
             gid, pid = compress_ids(rows["group_ids"][r0:r1].reshape(-1), rows["parent_ids"][r0:r1].reshape(-1))
             micro.append(dict(tokens=tokens, pos=pos, gid=gid.to(dev), pid=pid.to(dev), r0=r0, r1=r1))
 
+        ref_lp: dict[int, torch.Tensor] = {}     # micro-batch -> reference log-probs of its trainable tokens (last stage)
+
         class _Stage:
             def __init__(self):
                 self.live: dict = {}
@@ -351,8 +353,8 @@ class Trainer:
                     adv_c = shift_left(rows_d["advantages"][r0:r1], 0.0).reshape(-1)[sel]
                     hc = ew.gather_rows(hidden, sel)
                     with trainer.timer.phase("lm_head_loss"):
-                        res = lpl.forward(hc, model.lm_head, target[sel], old_c, adv_c, w_flat[sel], None, hyper.epsilon,
-                                          eps_hi, 0.0, accum)
+                        res = lpl.forward(hc, model.lm_head, target[sel], old_c, adv_c, w_flat[sel], ref_lp.get(mb),
+                                          hyper.epsilon, eps_hi, hyper.beta, accum)
                         dhc = lpl.backward(hc, model.lm_head, model.lm_head_t, target[sel], res.lse, res.coef)
                     ew.scatter_rows_(dhc, sel, dhidden)
                 self.live[mb] = (saved, final, dhidden)
@@ -363,10 +365,26 @@ class Trainer:
                 with trainer.timer.phase("backward"):
                     return model.backward(dhidden if model.is_last else dy, saved, final, micro[mb]["pos"])
 
-        if hyper.beta > 0:
-            raise NotImplementedError("the KL term needs a second (reference) pipeline pass; use beta = 0 with pp_group")
         runner = PipelineRunner(_Stage(), self.pp_group, act_shape=(per * S, self.cfg.hidden_size),
                                 act_dtype=torch.bfloat16, device=dev)
+        if hyper.beta > 0:
+            # KL term: the reference policy is the frozen base model, i.e. the same stages without their LoRA factors.
+            # One forward-only sweep of all micro-batches leaves the reference log-probs of the trainable tokens on
+            # the last stage, where the loss of the main schedule reads them.
+            def reference(mb, x):
+                m = micro[mb]
+                hidden, _, _ = model.forward(m["tokens"], m["pos"], m["gid"], m["pid"], S, use_lora=False, save=False, x_in=x)
+                if not model.is_last:
+                    return hidden
+                w_flat = tok_w.reshape(-1)[m["r0"] * S:m["r1"] * S]
+                sel = torch.nonzero(w_flat != 0, as_tuple=False).squeeze(1)
+                if sel.numel():
+                    target = torch.cat([m["tokens"][1:], m["tokens"][:1]]).to(torch.int32)
+                    part, _ = lpl.partials(ew.gather_rows(hidden, sel), model.lm_head, target[sel])
+                    ref_lp[mb] = lpl.grpo_tokens(part).logprobs
+                return None
+
+            runner.run_forward(len(micro), reference)
         runner.run(len(micro))
         self.model.export_grads()
         out = self._finish_step(None, hyper, device_accum=accum)

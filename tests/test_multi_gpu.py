@@ -529,7 +529,7 @@ for it in range(2):                                     # second step: refreshed
     assert tp_cos > 0.995, tp_cos
 
 # ---- pipeline parallel: layers split over the ranks, 1F1B over NCCL p2p == the same step on one GPU
-hy_pp = TrainHyper(learning_rate=1e-4, beta=0.0, rows_per_optimizer_step=4, tokens_per_microbatch=512)
+hy_pp = TrainHyper(learning_rate=1e-4, beta=0.05, rows_per_optimizer_step=4, tokens_per_microbatch=512)   # KL term: reference sweep through the stages
 packed_pp = _packed(cfg, 4, 256)
 ppt = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native", pp_group=dist.group.WORLD)
 one3 = Trainer(cfg, base, lcfg, {k: v.clone() for k, v in lora.items()}, device=dev, impl="native")

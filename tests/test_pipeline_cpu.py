@@ -78,9 +78,23 @@ for mb in range(n_micro):
 for i in ids:
     assert torch.allclose(layers[i].weight.grad, ref[i].weight.grad, atol=1e-6), i
     assert torch.allclose(layers[i].bias.grad, ref[i].bias.grad, atol=1e-6), i
+# forward-only sweep (the reference-policy pass of the KL term): every micro-batch crosses all stages once
+def fwd_only(mb, x):
+    y = data[mb] if x is None else x
+    with torch.no_grad():
+        for m in stage.mods: y = torch.tanh(m(y))
+    return y
+swept = runner.run_forward(n_micro, fwd_only)
 if rank == world - 1:
     assert abs(sum(float(o) for o in outs) - tot) < 1e-6
+    with torch.no_grad():
+        for mb in range(n_micro):
+            y = data[mb]
+            for m in ref: y = torch.tanh(m(y))
+            assert torch.allclose(swept[mb], y, atol=1e-6), mb
     print("PP_OK", world)
+else:
+    assert swept == []
 dist.destroy_process_group()
 '''
 
