@@ -106,7 +106,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(pa_smem);      // [16][LD]
   __nv_bfloat16* sKV = sQ + 16 * LD;                                   // [4 warps][2 (K,V)][PA_KT][LD]
   float* sM = reinterpret_cast<float*>(sKV + 4 * 2 * PA_KT * LD);      // merge: [4][16] max, [4][16] sum
-  float* sAcc = sM + 2 * 4 * 16;                                       // [4][16][HD]
+  // merge accumulators [4][16][HD] fp32: warp w's slice lives in warp w's own (by then finished) K/V staging area, which
+  // keeps a CTA under a third of the SM's shared memory: three CTAs = twelve warps per SM instead of eight
+  static_assert(16 * HD * 4 <= 2 * PA_KT * LD * 2, "a warp's accumulator slice must fit its K/V staging area");
 
   pdl_wait();                  // q, the cache rows of this step and the block table come from earlier kernels
   pdl_launch_dependents();
@@ -117,6 +119,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
   const int len = ctx_len[seq];
   const int kv_width = Hkv * HD;
   const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
+  const int bs_shift = (block_size & (block_size - 1)) == 0 ? 31 - __clz(block_size) : -1;   // power of two: shifts
 
   // Q rows: G real heads, rest zero
   for (int v = tid; v < 16 * (HD / 8); v += 128) {
@@ -146,17 +149,29 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
 
   __nv_bfloat16* wK = sKV + warp * 2 * PA_KT * LD;
   __nv_bfloat16* wV = wK + PA_KT * LD;
+  auto warp_acc = [&](int w) { return reinterpret_cast<float*>(sKV + w * 2 * PA_KT * LD); };
   for (int tile = tile_lo + warp; tile < tile_hi; tile += 4) {
     const int k0 = tile * PA_KT;
-    // warp-private load of 32 keys x HD for K and V
-    for (int v = lane; v < PA_KT * (HD / 8); v += 32) {
-      const int r = v / (HD / 8), c = (v % (HD / 8)) * 8;
-      const int kt = k0 + r;
-      const bool ok = kt < len;
-      size_t s = 0;
-      if (ok) s = static_cast<size_t>(bt[kt / block_size]) * block_size + kt % block_size;
-      pa_cp16(wK + r * LD + c, k_cache + s * kv_width + kvh * HD + c, ok);
-      pa_cp16(wV + r * LD + c, v_cache + s * kv_width + kvh * HD + c, ok);
+    // Warp-private load of 32 keys x HD for K and V.  A lane keeps one 16-byte column of the head and walks down the
+    // rows, so the per-copy work is one table lookup and one multiply-add; with a runtime division per copy (block
+    // index and offset of every key) the address arithmetic was two thirds of the kernel's instructions.
+    {
+      constexpr int CPR = HD / 8;                 // 16-byte copies per row
+      constexpr int RPI = 32 / CPR;               // rows covered by the warp per iteration
+      const int c = (lane % CPR) * 8;
+      const __nv_bfloat16* kc = k_cache + kvh * HD + c;
+      const __nv_bfloat16* vc = v_cache + kvh * HD + c;
+#pragma unroll 4
+      for (int r = lane / CPR; r < PA_KT; r += RPI) {
+        const int kt = k0 + r;
+        const bool ok = kt < len;
+        size_t s = 0;
+        if (ok)
+          s = bs_shift >= 0 ? (static_cast<size_t>(bt[kt >> bs_shift]) << bs_shift) + (kt & (block_size - 1))
+                            : static_cast<size_t>(bt[kt / block_size]) * block_size + kt % block_size;
+        pa_cp16(wK + r * LD + c, kc + s * kv_width, ok);
+        pa_cp16(wV + r * LD + c, vc + s * kv_width, ok);
+      }
     }
     pa_commit();
     pa_wait_all();
@@ -243,8 +258,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
   }
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) {
-    float* a0 = sAcc + (warp * 16 + g) * HD + i * 8 + 2 * t;
-    float* a1 = sAcc + (warp * 16 + g + 8) * HD + i * 8 + 2 * t;
+    float* a0 = warp_acc(warp) + g * HD + i * 8 + 2 * t;
+    float* a1 = warp_acc(warp) + (g + 8) * HD + i * 8 + 2 * t;
     a0[0] = acc[i][0];
     a0[1] = acc[i][1];
     a1[0] = acc[i][2];
@@ -263,7 +278,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
       for (int w = 0; w < 4; ++w) {
         const float sc = exp2f(sM[w * 16 + r] - mm);
         lsum += sM[64 + w * 16 + r] * sc;
-        o += sAcc[(w * 16 + r) * HD + d] * sc;
+        o += warp_acc(w)[r * HD + d] * sc;
       }
     }
     const int h = kvh * G + r;
@@ -300,7 +315,9 @@ __global__ void paged_decode_merge_kernel(const float* __restrict__ ws, int spli
 }
 
 template <int HD>
-static int decode_smem() { return (16 * (HD + 8) + 4 * 2 * PA_KT * (HD + 8)) * 2 + (2 * 4 * 16 + 4 * 16 * HD) * 4; }
+static int decode_smem() {
+  return (16 * (HD + 8) + 4 * 2 * PA_KT * (HD + 8)) * 2 + (2 * 4 * 16) * 4;
+}
 
 }  // namespace artb
 

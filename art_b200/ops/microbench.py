@@ -386,6 +386,44 @@ def bench_sampler(a) -> dict:
     return out
 
 
+def bench_paged_decode(a) -> dict:
+    """Decode attention over a paged KV cache at a rollout-engine shape: ``seqs`` sequences of ``ctx`` cached tokens,
+    ``layers`` distinct caches visited round-robin (together larger than L2, so every launch reads its keys and values
+    from HBM, as in a real step where 28 layers follow one another).  Reports the K+V bytes per second."""
+    from . import _lib, paged
+
+    dev = "cuda"
+    bs = 16
+    nblk = (a.ctx + bs - 1) // bs
+    g = torch.Generator(device=dev).manual_seed(0)
+    caches = []
+    for _ in range(a.layers):
+        k = (torch.randn(a.seqs * nblk, bs, a.hkv, a.hd, device=dev, generator=g) * 0.5).bfloat16()
+        v = (torch.randn(a.seqs * nblk, bs, a.hkv, a.hd, device=dev, generator=g) * 0.5).bfloat16()
+        caches.append((k, v))
+    perm = torch.randperm(a.seqs * nblk, device=dev, generator=g).to(torch.int32)
+    width = 64
+    while width < nblk:
+        width *= 2
+    bt = torch.zeros(a.seqs, width, dtype=torch.int32, device=dev)
+    bt[:, :nblk] = perm.view(a.seqs, nblk)
+    ctx = torch.full((a.seqs,), a.ctx, dtype=torch.int32, device=dev)
+    q = (torch.randn(a.seqs, a.hq * a.hd, device=dev, generator=g) * 0.5).bfloat16()
+    out = torch.empty_like(q)
+    splits = a.splits
+    ws = torch.empty(a.seqs * a.hq * splits * (a.hd + 2), dtype=torch.float32, device=dev) if splits > 1 else None
+
+    def run():                    # one launch per cache, back to back, as the layers of a step follow one another
+        for k, v in caches:
+            paged.paged_decode(q, k, v, bt, ctx, a.hq, a.hkv, a.hd, out, splits, ws)
+
+    ms = _time(run, a.iters, a.warmup, None) / a.layers
+    _lib.check_status()
+    kv_bytes = 2.0 * a.seqs * a.ctx * a.hkv * a.hd * 2
+    return {"op": "paged_decode", "seqs": a.seqs, "ctx": a.ctx, "hq": a.hq, "hkv": a.hkv, "hd": a.hd, "splits": splits,
+            "layers": a.layers, "ms": round(ms, 4), "kv_mb": round(kv_bytes / 1e6, 1), "kv_gb_s": round(kv_bytes / ms / 1e6, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -414,6 +452,14 @@ def main() -> None:
     sp.add_argument("--vocab", type=int, default=152064)
     sp.add_argument("--top-k", type=int, default=50)
     sp.add_argument("--top-p", type=float, default=0.9)
+    pd = sub.add_parser("paged-decode")
+    pd.add_argument("--seqs", type=int, default=256)
+    pd.add_argument("--ctx", type=int, default=640)
+    pd.add_argument("--hq", type=int, default=28)
+    pd.add_argument("--hkv", type=int, default=4)
+    pd.add_argument("--hd", type=int, default=128)
+    pd.add_argument("--splits", type=int, default=1)
+    pd.add_argument("--layers", type=int, default=8, help="distinct caches visited round-robin (8 x 335 MB at the defaults)")
     gl = sub.add_parser("gemm-layer")
     gl.add_argument("--model", default="qwen2.5-7b")
     gl.add_argument("--tokens", type=int, default=8192)
@@ -424,14 +470,14 @@ def main() -> None:
     tl.add_argument("--model", default="qwen2.5-7b")
     tl.add_argument("--tokens", type=int, default=16384)
     tl.add_argument("--seconds", type=float, default=0.4)
-    for p in (g, t, m, sp, gl, tl):
+    for p in (g, t, m, sp, gl, tl, pd):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
     res = {"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler,
-           "gemm-layer": bench_gemm_layer, "tp-layer": bench_tp_layer}[a.op](a)
+           "gemm-layer": bench_gemm_layer, "tp-layer": bench_tp_layer, "paged-decode": bench_paged_decode}[a.op](a)
     if res:
         print(json.dumps(res))
 
