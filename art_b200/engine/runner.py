@@ -368,6 +368,15 @@ class NativeRunner:
             decoder.lm_head = base["lm_head.weight"][self.vocab_offset:self.vocab_offset + self.vocab_local].to(dev, bf).contiguous()
             decoder.final_norm = base["model.norm.weight"].to(dev, bf).contiguous()
             decoder.layers = []
+            if cfg.is_moe:
+                # the experts keep ONE adapter's factors resident (the slot loaded last), in a flat store of their own
+                from ..models.moe import MoEMLP, expert_lora_order
+                from ..models.native import LoraFlat
+                from ..models.weights import init_lora
+
+                zero = {k: torch.zeros_like(v) for k, v in init_lora(cfg, lora_cfg, seed=0, device=dev).items()
+                        if ".mlp.experts." in k}
+                self._moe_flat = LoraFlat(cfg, lora_cfg, zero, dev, order=expert_lora_order(cfg, list(zero.keys())))
             row_sl = {"self_attn.q_proj": sl_q, "self_attn.k_proj": sl_kv, "self_attn.v_proj": sl_kv,
                       "mlp.gate_proj": sl_f, "mlp.up_proj": sl_f}
             col_sl = {"self_attn.o_proj": sl_q, "mlp.down_proj": sl_f}
@@ -387,11 +396,14 @@ class NativeRunner:
                                    for n in ("q_proj", "k_proj", "v_proj")]) if cfg.qkv_bias else None)
                 layer = {"qkv": LoraLinear(wqkv, bqkv, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
                          "o": LoraLinear(W("self_attn.o_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
-                         "gu": LoraLinear(ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj")), None, [],
-                                          lora_cfg.r, lora_cfg.scale, need_dgrad=False),
-                         "down": LoraLinear(W("mlp.down_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False),
                          "ln1": base[p + "input_layernorm.weight"].to(dev, bf).contiguous(),
                          "ln2": base[p + "post_attention_layernorm.weight"].to(dev, bf).contiguous()}
+                if cfg.is_moe:
+                    layer["mlp"] = MoEMLP(cfg, i, base, self._moe_flat, lora_cfg, dev)
+                else:
+                    layer["gu"] = LoraLinear(ew.interleave_gate_up(W("mlp.gate_proj"), W("mlp.up_proj")), None, [],
+                                             lora_cfg.r, lora_cfg.scale, need_dgrad=False)
+                    layer["down"] = LoraLinear(W("mlp.down_proj"), None, [], lora_cfg.r, lora_cfg.scale, need_dgrad=False)
                 if cfg.qk_norm:
                     layer["q_norm"] = base[p + "self_attn.q_norm.weight"].to(dev, bf).contiguous()
                     layer["k_norm"] = base[p + "self_attn.k_norm.weight"].to(dev, bf).contiguous()
@@ -404,11 +416,23 @@ class NativeRunner:
         r = lora_cfg.r
         self.layers = []
         self._ws_holder: dict = {}
+        self._moe_flat = getattr(self, "_moe_flat", None)   # None: dense, or experts that read a trainer's master buffer
+        self._moe_slot: int | None = None                   # adapter slot whose expert factors are resident
+        self._moe_mixed = False                             # the batch at hand mixes base-model rows and adapter rows
         for i, L in enumerate(decoder.layers):
+            if "gu" not in L and hasattr(L.get("mlp"), "Wg"):
+                # sparse feed-forward (router + grouped experts): served through the trainer-side module, forward only
+                self.layers.append({
+                    "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q), sl_q, None),
+                                                   ("self_attn.k_proj", ar(q, q + kvw), sl_kv, None),
+                                                   ("self_attn.v_proj", ar(q + kvw, q + 2 * kvw), sl_kv, None)],
+                                        r, max_loras, self._ws_holder),
+                    "o": EngineLinear(L["o"], [("self_attn.o_proj", ar(0, d), None, sl_q)], r, max_loras, self._ws_holder),
+                    "moe": L["mlp"], "ln1": L["ln1"], "ln2": L["ln2"], "q_norm": L.get("q_norm"), "k_norm": L.get("k_norm"),
+                })
+                continue
             if "gu" not in L:       # a trainer-side decoder keeps its feed-forward linears inside an MLP object
                 mlp = L["mlp"]
-                if not hasattr(mlp, "gu"):
-                    raise ValueError("the rollout runner serves dense feed-forward layers; this decoder's MLP is not dense")
                 L = {**L, "gu": mlp.gu, "down": mlp.down}
             self.layers.append({
                 "qkv": EngineLinear(L["qkv"], [("self_attn.q_proj", ar(0, q), sl_q, None),
@@ -502,7 +526,27 @@ class NativeRunner:
         """
         for i, L in enumerate(self.layers):
             for k in ("qkv", "o", "gu", "down"):
-                L[k].load_slot(slot, i, state, self.lora_cfg.scale)
+                if k in L:
+                    L[k].load_slot(slot, i, state, self.lora_cfg.scale)
+        if self._moe_flat is not None:
+            # Expert factors: one adapter at a time.  Rollouts of a training run all use the newest adapter, so the
+            # slot loaded last owns the experts; loading expert factors into a second slot while another slot's are
+            # resident would silently serve the wrong experts to the first, so it is refused.
+            has_experts = state is not None and any(".mlp.experts." in k for k in state)
+            if has_experts and self._moe_slot not in (None, slot) and self.slot_loaded[self._moe_slot]:
+                raise ValueError("a sparse model keeps the expert factors of one adapter resident; "
+                                 f"slot {self._moe_slot} holds them (remove that adapter first, or serve with max_loras=1)")
+            if has_experts or self._moe_slot == slot:
+                for k, v in self._moe_flat.views.items():
+                    if has_experts and k in state:
+                        v.copy_(state[k])
+                    else:
+                        v.zero_()
+                for L in self.layers:
+                    if "moe" in L:
+                        for lin in L["moe"].linears():
+                            lin.refresh()
+                self._moe_slot = slot if has_experts else None
         self.slot_loaded[slot] = state is not None
 
     # -- shared layer body ----------------------------------------------------------------------
@@ -510,6 +554,15 @@ class NativeRunner:
         from ..ops import elementwise as ew
 
         h2, _ = ew.rmsnorm_fwd(x2, L["ln2"], self.cfg.rms_norm_eps, want_rstd=False)
+        if "moe" in L:
+            moe = L["moe"]
+            if not any_lora:
+                return moe.forward(h2, x2, False, False)[0]
+            y = moe.forward(h2, x2, True, False)[0]
+            if self._moe_mixed:      # rows of the base model in the same batch: their experts run without the factors
+                y0 = moe.forward(h2, x2, False, False)[0]
+                y = torch.where((adapter_ids >= 0).unsqueeze(1), y, y0)
+            return y
         hact = torch.empty((x2.shape[0], self.cfg.intermediate_size), dtype=x2.dtype, device=x2.device)
         L["gu"](h2, adapter_ids, any_lora, swiglu_out=hact)
         return self._reduce(L["down"](hact, adapter_ids, any_lora, residual=self._res(x2)))
@@ -561,6 +614,7 @@ class NativeRunner:
         S_att = (att + 63) // 64 * 64
         gid += [-(j + 1) for j in range(S_att - att)]
         any_lora = any(a >= 0 for a in adapter)
+        self._moe_mixed = any_lora and any(a < 0 for a in adapter)
         use_index = bool(cached_spans) or S_att != M
         t_tok = torch.tensor(tok, dtype=torch.int64, device=dev)
         t_pos = torch.tensor(pos, dtype=torch.int32, device=dev)
@@ -814,6 +868,7 @@ class NativeRunner:
         st["inv_t"].copy_(torch.from_numpy(inv_t), non_blocking=True)
         st["seeds"].copy_(torch.from_numpy(seeds.astype(np.int64)).to(torch.int32), non_blocking=True)
         any_lora = any(s.adapter >= 0 for s in seqs)
+        self._moe_mixed = any_lora and (pad > 0 or any(s.adapter < 0 for s in seqs))
         procs = None
         if any(s.proc is not None for s in seqs):
             # logit edits depend on every token sampled so far: one step at a time, outside the captured graphs
@@ -828,7 +883,7 @@ class NativeRunner:
             st["min_p"].copy_(torch.tensor([s.min_p for s in seqs] + [0.0] * pad, dtype=torch.float32), non_blocking=True)
         max_ctx = max(lens) + n_steps
         splits = 1 if nb * cfg.num_kv_heads >= 128 else min(8, max(1, 1 << (max(1, max_ctx // 512).bit_length() - 1)))
-        key = (nb, max_blocks, n_steps, any_lora, splits, restricted)
+        key = (nb, max_blocks, n_steps, any_lora, splits, restricted, self._moe_mixed)
         ws = None
         if splits > 1:
             ws = st.get(("ws", splits))
