@@ -424,6 +424,29 @@ def bench_paged_decode(a) -> dict:
             "layers": a.layers, "ms": round(ms, 4), "kv_mb": round(kv_bytes / 1e6, 1), "kv_gb_s": round(kv_bytes / ms / 1e6, 1)}
 
 
+def bench_wgrad(a) -> dict:
+    """LoRA factor gradient ``acc[C, 64] += P[M, C]^T Q[M, 64]``: reads the wide operand once, so the figure of merit is
+    bytes of P (+ Q) per second against the copy bandwidth.  Several P buffers are visited round-robin (> L2 together)."""
+    from . import _lib, wgrad
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    n_buf = max(2, int(400e6 // (a.m * a.c * 2)) + 1)
+    Ps = [(torch.randn(a.m, a.c, device=dev, generator=g) * 0.5).bfloat16() for _ in range(n_buf)]
+    Q = (torch.randn(a.m, 64, device=dev, generator=g) * 0.5).bfloat16()
+    acc = torch.zeros(a.c, 64, device=dev)
+
+    def run():
+        for P in Ps:
+            wgrad.accumulate(acc, P, Q, False)
+
+    ms = _time(run, a.iters, a.warmup, None) / n_buf
+    _lib.check_status()
+    nbytes = a.m * (a.c + 64) * 2.0
+    return {"op": "lora_wgrad", "m": a.m, "c": a.c, "ms": round(ms, 4), "mb": round(nbytes / 1e6, 1),
+            "gb_s": round(nbytes / ms / 1e6, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -460,6 +483,9 @@ def main() -> None:
     pd.add_argument("--hd", type=int, default=128)
     pd.add_argument("--splits", type=int, default=1)
     pd.add_argument("--layers", type=int, default=8, help="distinct caches visited round-robin (8 x 335 MB at the defaults)")
+    wg = sub.add_parser("wgrad")
+    wg.add_argument("--m", type=int, default=8192)
+    wg.add_argument("--c", type=int, default=3584)
     gl = sub.add_parser("gemm-layer")
     gl.add_argument("--model", default="qwen2.5-7b")
     gl.add_argument("--tokens", type=int, default=8192)
@@ -470,14 +496,15 @@ def main() -> None:
     tl.add_argument("--model", default="qwen2.5-7b")
     tl.add_argument("--tokens", type=int, default=16384)
     tl.add_argument("--seconds", type=float, default=0.4)
-    for p in (g, t, m, sp, gl, tl, pd):
+    for p in (g, t, m, sp, gl, tl, pd, wg):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
     res = {"attn": bench_attn, "moe": bench_moe, "gemm": bench_gemm, "sampler": bench_sampler,
-           "gemm-layer": bench_gemm_layer, "tp-layer": bench_tp_layer, "paged-decode": bench_paged_decode}[a.op](a)
+           "gemm-layer": bench_gemm_layer, "tp-layer": bench_tp_layer, "paged-decode": bench_paged_decode,
+           "wgrad": bench_wgrad}[a.op](a)
     if res:
         print(json.dumps(res))
 
