@@ -12,3 +12,5 @@ class TrainConfig(TypedDict, total=False):
     rows_per_optimizer_step: int  # packed rows accumulated into one AdamW step (default 1)
     compat_row_positions: bool  # RoPE positions = position in the packed row instead of input_pos
     activation_recompute: str  # "auto" | "none" | "mlp" | "full" (overrides init_args.activation_recompute)
+    max_service_restarts: int  # supervision: times a dead / timed-out service process is restarted per train call (1)
+    step_timeout_s: float  # watchdog: longest time one gradient step may take before its process is replaced (off)

@@ -8,6 +8,7 @@ other processes.
 """
 from __future__ import annotations
 
+import asyncio
 import json
 import math
 from datetime import datetime
@@ -90,6 +91,8 @@ class LocalBackend(Backend):
         self._path = path or get_default_art_path()
         os.makedirs(self._path, exist_ok=True)
         self._services: dict[str, ModelService] = {}
+        self._server_configs: dict[str, tuple] = {}     # model name -> (OpenAI server config, (host, port)) of its start
+        self.service_restarts: dict[str, int] = {}      # model name -> times its service process was restarted
         self._tokenizers: dict[str, object] = {}
         self._wandb_runs: dict[str, object] = {}
         self._rng = random.Random()
@@ -136,6 +139,26 @@ class LocalBackend(Backend):
                                                             in_process=self._in_process, log_dir=f"{out}/logs")
         return self._services[model.name]
 
+
+    async def _restart_service(self, model: TrainableModel):
+        """Replace the model's service process: the new one loads the newest complete checkpoint and serves on the same
+        address, so clients that hold the inference URL keep working."""
+        old = self._services.pop(model.name, None)
+        if old is not None:
+            try:
+                old.close()          # terminates the child if it is still alive (watchdog case)
+            except Exception:  # noqa: BLE001 - the process may be half dead already
+                pass
+        self.service_restarts[model.name] = self.service_restarts.get(model.name, 0) + 1
+        service = await self._get_service(model)
+        if model.name in self._server_configs:
+            cfg, (_, port) = self._server_configs[model.name]
+            cfg = dict(cfg or {})
+            cfg["server_args"] = {**cfg.get("server_args", {}), "port": port}
+            host, new_port = await service.start_openai_server(config=cfg)
+            if new_port != port:
+                raise RuntimeError(f"the restarted service of {model.name!r} came up on port {new_port}, not {port}")
+        return service
 
     def _get_packed_tensors(self, model: TrainableModel, trajectory_groups: list[TrajectoryGroup],
                             allow_training_without_logprobs: bool, plot_tensors: bool) -> PackedTensors | None:
@@ -190,6 +213,7 @@ class LocalBackend(Backend):
                                             config: dev.OpenAIServerConfig | None = None) -> tuple[str, str]:
         service = await self._get_service(model)
         host, port = await service.start_openai_server(config=config)
+        self._server_configs[model.name] = (config, (host, port))
         server_args = (config or {}).get("server_args", {})
         api_key = server_args.get("api_key", None) or "default"
         shown = "127.0.0.1" if host in ("0.0.0.0", "") else host
@@ -234,12 +258,38 @@ class LocalBackend(Backend):
         num_gradient_steps = math.ceil(disk["num_sequences"] / per)
         results: list[dict[str, float]] = []
         bar = tqdm.tqdm(total=num_gradient_steps, desc="train")
+        # Supervision: a service process that dies, or a gradient step that exceeds ``step_timeout_s`` (its process is
+        # then killed), is replaced by a fresh process that resumes from the last complete checkpoint (adapter +
+        # optimizer state), and the call is run again from its first row; ``max_service_restarts`` bounds the retries.
+        from ..runtime.actors import ActorDiedError
+
+        max_restarts = 0 if self._in_process else int(dev_config.get("max_service_restarts", 1))
+        step_timeout = dev_config.get("step_timeout_s")
+        attempt = 0
         try:
-            async for result in service.train(disk, config, dev_config, verbose):
-                results.append(result)
-                yield {**result, "num_gradient_steps": num_gradient_steps}
-                bar.update(1)
-                bar.set_postfix(result)
+            while True:
+                agen = service.train(disk, config, dev_config, verbose).__aiter__()
+                try:
+                    while True:
+                        try:
+                            result = await asyncio.wait_for(agen.__anext__(), step_timeout) if step_timeout else await agen.__anext__()
+                        except StopAsyncIteration:
+                            break
+                        results.append(result)
+                        yield {**result, "num_gradient_steps": num_gradient_steps}
+                        bar.update(1)
+                        bar.set_postfix(result)
+                    break
+                except (ActorDiedError, asyncio.TimeoutError) as e:
+                    if attempt >= max_restarts:
+                        raise
+                    attempt += 1
+                    why = "exceeded step_timeout_s" if isinstance(e, asyncio.TimeoutError) else str(e)
+                    print(f"model service of {model.name!r} {why}; restarting it from the last checkpoint "
+                          f"(restart {attempt} of {max_restarts})")
+                    service = await self._restart_service(model)
+                    results.clear()
+                    bar.reset()
         finally:
             bar.close()
         keys = {k for d in results for k in d}

@@ -32,6 +32,10 @@ _ctx = mp.get_context("spawn")
 _SHUTDOWN = "__shutdown__"
 
 
+class ActorDiedError(RuntimeError):
+    """The child process behind a proxy exited while (or before) a call was in flight."""
+
+
 class RemoteError(RuntimeError):
     """Raised in the parent when the child's exception cannot be unpickled."""
 
@@ -96,7 +100,7 @@ class Proxy:
         if self._closed:
             raise RuntimeError("actor is closed")
         if not self._process.is_alive():
-            raise RuntimeError(f"actor process died (exit code {self._process.exitcode})")
+            raise ActorDiedError(f"actor process died (exit code {self._process.exitcode})")
         loop = asyncio.get_running_loop()
         fut = loop.create_future()
         with self._lock:
@@ -125,7 +129,7 @@ class Proxy:
                 return fut.result()
             if not self._process.is_alive():
                 fut.cancel()
-                raise RuntimeError(f"actor process died (exit code {self._process.exitcode})")
+                raise ActorDiedError(f"actor process died (exit code {self._process.exitcode})")
 
     async def _stream(self, name: str, args: tuple, kwargs: dict):
         rid = next(self._ids)
@@ -156,7 +160,7 @@ class Proxy:
                 return await asyncio.wait_for(q.get(), timeout=1.0)
             except asyncio.TimeoutError:
                 if not self._process.is_alive():
-                    raise RuntimeError(f"actor process died (exit code {self._process.exitcode})") from None
+                    raise ActorDiedError(f"actor process died (exit code {self._process.exitcode})") from None
 
     def close(self, timeout: float = 5.0) -> None:
         if self._closed:

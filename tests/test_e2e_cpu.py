@@ -148,3 +148,46 @@ def test_remote_backend_round_trip(tmp_path):
         assert ("log", 1, "val") in fake.calls and ("delete", "val/reward", 1.0) in fake.calls and ("close",) in fake.calls
 
     asyncio.run(main())
+
+
+def test_service_process_is_restarted_from_the_last_checkpoint(tmp_path):
+    """Supervision: the model service runs in a child process; it is killed between two train calls (a failure made on
+    the host) and the second call restarts it from the newest checkpoint, on the same inference address."""
+    async def main():
+        backend = LocalBackend(in_process=False, path=str(tmp_path))
+        model = make_model("agent-sup")
+        try:
+            await model.register(backend)
+            groups = await art.gather_trajectory_groups(
+                (art.TrajectoryGroup(rollout(model, f"q{g}", i) for i in range(4)) for g in range(2)), pbar_desc=None)
+            await model.train(groups, config=art.TrainConfig(learning_rate=1e-2), _config={"rows_per_optimizer_step": 1})
+            assert await model.get_step() == 1
+            svc = backend._services["agent-sup"]
+            await svc.flush_checkpoints()
+            svc._process.kill()
+            svc._process.join(10)
+            await model.train(groups, config=art.TrainConfig(learning_rate=1e-2), _config={"rows_per_optimizer_step": 1})
+            assert backend.service_restarts == {"agent-sup": 1}
+            assert await model.get_step() == 2
+            out = tmp_path / "proj" / "models" / "agent-sup"
+            await backend._services["agent-sup"].flush_checkpoints()
+            assert (out / "0002" / "adapter_model.safetensors").exists()
+            # the restarted process serves on the address the client already holds
+            t = await rollout(model, "q0", 3)
+            assert len(t.messages_and_choices[-1].logprobs.content) == 6
+            # watchdog: a gradient step that exceeds its time limit ends the call (no restart budget here)
+            with pytest.raises(asyncio.TimeoutError):
+                await model.train(groups, config=art.TrainConfig(learning_rate=1e-2),
+                                  _config={"rows_per_optimizer_step": 1, "step_timeout_s": 1e-4, "max_service_restarts": 0})
+            # no restart budget: the failure surfaces
+            backend._services["agent-sup"]._process.kill()
+            backend._services["agent-sup"]._process.join(10)
+            from art_b200.runtime.actors import ActorDiedError
+            with pytest.raises(ActorDiedError):
+                await model.train(groups, config=art.TrainConfig(learning_rate=1e-2),
+                                  _config={"rows_per_optimizer_step": 1, "max_service_restarts": 0})
+        finally:
+            await model.openai_client().close()
+            backend.close()
+
+    asyncio.run(main())
