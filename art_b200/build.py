@@ -29,6 +29,7 @@ OUT = ROOT / "_native"
 OBJ = OUT / "obj"
 
 KERNEL_LIB = OUT / "libartb_kernels.so"
+CHECKED_KERNEL_LIB = OUT / "libartb_kernels_checked.so"
 RUNTIME_LIB = OUT / "libartb_runtime.so"
 
 NVCC_FLAGS = [
@@ -57,11 +58,12 @@ def _digest(src: Path, flags: list[str]) -> str:
     return h.hexdigest()[:16]
 
 
-def _compile_one(src: Path, cmd_prefix: list[str], flags: list[str], verbose: bool) -> Path:
-    obj = OBJ / f"{src.stem}.{_digest(src, flags)}.o"
+def _compile_one(src: Path, cmd_prefix: list[str], flags: list[str], verbose: bool, obj_dir: Path | None = None) -> Path:
+    obj_dir = obj_dir or OBJ
+    obj = obj_dir / f"{src.stem}.{_digest(src, flags)}.o"
     if obj.exists():
         return obj
-    for stale in OBJ.glob(f"{src.stem}.*.o"):
+    for stale in obj_dir.glob(f"{src.stem}.*.o"):
         stale.unlink()
     cmd = cmd_prefix + flags + ["-c", str(src), "-o", str(obj)]
     if verbose:
@@ -83,7 +85,7 @@ def runtime_sources() -> list[Path]:
     return sorted(p for p in (CSRC / "engine").glob("*.cpp") if not p.name.endswith("_selftest.cpp"))
 
 
-def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> None:
+def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = False, checked: bool = False) -> None:
     OBJ.mkdir(parents=True, exist_ok=True)
     if force:
         for o in OBJ.glob("*.o"):
@@ -109,8 +111,19 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = Fal
 
     _link(KERNEL_LIB, kobjs, [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"])
     _link(RUNTIME_LIB, robjs, ["g++", "-shared", "-fPIC", "-pthread"])
+    if checked:
+        # the same kernels with device-side index checks compiled in (csrc/include/bounds_check.cuh); loaded instead of
+        # the normal library when ARTB_BOUNDS_CHECK=1 is set in the environment
+        cdir = OBJ / "checked"
+        cdir.mkdir(parents=True, exist_ok=True)
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
+            cjobs = [pool.submit(_compile_one, s, [nvcc], nv_flags + ["-DARTB_BOUNDS_CHECK"], verbose, cdir)
+                     for s in kernel_sources()]
+            cobjs = [j.result() for j in cjobs]
+        _link(CHECKED_KERNEL_LIB, cobjs, [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"])
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
-    print("built:", KERNEL_LIB, RUNTIME_LIB)
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+              checked="--checked" in sys.argv)
+    print("built:", KERNEL_LIB, RUNTIME_LIB, *([CHECKED_KERNEL_LIB] if "--checked" in sys.argv else []))

@@ -25,6 +25,7 @@ enum KernelStatus : int {
   ST_TIMEOUT_PEER = 5,      // bounded wait on another rank's flag expired
   ST_BAD_ARGS = 6,
   ST_OVERFLOW = 7,          // a data-dependent buffer (MoE dispatch) was too small
+  ST_BOUNDS = 8,            // checked build: an index read from memory was outside its buffer (access skipped)
 };
 
 #ifndef ARTB_SPIN_LIMIT

@@ -23,8 +23,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "bounds_check.cuh"
 #include "host_utils.h"
-#include "ptx_sm100.cuh"
 
 namespace artb {
 
@@ -209,7 +209,8 @@ decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int
                            const float* __restrict__ bias, const int* __restrict__ adapter,
                            const __nv_bfloat16* __restrict__ B_all, int ldb, int cols, const int* __restrict__ pos,
                            float log2_theta, const int* __restrict__ slot, __nv_bfloat16* __restrict__ k_cache,
-                           __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ q_out, int ldq) {
+                           __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ q_out, int ldq,
+                           long num_slots, int* status) {
   __shared__ float t_s[DF_MAX_COLS];
   __shared__ float cs_s[128], sn_s[128];     // cos / sin of the row's position for every frequency: shared by all heads
   pdl_wait();
@@ -223,7 +224,8 @@ decode_finalize_qkv_kernel(float* __restrict__ ws, int ldw, int Hq, int Hkv, int
   }
   const int a = stage_shrink(wrow, N, kpad, cols, adapter, row, t_s);      // contains the block barrier
   const __nv_bfloat16* Bs = B_all + (a >= 0 ? static_cast<size_t>(a) * cols * ldb : 0);
-  const int s = slot[row];
+  int s = slot[row];
+  if (s >= 0 && !index_ok(s, num_slots, status)) s = -1;      // checked build: a bad slot is reported, not written
   const int half = hd >> 1, per_head = half >> 3;
   const int rope_units = (Hq + Hkv) * per_head, v_units = kv_size >> 3;
   for (int u = threadIdx.x; u < rope_units + v_units; u += DQ_THREADS) {
@@ -299,7 +301,7 @@ ARTB_EXPORT int artb_decode_finalize_norm(float* ws, int ldw, int M, int N, int 
 ARTB_EXPORT int artb_decode_finalize_qkv(float* ws, int ldw, int M, int Hq, int Hkv, int hd, int kpad, const float* bias,
                                          const int* adapter, const void* B_all, int ldb, int cols, const int* pos,
                                          float theta, const int* slot, void* k_cache, void* v_cache, void* q_out, int ldq,
-                                         cudaStream_t st) {
+                                         long num_slots, int* status, cudaStream_t st) {
   if (M <= 0) return 0;
   if ((hd & 15) || hd > 256 || (ldw & 3) || (ldq & 7) || Hq <= 0 || Hkv <= 0 || !pos || !slot) return ERR_BAD_SHAPE;
   if (adapter && (cols <= 0 || cols > DF_MAX_COLS || (kpad & 3) || (ldb & 7) || !B_all)) return ERR_BAD_SHAPE;
@@ -308,7 +310,7 @@ ARTB_EXPORT int artb_decode_finalize_qkv(float* ws, int ldw, int M, int Hq, int 
       decode_finalize_qkv_kernel, dim3(M), dim3(DQ_THREADS), 0, st, ws, ldw, Hq, Hkv, hd, kpad, bias, adapter,
       reinterpret_cast<const __nv_bfloat16*>(B_all), ldb, cols, pos, log2f(theta), slot,
       reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache),
-      reinterpret_cast<__nv_bfloat16*>(q_out), ldq));
+      reinterpret_cast<__nv_bfloat16*>(q_out), ldq, num_slots, status));
 }
 
 // Programmatic dependent launch for the kernels of the decode step (see pdl_switch in host_utils.h); returns the

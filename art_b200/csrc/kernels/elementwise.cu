@@ -14,6 +14,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "bounds_check.cuh"
 #include "host_utils.h"
 
 namespace artb {
@@ -275,7 +276,7 @@ __global__ void headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dbuf, const __nv
 // ------------------------------------------------------------- row gather/scatter
 // out[i, :] = table[idx[i], :]   (embedding lookup, hidden-row compaction); D % 8 == 0.
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ idx,
-                                   __nv_bfloat16* __restrict__ out, long n, int D, long table_rows) {
+                                   __nv_bfloat16* __restrict__ out, long n, int D, long table_rows, int* status) {
   const int nvec = D >> 3;
   const long total = n * nvec;
   for (long t = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; t < total;
@@ -284,7 +285,8 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, cons
     const int v = t % nvec;
     long src = idx[r];
     bf16x8 val;
-    if (src < 0 || src >= table_rows) {
+    if (src < 0 || src >= table_rows) {      // always guarded (zeros); a checked build also reports it
+      index_ok(src, table_rows, status);
 #pragma unroll
       for (int i = 0; i < 4; ++i) val.v[i] = __floats2bfloat162_rn(0.f, 0.f);
     } else {
@@ -295,7 +297,7 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, cons
 }
 // out[idx[i], :] = src[i, :]  (idx unique); rows not named by idx are left untouched.
 __global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const int64_t* __restrict__ idx,
-                                    __nv_bfloat16* __restrict__ out, long n, int D, long out_rows) {
+                                    __nv_bfloat16* __restrict__ out, long n, int D, long out_rows, int* status) {
   const int nvec = D >> 3;
   const long total = n * nvec;
   for (long t = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; t < total;
@@ -303,7 +305,10 @@ __global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const
     const long r = t / nvec;
     const int v = t % nvec;
     const long dst = idx[r];
-    if (dst < 0 || dst >= out_rows) continue;
+    if (dst < 0 || dst >= out_rows) {        // always guarded (skipped); a checked build also reports it
+      index_ok(dst, out_rows, status);
+      continue;
+    }
     *reinterpret_cast<bf16x8*>(out + dst * D + v * 8) =
         *reinterpret_cast<const bf16x8*>(src + r * D + v * 8);
   }
@@ -407,18 +412,18 @@ ARTB_EXPORT int artb_headnorm_bwd(void* dbuf, const void* xbuf, const void* w, c
 }
 
 ARTB_EXPORT int artb_gather_rows(const void* table, const int64_t* idx, void* out, long n, int D, long table_rows,
-                                 cudaStream_t st) {
+                                 int* status, cudaStream_t st) {
   if (D % 8) return ERR_BAD_SHAPE;
   if (n == 0) return 0;
-  gather_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)table, idx, (bf16*)out, n, D, table_rows);
+  gather_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)table, idx, (bf16*)out, n, D, table_rows, status);
   return (int)cudaGetLastError();
 }
 
 ARTB_EXPORT int artb_scatter_rows(const void* src, const int64_t* idx, void* out, long n, int D, long out_rows,
-                                  cudaStream_t st) {
+                                  int* status, cudaStream_t st) {
   if (D % 8) return ERR_BAD_SHAPE;
   if (n == 0) return 0;
-  scatter_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)src, idx, (bf16*)out, n, D, out_rows);
+  scatter_rows_kernel<<<grid_for(n * (D / 8), 256), 256, 0, st>>>((const bf16*)src, idx, (bf16*)out, n, D, out_rows, status);
   return (int)cudaGetLastError();
 }
 
@@ -436,14 +441,15 @@ namespace artb {
 // row's request (adapter id < 0 = base model, whole row zero), so that the following extra-K
 // GEMM block adds exactly that request's B_a (A_a x).
 __global__ void lora_slot_mask_kernel(__nv_bfloat16* __restrict__ T, int ld, const int* __restrict__ adapter, long M,
-                                      int kpad, int cols) {
+                                      int kpad, int cols, int* status) {
   const int vec = kpad >> 3;
   const long total = M * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long m = i / vec;
     const int c = (i % vec) * 8;
-    const int a = adapter[m];
+    int a = adapter[m];
+    if (a >= 0 && !index_ok(static_cast<long long>(a + 1) * cols - 1, kpad, status)) a = -1;   // slot beyond the buffer
     const int lo = a * cols, hi = lo + cols;
     if (a >= 0 && c >= lo && c + 8 <= hi) continue;  // fully inside the live range
     __nv_bfloat16* p = T + m * ld + c;
@@ -478,10 +484,11 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, long* __r
 }
 }  // namespace artb
 
-ARTB_EXPORT int artb_lora_slot_mask(void* T, int ld, const int* adapter, long M, int kpad, int cols, cudaStream_t st) {
+ARTB_EXPORT int artb_lora_slot_mask(void* T, int ld, const int* adapter, long M, int kpad, int cols, int* status,
+                                    cudaStream_t st) {
   if (M <= 0) return 0;
   if ((kpad & 7) || (ld & 7)) return ERR_BAD_SHAPE;
-  lora_slot_mask_kernel<<<grid_for(M * (kpad / 8), 256), 256, 0, st>>>((bf16*)T, ld, adapter, M, kpad, cols);
+  lora_slot_mask_kernel<<<grid_for(M * (kpad / 8), 256), 256, 0, st>>>((bf16*)T, ld, adapter, M, kpad, cols, status);
   return (int)cudaGetLastError();
 }
 

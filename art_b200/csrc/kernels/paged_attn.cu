@@ -20,8 +20,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "bounds_check.cuh"
 #include "host_utils.h"
-#include "ptx_sm100.cuh"
 
 namespace artb {
 
@@ -59,14 +59,14 @@ __device__ __forceinline__ uint32_t pa_pack2(float a, float b) {
 // qkv [M, ld] holds q | k | v columns (post-RoPE).  slot[m] = block * block_size + offset, or < 0 to skip.
 __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int k_col, int v_col,
                                 const int* __restrict__ slot, __nv_bfloat16* __restrict__ k_cache,
-                                __nv_bfloat16* __restrict__ v_cache, int M, int kv_width) {
+                                __nv_bfloat16* __restrict__ v_cache, int M, int kv_width, long num_slots, int* status) {
   const int vec = kv_width >> 3;
   const long total = static_cast<long>(M) * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const int m = i / vec, c = (i % vec) * 8;
     const int s = slot[m];
-    if (s < 0) continue;
+    if (s < 0 || !index_ok(s, num_slots, status)) continue;
     const uint4 kv = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(m) * ld + k_col + c);
     const uint4 vv = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(m) * ld + v_col + c);
     *reinterpret_cast<uint4*>(k_cache + static_cast<size_t>(s) * kv_width + c) = kv;
@@ -77,13 +77,16 @@ __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, i
 // Gather the first n_tok cached tokens of one sequence into contiguous k | v columns of dst [*, ld].
 __global__ void kv_gather_kernel(const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                                  const int* __restrict__ block_table, int block_size, int n_tok,
-                                 __nv_bfloat16* __restrict__ dst, int ld, int k_col, int v_col, int kv_width) {
+                                 __nv_bfloat16* __restrict__ dst, int ld, int k_col, int v_col, int kv_width,
+                                 long num_blocks, int* status) {
   const int vec = kv_width >> 3;
   const long total = static_cast<long>(n_tok) * vec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const int t = i / vec, c = (i % vec) * 8;
-    const size_t s = static_cast<size_t>(block_table[t / block_size]) * block_size + t % block_size;
+    const int blk = block_table[t / block_size];
+    if (!index_ok(blk, num_blocks, status)) continue;
+    const size_t s = static_cast<size_t>(blk) * block_size + t % block_size;
     *reinterpret_cast<uint4*>(dst + static_cast<size_t>(t) * ld + k_col + c) =
         *reinterpret_cast<const uint4*>(k_cache + s * kv_width + c);
     *reinterpret_cast<uint4*>(dst + static_cast<size_t>(t) * ld + v_col + c) =
@@ -100,7 +103,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                     const int* __restrict__ ctx_len, int block_size, int Hq, int Hkv,
                     __nv_bfloat16* __restrict__ out, int ldo, float* __restrict__ ws, int splits,
-                    float scale_log2) {
+                    float scale_log2, long num_blocks, int* status) {
   constexpr int LD = HD + 8;
   extern __shared__ __align__(16) uint8_t pa_smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(pa_smem);      // [16][LD]
@@ -164,11 +167,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfl
 #pragma unroll 4
       for (int r = lane / CPR; r < PA_KT; r += RPI) {
         const int kt = k0 + r;
-        const bool ok = kt < len;
+        bool ok = kt < len;
         size_t s = 0;
-        if (ok)
-          s = bs_shift >= 0 ? (static_cast<size_t>(bt[kt >> bs_shift]) << bs_shift) + (kt & (block_size - 1))
-                            : static_cast<size_t>(bt[kt / block_size]) * block_size + kt % block_size;
+        if (ok) {
+          const int blk = bt[bs_shift >= 0 ? kt >> bs_shift : kt / block_size];
+          ok = index_ok(blk, num_blocks, status);          // checked build: a bad table entry reads zeros instead
+          s = static_cast<size_t>(blk) * block_size + (bs_shift >= 0 ? kt & (block_size - 1) : kt % block_size);
+        }
         pa_cp16(wK + r * LD + c, kc + s * kv_width, ok);
         pa_cp16(wV + r * LD + c, vc + s * kv_width, ok);
       }
@@ -325,25 +330,27 @@ using namespace artb;
 typedef __nv_bfloat16 bf16;
 
 ARTB_EXPORT int artb_kv_write(const void* qkv, int ld, int k_col, int v_col, const int* slot, void* k_cache,
-                              void* v_cache, int M, int kv_width, cudaStream_t st) {
+                              void* v_cache, int M, int kv_width, long num_slots, int* status, cudaStream_t st) {
   if (M <= 0) return 0;
   if ((kv_width & 7) || (ld & 7) || (k_col & 7) || (v_col & 7)) return ERR_BAD_SHAPE;
   long total = (long)M * (kv_width / 8);
   long blocks = (total + 255) / 256;
   if (blocks > 148L * 16) blocks = 148L * 16;
   kv_write_kernel<<<(unsigned)blocks, 256, 0, st>>>((const bf16*)qkv, ld, k_col, v_col, slot, (bf16*)k_cache,
-                                                   (bf16*)v_cache, M, kv_width);
+                                                   (bf16*)v_cache, M, kv_width, num_slots, status);
   return (int)cudaGetLastError();
 }
 
 ARTB_EXPORT int artb_kv_gather(const void* k_cache, const void* v_cache, const int* block_table, int block_size,
-                               int n_tok, void* dst, int ld, int k_col, int v_col, int kv_width, cudaStream_t st) {
+                               int n_tok, void* dst, int ld, int k_col, int v_col, int kv_width, long num_blocks,
+                               int* status, cudaStream_t st) {
   if (n_tok <= 0) return 0;
   long total = (long)n_tok * (kv_width / 8);
   long blocks = (total + 255) / 256;
   if (blocks > 148L * 16) blocks = 148L * 16;
   kv_gather_kernel<<<(unsigned)blocks, 256, 0, st>>>((const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                                                    block_size, n_tok, (bf16*)dst, ld, k_col, v_col, kv_width);
+                                                    block_size, n_tok, (bf16*)dst, ld, k_col, v_col, kv_width,
+                                                    num_blocks, status);
   return (int)cudaGetLastError();
 }
 
@@ -351,7 +358,7 @@ ARTB_EXPORT int artb_kv_gather(const void* k_cache, const void* v_cache, const i
 ARTB_EXPORT int artb_paged_decode(const void* q, int ldq, const void* k_cache, const void* v_cache,
                                   const int* block_table, int max_blocks, const int* ctx_len, int block_size,
                                   int num_seqs, int Hq, int Hkv, int hd, void* out, int ldo, float* ws, int splits,
-                                  cudaStream_t st) {
+                                  long num_blocks, int* status, cudaStream_t st) {
   if (num_seqs <= 0) return 0;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16 || splits < 1 || (splits > 1 && !ws)) return ERR_BAD_SHAPE;
   int dev_ = 0;
@@ -367,7 +374,7 @@ ARTB_EXPORT int artb_paged_decode(const void* q, int ldq, const void* k_cache, c
     }                                                                                                            \
     launch_kernel(paged_decode_kernel<HD_>, grid, dim3(128), decode_smem<HD_>(), st, (const bf16*)q, ldq,        \
                   (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, ctx_len, block_size, Hq, Hkv, \
-                  (bf16*)out, ldo, ws, splits, scale_log2);                                                      \
+                  (bf16*)out, ldo, ws, splits, scale_log2, num_blocks, status);                                  \
     if (splits > 1) paged_decode_merge_kernel<HD_><<<dim3(num_seqs, Hq), HD_, 0, st>>>(ws, splits, Hq, (bf16*)out, ldo); \
   }
   if (hd == 128) ARTB_PD(128)
@@ -420,5 +427,5 @@ ARTB_EXPORT int artb_paged_decode_noalloc(const void* q, int ldq, const void* k_
   float* ws = decode_static_ws_ptr(&err);
   if (!ws) return err;
   return artb_paged_decode(q, ldq, k_cache, v_cache, block_table, max_blocks, ctx_len, block_size, num_seqs, Hq, Hkv,
-                           hd, out, ldo, ws, splits, st);
+                           hd, out, ldo, ws, splits, /*num_blocks: unknown to this entry point*/ (1L << 40), nullptr, st);
 }

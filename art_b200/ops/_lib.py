@@ -35,6 +35,7 @@ STATUS_NAMES = {
     5: "timeout waiting for a peer rank's flag",
     6: "bad kernel arguments",
     7: "dispatch buffer overflow",
+    8: "index outside its buffer (checked build; the access was skipped)",
 }
 
 
@@ -55,7 +56,7 @@ def _load(name: str) -> ctypes.CDLL:
         from .. import build as _build
 
         try:
-            _build.build_all()
+            _build.build_all(checked=name.endswith("_checked.so"))
         except Exception as e:  # pragma: no cover - depends on toolchain
             raise NativeLibraryError(f"{path} is missing and could not be built: {e}") from e
     try:
@@ -70,8 +71,15 @@ def kernels() -> ctypes.CDLL:
     if _kernels is None:
         with _lock:
             if _kernels is None:
-                _kernels = _load("libartb_kernels.so")
+                # ARTB_BOUNDS_CHECK=1: the build with device-side index checks (python -m art_b200.build --checked);
+                # a missing library is an error, never a silent switch back to the unchecked one
+                _kernels = _load("libartb_kernels_checked.so" if bounds_checked() else "libartb_kernels.so")
     return _kernels
+
+
+def bounds_checked() -> bool:
+    """True when this process runs the kernel library that was compiled with index checks."""
+    return os.environ.get("ARTB_BOUNDS_CHECK", "0") not in ("", "0")
 
 
 def runtime() -> ctypes.CDLL:

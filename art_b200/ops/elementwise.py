@@ -20,8 +20,8 @@ _sigs = {
     "artb_swiglu_fwd": [vp, vp, cl, ci, vp],
     "artb_headnorm_fwd": [vp, vp, vp, ci, ci, ci, ci, ci, cf, vp],
     "artb_headnorm_bwd": [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp],
-    "artb_gather_rows": [vp, vp, vp, cl, ci, cl, vp],
-    "artb_scatter_rows": [vp, vp, vp, cl, ci, cl, vp],
+    "artb_gather_rows": [vp, vp, vp, cl, ci, cl, vp, vp],
+    "artb_scatter_rows": [vp, vp, vp, cl, ci, cl, vp, vp],
     "artb_adv_norm": [vp, vp, vp, vp, ci, vp],
 }
 _bound: dict[str, object] = {}
@@ -98,14 +98,15 @@ def gather_rows(table: torch.Tensor, idx: torch.Tensor, out: torch.Tensor | None
     n, D = idx.numel(), table.shape[1]
     o = torch.empty((n, D), dtype=table.dtype, device=table.device) if out is None else out
     _lib.check_rc(_f("artb_gather_rows")(_lib.ptr(table), _lib.ptr(idx), _lib.ptr(o), n, D, table.shape[0],
-                                         _lib.stream_ptr()), "gather_rows")
+                                         _lib.ptr(_lib.status_word(table.device)), _lib.stream_ptr()), "gather_rows")
     return o
 
 
 def scatter_rows_(src: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     assert idx.dtype == torch.int64 and out.is_contiguous() and src.is_contiguous()
     _lib.check_rc(_f("artb_scatter_rows")(_lib.ptr(src), _lib.ptr(idx), _lib.ptr(out), idx.numel(), out.shape[1],
-                                          out.shape[0], _lib.stream_ptr()), "scatter_rows")
+                                          out.shape[0], _lib.ptr(_lib.status_word(out.device)), _lib.stream_ptr()),
+                  "scatter_rows")
     return out
 
 

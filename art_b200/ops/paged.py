@@ -10,10 +10,10 @@ from . import _lib
 
 vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 _sigs = {
-    "artb_kv_write": [vp, ci, ci, ci, vp, vp, vp, ci, ci, vp],
-    "artb_kv_gather": [vp, vp, vp, ci, ci, vp, ci, ci, ci, ci, vp],
-    "artb_paged_decode": [vp, ci, vp, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp],
-    "artb_lora_slot_mask": [vp, ci, vp, cl, ci, ci, vp],
+    "artb_kv_write": [vp, ci, ci, ci, vp, vp, vp, ci, ci, cl, vp, vp],
+    "artb_kv_gather": [vp, vp, vp, ci, ci, vp, ci, ci, ci, ci, cl, vp, vp],
+    "artb_paged_decode": [vp, ci, vp, vp, vp, ci, vp, ci, ci, ci, ci, ci, vp, ci, vp, ci, cl, vp, vp],
+    "artb_lora_slot_mask": [vp, ci, vp, cl, ci, ci, vp, vp],
     "artb_decode_advance": [vp, vp, vp, vp, vp, vp, ci, ci, vp, ci, vp],
     "artb_sample_partials": [vp, ci, vp, ci, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp],
     "artb_sample_merge": [vp, ci, ci, vp, vp, vp],
@@ -23,7 +23,8 @@ _sigs = {
     "artb_top_logprobs": [vp, cl, vp, ci, ci, ci, vp, vp, vp],
     "artb_set_pdl": [ci],
     "artb_decode_finalize_norm": [vp, ci, ci, ci, ci, vp, vp, ci, vp, vp, ci, ci, vp, ctypes.c_float, vp, ci, vp, ci, vp],
-    "artb_decode_finalize_qkv": [vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, ci, vp, ctypes.c_float, vp, vp, vp, vp, ci, vp],
+    "artb_decode_finalize_qkv": [vp, ci, ci, ci, ci, ci, ci, vp, vp, vp, ci, ci, vp, ctypes.c_float, vp, vp, vp, vp, ci, cl, vp,
+                                 vp],
 }
 _bound: dict[str, object] = {}
 
@@ -38,11 +39,17 @@ def _f(name: str):
     return fn
 
 
+def _cache_slots(cache: torch.Tensor) -> int:
+    """Token slots of a paged cache [blocks, block_size, heads, head_dim] (what a checked build compares slots with)."""
+    return cache.shape[0] * cache.shape[1]
+
+
 def kv_write(qkv: torch.Tensor, k_col: int, v_col: int, slot: torch.Tensor, k_cache: torch.Tensor,
              v_cache: torch.Tensor) -> None:
     kv_width = k_cache.shape[-2] * k_cache.shape[-1]
     _lib.check_rc(_f("artb_kv_write")(_lib.ptr(qkv), qkv.stride(0), k_col, v_col, _lib.ptr(slot), _lib.ptr(k_cache),
-                                      _lib.ptr(v_cache), qkv.shape[0], kv_width, _lib.stream_ptr()), "kv_write")
+                                      _lib.ptr(v_cache), qkv.shape[0], kv_width, _cache_slots(k_cache),
+                                      _lib.ptr(_lib.status_word(qkv.device)), _lib.stream_ptr()), "kv_write")
 
 
 def set_pdl(on: bool) -> bool:
@@ -76,15 +83,16 @@ def decode_finalize_qkv(ws: torch.Tensor, M: int, Hq: int, Hkv: int, hd: int, kp
     _lib.check_rc(_f("artb_decode_finalize_qkv")(
         _lib.ptr(ws), ws.stride(0), M, Hq, Hkv, hd, kpad, _lib.ptr(bias), _lib.ptr(adapter), _lib.ptr(B_all),
         B_all.stride(0) if B_all is not None else 0, cols, _lib.ptr(pos), theta, _lib.ptr(slot), _lib.ptr(k_cache),
-        _lib.ptr(v_cache), _lib.ptr(q_out), q_out.stride(0), _lib.stream_ptr()), "decode_finalize_qkv")
+        _lib.ptr(v_cache), _lib.ptr(q_out), q_out.stride(0), _cache_slots(k_cache), _lib.ptr(_lib.status_word(ws.device)),
+        _lib.stream_ptr()), "decode_finalize_qkv")
 
 
 def kv_gather(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table_row: torch.Tensor, block_size: int, n_tok: int,
               dst: torch.Tensor, k_col: int, v_col: int) -> None:
     kv_width = k_cache.shape[-2] * k_cache.shape[-1]
     _lib.check_rc(_f("artb_kv_gather")(_lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(block_table_row), block_size,
-                                       n_tok, _lib.ptr(dst), dst.stride(0), k_col, v_col, kv_width,
-                                       _lib.stream_ptr()), "kv_gather")
+                                       n_tok, _lib.ptr(dst), dst.stride(0), k_col, v_col, kv_width, k_cache.shape[0],
+                                       _lib.ptr(_lib.status_word(dst.device)), _lib.stream_ptr()), "kv_gather")
 
 
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
@@ -98,13 +106,15 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     _lib.check_rc(_f("artb_paged_decode")(_lib.ptr(q), q.stride(0), _lib.ptr(k_cache), _lib.ptr(v_cache),
                                           _lib.ptr(block_table), block_table.stride(0), _lib.ptr(ctx_len), block_size,
                                           n, Hq, Hkv, hd, _lib.ptr(out), out.stride(0), _lib.ptr(ws), splits,
-                                          _lib.stream_ptr()), "paged_decode")
+                                          k_cache.shape[0], _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr()),
+                  "paged_decode")
     return out
 
 
 def lora_slot_mask_(T: torch.Tensor, adapter: torch.Tensor, cols_per_adapter: int) -> torch.Tensor:
     _lib.check_rc(_f("artb_lora_slot_mask")(_lib.ptr(T), T.stride(0), _lib.ptr(adapter), T.shape[0], T.shape[1],
-                                            cols_per_adapter, _lib.stream_ptr()), "lora_slot_mask")
+                                            cols_per_adapter, _lib.ptr(_lib.status_word(T.device)), _lib.stream_ptr()),
+                  "lora_slot_mask")
     return T
 
 
