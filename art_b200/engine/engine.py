@@ -45,6 +45,7 @@ class SamplingParams:
     frequency_penalty: float = 0.0         # subtracted per occurrence in the output
     logit_bias: dict[int, float] | None = None
     stream_events: bool = True             # False: only the final event is delivered (see Engine.complete)
+    include_stop_str_in_output: bool = False   # keep the matched stop string at the end of the returned text
 
     @property
     def needs_logits(self) -> bool:
@@ -346,7 +347,10 @@ class Engine:
             return
         outbox, self._outbox = self._outbox, {}
         for loop, per_queue in outbox.items():
-            loop.call_soon_threadsafe(_deliver, per_queue)
+            try:
+                loop.call_soon_threadsafe(_deliver, per_queue)
+            except RuntimeError:
+                pass        # that client's event loop is closed: nobody is left to read its events; the others go on
 
     def _release(self, seq: Sequence) -> None:
         if seq.blocks:
@@ -463,9 +467,13 @@ class Engine:
                 toks, n_prompt, adapter, loop, fut = self.score_queue.popleft()
             try:
                 res = self.runner.score(toks, n_prompt, adapter)
-                loop.call_soon_threadsafe(lambda f=fut, r=res: f.done() or f.set_result(r))
+                reply = lambda f=fut, r=res: f.done() or f.set_result(r)      # noqa: E731
             except BaseException as e:  # noqa: BLE001
-                loop.call_soon_threadsafe(lambda f=fut, e=e: f.done() or f.set_exception(e))
+                reply = lambda f=fut, e=e: f.done() or f.set_exception(e)     # noqa: E731
+            try:
+                loop.call_soon_threadsafe(reply)
+            except RuntimeError:
+                pass        # the caller's event loop is closed
         for s in [s for s in self.running + self.prefilling if s.aborted and not s.finished]:
             s.finished, s.finish_reason = True, "abort"
         for s in [s for s in self.prefilling if s.finished]:    # aborted half-way through its prompt
@@ -572,7 +580,10 @@ class Engine:
                 seqs = list(self.waiting) + self.running + self.prefilling
             for s in seqs:
                 if s.loop is not None:
-                    s.loop.call_soon_threadsafe(s.queue.put_nowait, e)
+                    try:
+                        s.loop.call_soon_threadsafe(s.queue.put_nowait, e)
+                    except RuntimeError:
+                        pass            # closed event loop
                 s.finished = True
                 s.done_event.set()
 

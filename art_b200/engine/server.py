@@ -152,7 +152,8 @@ class OpenAIServer:
                               min_p=float(body.get("min_p") or 0.0),
                               n=int(body.get("n") or 1), stop=stop, stop_token_ids=body.get("stop_token_ids"),
                               seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
-                              guided_choice=body.get("guided_choice"))
+                              guided_choice=body.get("guided_choice"),
+                              include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)))
 
     def _render_chat(self, body: dict) -> list[int]:
         tools = body.get("tools")
@@ -173,13 +174,16 @@ class OpenAIServer:
         seq_params = SamplingParams(**{**params.__dict__, "n": 1,
                                        "seed": None if params.seed is None else params.seed + index})
         stops = params.stop or []
-        text = ""
+        ids: list[int] = []
         agen = self.engine.generate(prompt_ids, seq_params, adapter)
         try:
             async for ev in agen:
                 yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason, ev.top_logprobs
                 if stops and not ev.finished:
-                    text += self.tok.decode([ev.token_id])
+                    # the same decoding as the text that is returned (token-by-token decoding differs from it as soon
+                    # as a character spans two tokens), so the cut in _cut_at_stop finds what was matched here
+                    ids.append(ev.token_id)
+                    text = self.tok.decode(ids, skip_special_tokens=True)
                     if any(s in text for s in stops):
                         yield index, None, None, True, "stop", None
                         return
@@ -291,7 +295,8 @@ class OpenAIServer:
                 lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}
                 if params.top_logprobs > 0:
                     lpo["top_logprobs"] = [{srv._token_str(t): l for t, l in (top or []) if t >= 0} for top in tops]
-                choices.append({"index": i, "text": srv.tok.decode(ids, skip_special_tokens=True), "finish_reason": reason,
+                choices.append({"index": i, "text": srv._cut_at_stop(srv.tok.decode(ids, skip_special_tokens=True), params),
+                                "finish_reason": reason,
                                 "logprobs": lpo})
             comp = sum(len(o[0]) for o in out)
             return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": _now(),
@@ -351,12 +356,39 @@ class OpenAIServer:
         except Exception:
             pass
 
+    @staticmethod
+    def _cut_at_stop(text: str, params: SamplingParams | None) -> str:
+        """The text up to the first stop string (the string itself only with ``include_stop_str_in_output``): a request
+        that ended on a stop string returns nothing past it, although the token that completed it may reach further."""
+        if params is None or not params.stop:
+            return text
+        hits = [(text.find(s), s) for s in params.stop if s and s in text]
+        if not hits:
+            return text
+        at, s_ = min(hits)
+        return text[:at + (len(s_) if params.include_stop_str_in_output else 0)]
+
+    @staticmethod
+    def _held_back(text: str, params: SamplingParams | None) -> int:
+        """Characters at the end of ``text`` that may be the beginning of a stop string and are therefore not streamed
+        yet (they are sent, or cut, once the next tokens decide)."""
+        if params is None or not params.stop:
+            return 0
+        keep = 0
+        for s_ in params.stop:
+            for n in range(min(len(s_) - 1, len(text)), 0, -1):
+                if text.endswith(s_[:n]):
+                    keep = max(keep, n)
+                    break
+        return keep
+
     def _strip_eos(self, ids: list[int]) -> list[int]:
         eos = self.engine.eos
         return ids[:-1] if ids and eos is not None and ids[-1] == eos else ids
 
-    def _message_from(self, ids: list[int], tools_on: bool, reason: str) -> tuple[dict, str]:
-        text = self.tok.decode(self._strip_eos(ids), skip_special_tokens=True)
+    def _message_from(self, ids: list[int], tools_on: bool, reason: str, params: SamplingParams | None = None
+                      ) -> tuple[dict, str]:
+        text = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=True), params)
         msg: dict[str, Any] = {"role": "assistant", "content": text}
         if tools_on:
             content, calls = self.tool_parser.extract(text)
@@ -370,7 +402,7 @@ class OpenAIServer:
         out = await self._collect(request, prompt_ids, params, adapter)
         choices = []
         for i, (ids, lps, reason, tops) in enumerate(out):
-            msg, reason = self._message_from(ids, tools_on, reason)
+            msg, reason = self._message_from(ids, tools_on, reason, params)
             choices.append({"index": i, "message": msg, "finish_reason": reason,
                             "logprobs": {"content": [self._logprob_entry(t, lp, top) for t, lp, top in zip(ids, lps, tops)]}})
         comp = sum(len(o[0]) for o in out)
@@ -420,15 +452,21 @@ class OpenAIServer:
                     bufs[i].append(tid)
                     lps = {"content": [self._logprob_entry(tid, lp, top)]}
                     if not tools_on:
-                        full = self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True)
-                        if not full.endswith("�"):
-                            delta["content"] = full[sent_text[i]:]
-                            sent_text[i] = len(full)
+                        full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True), params)
+                        upto = len(full) - self._held_back(full, params)       # a possible stop-string prefix waits
+                        if not full.endswith("�") and upto > sent_text[i]:
+                            delta["content"] = full[sent_text[i]:upto]
+                            sent_text[i] = upto
                 reason = None
                 if fin:
                     reason = why or "stop"
+                    if not tools_on:       # whatever was held back and did not become a stop string
+                        full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True), params)
+                        if len(full) > sent_text[i]:
+                            delta["content"] = delta.get("content", "") + full[sent_text[i]:]
+                            sent_text[i] = len(full)
                     if tools_on:   # tool calls are parsed once the choice is complete; log-probs were streamed per token
-                        msg, reason = self._message_from(bufs[i], True, reason)
+                        msg, reason = self._message_from(bufs[i], True, reason, params)
                         if msg.get("content"):
                             delta["content"] = msg["content"]
                         if msg.get("tool_calls"):

@@ -280,3 +280,25 @@ def test_prefix_cache_hits_are_budgeted_by_attended_tokens(tiny):
     while not all(s.finished for s in seqs):
         eng.step()
     assert all(s.output_ids == first.output_ids for s in seqs)
+
+
+def test_a_closed_client_event_loop_does_not_stop_the_engine(tiny):
+    """A request whose event loop went away (its process-level caller returned) only loses its own events: the
+    stepping thread keeps serving the others."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    loop = asyncio.new_event_loop()
+    orphan = eng.add_request([1, 2, 3], SamplingParams(max_tokens=3, temperature=0.0), None, loop)
+    loop.close()
+    eng.start()
+    try:
+        other = eng.generate_sync([4, 5, 6], SamplingParams(max_tokens=3, temperature=0.0))
+        assert len(other.output_ids) == 3 and eng.error is None
+        import time
+        for _ in range(100):
+            if orphan.finished:
+                break
+            time.sleep(0.05)
+        assert orphan.finished and len(orphan.output_ids) == 3
+    finally:
+        eng.shutdown()

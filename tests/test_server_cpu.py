@@ -185,3 +185,39 @@ def test_http_load_benchmark_runs_against_the_server(tmp_path):
         assert ("ttft_s" in res) == stream
         if stream:      # the prompt was sized to the requested token count under the serving tokenizer
             assert abs(res["avg_prompt_tokens"] - 120) <= 14
+
+
+def test_stop_strings_cut_the_text_like_the_reference_engine(server):
+    """A request that ends on a stop string returns nothing past it (the string itself only on request), streamed or
+    not; text that could be the beginning of a stop string is held back until the next tokens decide."""
+    from art_b200.engine.engine import SamplingParams
+
+    p = SamplingParams(stop=["END", "##"])
+    cut = OpenAIServer._cut_at_stop
+    assert cut("abc END def", p) == "abc " and cut("a##bEND", p) == "a" and cut("plain", p) == "plain"
+    assert cut("abc END def", SamplingParams(stop=["END"], include_stop_str_in_output=True)) == "abc END"
+    assert cut("x", None) == "x"
+    held = OpenAIServer._held_back
+    assert held("abc E", p) == 1 and held("abc EN", p) == 2 and held("abc #", p) == 1 and held("abc", p) == 0
+
+    async def main():
+        async with client(server) as c:
+            # find a string the model really produces, then use a piece from its middle as the stop string
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 24, "temperature": 0}
+            text = (await c.post("/v1/chat/completions", json=body)).json()["choices"][0]["message"]["content"]
+            if len(text) < 6:
+                return
+            stop = text[3:5]
+            want = text[:text.find(stop)]
+            r = (await c.post("/v1/chat/completions", json={**body, "stop": stop})).json()["choices"][0]
+            assert r["finish_reason"] == "stop" and r["message"]["content"] == want
+            r = (await c.post("/v1/chat/completions", json={**body, "stop": [stop], "include_stop_str_in_output": True})).json()
+            assert r["choices"][0]["message"]["content"] == want + stop
+            got = ""
+            async with c.stream("POST", "/v1/chat/completions", json={**body, "stop": stop, "stream": True}) as resp:
+                async for line in resp.aiter_lines():
+                    if line.startswith("data: ") and line != "data: [DONE]":
+                        for ch in json.loads(line[6:])["choices"]:
+                            got += ch["delta"].get("content") or ""
+            assert got == want
+    asyncio.run(main())
