@@ -155,6 +155,32 @@ class OpenAIServer:
                               guided_choice=body.get("guided_choice"),
                               include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)))
 
+    @staticmethod
+    def _forced_tool_call(body: dict) -> str | None:
+        """``tool_choice={"type": "function", "function": {"name": N}}``: the reply must be a call of tool N.  When that
+        tool's parameter schema admits exactly one value per field (one-value enums / consts, which is what
+        ``art.guided_completion.freeze_tool_schema`` builds for distillation), the whole call is determined and is
+        returned here as Hermes-format text; the request then runs like ``guided_choice`` with that one candidate.
+        Schemas that leave freedom would need grammar-constrained decoding, which this server does not have: 400."""
+        choice = body.get("tool_choice")
+        if not isinstance(choice, dict) or choice.get("type") != "function":
+            return None
+        name = (choice.get("function") or {}).get("name")
+        tool = next((t for t in body.get("tools") or [] if (t.get("function") or {}).get("name") == name), None)
+        if tool is None:
+            raise HTTPException(status_code=400, detail=f"tool_choice names {name!r}, which is not among the tools")
+        schema = tool["function"].get("parameters") or {}
+        args: dict = {}
+        for key, spec in (schema.get("properties") or {}).items():
+            if "const" in spec:
+                args[key] = spec["const"]
+            elif isinstance(spec.get("enum"), list) and len(spec["enum"]) == 1:
+                args[key] = spec["enum"][0]
+            else:
+                raise HTTPException(status_code=400, detail=f"a named tool_choice needs a schema with one value per field "
+                                                            f"(field {key!r} is free); use tool_choice=\"auto\" instead")
+        return "<tool_call>\n" + json.dumps({"name": name, "arguments": args}) + "\n</tool_call>"
+
     def _render_chat(self, body: dict) -> list[int]:
         tools = body.get("tools")
         if body.get("tool_choice") == "none":
@@ -264,9 +290,12 @@ class OpenAIServer:
                 raise HTTPException(status_code=400, detail=f"prompt has {len(prompt_ids)} tokens; the maximum context "
                                                             f"length is {srv.engine.max_model_len}")
             params = srv._params(body, len(prompt_ids))
+            forced = srv._forced_tool_call(body)
+            if forced is not None:
+                params.guided_choice = [forced]       # the call is teacher-forced and comes back with its log-probs
             rid = "chatcmpl-" + uuid.uuid4().hex
             model_name = body.get("model") or srv.base_model_name
-            tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and srv.auto_tools
+            tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and (srv.auto_tools or forced is not None)
             if body.get("stream"):
                 include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
                 return StreamingResponse(srv._counted(srv._chat_stream(request, rid, model_name, prompt_ids, params, adapter,

@@ -221,3 +221,44 @@ def test_stop_strings_cut_the_text_like_the_reference_engine(server):
                             got += ch["delta"].get("content") or ""
             assert got == want
     asyncio.run(main())
+
+
+@pytest.fixture()
+def long_server():
+    cfg = PRESETS["tiny"]
+    tok = ByteChatTokenizer(cfg.vocab_size)
+    eng = Engine(ReferenceRunner(cfg, init_base_weights(cfg, seed=0), LoraConfig(), max_loras=2), BlockManager(1024, 4, True),
+                 eos_token_id=tok.eos_token_id, max_loras=2, num_scheduler_steps=2, max_model_len=2048)
+    eng.set_adapter("agent-001", init_lora(cfg, LoraConfig()))
+    eng.start()
+    yield OpenAIServer(eng, tok, "tiny-base")
+    eng.shutdown()
+
+
+def test_named_tool_choice_with_a_frozen_schema_forces_the_call(long_server):
+    server = long_server
+    """The distillation path of ``get_guided_completion_params``: a teacher's tool call becomes a one-value schema plus
+    a named ``tool_choice``; the student's reply is that call, teacher-forced, with its log-probs."""
+    from art_b200.guided_completion import freeze_tool_schema
+
+    tool = {"type": "function", "function": {"name": "move", "description": "", "parameters": {
+        "type": "object", "properties": {"direction": {"type": "string"}, "steps": {"type": "integer"}}}}}
+    frozen = freeze_tool_schema(tool, {"direction": "left", "steps": 2})
+
+    async def main():
+        async with client(server) as c:
+            body = {"model": "agent-001", "messages": [{"role": "user", "content": "go"}], "tools": [frozen],
+                    "tool_choice": {"type": "function", "function": {"name": "move"}}, "max_tokens": 64}
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 200, r.text
+            ch = r.json()["choices"][0]
+            assert ch["finish_reason"] == "tool_calls"
+            call = ch["message"]["tool_calls"][0]["function"]
+            assert call["name"] == "move" and json.loads(call["arguments"]) == {"direction": "left", "steps": 2}
+            assert len(ch["logprobs"]["content"]) > 5 and all(e["logprob"] <= 0 for e in ch["logprobs"]["content"])
+            # a schema that leaves a field free cannot be forced without constrained decoding
+            r = await c.post("/v1/chat/completions", json={**body, "tools": [tool]})
+            assert r.status_code == 400 and "free" in r.json()["detail"]
+            r = await c.post("/v1/chat/completions", json={**body, "tool_choice": {"type": "function", "function": {"name": "nope"}}})
+            assert r.status_code == 400
+    asyncio.run(main())
