@@ -5,7 +5,7 @@ import argparse
 import asyncio
 import random
 
-from examples import game_2048, tic_tac_toe, yes_no_maybe
+from examples import game_2048, pipelined, self_play, tic_tac_toe, tool_use, yes_no_maybe
 from examples.common import add_model_flags
 
 
@@ -60,3 +60,34 @@ def test_each_example_loop_runs_one_step(tmp_path):
         # equal rewards give GRPO nothing to learn from, in which case the step is skipped without a checkpoint
         assert (out / "0000" / "adapter_model.safetensors").exists()
         assert (out / "trajectories" / "train" / "0000.yaml").exists()
+
+
+def test_self_play_teacher_and_tool_use_rules():
+    assert self_play.teacher_move(list("XX.OO...."), "X") == "C1"          # win
+    assert self_play.teacher_move(list("XX.O....."), "O") == "C1"          # block
+    assert self_play.teacher_move(list("........."), "X") == "B2"          # centre
+    assert tool_use.outcome("rock", "scissors") == 1.0 and tool_use.outcome("rock", "rock") == 0.5
+    assert tool_use.outcome("rock", "paper") == 0.0 and tool_use.outcome(None, "paper") == -1.0
+
+    class Msg:
+        tool_calls = None
+        content = "I choose Paper, not rock"
+    assert tool_use.move_from(Msg()) == "paper"
+    assert pipelined.reward_for("the answer is 57", 57) == 1.0 and pipelined.reward_for("58", 57) > 0.49
+    assert pipelined.reward_for(None, 57) == 0.0
+
+
+def test_self_play_tool_use_and_pipelined_loops_run(tmp_path):
+    # two trajectories per game, grouped by side, a quarter of the moves forced through guided_choice
+    a = _args("sp", tmp_path / "sp", teacher=0.5, seed=1, group_size=4)
+    hist = asyncio.run(self_play.main(a))
+    assert len(hist) == 1
+    # tool definitions in the prompt need a longer context than the other loops
+    a = _args("tu", tmp_path / "tu", group_size=2, max_seq_length=4096)
+    assert len(asyncio.run(tool_use.main(a))) == 1
+    # two pipelined batches, validation logged, training without the sampled log-probs
+    a = _args("pl", tmp_path / "pl", steps=2, groups=2, group_size=2, val_size=2, seed=0, keep_logprobs=False)
+    hist = asyncio.run(pipelined.main(a))
+    assert len(hist) == 2
+    out = tmp_path / "pl" / "pl" / "models" / "001"
+    assert (out / "trajectories" / "val").is_dir() and (out / "trajectories" / "train").is_dir()
