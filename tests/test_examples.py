@@ -5,7 +5,7 @@ import argparse
 import asyncio
 import random
 
-from examples import game_2048, pipelined, self_play, tic_tac_toe, tool_use, yes_no_maybe
+from examples import comparison_models, game_2048, pipelined, self_play, tic_tac_toe, tool_use, yes_no_maybe
 from examples.common import add_model_flags
 
 
@@ -91,3 +91,16 @@ def test_self_play_tool_use_and_pipelined_loops_run(tmp_path):
     assert len(hist) == 2
     out = tmp_path / "pl" / "pl" / "models" / "001"
     assert (out / "trajectories" / "val").is_dir() and (out / "trajectories" / "train").is_dir()
+
+
+def test_comparison_models_are_logged_and_charted_through_the_same_api(tmp_path):
+    a = _args("cmp", tmp_path / "cmp", steps=1, groups=1, group_size=4, val_size=3, seed=0, compare_name="prompted",
+              compare_model=None, compare_url=None, compare_key=None, chart=str(tmp_path / "progress.svg"),
+              bars=str(tmp_path / "bars.svg"))
+    out = asyncio.run(comparison_models.main(a))
+    assert set(out["scores"]) == {"001", "prompted"} and len(out["scores"]["001"]) == 2 and len(out["scores"]["prompted"]) == 1
+    root = tmp_path / "cmp" / "cmp" / "models"
+    assert (root / "prompted" / "trajectories" / "val" / "0000.yaml").exists() and (root / "prompted" / "model.json").exists()
+    assert (root / "001" / "trajectories" / "val").is_dir()
+    assert out["rows"] >= 3 * 3
+    assert (tmp_path / "progress.svg").read_text().startswith("<svg") and (tmp_path / "bars.svg").read_text().startswith("<svg")
