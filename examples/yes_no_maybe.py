@@ -33,13 +33,17 @@ def reward_for(content: str | None) -> float:
     return REWARDS.get((content or "").strip(), 0.0)
 
 
-def make_rollout(prompt_list: list[str]):
+def make_rollout(prompt_list: list[str], no_thinking: bool = False):
+    # new "thinking" model families (the reference's dev/new_models/qwen3_try.py): switch the reasoning preamble off
+    # through the chat template, so that the answer is the one word the reward looks for
+    extra = {"extra_body": {"chat_template_kwargs": {"enable_thinking": False}}} if no_thinking else {}
+
     async def rollout(model: art.TrainableModel, client, step: int) -> art.Trajectory:
         rollout.calls += 1
         prompt = prompt_list[(rollout.calls // rollout.group_size) % len(prompt_list)]
         messages: art.Messages = [{"role": "user", "content": prompt}]
         completion = await client.chat.completions.create(messages=messages, model=model.get_inference_name(),
-                                                          max_tokens=100, timeout=100)
+                                                          max_tokens=100, timeout=100, **extra)
         choice = completion.choices[0]
         return art.Trajectory(messages_and_choices=[*messages, choice], reward=reward_for(choice.message.content))
 
@@ -49,7 +53,7 @@ def make_rollout(prompt_list: list[str]):
 
 async def main(a) -> list[float]:
     backend = LocalBackend(in_process=True, path=a.path)
-    rollout = make_rollout(prompts())
+    rollout = make_rollout(prompts(), getattr(a, "no_thinking", False))
     rollout.group_size = a.group_size
     try:
         return await train_loop(make_model(a), backend, rollout, steps=a.steps, groups=a.groups, group_size=a.group_size,
@@ -61,5 +65,7 @@ async def main(a) -> list[float]:
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__)
     add_model_flags(ap, "yes-no-maybe")
+    ap.add_argument("--no-thinking", action="store_true",
+                    help="pass chat_template_kwargs={'enable_thinking': False} (Qwen3-style chat templates)")
     ap.set_defaults(lr=1e-4, groups=36, group_size=32, steps=1000)
     asyncio.run(main(ap.parse_args()))

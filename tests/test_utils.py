@@ -185,3 +185,39 @@ def test_small_m_gemm_plan_fills_one_wave_only():
                     bn2, sp2 = plan_small_m(M, N, K, pair=True)
                     units = (M // 256) * ((N + 255) // 256)
                     assert bn2 == 256 and (sp2 == 1 or units * sp2 <= 74), (M, N, K, sp2)
+
+
+def test_deploy_model_command_pulls_then_deploys(tmp_path, monkeypatch):
+    """``deploy-model``: with ``--step latest`` every checkpoint is pulled and the newest local step is deployed; with a
+    number only that step is pulled; a failed job raises."""
+    import asyncio
+
+    from art_b200.utils import deploy_cli
+    from art_b200.utils.deploy_model import LoRADeploymentJob, LoRADeploymentJobStatus
+
+    calls = []
+
+    async def fake_pull(**kw):
+        calls.append(("pull", kw.get("step")))
+        d = tmp_path / kw["project"] / "models" / kw["model_name"]
+        for s in ((3, 7) if kw.get("step") is None else (kw["step"],)):
+            (d / f"{s:04d}").mkdir(parents=True, exist_ok=True)
+
+    async def fake_deploy(**kw):
+        calls.append(("deploy", kw["step"], kw["pull_s3"], kw["deploy_to"]))
+        ok = kw["step"] != 5
+        return LoRADeploymentJob(status=LoRADeploymentJobStatus.COMPLETE if ok else LoRADeploymentJobStatus.FAILED,
+                                 job_id="job-1", model_name="acct/agent-001", failure_reason=None if ok else "quota")
+
+    monkeypatch.setenv("BACKUP_BUCKET", "bucket")
+    base = ["--project", "p", "--model", "agent-001", "--base-model", "random:tiny", "--art-path", str(tmp_path)]
+    job = asyncio.run(deploy_cli.deploy(deploy_cli.parse_args(base), pull=fake_pull, deploy_fn=fake_deploy))
+    assert job.model_name == "acct/agent-001" and calls == [("pull", None), ("deploy", 7, False, "together")]
+    calls.clear()
+    asyncio.run(deploy_cli.deploy(deploy_cli.parse_args(base + ["--step", "3"]), pull=fake_pull, deploy_fn=fake_deploy))
+    assert calls == [("pull", 3), ("deploy", 3, False, "together")]
+    with pytest.raises(RuntimeError, match="quota"):
+        asyncio.run(deploy_cli.deploy(deploy_cli.parse_args(base + ["--step", "5"]), pull=fake_pull, deploy_fn=fake_deploy))
+    monkeypatch.delenv("BACKUP_BUCKET")
+    with pytest.raises(SystemExit):
+        asyncio.run(deploy_cli.deploy(deploy_cli.parse_args(base), pull=fake_pull, deploy_fn=fake_deploy))
