@@ -36,14 +36,52 @@ def save_adapter(directory: str, state: dict[str, torch.Tensor], lcfg: LoraConfi
     from safetensors.torch import save_file
 
     os.makedirs(directory, exist_ok=True)
-    tensors = {k: v.detach().to("cpu", dtype).contiguous() for k, v in state.items()}
     tmp = os.path.join(directory, ADAPTER_WEIGHTS + ".tmp")
-    save_file(tensors, tmp, metadata={"format": "pt"})
+    if not _write_consecutive_views(tmp, state, dtype):
+        tensors = {k: v.detach().to("cpu", dtype).contiguous() for k, v in state.items()}
+        save_file(tensors, tmp, metadata={"format": "pt"})
     os.replace(tmp, os.path.join(directory, ADAPTER_WEIGHTS))
     tmpc = os.path.join(directory, ADAPTER_CONFIG + ".tmp")
     with open(tmpc, "w") as f:
         json.dump(adapter_config_dict(lcfg, base_model), f, indent=2)
     os.replace(tmpc, os.path.join(directory, ADAPTER_CONFIG))
+
+
+_ST_DTYPES = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16"}
+
+
+def _write_consecutive_views(path: str, state: dict[str, torch.Tensor], dtype: torch.dtype) -> bool:
+    """Fast path of :func:`save_adapter`: when the tensors are host views that lie back to back in ONE buffer (the
+    trainer's flat master copy), the safetensors file is its header followed by that buffer, written with a single
+    ``write`` and no intermediate copy (the generic writer copies every tensor twice before it writes; for the 81 MB
+    adapter of a 7B model that is 100 ms and more against about 40 ms, on the critical path of a training call).
+    Returns False when the layout is anything else; the caller then uses the generic writer."""
+    import struct
+
+    if dtype not in _ST_DTYPES or not state:
+        return False
+    items = list(state.items())
+    first = items[0][1]
+    if first.device.type != "cpu":
+        return False
+    esize = first.element_size()
+    header: dict = {"__metadata__": {"format": "pt"}}
+    ptr = first.data_ptr()
+    off = 0
+    for name, t in items:
+        if t.device.type != "cpu" or t.dtype != dtype or not t.is_contiguous() or t.data_ptr() != ptr + off or t.requires_grad:
+            return False
+        n = t.numel() * esize
+        header[name] = {"dtype": _ST_DTYPES[dtype], "shape": list(t.shape), "data_offsets": [off, off + n]}
+        off += n
+    blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    blob += b" " * (-len(blob) % 8)                      # the data section starts on an 8-byte boundary
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        whole = torch.as_strided(first, (off // esize,), (1,))     # all the views as one run of their shared storage
+        f.write(memoryview(whole.view(torch.uint8).numpy()))
+    return True
 
 
 def load_adapter(directory: str, device: str | torch.device = "cpu") -> tuple[dict[str, torch.Tensor], LoraConfig]:

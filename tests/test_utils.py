@@ -221,3 +221,32 @@ def test_deploy_model_command_pulls_then_deploys(tmp_path, monkeypatch):
     monkeypatch.delenv("BACKUP_BUCKET")
     with pytest.raises(SystemExit):
         asyncio.run(deploy_cli.deploy(deploy_cli.parse_args(base), pull=fake_pull, deploy_fn=fake_deploy))
+
+
+def test_adapter_writer_fast_path_matches_the_generic_writer(tmp_path):
+    """Views that lie back to back in the trainer's flat buffer are written as header + one buffer; the file loads to the
+    same tensors as the generic writer's, and any other layout falls back to the generic writer."""
+    import torch
+    from safetensors.torch import load_file
+
+    from art_b200.models import peft_io
+    from art_b200.models.config import PRESETS
+    from art_b200.models.native import LoraFlat
+    from art_b200.models.weights import LoraConfig, init_lora
+
+    cfg, lcfg = PRESETS["tiny"], LoraConfig()
+    lora = init_lora(cfg, lcfg, seed=0)
+    g = torch.Generator().manual_seed(0)
+    lora = {k: torch.randn(v.shape, generator=g) for k, v in lora.items()}
+    flat = LoraFlat(cfg, lcfg, lora, "cpu")
+    views = dict(flat.views)
+    assert peft_io._write_consecutive_views(str(tmp_path / "probe.safetensors"), views, torch.float32)
+    assert not peft_io._write_consecutive_views(str(tmp_path / "probe2.safetensors"), lora, torch.float32)       # separate tensors
+    assert not peft_io._write_consecutive_views(str(tmp_path / "probe3.safetensors"), views, torch.bfloat16)     # needs a cast
+    peft_io.save_adapter(str(tmp_path / "fast"), views, lcfg, "random:tiny")
+    peft_io.save_adapter(str(tmp_path / "generic"), lora, lcfg, "random:tiny")
+    a = load_file(str(tmp_path / "fast" / "adapter_model.safetensors"))
+    b = load_file(str(tmp_path / "generic" / "adapter_model.safetensors"))
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    st, got_cfg = peft_io.load_adapter(str(tmp_path / "fast"))
+    assert got_cfg.r == lcfg.r and all(torch.equal(st[k], lora[k]) for k in lora)
