@@ -280,8 +280,11 @@ class LocalBackend(Backend):
                         bar.update(1)
                         bar.set_postfix(result)
                     break
-                except (ActorDiedError, asyncio.TimeoutError) as e:
-                    if attempt >= max_restarts:
+                except Exception as e:  # noqa: BLE001 - filtered below
+                    # a rank whose process is gone may surface as the peers' failed collective rather than as its own
+                    # ActorDiedError; anything else (a bug in the step, bad data) is not a case for a restart
+                    died = isinstance(e, (ActorDiedError, asyncio.TimeoutError)) or _has_dead_rank(service)
+                    if not died or attempt >= max_restarts:
                         raise
                     attempt += 1
                     why = "exceeded step_timeout_s" if isinstance(e, asyncio.TimeoutError) else str(e)
@@ -343,6 +346,15 @@ class LocalBackend(Backend):
         return await deploy_model(deploy_to=deploy_to, model=model, step=step, s3_bucket=s3_bucket, prefix=prefix,
                                   verbose=verbose, pull_s3=pull_s3, wait_for_completion=wait_for_completion,
                                   art_path=self._path)
+
+
+def _has_dead_rank(service) -> bool:
+    """True when the service, or a rank of a multi-rank service, lives in a child process that has exited."""
+    for r in getattr(service, "ranks", [service]):
+        p = getattr(r, "_process", None)
+        if p is not None and not p.is_alive():
+            return True
+    return False
 
 
 class _Done:

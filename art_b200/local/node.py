@@ -62,14 +62,29 @@ class NodeService:
     async def train(self, disk_packed_tensors: DiskPackedTensors, config: types.TrainConfig, _config: dev.TrainConfig,
                     verbose: bool = False) -> AsyncIterator[dict[str, float]]:
         others = [asyncio.ensure_future(_drain(w.train(disk_packed_tensors, config, _config, False))) for w in self.workers]
+        lead = self.leader.train(disk_packed_tensors, config, _config, verbose).__aiter__()
+        nxt = None
         try:
-            async for metrics in self.leader.train(disk_packed_tensors, config, _config, verbose):
-                for t in others:              # a rank that failed must not leave the rest waiting in a collective
-                    if t.done() and t.exception() is not None:
-                        raise t.exception()
+            while True:
+                # the leader's next result races the workers: a rank that failed (its process died, its step raised)
+                # is reported at once instead of after the leader's collective has run into its time limit
+                nxt = asyncio.ensure_future(lead.__anext__())
+                while not nxt.done():
+                    await asyncio.wait({nxt, *[t for t in others if not t.done()]}, return_when=asyncio.FIRST_COMPLETED)
+                    for t in others:
+                        if t.done() and not t.cancelled() and t.exception() is not None:
+                            raise t.exception()
+                    if all(t.done() for t in others) and not nxt.done():
+                        await asyncio.wait({nxt})
+                try:
+                    metrics = nxt.result()
+                except StopAsyncIteration:
+                    break
                 yield metrics
             await asyncio.gather(*others)
         finally:
+            if nxt is not None and not nxt.done():
+                nxt.cancel()
             for t in others:
                 if not t.done():
                     t.cancel()

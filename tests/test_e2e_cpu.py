@@ -191,3 +191,38 @@ def test_service_process_is_restarted_from_the_last_checkpoint(tmp_path):
             backend.close()
 
     asyncio.run(main())
+
+
+def test_two_rank_service_recovers_from_a_dead_worker(tmp_path):
+    """A model over two data-parallel ranks (gloo, CPU), each in its own process: one worker is killed between two
+    train calls (a host-made failure); the failure is seen at once, every rank is replaced, and training goes on from
+    the last checkpoint."""
+    async def main():
+        backend = LocalBackend(in_process=False, path=str(tmp_path))
+        model = art.TrainableModel(name="agent-dp", project="proj", base_model="random:tiny",
+                                   _internal_config={"init_args": {"architecture": ARCH, "max_seq_length": 2048},
+                                                     "engine_args": {"num_scheduler_steps": 4, "max_model_len": 512,
+                                                                     "data_parallel_size": 2}})
+        try:
+            await model.register(backend)
+            groups = await art.gather_trajectory_groups(
+                (art.TrajectoryGroup(rollout(model, f"q{g}", i) for i in range(4)) for g in range(2)), pbar_desc=None)
+            await model.train(groups, config=art.TrainConfig(learning_rate=1e-2), _config={"rows_per_optimizer_step": 2})
+            assert await model.get_step() == 1
+            svc = backend._services["agent-dp"]
+            await svc.flush_checkpoints()
+            worker = svc.workers[0]
+            worker._process.kill()
+            worker._process.join(10)
+            import time
+            t0 = time.monotonic()
+            await model.train(groups, config=art.TrainConfig(learning_rate=1e-2), _config={"rows_per_optimizer_step": 2})
+            assert backend.service_restarts == {"agent-dp": 1} and await model.get_step() == 2
+            assert time.monotonic() - t0 < 120          # noticed through the dead process, not through a collective's time limit
+            t = await rollout(model, "q0", 3)
+            assert len(t.messages_and_choices[-1].logprobs.content) == 6
+        finally:
+            await model.openai_client().close()
+            backend.close()
+
+    asyncio.run(main())
