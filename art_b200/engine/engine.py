@@ -136,6 +136,8 @@ class Engine:
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self._outbox: dict = {}     # event loop -> {queue: [TokenEvent, ...]} of the scheduler step in progress
+        self.max_recoveries = 3     # automatic restarts of the stepping thread after an error (see recover())
+        self.recoveries = 0
         self.score_queue: deque = deque()
         self.adapters: dict[str, int] = {}
         self.adapter_version = [0] * max_loras
@@ -248,7 +250,12 @@ class Engine:
                       loop: asyncio.AbstractEventLoop | None) -> Sequence:
         """Validate a request and build its sequence (not yet queued)."""
         if self.error is not None:
-            raise RuntimeError("engine stopped after an error") from self.error
+            # a request arriving after a failure restarts the engine, a bounded number of times (a failure that comes
+            # back every time is a bug to look at, not something to loop on)
+            if self.recoveries < self.max_recoveries and self._thread is not None:
+                self.recover()
+            else:
+                raise RuntimeError("engine stopped after an error") from self.error
         if len(prompt_ids) + 1 > self.max_model_len:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_model_len}")
         adapter = -1
@@ -587,11 +594,42 @@ class Engine:
                 s.finished = True
                 s.done_event.set()
 
+    def recover(self) -> bool:
+        """Bring the engine back after its stepping thread stopped on an error: every request that was in flight has
+        already been failed; their blocks are returned, the prefix cache and the captured graphs are dropped (their
+        contents may be half written), and a new stepping thread starts.  Returns False when there was nothing to
+        recover from.  Adapters and weights stay as they are."""
+        if self.error is None:
+            return False
+        t, self._thread = self._thread, None
+        if t is not None:
+            t.join(timeout=10)
+        with self._lock:
+            dead = list(self.waiting) + self.running + self.prefilling
+            self.waiting.clear()
+            self.running, self.prefilling = [], []
+        for s in dead:
+            if s.blocks:
+                self.bm.free(s.blocks)
+                s.blocks = []
+        self.bm.reset_prefix_cache()
+        self._outbox = {}
+        drop = getattr(self.runner, "drop_graphs", None)
+        if drop is not None:
+            drop()
+        self.recoveries = self.recoveries + 1
+        self.error = None
+        self._stop = False
+        self._run_gate.set()
+        self.start()
+        return True
+
     def metrics(self) -> dict:
         st = self.bm.stats()
         dt = max(1e-9, time.monotonic() - self.stats.started)
         return {"running": len(self.running), "waiting": len(self.waiting), "prompt_tokens": self.stats.prompt_tokens,
                 "generated_tokens": self.stats.generated_tokens, "preemptions": self.stats.preemptions,
+                "recoveries": self.recoveries,
                 "kv_free_blocks": self.bm.num_free, "kv_total_blocks": self.bm.num_blocks,
                 "kv_utilisation": 1.0 - self.bm.num_free / self.bm.num_blocks, "tokens_per_s": self.stats.generated_tokens / dt,
                 "decode_steps": self.stats.decode_steps, "prefill_steps": self.stats.prefill_steps,

@@ -248,9 +248,15 @@ class OpenAIServer:
 
         @app.get("/health")
         async def health():
-            if srv.engine.error is not None:
-                raise HTTPException(status_code=500, detail=repr(srv.engine.error))
-            return {"status": "ok"}
+            eng = srv.engine
+            if eng.error is not None:
+                # a health probe restarts a stopped engine while its restart budget lasts; past it the probe fails and
+                # whoever supervises the server replaces the process
+                err = repr(eng.error)
+                if eng.recoveries >= eng.max_recoveries or not await asyncio.to_thread(eng.recover):
+                    raise HTTPException(status_code=500, detail=err)
+                return {"status": "recovered", "recoveries": eng.recoveries, "after": err}
+            return {"status": "ok", "recoveries": eng.recoveries}
 
         @app.get("/metrics")
         async def metrics():

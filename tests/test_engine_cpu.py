@@ -302,3 +302,44 @@ def test_a_closed_client_event_loop_does_not_stop_the_engine(tiny):
         assert orphan.finished and len(orphan.output_ids) == 3
     finally:
         eng.shutdown()
+
+
+def test_engine_recovers_after_its_stepping_thread_failed(tiny):
+    """A step that raises fails the requests in flight and stops the thread; the next request restarts the engine
+    (blocks returned, prefix cache dropped) a bounded number of times."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    eng.start()
+    real = eng.runner.decode
+    state = {"fail": 1}
+
+    def flaky(views, steps):
+        if state["fail"] > 0:
+            state["fail"] -= 1
+            raise RuntimeError("injected step failure")
+        return real(views, steps)
+
+    eng.runner.decode = flaky
+    try:
+        async def first():
+            with pytest.raises(RuntimeError, match="injected"):
+                async for _ in eng.generate([1, 2, 3], SamplingParams(max_tokens=4, temperature=0.0)):
+                    pass
+        asyncio.run(first())
+        for _ in range(100):
+            if eng.error is not None:
+                break
+            time.sleep(0.02)
+        assert eng.error is not None
+        free_before = eng.bm.num_free
+        seq = eng.generate_sync([1, 2, 3], SamplingParams(max_tokens=4, temperature=0.0))      # restarts the engine
+        assert len(seq.output_ids) == 4 and eng.error is None and eng.recoveries == 1
+        assert eng.bm.num_free >= free_before
+        # the budget is finite
+        eng.max_recoveries = 1
+        state["fail"] = 1
+        with pytest.raises(RuntimeError):
+            eng.generate_sync([4, 5, 6], SamplingParams(max_tokens=4, temperature=0.0))
+            eng.generate_sync([4, 5, 6], SamplingParams(max_tokens=4, temperature=0.0))
+    finally:
+        eng.shutdown()

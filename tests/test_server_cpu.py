@@ -262,3 +262,40 @@ def test_named_tool_choice_with_a_frozen_schema_forces_the_call(long_server):
             r = await c.post("/v1/chat/completions", json={**body, "tool_choice": {"type": "function", "function": {"name": "nope"}}})
             assert r.status_code == 400
     asyncio.run(main())
+
+
+def test_health_probe_restarts_a_stopped_engine_until_the_budget_is_spent(long_server):
+    srv = long_server
+    eng = srv.engine
+    real = eng.runner.decode
+    state = {"fail": 1}
+
+    def flaky(views, steps):
+        if state["fail"] > 0:
+            state["fail"] -= 1
+            raise RuntimeError("injected step failure")
+        return real(views, steps)
+
+    eng.runner.decode = flaky
+    eng.max_recoveries = 1
+
+    async def main():
+        body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4}
+        transport = httpx.ASGITransport(app=srv.app, raise_app_exceptions=False)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t",
+                                     headers={"Authorization": "Bearer default"}) as c:
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 500
+            r = await c.get("/health")
+            assert r.status_code == 200 and r.json()["status"] == "recovered" and "injected" in r.json()["after"]
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 4
+            assert (await c.get("/metrics")).json()["recoveries"] == 1
+            state["fail"] = 1
+            r = await c.post("/v1/chat/completions", json=body)
+            assert r.status_code == 500
+            assert (await c.get("/health")).status_code == 500          # budget spent
+    try:
+        asyncio.run(main())
+    finally:
+        eng.runner.decode = real
