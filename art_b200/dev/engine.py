@@ -79,6 +79,53 @@ class EngineArgs(TypedDict, total=False):
     worker_cls: str
     calculate_kv_scales: bool | None
     additional_config: dict[str, Any] | None
+    # native: the number of KV-cache blocks, instead of sizing the cache from gpu_memory_utilization
+    num_gpu_blocks_override: int | None
+    allowed_local_media_path: Any
+    code_revision: Any
+    device: Any
+    disable_async_output_proc: Any
+    disable_logprobs_during_spec_decoding: Any
+    disable_mm_preprocessor_cache: Any
+    disable_sliding_window: Any
+    enable_lora_bias: Any
+    enable_prompt_adapter: Any
+    fully_sharded_loras: Any
+    ignore_patterns: Any
+    limit_mm_per_prompt: Any
+    logits_processor_pattern: Any
+    long_lora_scaling_factors: Any
+    long_prefill_token_threshold: Any
+    lora_extra_vocab_size: Any
+    max_long_partial_prefills: Any
+    max_num_partial_prefills: Any
+    max_parallel_loading_workers: Any
+    max_prompt_adapter_token: Any
+    max_prompt_adapters: Any
+    mm_processor_kwargs: Any
+    model_impl: Any
+    model_loader_extra_config: Any
+    ngram_prompt_lookup_max: Any
+    ngram_prompt_lookup_min: Any
+    num_lookahead_slots: Any
+    override_generation_config: Any
+    override_neuron_config: Any
+    qlora_adapter_name_or_path: Any
+    ray_workers_use_nsight: Any
+    scheduler_cls: Any
+    scheduler_delay_factor: Any
+    spec_decoding_acceptance_method: Any
+    speculative_disable_by_batch_size: Any
+    speculative_disable_mqa_scorer: Any
+    speculative_draft_tensor_parallel_size: Any
+    speculative_max_model_len: Any
+    speculative_model_quantization: Any
+    tokenizer_pool_extra_config: Any
+    tokenizer_pool_size: Any
+    tokenizer_revision: Any
+    typical_acceptance_sampler_posterior_alpha: Any
+    typical_acceptance_sampler_posterior_threshold: Any
+    use_v2_block_manager: Any
 
 
 NATIVE_ENGINE_KEYS = frozenset({
@@ -87,7 +134,7 @@ NATIVE_ENGINE_KEYS = frozenset({
     "pipeline_parallel_size", "context_parallel_size", "expert_parallel_size", "data_parallel_size",
     "enable_prefix_caching", "enable_chunked_prefill", "num_scheduler_steps", "enforce_eager",
     "enable_sleep_mode", "enable_lora", "max_loras", "max_lora_rank", "max_logprobs",
-    "disable_log_stats", "disable_log_requests", "generation_config",
+    "disable_log_stats", "disable_log_requests", "generation_config", "num_gpu_blocks_override",
 })
 
 _warned: set[str] = set()

@@ -8,6 +8,8 @@ is the in-tree fused fp32 AdamW, and the KV cache stays resident during training
 """
 from __future__ import annotations
 
+from typing import Any
+
 from typing_extensions import TypedDict
 
 from .engine import EngineArgs
@@ -34,6 +36,10 @@ class InitArgs(TypedDict, total=False):
     disable_log_stats: bool
     enable_prefix_caching: bool
     use_async: bool
+    # accepted for source compatibility, no effect here
+    fix_tokenizer: Any
+    resize_model_vocab: Any
+    use_exact_model_name: Any
     # native additions
     random_init: bool  # build the architecture with N(0, 0.02) weights instead of loading a checkpoint
     architecture: dict  # explicit architecture (overrides config.json lookup); see models.config.ModelConfig
@@ -89,6 +95,124 @@ class TrainerArgs(TypedDict, total=False):
     gradient_checkpointing: bool
     max_steps: int
     num_train_epochs: float
+    # further keys of the reference's trainer configuration: accepted for source compatibility, no effect here (the
+    # step's learning rate and KL weight come with each train call, see dev/train.py)
+    accelerator_config: Any
+    adafactor: Any
+    auto_find_batch_size: Any
+    average_tokens_across_devices: Any
+    batch_eval_metrics: Any
+    beta: Any
+    bf16_full_eval: Any
+    data_seed: Any
+    dataloader_drop_last: Any
+    dataloader_num_workers: Any
+    dataloader_persistent_workers: Any
+    dataloader_pin_memory: Any
+    dataloader_prefetch_factor: Any
+    ddp_broadcast_buffers: Any
+    ddp_bucket_cap_mb: Any
+    ddp_timeout: Any
+    debug: Any
+    do_eval: Any
+    do_predict: Any
+    do_train: Any
+    ds3_gather_for_generation: Any
+    eval_accumulation_steps: Any
+    eval_delay: Any
+    eval_do_concat_batches: Any
+    eval_on_start: Any
+    eval_steps: Any
+    eval_strategy: Any
+    eval_use_gather_object: Any
+    fp16_backend: Any
+    fp16_full_eval: Any
+    fp16_opt_level: Any
+    fsdp_min_num_params: Any
+    fsdp_transformer_layer_cls_to_wrap: Any
+    full_determinism: Any
+    gradient_checkpointing_kwargs: Any
+    greater_is_better: Any
+    group_by_length: Any
+    half_precision_backend: Any
+    hub_always_push: Any
+    hub_model_id: Any
+    hub_private_repo: Any
+    hub_strategy: Any
+    hub_token: Any
+    ignore_data_skip: Any
+    include_for_metrics: Any
+    include_inputs_for_metrics: Any
+    include_num_input_tokens_seen: Any
+    include_tokens_per_second: Any
+    jit_mode_eval: Any
+    label_names: Any
+    label_smoothing_factor: Any
+    length_column_name: Any
+    load_best_model_at_end: Any
+    local_rank: Any
+    log_completions: Any
+    log_level: Any
+    log_level_replica: Any
+    log_on_each_node: Any
+    logging_dir: Any
+    logging_first_step: Any
+    logging_nan_inf_filter: Any
+    logging_strategy: Any
+    lr_scheduler_kwargs: Any
+    max_completion_length: Any
+    max_prompt_length: Any
+    metric_for_best_model: Any
+    model_init_kwargs: Any
+    mp_parameters: Any
+    neftune_noise_alpha: Any
+    no_cuda: Any
+    optim_args: Any
+    optim_target_modules: Any
+    overwrite_output_dir: Any
+    past_index: Any
+    per_device_eval_batch_size: Any
+    per_gpu_eval_batch_size: Any
+    per_gpu_train_batch_size: Any
+    prediction_loss_only: Any
+    push_to_hub: Any
+    push_to_hub_model_id: Any
+    push_to_hub_organization: Any
+    push_to_hub_token: Any
+    ray_scope: Any
+    ref_model_mixup_alpha: Any
+    ref_model_sync_steps: Any
+    remove_unused_columns: Any
+    restore_callback_states_from_checkpoint: Any
+    resume_from_checkpoint: Any
+    reward_weights: Any
+    run_name: Any
+    save_on_each_node: Any
+    save_only_model: Any
+    save_safetensors: Any
+    save_steps: Any
+    save_total_limit: Any
+    skip_memory_metrics: Any
+    sync_ref_model: Any
+    temperature: Any
+    tf32: Any
+    torch_compile: Any
+    torch_compile_backend: Any
+    torch_compile_mode: Any
+    torch_empty_cache_steps: Any
+    torchdynamo: Any
+    tpu_metrics_debug: Any
+    tpu_num_cores: Any
+    use_cpu: Any
+    use_ipex: Any
+    use_legacy_prediction_loop: Any
+    use_liger_kernel: Any
+    use_mps_device: Any
+    use_vllm: Any
+    vllm_device: Any
+    vllm_dtype: Any
+    vllm_gpu_memory_utilization: Any
+    vllm_max_model_len: Any
     # native additions
     tensor_parallel_size: int
     context_parallel_size: int

@@ -30,7 +30,19 @@ class ServerArgs(TypedDict, total=False):
     disable_fastapi_docs: bool
     enable_prompt_tokens_details: bool
     enable_reasoning: bool
-    reasoning_parser: str | None
+    reasoning_parser: str | None       # "deepseek_r1" (block open from the start), "qwen3", "granite"
+    ssl_keyfile: str | None
+    ssl_certfile: str | None
+    ssl_ca_certs: str | None
+    ssl_cert_reqs: int
+    middleware: list[str]              # import paths of ASGI middleware classes or async (request, call_next) functions
+    enable_server_load_tracking: bool  # GET /load
+    # accepted for source compatibility, no effect here
+    prompt_adapters: list[str] | None
+    chat_template_content_format: Literal["auto", "string", "openai"]
+    enable_ssl_refresh: bool
+    disable_frontend_multiprocessing: bool
+    tool_parser_plugin: str
 
 
 class OpenAIServerConfig(TypedDict, total=False):

@@ -60,6 +60,7 @@ class TokenEvent:
     finished: bool = False
     finish_reason: str | None = None
     top_logprobs: list[tuple[int, float]] | None = None
+    cached_tokens: int | None = None      # on the last event: prompt tokens whose KV came from the prefix cache
 
 
 class Sequence:
@@ -75,6 +76,7 @@ class Sequence:
         self.adapter = adapter
         self.blocks: list[int] = []
         self.num_cached = 0
+        self.prefix_hit_tokens = 0            # prompt tokens served from the prefix cache at (the last) admission
         self.salt: int | None = None          # prefix-cache salt (adapter slot + version) the KV was computed under
         self.finished = False
         self.finish_reason: str | None = None
@@ -347,7 +349,8 @@ class Engine:
         if seq.loop is not None and (p.stream_events or seq.finished):
             # delivered by _flush_events at the end of the scheduler step: one wake-up of the event loop per step and
             # one queue item per sequence, however many sequences and decode steps the step covered
-            self._outbox.setdefault(seq.loop, {}).setdefault(seq.queue, []).append(TokenEvent(tok, lp, seq.finished, reason, top))
+            self._outbox.setdefault(seq.loop, {}).setdefault(seq.queue, []).append(
+                TokenEvent(tok, lp, seq.finished, reason, top, seq.prefix_hit_tokens if seq.finished else None))
 
     def _flush_events(self) -> None:
         if not self._outbox:
@@ -424,6 +427,7 @@ class Engine:
                 self.waiting.popleft()
                 seq.blocks = cached + fresh
                 seq.num_cached = len(cached) * bs
+                seq.prefix_hit_tokens = min(seq.num_cached, len(seq.prompt_ids))
                 seq.salt = salt
                 picked.append((seq, seq.num_cached + take))
                 budget -= take

@@ -19,6 +19,9 @@ request subclass at ``src/art/local/vllm.py:234-247``):
 from __future__ import annotations
 
 import asyncio
+import importlib
+import logging
+import os
 import json
 import time
 import uuid
@@ -31,17 +34,81 @@ from .engine import Engine, SamplingParams
 from .tool_parser import HermesToolParser
 
 
+_log = logging.getLogger(__name__)
+
+
 def _now() -> int:
     return int(time.time())
+
+
+# reasoning parsers: name -> (opening tag, closing tag, block open from the start).  The last is True for model
+# families whose chat template opens the block itself, so that a completion starts inside it without an opening tag.
+_REASONING_TAGS = {"deepseek_r1": ("<think>", "</think>", True), "qwen3": ("<think>", "</think>", False),
+                   "granite": ("<think>", "</think>", False)}
+
+
+def _load_template(spec: str | None) -> str | None:
+    """A chat template given as a file path or as the template text itself."""
+    if not spec:
+        return None
+    if "{" not in spec and os.path.exists(spec):
+        with open(spec) as f:
+            return f.read()
+    return spec
+
+
+def split_reasoning(text: str, tags: tuple[str, str, bool], done: bool = True) -> tuple[str, str | None]:
+    """``(reasoning, content)`` of a completion.  With a closing tag, what precedes it is the reasoning (an opening
+    tag at its start is dropped) and what follows is the content.  With an opening tag only, or with neither tag
+    when the parser's block is open from the start, everything is reasoning and the content is None.  Otherwise the
+    text is content.  ``done`` False is the streaming case: a trailing piece that may still become the closing tag is
+    held back, and a text that may still become the opening tag is neither yet."""
+    open_t, close_t, implicit = tags
+    if close_t in text:
+        r, _, c = text.partition(close_t)
+        r = r.lstrip()
+        return (r[len(open_t):] if r.startswith(open_t) else r), c
+    lead = text.lstrip()
+    if lead.startswith(open_t):
+        body = lead[len(open_t):]
+        return (body if done else _without_partial(body, close_t)), None
+    if not done and lead and open_t.startswith(lead):
+        return "", None
+    if implicit:
+        return (text if done else _without_partial(text, close_t)), None
+    return "", text
+
+
+def _without_partial(text: str, tag: str) -> str:
+    """``text`` without a trailing proper prefix of ``tag`` (held back while streaming)."""
+    for k in range(min(len(tag) - 1, len(text)), 0, -1):
+        if text.endswith(tag[:k]):
+            return text[:-k]
+    return text
 
 
 class OpenAIServer:
     def __init__(self, engine: Engine, tokenizer, base_model_name: str, *, api_key: str | None = "default",
                  return_tokens_as_token_ids: bool = True, enable_auto_tool_choice: bool = True,
-                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256, peers: list[str] | None = None):
+                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256, peers: list[str] | None = None,
+                 response_role: str | None = None, chat_template: str | None = None, root_path: str | None = None,
+                 cors: dict | None = None, middleware: list[str] | None = None, request_id_headers: bool = False,
+                 fastapi_docs: bool = False, max_log_len: int | None = None, log_requests: bool = False,
+                 prompt_tokens_details: bool = False, reasoning_parser: str | None = None,
+                 load_tracking: bool = False):
         """``peers``: base URLs of further replicas of the same model (other GPUs of the node).  This server then
         spreads ``/v1/chat/completions`` and ``/v1/completions`` over itself and the peers, least loaded first,
-        passing a peer's answer (JSON or event stream) through unchanged; a client only ever sees this one URL."""
+        passing a peer's answer (JSON or event stream) through unchanged; a client only ever sees this one URL.
+
+        The remaining keywords are the server arguments of the reference's configuration
+        (src/art/dev/openai_server.py:60-125) with the meaning they have there: ``response_role`` (role of returned
+        messages), ``chat_template`` (a template file or the template itself, used instead of the tokenizer's),
+        ``root_path``, ``cors`` (``allow_origins`` / ``allow_methods`` / ``allow_headers`` / ``allow_credentials``),
+        ``middleware`` (import paths of ASGI middleware classes or of ``async def f(request, call_next)`` functions),
+        ``request_id_headers`` (``X-Request-Id`` on every response), ``fastapi_docs``, ``log_requests`` with
+        ``max_log_len`` (prompt characters / ids printed per request), ``prompt_tokens_details`` (prefix-cache hits
+        in ``usage``), ``reasoning_parser`` (text between ``<think>`` and ``</think>`` is returned as
+        ``reasoning_content``), ``load_tracking`` (``GET /load``)."""
         self.engine, self.tok = engine, tokenizer
         self.peers = list(peers or [])
         self._load = [0] * (1 + len(self.peers))       # requests in flight: [this replica, peer 0, peer 1, ...]
@@ -53,7 +120,50 @@ class OpenAIServer:
         self.auto_tools = enable_auto_tool_choice
         self.tool_parser = HermesToolParser() if tool_call_parser in ("hermes", None) else HermesToolParser()
         self.default_max_tokens = default_max_tokens
+        self.role = response_role or "assistant"
+        self.chat_template = _load_template(chat_template)
+        self.root_path = root_path or ""
+        self.cors = cors
+        self.middleware = list(middleware or [])
+        self.request_id_headers = request_id_headers
+        self.fastapi_docs = fastapi_docs
+        self.max_log_len = max_log_len
+        self.log_requests = log_requests
+        self.prompt_tokens_details = prompt_tokens_details
+        self.reasoning = _REASONING_TAGS.get(reasoning_parser or "", None) if reasoning_parser else None
+        if reasoning_parser and self.reasoning is None:
+            raise ValueError(f"unknown reasoning parser {reasoning_parser!r}; known: {sorted(_REASONING_TAGS)}")
+        self.load_tracking = load_tracking
         self.app = self._build()
+
+    @classmethod
+    def from_server_args(cls, engine: Engine, tokenizer, base_model_name: str, sargs: dict, *,
+                         log_requests: bool = False, peers: list[str] | None = None) -> "OpenAIServer":
+        """Builds the server from a ``ServerArgs`` dictionary (the keys that concern the HTTP listener itself, host,
+        port, TLS files and log level, are read by :func:`serve_kwargs`)."""
+        def jlist(key: str):
+            v = sargs.get(key)
+            if v is None:
+                return None
+            return json.loads(v) if isinstance(v, str) else list(v)
+
+        cors = None
+        if any(k in sargs for k in ("allowed_origins", "allowed_methods", "allowed_headers", "allow_credentials")):
+            cors = {"allow_origins": jlist("allowed_origins") or ["*"], "allow_methods": jlist("allowed_methods") or ["*"],
+                    "allow_headers": jlist("allowed_headers") or ["*"],
+                    "allow_credentials": bool(sargs.get("allow_credentials", False))}
+        return cls(engine, tokenizer, base_model_name, api_key=sargs.get("api_key", "default"),
+                   return_tokens_as_token_ids=bool(sargs.get("return_tokens_as_token_ids", True)),
+                   enable_auto_tool_choice=bool(sargs.get("enable_auto_tool_choice", True)),
+                   tool_call_parser=sargs.get("tool_call_parser", "hermes"), peers=peers,
+                   response_role=sargs.get("response_role"), chat_template=sargs.get("chat_template"),
+                   root_path=sargs.get("root_path"), cors=cors, middleware=sargs.get("middleware"),
+                   request_id_headers=bool(sargs.get("enable_request_id_headers", False)),
+                   fastapi_docs=sargs.get("disable_fastapi_docs") is False,
+                   max_log_len=sargs.get("max_log_len"), log_requests=log_requests,
+                   prompt_tokens_details=bool(sargs.get("enable_prompt_tokens_details", False)),
+                   reasoning_parser=(sargs.get("reasoning_parser") or "deepseek_r1") if sargs.get("enable_reasoning") else None,
+                   load_tracking=bool(sargs.get("enable_server_load_tracking", False)))
 
     # -- helpers ------------------------------------------------------------------------------------
     def _auth(self, request: Request) -> None:
@@ -186,13 +296,18 @@ class OpenAIServer:
         if body.get("tool_choice") == "none":
             tools = None
         kwargs = dict(body.get("chat_template_kwargs") or {})
+        template = body.get("chat_template") or self.chat_template
+        if template:
+            kwargs["chat_template"] = template
         ids = self.tok.apply_chat_template(body["messages"], tools=tools, add_generation_prompt=True, tokenize=True, **kwargs)
         if isinstance(ids, dict):
             ids = ids["input_ids"]
         return list(ids)
 
-    async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int):
-        """Async iterator over (index, token_id, logprob, finished, finish_reason, top_logprobs) for one choice."""
+    async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int,
+                       info: dict | None = None):
+        """Async iterator over (index, token_id, logprob, finished, finish_reason, top_logprobs) for one choice.
+        ``info["cached_tokens"]`` collects the prompt tokens that came out of the prefix cache."""
         if params.guided_choice:
             async for item in self._run_guided(prompt_ids, params, adapter, index):
                 yield item
@@ -204,6 +319,8 @@ class OpenAIServer:
         agen = self.engine.generate(prompt_ids, seq_params, adapter)
         try:
             async for ev in agen:
+                if info is not None and getattr(ev, "cached_tokens", None):
+                    info["cached_tokens"] = max(info.get("cached_tokens", 0), ev.cached_tokens)
                 yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason, ev.top_logprobs
                 if stops and not ev.finished:
                     # the same decoding as the text that is returned (token-by-token decoding differs from it as soon
@@ -243,8 +360,34 @@ class OpenAIServer:
 
     # -- app ----------------------------------------------------------------------------------------
     def _build(self) -> FastAPI:
-        app = FastAPI(title="art-b200 completion server", docs_url=None, redoc_url=None)
+        docs = {} if self.fastapi_docs else {"docs_url": None, "redoc_url": None, "openapi_url": None}
+        app = FastAPI(title="art-b200 completion server", root_path=self.root_path, **docs)
         srv = self
+        if self.cors is not None:
+            from fastapi.middleware.cors import CORSMiddleware
+
+            app.add_middleware(CORSMiddleware, **self.cors)
+        for path in self.middleware:
+            mod, _, attr = path.rpartition(".")
+            obj = getattr(importlib.import_module(mod), attr)
+            if isinstance(obj, type):
+                app.add_middleware(obj)
+            elif asyncio.iscoroutinefunction(obj):
+                app.middleware("http")(obj)
+            else:
+                raise ValueError(f"middleware {path!r} is neither a class nor an async function")
+        if self.request_id_headers:
+            @app.middleware("http")
+            async def request_id(request: Request, call_next):
+                rid = request.headers.get("x-request-id") or uuid.uuid4().hex
+                response = await call_next(request)
+                response.headers["X-Request-Id"] = rid
+                return response
+
+        if self.load_tracking:
+            @app.get("/load")
+            async def load():
+                return {"server_load": srv._load[0]}
 
         @app.get("/health")
         async def health():
@@ -300,6 +443,7 @@ class OpenAIServer:
             if forced is not None:
                 params.guided_choice = [forced]       # the call is teacher-forced and comes back with its log-probs
             rid = "chatcmpl-" + uuid.uuid4().hex
+            srv._log_request(rid, body, prompt_ids, params)
             model_name = body.get("model") or srv.base_model_name
             tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and (srv.auto_tools or forced is not None)
             if body.get("stream"):
@@ -324,7 +468,9 @@ class OpenAIServer:
             prompt = body.get("prompt", "")
             prompt_ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else srv.tok.encode(prompt)
             params = srv._params(body, len(prompt_ids))
-            out = await srv._collect(request, prompt_ids, params, adapter)
+            info: dict = {}
+            srv._log_request("cmpl", body, prompt_ids, params)
+            out = await srv._collect(request, prompt_ids, params, adapter, info)
             choices = []
             for i, (ids, lps, reason, tops) in enumerate(out):
                 lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}
@@ -336,7 +482,7 @@ class OpenAIServer:
             comp = sum(len(o[0]) for o in out)
             return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": _now(),
                     "model": body.get("model") or srv.base_model_name, "choices": choices,
-                    "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
+                    "usage": srv._usage(len(prompt_ids), comp, info)}
 
         return app
 
@@ -350,7 +496,7 @@ class OpenAIServer:
             self._load[0] -= 1
 
     # -- non-streaming ----------------------------------------------------------------------------------
-    async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter):
+    async def _collect(self, request: Request, prompt_ids, params: SamplingParams, adapter, info: dict | None = None):
 
         async def one(i: int):
             if not params.guided_choice and not params.stop and hasattr(self.engine, "complete"):
@@ -358,9 +504,11 @@ class OpenAIServer:
                 seq_params = SamplingParams(**{**params.__dict__, "n": 1,
                                                "seed": None if params.seed is None else params.seed + i})
                 seq = await self.engine.complete(prompt_ids, seq_params, adapter)
+                if info is not None:
+                    info["cached_tokens"] = max(info.get("cached_tokens", 0), getattr(seq, "prefix_hit_tokens", 0))
                 return list(seq.output_ids), list(seq.logprobs), seq.finish_reason or "stop", list(seq.top_logprobs)
             ids, lps, tops, reason = [], [], [], "stop"
-            async for _, tid, lp, fin, why, top in self._run_one(prompt_ids, params, adapter, i):
+            async for _, tid, lp, fin, why, top in self._run_one(prompt_ids, params, adapter, i, info):
                 if tid is not None:
                     ids.append(tid)
                     lps.append(lp)
@@ -421,10 +569,35 @@ class OpenAIServer:
         eos = self.engine.eos
         return ids[:-1] if ids and eos is not None and ids[-1] == eos else ids
 
+    def _usage(self, n_prompt: int, n_completion: int, info: dict | None = None) -> dict:
+        u: dict[str, Any] = {"prompt_tokens": n_prompt, "completion_tokens": n_completion,
+                             "total_tokens": n_prompt + n_completion}
+        if self.prompt_tokens_details:
+            u["prompt_tokens_details"] = {"cached_tokens": int((info or {}).get("cached_tokens", 0))}
+        return u
+
+    def _log_request(self, rid: str, body: dict, prompt_ids: list[int], params: SamplingParams) -> None:
+        if not self.log_requests:
+            return
+        n = self.max_log_len
+        text = body.get("prompt") if isinstance(body.get("prompt"), str) else None
+        if text is None and "messages" in body:
+            text = " | ".join(str(m.get("content")) for m in body["messages"])
+        ids = prompt_ids if n is None else prompt_ids[:n]
+        _log.info("request %s: model=%s n=%d max_tokens=%d temperature=%s prompt=%r prompt_token_ids=%s", rid,
+                  body.get("model"), params.n, params.max_tokens, params.temperature,
+                  text if n is None or text is None else text[:n], ids)
+
     def _message_from(self, ids: list[int], tools_on: bool, reason: str, params: SamplingParams | None = None
                       ) -> tuple[dict, str]:
         text = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=True), params)
-        msg: dict[str, Any] = {"role": "assistant", "content": text}
+        msg: dict[str, Any] = {"role": self.role, "content": text}
+        if self.reasoning is not None:
+            r, text = split_reasoning(text, self.reasoning)
+            msg["reasoning_content"] = r or None
+            msg["content"] = text
+            if text is None:
+                return msg, reason
         if tools_on:
             content, calls = self.tool_parser.extract(text)
             if calls:
@@ -434,7 +607,8 @@ class OpenAIServer:
         return msg, reason
 
     async def _chat_full(self, request, rid, model_name, prompt_ids, params, adapter, tools_on) -> dict:
-        out = await self._collect(request, prompt_ids, params, adapter)
+        info: dict = {}
+        out = await self._collect(request, prompt_ids, params, adapter, info)
         choices = []
         for i, (ids, lps, reason, tops) in enumerate(out):
             msg, reason = self._message_from(ids, tools_on, reason, params)
@@ -442,7 +616,7 @@ class OpenAIServer:
                             "logprobs": {"content": [self._logprob_entry(t, lp, top) for t, lp, top in zip(ids, lps, tops)]}})
         comp = sum(len(o[0]) for o in out)
         return {"id": rid, "object": "chat.completion", "created": _now(), "model": model_name, "choices": choices,
-                "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": comp, "total_tokens": len(prompt_ids) + comp}}
+                "usage": self._usage(len(prompt_ids), comp, info)}
 
     # -- streaming --------------------------------------------------------------------------------------
     async def _chat_stream(self, request, rid, model_name, prompt_ids, params, adapter, tools_on, include_usage
@@ -454,24 +628,41 @@ class OpenAIServer:
             return "data: " + json.dumps(d) + "\n\n"
 
         q: asyncio.Queue = asyncio.Queue()
+        info: dict = {}
 
         async def pump(i: int):
             try:
-                async for item in self._run_one(prompt_ids, params, adapter, i):
+                async for item in self._run_one(prompt_ids, params, adapter, i, info):
                     await q.put(item)
             except BaseException as e:  # noqa: BLE001
                 await q.put(e)
             finally:
                 await q.put((i, "done"))
 
+        def visible(ids: list[int], done: bool) -> tuple[str, str]:
+            """(reasoning, content) of a choice so far that may be sent: without a possible beginning of a stop
+            string or of a reasoning tag at the end, which wait for the next token."""
+            full = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=True), params)
+            if not done and full.endswith("\ufffd"):        # half a character: wait
+                return "", ""
+            if self.reasoning is None:
+                return "", full if done else full[:len(full) - self._held_back(full, params)]
+            r, c = split_reasoning(full, self.reasoning, done)
+            if c is None:
+                return r, ""
+            if not done:
+                c = c[:len(c) - self._held_back(c, params)]
+            return r, c
+
         tasks = [asyncio.create_task(pump(i)) for i in range(params.n)]
         live = params.n
         completion_tokens = 0
         bufs: dict[int, list[int]] = {i: [] for i in range(params.n)}
         sent_text: dict[int, int] = {i: 0 for i in range(params.n)}
+        sent_reason: dict[int, int] = {i: 0 for i in range(params.n)}
         try:
             for i in range(params.n):
-                yield chunk([{"index": i, "delta": {"role": "assistant", "content": ""}, "logprobs": None, "finish_reason": None}])
+                yield chunk([{"index": i, "delta": {"role": self.role, "content": ""}, "logprobs": None, "finish_reason": None}])
             while live:
                 item = await q.get()
                 if isinstance(item, BaseException):
@@ -486,42 +677,50 @@ class OpenAIServer:
                     completion_tokens += 1
                     bufs[i].append(tid)
                     lps = {"content": [self._logprob_entry(tid, lp, top)]}
-                    if not tools_on:
-                        full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True), params)
-                        upto = len(full) - self._held_back(full, params)       # a possible stop-string prefix waits
-                        if not full.endswith("�") and upto > sent_text[i]:
-                            delta["content"] = full[sent_text[i]:upto]
-                            sent_text[i] = upto
+                if not tools_on and (tid is not None or fin):
+                    r, c = visible(bufs[i], bool(fin))
+                    if len(r) > sent_reason[i]:
+                        delta["reasoning_content"] = r[sent_reason[i]:]
+                        sent_reason[i] = len(r)
+                    if len(c) > sent_text[i]:
+                        delta["content"] = c[sent_text[i]:]
+                        sent_text[i] = len(c)
                 reason = None
                 if fin:
                     reason = why or "stop"
-                    if not tools_on:       # whatever was held back and did not become a stop string
-                        full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[i]), skip_special_tokens=True), params)
-                        if len(full) > sent_text[i]:
-                            delta["content"] = delta.get("content", "") + full[sent_text[i]:]
-                            sent_text[i] = len(full)
                     if tools_on:   # tool calls are parsed once the choice is complete; log-probs were streamed per token
                         msg, reason = self._message_from(bufs[i], True, reason, params)
+                        if msg.get("reasoning_content"):
+                            delta["reasoning_content"] = msg["reasoning_content"]
                         if msg.get("content"):
                             delta["content"] = msg["content"]
                         if msg.get("tool_calls"):
                             delta["tool_calls"] = [{"index": k, **c} for k, c in enumerate(msg["tool_calls"])]
                 yield chunk([{"index": i, "delta": delta, "logprobs": lps, "finish_reason": reason}])
             if include_usage:
-                yield chunk([], {"prompt_tokens": len(prompt_ids), "completion_tokens": completion_tokens,
-                                 "total_tokens": len(prompt_ids) + completion_tokens})
+                yield chunk([], self._usage(len(prompt_ids), completion_tokens, info))
             yield "data: [DONE]\n\n"
         finally:
             for t in tasks:   # a disconnecting client lands here: abort only this request's sequences
                 t.cancel()
 
 
+def serve_kwargs(sargs: dict) -> dict:
+    """The listener's part of a ``ServerArgs`` dictionary as keyword arguments of :func:`serve`."""
+    out = {k: sargs[k] for k in ("ssl_keyfile", "ssl_certfile", "ssl_ca_certs", "ssl_cert_reqs") if sargs.get(k) is not None}
+    if sargs.get("uvicorn_log_level"):
+        out["log_level"] = sargs["uvicorn_log_level"]
+    return out
+
+
 async def serve(server: OpenAIServer, host: str = "0.0.0.0", port: int = 8000, log_level: str = "warning",
-                ready: asyncio.Event | None = None):
-    """Run the app with uvicorn inside the current event loop until cancelled."""
+                ready: asyncio.Event | None = None, **listener):
+    """Run the app with uvicorn inside the current event loop until cancelled.  ``listener``: further keyword
+    arguments of ``uvicorn.Config`` (TLS: ``ssl_keyfile``, ``ssl_certfile``, ``ssl_ca_certs``, ``ssl_cert_reqs``)."""
     import uvicorn
 
-    config = uvicorn.Config(server.app, host=host, port=port, log_level=log_level, access_log=False)
+    config = uvicorn.Config(server.app, host=host, port=port, log_level=log_level, access_log=False,
+                            root_path=server.root_path, **listener)
     uv = uvicorn.Server(config)
     uv.install_signal_handlers = lambda: None  # type: ignore[method-assign]
     task = asyncio.create_task(uv.serve())

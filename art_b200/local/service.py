@@ -263,7 +263,7 @@ class ModelService:
 
     # -- serving --------------------------------------------------------------------------------------
     async def start_openai_server(self, config: dev.OpenAIServerConfig | None = None) -> tuple[str, int]:
-        from ..engine.server import OpenAIServer, serve
+        from ..engine.server import OpenAIServer, serve, serve_kwargs
 
         st = self.state
         step0 = get_step_checkpoint_dir(self.output_dir, 0)
@@ -283,14 +283,15 @@ class ModelService:
         port = port0 + self.rank                # rank r serves its replica on the leader's port + r
         # the leader spreads requests over all replicas (its own included); the others serve what they are sent
         peers = [f"http://127.0.0.1:{port0 + r}" for r in range(1, self.world)] if self.rank == 0 else []
-        server = OpenAIServer(st.engine, st.tokenizer, self.base_model, api_key=sargs.get("api_key", "default"),
-                              return_tokens_as_token_ids=bool(sargs.get("return_tokens_as_token_ids", True)),
-                              enable_auto_tool_choice=bool(sargs.get("enable_auto_tool_choice", True)),
-                              tool_call_parser=sargs.get("tool_call_parser", "hermes"), peers=peers)
+        eargs = cfg.get("engine_args", {})
+        server = OpenAIServer.from_server_args(st.engine, st.tokenizer, self.base_model, sargs, peers=peers,
+                                               log_requests=eargs.get("disable_log_requests") is False)
         self._server = server
         await self.stop_openai_server()
         ready = asyncio.Event()
-        self._server_task = asyncio.create_task(serve(server, host, port, sargs.get("uvicorn_log_level", "warning"), ready))
+        listener = serve_kwargs(sargs) if self.rank == 0 else {}   # replicas behind the leader are reached over loopback
+        listener.setdefault("log_level", "warning")
+        self._server_task = asyncio.create_task(serve(server, host, port, ready=ready, **listener))
         try:
             await asyncio.wait_for(ready.wait(), timeout=30)
         except asyncio.TimeoutError as e:

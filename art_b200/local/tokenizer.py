@@ -132,8 +132,20 @@ class ByteChatTokenizer:
 
     def apply_chat_template(self, messages: list[dict], tools: list[dict] | None = None, tokenize: bool = True,
                             add_generation_prompt: bool = False, return_dict: bool = False,
-                            return_assistant_tokens_mask: bool = False, **_: Any):
-        pieces = list(self._segments(list(messages), tools, add_generation_prompt))
+                            return_assistant_tokens_mask: bool = False, chat_template: str | None = None, **kw: Any):
+        """``chat_template``: a Jinja template used instead of the built-in ChatML layout (variables ``messages``,
+        ``tools``, ``add_generation_prompt``, the special-token strings and any further keyword); a custom template has
+        no assistant mask."""
+        if chat_template:
+            import jinja2.sandbox
+
+            env = jinja2.sandbox.ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+            text = env.from_string(chat_template).render(
+                messages=messages, tools=tools, add_generation_prompt=add_generation_prompt,
+                bos_token="", eos_token=self._specials[self.IM_END], **kw)
+            pieces = [(text, False)]
+        else:
+            pieces = list(self._segments(list(messages), tools, add_generation_prompt))
         if not tokenize:
             return "".join(p for p, _a in pieces)
         ids: list[int] = []

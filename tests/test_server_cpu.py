@@ -299,3 +299,103 @@ def test_health_probe_restarts_a_stopped_engine_until_the_budget_is_spent(long_s
         asyncio.run(main())
     finally:
         eng.runner.decode = real
+
+
+def test_server_arguments_of_the_reference_configuration_take_effect(tmp_path):
+    """CORS, root path, request ids, load tracking, response role, chat template, prefix-cache hits in ``usage``,
+    request logging with ``max_log_len``, middleware by import path, TLS keywords for the listener."""
+    import logging
+
+    from art_b200.engine.server import serve_kwargs
+
+    cfg = PRESETS["tiny"]
+    tok = ByteChatTokenizer(cfg.vocab_size)
+    eng = Engine(ReferenceRunner(cfg, init_base_weights(cfg, seed=0), LoraConfig(), max_loras=2), BlockManager(256, 4, True),
+                 eos_token_id=tok.eos_token_id, max_loras=2, num_scheduler_steps=2, max_model_len=512)
+    eng.start()
+    template = tmp_path / "t.jinja"
+    template.write_text("{% for m in messages %}[{{ m.role }}] {{ m.content }}\n{% endfor %}[bot] ")
+    sargs = {"allowed_origins": '["https://a.example"]', "allow_credentials": True, "root_path": "/proxy",
+             "enable_request_id_headers": True, "enable_server_load_tracking": True, "response_role": "bot",
+             "chat_template": str(template), "enable_prompt_tokens_details": True, "max_log_len": 6,
+             "middleware": ["tests.helpers_middleware.add_header"], "api_key": None,
+             "ssl_keyfile": "/k.pem", "ssl_certfile": "/c.pem", "uvicorn_log_level": "info"}
+    srv = OpenAIServer.from_server_args(eng, tok, "tiny-base", sargs, log_requests=True)
+    assert serve_kwargs(sargs) == {"ssl_keyfile": "/k.pem", "ssl_certfile": "/c.pem", "log_level": "info"}
+
+    records: list[str] = []
+
+    class Grab(logging.Handler):
+        def emit(self, record):
+            records.append(record.getMessage())
+
+    lg = logging.getLogger("art_b200.engine.server")
+    h = Grab()
+    lg.addHandler(h)
+    lg.setLevel(logging.INFO)
+
+    async def main():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=srv.app), base_url="http://t") as c:
+            r = await c.post("/tokenize", json={"messages": [{"role": "user", "content": "hello"}]})
+            assert tok.decode(r.json()["tokens"]) == "[user] hello\n[bot] "
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hello there, friend"}], "max_tokens": 3}
+            r = await c.post("/v1/chat/completions", json=body, headers={"Origin": "https://a.example", "X-Request-Id": "abc"})
+            assert r.status_code == 200
+            assert r.headers["access-control-allow-origin"] == "https://a.example"
+            assert r.headers["x-request-id"] == "abc" and r.headers["x-test-middleware"] == "1"
+            d = r.json()
+            assert d["choices"][0]["message"]["role"] == "bot"
+            assert d["usage"]["prompt_tokens_details"] == {"cached_tokens": 0}
+            r = await c.post("/v1/chat/completions", json=body)           # same prompt: served from the prefix cache
+            hit = r.json()["usage"]["prompt_tokens_details"]["cached_tokens"]
+            assert 0 < hit < r.json()["usage"]["prompt_tokens"] and hit % 4 == 0
+            r = await c.post("/v1/chat/completions", json={**body, "stream": True, "stream_options": {"include_usage": True}})
+            last = [json.loads(l[6:]) for l in r.text.splitlines() if l.startswith("data: {")][-1]
+            assert last["usage"]["prompt_tokens_details"]["cached_tokens"] == hit
+            assert (await c.get("/load")).json() == {"server_load": 0}
+            assert "x-request-id" in (await c.get("/health")).headers
+    try:
+        asyncio.run(main())
+    finally:
+        lg.removeHandler(h)
+        eng.shutdown()
+    assert srv.app.root_path == "/proxy"
+    logged = [m for m in records if m.startswith("request chatcmpl-")]
+    assert logged and "prompt='hello '" in logged[0] and "prompt_token_ids=[91, 117, 115, 101, 114, 93]" in logged[0]
+
+
+def test_reasoning_parsers_split_thinking_from_content():
+    from art_b200.engine.server import split_reasoning
+
+    q = ("<think>", "</think>", False)
+    r1 = ("<think>", "</think>", True)
+    assert split_reasoning("<think>a b</think>yes", q) == ("a b", "yes")
+    assert split_reasoning("plain answer", q) == ("", "plain answer")
+    assert split_reasoning("<think>never closed", q) == ("never closed", None)
+    assert split_reasoning("a b</think>yes", r1) == ("a b", "yes")                   # the template opened the block
+    assert split_reasoning("still thinking", r1) == ("still thinking", None)
+    # streaming: possible tag beginnings wait
+    assert split_reasoning("<thi", q, done=False) == ("", None)
+    assert split_reasoning("<think>abc</th", q, done=False) == ("abc", None)
+    assert split_reasoning("abc</thi", r1, done=False) == ("abc", None)
+    assert split_reasoning("<think>abc</think>ye", q, done=False) == ("abc", "ye")
+
+
+def test_reasoning_content_in_full_and_streamed_answers(long_server):
+    """The model is made to 'think' by forcing its completion (guided choice); the server splits it."""
+    eng, tok = long_server.engine, long_server.tok
+    srv = OpenAIServer(eng, tok, "tiny-base", reasoning_parser="qwen3")
+
+    async def main():
+        async with client(srv) as c:
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "2+2?"}],
+                    "guided_choice": ["<think>two and two</think>four"]}
+            d = (await c.post("/v1/chat/completions", json=body)).json()
+            msg = d["choices"][0]["message"]
+            assert msg["reasoning_content"] == "two and two" and msg["content"] == "four"
+            r = await c.post("/v1/chat/completions", json={**body, "stream": True})
+            chunks = [json.loads(l[6:]) for l in r.text.splitlines() if l.startswith("data: {")]
+            think = "".join(ch["choices"][0]["delta"].get("reasoning_content") or "" for ch in chunks if ch["choices"])
+            text = "".join(ch["choices"][0]["delta"].get("content") or "" for ch in chunks if ch["choices"])
+            assert think == "two and two" and text == "four"
+    asyncio.run(main())
