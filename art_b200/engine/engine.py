@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import asyncio
 import itertools
+import logging
 import threading
 import os
 import time
@@ -24,6 +25,8 @@ from typing import AsyncIterator
 
 from .kv_cache import BlockManager
 from .runner import LogitProc, SeqView
+
+log = logging.getLogger(__name__)
 
 
 @dataclass
@@ -124,12 +127,15 @@ class EngineStats:
 class Engine:
     def __init__(self, runner, block_manager: BlockManager, *, eos_token_id: int | None, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 16384, num_scheduler_steps: int = 16, max_model_len: int = 32768,
-                 max_loras: int = 4, kv_cache=None, enable_chunked_prefill: bool = True):
+                 max_loras: int = 4, kv_cache=None, enable_chunked_prefill: bool = True,
+                 log_stats_interval: float | None = None):
         """``max_num_batched_tokens`` bounds the new tokens of one prefill step.  With ``enable_chunked_prefill`` a
         prompt longer than what is left of that budget is computed over several steps, a block-aligned chunk at a
         time (its KV accumulates in its blocks; the token is sampled after the last chunk), so a long prompt neither
         waits for an empty step nor builds one oversized forward pass; without it such a prompt runs alone, whole."""
         self.runner, self.bm, self.kv = runner, block_manager, kv_cache
+        self.log_stats_interval = log_stats_interval     # seconds between throughput lines in the log; None: no lines
+        self._stats_mark = (time.monotonic(), 0, 0, 0, 0)   # time, prompt tokens, generated tokens, cache queries, hits
         self.chunked = enable_chunked_prefill
         self.prefilling: list[Sequence] = []      # admitted, prompt KV partly computed
         self.eos = eos_token_id
@@ -582,6 +588,8 @@ class Engine:
                     if self._stop or not self._run_gate.is_set():
                         continue
                     worked = self._traced_step()
+                if self.log_stats_interval is not None:
+                    self._log_stats()
                 if not worked:
                     self._wake.wait(timeout=0.05)
                     self._wake.clear()
@@ -597,6 +605,26 @@ class Engine:
                         pass            # closed event loop
                 s.finished = True
                 s.done_event.set()
+
+    def _log_stats(self) -> None:
+        """One throughput line per ``log_stats_interval`` seconds in which tokens were processed (what the reference's
+        engine prints unless ``disable_log_stats`` is set)."""
+        now = time.monotonic()
+        t0, p0, g0, q0, h0 = self._stats_mark
+        if now - t0 < self.log_stats_interval:
+            return
+        st = self.bm.stats()
+        p, g = self.stats.prompt_tokens, self.stats.generated_tokens
+        q, h = st.get("prefix_queries", 0), st.get("prefix_hits", 0)
+        self._stats_mark = (now, p, g, q, h)
+        if p == p0 and g == g0 and not self.running and not self.waiting:
+            return
+        dt = now - t0
+        log.info("prompt throughput %.1f tokens/s, generation throughput %.1f tokens/s, running %d, waiting %d, "
+                 "KV cache usage %.1f %%, prefix cache hit rate %.1f %%, preemptions %d",
+                 (p - p0) / dt, (g - g0) / dt, len(self.running), len(self.waiting),
+                 100.0 * (1.0 - self.bm.num_free / self.bm.num_blocks), 100.0 * (h - h0) / max(1, q - q0),
+                 self.stats.preemptions)
 
     def recover(self) -> bool:
         """Bring the engine back after its stepping thread stopped on an error: every request that was in flight has

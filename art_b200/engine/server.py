@@ -705,6 +705,24 @@ class OpenAIServer:
                 t.cancel()
 
 
+def route_logs_to_file(path: str, level: int = logging.INFO) -> dict:
+    """Sends the engine's and the server's log records to ``path`` (appending; one handler per path however often this
+    is called) and returns a uvicorn ``log_config`` that sends uvicorn's own records there too, like the reference's
+    engine log (src/art/local/vllm.py:335-382)."""
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    lg = logging.getLogger("art_b200.engine")
+    path = os.path.abspath(path)
+    if not any(isinstance(h, logging.FileHandler) and h.baseFilename == path for h in lg.handlers):
+        h = logging.FileHandler(path)
+        h.setFormatter(logging.Formatter("%(levelname)s %(asctime)s %(name)s] %(message)s", "%m-%d %H:%M:%S"))
+        lg.addHandler(h)
+    lg.setLevel(min(level, lg.level) if lg.level else level)
+    from uvicorn.config import LOGGING_CONFIG
+
+    handler = {"formatter": "default", "class": "logging.FileHandler", "filename": path}
+    return {**LOGGING_CONFIG, "handlers": {"default": dict(handler), "access": {**handler, "formatter": "access"}}}
+
+
 def serve_kwargs(sargs: dict) -> dict:
     """The listener's part of a ``ServerArgs`` dictionary as keyword arguments of :func:`serve`."""
     out = {k: sargs[k] for k in ("ssl_keyfile", "ssl_certfile", "ssl_ca_certs", "ssl_cert_reqs") if sargs.get(k) is not None}

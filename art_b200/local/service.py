@@ -194,7 +194,9 @@ class ModelState:
                              max_num_batched_tokens=int(engine_args.get("max_num_batched_tokens") or 16384),
                              num_scheduler_steps=int(engine_args.get("num_scheduler_steps", 16)), max_model_len=max_len,
                              max_loras=max_loras, kv_cache=self.kv,
-                             enable_chunked_prefill=bool(engine_args.get("enable_chunked_prefill", True)))
+                             enable_chunked_prefill=bool(engine_args.get("enable_chunked_prefill", True)),
+                             log_stats_interval=None if engine_args.get("disable_log_stats", init_args.get("disable_log_stats"))
+                             else 10.0)
         self.sleep_mode = bool(engine_args.get("enable_sleep_mode", False))
 
     def close(self) -> None:
@@ -263,7 +265,7 @@ class ModelService:
 
     # -- serving --------------------------------------------------------------------------------------
     async def start_openai_server(self, config: dev.OpenAIServerConfig | None = None) -> tuple[str, int]:
-        from ..engine.server import OpenAIServer, serve, serve_kwargs
+        from ..engine.server import OpenAIServer, route_logs_to_file, serve, serve_kwargs
 
         st = self.state
         step0 = get_step_checkpoint_dir(self.output_dir, 0)
@@ -291,6 +293,9 @@ class ModelService:
         ready = asyncio.Event()
         listener = serve_kwargs(sargs) if self.rank == 0 else {}   # replicas behind the leader are reached over loopback
         listener.setdefault("log_level", "warning")
+        if cfg.get("log_file"):
+            suffix = f".rank{self.rank}" if self.rank else ""
+            listener["log_config"] = route_logs_to_file(cfg["log_file"] + suffix)
         self._server_task = asyncio.create_task(serve(server, host, port, ready=ready, **listener))
         try:
             await asyncio.wait_for(ready.wait(), timeout=30)

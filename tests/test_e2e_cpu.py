@@ -67,6 +67,7 @@ def test_full_loop(tmp_path):
             # base model is still served untouched under its own name
             r = await model.openai_client().chat.completions.create(model="random:tiny", messages=[{"role": "user", "content": "q0"}], max_tokens=2)
             assert len(r.choices[0].logprobs.content) == 2
+            assert (out / "logs" / "engine.log").exists()           # engine and listener write their log here
             await model.delete_checkpoints()      # val/reward was logged at step 0: best (0) and latest (1) are kept
             assert sorted(d for d in os.listdir(out) if d.isdigit()) == ["0000", "0001"]
             await model.delete_checkpoints(best_checkpoint_metric="val/none")   # unknown metric: only the latest stays

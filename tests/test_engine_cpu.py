@@ -343,3 +343,19 @@ def test_engine_recovers_after_its_stepping_thread_failed(tiny):
             eng.generate_sync([4, 5, 6], SamplingParams(max_tokens=4, temperature=0.0))
     finally:
         eng.shutdown()
+
+
+def test_engine_logs_throughput_lines_unless_switched_off(tiny, caplog):
+    import logging
+
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    eng.log_stats_interval = 0.0
+    eng.start()
+    try:
+        with caplog.at_level(logging.INFO, logger="art_b200.engine.engine"):
+            eng.generate_sync([1, 2, 3], SamplingParams(max_tokens=6, temperature=0.0))
+        lines = [r.getMessage() for r in caplog.records if "generation throughput" in r.getMessage()]
+        assert lines and "KV cache usage" in lines[0] and "prefix cache hit rate" in lines[0]
+    finally:
+        eng.shutdown()
