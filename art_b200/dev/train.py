@@ -10,6 +10,7 @@ class TrainConfig(TypedDict, total=False):
     # native additions
     tokens_per_microbatch: int  # packed rows are grouped to about this many tokens per fwd/bwd
     rows_per_optimizer_step: int  # packed rows accumulated into one AdamW step (default 1)
+    packing_seed: int  # prompt ids and shuffles of tokenizing / packing come from random.Random(packing_seed)
     compat_row_positions: bool  # RoPE positions = position in the packed row instead of input_pos
     activation_recompute: str  # "auto" | "none" | "mlp" | "full" (overrides init_args.activation_recompute)
     max_service_restarts: int  # supervision: times a dead / timed-out service process is restarted per train call (1)

@@ -161,7 +161,11 @@ class LocalBackend(Backend):
         return service
 
     def _get_packed_tensors(self, model: TrainableModel, trajectory_groups: list[TrajectoryGroup],
-                            allow_training_without_logprobs: bool, plot_tensors: bool) -> PackedTensors | None:
+                            allow_training_without_logprobs: bool, plot_tensors: bool,
+                            seed: int | None = None) -> PackedTensors | None:
+        """``seed``: the prompt ids and the two shuffles of this call come from ``random.Random(seed)``, which makes
+        the packed rows a function of the trajectories alone; without it the backend's own generator goes on."""
+        rng = self._rng if seed is None else random.Random(seed)
         if model.base_model not in self._tokenizers:
             arch = ((model._internal_config or {}).get("init_args", {}) or {}).get("architecture")
             vocab = arch.get("vocab_size") if arch else None
@@ -174,14 +178,14 @@ class LocalBackend(Backend):
                     vocab = None
             self._tokenizers[model.base_model] = load_tokenizer(model.base_model, vocab)
         tokenizer = self._tokenizers[model.base_model]
-        results = list(tokenize_trajectory_groups(tokenizer, trajectory_groups, allow_training_without_logprobs, self._rng))
+        results = list(tokenize_trajectory_groups(tokenizer, trajectory_groups, allow_training_without_logprobs, rng))
         if not results:
             return None
         longest = max(len(r.token_ids) for r in results)
         seq_len = math.ceil(longest / 2048) * 2048
         cap = (model._internal_config or dev.InternalModelConfig()).get("init_args", {}).get("max_seq_length", 32_768)
         seq_len = min(seq_len, cap)
-        packed = packed_tensors_from_tokenized_results(results, seq_len, pad_token_id=tokenizer.eos_token_id, rng=self._rng)
+        packed = packed_tensors_from_tokenized_results(results, seq_len, pad_token_id=tokenizer.eos_token_id, rng=rng)
         if not allow_training_without_logprobs and bool(packed["logprobs"].isnan().all()):
             print("There are no assistant logprobs to train on. Did you forget to include at least one Choice in "
                   "Trajectory.messages_and_choices?")
@@ -248,7 +252,7 @@ class LocalBackend(Backend):
         await self._log(model, trajectory_groups, "train")
         packed = self._get_packed_tensors(model, trajectory_groups,
                                           allow_training_without_logprobs=dev_config.get("allow_training_without_logprobs", False),
-                                          plot_tensors=False)
+                                          plot_tensors=False, seed=dev_config.get("packing_seed"))
         if packed is None:
             print("Skipping tuning as there is no suitable data. This can happen when all the trajectories in the same "
                   "group have the same reward and thus no advantage to train on.")

@@ -99,3 +99,18 @@ def test_grpo_loss_clipping_and_nan_old_logprobs():
     assert abs(float(new.grad[0, 0]) + 0.25) < 1e-6                 # d(-ratio*adv)/dnew / 4
     assert new.grad[0, 1] == 0 and new.grad[0, 3] == 0              # clipped branches carry no gradient
     assert new.grad[0, 4] == 0 and new.grad[0, 5] == 0              # masked out
+
+
+def test_packing_seed_makes_the_packed_rows_a_function_of_the_trajectories(tmp_path):
+    from art_b200.local import LocalBackend
+
+    backend = LocalBackend(in_process=True, path=str(tmp_path))
+    model = art.TrainableModel(name="m", project="p", base_model="random:tiny",
+                               _internal_config={"init_args": {"architecture": {"vocab_size": 512}}})
+    groups = [art.TrajectoryGroup([traj(float(i % 2), [10 + i, 20 + g], prompt=f"q{g}") for i in range(4)]) for g in range(3)]
+    a = backend._get_packed_tensors(model, groups, False, False, seed=7)
+    b = backend._get_packed_tensors(model, groups, False, False, seed=7)
+    c = backend._get_packed_tensors(model, groups, False, False, seed=8)
+    for k in ("tokens", "group_ids", "parent_ids", "advantages"):
+        assert torch.equal(a[k], b[k])
+    assert not torch.equal(a["group_ids"], c["group_ids"])      # other ids (and very likely another order)
