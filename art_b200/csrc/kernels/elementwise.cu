@@ -180,6 +180,40 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restri
   }
 }
 
+// The same rotation with the pair frequencies read from a table (frequency-scaled rotary embeddings: linear, llama3,
+// YaRN) and cos / sin multiplied by `mscale` (YaRN's attention factor; the inverse rotation carries it as well, being
+// the transpose of the forward map).
+__global__ void rope_table_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ pos, int M, int ld,
+                                  int col0, int heads, int hd, const float* __restrict__ inv_freq, float mscale,
+                                  float sign) {
+  const int half = hd >> 1;
+  const int vec_per_head = half >> 3;  // 8 pairs per thread
+  const long total = static_cast<long>(M) * heads * vec_per_head;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int vv = idx % vec_per_head;
+    const int h = (idx / vec_per_head) % heads;
+    const int m = idx / (static_cast<long>(vec_per_head) * heads);
+    __nv_bfloat16* p = buf + static_cast<size_t>(m) * ld + col0 + h * hd + vv * 8;
+    float a[8], b[8];
+    load8(p, a);
+    load8(p + half, b);
+    const float fp = static_cast<float>(pos[m]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s, c;
+      sincosf(fp * __ldg(inv_freq + vv * 8 + j), &s, &c);
+      s *= sign * mscale;
+      c *= mscale;
+      const float x1 = a[j], x2 = b[j];
+      a[j] = x1 * c - x2 * s;
+      b[j] = x2 * c + x1 * s;
+    }
+    store8(p, a);
+    store8(p + half, b);
+  }
+}
+
 // ------------------------------------------------------------ SwiGLU backward
 // gu / dgu are [M, 2F] with columns interleaved in blocks of 16: [gate 16 | up 16].
 // dgate = dh * up * s * (1 + gate * (1 - s)),  dup = dh * gate * s,  s = sigmoid(gate)
@@ -382,6 +416,15 @@ ARTB_EXPORT int artb_rope(void* buf, const int* pos, int M, int ld, int col0, in
   const long total = (long)M * heads * (hd / 16);
   rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((bf16*)buf, pos, M, ld, col0, heads, hd, log2f(theta),
                                                     inverse ? -1.f : 1.f);
+  return (int)cudaGetLastError();
+}
+
+ARTB_EXPORT int artb_rope_table(void* buf, const int* pos, int M, int ld, int col0, int heads, int hd,
+                                const float* inv_freq, float mscale, int inverse, cudaStream_t st) {
+  if (hd % 16 || ld % 8 || col0 % 8 || !inv_freq) return ERR_BAD_SHAPE;
+  const long total = (long)M * heads * (hd / 16);
+  rope_table_kernel<<<grid_for(total, 256), 256, 0, st>>>((bf16*)buf, pos, M, ld, col0, heads, hd, inv_freq, mscale,
+                                                          inverse ? -1.f : 1.f);
   return (int)cudaGetLastError();
 }
 

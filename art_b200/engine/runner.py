@@ -335,6 +335,7 @@ class NativeRunner:
         from ..ops import elementwise as ew
 
         self.full_cfg = cfg
+        ew.rope_args(cfg, torch.device(device))     # frequency table of a scaled rotary embedding: never built under capture
         self.tp_group = tp_group
         self.tp = 1 if tp_group is None else torch.distributed.get_world_size(tp_group)
         self.tp_rank = 0 if tp_group is None else torch.distributed.get_rank(tp_group)
@@ -576,7 +577,7 @@ class NativeRunner:
         if cfg.qk_norm:
             ew.headnorm_fwd_(qkv, L["q_norm"], 0, cfg.num_heads, cfg.head_dim, cfg.rms_norm_eps)
             ew.headnorm_fwd_(qkv, L["k_norm"], cfg.q_size, cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
-        ew.rope_(qkv, pos, 0, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta)
+        ew.rope_(qkv, pos, 0, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, cfg.rope_theta, **ew.rope_args(cfg, qkv.device))
         return qkv
 
     # -- prefill ------------------------------------------------------------------------------------
@@ -785,8 +786,10 @@ class NativeRunner:
 
     def _fused_decode_ok(self, M: int) -> bool:
         """The fused finish kernels cover one GPU per replica (a tensor-parallel replica all-reduces between the
-        projection and the norm), no per-head q/k norm, dense MLPs, and adapter slots of at most 64 shrink columns."""
-        if self.tp > 1 or self.cfg.qk_norm or M > 512 or os.environ.get("ARTB_DECODE_FUSED", "1") == "0":
+        projection and the norm), no per-head q/k norm, the unscaled rotary embedding, dense MLPs, and adapter slots
+        of at most 64 shrink columns."""
+        if (self.tp > 1 or self.cfg.qk_norm or self.cfg.rope_scaling is not None or M > 512
+                or os.environ.get("ARTB_DECODE_FUSED", "1") == "0"):
             return False
         L = self.layers[0]
         return all(isinstance(L.get(k), EngineLinear) and L[k].cols <= 64 for k in ("qkv", "o", "gu", "down"))

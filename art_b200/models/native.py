@@ -264,6 +264,7 @@ class NativeDecoder:
                  layer_range: range | None = None):
         self.cfg, self.lora_cfg, self.attn_impl = cfg, lora_cfg, attn_impl
         self.device = torch.device(device)
+        ew.rope_args(cfg, self.device)       # builds the frequency table of a scaled rotary embedding now, not mid-step
         # pipeline parallelism: this instance holds the decoder layers of `layer_range` only; the first stage embeds,
         # the last applies the final norm (the LM head / loss stay with the caller, as without pipelining)
         self.layer_ids = list(layer_range) if layer_range is not None else list(range(cfg.num_layers))
@@ -365,7 +366,7 @@ class NativeDecoder:
             rq = ew.headnorm_fwd_(qkv, layer["q_norm"], 0, Hq, hd, cfg.rms_norm_eps)
             rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
             sv.qk_rstd = (rq, rk)
-        ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
+        ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, **ew.rope_args(cfg, qkv.device))
         if cp is not None:
             o, actx = cp.forward(li, qkv, plan)
         else:
@@ -444,7 +445,7 @@ class NativeDecoder:
             do = layer["o"].backward(dx2, sv.o, sv.T_o)
             dqkv = final["cp"].backward(do, sv.attn_ctx) if final.get("cp") is not None else attn_ops.backward(do, sv.attn_ctx)
             del do
-            ew.rope_(dqkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, inverse=True)
+            ew.rope_(dqkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, inverse=True, **ew.rope_args(cfg, dqkv.device))
             if cfg.qk_norm:
                 pre = torch.empty_like(dqkv)
                 pre[:, : (Hq + Hkv) * hd] = sv.qk_pre

@@ -38,7 +38,15 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
 
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, cfg: ModelConfig | None = None
+                 ) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin [..., hd/2] of the rotary embedding; with ``cfg`` carrying a ``rope_scaling`` the frequencies and the
+    attention scale come from ``cfg.rope_inv_freq()``."""
+    if cfg is not None and cfg.rope_scaling is not None:
+        inv_l, att = cfg.rope_inv_freq()
+        inv = torch.tensor(inv_l, dtype=torch.float32, device=positions.device)
+        ang = positions.float().unsqueeze(-1) * inv
+        return ang.cos() * att, ang.sin() * att
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
     ang = positions.float().unsqueeze(-1) * inv  # [..., hd/2]
     return ang.cos(), ang.sin()
@@ -124,7 +132,7 @@ class ReferenceModel:
         cfg = self.cfg
         B, S = tokens.shape
         pos = input_pos if input_pos is not None else torch.arange(S, device=tokens.device).expand(B, S)
-        cos, sin = rope_cos_sin(pos, cfg.head_dim, cfg.rope_theta)
+        cos, sin = rope_cos_sin(pos, cfg.head_dim, cfg.rope_theta, cfg)
         mask = tree_attention_mask(group_ids, parent_ids)
         x = F.embedding(tokens, self.base["model.embed_tokens.weight"])
         for i in range(cfg.num_layers):

@@ -219,6 +219,7 @@ class TPDecoder:
             raise ValueError("heads and feed-forward width must divide over the tensor-parallel group")
         self.cfg, self.lora_cfg, self.tp = cfg, lora_cfg, tp
         self.device = dev = torch.device(device)
+        ew.rope_args(cfg, dev)               # frequency table of a scaled rotary embedding, built outside the step
         bf = torch.bfloat16
         self.embed = base["model.embed_tokens.weight"].to(dev, bf).contiguous()
         self.lm_head = base["lm_head.weight"].to(dev, bf).contiguous()
@@ -308,7 +309,7 @@ class TPDecoder:
                 rq = ew.headnorm_fwd_(qkv, layer["q_norm"], 0, Hq, hd, cfg.rms_norm_eps)
                 rk = ew.headnorm_fwd_(qkv, layer["k_norm"], Hq * hd, Hkv, hd, cfg.rms_norm_eps)
                 sv.qk_rstd = (rq, rk)
-            ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta)
+            ew.rope_(qkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, **ew.rope_args(cfg, qkv.device))
             o, actx = attn_ops.forward(qkv, Hq, Hkv, hd, plan, need_grad=save)
             x2, T_o = layer["o"].forward(o, x, use_lora, save=save)
             h2, rstd2 = ew.rmsnorm_fwd(x2, layer["ln2"], cfg.rms_norm_eps, out=self.tp.ag_input(cfg.hidden_size))
@@ -341,7 +342,7 @@ class TPDecoder:
             do = layer["o"].backward(dx2, sv.o, sv.T_o)                        # [M, q/P]
             dqkv = attn_ops.backward(do, sv.attn_ctx)
             del do
-            ew.rope_(dqkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, inverse=True)
+            ew.rope_(dqkv, pos, 0, Hq + Hkv, hd, cfg.rope_theta, inverse=True, **ew.rope_args(cfg, dqkv.device))
             if cfg.qk_norm:
                 pre = torch.empty_like(dqkv)
                 pre[:, : (Hq + Hkv) * hd] = sv.qk_pre

@@ -5,6 +5,7 @@ Each function has a ``*_reference`` twin in plain fp32 PyTorch used by the numer
 from __future__ import annotations
 
 import ctypes
+import json
 import math
 
 import torch
@@ -16,6 +17,7 @@ _sigs = {
     "artb_rmsnorm_fwd": [vp, vp, vp, vp, ci, ci, cf, vp],
     "artb_rmsnorm_bwd": [vp, vp, vp, vp, vp, vp, ci, ci, vp],
     "artb_rope": [vp, vp, ci, ci, ci, ci, ci, cf, ci, vp],
+    "artb_rope_table": [vp, vp, ci, ci, ci, ci, ci, vp, cf, ci, vp],
     "artb_swiglu_bwd": [vp, vp, vp, cl, ci, vp],
     "artb_swiglu_fwd": [vp, vp, cl, ci, vp],
     "artb_headnorm_fwd": [vp, vp, vp, ci, ci, ci, ci, ci, cf, vp],
@@ -57,12 +59,38 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
 
 
 def rope_(buf: torch.Tensor, pos: torch.Tensor, col0: int, heads: int, hd: int, theta: float,
-          inverse: bool = False) -> torch.Tensor:
-    """Rotate ``heads`` heads of width ``hd`` starting at column ``col0`` of ``buf`` [M, ld], in place."""
+          inverse: bool = False, freqs: torch.Tensor | None = None, mscale: float = 1.0) -> torch.Tensor:
+    """Rotate ``heads`` heads of width ``hd`` starting at column ``col0`` of ``buf`` [M, ld], in place.  ``freqs``
+    (fp32 [hd / 2] on the device) replaces ``theta ** (-2 i / hd)`` for frequency-scaled rotary embeddings; ``mscale``
+    multiplies cos and sin (see :func:`rope_args`)."""
     assert pos.dtype == torch.int32 and buf.stride(1) == 1
-    _lib.check_rc(_f("artb_rope")(_lib.ptr(buf), _lib.ptr(pos), buf.shape[0], buf.stride(0), col0, heads, hd, theta,
-                                  1 if inverse else 0, _lib.stream_ptr()), "rope")
+    if freqs is None:
+        _lib.check_rc(_f("artb_rope")(_lib.ptr(buf), _lib.ptr(pos), buf.shape[0], buf.stride(0), col0, heads, hd, theta,
+                                      1 if inverse else 0, _lib.stream_ptr()), "rope")
+    else:
+        assert freqs.dtype == torch.float32 and freqs.numel() == hd // 2 and freqs.is_contiguous() and freqs.device == buf.device
+        _lib.check_rc(_f("artb_rope_table")(_lib.ptr(buf), _lib.ptr(pos), buf.shape[0], buf.stride(0), col0, heads, hd,
+                                            _lib.ptr(freqs), mscale, 1 if inverse else 0,
+                                            _lib.stream_ptr()), "rope_table")
     return buf
+
+
+_rope_tables: dict = {}
+
+
+def rope_args(cfg, device) -> dict:
+    """Keyword arguments of :func:`rope_` for a model configuration: empty for the plain rotation, else the frequency
+    table of ``cfg.rope_inv_freq()`` on ``device`` (built once per configuration and device) and the attention scale."""
+    if getattr(cfg, "rope_scaling", None) is None:
+        return {}
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    key = (cfg.head_dim, cfg.rope_theta, json.dumps(cfg.rope_scaling, sort_keys=True), str(device))
+    if key not in _rope_tables:
+        inv, att = cfg.rope_inv_freq()
+        _rope_tables[key] = {"freqs": torch.tensor(inv, dtype=torch.float32, device=device), "mscale": float(att)}
+    return _rope_tables[key]
 
 
 def swiglu_fwd(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -125,12 +153,12 @@ def rmsnorm_reference(x, w, eps):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype).float() * w.float()
 
 
-def rope_reference(x, pos, theta, inverse=False):
+def rope_reference(x, pos, theta, inverse=False, freqs=None, mscale=1.0):
     """x [M, H, hd] float; rotate-half."""
     hd = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, device=x.device, dtype=torch.float32) / hd))
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, device=x.device, dtype=torch.float32) / hd)) if freqs is None else freqs
     ang = pos.float().unsqueeze(-1) * inv
-    c, s = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    c, s = ang.cos().unsqueeze(1) * mscale, ang.sin().unsqueeze(1) * mscale
     if inverse:
         s = -s
     x1, x2 = x[..., : hd // 2].float(), x[..., hd // 2:].float()

@@ -179,7 +179,7 @@ def test_http_load_benchmark_runs_against_the_server(tmp_path):
                               prompt_tokens=120, max_tokens=5, stream=stream, path=str(tmp_path / f"s{int(stream)}"),
                               engine_args={"max_model_len": 256, "num_scheduler_steps": 2}))
         assert res["concurrency"] == 6 and res["iterations"] == 2
-        assert res["avg_completion_tokens"] == 5.0 and res["avg_prompt_tokens"] > 20
+        assert 4.0 < res["avg_completion_tokens"] <= 5.0 and res["avg_prompt_tokens"] > 20    # a sampled EOS ends early
         assert res["requests_per_s"] > 0 and res["completion_tokens_per_s"] > 0
         assert res["request_s"]["max"] <= res["iteration_s"]["max"] + 1e-3
         assert ("ttft_s" in res) == stream
