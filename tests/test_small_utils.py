@@ -1,0 +1,106 @@
+"""Small helpers of the public surface that the larger tests do not reach."""
+import asyncio
+import os
+
+import httpx
+import pandas as pd
+import pytest
+
+import art_b200 as art
+from art_b200.errors import (ForbiddenBucketCreationError, LoRADeploymentTimedOutError,
+                             UnsupportedBaseModelDeploymentError, UnsupportedLoRADeploymentProviderError)
+from art_b200.local.checkpoints import get_last_checkpoint_dir
+from art_b200.utils.benchmark_rollout import benchmark_rollout
+from art_b200.utils.benchmarking.filter_model_split import filter_rename_model_split
+from art_b200.utils.benchmarking.types import BenchmarkModelKey
+from art_b200.utils.get_repo_root_path import get_repo_root_path
+from art_b200.utils.get_trajectory_messages import get_trajectory_messages
+from art_b200.utils.litellm import convert_litellm_choice_to_openai
+from art_b200.utils.log_http_errors import log_http_errors
+from art_b200.utils.old_benchmarking.calculate_step_metrics import calculate_step_std_dev
+from tests.test_api_trajectories import make_choice
+
+
+def test_litellm_choice_keeps_tool_calls_and_logprobs():
+    raw = {"index": 1, "finish_reason": "tool_calls",
+           "message": {"content": None, "tool_calls": [{"id": "c1", "function": {"name": "f", "arguments": '{"x": 1}'}}]},
+           "logprobs": {"content": [{"token": "token_id:5", "logprob": -0.25, "bytes": [53]}]}}
+    ch = convert_litellm_choice_to_openai(raw)
+    assert ch.index == 1 and ch.finish_reason == "tool_calls"
+    assert ch.message.tool_calls[0].function.name == "f" and ch.message.tool_calls[0].function.arguments == '{"x": 1}'
+    assert ch.logprobs.content[0].token == "token_id:5" and ch.logprobs.content[0].logprob == -0.25
+
+    class Obj:                      # attribute-style objects work as well as dictionaries
+        index, finish_reason, logprobs = 0, None, None
+        message = type("M", (), {"content": "hi", "tool_calls": None})()
+
+    ch = convert_litellm_choice_to_openai(Obj())
+    assert ch.message.content == "hi" and ch.finish_reason == "stop" and ch.logprobs is None
+    art.Trajectory(messages_and_choices=[{"role": "user", "content": "q"}, ch], reward=1.0)       # usable as a choice
+
+
+def test_log_http_errors_shows_the_servers_detail():
+    req = httpx.Request("POST", "http://h/x")
+
+    @log_http_errors
+    async def with_detail():
+        raise httpx.HTTPStatusError("boom", request=req, response=httpx.Response(422, json={"detail": "bad rows"}, request=req))
+
+    @log_http_errors
+    async def without_json():
+        raise httpx.HTTPStatusError("boom", request=req, response=httpx.Response(500, text="<html>", request=req))
+
+    with pytest.raises(Exception, match=r"\[HTTP 422\] http://h/x bad rows"):
+        asyncio.run(with_detail())
+    with pytest.raises(httpx.HTTPStatusError):
+        asyncio.run(without_json())
+
+
+def test_benchmark_rollout_averages_rewards_and_tolerates_failures():
+    async def rollout(model: str, i: int, is_training: bool) -> art.Trajectory:
+        assert model == "m" and not is_training
+        if i == 2:
+            raise RuntimeError("rollout failed")
+        return art.Trajectory(messages_and_choices=[{"role": "user", "content": "q"}, make_choice(content="a")], reward=float(i))
+
+    assert asyncio.run(benchmark_rollout("m", 4, rollout)) == pytest.approx((0 + 1 + 3) / 3)
+
+
+def test_trajectory_messages_and_step_spread():
+    t = art.Trajectory(messages_and_choices=[{"role": "user", "content": "q"}, make_choice(content="a")], reward=1.0)
+    assert get_trajectory_messages(t) == [{"role": "user", "content": "q"}, {"role": "assistant", "content": "a"}]
+
+    def group(rewards):
+        return art.TrajectoryGroup([art.Trajectory(messages_and_choices=[{"role": "user", "content": "q"}, make_choice(content="a")],
+                                                   reward=r) for r in rewards])
+
+    # population standard deviation per group, averaged; a single-trajectory group does not count
+    assert calculate_step_std_dev([group([0.0, 1.0]), group([1.0, 1.0, 1.0]), group([5.0])]) == pytest.approx(0.25)
+    assert calculate_step_std_dev([]) == 0.0
+
+
+def test_filter_rename_model_split():
+    df = pd.DataFrame({"model": ["a", "a", "b", "c"], "split": ["val", "train", "val", "val"], "reward": [1, 2, 3, 4]})
+    out = filter_rename_model_split(df, [BenchmarkModelKey("a", "Model A", "val"), BenchmarkModelKey("b")])
+    assert out["model"].tolist() == ["Model A", "b"] and out["reward"].tolist() == [1, 3]
+    assert filter_rename_model_split(df, BenchmarkModelKey("a", split="train"))["reward"].tolist() == [2]
+    assert filter_rename_model_split(df, []).empty and df["model"].tolist() == ["a", "a", "b", "c"]       # input untouched
+
+
+def test_error_types_carry_their_http_status():
+    for cls, code in ((ForbiddenBucketCreationError, 403), (UnsupportedLoRADeploymentProviderError, 400),
+                      (UnsupportedBaseModelDeploymentError, 400), (LoRADeploymentTimedOutError, 504)):
+        e = cls("why")
+        assert e.status_code == code and e.detail == "why"
+
+
+def test_repo_root_and_last_checkpoint_dir(tmp_path):
+    (tmp_path / ".git").mkdir()
+    deep = tmp_path / "a" / "b"
+    deep.mkdir(parents=True)
+    assert get_repo_root_path(str(deep)) == str(tmp_path)
+    out = tmp_path / "model"
+    assert get_last_checkpoint_dir(str(out)) is None
+    for name in ("0000", "0003", "0010", "logs", "0011.tmp"):
+        (out / name).mkdir(parents=True)
+    assert os.path.basename(get_last_checkpoint_dir(str(out))) == "0010"
