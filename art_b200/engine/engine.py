@@ -49,11 +49,13 @@ class SamplingParams:
     logit_bias: dict[int, float] | None = None
     stream_events: bool = True             # False: only the final event is delivered (see Engine.complete)
     include_stop_str_in_output: bool = False   # keep the matched stop string at the end of the returned text
+    guided_regex: str | None = None        # the completion's text has to match this expression (engine/grammar.py);
+                                           # needs Engine.token_masker (the server sets it from its tokenizer)
 
     @property
     def needs_logits(self) -> bool:
         return (self.top_logprobs > 0 or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
-                or self.frequency_penalty != 0.0 or bool(self.logit_bias))
+                or self.frequency_penalty != 0.0 or bool(self.logit_bias) or self.guided_regex is not None)
 
 
 @dataclass
@@ -144,6 +146,7 @@ class Engine:
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self._outbox: dict = {}     # event loop -> {queue: [TokenEvent, ...]} of the scheduler step in progress
+        self.token_masker = None    # grammar.TokenMasker of the serving tokenizer: enables SamplingParams.guided_regex
         self.max_recoveries = 3     # automatic restarts of the stepping thread after an error (see recover())
         self.recoveries = 0
         self.score_queue: deque = deque()
@@ -271,7 +274,14 @@ class Engine:
             if adapter_name not in self.adapters:
                 raise KeyError(f"unknown adapter {adapter_name!r}")
             adapter = self.adapters[adapter_name]
-        return Sequence(prompt_ids, params, adapter, loop)
+        seq = Sequence(prompt_ids, params, adapter, loop)
+        if params.guided_regex is not None:
+            if self.token_masker is None:
+                raise ValueError("guided_regex needs Engine.token_masker (a grammar.TokenMasker over the tokenizer's vocabulary)")
+            from .grammar import GrammarState, compile_cached
+
+            seq.proc.grammar = GrammarState(compile_cached(params.guided_regex), self.token_masker)
+        return seq
 
     def abort(self, seq: Sequence) -> None:
         seq.aborted = True
@@ -344,7 +354,12 @@ class Engine:
         self.stats.generated_tokens += 1
         p = seq.params
         reason = None
-        if not p.ignore_eos and self.eos is not None and tok == self.eos:
+        grammar = seq.proc.grammar if seq.proc is not None else None
+        if grammar is not None:
+            grammar.advance(tok)
+        if grammar is not None and (grammar.exhausted or (self.eos is not None and tok == self.eos)):
+            reason = "stop"         # nothing can follow (or the automaton accepted and the model ended the text)
+        elif not p.ignore_eos and self.eos is not None and tok == self.eos:
             reason = "stop"
         elif p.stop_token_ids and tok in p.stop_token_ids:
             reason = "stop"

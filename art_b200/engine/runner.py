@@ -34,11 +34,31 @@ class LogitProc:
     frequency_penalty: float = 0.0
     logit_bias: dict | None = None
     top_logprobs: int = 0
+    grammar: object | None = None       # grammar.GrammarState: only tokens of its mask may be drawn
 
     @property
     def edits(self) -> bool:
         return (self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
                 or bool(self.logit_bias))
+
+
+def apply_token_mask(logits: torch.Tensor, grammars: list) -> torch.Tensor:
+    """Sets the logits of tokens outside each row's grammar mask to -1e30 (finite: the samplers scale logits by an
+    inverse temperature that may be 0), in place.  ``logits`` [M, V] fp32; ``grammars[i]`` is None or a
+    ``grammar.GrammarState``.  Ids past the tokenizer's vocabulary (padding rows of the embedding) are never allowed; a
+    row whose mask is empty is left alone.  Plain PyTorch: the path is taken one decode step at a time and only by
+    requests with structured outputs."""
+    V = logits.shape[1]
+    for i, g in enumerate(grammars):
+        if g is None:
+            continue
+        m = torch.from_numpy(g.allowed())
+        if not bool(m[:V].any()):
+            continue
+        allowed = torch.zeros(V, dtype=torch.bool)
+        allowed[: min(V, m.numel())] = m[:V]
+        logits[i].masked_fill_(~allowed.to(logits.device), -1e30)
+    return logits
 
 
 @dataclass
@@ -100,6 +120,8 @@ class ReferenceRunner:
 
             if sv.proc.edits:
                 logits = logit_adjust_(logits[None].clone(), build_logit_edits([(sv.proc, sv.tokens)]))[0]
+            if sv.proc.grammar is not None:
+                logits = apply_token_mask(logits[None].clone(), [sv.proc.grammar])[0]
             if sv.proc.top_logprobs > 0:
                 it = torch.tensor([0.0 if sv.temperature <= 0 else 1.0 / sv.temperature])
                 ti, tl = top_logprobs(logits[None].cpu(), it, sv.proc.top_logprobs)
@@ -493,6 +515,9 @@ class NativeRunner:
                 logits = allv.permute(1, 0, 2).reshape(logits.shape[0], -1).contiguous()
             n = len(procs)
             paged.logit_adjust_(logits, paged.build_logit_edits([p if p is not None and p[0].edits else None for p in procs]))
+            grammars = [p[0].grammar if p is not None else None for p in procs]
+            if any(g is not None for g in grammars):
+                apply_token_mask(logits, grammars + [None] * (logits.shape[0] - len(grammars)))
             kmax = max((p[0].top_logprobs for p in procs if p is not None), default=0)
             if kmax > 0:
                 ti, tl = paged.top_logprobs(logits, inv_t, kmax)

@@ -262,7 +262,8 @@ class OpenAIServer:
                               min_p=float(body.get("min_p") or 0.0),
                               n=int(body.get("n") or 1), stop=stop, stop_token_ids=body.get("stop_token_ids"),
                               seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
-                              guided_choice=body.get("guided_choice"),
+                              guided_choice=body.get("guided_choice") or (body.get("structured_outputs") or {}).get("choice")
+                              if not body.get("guided_regex") else None,
                               include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)))
 
     @staticmethod
@@ -271,7 +272,7 @@ class OpenAIServer:
         tool's parameter schema admits exactly one value per field (one-value enums / consts, which is what
         ``art.guided_completion.freeze_tool_schema`` builds for distillation), the whole call is determined and is
         returned here as Hermes-format text; the request then runs like ``guided_choice`` with that one candidate.
-        Schemas that leave freedom would need grammar-constrained decoding, which this server does not have: 400."""
+        A schema that leaves freedom returns None here and becomes a constraint on the decoding (:meth:`_guided_regex`)."""
         choice = body.get("tool_choice")
         if not isinstance(choice, dict) or choice.get("type") != "function":
             return None
@@ -287,9 +288,63 @@ class OpenAIServer:
             elif isinstance(spec.get("enum"), list) and len(spec["enum"]) == 1:
                 args[key] = spec["enum"][0]
             else:
-                raise HTTPException(status_code=400, detail=f"a named tool_choice needs a schema with one value per field "
-                                                            f"(field {key!r} is free); use tool_choice=\"auto\" instead")
+                return None
         return "<tool_call>\n" + json.dumps({"name": name, "arguments": args}) + "\n</tool_call>"
+
+    @staticmethod
+    def _has_constraint(body: dict) -> bool:
+        """Whether the request carries any structured-output field (the common request has none and is not made to
+        wait for the worker thread that compiles constraints)."""
+        choice = body.get("tool_choice")
+        return bool(body.get("guided_regex") or body.get("guided_json") is not None or body.get("structured_outputs")
+                    or body.get("guided_grammar") or (body.get("response_format") or {}).get("type") in ("json_object", "json_schema")
+                    or choice == "required" or (isinstance(choice, dict) and choice.get("type") == "function"))
+
+    def _guided_regex(self, body: dict) -> str | None:
+        """The regular expression a completion has to match, from whichever structured-output field the request uses:
+        ``guided_regex``, ``guided_json``, ``response_format`` (``json_object`` / ``json_schema``), ``structured_outputs``
+        (``{"regex" | "json" | "choice": ...}``), or a ``tool_choice`` that demands a call (a named function, or
+        ``"required"``: Hermes-format call text whose arguments satisfy the tool's parameter schema)."""
+        from .grammar import RegexError, compile_cached, escape_literal, schema_to_regex
+
+        so = body.get("structured_outputs") or {}
+        try:
+            rx = body.get("guided_regex") or so.get("regex")
+            schema = body.get("guided_json") if body.get("guided_json") is not None else so.get("json")
+            if rx is None and schema is not None:
+                rx = schema_to_regex(schema)
+            if rx is None and so.get("choice"):
+                rx = "(" + "|".join(escape_literal(str(c)) for c in so["choice"]) + ")"
+            fmt = body.get("response_format") or {}
+            if rx is None and fmt.get("type") == "json_object":
+                rx = schema_to_regex({"type": "object"})
+            if rx is None and fmt.get("type") == "json_schema":
+                rx = schema_to_regex((fmt.get("json_schema") or {}).get("schema", True))
+            choice = body.get("tool_choice")
+            if rx is None and (choice == "required" or (isinstance(choice, dict) and choice.get("type") == "function")):
+                tools = [t.get("function") or {} for t in body.get("tools") or []]
+                if isinstance(choice, dict):
+                    name = (choice.get("function") or {}).get("name")
+                    tools = [t for t in tools if t.get("name") == name]
+                if not tools:
+                    raise HTTPException(status_code=400, detail="tool_choice demands a call but no matching tool is given")
+                calls = [r'\{"name": "' + escape_literal(t["name"]) + '", "arguments": '
+                         + schema_to_regex(t.get("parameters") or {"type": "object"}) + r"\}" for t in tools]
+                rx = "<tool_call>\n(" + "|".join(calls) + ")\n</tool_call>"
+            if body.get("guided_grammar") or so.get("grammar"):
+                raise HTTPException(status_code=400, detail="context-free grammars are not supported; use a JSON schema or a regular expression")
+            if rx is not None:
+                compile_cached(rx)             # syntax and size errors surface here, as a 400
+        except (RegexError, ValueError, KeyError, TypeError) as e:
+            raise HTTPException(status_code=400, detail=f"cannot build the structured-output constraint: {e}") from e
+        return rx
+
+    def _ensure_masker(self) -> None:
+        """The allowed-token index of the serving tokenizer, built at the first structured-output request."""
+        if self.engine.token_masker is None:
+            from .grammar import TokenMasker, vocabulary_bytes
+
+            self.engine.token_masker = TokenMasker(vocabulary_bytes(self.tok), self.engine.eos)
 
     def _render_chat(self, body: dict) -> list[int]:
         tools = body.get("tools")
@@ -442,10 +497,15 @@ class OpenAIServer:
             forced = srv._forced_tool_call(body)
             if forced is not None:
                 params.guided_choice = [forced]       # the call is teacher-forced and comes back with its log-probs
+            elif not params.guided_choice and srv._has_constraint(body):
+                params.guided_regex = await asyncio.to_thread(srv._guided_regex, body)
+                if params.guided_regex is not None:
+                    await asyncio.to_thread(srv._ensure_masker)
+            demanded = forced is not None or (params.guided_regex or "").startswith("<tool_call>")
             rid = "chatcmpl-" + uuid.uuid4().hex
             srv._log_request(rid, body, prompt_ids, params)
             model_name = body.get("model") or srv.base_model_name
-            tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and (srv.auto_tools or forced is not None)
+            tools_on = bool(body.get("tools")) and body.get("tool_choice") != "none" and (srv.auto_tools or demanded)
             if body.get("stream"):
                 include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
                 return StreamingResponse(srv._counted(srv._chat_stream(request, rid, model_name, prompt_ids, params, adapter,
@@ -468,6 +528,10 @@ class OpenAIServer:
             prompt = body.get("prompt", "")
             prompt_ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else srv.tok.encode(prompt)
             params = srv._params(body, len(prompt_ids))
+            if not params.guided_choice and srv._has_constraint({**body, "tool_choice": None}):
+                params.guided_regex = await asyncio.to_thread(srv._guided_regex, {**body, "tool_choice": None})
+                if params.guided_regex is not None:
+                    await asyncio.to_thread(srv._ensure_masker)
             info: dict = {}
             srv._log_request("cmpl", body, prompt_ids, params)
             out = await srv._collect(request, prompt_ids, params, adapter, info)

@@ -256,9 +256,10 @@ def test_named_tool_choice_with_a_frozen_schema_forces_the_call(long_server):
             call = ch["message"]["tool_calls"][0]["function"]
             assert call["name"] == "move" and json.loads(call["arguments"]) == {"direction": "left", "steps": 2}
             assert len(ch["logprobs"]["content"]) > 5 and all(e["logprob"] <= 0 for e in ch["logprobs"]["content"])
-            # a schema that leaves a field free cannot be forced without constrained decoding
-            r = await c.post("/v1/chat/completions", json={**body, "tools": [tool]})
-            assert r.status_code == 400 and "free" in r.json()["detail"]
+            # a schema that leaves fields free is enforced by constrained decoding instead: still a call of that tool
+            r = await c.post("/v1/chat/completions", json={**body, "tools": [tool], "max_tokens": 200, "seed": 0})
+            call = r.json()["choices"][0]["message"]["tool_calls"][0]["function"]
+            assert call["name"] == "move" and set(json.loads(call["arguments"])) <= {"direction", "steps"}
             r = await c.post("/v1/chat/completions", json={**body, "tool_choice": {"type": "function", "function": {"name": "nope"}}})
             assert r.status_code == 400
     asyncio.run(main())
@@ -398,4 +399,57 @@ def test_reasoning_content_in_full_and_streamed_answers(long_server):
             think = "".join(ch["choices"][0]["delta"].get("reasoning_content") or "" for ch in chunks if ch["choices"])
             text = "".join(ch["choices"][0]["delta"].get("content") or "" for ch in chunks if ch["choices"])
             assert think == "two and two" and text == "four"
+    asyncio.run(main())
+
+
+def test_structured_outputs_constrain_the_completion(long_server):
+    """``guided_regex``, ``guided_json``, ``response_format`` and a tool_choice that demands a call of a tool with a
+    free schema: a random-weight model produces text that satisfies the constraint, with a log-prob per token."""
+    import re
+
+    srv = long_server
+    schema = {"type": "object", "properties": {"city": {"type": "string", "maxLength": 12}, "days": {"type": "integer", "minimum": 0, "maximum": 999},
+                                               "units": {"enum": ["C", "F"]}}, "required": ["city", "days"]}
+    tools = [{"type": "function", "function": {"name": "forecast", "parameters": schema}}]
+    msgs = [{"role": "user", "content": "weather?"}]
+
+    async def main():
+        async with client(srv) as c:
+            async def ask(**kw):
+                r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "max_tokens": 120,
+                                                               "seed": 3, **kw})
+                assert r.status_code == 200, r.text
+                return r.json()["choices"][0]
+
+            ch = await ask(guided_regex=r"(yes|no|maybe)[.!]")
+            assert re.fullmatch(r"(yes|no|maybe)[.!]", ch["message"]["content"]) and ch["finish_reason"] == "stop"
+            assert len(ch["logprobs"]["content"]) == len(ch["message"]["content"])          # byte tokenizer: one per character
+            ch = await ask(guided_json=schema)
+            val = json.loads(ch["message"]["content"])
+            assert isinstance(val["city"], str) and len(val["city"]) <= 12 and isinstance(val["days"], int)
+            assert val.get("units", "C") in ("C", "F")
+            ch = await ask(response_format={"type": "json_schema", "json_schema": {"name": "s", "schema": schema}}, temperature=0)
+            assert set(json.loads(ch["message"]["content"])) >= {"city", "days"}
+            ch = await ask(tools=tools, tool_choice={"type": "function", "function": {"name": "forecast"}})
+            call = ch["message"]["tool_calls"][0]["function"]
+            assert call["name"] == "forecast" and isinstance(json.loads(call["arguments"])["days"], int)
+            assert ch["finish_reason"] == "tool_calls"
+            ch = await ask(tools=tools, tool_choice="required", stream=False)
+            assert ch["message"]["tool_calls"][0]["function"]["name"] == "forecast"
+            # streamed, two choices
+            r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "max_tokens": 40, "n": 2,
+                                                           "guided_regex": r"[0-9]{3}-[0-9]{4}", "stream": True})
+            text = {0: "", 1: ""}
+            for line in r.text.splitlines():
+                if line.startswith("data: {"):
+                    for chs in json.loads(line[6:])["choices"]:
+                        text[chs["index"]] += chs["delta"].get("content") or ""
+            assert all(re.fullmatch(r"[0-9]{3}-[0-9]{4}", t) for t in text.values())
+            # /v1/completions takes the same fields; bad constraints are the caller's error
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": "n=", "max_tokens": 10, "guided_regex": r"-?[1-9][0-9]?"})
+            assert re.fullmatch(r"-?[1-9][0-9]?", r.json()["choices"][0]["text"])
+            r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "guided_regex": "(unclosed"})
+            assert r.status_code == 400 and "structured-output" in r.text
+            r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "guided_grammar": "root ::= x"})
+            assert r.status_code == 400
     asyncio.run(main())
