@@ -91,6 +91,12 @@ class SkyPilotBackend(Backend):
     async def _endpoint(self, port: int) -> str:
         return await utils._endpoint(self._cluster_name, port, self._sky)
 
+    async def register(self, model) -> None:
+        """Registers the model with the server on the cluster (and says where its logs are)."""
+        print("Registering model with server")
+        print(f"To view logs, run: 'sky logs {self._cluster_name}'")
+        await super().register(model)
+
     async def _prepare_backend_for_training(self, model, config: dev.OpenAIServerConfig | None) -> tuple[str, str]:
         """The completion server is reached through the cluster's public port-8000 endpoint."""
         _, api_key = await super()._prepare_backend_for_training(model, config)
