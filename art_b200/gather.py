@@ -62,8 +62,8 @@ _ctx_var: contextvars.ContextVar[GatherContext] = contextvars.ContextVar("art_b2
 
 
 @contextlib.contextmanager
-def set_gather_context(ctx: GatherContext) -> Iterator[None]:
-    tok = _ctx_var.set(ctx)
+def set_gather_context(context: GatherContext) -> Iterator[None]:
+    tok = _ctx_var.set(context)
     try:
         yield
     finally:
@@ -74,14 +74,14 @@ def get_gather_context() -> GatherContext:
     return _ctx_var.get()
 
 
-def record_metrics(ctx: GatherContext, trajectory: Trajectory) -> None:
+def record_metrics(context: GatherContext, trajectory: Trajectory) -> None:
     lps = [m.logprobs for m in trajectory.messages_and_choices if isinstance(m, Choice) and m.logprobs]
     if lps:
         trajectory.metrics["completion_tokens"] = sum(len(l.content or l.refusal or []) for l in lps) / len(lps)
-    ctx.metric_sums["reward"] += trajectory.reward  # type: ignore[assignment]
-    ctx.metric_divisors["reward"] += 1
-    ctx.metric_sums.update(trajectory.metrics)
-    ctx.metric_divisors.update(trajectory.metrics.keys())
+    context.metric_sums["reward"] += trajectory.reward  # type: ignore[assignment]
+    context.metric_divisors["reward"] += 1
+    context.metric_sums.update(trajectory.metrics)
+    context.metric_divisors.update(trajectory.metrics.keys())
 
 
 async def wrap_group_awaitable(awaitable: Awaitable[TrajectoryGroup]) -> TrajectoryGroup | None:

@@ -140,7 +140,7 @@ class PackedDataset(torch.utils.data.Dataset):
         return {k: v[i] for k, v in self.tensors.items()}  # type: ignore[return-value]
 
 
-def plot_packed_tensors(packed: PackedTensors, path: str | None = None) -> None:
+def plot_packed_tensors(packed_tensors: PackedTensors, path: str | None = None) -> None:
     """Eight heat-maps of the packed tensors (needs matplotlib; written to ``path`` if given)."""
     try:
         import matplotlib
@@ -151,7 +151,7 @@ def plot_packed_tensors(packed: PackedTensors, path: str | None = None) -> None:
         raise RuntimeError("plot_packed_tensors needs matplotlib, which is not installed") from e
     fig, axes = plt.subplots(4, 2, figsize=(15, 24))
     for ax, key in zip(axes.flat, KEYS_DTYPES):
-        im = ax.imshow(packed[key].float().nan_to_num().numpy(), aspect="auto", cmap="viridis")  # type: ignore[literal-required]
+        im = ax.imshow(packed_tensors[key].float().nan_to_num().numpy(), aspect="auto", cmap="viridis")  # type: ignore[literal-required]
         ax.set_title(key)
         ax.set_xlabel("Sequence Position")
         ax.set_ylabel("Batch")

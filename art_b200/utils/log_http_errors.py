@@ -5,11 +5,11 @@ import functools
 import httpx
 
 
-def log_http_errors(fn):
-    @functools.wraps(fn)
+def log_http_errors(func):
+    @functools.wraps(func)
     async def wrapper(*a, **kw):
         try:
-            return await fn(*a, **kw)
+            return await func(*a, **kw)
         except httpx.HTTPStatusError as e:
             try:
                 detail = e.response.json().get("detail")

@@ -10,29 +10,29 @@ from openai.types.chat.chat_completion import Choice
 from ..trajectories import Trajectory, TrajectoryGroup
 
 
-def message_or_choice_to_dict(item) -> dict[str, Any]:
-    d = dict(item) if isinstance(item, dict) else item.to_dict()
+def message_or_choice_to_dict(message_or_choice) -> dict[str, Any]:
+    d = dict(message_or_choice) if isinstance(message_or_choice, dict) else message_or_choice.to_dict()
     d.pop("logprobs", None)
     return d
 
 
-def trajectory_to_dict(t: Trajectory) -> dict[str, Any]:
+def trajectory_to_dict(trajectory: Trajectory) -> dict[str, Any]:
     return {
-        "reward": t.reward,
-        "metrics": dict(t.metrics),
-        "metadata": dict(t.metadata),
-        "messages_and_choices": [message_or_choice_to_dict(m) for m in t.messages_and_choices],
-        "logs": list(t.logs),
+        "reward": trajectory.reward,
+        "metrics": dict(trajectory.metrics),
+        "metadata": dict(trajectory.metadata),
+        "messages_and_choices": [message_or_choice_to_dict(m) for m in trajectory.messages_and_choices],
+        "logs": list(trajectory.logs),
     }
 
 
-def trajectory_group_to_dict(g: TrajectoryGroup) -> dict[str, Any]:
-    return {"trajectories": [trajectory_to_dict(t) for t in g.trajectories if isinstance(t, Trajectory)],
-            "metadata": dict(g.metadata)}
+def trajectory_group_to_dict(trajectory_group: TrajectoryGroup) -> dict[str, Any]:
+    return {"trajectories": [trajectory_to_dict(t) for t in trajectory_group.trajectories if isinstance(t, Trajectory)],
+            "metadata": dict(trajectory_group.metadata)}
 
 
-def serialize_trajectory_groups(groups: list[TrajectoryGroup]) -> str:
-    return yaml.safe_dump([trajectory_group_to_dict(g) for g in groups], sort_keys=True)
+def serialize_trajectory_groups(trajectory_groups: list[TrajectoryGroup]) -> str:
+    return yaml.safe_dump([trajectory_group_to_dict(g) for g in trajectory_groups], sort_keys=True)
 
 
 def dict_to_message_or_choice(d: dict[str, Any]):
@@ -54,5 +54,5 @@ def dict_to_trajectory_group(d: dict[str, Any]) -> TrajectoryGroup:
     return TrajectoryGroup([dict_to_trajectory(t) for t in d["trajectories"]], metadata=d.get("metadata", {}), exceptions=[])
 
 
-def deserialize_trajectory_groups(text: str) -> list[TrajectoryGroup]:
-    return [dict_to_trajectory_group(g) for g in (yaml.safe_load(text) or [])]
+def deserialize_trajectory_groups(serialized: str) -> list[TrajectoryGroup]:
+    return [dict_to_trajectory_group(g) for g in (yaml.safe_load(serialized) or [])]
