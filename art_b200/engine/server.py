@@ -525,30 +525,139 @@ class OpenAIServer:
             idx = srv._pick_replica() if srv.peers and not request.headers.get("x-art-routed") else 0
             if idx:
                 return await srv._forward(idx, "/v1/completions", body, request)
-            prompt = body.get("prompt", "")
-            prompt_ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else srv.tok.encode(prompt)
-            params = srv._params(body, len(prompt_ids))
+            prompts = srv._completion_prompts(body.get("prompt", ""))
+            params = srv._params(body, max(len(p) for p in prompts))
+            for p in prompts:
+                if len(p) + 1 >= srv.engine.max_model_len:
+                    raise HTTPException(status_code=400, detail=f"prompt has {len(p)} tokens; the maximum context length "
+                                                                f"is {srv.engine.max_model_len}")
             if not params.guided_choice and srv._has_constraint({**body, "tool_choice": None}):
                 params.guided_regex = await asyncio.to_thread(srv._guided_regex, {**body, "tool_choice": None})
                 if params.guided_regex is not None:
                     await asyncio.to_thread(srv._ensure_masker)
+            rid = "cmpl-" + uuid.uuid4().hex
+            model_name = body.get("model") or srv.base_model_name
+            srv._log_request(rid, body, prompts[0], params)
+            echo = bool(body.get("echo"))
+            if body.get("stream"):
+                include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+                return StreamingResponse(srv._counted(srv._completion_stream(rid, model_name, prompts, params, adapter, echo,
+                                                                             include_usage)),
+                                         media_type="text/event-stream")
             info: dict = {}
-            srv._log_request("cmpl", body, prompt_ids, params)
-            out = await srv._collect(request, prompt_ids, params, adapter, info)
+            srv._load[0] += 1
+            try:
+                outs = await asyncio.gather(*[srv._collect(request, p, params, adapter, info) for p in prompts])
+                heads = await asyncio.gather(*[srv._echo_part(p, adapter, params) for p in prompts]) if echo else None
+            finally:
+                srv._load[0] -= 1
             choices = []
-            for i, (ids, lps, reason, tops) in enumerate(out):
-                lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": lps}
-                if params.top_logprobs > 0:
-                    lpo["top_logprobs"] = [{srv._token_str(t): l for t, l in (top or []) if t >= 0} for top in tops]
-                choices.append({"index": i, "text": srv._cut_at_stop(srv.tok.decode(ids, skip_special_tokens=True), params),
-                                "finish_reason": reason,
-                                "logprobs": lpo})
-            comp = sum(len(o[0]) for o in out)
-            return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": _now(),
-                    "model": body.get("model") or srv.base_model_name, "choices": choices,
-                    "usage": srv._usage(len(prompt_ids), comp, info)}
+            for pi, out in enumerate(outs):
+                for i, (ids, lps, reason, tops) in enumerate(out):
+                    lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": list(lps)}
+                    if params.top_logprobs > 0:
+                        lpo["top_logprobs"] = [{srv._token_str(t): l for t, l in (top or []) if t >= 0} for top in tops]
+                    text = srv._cut_at_stop(srv.tok.decode(ids, skip_special_tokens=True), params)
+                    if echo:        # the prompt comes back in front, its tokens with their log-probs (None for the first)
+                        h_text, h_tokens, h_lps = heads[pi]
+                        text = h_text + text
+                        lpo["tokens"] = h_tokens + lpo["tokens"]
+                        lpo["token_logprobs"] = h_lps + lpo["token_logprobs"]
+                        if "top_logprobs" in lpo:
+                            lpo["top_logprobs"] = [None] * len(h_tokens) + lpo["top_logprobs"]
+                    choices.append({"index": pi * params.n + i, "text": text, "finish_reason": reason, "logprobs": lpo})
+            comp = sum(len(o[0]) for out in outs for o in out)
+            return {"id": rid, "object": "text_completion", "created": _now(), "model": model_name, "choices": choices,
+                    "usage": srv._usage(sum(len(p) for p in prompts), comp, info)}
 
         return app
+
+    def _completion_prompts(self, prompt) -> list[list[int]]:
+        """``prompt`` of ``/v1/completions``: a string, a list of token ids, or a list of either (one request each)."""
+        def one(p) -> list[int]:
+            if isinstance(p, str):
+                return self.tok.encode(p)
+            if isinstance(p, list) and all(isinstance(t, int) for t in p):
+                return list(p)
+            raise HTTPException(status_code=400, detail="prompt must be a string, a list of token ids, or a list of those")
+
+        if isinstance(prompt, list) and prompt and not isinstance(prompt[0], int):
+            out = [one(p) for p in prompt]
+        else:
+            out = [one(prompt)]
+        if any(not p for p in out):
+            raise HTTPException(status_code=400, detail="empty prompt")
+        return out
+
+    async def _echo_part(self, prompt_ids: list[int], adapter, params: SamplingParams) -> tuple[str, list[str], list]:
+        """Text, token strings and log-probs (None for the first token) of a prompt that ``echo`` sends back."""
+        lps: list = [None]
+        if len(prompt_ids) > 1:
+            lps += await self.engine.score(prompt_ids[:1], prompt_ids[1:], adapter)
+        return self.tok.decode(prompt_ids, skip_special_tokens=True), [self._token_str(t) for t in prompt_ids], lps
+
+    async def _completion_stream(self, rid, model_name, prompts, params, adapter, echo: bool, include_usage: bool
+                                 ) -> AsyncIterator[str]:
+        """Event stream of ``/v1/completions``: one chunk per token and choice with the new text, the token and its
+        log-prob; choices of several prompts are numbered prompt-major."""
+        def chunk(choices: list[dict], usage: dict | None = None) -> str:
+            d = {"id": rid, "object": "text_completion", "created": _now(), "model": model_name, "choices": choices}
+            if include_usage:
+                d["usage"] = usage
+            return "data: " + json.dumps(d) + "\n\n"
+
+        q: asyncio.Queue = asyncio.Queue()
+        info: dict = {}
+
+        async def pump(pi: int, i: int):
+            try:
+                async for item in self._run_one(prompts[pi], params, adapter, i, info):
+                    await q.put((pi * params.n + i, item))
+            except BaseException as e:  # noqa: BLE001
+                await q.put(e)
+            finally:
+                await q.put((pi * params.n + i, None))
+
+        tasks = [asyncio.create_task(pump(pi, i)) for pi in range(len(prompts)) for i in range(params.n)]
+        live = len(tasks)
+        bufs: dict[int, list[int]] = {k: [] for k in range(live)}
+        sent: dict[int, int] = {k: 0 for k in range(live)}
+        completion_tokens = 0
+        try:
+            if echo:
+                for pi, p in enumerate(prompts):
+                    text, tokens, lps = await self._echo_part(p, adapter, params)
+                    for i in range(params.n):
+                        yield chunk([{"index": pi * params.n + i, "text": text, "finish_reason": None,
+                                      "logprobs": {"tokens": tokens, "token_logprobs": lps}}])
+            while live:
+                item = await q.get()
+                if isinstance(item, BaseException):
+                    raise item
+                k, ev = item
+                if ev is None:
+                    live -= 1
+                    continue
+                _, tid, lp, fin, why, top = ev
+                lpo = None
+                if tid is not None:
+                    completion_tokens += 1
+                    bufs[k].append(tid)
+                    lpo = {"tokens": [self._token_str(tid)], "token_logprobs": [lp]}
+                    if params.top_logprobs > 0:
+                        lpo["top_logprobs"] = [{self._token_str(t): l for t, l in (top or []) if t >= 0}]
+                full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[k]), skip_special_tokens=True), params)
+                upto = len(full) if fin else len(full) - self._held_back(full, params)
+                text = ""
+                if (fin or not full.endswith("\ufffd")) and upto > sent[k]:
+                    text, sent[k] = full[sent[k]:upto], upto
+                yield chunk([{"index": k, "text": text, "finish_reason": (why or "stop") if fin else None, "logprobs": lpo}])
+            if include_usage:
+                yield chunk([], self._usage(sum(len(p) for p in prompts), completion_tokens, info))
+            yield "data: [DONE]\n\n"
+        finally:
+            for t in tasks:
+                t.cancel()
 
     async def _counted(self, agen):
         """Count a locally served stream as load of this replica while it runs."""

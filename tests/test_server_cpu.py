@@ -453,3 +453,38 @@ def test_structured_outputs_constrain_the_completion(long_server):
             r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "guided_grammar": "root ::= x"})
             assert r.status_code == 400
     asyncio.run(main())
+
+
+def test_text_completions_batch_echo_and_stream(server):
+    """``/v1/completions`` with a list of prompts, ``echo`` (prompt text and prompt log-probs in front) and streaming."""
+    async def main():
+        async with client(server) as c:
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": ["ab", [104, 105, 33]], "max_tokens": 3, "n": 2,
+                                                      "temperature": 0, "logprobs": 1})
+            d = r.json()
+            assert r.status_code == 200 and [ch["index"] for ch in d["choices"]] == [0, 1, 2, 3]
+            assert d["choices"][0]["text"] == d["choices"][1]["text"] and d["usage"]["prompt_tokens"] == 5
+            assert d["usage"]["completion_tokens"] == 12 and len(d["choices"][2]["logprobs"]["top_logprobs"]) == 3
+            plain = d["choices"][2]
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": [104, 105, 33], "max_tokens": 3,
+                                                      "temperature": 0, "echo": True})
+            e = r.json()["choices"][0]
+            assert e["text"] == "hi!" + plain["text"]
+            assert e["logprobs"]["tokens"][:3] == ["token_id:104", "token_id:105", "token_id:33"]
+            lps = e["logprobs"]["token_logprobs"]
+            assert lps[0] is None and all(x <= 0 for x in lps[1:]) and len(lps) == 6
+            assert lps[3:] == pytest.approx(plain["logprobs"]["token_logprobs"], abs=1e-4)
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": ["hi!", "ab"], "max_tokens": 3, "temperature": 0,
+                                                      "stream": True, "stream_options": {"include_usage": True}})
+            chunks = [json.loads(l[6:]) for l in r.text.splitlines() if l.startswith("data: {")]
+            assert r.text.rstrip().endswith("data: [DONE]")
+            text = {0: "", 1: ""}
+            for ch in chunks:
+                for x in ch["choices"]:
+                    text[x["index"]] += x["text"]
+            assert text[0] == plain["text"] and chunks[-1]["usage"]["completion_tokens"] == 6
+            fins = [x["finish_reason"] for ch in chunks for x in ch["choices"] if x["finish_reason"]]
+            assert fins == ["length", "length"]
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": [], "max_tokens": 3})
+            assert r.status_code == 400
+    asyncio.run(main())
