@@ -186,6 +186,13 @@ class Engine:
             self.runner.set_adapter(slot, None)
             self.adapter_version[slot] += 1
 
+    def set_vocabulary(self, vocab: list[bytes], eos_token_id: int | None = None) -> None:
+        """The byte string of every token id (``grammar.vocabulary_bytes``): builds the allowed-token index that
+        ``SamplingParams.guided_regex`` needs."""
+        from .grammar import TokenMasker
+
+        self.token_masker = TokenMasker(vocab, self.eos if eos_token_id is None else eos_token_id)
+
     def _salt(self, adapter: int) -> int:
         return 0x51 if adapter < 0 else (adapter + 1) * 1_000_003 + self.adapter_version[adapter]
 

@@ -99,6 +99,9 @@ class ReplicaEngine(Engine):
         self._call_everywhere("set_adapter", name, cpu)
         return self.adapters[name]
 
+    def set_vocabulary(self, vocab, eos_token_id=None) -> None:
+        self._call_everywhere("set_vocabulary", vocab, eos_token_id)      # followers constrain the same way
+
     def remove_adapter(self, name: str) -> None:
         self._call_everywhere("remove_adapter", name)
 

@@ -342,9 +342,9 @@ class OpenAIServer:
     def _ensure_masker(self) -> None:
         """The allowed-token index of the serving tokenizer, built at the first structured-output request."""
         if self.engine.token_masker is None:
-            from .grammar import TokenMasker, vocabulary_bytes
+            from .grammar import vocabulary_bytes
 
-            self.engine.token_masker = TokenMasker(vocabulary_bytes(self.tok), self.engine.eos)
+            self.engine.set_vocabulary(vocabulary_bytes(self.tok), self.engine.eos)
 
     def _render_chat(self, body: dict) -> list[int]:
         tools = body.get("tools")

@@ -42,9 +42,18 @@ if rank == 0:
     s4 = eng.add_request([1, 2, 3, 4, 5], SamplingParams(max_tokens=6, temperature=0.0))
     assert s4.done_event.wait(60)
     assert s4.output_ids == seqs[0].output_ids   # prefix-cached, deterministic
+    # structured outputs: the vocabulary reaches every rank, which then masks the same tokens
+    from art_b200.engine.grammar import vocabulary_bytes
+    from art_b200.local.tokenizer import ByteChatTokenizer
+    tok = ByteChatTokenizer(cfg.vocab_size)
+    eng.set_vocabulary(vocabulary_bytes(tok), tok.eos_token_id)
+    s5 = eng.add_request([7, 7, 7], SamplingParams(max_tokens=20, temperature=1.0, seed=5, guided_regex="(left|right)-[0-9]{2}"))
+    assert s5.done_event.wait(60)
+    import re
+    assert re.fullmatch("(left|right)-[0-9]{2}", tok.decode(s5.output_ids)), tok.decode(s5.output_ids)
     eng.reset_prefix_cache()
     eng.shutdown()
-    out = [s.output_ids for s in seqs + [s4]]
+    out = [s.output_ids for s in seqs + [s4, s5]]
 else:
     try:
         eng.add_request([1], SamplingParams()); raise SystemExit("followers must refuse requests")
