@@ -84,7 +84,10 @@ class RecvPlan:
 
 class ExpertParallel:
     def __init__(self, device, group, max_tokens: int, k: int, num_experts: int, d_model: int,
-                 capacity_factor: float = 2.0, wait_ms: int = 4000, drop_overflow: bool = False):
+                 capacity_factor: float | None = 2.0, wait_ms: int = 4000, drop_overflow: bool = False):
+        """``capacity_factor``: rows an owner can receive per step, as a multiple of the rows one rank sends
+        (``max_tokens * k``).  ``None`` sizes the buffers for the worst case, every rank sending everything to one
+        owner (= the group size): no row can ever be dropped, at ``world / 2`` times the memory of the default."""
         self.device = torch.device(device)
         self.group = group
         self.rank = dist.get_rank(group)
@@ -96,7 +99,8 @@ class ExpertParallel:
         # drop_overflow=False that is reported as an error at the next status check; True = capacity-factor training.
         self.drop_overflow = drop_overflow
         self.cap_src_tiles = (max_tokens * k + num_experts * 127 + 127) // 128
-        recv_rows = int(capacity_factor * max_tokens * k) + self.El * 127
+        self.dropless = capacity_factor is None or capacity_factor >= self.world
+        recv_rows = int((self.world if capacity_factor is None else capacity_factor) * max_tokens * k) + self.El * 127
         self.cap_recv_tiles = (recv_rows + 127) // 128
         P, E = self.world, self.E
         off = 0

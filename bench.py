@@ -56,6 +56,9 @@ def parse_args():
                          "ep: experts sharded over GPUs (MoE presets); tp: tensor-parallel groups of --tp-size "
                          "GPUs, data parallel across the groups; pp: layers split over the GPUs, 1F1B pipeline")
     ap.add_argument("--tp-size", type=int, default=2)
+    ap.add_argument("--ep-capacity", default="2.0",
+                    help="--parallel ep: receive capacity of an expert owner as a multiple of one rank's rows; "
+                         "'dropless' sizes for the worst case (no row can be dropped; world/2 times the memory)")
     ap.add_argument("--rollout", type=int, default=1, help="also measure rollout decode tokens/s (reported beside the headline)")
     ap.add_argument("--rollout-new-tokens", type=int, default=1536,
                     help="sampled tokens per sequence in the rollout measurement (the configuration: up to 1536)")
@@ -246,7 +249,8 @@ def main():
             if not cfg.is_moe:
                 raise SystemExit("bench.py: --parallel ep needs a mixture-of-experts preset (e.g. --model qwen3-30b-a3b)")
             ep = ExpertParallel(dev, None, micro, cfg.num_experts_per_tok, cfg.num_experts, cfg.hidden_size,
-                                capacity_factor=2.0, drop_overflow=True)
+                                capacity_factor=None if args.ep_capacity == "dropless" else float(args.ep_capacity),
+                                drop_overflow=args.ep_capacity != "dropless")
             El = cfg.num_experts // world
             expert_range, sync_name = (rank * El, (rank + 1) * El), "nccl-allreduce(shared factors) + 1/world(experts)"
             # this rank keeps only its experts' frozen weights
@@ -440,7 +444,7 @@ def main():
             "config": {"model": cfg.name, "global_batch": m["global_batch"], "seq_len": S, "parallelism": m["label"],
                        "lora_rank": lcfg.r, "tokens_per_step": tokens_per_step, "micro_tokens": m["micro"],
                        "attention": attn_impl, "grad_sync": sync_name, "optimizer_steps_per_step": 1,
-                       **({"ep_capacity_factor": 2.0, "ep_dropped_row_share": ep_drop} if ep_drop is not None else {}),
+                       **({"ep_capacity_factor": args.ep_capacity, "ep_dropped_row_share": ep_drop} if ep_drop is not None else {}),
                        "l2": f"inputs larger than L2: each step streams the bf16 weights (W and W^T, "
                              f"{weight_gb:.0f} GB on this GPU for {cfg.name}) plus activations"},
             "clocks": clocks,

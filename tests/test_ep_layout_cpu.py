@@ -33,3 +33,30 @@ def test_expert_parallel_layout_never_leaves_the_receive_buffer():
                     if seg[j] < cap:
                         assert so[e] == seg[j] + int(lay["src_start"][j, s])
             assert kept == real, (P, E, cap_tiles, skew, owner, kept, real)
+
+
+def test_worst_case_capacity_drops_nothing_whatever_the_routing():
+    """``capacity_factor=None`` sizes an owner's receive buffer for every rank sending all its rows there: with that
+    many tiles the layout keeps every row even when the router puts all tokens on one expert."""
+    import torch
+
+    from art_b200.parallel.ep import reference_exchange_layout
+
+    for P, E, rows_per_rank in ((2, 8, 500), (8, 128, 1000), (4, 16, 128)):
+        El = E // P
+        cap_tiles = (P * rows_per_rank + El * 127 + 127) // 128          # what ExpertParallel allocates for None
+        for pattern in ("one-expert", "one-owner", "uneven"):
+            cnt = torch.zeros(P, E, dtype=torch.long)
+            if pattern == "one-expert":
+                cnt[:, 3] = rows_per_rank
+            elif pattern == "one-owner":
+                cnt[:, :El] = rows_per_rank // El
+                cnt[:, 0] += rows_per_rank - (rows_per_rank // El) * El
+            else:
+                g = torch.Generator().manual_seed(P)
+                w = torch.rand(P, E, generator=g) ** 8
+                cnt = (w / w.sum(1, keepdim=True) * rows_per_rank).long()
+            for owner in range(P):
+                lay = reference_exchange_layout(cnt, owner, cap_tiles)
+                want = [int(cnt[:, owner * El + j].sum()) for j in range(El)]
+                assert lay["real_rows"].tolist() == want, (P, E, pattern, owner)
