@@ -49,13 +49,17 @@ class SamplingParams:
     logit_bias: dict[int, float] | None = None
     stream_events: bool = True             # False: only the final event is delivered (see Engine.complete)
     include_stop_str_in_output: bool = False   # keep the matched stop string at the end of the returned text
+    min_tokens: int = 0                    # no end-of-sequence / stop token before this many tokens
+    allowed_token_ids: list[int] | None = None   # only these ids may be drawn
+    bad_words_ids: list[list[int]] | None = None  # token sequences that must not appear in the output
     guided_regex: str | None = None        # the completion's text has to match this expression (engine/grammar.py);
                                            # needs Engine.token_masker (the server sets it from its tokenizer)
 
     @property
     def needs_logits(self) -> bool:
         return (self.top_logprobs > 0 or self.repetition_penalty != 1.0 or self.presence_penalty != 0.0
-                or self.frequency_penalty != 0.0 or bool(self.logit_bias) or self.guided_regex is not None)
+                or self.frequency_penalty != 0.0 or bool(self.logit_bias) or self.guided_regex is not None
+                or self.min_tokens > 0 or bool(self.allowed_token_ids) or bool(self.bad_words_ids))
 
 
 @dataclass
@@ -93,7 +97,8 @@ class Sequence:
         self.forced: deque[int] = deque()     # guided decoding: tokens to emit verbatim
         self.top_logprobs: list = []          # per generated token: None or [(token, logprob)] (when requested)
         self.proc = (LogitProc(len(self.prompt_ids), params.repetition_penalty, params.presence_penalty,
-                               params.frequency_penalty, params.logit_bias, params.top_logprobs)
+                               params.frequency_penalty, params.logit_bias, params.top_logprobs,
+                               min_tokens=params.min_tokens, bad_words_ids=params.bad_words_ids)
                      if params.needs_logits else None)
         self.done_event = threading.Event()
 
@@ -282,6 +287,15 @@ class Engine:
                 raise KeyError(f"unknown adapter {adapter_name!r}")
             adapter = self.adapters[adapter_name]
         seq = Sequence(prompt_ids, params, adapter, loop)
+        if seq.proc is not None and params.min_tokens > 0:
+            seq.proc.end_ids = tuple(([self.eos] if self.eos is not None and not params.ignore_eos else [])
+                                     + list(params.stop_token_ids or []))
+        if params.allowed_token_ids:
+            if params.guided_regex is not None:
+                raise ValueError("allowed_token_ids and guided_regex exclude each other")
+            from .grammar import AllowedSet
+
+            seq.proc.grammar = AllowedSet(params.allowed_token_ids)
         if params.guided_regex is not None:
             if self.token_masker is None:
                 raise ValueError("guided_regex needs Engine.token_masker (a grammar.TokenMasker over the tokenizer's vocabulary)")

@@ -695,6 +695,27 @@ class GrammarState:
         return self.complete and not (self.dfa.trans[self.state] >= 0).any()
 
 
+class AllowedSet:
+    """A fixed set of token ids with the interface of :class:`GrammarState` (``allowed_token_ids`` of a request)."""
+
+    failed = False
+    complete = True
+    exhausted = False
+
+    def __init__(self, token_ids):
+        self.ids = sorted({int(t) for t in token_ids if int(t) >= 0})
+        if not self.ids:
+            raise ValueError("allowed_token_ids is empty")
+        self._mask = np.zeros(self.ids[-1] + 1, dtype=bool)
+        self._mask[self.ids] = True
+
+    def allowed(self) -> np.ndarray:
+        return self._mask
+
+    def advance(self, token_id: int) -> None:
+        pass
+
+
 _compiled: dict[str, ByteDFA] = {}
 
 

@@ -34,12 +34,15 @@ class LogitProc:
     frequency_penalty: float = 0.0
     logit_bias: dict | None = None
     top_logprobs: int = 0
-    grammar: object | None = None       # grammar.GrammarState: only tokens of its mask may be drawn
+    grammar: object | None = None       # grammar.GrammarState / AllowedSet: only tokens of its mask may be drawn
+    min_tokens: int = 0                 # tokens of `end_ids` are excluded while the output is shorter than this
+    end_ids: tuple = ()
+    bad_words_ids: list | None = None   # token sequences whose last token is excluded once the others have been emitted
 
     @property
     def edits(self) -> bool:
         return (self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
-                or bool(self.logit_bias))
+                or bool(self.logit_bias) or self.min_tokens > 0 or bool(self.bad_words_ids))
 
 
 def apply_token_mask(logits: torch.Tensor, grammars: list) -> torch.Tensor:

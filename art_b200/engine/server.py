@@ -264,7 +264,23 @@ class OpenAIServer:
                               seed=body.get("seed"), ignore_eos=bool(body.get("ignore_eos", False)),
                               guided_choice=body.get("guided_choice") or (body.get("structured_outputs") or {}).get("choice")
                               if not body.get("guided_regex") else None,
-                              include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)))
+                              include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)),
+                              min_tokens=max(0, min(int(body.get("min_tokens") or 0), max_tokens)),
+                              allowed_token_ids=[int(t) for t in body["allowed_token_ids"]] if body.get("allowed_token_ids") else None,
+                              bad_words_ids=self._bad_words(body.get("bad_words")))
+
+    def _bad_words(self, words) -> list[list[int]] | None:
+        """Token sequences of the request's ``bad_words``: each word as it is and with a leading space (the two are
+        different tokens in most vocabularies)."""
+        if not words:
+            return None
+        out: list[list[int]] = []
+        for w in words:
+            for text in {str(w), " " + str(w).lstrip()}:
+                ids = list(self.tok.encode(text))
+                if ids and ids not in out:
+                    out.append(ids)
+        return out or None
 
     @staticmethod
     def _forced_tool_call(body: dict) -> str | None:
@@ -354,7 +370,11 @@ class OpenAIServer:
         template = body.get("chat_template") or self.chat_template
         if template:
             kwargs["chat_template"] = template
-        ids = self.tok.apply_chat_template(body["messages"], tools=tools, add_generation_prompt=True, tokenize=True, **kwargs)
+        cont = bool(body.get("continue_final_message", False))
+        if cont:
+            kwargs["continue_final_message"] = True
+        ids = self.tok.apply_chat_template(body["messages"], tools=tools, tokenize=True,
+                                           add_generation_prompt=bool(body.get("add_generation_prompt", not cont)), **kwargs)
         if isinstance(ids, dict):
             ids = ids["input_ids"]
         return list(ids)
@@ -471,6 +491,21 @@ class OpenAIServer:
                                                 "root": srv.base_model_name,
                                                 "parent": None if n == srv.base_model_name else srv.base_model_name}
                                                for n in names]}
+
+        @app.get("/ping")
+        async def ping():
+            return await health()
+
+        @app.get("/version")
+        async def version():
+            from .. import __version__
+
+            return {"version": __version__}
+
+        @app.post("/detokenize")
+        async def detokenize(request: Request):
+            body = await request.json()
+            return {"prompt": srv.tok.decode([int(t) for t in body.get("tokens", [])])}
 
         @app.post("/tokenize")
         async def tokenize(request: Request):

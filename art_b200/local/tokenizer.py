@@ -101,8 +101,10 @@ class ByteChatTokenizer:
             text += ("\n" if text else "") + "<tool_call>\n" + json.dumps({"name": fn["name"], "arguments": json.loads(args) if args else {}}) + "\n</tool_call>"
         return text
 
-    def _segments(self, messages: list[dict], tools: list[dict] | None, add_generation_prompt: bool):
-        """Yield ``(text, is_assistant_content)`` pieces of the rendered conversation."""
+    def _segments(self, messages: list[dict], tools: list[dict] | None, add_generation_prompt: bool,
+                  continue_final_message: bool = False):
+        """Yield ``(text, is_assistant_content)`` pieces of the rendered conversation.  ``continue_final_message``
+        leaves the last message open (no end marker), so that the model goes on writing it."""
         if tools:
             sys_txt = ("# Tools\n\nYou may call one or more functions to assist with the user query.\n\n"
                        "You are provided with function signatures within <tools></tools> XML tags:\n<tools>\n"
@@ -116,8 +118,12 @@ class ByteChatTokenizer:
                 messages = [first] + list(messages[1:])
             else:
                 messages = [{"role": "system", "content": sys_txt}] + list(messages)
-        for m in messages:
+        for idx, m in enumerate(messages):
             role = m["role"]
+            if continue_final_message and idx == len(messages) - 1:
+                yield f"<|im_start|>{role}\n", False
+                yield self._render_content(m), role == "assistant"
+                return
             if role == "tool":
                 yield f"<|im_start|>user\n<tool_response>\n{self._render_content(m)}\n</tool_response><|im_end|>\n", False
                 continue
@@ -132,7 +138,8 @@ class ByteChatTokenizer:
 
     def apply_chat_template(self, messages: list[dict], tools: list[dict] | None = None, tokenize: bool = True,
                             add_generation_prompt: bool = False, return_dict: bool = False,
-                            return_assistant_tokens_mask: bool = False, chat_template: str | None = None, **kw: Any):
+                            return_assistant_tokens_mask: bool = False, chat_template: str | None = None,
+                            continue_final_message: bool = False, **kw: Any):
         """``chat_template``: a Jinja template used instead of the built-in ChatML layout (variables ``messages``,
         ``tools``, ``add_generation_prompt``, the special-token strings and any further keyword); a custom template has
         no assistant mask."""
@@ -145,7 +152,9 @@ class ByteChatTokenizer:
                 bos_token="", eos_token=self._specials[self.IM_END], **kw)
             pieces = [(text, False)]
         else:
-            pieces = list(self._segments(list(messages), tools, add_generation_prompt))
+            if continue_final_message and add_generation_prompt:
+                raise ValueError("continue_final_message and add_generation_prompt exclude each other")
+            pieces = list(self._segments(list(messages), tools, add_generation_prompt, continue_final_message))
         if not tokenize:
             return "".join(p for p, _a in pieces)
         ids: list[int] = []

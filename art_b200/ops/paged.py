@@ -237,6 +237,14 @@ def build_logit_edits(per_row: list) -> tuple[list[int], list[int], list[float],
                 edits.setdefault(t, [1.0, 1.0, 0.0])[2] += fp * c + pp
         for t, b in (a.logit_bias or {}).items():
             edits.setdefault(int(t), [1.0, 1.0, 0.0])[2] -= float(b)
+        banned: set[int] = set()
+        if getattr(a, "min_tokens", 0) > len(output_ids):
+            banned.update(int(t) for t in getattr(a, "end_ids", ()))
+        for word in getattr(a, "bad_words_ids", None) or []:
+            if word and (len(word) == 1 or (len(output_ids) >= len(word) - 1 and list(output_ids[len(output_ids) - len(word) + 1:]) == list(word[:-1]))):
+                banned.add(int(word[-1]))
+        for t in banned:
+            edits[t] = [0.0, 0.0, 1e30]          # x -> 0 * x - 1e30: out of reach of any sampler, and finite
         for t, (p_, n_, s_) in edits.items():
             rows.append(i)
             toks.append(int(t))

@@ -488,3 +488,36 @@ def test_text_completions_batch_echo_and_stream(server):
             r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": [], "max_tokens": 3})
             assert r.status_code == 400
     asyncio.run(main())
+
+
+def test_min_tokens_allowed_ids_bad_words_and_open_final_message(server):
+    tok = server.tok
+
+    async def main():
+        async with client(server) as c:
+            base = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "seed": 11}
+            # only the digits may be drawn
+            digits = [ord(ch) for ch in "0123456789"]
+            d = (await c.post("/v1/chat/completions", json={**base, "max_tokens": 12, "allowed_token_ids": digits})).json()
+            assert re.fullmatch(r"[0-9]{12}", d["choices"][0]["message"]["content"])
+            # ... digits and the end marker, which min_tokens keeps away for the first 8 tokens
+            d = (await c.post("/v1/chat/completions", json={**base, "max_tokens": 30, "min_tokens": 8, "logit_bias": {str(tok.eos_token_id): 100},
+                                                            "allowed_token_ids": digits + [tok.eos_token_id]})).json()
+            ch = d["choices"][0]
+            assert ch["finish_reason"] == "stop" and len(ch["logprobs"]["content"]) == 9 and re.fullmatch(r"[0-9]{8}", ch["message"]["content"])
+            # bad words: "1" never appears, "23" never appears as a pair although 2 and 3 do
+            d = (await c.post("/v1/chat/completions", json={**base, "max_tokens": 200, "allowed_token_ids": [ord(x) for x in "1234"],
+                                                            "bad_words": ["1", "23"]})).json()
+            text = d["choices"][0]["message"]["content"]
+            assert len(text) == 200 and "1" not in text and "23" not in text and "2" in text and "3" in text and "4" in text
+            # the last message stays open and is continued
+            msgs = [{"role": "user", "content": "count"}, {"role": "assistant", "content": "1, 2, "}]
+            r = await c.post("/tokenize", json={"messages": msgs, "continue_final_message": True})
+            assert tok.decode(r.json()["tokens"]).endswith("<|im_start|>assistant\n1, 2, ")
+            r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": msgs, "continue_final_message": True, "max_tokens": 3})
+            assert r.status_code == 200
+            ids = (await c.post("/tokenize", json={"prompt": "héllo"})).json()["tokens"]
+            assert (await c.post("/detokenize", json={"tokens": ids})).json() == {"prompt": "héllo"}
+            assert (await c.get("/version")).json()["version"] and (await c.get("/ping")).status_code == 200
+    import re
+    asyncio.run(main())
