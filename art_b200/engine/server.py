@@ -529,6 +529,7 @@ class OpenAIServer:
                 raise HTTPException(status_code=400, detail=f"prompt has {len(prompt_ids)} tokens; the maximum context "
                                                             f"length is {srv.engine.max_model_len}")
             params = srv._params(body, len(prompt_ids))
+            want_prompt_lps = bool(body.get("prompt_logprobs")) and not body.get("stream")
             forced = srv._forced_tool_call(body)
             if forced is not None:
                 params.guided_choice = [forced]       # the call is teacher-forced and comes back with its log-probs
@@ -548,7 +549,8 @@ class OpenAIServer:
                                          media_type="text/event-stream")
             srv._load[0] += 1
             try:
-                return JSONResponse(await srv._chat_full(request, rid, model_name, prompt_ids, params, adapter, tools_on))
+                return JSONResponse(await srv._chat_full(request, rid, model_name, prompt_ids, params, adapter, tools_on,
+                                                         want_prompt_lps))
             finally:
                 srv._load[0] -= 1
 
@@ -814,7 +816,8 @@ class OpenAIServer:
                 reason = "tool_calls"
         return msg, reason
 
-    async def _chat_full(self, request, rid, model_name, prompt_ids, params, adapter, tools_on) -> dict:
+    async def _chat_full(self, request, rid, model_name, prompt_ids, params, adapter, tools_on,
+                         prompt_logprobs: bool = False) -> dict:
         info: dict = {}
         out = await self._collect(request, prompt_ids, params, adapter, info)
         choices = []
@@ -823,8 +826,18 @@ class OpenAIServer:
             choices.append({"index": i, "message": msg, "finish_reason": reason,
                             "logprobs": {"content": [self._logprob_entry(t, lp, top) for t, lp, top in zip(ids, lps, tops)]}})
         comp = sum(len(o[0]) for o in out)
-        return {"id": rid, "object": "chat.completion", "created": _now(), "model": model_name, "choices": choices,
+        resp = {"id": rid, "object": "chat.completion", "created": _now(), "model": model_name, "choices": choices,
                 "usage": self._usage(len(prompt_ids), comp, info)}
+        if prompt_logprobs:
+            resp["prompt_logprobs"] = await self._prompt_logprobs(prompt_ids, adapter)
+        return resp
+
+    async def _prompt_logprobs(self, prompt_ids: list[int], adapter) -> list:
+        """Log-probability of every prompt token given the ones before it (None for the first), in the shape the
+        reference's engine returns for ``prompt_logprobs``: one ``{token_id: {"logprob", "decoded_token"}}`` per token."""
+        _, _, lps = await self._echo_part(prompt_ids, adapter, None)
+        return [None if lp is None else {str(t): {"logprob": lp, "decoded_token": self.tok.decode([t])}}
+                for t, lp in zip(prompt_ids, lps)]
 
     # -- streaming --------------------------------------------------------------------------------------
     async def _chat_stream(self, request, rid, model_name, prompt_ids, params, adapter, tools_on, include_usage

@@ -521,3 +521,18 @@ def test_min_tokens_allowed_ids_bad_words_and_open_final_message(server):
             assert (await c.get("/version")).json()["version"] and (await c.get("/ping")).status_code == 200
     import re
     asyncio.run(main())
+
+
+def test_prompt_logprobs_come_back_with_the_completion(server):
+    async def main():
+        async with client(server) as c:
+            body = {"model": "agent-001", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "prompt_logprobs": 1}
+            d = (await c.post("/v1/chat/completions", json=body)).json()
+            n = d["usage"]["prompt_tokens"]
+            plp = d["prompt_logprobs"]
+            assert len(plp) == n and plp[0] is None
+            ids = (await c.post("/tokenize", json={"messages": body["messages"]})).json()["tokens"]
+            for t, e in zip(ids[1:], plp[1:]):
+                (k, v), = e.items()
+                assert int(k) == t and v["logprob"] <= 0 and isinstance(v["decoded_token"], str)
+    asyncio.run(main())
