@@ -621,6 +621,7 @@ class TokenMasker:
                 m[self.eos] = bool(dfa.accepting[state])
             if len(self._cache) > 4096:
                 self._cache.clear()
+                self._dfa_refs = {id(dfa): dfa}      # automata are pinned only while masks of theirs are cached
             self._cache[key] = m
         return m
 
