@@ -727,3 +727,57 @@ def compile_cached(pattern: str) -> ByteDFA:
             _compiled.clear()
         dfa = _compiled[pattern] = compile_regex(pattern)
     return dfa
+
+
+def _bench(n_tokens: int = 151_936, seed: int = 0) -> dict:
+    """Host-side cost of structured outputs on a synthetic vocabulary of the size of Qwen2.5's: automaton build, trie
+    build, and allowed-token masks per automaton state (native walk and its Python twin)."""
+    import random
+    import string
+    import time
+
+    rng = random.Random(seed)
+    vocab = [bytes([i]) for i in range(256)]
+    chars = string.ascii_letters + string.digits + ' {}[]":,.-_\n'
+    while len(vocab) < n_tokens - 1:
+        vocab.append("".join(rng.choice(chars) for _ in range(rng.randint(2, 9))).encode())
+    vocab.append(b"")
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                                               "tags": {"type": "array", "items": {"type": "string"}, "maxItems": 4},
+                                               "kind": {"enum": ["a", "b", "c"]}}, "required": ["name", "age"]}
+    t0 = time.perf_counter()
+    dfa = compile_regex(schema_to_regex(schema))
+    t_dfa = time.perf_counter() - t0
+    from ..ops import _lib
+
+    _lib.runtime()                       # load the library (and what it imports) outside the timed part
+    t0 = time.perf_counter()
+    native = TokenMasker(vocab, len(vocab) - 1)
+    t_trie = time.perf_counter() - t0
+    if native._native is None:
+        raise SystemExit("the runtime library is not built: python -m art_b200.build")
+    plain = TokenMasker(vocab, len(vocab) - 1, use_native=False)
+    plain._py_trie()
+    states = list(range(dfa.n_states))
+    t0 = time.perf_counter()
+    counts = [int(native.mask(dfa, s).sum()) for s in states]
+    t_native = time.perf_counter() - t0
+    widest = max(states, key=lambda s: counts[s])
+    native._cache.clear()
+    t0 = time.perf_counter()
+    native.mask(dfa, widest)
+    t_widest = time.perf_counter() - t0
+    sample = states[:: max(1, len(states) // 12)]
+    t0 = time.perf_counter()
+    for s in sample:
+        assert int(plain.mask(dfa, s).sum()) == counts[s]
+    t_py = time.perf_counter() - t0
+    return {"op": "token_mask", "vocabulary": len(vocab), "automaton_states": dfa.n_states,
+            "automaton_build_ms": round(t_dfa * 1e3, 1), "trie_build_ms": round(t_trie * 1e3, 1),
+            "native_ms_per_state": round(t_native / len(states) * 1e3, 3),
+            "native_ms_widest_state": round(t_widest * 1e3, 3), "python_ms_per_state": round(t_py / len(sample) * 1e3, 1),
+            "allowed_tokens_min_max": [min(counts), max(counts)]}
+
+
+if __name__ == "__main__":
+    print(json.dumps(_bench()))
