@@ -350,6 +350,8 @@ class OpenAIServer:
             if body.get("guided_grammar") or so.get("grammar"):
                 raise HTTPException(status_code=400, detail="context-free grammars are not supported; use a JSON schema or a regular expression")
             if rx is not None:
+                if len(rx) > 200_000:
+                    raise ValueError(f"the constraint expands to an expression of {len(rx)} characters (limit 200 000)")
                 compile_cached(rx)             # syntax and size errors surface here, as a 400
         except (RegexError, ValueError, KeyError, TypeError) as e:
             raise HTTPException(status_code=400, detail=f"cannot build the structured-output constraint: {e}") from e
