@@ -269,3 +269,36 @@ def get_model_config(base_model: str, output_dir: str, config: InternalModelConf
     trainer_args.update(config.get("trainer_args", {}))
     return InternalModelConfig(init_args=init_args, engine_args=engine_args, peft_args=peft_args,
                                trainer_args=trainer_args)
+
+
+_PEFT_WITHOUT_EFFECT = {"lora_dropout": (0, 0.0, None), "bias": ("none", None), "layers_to_transform": (None,),
+                        "layers_pattern": (None,), "modules_to_save": (None, []), "loftq_config": (None, {}),
+                        "init_lora_weights": (True, None)}
+_warned: set[str] = set()
+
+
+def warn_ignored(config: InternalModelConfig) -> list[str]:
+    """Names (and logs once each) the settings of ``config`` that ask for something this trainer does not do:
+    adapter options other than plain LoRA / rsLoRA on the listed target modules, quantised loading, full fine-tuning.
+    Returns the messages."""
+    import logging
+
+    msgs = []
+    for key, neutral in _PEFT_WITHOUT_EFFECT.items():
+        val = config.get("peft_args", {}).get(key, neutral[0])
+        if val not in neutral:
+            msgs.append(f"peft_args[{key!r}]={val!r} has no effect: adapters are plain LoRA on the target modules of every layer")
+    init = config.get("init_args", {})
+    if init.get("full_finetuning"):
+        msgs.append("init_args['full_finetuning'] has no effect: only LoRA adapters are trained")
+    if init.get("load_in_8bit"):
+        msgs.append("init_args['load_in_8bit'] has no effect: base weights are bf16")
+    unknown = [m for m in config.get("peft_args", {}).get("target_modules", []) if m not in DEFAULT_TARGET_MODULES]
+    if unknown:
+        msgs.append(f"peft_args['target_modules'] names {unknown}, which are not adapted (supported: {DEFAULT_TARGET_MODULES})")
+    log = logging.getLogger(__name__)
+    for m in msgs:
+        if m not in _warned:
+            _warned.add(m)
+            log.warning(m)
+    return msgs

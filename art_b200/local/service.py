@@ -83,6 +83,7 @@ class ModelState:
         targs = config.get("trainer_args", {})
         if rank == 0:
             dev.engine.split_engine_args(dict(engine_args))     # names, once each, the keys that have no effect here
+            dev.model.warn_ignored(config)
         self.rank, self.world, self.tp_size = rank, world, tp
         self.data_index, self.data_ranks = 0, 1
         if world > 1 and rank > 0 and not torch.cuda.is_initialized():

@@ -104,3 +104,17 @@ def test_repo_root_and_last_checkpoint_dir(tmp_path):
     for name in ("0000", "0003", "0010", "logs", "0011.tmp"):
         (out / name).mkdir(parents=True)
     assert os.path.basename(get_last_checkpoint_dir(str(out))) == "0010"
+
+
+def test_settings_without_effect_are_named(caplog):
+    import logging
+
+    from art_b200 import dev
+
+    with caplog.at_level(logging.WARNING):
+        msgs = dev.model.warn_ignored({"peft_args": {"lora_dropout": 0.1, "bias": "none", "target_modules": ["q_proj", "embed_tokens"]},
+                                       "init_args": {"full_finetuning": True}})
+    assert len(msgs) == 3 and any("lora_dropout" in m for m in msgs) and any("embed_tokens" in m for m in msgs)
+    assert dev.model.warn_ignored(dev.model.get_model_config("x", "/nonexistent/dir", None)) == []      # the defaults are clean
+    used, ignored = dev.engine.split_engine_args({"max_model_len": 512, "ray_workers_use_nsight": True})
+    assert used == {"max_model_len": 512} and ignored == {"ray_workers_use_nsight": True}
