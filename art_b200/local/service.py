@@ -60,6 +60,12 @@ def node_layout(config: dev.InternalModelConfig) -> tuple[int, int]:
     (src/art/dev/engine.py:27); here it also sets the trainer's tensor-parallel group size, and
     ``engine_args.data_parallel_size`` the number of such groups.  The service then runs one rank per GPU."""
     ea = config.get("engine_args", {}) or {}
+    ta = config.get("trainer_args", {}) or {}
+    for key in ("pipeline_parallel_size", "context_parallel_size", "expert_parallel_size"):
+        if int(ea.get(key) or ta.get(key) or 1) > 1:
+            raise ValueError(f"{key} > 1: the model service lays a model out as tensor parallel x data parallel; context, "
+                             f"expert and pipeline parallel training are reached through trainer.Trainer(cp_group= / ep= / "
+                             f"pp_group=) (see bench.py --parallel cp|ep|pp), not through LocalBackend yet")
     return max(1, int(ea.get("tensor_parallel_size") or 1)), max(1, int(ea.get("data_parallel_size") or 1))
 
 

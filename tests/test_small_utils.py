@@ -118,3 +118,13 @@ def test_settings_without_effect_are_named(caplog):
     assert dev.model.warn_ignored(dev.model.get_model_config("x", "/nonexistent/dir", None)) == []      # the defaults are clean
     used, ignored = dev.engine.split_engine_args({"max_model_len": 512, "ray_workers_use_nsight": True})
     assert used == {"max_model_len": 512} and ignored == {"ray_workers_use_nsight": True}
+
+
+def test_model_service_refuses_layouts_it_does_not_run():
+    from art_b200.local.service import node_layout
+
+    assert node_layout({"engine_args": {"tensor_parallel_size": 2, "data_parallel_size": 4}}) == (2, 4)
+    assert node_layout({}) == (1, 1)
+    for key in ("pipeline_parallel_size", "context_parallel_size", "expert_parallel_size"):
+        with pytest.raises(ValueError, match=key):
+            node_layout({"engine_args": {key: 2}})
