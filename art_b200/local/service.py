@@ -61,12 +61,23 @@ def node_layout(config: dev.InternalModelConfig) -> tuple[int, int]:
     ``engine_args.data_parallel_size`` the number of such groups.  The service then runs one rank per GPU."""
     ea = config.get("engine_args", {}) or {}
     ta = config.get("trainer_args", {}) or {}
-    for key in ("pipeline_parallel_size", "context_parallel_size", "expert_parallel_size"):
+    for key in ("pipeline_parallel_size", "expert_parallel_size"):
         if int(ea.get(key) or ta.get(key) or 1) > 1:
-            raise ValueError(f"{key} > 1: the model service lays a model out as tensor parallel x data parallel; context, "
-                             f"expert and pipeline parallel training are reached through trainer.Trainer(cp_group= / ep= / "
-                             f"pp_group=) (see bench.py --parallel cp|ep|pp), not through LocalBackend yet")
-    return max(1, int(ea.get("tensor_parallel_size") or 1)), max(1, int(ea.get("data_parallel_size") or 1))
+            raise ValueError(f"{key} > 1: the model service lays a model out as (tensor or context parallel) x data "
+                             f"parallel; expert and pipeline parallel training are reached through "
+                             f"trainer.Trainer(ep= / pp_group=) (see bench.py --parallel ep|pp), not through LocalBackend yet")
+    tp = max(1, int(ea.get("tensor_parallel_size") or 1))
+    cp = context_parallel_size(config)
+    if tp > 1 and cp > 1:
+        raise ValueError("tensor_parallel_size and context_parallel_size cannot both exceed 1 (the two do not compose yet)")
+    return max(tp, cp), max(1, int(ea.get("data_parallel_size") or 1))
+
+
+def context_parallel_size(config: dev.InternalModelConfig) -> int:
+    """``context_parallel_size`` of the engine or trainer arguments: groups of that many adjacent GPUs split every
+    packed row between them (zig-zag shards) instead of splitting heads and FFN columns."""
+    ea, ta = config.get("engine_args", {}) or {}, config.get("trainer_args", {}) or {}
+    return max(1, int(ea.get("context_parallel_size") or ta.get("context_parallel_size") or 1))
 
 
 class ModelState:
@@ -90,7 +101,8 @@ class ModelState:
         if rank == 0:
             dev.engine.split_engine_args(dict(engine_args))     # names, once each, the keys that have no effect here
             dev.model.warn_ignored(config)
-        self.rank, self.world, self.tp_size = rank, world, tp
+        self.rank, self.world, self.tp_size = rank, world, tp       # tp_size: ranks that share rows (TP or CP group)
+        self.group_kind = "cp" if context_parallel_size(config) > 1 else "tp"
         self.data_index, self.data_ranks = 0, 1
         if world > 1 and rank > 0 and not torch.cuda.is_initialized():
             # a worker rank lives in a process of its own: list its GPU first, so that it is device 0 for every thread of
@@ -121,6 +133,9 @@ class ModelState:
             groups = layout.create_groups(rank)
             tp_group, dp_group = groups["tp"], groups["dp"]
             self.data_index, self.data_ranks = layout.data_shard(rank)
+        cp_group = None
+        if self.group_kind == "cp":      # the same groups of adjacent ranks, used to split rows instead of heads
+            tp_group, cp_group = None, tp_group
         self.cfg = resolve_config(base_model, init_args.get("architecture"))
         self.lora_cfg = LoraConfig(r=int(peft_args.get("r", 8)), alpha=float(peft_args.get("lora_alpha", 16)),
                                    target_modules=tuple(peft_args.get("target_modules", LoraConfig().target_modules)),
@@ -155,14 +170,14 @@ class ModelState:
 
                 grad_sync = nccl_grad_sync(self.data_ranks, dp_group)      # CPU ranks: the library all-reduce on gloo
         if tp > 1 and not has_gpu:
-            raise ValueError("tensor-parallel training needs GPUs (the CPU path is data parallel only)")
+            raise ValueError("tensor- and context-parallel training need GPUs (the CPU path is data parallel only)")
         self.tp_tokens = int(targs.get("tokens_per_microbatch") or 8192 * tp)
         self.trainer = Trainer(self.cfg, base, self.lora_cfg, lora, device=self.device,
                                betas=(float(targs.get("adam_beta1", 0.9)), float(targs.get("adam_beta2", 0.99))),
                                weight_decay=float(targs.get("weight_decay", 0.1)),
                                max_grad_norm=float(targs.get("max_grad_norm", 0.1)),
                                adam_eps=float(targs.get("adam_epsilon", 1e-8)), grad_sync=grad_sync, dp_group=dp_group,
-                               tp_group=tp_group, tp_tokens=self.tp_tokens)
+                               tp_group=tp_group, tp_tokens=self.tp_tokens, cp_group=cp_group)
         if last and os.path.exists(os.path.join(last, TRAINER_STATE)):
             self.trainer.load_trainer_state(torch.load(os.path.join(last, TRAINER_STATE), map_location="cpu"))
         # rollout engine: one replica per rank
@@ -186,7 +201,7 @@ class ModelState:
             except RuntimeError:   # no VMM support: plain tensors; Engine.sleep() then drops the captured graphs
                 self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim,
                                   self.device)
-            if tp > 1:      # the trainer's weights are sharded: the replica keeps its own full copy
+            if tp_group is not None:      # the trainer's weights are sharded: the replica keeps its own full copy
                 runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, base=base, max_loras=max_loras, device=self.device)
             else:           # trainer and engine share the frozen weights
                 runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
@@ -361,7 +376,7 @@ class ModelService:
                 slept = True
             n_rows = packed["tokens"].shape[0]
             per = max(1, hyper.rows_per_optimizer_step)
-            if st.tp_size > 1:      # a tensor-parallel micro-batch has a fixed token count: whole micro-batches per step
+            if st.tp_size > 1 and st.group_kind == "tp":      # a tensor-parallel micro-batch has a fixed token count: whole micro-batches per step
                 S_row = packed["tokens"].shape[1]
                 rows_mb = max(1, st.tp_tokens // S_row)
                 per = (per + rows_mb - 1) // rows_mb * rows_mb

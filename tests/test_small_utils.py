@@ -125,6 +125,10 @@ def test_model_service_refuses_layouts_it_does_not_run():
 
     assert node_layout({"engine_args": {"tensor_parallel_size": 2, "data_parallel_size": 4}}) == (2, 4)
     assert node_layout({}) == (1, 1)
-    for key in ("pipeline_parallel_size", "context_parallel_size", "expert_parallel_size"):
+    assert node_layout({"engine_args": {"context_parallel_size": 4, "data_parallel_size": 2}}) == (4, 2)
+    assert node_layout({"trainer_args": {"context_parallel_size": 2}}) == (2, 1)
+    with pytest.raises(ValueError, match="do not compose"):
+        node_layout({"engine_args": {"context_parallel_size": 2, "tensor_parallel_size": 2}})
+    for key in ("pipeline_parallel_size", "expert_parallel_size"):
         with pytest.raises(ValueError, match=key):
             node_layout({"engine_args": {key: 2}})
