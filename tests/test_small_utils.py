@@ -132,3 +132,42 @@ def test_model_service_refuses_layouts_it_does_not_run():
     for key in ("pipeline_parallel_size", "expert_parallel_size"):
         with pytest.raises(ValueError, match=key):
             node_layout({"engine_args": {key: 2}})
+
+
+def test_metrics_go_to_history_and_to_wandb_when_a_key_is_set(tmp_path, monkeypatch):
+    """``history.jsonl`` is always written; with ``WANDB_API_KEY`` the same numbers go to a run named after the model
+    (a fake ``wandb`` module stands in: there is no network here)."""
+    import json
+    import sys
+    import types
+
+    from art_b200.local import LocalBackend
+
+    calls = {"init": [], "log": []}
+    fake = types.ModuleType("wandb")
+
+    class Run:
+        _is_finished = False
+
+        def log(self, metrics, step=None):
+            calls["log"].append((dict(metrics), step))
+
+    def init(**kw):
+        calls["init"].append(kw)
+        return Run()
+
+    fake.init = init
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.setitem(sys.modules, "weave", None)          # "not installed": tracing is optional
+    model = art.Model(name="prompted", project="proj")
+    backend = LocalBackend(in_process=True, path=str(tmp_path))
+    monkeypatch.delenv("WANDB_API_KEY", raising=False)
+    backend._log_metrics(model, {"reward": 0.25}, "val")
+    assert calls["init"] == []
+    monkeypatch.setenv("WANDB_API_KEY", "k")
+    backend._log_metrics(model, {"reward": 0.5, "exception_rate": 0.0}, "val")
+    backend._log_metrics(model, {"reward": 0.75}, "val")
+    assert calls["init"] == [{"project": "proj", "name": "prompted", "id": "prompted", "resume": "allow"}]       # one run, reused
+    assert calls["log"] == [({"val/reward": 0.5, "val/exception_rate": 0.0}, 0), ({"val/reward": 0.75}, 0)]
+    rows = [json.loads(l) for l in open(tmp_path / "proj" / "models" / "prompted" / "history.jsonl")]
+    assert [r["val/reward"] for r in rows] == [0.25, 0.5, 0.75] and all("recorded_at" in r for r in rows)
