@@ -179,6 +179,8 @@ class _Parser:
             return "negmask", _CLASS_ESC[c.lower()]
         if c in _CHAR_ESC:
             return "char", _CHAR_ESC[c]
+        if c in "bBAZzGpPkK" or (c.isdigit() and c != "0"):
+            raise RegexError(f"\\{c} (boundaries, back-references, Unicode properties) is not supported")
         if c in "xu":
             n = 2 if c == "x" else 4
             hexs = self.s[self.i:self.i + n]

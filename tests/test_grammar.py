@@ -36,7 +36,7 @@ def test_automaton_works_on_utf8_bytes():
     assert neg.matches("añb") and not neg.matches('a"b')
 
 
-@pytest.mark.parametrize("bad", ["(unclosed", "a{3,2}", "*a", "[abc", "(?=x)y", "a{2000}", "\\"])
+@pytest.mark.parametrize("bad", ["(unclosed", "a{3,2}", "*a", "[abc", "(?=x)y", "a{2000}", "\\", r"\bword\b", r"(a)\1"])
 def test_bad_expressions_are_reported(bad):
     with pytest.raises(RegexError):
         compile_regex(bad)
