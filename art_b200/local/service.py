@@ -61,23 +61,27 @@ def node_layout(config: dev.InternalModelConfig) -> tuple[int, int]:
     ``engine_args.data_parallel_size`` the number of such groups.  The service then runs one rank per GPU."""
     ea = config.get("engine_args", {}) or {}
     ta = config.get("trainer_args", {}) or {}
-    for key in ("pipeline_parallel_size", "expert_parallel_size"):
-        if int(ea.get(key) or ta.get(key) or 1) > 1:
-            raise ValueError(f"{key} > 1: the model service lays a model out as (tensor or context parallel) x data "
-                             f"parallel; expert and pipeline parallel training are reached through "
-                             f"trainer.Trainer(ep= / pp_group=) (see bench.py --parallel ep|pp), not through LocalBackend yet")
-    tp = max(1, int(ea.get("tensor_parallel_size") or 1))
-    cp = context_parallel_size(config)
-    if tp > 1 and cp > 1:
-        raise ValueError("tensor_parallel_size and context_parallel_size cannot both exceed 1 (the two do not compose yet)")
-    return max(tp, cp), max(1, int(ea.get("data_parallel_size") or 1))
+    if int(ea.get("expert_parallel_size") or ta.get("expert_parallel_size") or 1) > 1:
+        raise ValueError("expert_parallel_size > 1: the model service lays a model out as (tensor, context or pipeline "
+                         "parallel) x data parallel; expert parallel training is reached through trainer.Trainer(ep=) "
+                         "(see bench.py --parallel ep), not through LocalBackend yet")
+    kind, size = group_layout(config)
+    return size, max(1, int(ea.get("data_parallel_size") or 1))
 
 
-def context_parallel_size(config: dev.InternalModelConfig) -> int:
-    """``context_parallel_size`` of the engine or trainer arguments: groups of that many adjacent GPUs split every
-    packed row between them (zig-zag shards) instead of splitting heads and FFN columns."""
+def group_layout(config: dev.InternalModelConfig) -> tuple[str, int]:
+    """What the groups of adjacent GPUs of a model split, and how many GPUs a group has: ``("tp", n)`` heads and FFN
+    columns (``tensor_parallel_size``), ``("cp", n)`` the tokens of every packed row (``context_parallel_size``), or
+    ``("pp", n)`` the layers (``pipeline_parallel_size``).  The sizes are read from the engine arguments, then the
+    trainer arguments; at most one of them may exceed 1 (the three do not compose inside the service)."""
     ea, ta = config.get("engine_args", {}) or {}, config.get("trainer_args", {}) or {}
-    return max(1, int(ea.get("context_parallel_size") or ta.get("context_parallel_size") or 1))
+    sizes = {kind: max(1, int(ea.get(key) or ta.get(key) or 1))
+             for kind, key in (("tp", "tensor_parallel_size"), ("cp", "context_parallel_size"), ("pp", "pipeline_parallel_size"))}
+    big = [k for k, v in sizes.items() if v > 1]
+    if len(big) > 1:
+        raise ValueError(f"tensor, context and pipeline parallel sizes do not compose in the model service yet: "
+                         f"{ {k: sizes[k] for k in big} }")
+    return (big[0], sizes[big[0]]) if big else ("tp", 1)
 
 
 class ModelState:
@@ -102,7 +106,7 @@ class ModelState:
             dev.engine.split_engine_args(dict(engine_args))     # names, once each, the keys that have no effect here
             dev.model.warn_ignored(config)
         self.rank, self.world, self.tp_size = rank, world, tp       # tp_size: ranks that share rows (TP or CP group)
-        self.group_kind = "cp" if context_parallel_size(config) > 1 else "tp"
+        self.group_kind = group_layout(config)[0]
         self.data_index, self.data_ranks = 0, 1
         if world > 1 and rank > 0 and not torch.cuda.is_initialized():
             # a worker rank lives in a process of its own: list its GPU first, so that it is device 0 for every thread of
@@ -133,9 +137,11 @@ class ModelState:
             groups = layout.create_groups(rank)
             tp_group, dp_group = groups["tp"], groups["dp"]
             self.data_index, self.data_ranks = layout.data_shard(rank)
-        cp_group = None
+        cp_group = pp_group = None
         if self.group_kind == "cp":      # the same groups of adjacent ranks, used to split rows instead of heads
             tp_group, cp_group = None, tp_group
+        elif self.group_kind == "pp":    # ... or to hold consecutive blocks of layers
+            tp_group, pp_group = None, tp_group
         self.cfg = resolve_config(base_model, init_args.get("architecture"))
         self.lora_cfg = LoraConfig(r=int(peft_args.get("r", 8)), alpha=float(peft_args.get("lora_alpha", 16)),
                                    target_modules=tuple(peft_args.get("target_modules", LoraConfig().target_modules)),
@@ -177,7 +183,7 @@ class ModelState:
                                weight_decay=float(targs.get("weight_decay", 0.1)),
                                max_grad_norm=float(targs.get("max_grad_norm", 0.1)),
                                adam_eps=float(targs.get("adam_epsilon", 1e-8)), grad_sync=grad_sync, dp_group=dp_group,
-                               tp_group=tp_group, tp_tokens=self.tp_tokens, cp_group=cp_group)
+                               tp_group=tp_group, tp_tokens=self.tp_tokens, cp_group=cp_group, pp_group=pp_group)
         if last and os.path.exists(os.path.join(last, TRAINER_STATE)):
             self.trainer.load_trainer_state(torch.load(os.path.join(last, TRAINER_STATE), map_location="cpu"))
         # rollout engine: one replica per rank
@@ -201,7 +207,7 @@ class ModelState:
             except RuntimeError:   # no VMM support: plain tensors; Engine.sleep() then drops the captured graphs
                 self.kv = KVCache(self.cfg.num_layers, num_blocks, block_size, self.cfg.num_kv_heads, self.cfg.head_dim,
                                   self.device)
-            if tp_group is not None:      # the trainer's weights are sharded: the replica keeps its own full copy
+            if tp_group is not None or pp_group is not None:      # the trainer holds a part of the weights: the replica keeps its own full copy
                 runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, base=base, max_loras=max_loras, device=self.device)
             else:           # trainer and engine share the frozen weights
                 runner = NativeRunner(self.cfg, self.lora_cfg, self.kv, decoder=self.trainer.model, max_loras=max_loras,
@@ -381,6 +387,10 @@ class ModelService:
                 rows_mb = max(1, st.tp_tokens // S_row)
                 per = (per + rows_mb - 1) // rows_mb * rows_mb
                 hyper.rows_per_optimizer_step, hyper.tokens_per_microbatch = per, rows_mb * S_row
+            elif st.tp_size > 1 and st.group_kind == "pp":    # pipeline micro-batches all have the same number of rows
+                rows_mb = max(1, min(per, hyper.tokens_per_microbatch // packed["tokens"].shape[1]))
+                per = (per + rows_mb - 1) // rows_mb * rows_mb
+                hyper.rows_per_optimizer_step = per
             D, j = st.data_ranks, st.data_index
             t0 = time.monotonic()
             tokens_done = 0

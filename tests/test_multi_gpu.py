@@ -818,7 +818,7 @@ from test_node_service_cpu import _packed
 ARCH = dict(name="small", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
             intermediate_size=512)
 out_root, tp, dp = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
-kind = sys.argv[4] if len(sys.argv) > 4 else "tp"       # "cp": the groups of `tp` ranks split rows instead of heads
+kind = sys.argv[4] if len(sys.argv) > 4 else "tp"       # "cp" / "pp": the groups of `tp` ranks split rows / layers instead of heads
 
 
 async def main():
@@ -829,7 +829,7 @@ async def main():
     cfg = dev.get_model_config("random:small", out, {
         "init_args": {"architecture": ARCH, "max_seq_length": 2048},
         "engine_args": {"num_scheduler_steps": 4, "max_model_len": 512, "data_parallel_size": dp, "num_gpu_blocks_override": 512,
-                        ("context_parallel_size" if kind == "cp" else "tensor_parallel_size"): tp},
+                        {"cp": "context_parallel_size", "pp": "pipeline_parallel_size"}.get(kind, "tensor_parallel_size"): tp},
         "trainer_args": {"tokens_per_microbatch": 2048}})
     port = 18800 + (os.getpid() % 40) * 8
     svc = build_node_service(model_name="m", base_model="random:small", config=cfg, output_dir=out, port=port, in_process=True)
@@ -861,12 +861,13 @@ if __name__ == "__main__":       # the rank-1 service is a spawned child that im
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("tp,dp,kind", [(1, 2, "tp"), (2, 1, "tp"), (2, 1, "cp")])
+@pytest.mark.parametrize("tp,dp,kind", [(1, 2, "tp"), (2, 1, "tp"), (2, 1, "cp"), (2, 1, "pp")])
 def test_node_service_over_two_gpus(tmp_path, tp, dp, kind):
     """The model service over two GPUs through its public entry point: one engine replica per GPU behind one port,
-    a training call that runs data parallel (tp=1, dp=2), tensor parallel (tp=2) or context parallel (kind "cp": the
-    same group of two ranks splits every row) across the ranks, the adapter handed to every replica on its own device.
-    (The context-parallel case was added without a 2-GPU machine at hand.)"""
+    a training call that runs data parallel (tp=1, dp=2), tensor parallel (tp=2), context parallel (kind "cp": the
+    same group of two ranks splits every row) or pipeline parallel (kind "pp": it splits the layers) across the ranks,
+    the adapter handed to every replica on its own device.  (The context- and pipeline-parallel cases were added
+    without a 2-GPU machine at hand.)"""
     script = tmp_path / "node_worker.py"
     script.write_text(NODE_WORKER)
     env = dict(os.environ, ARTB_ROOT=ROOT, NCCL_NVLS_ENABLE="0", ART_B200_DIST_TIMEOUT_S="60")

@@ -127,11 +127,13 @@ def test_model_service_refuses_layouts_it_does_not_run():
     assert node_layout({}) == (1, 1)
     assert node_layout({"engine_args": {"context_parallel_size": 4, "data_parallel_size": 2}}) == (4, 2)
     assert node_layout({"trainer_args": {"context_parallel_size": 2}}) == (2, 1)
+    assert node_layout({"engine_args": {"pipeline_parallel_size": 2}}) == (2, 1)
+    from art_b200.local.service import group_layout
+    assert group_layout({"engine_args": {"pipeline_parallel_size": 4}}) == ("pp", 4) and group_layout({}) == ("tp", 1)
     with pytest.raises(ValueError, match="do not compose"):
         node_layout({"engine_args": {"context_parallel_size": 2, "tensor_parallel_size": 2}})
-    for key in ("pipeline_parallel_size", "expert_parallel_size"):
-        with pytest.raises(ValueError, match=key):
-            node_layout({"engine_args": {key: 2}})
+    with pytest.raises(ValueError, match="expert_parallel_size"):
+        node_layout({"engine_args": {"expert_parallel_size": 2}})
 
 
 def test_metrics_go_to_history_and_to_wandb_when_a_key_is_set(tmp_path, monkeypatch):
