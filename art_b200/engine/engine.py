@@ -308,22 +308,38 @@ class Engine:
         seq.aborted = True
         self._wake.set()
 
-    async def generate(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None
-                       ) -> AsyncIterator[TokenEvent]:
-        """Async stream of sampled tokens for one request; cancelling the consumer aborts the request."""
+    async def generate_steps(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None
+                             ) -> AsyncIterator[list[TokenEvent]]:
+        """Async stream of one request's sampled tokens, grouped as the scheduler produced them: one list per scheduler
+        step (up to ``num_scheduler_steps`` tokens).  Cancelling the consumer aborts the request."""
         seq = self.add_request(prompt_ids, params, adapter_name, asyncio.get_running_loop())
         try:
             while True:
                 item = await seq.queue.get()
                 if isinstance(item, BaseException):
                     raise item
-                for ev in (item if isinstance(item, list) else (item,)):     # one list per scheduler step
-                    yield ev
+                events = item if isinstance(item, list) else [item]
+                for k, ev in enumerate(events):
                     if ev.finished:
-                        return
+                        events = events[:k + 1]
+                        break
+                yield events
+                if events and events[-1].finished:
+                    return
         finally:
             if not seq.finished:
                 self.abort(seq)
+
+    async def generate(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None
+                       ) -> AsyncIterator[TokenEvent]:
+        """Async stream of sampled tokens for one request; cancelling the consumer aborts the request."""
+        agen = self.generate_steps(prompt_ids, params, adapter_name)
+        try:
+            async for events in agen:
+                for ev in events:
+                    yield ev
+        finally:
+            await agen.aclose()
 
     async def complete(self, prompt_ids: list[int], params: SamplingParams, adapter_name: str | None = None) -> Sequence:
         """Runs one request to its end and returns its sequence (``output_ids``, ``logprobs``, ``top_logprobs``,

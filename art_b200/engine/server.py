@@ -87,6 +87,39 @@ def _without_partial(text: str, tag: str) -> str:
     return text
 
 
+class IncrementalDecoder:
+    """Text of a growing token sequence without decoding it from the start at every token: only a short window of
+    recent tokens is decoded (the part already turned into text, to have its length, and the same plus what is new),
+    and nothing is emitted while the window ends in half a character.  Cost per token is constant; decoding the whole
+    completion at every token made a streamed 1000-token answer cost 500 000 token decodes."""
+
+    def __init__(self, tok, skip_special_tokens: bool = True):
+        self.tok, self.skip = tok, skip_special_tokens
+        self.ids: list[int] = []
+        self.prefix = self.read = 0
+        self.text = ""
+
+    def push(self, tid: int) -> str:
+        """Adds a token; returns the text it completed ("" while a character is still open)."""
+        self.ids.append(tid)
+        old = self.tok.decode(self.ids[self.prefix:self.read], skip_special_tokens=self.skip) if self.read > self.prefix else ""
+        new = self.tok.decode(self.ids[self.prefix:], skip_special_tokens=self.skip)
+        if len(new) > len(old) and not new.endswith("\ufffd"):
+            delta = new[len(old):]
+            self.prefix, self.read = self.read, len(self.ids)
+            self.text += delta
+            return delta
+        return ""
+
+    def final(self) -> str:
+        """The whole text, including a trailing piece that never became a full character."""
+        if self.read == len(self.ids):
+            return self.text
+        old = self.tok.decode(self.ids[self.prefix:self.read], skip_special_tokens=self.skip) if self.read > self.prefix else ""
+        new = self.tok.decode(self.ids[self.prefix:], skip_special_tokens=self.skip)
+        return self.text + new[len(old):]
+
+
 class OpenAIServer:
     def __init__(self, engine: Engine, tokenizer, base_model_name: str, *, api_key: str | None = "default",
                  return_tokens_as_token_ids: bool = True, enable_auto_tool_choice: bool = True,
@@ -134,6 +167,7 @@ class OpenAIServer:
         if reasoning_parser and self.reasoning is None:
             raise ValueError(f"unknown reasoning parser {reasoning_parser!r}; known: {sorted(_REASONING_TAGS)}")
         self.load_tracking = load_tracking
+        self._tok_fields: dict[int, tuple[str, list[int]]] = {}
         self.app = self._build()
 
     @classmethod
@@ -224,13 +258,26 @@ class OpenAIServer:
         return JSONResponse(resp.json(), status_code=resp.status_code)
 
     def _token_str(self, tid: int) -> str:
-        return f"token_id:{tid}" if self.token_ids_as_strings else self.tok.decode([tid])
+        return self._token_fields(tid)[0]
+
+    def _token_fields(self, tid: int) -> tuple[str, list[int]]:
+        """The ``token`` string and the ``bytes`` list of a token id, computed once per id: detokenising one token costs
+        microseconds with a byte-level tokenizer and tens of them with a BPE vocabulary, per token and request."""
+        hit = self._tok_fields.get(tid)
+        if hit is None:
+            text = self.tok.decode([tid])
+            hit = self._tok_fields[tid] = (f"token_id:{tid}" if self.token_ids_as_strings else text,
+                                           list(text.encode("utf-8")))
+        return hit
 
     def _logprob_entry(self, tid: int, lp: float, top=None) -> dict:
-        text = self.tok.decode([tid])
-        alts = [{"token": self._token_str(t), "logprob": l, "bytes": list(self.tok.decode([t]).encode("utf-8"))}
-                for t, l in (top or []) if t >= 0]
-        return {"token": self._token_str(tid), "logprob": lp, "bytes": list(text.encode("utf-8")), "top_logprobs": alts}
+        token, raw = self._token_fields(tid)
+        alts = []
+        for t, l in (top or ()):
+            if t >= 0:
+                tt, tb = self._token_fields(t)
+                alts.append({"token": tt, "logprob": l, "bytes": tb})
+        return {"token": token, "logprob": lp, "bytes": raw, "top_logprobs": alts}
 
     def _params(self, body: dict, prompt_len: int) -> SamplingParams:
         max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
@@ -381,34 +428,53 @@ class OpenAIServer:
             ids = ids["input_ids"]
         return list(ids)
 
-    async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int,
-                       info: dict | None = None):
-        """Async iterator over (index, token_id, logprob, finished, finish_reason, top_logprobs) for one choice.
+    async def _run_steps(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int,
+                         info: dict | None = None):
+        """Async iterator over lists of (index, token_id, logprob, finished, finish_reason, top_logprobs) for one choice:
+        one list per scheduler step, which is what a stream sends as one chunk.
         ``info["cached_tokens"]`` collects the prompt tokens that came out of the prefix cache."""
         if params.guided_choice:
             async for item in self._run_guided(prompt_ids, params, adapter, index):
-                yield item
+                yield [item]
             return
         seq_params = SamplingParams(**{**params.__dict__, "n": 1,
                                        "seed": None if params.seed is None else params.seed + index})
         stops = params.stop or []
-        ids: list[int] = []
-        agen = self.engine.generate(prompt_ids, seq_params, adapter)
+        dec = IncrementalDecoder(self.tok) if stops else None
+        longest = max((len(x) for x in stops), default=0)
+        agen = self.engine.generate_steps(prompt_ids, seq_params, adapter)
         try:
-            async for ev in agen:
-                if info is not None and getattr(ev, "cached_tokens", None):
-                    info["cached_tokens"] = max(info.get("cached_tokens", 0), ev.cached_tokens)
-                yield index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason, ev.top_logprobs
-                if stops and not ev.finished:
-                    # the same decoding as the text that is returned (token-by-token decoding differs from it as soon
-                    # as a character spans two tokens), so the cut in _cut_at_stop finds what was matched here
-                    ids.append(ev.token_id)
-                    text = self.tok.decode(ids, skip_special_tokens=True)
-                    if any(s in text for s in stops):
-                        yield index, None, None, True, "stop", None
-                        return
-                if ev.finished:
+            async for events in agen:
+                out = []
+                for ev in events:
+                    if info is not None and getattr(ev, "cached_tokens", None):
+                        info["cached_tokens"] = max(info.get("cached_tokens", 0), ev.cached_tokens)
+                    out.append((index, ev.token_id, ev.logprob, ev.finished, ev.finish_reason, ev.top_logprobs))
+                    if stops and not ev.finished:
+                        # windowed decoding (whole characters only, like the text that is returned); only the end of
+                        # the text can hold a new match
+                        delta = dec.push(ev.token_id)
+                        tail = dec.text[-(longest + len(delta)):] if delta else ""
+                        if delta and any(s in tail for s in stops):
+                            out.append((index, None, None, True, "stop", None))
+                            yield out
+                            return
+                    if ev.finished:
+                        break
+                yield out
+                if out and out[-1][3]:
                     return
+        finally:
+            await agen.aclose()
+
+    async def _run_one(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int,
+                       info: dict | None = None):
+        """:meth:`_run_steps`, one token at a time."""
+        agen = self._run_steps(prompt_ids, params, adapter, index, info)
+        try:
+            async for items in agen:
+                for item in items:
+                    yield item
         finally:
             await agen.aclose()
 
@@ -637,8 +703,8 @@ class OpenAIServer:
 
     async def _completion_stream(self, rid, model_name, prompts, params, adapter, echo: bool, include_usage: bool
                                  ) -> AsyncIterator[str]:
-        """Event stream of ``/v1/completions``: one chunk per token and choice with the new text, the token and its
-        log-prob; choices of several prompts are numbered prompt-major."""
+        """Event stream of ``/v1/completions``: one chunk per scheduler step and choice with the new text, the tokens and
+        their log-probs; choices of several prompts are numbered prompt-major."""
         def chunk(choices: list[dict], usage: dict | None = None) -> str:
             d = {"id": rid, "object": "text_completion", "created": _now(), "model": model_name, "choices": choices}
             if include_usage:
@@ -650,8 +716,8 @@ class OpenAIServer:
 
         async def pump(pi: int, i: int):
             try:
-                async for item in self._run_one(prompts[pi], params, adapter, i, info):
-                    await q.put((pi * params.n + i, item))
+                async for items in self._run_steps(prompts[pi], params, adapter, i, info):
+                    await q.put((pi * params.n + i, items))
             except BaseException as e:  # noqa: BLE001
                 await q.put(e)
             finally:
@@ -660,6 +726,7 @@ class OpenAIServer:
         tasks = [asyncio.create_task(pump(pi, i)) for pi in range(len(prompts)) for i in range(params.n)]
         live = len(tasks)
         bufs: dict[int, list[int]] = {k: [] for k in range(live)}
+        decs = {k: IncrementalDecoder(self.tok) for k in range(live)}
         sent: dict[int, int] = {k: 0 for k in range(live)}
         completion_tokens = 0
         try:
@@ -673,22 +740,30 @@ class OpenAIServer:
                 item = await q.get()
                 if isinstance(item, BaseException):
                     raise item
-                k, ev = item
-                if ev is None:
+                k, events = item
+                if events is None:
                     live -= 1
                     continue
-                _, tid, lp, fin, why, top = ev
                 lpo = None
-                if tid is not None:
-                    completion_tokens += 1
-                    bufs[k].append(tid)
-                    lpo = {"tokens": [self._token_str(tid)], "token_logprobs": [lp]}
-                    if params.top_logprobs > 0:
-                        lpo["top_logprobs"] = [{self._token_str(t): l for t, l in (top or []) if t >= 0}]
-                full = self._cut_at_stop(self.tok.decode(self._strip_eos(bufs[k]), skip_special_tokens=True), params)
+                fin, why = False, None
+                for _, tid, lp, fin, why, top in events:
+                    if tid is not None:
+                        completion_tokens += 1
+                        bufs[k].append(tid)
+                        if tid != self.engine.eos:
+                            decs[k].push(tid)
+                        if lpo is None:
+                            lpo = {"tokens": [], "token_logprobs": []}
+                            if params.top_logprobs > 0:
+                                lpo["top_logprobs"] = []
+                        lpo["tokens"].append(self._token_str(tid))
+                        lpo["token_logprobs"].append(lp)
+                        if params.top_logprobs > 0:
+                            lpo["top_logprobs"].append({self._token_str(t): l for t, l in (top or []) if t >= 0})
+                full = self._cut_at_stop(decs[k].final() if fin else decs[k].text, params)
                 upto = len(full) if fin else len(full) - self._held_back(full, params)
                 text = ""
-                if (fin or not full.endswith("\ufffd")) and upto > sent[k]:
+                if upto > sent[k]:
                     text, sent[k] = full[sent[k]:upto], upto
                 yield chunk([{"index": k, "text": text, "finish_reason": (why or "stop") if fin else None, "logprobs": lpo}])
             if include_usage:
@@ -855,19 +930,17 @@ class OpenAIServer:
 
         async def pump(i: int):
             try:
-                async for item in self._run_one(prompt_ids, params, adapter, i, info):
-                    await q.put(item)
+                async for items in self._run_steps(prompt_ids, params, adapter, i, info):
+                    await q.put(items)         # the tokens of one scheduler step: one chunk of the stream
             except BaseException as e:  # noqa: BLE001
                 await q.put(e)
             finally:
                 await q.put((i, "done"))
 
-        def visible(ids: list[int], done: bool) -> tuple[str, str]:
-            """(reasoning, content) of a choice so far that may be sent: without a possible beginning of a stop
-            string or of a reasoning tag at the end, which wait for the next token."""
-            full = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=True), params)
-            if not done and full.endswith("\ufffd"):        # half a character: wait
-                return "", ""
+        def visible(dec: IncrementalDecoder, done: bool) -> tuple[str, str]:
+            """(reasoning, content) of a choice so far that may be sent: whole characters only, and without a possible
+            beginning of a stop string or of a reasoning tag at the end, which wait for the next token."""
+            full = self._cut_at_stop(dec.final() if done else dec.text, params)
             if self.reasoning is None:
                 return "", full if done else full[:len(full) - self._held_back(full, params)]
             r, c = split_reasoning(full, self.reasoning, done)
@@ -881,6 +954,7 @@ class OpenAIServer:
         live = params.n
         completion_tokens = 0
         bufs: dict[int, list[int]] = {i: [] for i in range(params.n)}
+        decs = {i: IncrementalDecoder(self.tok) for i in range(params.n)}
         sent_text: dict[int, int] = {i: 0 for i in range(params.n)}
         sent_reason: dict[int, int] = {i: 0 for i in range(params.n)}
         try:
@@ -890,18 +964,25 @@ class OpenAIServer:
                 item = await q.get()
                 if isinstance(item, BaseException):
                     raise item
-                if len(item) == 2:
+                if isinstance(item, tuple):
                     live -= 1
                     continue
-                i, tid, lp, fin, why, top = item
+                if not item:
+                    continue
+                i = item[0][0]
                 delta: dict[str, Any] = {}
-                lps = None
-                if tid is not None:
-                    completion_tokens += 1
-                    bufs[i].append(tid)
-                    lps = {"content": [self._logprob_entry(tid, lp, top)]}
-                if not tools_on and (tid is not None or fin):
-                    r, c = visible(bufs[i], bool(fin))
+                entries = []
+                fin, why = False, None
+                for _, tid, lp, fin, why, top in item:
+                    if tid is not None:
+                        completion_tokens += 1
+                        bufs[i].append(tid)
+                        if tid != self.engine.eos:
+                            decs[i].push(tid)
+                        entries.append(self._logprob_entry(tid, lp, top))
+                lps = {"content": entries} if entries else None
+                if not tools_on and (entries or fin):
+                    r, c = visible(decs[i], bool(fin))
                     if len(r) > sent_reason[i]:
                         delta["reasoning_content"] = r[sent_reason[i]:]
                         sent_reason[i] = len(r)

@@ -536,3 +536,31 @@ def test_prompt_logprobs_come_back_with_the_completion(server):
                 (k, v), = e.items()
                 assert int(k) == t and v["logprob"] <= 0 and isinstance(v["decoded_token"], str)
     asyncio.run(main())
+
+
+def test_incremental_decoder_equals_a_full_decode_and_waits_for_whole_characters():
+    import random
+
+    from art_b200.engine.server import IncrementalDecoder
+
+    tok = ByteChatTokenizer(512)
+    text = "héllo wörld 日本語 ✓ done"
+    ids = tok.encode(text)
+    dec = IncrementalDecoder(tok)
+    pieces = [dec.push(t) for t in ids]
+    assert "".join(pieces) == text == dec.text == dec.final()
+    assert "" in pieces and all("�" not in p for p in pieces)         # bytes inside a character emit nothing yet
+    # a completion cut in the middle of a character: final() still returns what a full decode returns
+    cut = ids[: ids.index("日".encode()[0]) + 2]
+    dec = IncrementalDecoder(tok)
+    for t in cut:
+        dec.push(t)
+    assert dec.final() == tok.decode(cut, skip_special_tokens=True) and dec.text == "héllo wörld "
+    # random byte soup, specials included
+    rng = random.Random(0)
+    for _ in range(50):
+        ids = [rng.choice([rng.randrange(32, 127), rng.randrange(0xC3, 0xC5), rng.randrange(0x80, 0xC0), 256, 257]) for _ in range(40)]
+        dec = IncrementalDecoder(tok)
+        for t in ids:
+            dec.push(t)
+        assert dec.final() == tok.decode(ids, skip_special_tokens=True)
