@@ -75,10 +75,11 @@ class EngineArgs(TypedDict, total=False):
     speculative_model: str | None
     num_speculative_tokens: int | None
     preemption_mode: str | None
-    multi_step_stream_outputs: bool
     worker_cls: str
     calculate_kv_scales: bool | None
     additional_config: dict[str, Any] | None
+    # native: True = one stream chunk per token; False (default here) = one chunk per scheduler step
+    multi_step_stream_outputs: bool
     # native: the number of KV-cache blocks, instead of sizing the cache from gpu_memory_utilization
     num_gpu_blocks_override: int | None
     allowed_local_media_path: Any
@@ -135,6 +136,7 @@ NATIVE_ENGINE_KEYS = frozenset({
     "enable_prefix_caching", "enable_chunked_prefill", "num_scheduler_steps", "enforce_eager",
     "enable_sleep_mode", "enable_lora", "max_loras", "max_lora_rank", "max_logprobs",
     "disable_log_stats", "disable_log_requests", "generation_config", "num_gpu_blocks_override",
+    "multi_step_stream_outputs",
 })
 
 _warned: set[str] = set()

@@ -128,7 +128,7 @@ class OpenAIServer:
                  cors: dict | None = None, middleware: list[str] | None = None, request_id_headers: bool = False,
                  fastapi_docs: bool = False, max_log_len: int | None = None, log_requests: bool = False,
                  prompt_tokens_details: bool = False, reasoning_parser: str | None = None,
-                 load_tracking: bool = False):
+                 load_tracking: bool = False, stream_per_token: bool = False):
         """``peers``: base URLs of further replicas of the same model (other GPUs of the node).  This server then
         spreads ``/v1/chat/completions`` and ``/v1/completions`` over itself and the peers, least loaded first,
         passing a peer's answer (JSON or event stream) through unchanged; a client only ever sees this one URL.
@@ -141,7 +141,9 @@ class OpenAIServer:
         ``request_id_headers`` (``X-Request-Id`` on every response), ``fastapi_docs``, ``log_requests`` with
         ``max_log_len`` (prompt characters / ids printed per request), ``prompt_tokens_details`` (prefix-cache hits
         in ``usage``), ``reasoning_parser`` (text between ``<think>`` and ``</think>`` is returned as
-        ``reasoning_content``), ``load_tracking`` (``GET /load``)."""
+        ``reasoning_content``), ``load_tracking`` (``GET /load``).  ``stream_per_token``: one stream chunk per token instead of
+        one per scheduler step (``engine_args.multi_step_stream_outputs`` of the reference's engine; four times the host
+        cost per streamed token)."""
         self.engine, self.tok = engine, tokenizer
         self.peers = list(peers or [])
         self._load = [0] * (1 + len(self.peers))       # requests in flight: [this replica, peer 0, peer 1, ...]
@@ -167,12 +169,14 @@ class OpenAIServer:
         if reasoning_parser and self.reasoning is None:
             raise ValueError(f"unknown reasoning parser {reasoning_parser!r}; known: {sorted(_REASONING_TAGS)}")
         self.load_tracking = load_tracking
+        self.stream_per_token = stream_per_token
         self._tok_fields: dict[int, tuple[str, list[int]]] = {}
         self.app = self._build()
 
     @classmethod
     def from_server_args(cls, engine: Engine, tokenizer, base_model_name: str, sargs: dict, *,
-                         log_requests: bool = False, peers: list[str] | None = None) -> "OpenAIServer":
+                         log_requests: bool = False, peers: list[str] | None = None,
+                         stream_per_token: bool = False) -> "OpenAIServer":
         """Builds the server from a ``ServerArgs`` dictionary (the keys that concern the HTTP listener itself, host,
         port, TLS files and log level, are read by :func:`serve_kwargs`)."""
         def jlist(key: str):
@@ -197,7 +201,7 @@ class OpenAIServer:
                    max_log_len=sargs.get("max_log_len"), log_requests=log_requests,
                    prompt_tokens_details=bool(sargs.get("enable_prompt_tokens_details", False)),
                    reasoning_parser=(sargs.get("reasoning_parser") or "deepseek_r1") if sargs.get("enable_reasoning") else None,
-                   load_tracking=bool(sargs.get("enable_server_load_tracking", False)))
+                   load_tracking=bool(sargs.get("enable_server_load_tracking", False)), stream_per_token=stream_per_token)
 
     # -- helpers ------------------------------------------------------------------------------------
     def _auth(self, request: Request) -> None:
@@ -717,7 +721,8 @@ class OpenAIServer:
         async def pump(pi: int, i: int):
             try:
                 async for items in self._run_steps(prompts[pi], params, adapter, i, info):
-                    await q.put((pi * params.n + i, items))
+                    for part in ([[it] for it in items] if self.stream_per_token else [items]):
+                        await q.put((pi * params.n + i, part))
             except BaseException as e:  # noqa: BLE001
                 await q.put(e)
             finally:
@@ -931,7 +936,11 @@ class OpenAIServer:
         async def pump(i: int):
             try:
                 async for items in self._run_steps(prompt_ids, params, adapter, i, info):
-                    await q.put(items)         # the tokens of one scheduler step: one chunk of the stream
+                    if self.stream_per_token:
+                        for it in items:
+                            await q.put([it])
+                    else:
+                        await q.put(items)     # the tokens of one scheduler step: one chunk of the stream
             except BaseException as e:  # noqa: BLE001
                 await q.put(e)
             finally:

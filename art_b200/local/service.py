@@ -317,7 +317,8 @@ class ModelService:
         peers = [f"http://127.0.0.1:{port0 + r}" for r in range(1, self.world)] if self.rank == 0 else []
         eargs = cfg.get("engine_args", {})
         server = OpenAIServer.from_server_args(st.engine, st.tokenizer, self.base_model, sargs, peers=peers,
-                                               log_requests=eargs.get("disable_log_requests") is False)
+                                               log_requests=eargs.get("disable_log_requests") is False,
+                                               stream_per_token=bool(eargs.get("multi_step_stream_outputs", False)))
         self._server = server
         await self.stop_openai_server()
         ready = asyncio.Event()

@@ -564,3 +564,30 @@ def test_incremental_decoder_equals_a_full_decode_and_waits_for_whole_characters
         for t in ids:
             dec.push(t)
         assert dec.final() == tok.decode(ids, skip_special_tokens=True)
+
+
+def test_stream_chunks_carry_a_scheduler_step_each_or_one_token_on_request(server):
+    """The fixture's engine takes two decode steps per scheduler iteration: a stream then has two tokens per chunk;
+    ``stream_per_token`` restores one chunk per token.  Both fold back into the same completion."""
+    from art_b200.openai import consume_chat_completion_stream
+    from openai.types.chat.chat_completion_chunk import ChatCompletionChunk
+
+    per_token = OpenAIServer(server.engine, server.tok, "tiny-base", stream_per_token=True)
+    body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 8, "stream": True,
+            "temperature": 0, "ignore_eos": True}
+
+    async def run(srv):
+        async with client(srv) as c:
+            r = await c.post("/v1/chat/completions", json=body)
+            chunks = [ChatCompletionChunk.model_validate_json(l[6:]) for l in r.text.splitlines() if l.startswith("data: {")]
+            sizes = [len(ch.choices[0].logprobs.content) for ch in chunks if ch.choices and ch.choices[0].logprobs]
+
+            async def replay():
+                for ch in chunks:
+                    yield ch
+            return sizes, await consume_chat_completion_stream(replay())
+
+    (a_sizes, a), (b_sizes, b) = asyncio.run(run(server)), asyncio.run(run(per_token))
+    assert sum(a_sizes) == sum(b_sizes) == 8 and max(a_sizes) == 2 and b_sizes == [1] * 8
+    assert a.choices[0].message.content == b.choices[0].message.content
+    assert [t.token for t in a.choices[0].logprobs.content] == [t.token for t in b.choices[0].logprobs.content]
