@@ -101,7 +101,11 @@ class IncrementalDecoder:
 
     def push(self, tid: int) -> str:
         """Adds a token; returns the text it completed ("" while a character is still open)."""
-        self.ids.append(tid)
+        return self.extend((tid,))
+
+    def extend(self, tids) -> str:
+        """Adds the tokens of one step with one pass over the window."""
+        self.ids.extend(tids)
         old = self.tok.decode(self.ids[self.prefix:self.read], skip_special_tokens=self.skip) if self.read > self.prefix else ""
         new = self.tok.decode(self.ids[self.prefix:], skip_special_tokens=self.skip)
         if len(new) > len(old) and not new.endswith("\ufffd"):
@@ -755,8 +759,6 @@ class OpenAIServer:
                     if tid is not None:
                         completion_tokens += 1
                         bufs[k].append(tid)
-                        if tid != self.engine.eos:
-                            decs[k].push(tid)
                         if lpo is None:
                             lpo = {"tokens": [], "token_logprobs": []}
                             if params.top_logprobs > 0:
@@ -765,6 +767,8 @@ class OpenAIServer:
                         lpo["token_logprobs"].append(lp)
                         if params.top_logprobs > 0:
                             lpo["top_logprobs"].append({self._token_str(t): l for t, l in (top or []) if t >= 0})
+                if lpo is not None:
+                    decs[k].extend([t[1] for t in events if t[1] is not None and t[1] != self.engine.eos])
                 full = self._cut_at_stop(decs[k].final() if fin else decs[k].text, params)
                 upto = len(full) if fin else len(full) - self._held_back(full, params)
                 text = ""
@@ -986,9 +990,9 @@ class OpenAIServer:
                     if tid is not None:
                         completion_tokens += 1
                         bufs[i].append(tid)
-                        if tid != self.engine.eos:
-                            decs[i].push(tid)
                         entries.append(self._logprob_entry(tid, lp, top))
+                if entries:
+                    decs[i].extend([t[1] for t in item if t[1] is not None and t[1] != self.engine.eos])
                 lps = {"content": entries} if entries else None
                 if not tools_on and (entries or fin):
                     r, c = visible(decs[i], bool(fin))
