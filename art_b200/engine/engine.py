@@ -62,7 +62,7 @@ class SamplingParams:
                 or self.min_tokens > 0 or bool(self.allowed_token_ids) or bool(self.bad_words_ids))
 
 
-@dataclass
+@dataclass(slots=True)
 class TokenEvent:
     token_id: int
     logprob: float

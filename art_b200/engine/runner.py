@@ -64,7 +64,7 @@ def apply_token_mask(logits: torch.Tensor, grammars: list) -> torch.Tensor:
     return logits
 
 
-@dataclass
+@dataclass(slots=True)
 class SeqView:
     """What a runner needs to know about one scheduled sequence."""
     tokens: list[int]          # prompt + generated so far
