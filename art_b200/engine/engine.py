@@ -151,6 +151,7 @@ class Engine:
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self._outbox: dict = {}     # event loop -> {queue: [TokenEvent, ...]} of the scheduler step in progress
+        self._inflight: list = []   # sequences handed to the runner for prefill (in no queue meanwhile)
         self.token_masker = None    # grammar.TokenMasker of the serving tokenizer: enables SamplingParams.guided_regex
         self.max_recoveries = 3     # automatic restarts of the stepping thread after an error (see recover())
         self.recoveries = 0
@@ -279,6 +280,8 @@ class Engine:
                 self.recover()
             else:
                 raise RuntimeError("engine stopped after an error") from self.error
+        if not prompt_ids or not all(isinstance(t, int) for t in prompt_ids):
+            raise ValueError("a prompt is a non-empty list of token ids")
         if len(prompt_ids) + 1 > self.max_model_len:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_model_len}")
         adapter = -1
@@ -565,7 +568,9 @@ class Engine:
                 v.upto = upto
                 views.append(v)
             t0 = time.monotonic()
+            self._inflight = [s for s, _ in work]       # out of the queues while the runner works: told if it fails
             toks, lps = self.runner.prefill(views)
+            self._inflight = []
             self.stats.runner_s += time.monotonic() - t0
             tops = getattr(self.runner, "last_top_logprobs", None)
             for i, (s, upto) in enumerate(work):
@@ -649,6 +654,8 @@ class Engine:
             self.error = e
             with self._lock:
                 seqs = list(self.waiting) + self.running + self.prefilling
+            seqs += [s for s in self._inflight if s not in seqs]
+            self._inflight = []
             for s in seqs:
                 if s.loop is not None:
                     try:

@@ -25,6 +25,7 @@ import os
 import json
 import time
 import uuid
+from collections.abc import Mapping
 from typing import Any, AsyncIterator
 
 from fastapi import FastAPI, HTTPException, Request
@@ -432,9 +433,9 @@ class OpenAIServer:
             kwargs["continue_final_message"] = True
         ids = self.tok.apply_chat_template(body["messages"], tools=tools, tokenize=True,
                                            add_generation_prompt=bool(body.get("add_generation_prompt", not cont)), **kwargs)
-        if isinstance(ids, dict):
+        if isinstance(ids, Mapping):       # newer tokenizer libraries return the dictionary form by default
             ids = ids["input_ids"]
-        return list(ids)
+        return [int(t) for t in ids]
 
     async def _run_steps(self, prompt_ids: list[int], params: SamplingParams, adapter: str | None, index: int,
                          info: dict | None = None):

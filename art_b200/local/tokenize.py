@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import math
 import random
+from collections.abc import Mapping
 from dataclasses import dataclass, replace
 from typing import Any, Iterator
 
@@ -109,7 +110,7 @@ def tokenize_trajectory(tokenizer, trajectory: Trajectory, advantage: float,
     tools = trajectory.tools
     chat = tokenizer.apply_chat_template(messages, tools=tools, tokenize=False)
     original_ids = tokenizer.apply_chat_template(messages, tools=tools)
-    if isinstance(original_ids, dict):
+    if isinstance(original_ids, Mapping):      # newer tokenizer libraries return the dictionary form by default
         original_ids = original_ids["input_ids"]
     used = set(original_ids)
     sentinel_id = next(i for i in range(int(tokenizer.vocab_size) - 1, -1, -1) if i not in used)

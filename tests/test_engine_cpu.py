@@ -359,3 +359,29 @@ def test_engine_logs_throughput_lines_unless_switched_off(tiny, caplog):
         assert lines and "KV cache usage" in lines[0] and "prefix cache hit rate" in lines[0]
     finally:
         eng.shutdown()
+
+
+def test_a_failing_prefill_reaches_the_request_that_was_being_prefilled(tiny):
+    """A sequence is in no queue while the runner prefills it; if the runner raises there, the request must still be
+    told (it used to wait for ever)."""
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=1)
+    eng.start()
+
+    def broken(views):
+        raise RuntimeError("injected prefill failure")
+
+    real = eng.runner.prefill
+    eng.runner.prefill = broken
+    try:
+        async def main():
+            with pytest.raises(RuntimeError, match="injected prefill"):
+                await asyncio.wait_for(eng.complete([1, 2, 3], SamplingParams(max_tokens=4)), timeout=20)
+        asyncio.run(main())
+        with pytest.raises(ValueError, match="token ids"):
+            eng.add_request(["input_ids", "attention_mask"], SamplingParams())
+        eng.runner.prefill = real
+        seq = eng.generate_sync([1, 2, 3], SamplingParams(max_tokens=4, temperature=0.0))       # recovers
+        assert len(seq.output_ids) == 4
+    finally:
+        eng.shutdown()
