@@ -333,7 +333,7 @@ class OpenAIServer:
         out: list[list[int]] = []
         for w in words:
             for text in {str(w), " " + str(w).lstrip()}:
-                ids = list(self.tok.encode(text))
+                ids = list(self.tok.encode(text, add_special_tokens=False))
                 if ids and ids not in out:
                     out.append(ids)
         return out or None
@@ -495,7 +495,7 @@ class OpenAIServer:
         import random
 
         eos = [self.engine.eos] if self.engine.eos is not None else []
-        cands = [self.tok.encode(c) + eos for c in params.guided_choice]
+        cands = [list(self.tok.encode(c, add_special_tokens=False)) + eos for c in params.guided_choice]   # no BOS inside a completion
         scores = [await self.engine.score(prompt_ids, c, adapter) for c in cands]
         totals = [sum(s) for s in scores]
         if params.temperature <= 0 or len(cands) == 1:

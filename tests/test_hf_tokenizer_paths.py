@@ -136,3 +136,42 @@ def test_training_tokenisation_splices_sampled_ids_with_a_bpe_tokenizer(bpe):
     assert sum(a.assistant_mask) == len(ids_a) and a.assistant_mask[n:n + len(ids_a)] == [1] * len(ids_a)
     assert a.logprobs[n] == -0.5 and math.isnan(a.logprobs[0])
     assert bpe.decode(a.token_ids).startswith("<|user|>who are you?<|end|><|assistant|>the quick brown fox")
+
+
+def test_candidates_and_bad_words_are_encoded_without_special_tokens(bpe):
+    """A tokenizer whose ``encode`` puts a beginning-of-text token in front (Llama style): the candidates of
+    ``guided_choice`` and the ``bad_words`` of a request sit inside a completion and must not get one."""
+    from tokenizers import processors
+
+    from art_b200.engine.engine import Engine
+    from art_b200.engine.kv_cache import BlockManager
+    from art_b200.engine.runner import ReferenceRunner
+    from art_b200.engine.server import OpenAIServer
+    from art_b200.models.config import PRESETS
+    from art_b200.models.weights import LoraConfig, init_base_weights
+
+    bos = bpe.convert_tokens_to_ids("<|user|>")
+    old = bpe.backend_tokenizer.post_processor
+    bpe.backend_tokenizer.post_processor = processors.TemplateProcessing(single="<|user|> $A", special_tokens=[("<|user|>", bos)])
+    try:
+        assert bpe.encode("yes")[0] == bos and bpe.encode("yes", add_special_tokens=False)[0] != bos
+        cfg = PRESETS["tiny"]
+        eng = Engine(ReferenceRunner(cfg, init_base_weights(cfg, seed=0), LoraConfig(), max_loras=2), BlockManager(256, 4, True),
+                     eos_token_id=bpe.eos_token_id, max_loras=2, num_scheduler_steps=2, max_model_len=512)
+        eng.start()
+        srv = OpenAIServer(eng, bpe, "tiny-base", api_key=None)
+        assert all(bos not in w for w in srv._bad_words(["fox"]))
+
+        async def main():
+            async with httpx.AsyncClient(transport=httpx.ASGITransport(app=srv.app), base_url="http://t") as c:
+                r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": [{"role": "user", "content": "ok?"}],
+                                                               "guided_choice": ["yes", "no"]})
+                ch = r.json()["choices"][0]
+                toks = [int(e["token"].split(":")[1]) for e in ch["logprobs"]["content"]]
+                assert ch["message"]["content"] in ("yes", "no") and bos not in toks
+        try:
+            asyncio.run(main())
+        finally:
+            eng.shutdown()
+    finally:
+        bpe.backend_tokenizer.post_processor = old
