@@ -175,3 +175,62 @@ def test_candidates_and_bad_words_are_encoded_without_special_tokens(bpe):
             eng.shutdown()
     finally:
         bpe.backend_tokenizer.post_processor = old
+
+
+def test_full_loop_from_a_checkpoint_directory_in_hugging_face_layout(bpe, tmp_path):
+    """``base_model`` as a local directory: ``config.json``, tokenizer files and ``model.safetensors`` with the usual
+    parameter names are read, rollouts go through the tokenizer's own chat template, a training step produces a PEFT
+    adapter.  (CPU: the oracle model and runner; what is under test is the loading and the tokenizer path.)"""
+    import os
+
+    from safetensors.torch import save_file
+
+    import art_b200 as art
+    from art_b200.local import LocalBackend
+    from art_b200.models.config import ModelConfig
+    from art_b200.models.weights import init_base_weights
+
+    ckpt = tmp_path / "Tiny-Qwen2-Instruct"
+    ckpt.mkdir()
+    hf = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 640, "hidden_size": 64,
+          "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 128,
+          "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 4096, "hidden_act": "silu",
+          "tie_word_embeddings": False, "sliding_window": 4096, "use_sliding_window": False, "torch_dtype": "bfloat16"}
+    (ckpt / "config.json").write_text(json.dumps(hf))
+    cfg = ModelConfig.from_pretrained_dir(str(ckpt))
+    assert cfg.name == "Tiny-Qwen2-Instruct" and cfg.head_dim == 16 and cfg.qkv_bias
+    weights = {k: v.contiguous() for k, v in init_base_weights(cfg, seed=0).items()}
+    save_file(weights, str(ckpt / "model.safetensors"))
+    bpe.save_pretrained(str(ckpt))
+    assert os.path.exists(ckpt / "tokenizer.json")
+
+    async def main():
+        backend = LocalBackend(in_process=True, path=str(tmp_path / "art"))
+        model = art.TrainableModel(name="agent", project="p", base_model=str(ckpt),
+                                   _internal_config={"init_args": {"max_seq_length": 2048},
+                                                     "engine_args": {"num_scheduler_steps": 4, "max_model_len": 512}})
+        try:
+            await model.register(backend)
+            client = model.openai_client()
+
+            async def rollout(i):
+                messages = [{"role": "user", "content": "say something"}]
+                r = await client.chat.completions.create(model=model.get_inference_name(), messages=messages, max_tokens=8, seed=i)
+                return art.Trajectory(messages_and_choices=[*messages, r.choices[0]], reward=float(i % 2))
+
+            groups = await art.gather_trajectory_groups([art.TrajectoryGroup(rollout(i) for i in range(4))], pbar_desc=None)
+            choice = groups[0].trajectories[0].messages_and_choices[-1]
+            ids = [int(t.token.split(":")[1]) for t in choice.logprobs.content]
+            assert all(0 <= t < 640 for t in ids)
+            assert bpe.decode([t for t in ids if t != bpe.eos_token_id]) == (choice.message.content or "")
+            await model.train(groups, config=art.TrainConfig(learning_rate=1e-3))
+            assert await model.get_step() == 1
+            out = tmp_path / "art" / "p" / "models" / "agent" / "0001"
+            cfg_a = json.load(open(out / "adapter_config.json"))
+            assert cfg_a["base_model_name_or_path"] == str(ckpt) and os.path.exists(out / "adapter_model.safetensors")
+        finally:
+            await model.openai_client().close()
+            for s in backend._services.values():
+                await s.shutdown()
+            backend.close()
+    asyncio.run(main())
