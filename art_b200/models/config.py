@@ -151,6 +151,8 @@ class ModelConfig:
         window = d.get("sliding_window")
         if window and d.get("use_sliding_window", mt == "mistral") and window < int(d.get("max_position_embeddings", 0) or 0):
             raise ValueError(f"sliding-window attention (window {window}) is not supported")
+        if mt == "qwen3_moe" and (d.get("mlp_only_layers") or int(d.get("decoder_sparse_step") or 1) != 1):
+            raise ValueError("sparse models with dense layers in between (mlp_only_layers, decoder_sparse_step != 1) are not supported")
         for k in ("attn_logit_softcapping", "final_logit_softcapping"):
             if d.get(k):
                 raise ValueError(f"{k} is not supported")

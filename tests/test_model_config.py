@@ -70,6 +70,8 @@ def test_unscaled_configuration_has_no_table_and_reference_model_follows_the_sca
     ({"model_type": "mistral", "sliding_window": 4096, "max_position_embeddings": 32768}, "sliding-window"),
     ({"rope_scaling": {"rope_type": "longrope", "factor": 4.0}}, "longrope"),
     ({"final_logit_softcapping": 30.0}, "softcapping"),
+    ({"model_type": "qwen3_moe", "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64, "mlp_only_layers": [0]}, "dense layers"),
+    ({"model_type": "qwen2_moe"}, "model_type"),
 ])
 def test_configurations_the_kernels_do_not_cover_are_refused(over, what):
     with pytest.raises(ValueError, match=what):
