@@ -390,6 +390,46 @@ _FORMATS = {
 }
 
 
+def int_range_regex(lo: int, hi: int) -> str:
+    """The decimal integers ``lo..hi`` (no leading zeros, no ``-0``) as a regular expression."""
+    if lo > hi:
+        raise ValueError(f"empty integer range {lo}..{hi}")
+
+    def group(alts: list[str]) -> str:
+        return alts[0] if len(alts) == 1 else "(" + "|".join(alts) + ")"
+
+    def same_len(a: str, b: str) -> list[str]:
+        """Digit strings of one length between ``a`` and ``b`` (inner digits: zeros allowed)."""
+        if a == b:
+            return [a]
+        if len(a) == 1:
+            return [f"[{a}-{b}]"]
+        n = len(a) - 1
+        if a[0] == b[0]:
+            return [a[0] + group(same_len(a[1:], b[1:]))]
+        out = [a[0] + group(same_len(a[1:], "9" * n))]
+        if int(b[0]) - int(a[0]) > 1:
+            out.append(f"[{int(a[0]) + 1}-{int(b[0]) - 1}][0-9]{{{n}}}")
+        out.append(b[0] + group(same_len("0" * n, b[1:])))
+        return out
+
+    def non_negative(a: int, b: int) -> list[str]:
+        out: list[str] = []
+        for nd in range(len(str(a)), len(str(b)) + 1):
+            first = max(a, 10 ** (nd - 1) if nd > 1 else 0)
+            last = min(b, 10 ** nd - 1)
+            if first <= last:
+                out += same_len(str(first), str(last))
+        return out
+
+    alts: list[str] = []
+    if lo < 0:
+        alts.append("-" + group(non_negative(max(1, -hi) if hi < 0 else 1, -lo)))
+    if hi >= 0:
+        alts += non_negative(max(lo, 0), hi)
+    return group(alts)
+
+
 def escape_literal(text: str) -> str:
     return "".join("\\" + c if c in r"\.[]{}()*+?|^$-" else c for c in text)
 
@@ -462,10 +502,9 @@ def schema_to_regex(schema: dict | bool | str, *, any_depth: int = 2, max_ref_de
         if t == "integer":
             lo, hi = s.get("minimum", s.get("exclusiveMinimum")), s.get("maximum", s.get("exclusiveMaximum"))
             if lo is not None and hi is not None:
-                # bounds limit the number of digits and the sign (not the exact range: that is left to validation)
-                digits = max(len(str(abs(int(lo)))), len(str(abs(int(hi)))))
-                sign = "-?" if lo < 0 <= hi else ("-" if hi < 0 else "")
-                return f"{sign}(0|[1-9][0-9]{{0,{digits - 1}}})"
+                lo_i = int(lo) + (1 if "exclusiveMinimum" in s and "minimum" not in s else 0)
+                hi_i = int(hi) - (1 if "exclusiveMaximum" in s and "maximum" not in s else 0)
+                return int_range_regex(lo_i, hi_i)
             if lo is not None and lo >= 0:
                 return "(0|[1-9][0-9]*)"
             return INTEGER

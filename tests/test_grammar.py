@@ -203,3 +203,89 @@ def test_engine_mixes_constrained_and_free_sequences_in_one_batch():
     assert re.fullmatch(r"-?[0-9]{1,3}", text_c) and c.finish_reason == "stop"
     assert all(lp <= 0 and lp == lp for lp in a.logprobs + c.logprobs)
     assert torch.isfinite(torch.tensor(a.logprobs)).all()
+
+
+def _random_accepted_text(dfa, rng, max_len=400):
+    """A random walk through the automaton that ends in an accepting state (None if it runs too long).  Bytes are
+    drawn from what the current state allows, preferring printable ASCII so that strings stay short and readable."""
+    state, out = 0, bytearray()
+    while len(out) < max_len:
+        if dfa.accepting[state] and (rng.random() < 0.3 or not (dfa.trans[state] >= 0).any()):
+            return bytes(out)
+        allowed = np.flatnonzero(dfa.trans[state] >= 0)
+        if len(allowed) == 0:
+            return bytes(out) if dfa.accepting[state] else None
+        closing = [b for b in allowed if b in b'"}],:']
+        pick = int(rng.choice(closing)) if closing and rng.random() < 0.35 else int(rng.choice(allowed))
+        out.append(pick)
+        state = int(dfa.trans[state, pick])
+    return None
+
+
+def test_everything_the_automaton_accepts_satisfies_the_schema():
+    """Soundness against an independent validator: random texts drawn from the automaton parse as JSON and validate
+    against the schema they were compiled from."""
+    jsonschema = pytest.importorskip("jsonschema")
+    schemas = [SCHEMA,
+               {"type": "array", "items": {"type": "object", "properties": {"id": {"type": "integer", "minimum": 1, "maximum": 500},
+                                                                              "tag": {"enum": ["x", "y"]}}, "required": ["id"]},
+                "minItems": 1, "maxItems": 3},
+               {"type": "object", "properties": {"when": {"type": "string", "format": "date"}, "ratio": {"type": "number"},
+                                                 "flags": {"type": "array", "items": {"type": "boolean"}}}, "required": ["when", "ratio"]},
+               {"anyOf": [{"type": "string", "maxLength": 5}, {"type": "integer"}, {"type": "null"}]}]
+    rng = random.Random(0)
+    for schema in schemas:
+        dfa = compile_regex(schema_to_regex(schema))
+        checked = 0
+        for _ in range(400):
+            raw = _random_accepted_text(dfa, rng)
+            if raw is None:
+                continue
+            try:
+                text = raw.decode("utf-8")
+            except UnicodeDecodeError:
+                continue                      # a random walk over bytes may stop inside a character
+            value = json.loads(text)
+            bounded = {k: v for k, v in schema.items()}
+            jsonschema.validate(value, bounded, format_checker=None)
+            checked += 1
+        assert checked > 50, (schema, checked)
+
+
+def test_instances_of_a_schema_are_accepted_in_compact_and_spaced_form():
+    """Completeness on random instances (built by a small generator): what satisfies the schema is accepted as
+    ``json.dumps`` writes it, with and without spaces."""
+    rng = random.Random(1)
+    dfa = compile_regex(schema_to_regex(SCHEMA))
+    for _ in range(200):
+        inst = {"name": "".join(rng.choice("abcé\"\\ \n") for _ in range(rng.randint(1, 8))), "age": rng.randint(0, 150)}
+        if rng.random() < 0.5:
+            inst["score"] = rng.choice([0, -1.5, 3.25e10, 7, -2e-3])
+        if rng.random() < 0.5:
+            inst["tags"] = ["".join(rng.choice("xyz ") for _ in range(rng.randint(0, 4))) for _ in range(rng.randint(1, 3))]
+        if rng.random() < 0.5:
+            inst["kind"] = rng.choice(["a", "b", 3, None])
+        if rng.random() < 0.3:
+            inst["address"] = {"zip": "".join(rng.choice("0123456789") for _ in range(5))}
+        if rng.random() < 0.3:
+            inst["alt"] = rng.choice([True, False, None])
+        for text in (json.dumps(inst, ensure_ascii=False), json.dumps(inst, ensure_ascii=False, separators=(",", ":")),
+                     json.dumps(inst)):
+            assert dfa.matches(text), text
+
+
+def test_integer_ranges_are_exact():
+    from art_b200.engine.grammar import int_range_regex
+
+    rng = random.Random(0)
+    for _ in range(120):
+        a = rng.randint(-1500, 1500)
+        b = a + rng.choice([0, 1, 5, 37, 999, 2600])
+        pat = re.compile(int_range_regex(a, b))
+        for v in list(range(a - 25, a + 25)) + list(range(b - 25, b + 25)) + [rng.randint(-5000, 5000) for _ in range(40)]:
+            assert bool(pat.fullmatch(str(v))) == (a <= v <= b), (a, b, v)
+        assert not pat.fullmatch("-0") and not pat.fullmatch("007") and not pat.fullmatch("+1")
+    dfa = compile_regex(schema_to_regex({"type": "integer", "minimum": -3, "maximum": 12}))
+    assert [v for v in range(-10, 20) if dfa.matches(str(v))] == list(range(-3, 13))
+    ex = compile_regex(schema_to_regex({"type": "integer", "exclusiveMinimum": 0, "exclusiveMaximum": 10}))
+    assert [v for v in range(-3, 13) if ex.matches(str(v))] == list(range(1, 10))
