@@ -289,3 +289,42 @@ def test_integer_ranges_are_exact():
     assert [v for v in range(-10, 20) if dfa.matches(str(v))] == list(range(-3, 13))
     ex = compile_regex(schema_to_regex({"type": "integer", "exclusiveMinimum": 0, "exclusiveMaximum": 10}))
     assert [v for v in range(-3, 13) if ex.matches(str(v))] == list(range(1, 10))
+
+
+def test_schemas_written_by_pydantic_models_are_understood():
+    """What ``client.beta.chat.completions.parse(response_format=Model)`` sends: ``$defs`` with references, enums,
+    bounded integers, ``Optional`` as ``anyOf``, literals, bounded lists, dictionaries as ``additionalProperties``."""
+    from enum import Enum
+    from typing import Literal, Optional
+
+    from pydantic import BaseModel, Field
+
+    class Color(str, Enum):
+        red = "red"
+        blue = "blue"
+
+    class Item(BaseModel):
+        sku: str = Field(max_length=8)
+        qty: int = Field(ge=1, le=20)
+        color: Color
+
+    class Order(BaseModel):
+        id: int
+        items: list[Item] = Field(min_length=1, max_length=2)
+        note: Optional[str] = None
+        kind: Literal["a", "b"] = "a"
+        price: float
+        meta: dict[str, int] = {}
+
+    dfa = compile_regex(schema_to_regex(Order.model_json_schema()))
+    full = Order(id=5, items=[Item(sku="ab", qty=3, color=Color.red)], note="hi", kind="b", price=2.5, meta={"x": 1})
+    short = Order(id=1, items=[Item(sku="z", qty=20, color="blue")] * 2, price=1)
+    for o in (full, short):
+        for text in (o.model_dump_json(), json.dumps(o.model_dump(mode="json"))):
+            assert dfa.matches(text), text
+            Order.model_validate_json(text)
+    for bad in ('{"id":5,"items":[],"price":1.0}',
+                '{"id":5,"items":[{"sku":"a","qty":21,"color":"red"}],"note":null,"kind":"a","price":1.0,"meta":{}}',
+                '{"id":5,"items":[{"sku":"a","qty":2,"color":"green"}],"note":null,"kind":"a","price":1.0,"meta":{}}',
+                '{"id":5,"items":[{"sku":"a","qty":2,"color":"red"}],"note":null,"kind":"c","price":1.0,"meta":{}}'):
+        assert not dfa.matches(bad), bad
