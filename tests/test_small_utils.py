@@ -173,3 +173,25 @@ def test_metrics_go_to_history_and_to_wandb_when_a_key_is_set(tmp_path, monkeypa
     assert calls["log"] == [({"val/reward": 0.5, "val/exception_rate": 0.0}, 0), ({"val/reward": 0.75}, 0)]
     rows = [json.loads(l) for l in open(tmp_path / "proj" / "models" / "prompted" / "history.jsonl")]
     assert [r["val/reward"] for r in rows] == [0.25, 0.5, 0.75] and all("recorded_at" in r for r in rows)
+
+
+def test_flat_adamw_on_cpu_equals_torch_adamw_with_gradient_clipping():
+    import torch
+
+    from art_b200.ops.optim import FlatAdamW
+
+    g = torch.Generator().manual_seed(0)
+    p0 = torch.randn(1000, generator=g)
+    params, grads = p0.clone(), torch.zeros(1000)
+    opt = FlatAdamW(params, grads, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1, max_grad_norm=0.1)
+    ref_p = torch.nn.Parameter(p0.clone())
+    ref = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    for step in range(5):
+        gr = torch.randn(1000, generator=g) * (0.001 if step == 2 else 1.0)      # one step below the clipping threshold
+        grads.copy_(gr)
+        ref_p.grad = gr.clone()
+        want_norm = torch.nn.utils.clip_grad_norm_([ref_p], 0.1)
+        ref.step()
+        got_norm = opt.step(1e-3)
+        assert float(got_norm) == pytest.approx(float(want_norm), rel=1e-5)
+        torch.testing.assert_close(params, ref_p.detach(), rtol=1e-5, atol=1e-7)
