@@ -611,7 +611,7 @@ class TokenMasker:
                 self._native = _NativeTrie(vocab)
             except (OSError, AttributeError):
                 self._native = None
-        self._cache: dict[tuple[int, int], np.ndarray] = {}
+        self._cache: dict[tuple[int, int], np.ndarray] = {}       # (automaton, state) -> bit-packed mask
         self._dfa_refs: dict[int, ByteDFA] = {}
 
     # -- Python twin of the native walk ----------------------------------------------------
@@ -654,16 +654,17 @@ class TokenMasker:
 
     def mask(self, dfa: ByteDFA, state: int) -> np.ndarray:
         key = (id(dfa), state)
-        m = self._cache.get(key)
-        if m is None:
-            self._dfa_refs[id(dfa)] = dfa          # keeps the id stable while its masks are cached
-            m = self._native.mask(dfa, state) if self._native is not None else self._py_mask(dfa, state)
-            if self.eos is not None and 0 <= self.eos < self.n:
-                m[self.eos] = bool(dfa.accepting[state])
-            if len(self._cache) > 4096:
-                self._cache.clear()
-                self._dfa_refs = {id(dfa): dfa}      # automata are pinned only while masks of theirs are cached
-            self._cache[key] = m
+        packed = self._cache.get(key)
+        if packed is not None:
+            return np.unpackbits(packed, count=self.n).view(bool)
+        self._dfa_refs[id(dfa)] = dfa          # keeps the id stable while its masks are cached
+        m = self._native.mask(dfa, state) if self._native is not None else self._py_mask(dfa, state)
+        if self.eos is not None and 0 <= self.eos < self.n:
+            m[self.eos] = bool(dfa.accepting[state])
+        if len(self._cache) > 4096:
+            self._cache.clear()
+            self._dfa_refs = {id(dfa): dfa}      # automata are pinned only while masks of theirs are cached
+        self._cache[key] = np.packbits(m)        # one bit per token: 19 KB per state for a 150 k vocabulary
         return m
 
 
