@@ -16,6 +16,7 @@ from __future__ import annotations
 import asyncio
 import itertools
 import logging
+import numbers
 import threading
 import os
 import time
@@ -280,7 +281,7 @@ class Engine:
                 self.recover()
             else:
                 raise RuntimeError("engine stopped after an error") from self.error
-        if not prompt_ids or not all(isinstance(t, int) for t in prompt_ids):
+        if len(prompt_ids) == 0 or not all(isinstance(t, numbers.Integral) for t in prompt_ids):
             raise ValueError("a prompt is a non-empty list of token ids")
         if len(prompt_ids) + 1 > self.max_model_len:
             raise ValueError(f"prompt of {len(prompt_ids)} tokens exceeds max_model_len={self.max_model_len}")
