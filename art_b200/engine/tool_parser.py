@@ -27,5 +27,5 @@ class HermesToolParser:
                           "function": {"name": name, "arguments": args if isinstance(args, str) else json.dumps(args)}})
         if not calls:
             return text, []
-        content = text[: text.index("<tool_call>")].strip()
+        content = text[: text.index("<tool_call>")]       # as written, like the reference's parser (no stripping)
         return (content or None), calls

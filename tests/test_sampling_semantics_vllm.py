@@ -51,3 +51,34 @@ def test_top_k_top_p_restriction_equals_the_librarys():
         p = float(torch.rand(1, generator=g) * 0.94 + 0.05)
         want = torch.isfinite(apply_top_k_top_p(x.clone(), torch.tensor([k]), torch.tensor([p]))[0])
         assert torch.equal(reference_restrict(x[0], k, p), want), (trial, k, p)
+
+
+def test_hermes_tool_calls_are_extracted_like_the_librarys_parser():
+    import json
+
+    try:
+        from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+        from transformers import PreTrainedTokenizerFast
+        from vllm.tool_parsers.hermes_tool_parser import Hermes2ProToolParser
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"inference library not importable: {type(e).__name__}")
+    from art_b200.engine.tool_parser import HermesToolParser
+
+    t = Tokenizer(models.BPE())
+    t.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    t.decoder = decoders.ByteLevel()
+    t.train_from_iterator(["tool call text"] * 4, trainers.BpeTrainer(
+        vocab_size=300, special_tokens=["<|end|>", "<tool_call>", "</tool_call>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    theirs = Hermes2ProToolParser(PreTrainedTokenizerFast(tokenizer_object=t, eos_token="<|end|>"))
+    ours = HermesToolParser()
+    texts = ['I will look.\n<tool_call>\n{"name": "search", "arguments": {"q": "fox", "n": 3}}\n</tool_call>',
+             '<tool_call>\n{"name": "a", "arguments": {}}\n</tool_call>\n<tool_call>\n{"name": "b", "arguments": {"x": [1, 2]}}\n</tool_call>',
+             'no tools here', '<tool_call>\n{"name": "broken", "arguments": {\n</tool_call>',
+             'text <tool_call>{"name": "inline", "arguments": {"k": "v"}}</tool_call>',
+             '<tool_call>\n{"name": "unterminated", "arguments": {"a": 1}}']
+    for text in texts:
+        r = theirs.extract_tool_calls(text, request=None)
+        want = (r.content, [(c.function.name, json.loads(c.function.arguments)) for c in r.tool_calls])
+        content, calls = ours.extract(text)
+        got = (content, [(c["function"]["name"], json.loads(c["function"]["arguments"])) for c in calls])
+        assert got == want, text
