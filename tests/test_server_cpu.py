@@ -115,7 +115,7 @@ def test_hermes_tool_parser():
     p = HermesToolParser()
     text = 'Let me check.\n<tool_call>\n{"name": "search", "arguments": {"q": "x"}}\n</tool_call>'
     content, calls = p.extract(text)
-    assert content == "Let me check." and calls[0]["function"]["name"] == "search"
+    assert content == "Let me check.\n" and calls[0]["function"]["name"] == "search"      # kept as written
     assert json.loads(calls[0]["function"]["arguments"]) == {"q": "x"}
     assert p.extract("no tools here") == ("no tools here", [])
     assert p.extract("<tool_call>not json</tool_call>")[1] == []
