@@ -16,7 +16,8 @@ LLAMA3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_fr
           "original_max_position_embeddings": 64}
 
 
-def _check(hf_config, hf_cls, positions=None, atol=2e-4):
+def _pair(hf_config, hf_cls):
+    """The library's model and this repository's configuration + weight dictionary, holding the same weights."""
     torch.manual_seed(0)
     hf_config._attn_implementation = "eager"
     model = hf_cls(hf_config).eval().float()
@@ -46,6 +47,11 @@ def _check(hf_config, hf_cls, positions=None, atol=2e-4):
     assert not missing.unexpected_keys and set(missing.missing_keys) <= {"lm_head.weight"}
     if "lm_head.weight" in missing.missing_keys:
         ours["lm_head.weight"] = ours["model.embed_tokens.weight"]
+    return model, cfg, ours, g
+
+
+def _check(hf_config, hf_cls, positions=None, atol=2e-4):
+    model, cfg, ours, g = _pair(hf_config, hf_cls)
     B, S = 2, 24
     tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=g)
     pos = torch.arange(S).expand(B, S) if positions is None else positions
@@ -101,3 +107,28 @@ def test_qwen3_moe_matches():
                           norm_topk_prob=True, rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=512,
                           decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False, attention_bias=False,
                           output_router_logits=False), Qwen3MoeForCausalLM, atol=5e-4)
+
+
+def test_engine_greedy_decoding_equals_the_librarys_generate():
+    """The rollout engine end to end (scheduler, block manager, reference runner) against ``generate`` of the library:
+    the same greedy continuation for several prompts batched together."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    from art_b200.engine.engine import Engine, SamplingParams
+    from art_b200.engine.kv_cache import BlockManager
+    from art_b200.engine.runner import ReferenceRunner
+    from art_b200.models.weights import LoraConfig
+
+    model, cfg, ours, g = _pair(Qwen2Config(vocab_size=300, hidden_size=64, intermediate_size=160, num_hidden_layers=2,
+                                            num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6, rms_norm_eps=1e-6,
+                                            max_position_embeddings=512, tie_word_embeddings=False), Qwen2ForCausalLM)
+    eng = Engine(ReferenceRunner(cfg, ours, LoraConfig(), max_loras=2), BlockManager(256, 4, True), eos_token_id=None,
+                 max_loras=2, num_scheduler_steps=4)
+    prompts = [torch.randint(0, 300, (n,), generator=g).tolist() for n in (5, 11, 3)]
+    seqs = [eng.add_request(p, SamplingParams(max_tokens=10, temperature=0.0)) for p in prompts]
+    while not all(s.finished for s in seqs):
+        eng.step()
+    for p, s in zip(prompts, seqs):
+        with torch.no_grad():
+            out = model.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0, eos_token_id=None)
+        assert s.output_ids == out[0, len(p):].tolist()
