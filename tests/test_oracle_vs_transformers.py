@@ -132,3 +132,38 @@ def test_engine_greedy_decoding_equals_the_librarys_generate():
         with torch.no_grad():
             out = model.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, pad_token_id=0, eos_token_id=None)
         assert s.output_ids == out[0, len(p):].tolist()
+
+
+def test_lora_adapters_mean_what_merging_them_into_the_weights_means():
+    """The PEFT convention: ``W + (alpha / r) * B @ A`` with ``lora_A`` [r, in] and ``lora_B`` [out, r].  The oracle with
+    an adapter gives the logits of the library's model with the merged weights."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    from art_b200.models.weights import LoraConfig, init_lora
+
+    model, cfg, ours, g = _pair(Qwen2Config(vocab_size=300, hidden_size=64, intermediate_size=160, num_hidden_layers=2,
+                                            num_attention_heads=4, num_key_value_heads=2, rope_theta=1e6, rms_norm_eps=1e-6,
+                                            max_position_embeddings=512, tie_word_embeddings=False), Qwen2ForCausalLM)
+    lcfg = LoraConfig(r=4, alpha=16)
+    lora = init_lora(cfg, lcfg, seed=3)
+    for k in lora:
+        lora[k] = torch.randn(lora[k].shape, generator=g) * 0.1
+    merged = dict(model.state_dict())
+    n = 0
+    for k, a in lora.items():
+        if ".lora_A." not in k:
+            continue
+        b = lora[k.replace(".lora_A.", ".lora_B.")]
+        name = k.replace("base_model.model.", "", 1).replace(".lora_A.weight", ".weight")
+        merged[name] = merged[name] + (lcfg.alpha / lcfg.r) * (b @ a)
+        n += 1
+    assert n == 2 * 7
+    model.load_state_dict(merged)
+    tokens = torch.randint(0, 300, (2, 16), generator=g)
+    ids = torch.zeros(2, 16, dtype=torch.long)
+    with torch.no_grad():
+        want = model(input_ids=tokens).logits
+        ref = ReferenceModel(cfg, ours, lora, lcfg)
+        got = ref.hidden_states(tokens, ids, ids, None, use_lora=True).float() @ ours["lm_head.weight"].float().t()
+        base = ref.hidden_states(tokens, ids, ids, None, use_lora=False).float() @ ours["lm_head.weight"].float().t()
+    assert (got - want).abs().max() < 2e-4 * want.abs().max() and (base - want).abs().max() > 1e-2
