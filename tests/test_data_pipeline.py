@@ -114,3 +114,54 @@ def test_packing_seed_makes_the_packed_rows_a_function_of_the_trajectories(tmp_p
     for k in ("tokens", "group_ids", "parent_ids", "advantages"):
         assert torch.equal(a[k], b[k])
     assert not torch.equal(a["group_ids"], c["group_ids"])      # other ids (and very likely another order)
+
+
+def test_packed_rows_give_the_log_probs_of_running_every_trajectory_alone():
+    """The point of the whole data path: tokenise, share prompts, pack, mask by ids, position by ``input_pos``.  The
+    log-prob of every trainable token in the packed row equals the log-prob of the same token when its trajectory is
+    run on its own as one ordinary causal sequence."""
+    from art_b200.models.config import PRESETS
+    from art_b200.models.reference import ReferenceModel
+    from art_b200.models.weights import init_base_weights
+
+    cfg = PRESETS["tiny"]
+    model = ReferenceModel(cfg, init_base_weights(cfg, seed=0))
+    groups = [art.TrajectoryGroup([traj(1.0, (300, 301, 302, 65)), traj(0.0, (303, 304)), traj(0.5, (66,))]),
+              art.TrajectoryGroup([traj(0.0, (310,), "another prompt"), traj(1.0, (311, 312, 313), "another prompt")])]
+    rng = random.Random(3)
+    res = list(tokenize_trajectory_groups(TOK, groups, False, rng))
+    packed = packed_tensors_from_tokenized_results(res, 256, pad_token_id=TOK.eos_token_id, rng=rng)
+    assert packed["tokens"].shape[0] == 1
+    tok, gid, pid, pos = (packed[k] for k in ("tokens", "group_ids", "parent_ids", "input_pos"))
+    with torch.no_grad():
+        h = model.hidden_states(tok, gid, pid, pos, use_lora=False)
+        lp_packed = torch.log_softmax(h[0].float() @ model.base["lm_head.weight"].float().t(), -1)
+    checked = 0
+    for r in res:
+        ids = torch.tensor([r.token_ids])
+        z = torch.zeros_like(ids)
+        with torch.no_grad():
+            ha = model.hidden_states(ids, z, z, None, use_lora=False)
+            lp_alone = torch.log_softmax(ha[0].float() @ model.base["lm_head.weight"].float().t(), -1)
+        n_train = sum(r.assistant_mask)
+        comp = r.token_ids[r.prompt_length:r.prompt_length + n_train]          # the sampled tokens follow the prompt
+        assert r.assistant_mask[r.prompt_length:r.prompt_length + n_train] == [1] * n_train
+        # locate them in the packed row: a run of trainable tokens with these ids that starts at this position
+        starts = [i for i in range(tok.shape[1] - len(comp) + 1)
+                  if tok[0, i:i + len(comp)].tolist() == comp and bool(packed["assistant_mask"][0, i:i + len(comp)].all())
+                  and int(pos[0, i]) == r.prompt_length]
+        assert len(starts) >= 1
+        s0 = starts[0]
+        for j, t in enumerate(comp):
+            # the token at packed index s0 + j is predicted from the index before it in the tree: the previous
+            # completion token, or the last prompt token (which is the last token of the parent group) for j = 0
+            if j == 0:
+                parent = int(pid[0, s0])
+                prev = max(i for i in range(tok.shape[1]) if int(gid[0, i]) == parent)
+            else:
+                prev = s0 + j - 1
+            want = lp_alone[r.prompt_length + j - 1, t]
+            got = lp_packed[prev, t]
+            assert abs(float(got - want)) < 2e-4, (r.prompt_id, j, float(got), float(want))
+            checked += 1
+    assert checked == sum(sum(r.assistant_mask) for r in res) == 4 + 2 + 1 + 3      # the mean-reward trajectory has no advantage and is dropped
