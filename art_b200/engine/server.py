@@ -579,6 +579,51 @@ class OpenAIServer:
 
             return {"version": __version__}
 
+        @app.post("/v1/load_lora_adapter")
+        async def load_lora_adapter(request: Request):
+            """Serve the adapter in the directory ``lora_path`` under the name ``lora_name`` (replacing an adapter of
+            that name), between two engine steps."""
+            srv._auth(request)
+            body = await request.json()
+            name, path = body.get("lora_name"), body.get("lora_path")
+            if not name or not path:
+                raise HTTPException(status_code=400, detail="lora_name and lora_path are required")
+            from ..models.peft_io import is_adapter_dir, load_adapter
+
+            if not is_adapter_dir(path):
+                raise HTTPException(status_code=404, detail=f"{path} holds no adapter_model.safetensors + adapter_config.json")
+
+            def swap():
+                state, _ = load_adapter(path, getattr(srv.engine.runner, "device", "cpu"))
+                srv.engine.pause()
+                try:
+                    srv.engine.set_adapter(name, state)
+                finally:
+                    srv.engine.resume()
+
+            try:
+                await asyncio.to_thread(swap)
+            except (RuntimeError, ValueError, KeyError) as e:
+                raise HTTPException(status_code=400, detail=f"cannot load the adapter: {e}") from e
+            return {"status": "ok", "lora_name": name}
+
+        @app.post("/v1/unload_lora_adapter")
+        async def unload_lora_adapter(request: Request):
+            srv._auth(request)
+            name = (await request.json()).get("lora_name")
+            if name not in srv.engine.adapters:
+                raise HTTPException(status_code=404, detail=f"no adapter named {name!r}")
+
+            def drop():
+                srv.engine.pause()
+                try:
+                    srv.engine.remove_adapter(name)
+                finally:
+                    srv.engine.resume()
+
+            await asyncio.to_thread(drop)
+            return {"status": "ok", "lora_name": name}
+
         @app.post("/detokenize")
         async def detokenize(request: Request):
             body = await request.json()

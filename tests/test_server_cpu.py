@@ -591,3 +591,36 @@ def test_stream_chunks_carry_a_scheduler_step_each_or_one_token_on_request(serve
     assert sum(a_sizes) == sum(b_sizes) == 8 and max(a_sizes) == 2 and b_sizes == [1] * 8
     assert a.choices[0].message.content == b.choices[0].message.content
     assert [t.token for t in a.choices[0].logprobs.content] == [t.token for t in b.choices[0].logprobs.content]
+
+
+def test_adapters_can_be_loaded_and_unloaded_while_serving(server, tmp_path):
+    """The runtime adapter endpoints: a directory in PEFT layout becomes a served model name; unloading frees it."""
+    from art_b200.models.peft_io import save_adapter
+
+    cfg = PRESETS["tiny"]
+    lcfg = LoraConfig()
+    lora = init_lora(cfg, lcfg, seed=9)
+    import torch
+    g = torch.Generator().manual_seed(1)
+    for k in lora:
+        if "lora_B" in k:
+            lora[k] = torch.randn(lora[k].shape, generator=g) * 0.3
+    path = str(tmp_path / "extra")
+    save_adapter(path, lora, lcfg, "tiny-base")
+
+    async def main():
+        async with client(server) as c:
+            body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0}
+            r = await c.post("/v1/chat/completions", json={**body, "model": "extra"})
+            assert r.status_code == 404
+            r = await c.post("/v1/load_lora_adapter", json={"lora_name": "extra", "lora_path": path})
+            assert r.status_code == 200, r.text
+            assert "extra" in [m["id"] for m in (await c.get("/v1/models")).json()["data"]]
+            a = (await c.post("/v1/chat/completions", json={**body, "model": "extra"})).json()["choices"][0]
+            b = (await c.post("/v1/chat/completions", json={**body, "model": "tiny-base"})).json()["choices"][0]
+            assert [e["logprob"] for e in a["logprobs"]["content"]] != [e["logprob"] for e in b["logprobs"]["content"]]
+            assert (await c.post("/v1/load_lora_adapter", json={"lora_name": "x", "lora_path": str(tmp_path / "nope")})).status_code == 404
+            assert (await c.post("/v1/unload_lora_adapter", json={"lora_name": "extra"})).status_code == 200
+            assert (await c.post("/v1/chat/completions", json={**body, "model": "extra"})).status_code == 404
+            assert (await c.post("/v1/unload_lora_adapter", json={"lora_name": "extra"})).status_code == 404
+    asyncio.run(main())
