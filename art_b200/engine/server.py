@@ -128,7 +128,7 @@ class IncrementalDecoder:
 class OpenAIServer:
     def __init__(self, engine: Engine, tokenizer, base_model_name: str, *, api_key: str | None = "default",
                  return_tokens_as_token_ids: bool = True, enable_auto_tool_choice: bool = True,
-                 tool_call_parser: str | None = "hermes", default_max_tokens: int = 256, peers: list[str] | None = None,
+                 tool_call_parser: str | None = "hermes", default_max_tokens: int | None = None, peers: list[str] | None = None,
                  response_role: str | None = None, chat_template: str | None = None, root_path: str | None = None,
                  cors: dict | None = None, middleware: list[str] | None = None, request_id_headers: bool = False,
                  fastapi_docs: bool = False, max_log_len: int | None = None, log_requests: bool = False,
@@ -289,7 +289,9 @@ class OpenAIServer:
         return {"token": token, "logprob": lp, "bytes": raw, "top_logprobs": alts}
 
     def _params(self, body: dict, prompt_len: int) -> SamplingParams:
-        max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
+        # without a limit in the request a completion may use the rest of the context, as with the reference's engine
+        max_tokens = (body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
+                      or self.engine.max_model_len)
         max_tokens = max(1, min(int(max_tokens), self.engine.max_model_len - prompt_len - 1))
         stop = body.get("stop")
         if isinstance(stop, str):
