@@ -289,6 +289,9 @@ class OpenAIServer:
         return {"token": token, "logprob": lp, "bytes": raw, "top_logprobs": alts}
 
     def _params(self, body: dict, prompt_len: int) -> SamplingParams:
+        n_req = int(body.get("n") or 1)
+        if body.get("use_beam_search") or int(body.get("best_of") or n_req) != n_req:
+            raise HTTPException(status_code=400, detail="beam search and best_of are not supported (sample n choices instead)")
         # without a limit in the request a completion may use the rest of the context, as with the reference's engine
         max_tokens = (body.get("max_completion_tokens") or body.get("max_tokens") or self.default_max_tokens
                       or self.engine.max_model_len)

@@ -624,3 +624,17 @@ def test_adapters_can_be_loaded_and_unloaded_while_serving(server, tmp_path):
             assert (await c.post("/v1/chat/completions", json={**body, "model": "extra"})).status_code == 404
             assert (await c.post("/v1/unload_lora_adapter", json={"lora_name": "extra"})).status_code == 404
     asyncio.run(main())
+
+
+def test_unsupported_search_modes_are_refused_not_ignored(server):
+    async def main():
+        async with client(server) as c:
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2}
+            assert (await c.post("/v1/chat/completions", json={**body, "use_beam_search": True})).status_code == 400
+            assert (await c.post("/v1/chat/completions", json={**body, "n": 2, "best_of": 4})).status_code == 400
+            assert (await c.post("/v1/chat/completions", json={**body, "n": 2, "best_of": 2})).status_code == 200
+            # no max_tokens: the rest of the context may be used (the tiny model stops at its context of 512)
+            r = await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": body["messages"], "ignore_eos": True})
+            u = r.json()["usage"]
+            assert u["prompt_tokens"] + u["completion_tokens"] >= 510 and r.json()["choices"][0]["finish_reason"] == "length"
+    asyncio.run(main())
