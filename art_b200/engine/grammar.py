@@ -26,7 +26,6 @@ from dataclasses import dataclass
 import numpy as np
 
 MAX_DFA_STATES = 50_000
-ALL_BYTES = (1 << 256) - 1
 
 
 # ------------------------------------------------------------------------------------------- regex -> AST
