@@ -50,6 +50,7 @@ class SamplingParams:
     logit_bias: dict[int, float] | None = None
     stream_events: bool = True             # False: only the final event is delivered (see Engine.complete)
     include_stop_str_in_output: bool = False   # keep the matched stop string at the end of the returned text
+    skip_special_tokens: bool = True       # the returned text leaves special tokens out (a matter of the server's decoding)
     min_tokens: int = 0                    # no end-of-sequence / stop token before this many tokens
     allowed_token_ids: list[int] | None = None   # only these ids may be drawn
     bad_words_ids: list[list[int]] | None = None  # token sequences that must not appear in the output

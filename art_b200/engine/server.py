@@ -326,6 +326,7 @@ class OpenAIServer:
                               guided_choice=body.get("guided_choice") or (body.get("structured_outputs") or {}).get("choice")
                               if not body.get("guided_regex") else None,
                               include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)),
+                              skip_special_tokens=bool(body.get("skip_special_tokens", True)),
                               min_tokens=max(0, min(int(body.get("min_tokens") or 0), max_tokens)),
                               allowed_token_ids=[int(t) for t in body["allowed_token_ids"]] if body.get("allowed_token_ids") else None,
                               bad_words_ids=self._bad_words(body.get("bad_words")))
@@ -454,7 +455,7 @@ class OpenAIServer:
         seq_params = SamplingParams(**{**params.__dict__, "n": 1,
                                        "seed": None if params.seed is None else params.seed + index})
         stops = params.stop or []
-        dec = IncrementalDecoder(self.tok) if stops else None
+        dec = IncrementalDecoder(self.tok, params.skip_special_tokens) if stops else None
         longest = max((len(x) for x in stops), default=0)
         agen = self.engine.generate_steps(prompt_ids, seq_params, adapter)
         try:
@@ -721,7 +722,7 @@ class OpenAIServer:
                     lpo = {"tokens": [srv._token_str(t) for t in ids], "token_logprobs": list(lps)}
                     if params.top_logprobs > 0:
                         lpo["top_logprobs"] = [{srv._token_str(t): l for t, l in (top or []) if t >= 0} for top in tops]
-                    text = srv._cut_at_stop(srv.tok.decode(ids, skip_special_tokens=True), params)
+                    text = srv._cut_at_stop(srv.tok.decode(ids, skip_special_tokens=params.skip_special_tokens), params)
                     if echo:        # the prompt comes back in front, its tokens with their log-probs (None for the first)
                         h_text, h_tokens, h_lps = heads[pi]
                         text = h_text + text
@@ -786,7 +787,7 @@ class OpenAIServer:
         tasks = [asyncio.create_task(pump(pi, i)) for pi in range(len(prompts)) for i in range(params.n)]
         live = len(tasks)
         bufs: dict[int, list[int]] = {k: [] for k in range(live)}
-        decs = {k: IncrementalDecoder(self.tok) for k in range(live)}
+        decs = {k: IncrementalDecoder(self.tok, params.skip_special_tokens) for k in range(live)}
         sent: dict[int, int] = {k: 0 for k in range(live)}
         completion_tokens = 0
         try:
@@ -937,7 +938,8 @@ class OpenAIServer:
 
     def _message_from(self, ids: list[int], tools_on: bool, reason: str, params: SamplingParams | None = None
                       ) -> tuple[dict, str]:
-        text = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=True), params)
+        skip = True if params is None else params.skip_special_tokens
+        text = self._cut_at_stop(self.tok.decode(self._strip_eos(ids), skip_special_tokens=skip), params)
         msg: dict[str, Any] = {"role": self.role, "content": text}
         if self.reasoning is not None:
             r, text = split_reasoning(text, self.reasoning)
@@ -1018,7 +1020,7 @@ class OpenAIServer:
         live = params.n
         completion_tokens = 0
         bufs: dict[int, list[int]] = {i: [] for i in range(params.n)}
-        decs = {i: IncrementalDecoder(self.tok) for i in range(params.n)}
+        decs = {i: IncrementalDecoder(self.tok, params.skip_special_tokens) for i in range(params.n)}
         sent_text: dict[int, int] = {i: 0 for i in range(params.n)}
         sent_reason: dict[int, int] = {i: 0 for i in range(params.n)}
         try:

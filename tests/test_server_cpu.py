@@ -638,3 +638,19 @@ def test_unsupported_search_modes_are_refused_not_ignored(server):
             u = r.json()["usage"]
             assert u["prompt_tokens"] + u["completion_tokens"] >= 510 and r.json()["choices"][0]["finish_reason"] == "length"
     asyncio.run(main())
+
+
+def test_special_tokens_can_be_kept_in_the_returned_text(server):
+    tok = server.tok
+
+    async def main():
+        async with client(server) as c:
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6,
+                    "allowed_token_ids": [tok.IM_START, ord("a")], "seed": 4, "temperature": 1.0}
+            plain = (await c.post("/v1/chat/completions", json=body)).json()["choices"][0]
+            kept = (await c.post("/v1/chat/completions", json={**body, "skip_special_tokens": False})).json()["choices"][0]
+            ids = [int(e["token"].split(":")[1]) for e in kept["logprobs"]["content"]]
+            assert ids == [int(e["token"].split(":")[1]) for e in plain["logprobs"]["content"]] and tok.IM_START in ids
+            assert "<|im_start|>" in kept["message"]["content"] and "<|im_start|>" not in plain["message"]["content"]
+            assert kept["message"]["content"].replace("<|im_start|>", "") == plain["message"]["content"]
+    asyncio.run(main())
