@@ -653,6 +653,8 @@ class OpenAIServer:
                 prompt_ids = srv._render_chat(body)
             except Exception as e:
                 raise HTTPException(status_code=400, detail=f"cannot render chat template: {e}") from e
+            if body.get("truncate_prompt_tokens"):              # keep the end of an over-long prompt
+                prompt_ids = prompt_ids[-int(body["truncate_prompt_tokens"]):]
             if len(prompt_ids) + 1 >= srv.engine.max_model_len:
                 raise HTTPException(status_code=400, detail=f"prompt has {len(prompt_ids)} tokens; the maximum context "
                                                             f"length is {srv.engine.max_model_len}")
@@ -691,6 +693,8 @@ class OpenAIServer:
             if idx:
                 return await srv._forward(idx, "/v1/completions", body, request)
             prompts = srv._completion_prompts(body.get("prompt", ""))
+            if body.get("truncate_prompt_tokens"):
+                prompts = [p[-int(body["truncate_prompt_tokens"]):] for p in prompts]
             params = srv._params(body, max(len(p) for p in prompts))
             for p in prompts:
                 if len(p) + 1 >= srv.engine.max_model_len:

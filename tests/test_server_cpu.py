@@ -654,3 +654,16 @@ def test_special_tokens_can_be_kept_in_the_returned_text(server):
             assert "<|im_start|>" in kept["message"]["content"] and "<|im_start|>" not in plain["message"]["content"]
             assert kept["message"]["content"].replace("<|im_start|>", "") == plain["message"]["content"]
     asyncio.run(main())
+
+
+def test_truncate_prompt_tokens_keeps_the_end_of_the_prompt(server):
+    async def main():
+        async with client(server) as c:
+            long = "x" * 700                                  # more than the context of 512
+            body = {"model": "tiny-base", "messages": [{"role": "user", "content": long}], "max_tokens": 2}
+            assert (await c.post("/v1/chat/completions", json=body)).status_code == 400
+            r = await c.post("/v1/chat/completions", json={**body, "truncate_prompt_tokens": 100})
+            assert r.status_code == 200 and r.json()["usage"]["prompt_tokens"] == 100
+            r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": long, "max_tokens": 2, "truncate_prompt_tokens": 64})
+            assert r.json()["usage"]["prompt_tokens"] == 64
+    asyncio.run(main())
