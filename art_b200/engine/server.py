@@ -232,6 +232,17 @@ class OpenAIServer:
         self._rr = (best + 1) % n
         return best
 
+    async def _fan_out(self, path: str, body: dict, request: Request) -> None:
+        """Repeats an administrative request (adapter load / unload) on every peer replica, so that whichever replica
+        a later completion request is routed to knows the adapter; raises with the first peer's refusal."""
+        if not self.peers or request.headers.get("x-art-routed"):
+            return
+        results = await asyncio.gather(*[self._forward(i + 1, path, {**body, "stream": False}, request)
+                                         for i in range(len(self.peers))])
+        for i, r in enumerate(results):
+            if r.status_code >= 400:
+                raise HTTPException(status_code=r.status_code, detail=f"replica {i + 1}: {bytes(r.body).decode(errors='replace')}")
+
     async def _forward(self, idx: int, path: str, body: dict, request: Request):
         """Send the request to peer ``idx - 1`` and pass its answer through."""
         import httpx
@@ -611,6 +622,7 @@ class OpenAIServer:
                 await asyncio.to_thread(swap)
             except (RuntimeError, ValueError, KeyError) as e:
                 raise HTTPException(status_code=400, detail=f"cannot load the adapter: {e}") from e
+            await srv._fan_out("/v1/load_lora_adapter", body, request)
             return {"status": "ok", "lora_name": name}
 
         @app.post("/v1/unload_lora_adapter")
@@ -628,6 +640,7 @@ class OpenAIServer:
                     srv.engine.resume()
 
             await asyncio.to_thread(drop)
+            await srv._fan_out("/v1/unload_lora_adapter", {"lora_name": name}, request)
             return {"status": "ok", "lora_name": name}
 
         @app.post("/detokenize")

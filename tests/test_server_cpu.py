@@ -667,3 +667,58 @@ def test_truncate_prompt_tokens_keeps_the_end_of_the_prompt(server):
             r = await c.post("/v1/completions", json={"model": "tiny-base", "prompt": long, "max_tokens": 2, "truncate_prompt_tokens": 64})
             assert r.json()["usage"]["prompt_tokens"] == 64
     asyncio.run(main())
+
+
+def test_adapter_loading_reaches_every_replica_behind_the_leader(tmp_path):
+    import socket
+
+    import torch
+
+    from art_b200.engine.server import serve
+    from art_b200.models.peft_io import save_adapter
+
+    cfg = PRESETS["tiny"]
+    base = init_base_weights(cfg, seed=0)
+    tok = ByteChatTokenizer(cfg.vocab_size)
+    lcfg = LoraConfig()
+    path = str(tmp_path / "extra")
+    save_adapter(path, init_lora(cfg, lcfg, seed=9), lcfg, "tiny-base")
+
+    def engine():
+        e = Engine(ReferenceRunner(cfg, base, lcfg, max_loras=2), BlockManager(128, 4, True), eos_token_id=tok.eos_token_id,
+                   max_loras=2, num_scheduler_steps=2, max_model_len=256)
+        e.start()
+        return e
+
+    def free_port():
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            return s.getsockname()[1]
+
+    async def main():
+        e0, e1 = engine(), engine()
+        p0, p1 = free_port(), free_port()
+        follower = OpenAIServer(e1, tok, "tiny-base")
+        leader = OpenAIServer(e0, tok, "tiny-base", peers=[f"http://127.0.0.1:{p1}"])
+        r0, r1 = asyncio.Event(), asyncio.Event()
+        tasks = [asyncio.create_task(serve(leader, "127.0.0.1", p0, ready=r0)), asyncio.create_task(serve(follower, "127.0.0.1", p1, ready=r1))]
+        await r0.wait()
+        await r1.wait()
+        try:
+            async with httpx.AsyncClient(headers={"Authorization": "Bearer default"}, timeout=60) as c:
+                r = await c.post(f"http://127.0.0.1:{p0}/v1/load_lora_adapter", json={"lora_name": "extra", "lora_path": path})
+                assert r.status_code == 200, r.text
+                assert "extra" in e0.adapters and "extra" in e1.adapters
+                for _ in range(4):      # wherever the leader routes it, the name is known
+                    r = await c.post(f"http://127.0.0.1:{p0}/v1/chat/completions",
+                                     json={"model": "extra", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2})
+                    assert r.status_code == 200, r.text
+                r = await c.post(f"http://127.0.0.1:{p0}/v1/unload_lora_adapter", json={"lora_name": "extra"})
+                assert r.status_code == 200 and "extra" not in e0.adapters and "extra" not in e1.adapters
+        finally:
+            for t in tasks:
+                t.cancel()
+            await asyncio.gather(*tasks, return_exceptions=True)
+            e0.shutdown()
+            e1.shutdown()
+    asyncio.run(main())
