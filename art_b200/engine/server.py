@@ -577,6 +577,24 @@ class OpenAIServer:
                 m["replica_load"] = list(srv._load)
             return m
 
+        @app.get("/metrics/prometheus")
+        async def metrics_prometheus():
+            """The numeric entries of ``/metrics`` in the Prometheus text format (names prefixed ``art_b200_``; counters
+            where the value only grows)."""
+            from fastapi.responses import PlainTextResponse
+
+            counters = {"prompt_tokens", "generated_tokens", "preemptions", "recoveries", "decode_steps", "prefill_steps",
+                        "prefix_queries", "prefix_hits", "runner_seconds", "step_seconds"}
+            lines = []
+            for k, v in srv.engine.metrics().items():
+                if isinstance(v, bool) or not isinstance(v, (int, float)):
+                    continue
+                name = f"art_b200_{k}" + ("_total" if k in counters else "")
+                lines += [f"# TYPE {name} {'counter' if k in counters else 'gauge'}", f"{name} {float(v):.10g}"]
+            for i, n in enumerate(srv._load):
+                lines.append(f'art_b200_requests_in_flight{{replica="{i}"}} {n}')
+            return PlainTextResponse("\n".join(lines) + "\n", media_type="text/plain; version=0.0.4")
+
         @app.get("/v1/models")
         async def models(request: Request):
             srv._auth(request)

@@ -722,3 +722,17 @@ def test_adapter_loading_reaches_every_replica_behind_the_leader(tmp_path):
             e0.shutdown()
             e1.shutdown()
     asyncio.run(main())
+
+
+def test_prometheus_metrics_parse(server):
+    from prometheus_client.parser import text_string_to_metric_families
+
+    async def main():
+        async with client(server) as c:
+            await c.post("/v1/chat/completions", json={"model": "tiny-base", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+            r = await c.get("/metrics/prometheus")
+            assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+            fams = {f.name: f for f in text_string_to_metric_families(r.text)}
+            assert fams["art_b200_generated_tokens"].type == "counter" and fams["art_b200_generated_tokens"].samples[0].value >= 3
+            assert fams["art_b200_kv_free_blocks"].type == "gauge" and "art_b200_requests_in_flight" in fams
+    asyncio.run(main())
