@@ -128,6 +128,9 @@ class EngineStats:
     prefill_steps: int = 0
     decode_steps: int = 0
     preemptions: int = 0
+    finished_requests: int = 0
+    ttft_s: float = 0.0         # sum over requests: arrival -> first token
+    request_s: float = 0.0      # sum over finished requests: arrival -> last token
     runner_s: float = 0.0       # wall time inside runner.prefill / runner.decode (device work + its host staging)
     step_s: float = 0.0         # wall time of scheduler steps that did work (runner time included)
     started: float = field(default_factory=time.monotonic)
@@ -407,8 +410,12 @@ class Engine:
             reason = "stop"
         elif len(seq.output_ids) >= p.max_tokens or len(seq.prompt_ids) + len(seq.output_ids) >= self.max_model_len:
             reason = "length"
+        if len(seq.output_ids) == 1:
+            self.stats.ttft_s += time.monotonic() - seq.arrival
         if reason:
             seq.finished, seq.finish_reason = True, reason
+            self.stats.finished_requests += 1
+            self.stats.request_s += time.monotonic() - seq.arrival
         if seq.loop is not None and (p.stream_events or seq.finished):
             # delivered by _flush_events at the end of the scheduler step: one wake-up of the event loop per step and
             # one queue item per sequence, however many sequences and decode steps the step covered
@@ -722,7 +729,9 @@ class Engine:
         dt = max(1e-9, time.monotonic() - self.stats.started)
         return {"running": len(self.running), "waiting": len(self.waiting), "prompt_tokens": self.stats.prompt_tokens,
                 "generated_tokens": self.stats.generated_tokens, "preemptions": self.stats.preemptions,
-                "recoveries": self.recoveries,
+                "recoveries": self.recoveries, "finished_requests": self.stats.finished_requests,
+                "mean_time_to_first_token_s": self.stats.ttft_s / max(1, self.stats.finished_requests + len(self.running)),
+                "mean_request_s": self.stats.request_s / max(1, self.stats.finished_requests),
                 "kv_free_blocks": self.bm.num_free, "kv_total_blocks": self.bm.num_blocks,
                 "kv_utilisation": 1.0 - self.bm.num_free / self.bm.num_blocks, "tokens_per_s": self.stats.generated_tokens / dt,
                 "decode_steps": self.stats.decode_steps, "prefill_steps": self.stats.prefill_steps,

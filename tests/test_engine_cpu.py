@@ -385,3 +385,13 @@ def test_a_failing_prefill_reaches_the_request_that_was_being_prefilled(tiny):
         assert len(seq.output_ids) == 4
     finally:
         eng.shutdown()
+
+
+def test_latency_statistics_in_the_metrics(tiny):
+    cfg, base = tiny
+    eng = make_engine(cfg, base, num_scheduler_steps=2)
+    seqs = [eng.add_request([1, 2, 3 + i], SamplingParams(max_tokens=5, temperature=0.0)) for i in range(3)]
+    while not all(s.finished for s in seqs):
+        eng.step()
+    m = eng.metrics()
+    assert m["finished_requests"] == 3 and 0 < m["mean_time_to_first_token_s"] <= m["mean_request_s"]
