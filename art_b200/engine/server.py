@@ -133,7 +133,8 @@ class OpenAIServer:
                  cors: dict | None = None, middleware: list[str] | None = None, request_id_headers: bool = False,
                  fastapi_docs: bool = False, max_log_len: int | None = None, log_requests: bool = False,
                  prompt_tokens_details: bool = False, reasoning_parser: str | None = None,
-                 load_tracking: bool = False, stream_per_token: bool = False):
+                 load_tracking: bool = False, stream_per_token: bool = False, max_logprobs: int = 20,
+                 extra_base_names: list[str] | None = None):
         """``peers``: base URLs of further replicas of the same model (other GPUs of the node).  This server then
         spreads ``/v1/chat/completions`` and ``/v1/completions`` over itself and the peers, least loaded first,
         passing a peer's answer (JSON or event stream) through unchanged; a client only ever sees this one URL.
@@ -175,13 +176,16 @@ class OpenAIServer:
             raise ValueError(f"unknown reasoning parser {reasoning_parser!r}; known: {sorted(_REASONING_TAGS)}")
         self.load_tracking = load_tracking
         self.stream_per_token = stream_per_token
+        self.max_logprobs = int(max_logprobs)                     # largest top_logprobs a request may ask for
+        self.base_names = [base_model_name] + [n for n in (extra_base_names or []) if n != base_model_name]
         self._tok_fields: dict[int, tuple[str, list[int]]] = {}
         self.app = self._build()
 
     @classmethod
     def from_server_args(cls, engine: Engine, tokenizer, base_model_name: str, sargs: dict, *,
                          log_requests: bool = False, peers: list[str] | None = None,
-                         stream_per_token: bool = False) -> "OpenAIServer":
+                         stream_per_token: bool = False, max_logprobs: int = 20,
+                         extra_base_names: list[str] | None = None) -> "OpenAIServer":
         """Builds the server from a ``ServerArgs`` dictionary (the keys that concern the HTTP listener itself, host,
         port, TLS files and log level, are read by :func:`serve_kwargs`)."""
         def jlist(key: str):
@@ -206,7 +210,8 @@ class OpenAIServer:
                    max_log_len=sargs.get("max_log_len"), log_requests=log_requests,
                    prompt_tokens_details=bool(sargs.get("enable_prompt_tokens_details", False)),
                    reasoning_parser=(sargs.get("reasoning_parser") or "deepseek_r1") if sargs.get("enable_reasoning") else None,
-                   load_tracking=bool(sargs.get("enable_server_load_tracking", False)), stream_per_token=stream_per_token)
+                   load_tracking=bool(sargs.get("enable_server_load_tracking", False)), stream_per_token=stream_per_token,
+                   max_logprobs=max_logprobs, extra_base_names=extra_base_names)
 
     # -- helpers ------------------------------------------------------------------------------------
     def _auth(self, request: Request) -> None:
@@ -218,7 +223,7 @@ class OpenAIServer:
 
     def _route(self, model: str | None) -> str | None:
         """Adapter name for ``model`` (None = base model)."""
-        if model is None or model == self.base_model_name:
+        if model is None or model in self.base_names:
             return None
         if model in self.engine.adapters:
             return model
@@ -315,8 +320,8 @@ class OpenAIServer:
         if top_lp is None and isinstance(body.get("logprobs"), int) and not isinstance(body.get("logprobs"), bool):
             top_lp = body["logprobs"]                       # /v1/completions spelling
         top_lp = int(top_lp or 0)
-        if not 0 <= top_lp <= 20:
-            raise HTTPException(status_code=400, detail="top_logprobs must be between 0 and 20")
+        if not 0 <= top_lp <= self.max_logprobs:
+            raise HTTPException(status_code=400, detail=f"top_logprobs must be between 0 and {self.max_logprobs}")
         bias = body.get("logit_bias") or None
         if bias:
             try:
@@ -598,10 +603,10 @@ class OpenAIServer:
         @app.get("/v1/models")
         async def models(request: Request):
             srv._auth(request)
-            names = [srv.base_model_name] + list(srv.engine.adapters)
+            names = srv.base_names + list(srv.engine.adapters)
             return {"object": "list", "data": [{"id": n, "object": "model", "created": _now(), "owned_by": "art-b200",
                                                 "root": srv.base_model_name,
-                                                "parent": None if n == srv.base_model_name else srv.base_model_name}
+                                                "parent": None if n in srv.base_names else srv.base_model_name}
                                                for n in names]}
 
         @app.get("/ping")

@@ -53,6 +53,10 @@ def shard_rows(packed: dict, keys, start: int, count: int, n_rows: int) -> dict:
     return rows
 
 
+def _as_list(x) -> list[str]:
+    return [] if not x else ([x] if isinstance(x, str) else list(x))
+
+
 def node_layout(config: dev.InternalModelConfig) -> tuple[int, int]:
     """(tensor_parallel_size, data_parallel_size) a model's configuration asks for; (1, 1) = one GPU.
 
@@ -318,7 +322,9 @@ class ModelService:
         eargs = cfg.get("engine_args", {})
         server = OpenAIServer.from_server_args(st.engine, st.tokenizer, self.base_model, sargs, peers=peers,
                                                log_requests=eargs.get("disable_log_requests") is False,
-                                               stream_per_token=bool(eargs.get("multi_step_stream_outputs", False)))
+                                               stream_per_token=bool(eargs.get("multi_step_stream_outputs", False)),
+                                               max_logprobs=int(eargs.get("max_logprobs") or 20),
+                                               extra_base_names=_as_list(eargs.get("served_model_name")))
         self._server = server
         await self.stop_openai_server()
         ready = asyncio.Event()

@@ -736,3 +736,19 @@ def test_prometheus_metrics_parse(server):
             assert fams["art_b200_generated_tokens"].type == "counter" and fams["art_b200_generated_tokens"].samples[0].value >= 3
             assert fams["art_b200_kv_free_blocks"].type == "gauge" and "art_b200_requests_in_flight" in fams
     asyncio.run(main())
+
+
+def test_served_model_names_and_the_logprob_limit(server):
+    srv = OpenAIServer(server.engine, server.tok, "tiny-base", extra_base_names=["alias-a", "tiny-base"], max_logprobs=3)
+
+    async def main():
+        async with client(srv) as c:
+            ids = [m["id"] for m in (await c.get("/v1/models")).json()["data"]]
+            assert ids[:2] == ["tiny-base", "alias-a"]
+            body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0}
+            a = (await c.post("/v1/chat/completions", json={**body, "model": "alias-a"})).json()["choices"][0]["message"]["content"]
+            b = (await c.post("/v1/chat/completions", json={**body, "model": "tiny-base"})).json()["choices"][0]["message"]["content"]
+            assert a == b
+            assert (await c.post("/v1/chat/completions", json={**body, "model": "tiny-base", "logprobs": True, "top_logprobs": 4})).status_code == 400
+            assert (await c.post("/v1/chat/completions", json={**body, "model": "tiny-base", "logprobs": True, "top_logprobs": 3})).status_code == 200
+    asyncio.run(main())
